@@ -1,0 +1,230 @@
+// Attention over the paged cache, for a ragged batch of prompt portions and
+// single decoded tokens.
+//
+//  gb_qk_norm_rope_store: per-head RMSNorm of q and k (optional), rotary
+//    position encoding of q and k (optional; half-split or adjacent pairs),
+//    q rewritten in place, k and v written into the pages of their positions.
+//  gb_paged_attention: for every (token, head) softmax((q.K_j)*scale) V_j over
+//    the visible keys j <= pos (and j > pos - window), read through the
+//    request's block table.
+//
+// Formulas (MisterTK/gibbs): per-head norm arch/lib/transformer.json5:22-24,
+// 55-58; RoPE src/graph/cpu.rs:632-697 (angle = (float)pos * inv_freq[j] in
+// 32-bit); attention src/graph/cpu.rs:826-951 (keys are written first, query
+// head h reads kv head h / (heads/kv_heads), max-subtracted softmax).
+//
+// Page layout: [n_pages, kv_heads, page_size, head_dim]; position p of a
+// request lives in page block_table[request][p / page_size] at row
+// p % page_size.  A page id outside 0..n_pages-1 is never dereferenced: the
+// access is skipped and *status is set to a nonzero code.
+#include "common.cuh"
+
+namespace {
+
+enum { STATUS_BAD_PAGE_WRITE = 1, STATUS_BAD_PAGE_READ = 2 };
+
+template <typename T>
+__global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, long long ld, const float* __restrict__ q_gain,
+                                          const float* __restrict__ k_gain, float eps,
+                                          const float* __restrict__ inv_freq, int rotary_dim, int adjacent,
+                                          const int* __restrict__ tok_req, const int* __restrict__ tok_pos,
+                                          const int* __restrict__ block_table, int bt_stride, int page_size,
+                                          T* __restrict__ k_pages, T* __restrict__ v_pages, int n_pages,
+                                          int n_tokens, int heads, int kv_heads, int hd, int write_kv,
+                                          int* __restrict__ status) {
+  const int lane = threadIdx.x & 31;
+  const int slots = heads + (write_kv ? 2 * kv_heads : 0);
+  const long long idx = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (idx >= (long long)n_tokens * slots) return;
+  const int t = (int)(idx / slots), slot = (int)(idx - (long long)t * slots);
+  const int pos = tok_pos[t];
+  // columns of the fused row: [q heads | k heads | v heads]
+  T* src = qkv + (size_t)t * ld + (size_t)slot * hd;
+  const bool is_q = slot < heads;
+  const bool is_k = !is_q && slot < heads + kv_heads;
+  const int kvh = is_q ? 0 : (is_k ? slot - heads : slot - heads - kv_heads);
+
+  T* dst = src;  // q in place
+  if (!is_q) {
+    const int page = block_table[(size_t)tok_req[t] * bt_stride + pos / page_size];
+    if (page < 0 || page >= n_pages) {
+      if (lane == 0) atomicExch(status, STATUS_BAD_PAGE_WRITE);
+      return;
+    }
+    T* pages = is_k ? k_pages : v_pages;
+    dst = pages + (((size_t)page * kv_heads + kvh) * page_size + pos % page_size) * hd;
+  }
+  if (!is_q && !is_k) {  // v: plain copy
+    for (int d = lane; d < hd; d += 32) dst[d] = src[d];
+    return;
+  }
+  const float* gain = is_q ? q_gain : k_gain;
+  float scale = 1.f;
+  if (gain) {
+    float ss = 0.f;
+    for (int d = lane; d < hd; d += 32) {
+      const float v = to_f32(src[d]);
+      ss += v * v;
+    }
+    ss = warp_sum(ss);
+    scale = 1.0f / sqrtf(ss / (float)hd + eps);
+  }
+  const int half = inv_freq ? rotary_dim / 2 : 0;
+  for (int j = lane; j < half; j += 32) {
+    const int i0 = adjacent ? 2 * j : j;
+    const int i1 = adjacent ? 2 * j + 1 : j + half;
+    float a = to_f32(src[i0]), b = to_f32(src[i1]);
+    if (gain) {
+      a = a * scale * gain[i0];
+      b = b * scale * gain[i1];
+    }
+    const float ang = (float)pos * inv_freq[j];
+    const float c = cosf(ang), s = sinf(ang);
+    dst[i0] = from_f32<T>(a * c - b * s);
+    dst[i1] = from_f32<T>(a * s + b * c);
+  }
+  for (int d = 2 * half + lane; d < hd; d += 32) {
+    float a = to_f32(src[d]);
+    if (gain) a = a * scale * gain[d];
+    dst[d] = from_f32<T>(a);
+  }
+}
+
+// One warp per (token, head).  Lane l takes the keys lo + l, lo + l + 32, ...
+// with its own running (max, sum, output); the 32 partial states are merged at
+// the end.  Which keys a lane takes depends on the query's position only, so
+// the result is the same however the batch was cut.
+template <typename T, int HD_MAX>
+__global__ void __launch_bounds__(128)
+paged_attention_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k_pages,
+                       const T* __restrict__ v_pages, const int* __restrict__ block_table, int bt_stride,
+                       int page_size, int n_pages, const int* __restrict__ tok_req,
+                       const int* __restrict__ tok_pos, T* __restrict__ out, long long ldo, int n_tokens,
+                       int heads, int kv_heads, int hd, float scale, int window, int* __restrict__ status) {
+  __shared__ float qs[4][HD_MAX];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long idx = (long long)blockIdx.x * 4 + warp;
+  if (idx >= (long long)n_tokens * heads) return;
+  const int t = (int)(idx / heads), h = (int)(idx - (long long)t * heads);
+  const int kvh = h / (heads / kv_heads);
+  const int pos = tok_pos[t];
+  const int* bt = block_table + (size_t)tok_req[t] * bt_stride;
+  for (int d = lane; d < hd; d += 32) qs[warp][d] = to_f32(q[(size_t)t * ldq + (size_t)h * hd + d]);
+  __syncwarp();
+
+  float m = -INFINITY, l = 0.f;
+  float o[HD_MAX];
+#pragma unroll
+  for (int d = 0; d < HD_MAX; ++d) o[d] = 0.f;
+
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  for (int j = lo + lane; j <= pos; j += 32) {
+    const int page = bt[j / page_size];
+    if (page < 0 || page >= n_pages) {
+      atomicExch(status, STATUS_BAD_PAGE_READ);
+      continue;
+    }
+    const size_t row = (((size_t)page * kv_heads + kvh) * page_size + j % page_size) * hd;
+    const T* kp = k_pages + row;
+    const T* vp = v_pages + row;
+    float dot = 0.f;
+#pragma unroll
+    for (int d = 0; d < HD_MAX; ++d)
+      if (d < hd) dot = fmaf(qs[warp][d], to_f32(kp[d]), dot);
+    const float s = dot * scale;
+    const float m_new = fmaxf(m, s);
+    const float corr = expf(m - m_new);
+    const float p = expf(s - m_new);
+    l = l * corr + p;
+#pragma unroll
+    for (int d = 0; d < HD_MAX; ++d)
+      if (d < hd) o[d] = o[d] * corr + p * to_f32(vp[d]);
+    m = m_new;
+  }
+
+  const float m_all = warp_max(m);
+  const float f = (m == -INFINITY) ? 0.f : expf(m - m_all);
+  const float l_all = warp_sum(l * f);
+  const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+  T* dst = out + (size_t)t * ldo + (size_t)h * hd;
+#pragma unroll
+  for (int d = 0; d < HD_MAX; ++d) {
+    if (d < hd) {
+      const float v = warp_sum(o[d] * f);
+      if ((d & 31) == lane) dst[d] = from_f32<T>(v * inv);
+    }
+  }
+}
+
+template <typename T>
+int launch_attention(const void* q, long long ldq, const void* k_pages, const void* v_pages, const int* block_table,
+                     int bt_stride, int page_size, int n_pages, const int* tok_req, const int* tok_pos, void* out,
+                     long long ldo, int n_tokens, int heads, int kv_heads, int hd, float scale, int window,
+                     int* status, cudaStream_t stream) {
+  const long long warps = (long long)n_tokens * heads;
+  const int blocks = gb_div_up(warps, 4);
+#define GB_ATTN(HD)                                                                                              \
+  paged_attention_kernel<T, HD><<<blocks, 128, 0, stream>>>((const T*)q, ldq, (const T*)k_pages, (const T*)v_pages, \
+                                                            block_table, bt_stride, page_size, n_pages, tok_req, \
+                                                            tok_pos, (T*)out, ldo, n_tokens, heads, kv_heads, hd, \
+                                                            scale, window, status)
+  if (hd <= 32) GB_ATTN(32);
+  else if (hd <= 64) GB_ATTN(64);
+  else if (hd <= 128) GB_ATTN(128);
+  else GB_ATTN(256);
+#undef GB_ATTN
+  return 0;
+}
+
+}  // namespace
+
+GB_API int gb_qk_norm_rope_store(void* qkv, int dtype, long long ld, const float* q_gain, const float* k_gain,
+                                 float eps, const float* inv_freq, int rotary_dim, int adjacent, const int* tok_req,
+                                 const int* tok_pos, const int* block_table, int bt_stride, int page_size,
+                                 void* k_pages, void* v_pages, int n_pages, int n_tokens, int heads, int kv_heads,
+                                 int hd, int write_kv, int* status, cudaStream_t stream) {
+  if (n_tokens <= 0) return GB_OK;
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0)
+    GB_FAIL(GB_ERR_ARG, "gb_qk_norm_rope_store: %d heads over %d kv heads", heads, kv_heads);
+  if (inv_freq && (rotary_dim % 2 != 0 || rotary_dim > hd || rotary_dim <= 0))
+    GB_FAIL(GB_ERR_ARG, "gb_qk_norm_rope_store: rotary_dim %d for head_dim %d", rotary_dim, hd);
+  if (page_size <= 0) GB_FAIL(GB_ERR_ARG, "gb_qk_norm_rope_store: page_size %d", page_size);
+  const int slots = heads + (write_kv ? 2 * kv_heads : 0);
+  const long long warps = (long long)n_tokens * slots;
+  const int blocks = gb_div_up(warps, 4);
+  if (dtype == GB_F32)
+    qk_norm_rope_store_kernel<float><<<blocks, 128, 0, stream>>>(
+        (float*)qkv, ld, q_gain, k_gain, eps, inv_freq, rotary_dim, adjacent, tok_req, tok_pos, block_table,
+        bt_stride, page_size, (float*)k_pages, (float*)v_pages, n_pages, n_tokens, heads, kv_heads, hd, write_kv,
+        status);
+  else if (dtype == GB_BF16)
+    qk_norm_rope_store_kernel<bf16><<<blocks, 128, 0, stream>>>(
+        (bf16*)qkv, ld, q_gain, k_gain, eps, inv_freq, rotary_dim, adjacent, tok_req, tok_pos, block_table,
+        bt_stride, page_size, (bf16*)k_pages, (bf16*)v_pages, n_pages, n_tokens, heads, kv_heads, hd, write_kv,
+        status);
+  else
+    GB_FAIL(GB_ERR_ARG, "gb_qk_norm_rope_store: unknown dtype %d", dtype);
+  GB_CHECK_LAUNCH("gb_qk_norm_rope_store");
+  return GB_OK;
+}
+
+GB_API int gb_paged_attention(const void* q, int dtype, long long ldq, const void* k_pages, const void* v_pages,
+                              const int* block_table, int bt_stride, int page_size, int n_pages, const int* tok_req,
+                              const int* tok_pos, void* out, long long ldo, int n_tokens, int heads, int kv_heads,
+                              int hd, float scale, int window, int* status, cudaStream_t stream) {
+  if (n_tokens <= 0) return GB_OK;
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0)
+    GB_FAIL(GB_ERR_ARG, "gb_paged_attention: %d heads over %d kv heads", heads, kv_heads);
+  if (hd <= 0 || hd > 256) GB_FAIL(GB_ERR_ARG, "gb_paged_attention: head_dim %d outside 1..256", hd);
+  if (page_size <= 0) GB_FAIL(GB_ERR_ARG, "gb_paged_attention: page_size %d", page_size);
+  if (dtype == GB_F32)
+    launch_attention<float>(q, ldq, k_pages, v_pages, block_table, bt_stride, page_size, n_pages, tok_req, tok_pos,
+                            out, ldo, n_tokens, heads, kv_heads, hd, scale, window, status, stream);
+  else if (dtype == GB_BF16)
+    launch_attention<bf16>(q, ldq, k_pages, v_pages, block_table, bt_stride, page_size, n_pages, tok_req, tok_pos,
+                           out, ldo, n_tokens, heads, kv_heads, hd, scale, window, status, stream);
+  else
+    GB_FAIL(GB_ERR_ARG, "gb_paged_attention: unknown dtype %d", dtype);
+  GB_CHECK_LAUNCH("gb_paged_attention");
+  return GB_OK;
+}

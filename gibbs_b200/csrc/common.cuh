@@ -1,0 +1,80 @@
+// Shared helpers of the gibbs_b200 kernels: element types, 32-bit conversion,
+// warp reductions and the C-ABI error convention.
+//
+// Every exported function returns 0 on success and a negative code otherwise;
+// gb_last_error() gives the message of the last failure on the calling thread.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define GB_API extern "C" __attribute__((visibility("default")))
+
+enum GbDtype : int { GB_F32 = 0, GB_BF16 = 1 };
+
+enum GbStatus : int {
+  GB_OK = 0,
+  GB_ERR_ARG = -1,      // a size or option the kernel does not take
+  GB_ERR_CUDA = -2,     // the launch failed
+  GB_ERR_TIMEOUT = -3,  // a bounded device-side wait ran out
+};
+
+char* gb_error_buffer();  // thread-local, 512 bytes (defined in errors.cu)
+
+#define GB_FAIL(code, ...)                              \
+  do {                                                  \
+    snprintf(gb_error_buffer(), 512, __VA_ARGS__);      \
+    return (code);                                      \
+  } while (0)
+
+#define GB_CHECK_LAUNCH(name)                                                        \
+  do {                                                                               \
+    cudaError_t e_ = cudaGetLastError();                                             \
+    if (e_ != cudaSuccess) GB_FAIL(GB_ERR_CUDA, "%s: %s", name, cudaGetErrorString(e_)); \
+  } while (0)
+
+#define GB_CUDA(call)                                                                \
+  do {                                                                               \
+    cudaError_t e_ = (call);                                                         \
+    if (e_ != cudaSuccess) GB_FAIL(GB_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e_)); \
+  } while (0)
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum for blocks of up to 1024 threads; `scratch` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  float t = (threadIdx.x < nw) ? scratch[threadIdx.x] : 0.f;
+  if (warp == 0) {
+    t = warp_sum(t);
+    if (lane == 0) scratch[0] = t;
+  }
+  __syncthreads();
+  return scratch[0];
+}
+
+static inline int gb_div_up(long long a, long long b) { return (int)((a + b - 1) / b); }

@@ -1,0 +1,109 @@
+// Gated short convolution over a ragged batch: for every request its next
+// n tokens (a prompt portion or one decoded token) continue a depthwise
+// causal convolution whose last K-1 inputs live in the request's state slot.
+//
+//   bx[t, c]  = B[t, c] * x[t, c]                       (rows of [B | C | x])
+//   cv[t, c]  = sum_j taps[c, j] * win[(K-1) + i - (K-1-j), c] (+ bias[c])
+//               win = [state (K-1 rows); bx of this request (n rows)], i = t's
+//               index among the request's tokens: tap K-1 multiplies the
+//               current token, tap 0 the oldest
+//   out[t, c] = C[t, c] * cv[t, c]
+//   state    <- last K-1 rows of win
+// (MisterTK/gibbs arch/lib/transformer.json5:140-151; src/graph/cpu.rs:952-994.)
+//
+// Two launches: outputs first (token-parallel, read the old state), then the
+// state update (one thread per request and channel).  The state holds the
+// 32-bit products B*x, so decoding from it repeats the prompt pass exactly.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_TAPS = 16;
+
+template <typename T>
+__global__ void short_conv_out_kernel(const T* __restrict__ bcx, long long ld, const float* __restrict__ taps,
+                                      const float* __restrict__ bias, const float* __restrict__ state,
+                                      long long slot_stride, const int* __restrict__ slot_ids,
+                                      const int* __restrict__ tok_req, const int* __restrict__ q_start,
+                                      T* __restrict__ out, int n_tokens, int hidden, int K) {
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= (long long)n_tokens * hidden) return;
+  const int t = (int)(gid / hidden), c = (int)(gid - (long long)t * hidden);
+  const int r = tok_req[t];
+  const int first = q_start[r];
+  const int i = t - first;
+  const float* st = state + (size_t)slot_ids[r] * slot_stride;
+  float acc = 0.f;
+  for (int j = 0; j < K; ++j) {
+    const int src = i - (K - 1 - j);
+    float v;
+    if (src >= 0) {
+      const T* row = bcx + (size_t)(first + src) * ld;
+      v = to_f32(row[c]) * to_f32(row[2 * hidden + c]);
+    } else {
+      v = st[(size_t)(K - 1 + src) * hidden + c];
+    }
+    acc = fmaf(taps[(size_t)c * K + j], v, acc);
+  }
+  if (bias) acc += bias[c];
+  out[(size_t)t * hidden + c] = from_f32<T>(to_f32(bcx[(size_t)t * ld + hidden + c]) * acc);
+}
+
+template <typename T>
+__global__ void short_conv_state_kernel(const T* __restrict__ bcx, long long ld, float* __restrict__ state,
+                                        long long slot_stride, const int* __restrict__ slot_ids,
+                                        const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                        int n_requests, int hidden, int K) {
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= (long long)n_requests * hidden) return;
+  const int r = (int)(gid / hidden), c = (int)(gid - (long long)r * hidden);
+  const int n = q_len[r], first = q_start[r];
+  if (n <= 0) return;
+  float* st = state + (size_t)slot_ids[r] * slot_stride;
+  // new[j] = win[n + j]: an old state row while n + j < K-1 (read above the
+  // row being written, so ascending j is safe in place), else a new product.
+  for (int j = 0; j < K - 1; ++j) {
+    const int w = n + j;
+    float v;
+    if (w < K - 1) {
+      v = st[(size_t)w * hidden + c];
+    } else {
+      const T* row = bcx + (size_t)(first + w - (K - 1)) * ld;
+      v = to_f32(row[c]) * to_f32(row[2 * hidden + c]);
+    }
+    st[(size_t)j * hidden + c] = v;
+  }
+}
+
+}  // namespace
+
+// bcx: [n_tokens, 3*hidden] rows of [B | C | x] with row stride ld; taps
+// [hidden, K] and bias [hidden] (optional) in 32-bit; state: 32-bit, slot s at
+// state + s*slot_stride holding [K-1, hidden]; out: [n_tokens, hidden].
+GB_API int gb_short_conv(const void* bcx, int dtype, long long ld, const float* taps, const float* bias,
+                         float* state, long long slot_stride, const int* slot_ids, const int* tok_req,
+                         const int* q_start, const int* q_len, void* out, int n_tokens, int n_requests, int hidden,
+                         int K, cudaStream_t stream) {
+  if (n_tokens <= 0) return GB_OK;
+  if (K < 2 || K > MAX_TAPS) GB_FAIL(GB_ERR_ARG, "gb_short_conv: kernel width %d outside 2..%d", K, MAX_TAPS);
+  const int threads = 256;
+  const long long total = (long long)n_tokens * hidden;
+  const long long total_s = (long long)n_requests * hidden;
+  if (dtype == GB_F32) {
+    short_conv_out_kernel<float><<<gb_div_up(total, threads), threads, 0, stream>>>(
+        (const float*)bcx, ld, taps, bias, state, slot_stride, slot_ids, tok_req, q_start, (float*)out, n_tokens,
+        hidden, K);
+    short_conv_state_kernel<float><<<gb_div_up(total_s, threads), threads, 0, stream>>>(
+        (const float*)bcx, ld, state, slot_stride, slot_ids, q_start, q_len, n_requests, hidden, K);
+  } else if (dtype == GB_BF16) {
+    short_conv_out_kernel<bf16><<<gb_div_up(total, threads), threads, 0, stream>>>(
+        (const bf16*)bcx, ld, taps, bias, state, slot_stride, slot_ids, tok_req, q_start, (bf16*)out, n_tokens,
+        hidden, K);
+    short_conv_state_kernel<bf16><<<gb_div_up(total_s, threads), threads, 0, stream>>>(
+        (const bf16*)bcx, ld, state, slot_stride, slot_ids, q_start, q_len, n_requests, hidden, K);
+  } else {
+    GB_FAIL(GB_ERR_ARG, "gb_short_conv: unknown dtype %d", dtype);
+  }
+  GB_CHECK_LAUNCH("gb_short_conv");
+  return GB_OK;
+}

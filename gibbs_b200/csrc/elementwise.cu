@@ -1,0 +1,122 @@
+// Row-wise kernels that are bound by memory traffic: embedding gather,
+// RMSNorm (with an optional row gather), SwiGLU over a fused [gate | up] row.
+//
+// Formulas (MisterTK/gibbs): embedding src/graph/cpu.rs:161-248; RMSNorm
+// src/model/simd.rs:73-111 (scale = 1/sqrt(sum/n + eps), out = x*scale*g);
+// SwiGLU src/graph/cpu.rs:378-390 ((g*sigmoid(g))*u).
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
+                             int dim, int vocab) {
+  const int row = blockIdx.x;
+  int id = ids[row];
+  // Token ids are checked on the host before the step; a bad id reads row 0.
+  if (id < 0 || id >= vocab) id = 0;
+  const T* src = table + (size_t)id * dim;
+  float* dst = out + (size_t)row * dim;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = to_f32(src[d]);
+}
+
+GB_API int gb_embed(const void* table, int table_dtype, const int* ids, float* out, int n, int dim, int vocab,
+                    cudaStream_t stream) {
+  if (n <= 0) return GB_OK;
+  const int threads = dim >= 1024 ? 256 : 128;
+  if (table_dtype == GB_F32)
+    embed_kernel<float><<<n, threads, 0, stream>>>((const float*)table, ids, out, dim, vocab);
+  else if (table_dtype == GB_BF16)
+    embed_kernel<bf16><<<n, threads, 0, stream>>>((const bf16*)table, ids, out, dim, vocab);
+  else
+    GB_FAIL(GB_ERR_ARG, "gb_embed: unknown table dtype %d", table_dtype);
+  GB_CHECK_LAUNCH("gb_embed");
+  return GB_OK;
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// One block per output row.  `rows` (optional) gathers input rows.  The sum of
+// squares is taken in a fixed order, so a row's result does not depend on
+// what else is in the batch.
+template <typename TOut>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ gain,
+                               TOut* __restrict__ out, const int* __restrict__ rows, int dim, float eps) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const float* src = x + (size_t)(rows ? rows[r] : r) * ldx;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    const float v = src[d];
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)dim + eps);
+  TOut* dst = out + (size_t)r * dim;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = from_f32<TOut>(src[d] * scale * gain[d]);
+}
+
+GB_API int gb_rmsnorm(const float* x, long long ldx, const float* gain, void* out, int out_dtype, const int* rows,
+                      int n_rows, int dim, float eps, cudaStream_t stream) {
+  if (n_rows <= 0) return GB_OK;
+  int threads = 32;
+  while (threads < 512 && threads * 4 < dim) threads <<= 1;
+  if (out_dtype == GB_F32)
+    rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, ldx, gain, (float*)out, rows, dim, eps);
+  else if (out_dtype == GB_BF16)
+    rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, ldx, gain, (bf16*)out, rows, dim, eps);
+  else
+    GB_FAIL(GB_ERR_ARG, "gb_rmsnorm: unknown output dtype %d", out_dtype);
+  GB_CHECK_LAUNCH("gb_rmsnorm");
+  return GB_OK;
+}
+
+// ---------------------------------------------------------------- SwiGLU
+// in: [n, 2*inner] rows of [gate | up]; out: [n, inner].
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int inner) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / inner;
+    const int c = (int)(i - row * inner);
+    const float g = to_f32(gu[row * 2 * inner + c]);
+    const float u = to_f32(gu[row * 2 * inner + inner + c]);
+    const float sig = 1.0f / (1.0f + expf(-g));
+    out[i] = from_f32<T>((g * sig) * u);
+  }
+}
+
+GB_API int gb_swiglu(const void* gu, void* out, int dtype, int n, int inner, cudaStream_t stream) {
+  const long long total = (long long)n * inner;
+  if (total <= 0) return GB_OK;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (dtype == GB_F32)
+    swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, total, inner);
+  else if (dtype == GB_BF16)
+    swiglu_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, total, inner);
+  else
+    GB_FAIL(GB_ERR_ARG, "gb_swiglu: unknown dtype %d", dtype);
+  GB_CHECK_LAUNCH("gb_swiglu");
+  return GB_OK;
+}
+
+// ---------------------------------------------------------------- cast
+template <typename TIn, typename TOut>
+__global__ void cast_kernel(const TIn* __restrict__ in, TOut* __restrict__ out, long long total) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x)
+    out[i] = from_f32<TOut>(to_f32(in[i]));
+}
+
+GB_API int gb_cast(const void* in, int in_dtype, void* out, int out_dtype, long long total, cudaStream_t stream) {
+  if (total <= 0) return GB_OK;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (in_dtype == GB_F32 && out_dtype == GB_BF16)
+    cast_kernel<float, bf16><<<blocks, threads, 0, stream>>>((const float*)in, (bf16*)out, total);
+  else if (in_dtype == GB_BF16 && out_dtype == GB_F32)
+    cast_kernel<bf16, float><<<blocks, threads, 0, stream>>>((const bf16*)in, (float*)out, total);
+  else
+    GB_FAIL(GB_ERR_ARG, "gb_cast: unsupported conversion %d -> %d", in_dtype, out_dtype);
+  GB_CHECK_LAUNCH("gb_cast");
+  return GB_OK;
+}

@@ -1,0 +1,231 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A step takes any mix of prompt portions and single decoded tokens, cut
+anywhere, runs exactly the tokens it is given as one ragged batch against the
+cache that earlier steps left, and returns the 32-bit logits at the wanted
+places.  The reference runs one sequence per forward call
+(MisterTK/gibbs ``src/scheduler/mod.rs:1254-1530``, ``src/runtime/lm.rs:513-682``);
+batching over block tables is this engine's own design.  As there, a step
+continues each request exactly where it stands, and going past the context
+is an error (``src/runtime/lm.rs:531-544``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..cache import CacheManager, OutOfPages
+from ..parts.model import CausalLM
+
+
+class StepError(RuntimeError):
+    pass
+
+
+@dataclass
+class StepEntry:
+    request_id: object
+    tokens: Sequence[int]
+    want: Sequence[int] = ()          # indices into ``tokens`` whose logits are wanted
+
+
+@dataclass
+class StepState:
+    """What the parts see of one step.  All tensors are int32 on the device."""
+    n_tokens: int
+    n_requests: int
+    n_want: int
+    token_ids: torch.Tensor           # [N]
+    tok_req: torch.Tensor             # [N] index of the token's request within this step
+    tok_pos: torch.Tensor             # [N] absolute position of the token in its request
+    q_start: torch.Tensor             # [R] row of the request's first token in this step
+    q_len: torch.Tensor               # [R] number of its tokens in this step
+    start_pos: torch.Tensor           # [R] its length before this step
+    ctx_len: torch.Tensor             # [R] its length after this step
+    want_rows: torch.Tensor           # [W] rows whose logits are wanted
+    status: torch.Tensor              # [1] set nonzero by a kernel that met a bad page id
+    max_q_len: int = 0                # host copies, for launch sizing
+    max_ctx_len: int = 0
+    host_q_start: list = field(default_factory=list)
+    host_q_len: list = field(default_factory=list)
+    host_start_pos: list = field(default_factory=list)
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class Engine:
+    """A model, its cache and the step function over them."""
+
+    def __init__(self, model: CausalLM, n_pages: int, page_size: int = 16, max_requests: int = 64,
+                 max_step_tokens: int = 8192, max_context: Optional[int] = None):
+        self.model = model
+        self.device = model.rt.device
+        if self.device.type != "cuda":
+            raise StepError("the engine runs on a CUDA device; there is no host path")
+        ops.ensure_built(sorted(model.kernel_libraries()))
+        self.max_context = int(max_context or model.plan.max_context)
+        self.max_requests, self.max_step_tokens = int(max_requests), int(max_step_tokens)
+        self.cache = CacheManager(model.entry_needs(), n_pages, page_size, self.max_requests, model.rt.dtype,
+                                  self.device, self.max_context)
+        self.vocab_size = model.vocab_size
+        n_groups = len(self.cache.groups)
+        cap = 3 * _align4(self.max_step_tokens) + 5 * _align4(self.max_requests) + _align4(self.max_step_tokens) \
+            + n_groups * self.max_requests * self.cache.max_blocks + 16
+        self._cap = cap
+        self._staging = [torch.empty(cap, dtype=torch.int32).pin_memory() for _ in range(4)]
+        self._staging_np = [s.numpy() for s in self._staging]
+        self._staging_evt = [None] * 4
+        self._turn = 0
+        self._dev_meta = torch.empty(cap, dtype=torch.int32, device=self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.steps_run = 0
+
+    # -- request life ----------------------------------------------------------
+    def open(self, request_id) -> None:
+        self.cache.open(request_id)
+
+    def close(self, request_id) -> None:
+        self.cache.close(request_id)
+
+    def length(self, request_id) -> int:
+        return self.cache.live[request_id].length
+
+    def is_live(self, request_id) -> bool:
+        return request_id in self.cache.live
+
+    # -- the step ---------------------------------------------------------------
+    def can_run(self, entries: Sequence[StepEntry]) -> bool:
+        """Whether the pools have the pages this step would take."""
+        need = [0] * len(self.cache.groups)
+        for e in entries:
+            rc = self.cache.live[e.request_id]
+            new_len = rc.length + len(e.tokens)
+            for g, group in enumerate(self.cache.groups):
+                table = rc.block_tables[g]
+                first = self.cache._first_needed_page(group, rc.length)
+                freed = sum(1 for p in table[:first] if p >= 0)
+                need[g] += self.cache.pages_needed(new_len) - len(table) - freed
+        return all(n <= g.pool.n_free for n, g in zip(need, self.cache.groups))
+
+    def _validate(self, entries):
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        seen = set()
+        total = 0
+        for e in entries:
+            if e.request_id in seen:
+                raise StepError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            if e.request_id not in self.cache.live:
+                raise StepError(f"request {e.request_id!r} is not open")
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"request {e.request_id!r} brings no tokens")
+            bad = [t for t in e.tokens if not 0 <= int(t) < self.vocab_size]
+            if bad:
+                raise StepError(f"request {e.request_id!r}: token id {bad[0]} outside the vocabulary of "
+                                f"{self.vocab_size}")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise StepError(f"request {e.request_id!r}: wanted place {w} outside its {n} tokens")
+            new_len = self.cache.live[e.request_id].length + n
+            if new_len > self.max_context:
+                raise StepError(f"request {e.request_id!r} would reach {new_len} positions; the context is "
+                                f"{self.max_context}")
+            total += n
+        if len(entries) > self.max_requests:
+            raise StepError(f"{len(entries)} requests in one step; the engine was made for {self.max_requests}")
+        if total > self.max_step_tokens:
+            raise StepError(f"{total} tokens in one step; the engine was made for {self.max_step_tokens}")
+        return total
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one batch.  Returns float32 logits [number of wanted places,
+        vocab] on the device, in the order of the entries and of each entry's
+        ``want``; None when nothing is wanted.  Raises OutOfPages, before
+        anything changes, if the pools cannot hold the step."""
+        entries = list(entries)
+        n_tok = self._validate(entries)
+        if not self.can_run(entries):
+            raise OutOfPages(f"the step needs more pages than are free {self.cache.free_pages()}")
+        rcs = [self.cache.live[e.request_id] for e in entries]
+        for e, rc in zip(entries, rcs):
+            self.cache.reserve(rc, rc.length + len(e.tokens))
+
+        n_req = len(entries)
+        n_want = sum(len(e.want) for e in entries)
+        n_groups = len(self.cache.groups)
+        mb = self.cache.max_blocks
+        # layout of the metadata buffer (int32), every section 16-byte aligned
+        sizes = [n_tok, n_tok, n_tok, n_req, n_req, n_req, n_req, n_req, max(n_want, 1), n_groups * n_req * mb]
+        offs, o = [], 0
+        for s in sizes:
+            offs.append(o)
+            o += _align4(s)
+        total = o
+
+        turn = self._turn
+        self._turn = (turn + 1) % len(self._staging)
+        if self._staging_evt[turn] is not None:
+            self._staging_evt[turn].synchronize()
+        buf = self._staging_np[turn]
+        ids, treq, tpos = (buf[offs[i]:offs[i] + n_tok] for i in range(3))
+        qs, ql, sp, cl, sl = (buf[offs[i]:offs[i] + n_req] for i in range(3, 8))
+        wr = buf[offs[8]:offs[8] + max(n_want, 1)]
+        row, w_i = 0, 0
+        for r, (e, rc) in enumerate(zip(entries, rcs)):
+            n = len(e.tokens)
+            ids[row:row + n] = e.tokens
+            treq[row:row + n] = r
+            tpos[row:row + n] = np.arange(rc.length, rc.length + n, dtype=np.int32)
+            qs[r], ql[r], sp[r], cl[r] = row, n, rc.length, rc.length + n
+            sl[r] = rc.slot if rc.slot is not None else -1
+            for w in e.want:
+                wr[w_i] = row + int(w)
+                w_i += 1
+            row += n
+        if n_groups:
+            bt = buf[offs[9]:offs[9] + n_groups * n_req * mb].reshape(n_groups, n_req, mb)
+            self.cache.fill_block_tables(rcs, bt)
+
+        dev = self._dev_meta
+        dev[:total].copy_(self._staging[turn][:total], non_blocking=True)
+        evt = torch.cuda.Event()
+        evt.record()
+        self._staging_evt[turn] = evt
+
+        def view(i, n):
+            return dev[offs[i]:offs[i] + n]
+
+        step = StepState(
+            n_tokens=n_tok, n_requests=n_req, n_want=n_want,
+            token_ids=view(0, n_tok), tok_req=view(1, n_tok), tok_pos=view(2, n_tok),
+            q_start=view(3, n_req), q_len=view(4, n_req), start_pos=view(5, n_req), ctx_len=view(6, n_req),
+            want_rows=view(8, n_want), status=self.status,
+            max_q_len=max(len(e.tokens) for e in entries),
+            max_ctx_len=max(rc.length + len(e.tokens) for e, rc in zip(entries, rcs)),
+            host_q_start=[int(v) for v in qs], host_q_len=[int(v) for v in ql],
+            host_start_pos=[int(v) for v in sp],
+        )
+        tables = [dev[offs[9] + g * n_req * mb: offs[9] + (g + 1) * n_req * mb].view(n_req, mb)
+                  for g in range(n_groups)]
+        caches = self.cache.views(tables, view(7, n_req), [rc.slot for rc in rcs])
+        logits = self.model.forward(step, caches)
+        for e, rc in zip(entries, rcs):
+            self.cache.advance(rc, rc.length + len(e.tokens))
+        self.steps_run += 1
+        return logits
+
+    def check_status(self) -> None:
+        """Synchronise and raise if a kernel met a page id outside its pool."""
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            raise StepError(f"a cache kernel met a page id outside its pool (code {code}); "
+                            "the block tables and the pools disagree")

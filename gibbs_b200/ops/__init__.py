@@ -1,0 +1,254 @@
+"""Python bindings of the hand-written CUDA kernels.
+
+Every function takes CUDA tensors, checks what the kernel assumes (device,
+dtype, contiguous rows) and launches on the current CUDA stream.  Nothing
+here computes on the host or calls a library kernel: if a tensor is not on a
+GPU or a kernel library is missing, the call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .library import KernelError, check, ensure_built, library
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+_c_int, _c_ll, _c_float, _c_void = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DT[dt]
+    except KeyError:
+        raise KernelError(f"kernels take float32 and bfloat16 tensors, not {dt}") from None
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return _c_void(t.data_ptr()) if t is not None else _c_void(0)
+
+
+def _stream():
+    return _c_void(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("gibbs_b200 kernels run on CUDA tensors only; got a tensor on " + str(t.device))
+
+
+def _rows(t: torch.Tensor, what: str) -> int:
+    """Row stride (in elements) of a 2-d tensor whose rows are contiguous."""
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise KernelError(f"{what}: expected a 2-d tensor with contiguous rows, got shape {tuple(t.shape)} "
+                          f"strides {t.stride()}")
+    return t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
+
+
+def _i32(t: Optional[torch.Tensor], what: str):
+    if t is not None and (t.dtype != torch.int32 or not t.is_contiguous()):
+        raise KernelError(f"{what}: expected a contiguous int32 tensor")
+    return t
+
+
+def _f32vec(t: Optional[torch.Tensor], n: int, what: str):
+    if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != n):
+        raise KernelError(f"{what}: expected {n} contiguous float32 values, got {tuple(t.shape)} {t.dtype}")
+    return t
+
+
+# ---------------------------------------------------------------------------
+
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, :] = table[ids[t], :] widened to 32-bit."""
+    _need_cuda(table, ids, out)
+    lib = library("core")
+    n, dim = out.shape
+    if not table.is_contiguous() or table.shape[1] != dim or out.dtype != torch.float32 or not out.is_contiguous():
+        raise KernelError("embed: table [vocab, dim] contiguous and out [n, dim] float32 contiguous expected")
+    _i32(ids, "embed ids")
+    check(lib, lib.gb_embed(_ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out), _c_int(n), _c_int(dim),
+                            _c_int(table.shape[0]), _stream()))
+    return out
+
+
+def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
+            rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r, :] = x[rows[r] or r, :] * rsqrt(mean(x^2) + eps) * gain; x is 32-bit."""
+    _need_cuda(x, gain, out, rows)
+    lib = library("core")
+    dim = x.shape[1]
+    if x.dtype != torch.float32:
+        raise KernelError("rmsnorm: the input (the residual stream) is float32")
+    ldx = _rows(x, "rmsnorm x")
+    n_rows = out.shape[0]
+    if not out.is_contiguous() or out.shape[1] != dim:
+        raise KernelError("rmsnorm: out must be contiguous [rows, dim]")
+    if rows is None and n_rows != x.shape[0]:
+        raise KernelError("rmsnorm: out has a different number of rows than x")
+    _f32vec(gain, dim, "rmsnorm gain")
+    _i32(rows, "rmsnorm rows")
+    check(lib, lib.gb_rmsnorm(_ptr(x), _c_ll(ldx), _ptr(gain), _ptr(out), dtype_code(out.dtype), _ptr(rows),
+                              _c_int(n_rows), _c_int(dim), _c_float(eps), _stream()))
+    return out
+
+
+def linear_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                accumulate: bool = False) -> torch.Tensor:
+    """out (+)= a @ w.T (+ bias) with 32-bit FMA on the CUDA cores."""
+    _need_cuda(a, w, bias, out)
+    lib = library("core")
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape[0] != m or out.shape[1] != n:
+        raise KernelError(f"linear: shapes a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} disagree")
+    _f32vec(bias, n, "linear bias")
+    check(lib, lib.gb_linear_simt(
+        _ptr(a), dtype_code(a.dtype), _c_ll(_rows(a, "linear a")), _ptr(w), dtype_code(w.dtype),
+        _c_ll(_rows(w, "linear w")), _ptr(bias), _ptr(out), dtype_code(out.dtype), _c_ll(_rows(out, "linear out")),
+        _c_int(1 if accumulate else 0), _c_int(m), _c_int(n), _c_int(k), _stream()))
+    return out
+
+
+def linear_libraries(weight_dtype: torch.dtype, compute_dtype: torch.dtype):
+    """Kernel libraries a projection with these operand types launches from."""
+    return ("core",)
+
+
+def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+           accumulate: bool = False) -> torch.Tensor:
+    """out (+)= a @ w.T (+ bias); picks the matrix-product kernel for the operand types."""
+    return linear_simt(a, w, bias, out, accumulate)
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = (g * sigmoid(g)) * u for rows [g | u]."""
+    _need_cuda(gate_up, out)
+    lib = library("core")
+    n, inner = out.shape
+    if gate_up.shape != (n, 2 * inner) or not gate_up.is_contiguous() or not out.is_contiguous() \
+            or gate_up.dtype != out.dtype:
+        raise KernelError("swiglu: gate_up [n, 2*inner] and out [n, inner], contiguous, same dtype expected")
+    check(lib, lib.gb_swiglu(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), _c_int(n), _c_int(inner), _stream()))
+    return out
+
+
+def cast(src: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    _need_cuda(src, out)
+    lib = library("core")
+    if not src.is_contiguous() or not out.is_contiguous() or src.numel() != out.numel():
+        raise KernelError("cast: contiguous tensors of equal size expected")
+    check(lib, lib.gb_cast(_ptr(src), dtype_code(src.dtype), _ptr(out), dtype_code(out.dtype),
+                           _c_ll(src.numel()), _stream()))
+    return out
+
+
+def short_conv(bcx: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
+               slot_ids: torch.Tensor, tok_req: torch.Tensor, q_start: torch.Tensor, q_len: torch.Tensor,
+               out: torch.Tensor) -> torch.Tensor:
+    """Gated short convolution over a ragged batch; see csrc/conv.cu.
+    state: float32 [n_slots, kernel-1, hidden] (the slot axis may be strided)."""
+    _need_cuda(bcx, taps, bias, state, slot_ids, tok_req, q_start, q_len, out)
+    lib = library("core")
+    n, hidden = out.shape
+    kk = taps.shape[1]
+    if bcx.shape != (n, 3 * hidden) or bcx.dtype != out.dtype or not out.is_contiguous():
+        raise KernelError("short_conv: bcx [n, 3*hidden] and out [n, hidden] of one dtype expected")
+    _f32vec(taps, hidden * kk, "short_conv taps")
+    _f32vec(bias, hidden, "short_conv bias")
+    if state.dtype != torch.float32 or state.shape[1:] != (kk - 1, hidden) or state[0].stride() != (hidden, 1):
+        raise KernelError(f"short_conv: state must be float32 [slots, {kk - 1}, {hidden}] with contiguous slots")
+    for t, w in ((slot_ids, "slot_ids"), (tok_req, "tok_req"), (q_start, "q_start"), (q_len, "q_len")):
+        _i32(t, "short_conv " + w)
+    check(lib, lib.gb_short_conv(
+        _ptr(bcx), dtype_code(bcx.dtype), _c_ll(_rows(bcx, "short_conv bcx")), _ptr(taps), _ptr(bias), _ptr(state),
+        _c_ll(state.stride(0)), _ptr(slot_ids), _ptr(tok_req), _ptr(q_start), _ptr(q_len), _ptr(out), _c_int(n),
+        _c_int(q_len.numel()), _c_int(hidden), _c_int(kk), _stream()))
+    return out
+
+
+def _check_pages(k_pages, v_pages, kv_heads, hd, dtype, what):
+    for p in (k_pages, v_pages):
+        if p.dim() != 4 or p.shape[1] != kv_heads or p.shape[3] != hd or not p.is_contiguous() or p.dtype != dtype:
+            raise KernelError(f"{what}: pages must be contiguous [n_pages, {kv_heads}, page_size, {hd}] {dtype}, "
+                              f"got {tuple(p.shape)} {p.dtype}")
+    if k_pages.shape != v_pages.shape:
+        raise KernelError(f"{what}: key and value pages differ in shape")
+
+
+def qk_norm_rope_store(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
+                       q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], eps: float,
+                       inv_freq: Optional[torch.Tensor], rotary_dim: int, adjacent_pairs: bool,
+                       tok_req: torch.Tensor, tok_pos: torch.Tensor, block_table: torch.Tensor,
+                       k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+                       status: torch.Tensor) -> None:
+    """Per-head RMSNorm and rotary encoding of q (in place) and k; k and v go
+    into their pages.  With k_pages None only q is processed (a layer that
+    reads another layer's cache)."""
+    _need_cuda(qkv, q_gain, k_gain, inv_freq, tok_req, tok_pos, block_table, k_pages, v_pages, status)
+    lib = library("core")
+    n = qkv.shape[0]
+    write = k_pages is not None
+    cols = (heads + (2 * kv_heads if write else 0)) * head_dim
+    if qkv.shape[1] < cols:
+        raise KernelError(f"qk_norm_rope_store: rows of {qkv.shape[1]} columns, {cols} needed")
+    _f32vec(q_gain, head_dim, "q gain")
+    _f32vec(k_gain, head_dim, "k gain")
+    if inv_freq is not None:
+        _f32vec(inv_freq, rotary_dim // 2, "inv_freq")
+    _i32(tok_req, "tok_req"), _i32(tok_pos, "tok_pos"), _i32(block_table, "block_table"), _i32(status, "status")
+    page_size, n_pages = 1, 0
+    if write:
+        _check_pages(k_pages, v_pages, kv_heads, head_dim, qkv.dtype, "qk_norm_rope_store")
+        page_size, n_pages = k_pages.shape[2], k_pages.shape[0]
+    check(lib, lib.gb_qk_norm_rope_store(
+        _ptr(qkv), dtype_code(qkv.dtype), _c_ll(_rows(qkv, "qkv")), _ptr(q_gain), _ptr(k_gain), _c_float(eps),
+        _ptr(inv_freq), _c_int(rotary_dim), _c_int(1 if adjacent_pairs else 0), _ptr(tok_req), _ptr(tok_pos),
+        _ptr(block_table), _c_int(block_table.shape[1] if block_table.dim() == 2 else 0), _c_int(page_size),
+        _ptr(k_pages), _ptr(v_pages), _c_int(n_pages), _c_int(n), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
+        _c_int(1 if write else 0), _ptr(status), _stream()))
+
+
+def paged_attention(q: torch.Tensor, heads: int, kv_heads: int, head_dim: int, k_pages: torch.Tensor,
+                    v_pages: torch.Tensor, block_table: torch.Tensor, tok_req: torch.Tensor, tok_pos: torch.Tensor,
+                    scale: float, window: int, out: torch.Tensor, status: torch.Tensor, hints=None) -> torch.Tensor:
+    """out[t, h, :] = softmax over visible keys of (q.K)*scale, times V; q may be
+    a column slice of a wider row (its row stride is passed on)."""
+    _need_cuda(q, k_pages, v_pages, block_table, tok_req, tok_pos, out, status)
+    lib = library("core")
+    n = q.shape[0]
+    if q.shape[1] != heads * head_dim or out.shape != (n, heads * head_dim) or q.dtype != out.dtype:
+        raise KernelError("paged_attention: q and out must be [n, heads*head_dim] of one dtype")
+    _check_pages(k_pages, v_pages, kv_heads, head_dim, q.dtype, "paged_attention")
+    _i32(tok_req, "tok_req"), _i32(tok_pos, "tok_pos"), _i32(block_table, "block_table"), _i32(status, "status")
+    check(lib, lib.gb_paged_attention(
+        _ptr(q), dtype_code(q.dtype), _c_ll(_rows(q, "q")), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+        _c_int(block_table.shape[1]), _c_int(k_pages.shape[2]), _c_int(k_pages.shape[0]), _ptr(tok_req),
+        _ptr(tok_pos), _ptr(out), _c_ll(_rows(out, "out")), _c_int(n), _c_int(heads), _c_int(kv_heads),
+        _c_int(head_dim), _c_float(scale), _c_int(window or 0), _ptr(status), _stream()))
+    return out
+
+
+def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,
+           top_k: Optional[torch.Tensor] = None, top_p: Optional[torch.Tensor] = None,
+           seed: Optional[torch.Tensor] = None, counter: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token id per logits row; per-row parameters (None: greedy)."""
+    _need_cuda(logits, out, temperature, top_k, top_p, seed, counter)
+    lib = library("core")
+    rows, vocab = logits.shape
+    if logits.dtype != torch.float32:
+        raise KernelError("sample: logits are float32")
+    _i32(out, "sample out"), _i32(top_k, "top_k")
+    for t, w in ((temperature, "temperature"), (top_p, "top_p")):
+        _f32vec(t, rows, "sample " + w)
+    for t, w in ((seed, "seed"), (counter, "counter")):
+        if t is not None and (t.dtype != torch.int64 or t.numel() != rows or not t.is_contiguous()):
+            raise KernelError(f"sample {w}: expected {rows} int64 values")
+    check(lib, lib.gb_sample(_ptr(logits), _c_ll(_rows(logits, "logits")), _c_int(rows), _c_int(vocab),
+                             _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(seed), _ptr(counter), _ptr(out),
+                             _stream()))
+    return out

@@ -1,0 +1,164 @@
+"""Interfaces of the parts a model is put together from, and the registries
+that map a plan's ``kind`` strings to their classes.
+
+A part
+  * declares the tensors it needs (``declare(params)``: local name ->
+    ``TensorDecl``), so that the loader can check a checkpoint before anything
+    is copied;
+  * is built from ``(params, tensors, runtime)``, where ``tensors`` maps its
+    local names to device tensors already in their in-memory dtype;
+  * knows its own sizes only: nothing tells it which model, layer index or
+    architecture it belongs to.
+
+Categories and what each must implement:
+
+  norm        ``forward(x_f32 [N, dim], out=None, rows=None) -> [N or len(rows), dim]``
+              in the compute dtype.
+  position    ``rotary() -> Rotary | None`` (tables a mixer's kernel applies)
+              and ``embed(x_f32, step)`` (an in-place hook on the embedded
+              tokens; default nothing).
+  mixer       ``cache_needs() -> [PagedKV | SlotState, ...]`` and
+              ``forward(h, residual_f32, step, caches)`` which ADDS the mixer's
+              output into ``residual_f32``; ``caches`` holds one view per need.
+  feed_forward ``forward(h, residual_f32, step)``, adding likewise.
+  block       built from its four parts; ``forward(x_f32, step, caches)``.
+  embedding   ``forward(ids_i32 [N]) -> x_f32 [N, dim]``.
+  head        ``forward(z [R, dim]) -> logits_f32 [R, vocab]``.
+
+The residual stream is 32-bit in every compute dtype, so the residual sum is
+exact to 32-bit rounding.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Optional, Sequence
+
+import torch
+
+# roles decide the dtype a checkpoint tensor gets in memory (see weights.loader)
+MATRIX = "matrix"     # operand of a matrix product, or an embedding table
+VECTOR = "vector"     # gains, biases, filter taps: always 32-bit in memory
+INT_TABLE = "int"     # integer tables: int32 in memory
+
+
+@dataclass(frozen=True)
+class TensorDecl:
+    shapes: tuple[tuple[int, ...], ...]   # accepted checkpoint shapes; the first is what the part receives
+    role: str = MATRIX
+
+    @staticmethod
+    def of(*shape: int, role: str = MATRIX) -> "TensorDecl":
+        return TensorDecl((tuple(shape),), role)
+
+
+@dataclass(frozen=True)
+class PagedKV:
+    """Keys and values of every position (or of the last ``window`` positions)
+    in pages: [n_pages, kv_heads, page_size, head_dim] each."""
+    kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class SlotState:
+    """Per-request state of fixed size, zero when a request starts."""
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class Runtime:
+    """What a part needs to know about where and how it computes."""
+    dtype: torch.dtype                 # compute dtype: torch.float32 or torch.bfloat16
+    device: torch.device
+
+    def empty(self, *shape, dtype=None) -> torch.Tensor:
+        return torch.empty(*shape, dtype=dtype or self.dtype, device=self.device)
+
+
+class Part:
+    category: str = ""
+
+    @classmethod
+    def declare(cls, params: dict) -> dict[str, TensorDecl]:
+        return {}
+
+    def __init__(self, params: dict, tensors: dict[str, torch.Tensor], rt: Runtime):
+        self.params, self.rt = params, rt
+
+    def kernel_libraries(self) -> Sequence[str]:
+        """Kernel libraries this part launches from (built before the first step)."""
+        return ("core",)
+
+
+class Norm(Part):
+    category = "norm"
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+@dataclass(frozen=True)
+class Rotary:
+    inv_freq: torch.Tensor    # float32 [rotary_dim / 2]
+    rotary_dim: int
+    adjacent_pairs: bool      # pairs (2j, 2j+1) instead of (j, j + rotary_dim/2)
+
+
+class PositionEncoding(Part):
+    category = "position"
+
+    def rotary(self) -> Optional[Rotary]:
+        return None
+
+    def embed(self, x: torch.Tensor, step) -> None:
+        return None
+
+
+class Mixer(Part):
+    category = "mixer"
+
+    def cache_needs(self) -> list:
+        return []
+
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, step, caches: list) -> None:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    category = "feed_forward"
+
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, step) -> None:
+        raise NotImplementedError
+
+
+class Block:
+    category = "block"
+
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, ffn: FeedForward, rt: Runtime):
+        self.mixer_norm, self.mixer, self.ffn_norm, self.ffn, self.rt = mixer_norm, mixer, ffn_norm, ffn, rt
+
+    def forward(self, x: torch.Tensor, step, caches: list) -> None:
+        raise NotImplementedError
+
+
+# ---------------------------------------------------------------------------
+_REGISTRY: dict[tuple[str, str], Any] = {}
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head")
+
+
+def register_part(category: str, kind: str, cls) -> None:
+    """Make ``kind`` available to plans.  Registering a kind again replaces it."""
+    if category not in CATEGORIES:
+        raise KeyError(f"unknown part category '{category}'; known: {CATEGORIES}")
+    _REGISTRY[(category, kind)] = cls
+
+
+def part_class(category: str, kind: str):
+    try:
+        return _REGISTRY[(category, kind)]
+    except KeyError:
+        known = sorted(k for c, k in _REGISTRY if c == category)
+        raise KeyError(f"no {category} of kind '{kind}' is registered; known: {known}") from None

@@ -1,0 +1,52 @@
+"""Token embedding and the output head."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import Part, TensorDecl, register_part
+from .linear import Linear
+
+
+class TokenEmbedding(Part):
+    """x[t, :] = table[id_t, :], no scaling (MisterTK/gibbs arch/families/lfm2.json5:74)."""
+    category = "embedding"
+
+    @classmethod
+    def declare(cls, params):
+        return {"weight": TensorDecl.of(params["vocab"], params["dim"])}
+
+    def __init__(self, params, tensors, rt):
+        super().__init__(params, tensors, rt)
+        self.vocab, self.dim = int(params["vocab"]), int(params["dim"])
+        self.table = tensors["weight"].contiguous()
+
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        out = self.rt.empty(ids.numel(), self.dim, dtype=torch.float32)
+        return ops.embed(self.table, ids, out)
+
+
+class LMHead(Part):
+    """logits = z W^T in 32-bit, no scale and no soft cap
+    (MisterTK/gibbs arch/lib/transformer.json5:170-175).  A tied head is given
+    the embedding table's tensor and shares its memory."""
+    category = "head"
+
+    @classmethod
+    def declare(cls, params):
+        return {"weight": TensorDecl.of(params["vocab"], params["dim"])}
+
+    def __init__(self, params, tensors, rt):
+        super().__init__(params, tensors, rt)
+        self.vocab = int(params["vocab"])
+        self.proj = Linear(tensors["weight"], None, rt)
+
+    def kernel_libraries(self):
+        return self.proj.kernel_libraries()
+
+    def forward(self, z: torch.Tensor) -> torch.Tensor:
+        return self.proj(z, out_dtype=torch.float32)
+
+
+register_part("embedding", "token_embedding", TokenEmbedding)
+register_part("head", "lm_head", LMHead)
