@@ -1,38 +1,94 @@
 """The engine against the plain implementation, in 32-bit and in bfloat16,
-under every way of cutting the work."""
+under every way of cutting the work: each request alone and whole; most of it
+in one step and the last 32 tokens one by one; in portions of changing size;
+and mixed, up to four live requests with so few pages that they are reused."""
 import numpy as np
 import pytest
 import torch
 
-from helpers import TINY, TOL, make_folder, plain_logits, random_ids, rel_err
+from helpers import (TINY, TOL, first_wrong, make_folder, plain_logits, random_ids, rel_err, run_trace_on_engine,
+                     trace_mixed, trace_portions, trace_tail_decoded, trace_whole)
 
 pytestmark = pytest.mark.gpu
 
-
-def _engine(folder, dtype, n_pages=64, page_size=16, **kw):
-    from gibbs_b200 import Engine, load_model
-    model = load_model(folder, dtype=dtype, device="cuda:0")
-    return Engine(model, n_pages=n_pages, page_size=page_size, **kw)
+DTYPES = ["float32", "bfloat16"]
+_cache = {}
 
 
 def _stored(dtype):
     return torch.bfloat16 if dtype == "bfloat16" else torch.float32
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
-def test_whole_prompt(tmp_path, name, dtype):
-    from gibbs_b200 import StepEntry
-    folder = make_folder(tmp_path, name, stored=_stored(dtype))
-    eng = _engine(folder, dtype)
+def _setup(tmp_path_factory, name, dtype):
+    """(folder, model) for a tiny configuration, built once per session."""
+    key = (name, dtype)
+    if key not in _cache:
+        from gibbs_b200 import load_model
+        folder = make_folder(tmp_path_factory.mktemp("models"), name, stored=_stored(dtype))
+        _cache[key] = (folder, load_model(folder, dtype=dtype, device="cuda:0"))
+    return _cache[key]
+
+
+def _requests(name, lengths, seed=0):
     vocab = TINY[name][0]["vocab_size"]
-    for seed, n in ((1, 1), (2, 7), (3, 40), (4, 150)):
-        ids = random_ids(seed, n, vocab)
-        eng.open("r")
-        got = eng.step([StepEntry("r", ids, list(range(n)))]).cpu().numpy()
-        eng.check_status()
-        eng.close("r")
+    return {f"r{i}": random_ids(seed * 100 + i, n, vocab) for i, n in enumerate(lengths)}
+
+
+def _compare(folder, requests, got, dtype):
+    worst = 0.0
+    for rid, ids in requests.items():
         want = plain_logits(folder, ids)
-        assert got.shape == want.shape
-        assert rel_err(got, want) < TOL[dtype], (n, rel_err(got, want))
-    eng.cache.check()
+        assert got[rid].shape == want.shape, rid
+        bad = first_wrong(got[rid], want, TOL[dtype])
+        assert bad is None, f"request {rid}: first wrong position {bad[0]} of {len(ids)} (rel err {bad[1]:.3g})"
+        worst = max(worst, rel_err(got[rid], want))
+    return worst
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_whole_prompt(tmp_path_factory, name, dtype):
+    from gibbs_b200 import Engine
+    folder, model = _setup(tmp_path_factory, name, dtype)
+    eng = Engine(model, n_pages=32, page_size=16)
+    reqs = _requests(name, [1, 7, 40, 150, 300])
+    worst = _compare(folder, reqs, run_trace_on_engine(eng, trace_whole(reqs)), dtype)
+    print(f"whole {name} {dtype}: worst rel err {worst:.3g}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_last_32_tokens_one_by_one(tmp_path_factory, name, dtype):
+    from gibbs_b200 import Engine
+    folder, model = _setup(tmp_path_factory, name, dtype)
+    eng = Engine(model, n_pages=16, page_size=16)
+    reqs = _requests(name, [33, 100, 177], seed=1)
+    worst = _compare(folder, reqs, run_trace_on_engine(eng, trace_tail_decoded(reqs)), dtype)
+    print(f"tail {name} {dtype}: worst rel err {worst:.3g}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_portions_of_changing_size(tmp_path_factory, name, dtype):
+    from gibbs_b200 import Engine
+    folder, model = _setup(tmp_path_factory, name, dtype)
+    eng = Engine(model, n_pages=26, page_size=8)
+    reqs = _requests(name, [5, 64, 131, 200], seed=2)
+    worst = _compare(folder, reqs, run_trace_on_engine(eng, trace_portions(reqs)), dtype)
+    print(f"portions {name} {dtype}: worst rel err {worst:.3g}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_mixed_batches_with_page_reuse(tmp_path_factory, name, dtype):
+    from gibbs_b200 import Engine
+    folder, model = _setup(tmp_path_factory, name, dtype)
+    capacity = 448
+    eng = Engine(model, n_pages=capacity // 16, page_size=16, max_requests=4)
+    reqs = _requests(name, [90, 37, 128, 61, 150, 2, 75, 100, 33, 119], seed=3)
+    steps = trace_mixed(reqs, capacity_tokens=capacity, max_live=4, seed=5)
+    assert max(len(s["entries"]) for s in steps) >= 3
+    worst = _compare(folder, reqs, run_trace_on_engine(eng, steps), dtype)
+    # every page and slot was handed out more than once
+    assert sum(len(v) for v in reqs.values()) > capacity
+    print(f"mixed {name} {dtype}: worst rel err {worst:.3g}, {len(steps)} steps")
