@@ -9,9 +9,10 @@ ragged batches, a scheduler and entry points (``engine``), sampling
 """
 from .config import Lfm2Config, ModelPlan, parse_config, register_architecture
 from .parts import register_part
-from .engine import Engine, StepEntry, load_model, random_model
+from .engine import Engine, Generator, Scheduler, StepEntry, load_model, random_model
+from .sampling import Sampler, SamplingParams
 from .weights import write_random_model
 
 __version__ = "0.1.0"
-__all__ = ["Lfm2Config", "ModelPlan", "parse_config", "register_architecture", "register_part", "Engine",
+__all__ = ["Lfm2Config", "ModelPlan", "parse_config", "register_architecture", "register_part", "Engine", "Generator", "Scheduler", "Sampler", "SamplingParams",
            "StepEntry", "load_model", "random_model", "write_random_model"]

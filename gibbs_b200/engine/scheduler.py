@@ -1,0 +1,307 @@
+"""Continuous batching above the step function: admit requests, cut prompts
+into portions under a token budget, decode, finish and free.
+
+Policy, after MisterTK/gibbs ``ContinuousBatchScheduler::step``
+(``src/scheduler/mod.rs:1128-1580``):
+
+* Admission is first come, first served, while a state slot and the pages of
+  the first portion are free (``:1155-1221``).  ``max_new_tokens`` is clamped
+  to ``ctx - prompt`` at submission (``:953-955``); an empty prompt becomes the
+  single token 1 (``:1005-1008``).
+* Every decoding request gets one token per step (``:1376-1528``).  What is
+  left of the token budget goes to prompt portions, shortest remaining prompt
+  first, while the oldest prefilling request keeps at least half of the
+  budget (``:1231-1246, 1270-1284``).
+* The first token is sampled from the logits of the last prompt position in
+  the same step (``:1347-1372``).
+* A request finishes with ``stop`` on an end-of-sequence id (the id is not
+  emitted), with ``length`` at ``max_new_tokens`` or the context's end
+  (``:1361-1371, 1504-1528``), with ``cancelled`` when its client gave up
+  (``:1259-1262``) and with ``error`` when its step failed (``:1332-1340``).
+
+Unlike the reference, all requests of a step run as ONE batch, and page ids
+are real memory.  When the pages run out in mid-flight the reference carries
+on (its ids are bookkeeping, ``:1294-1300``); here the request admitted last
+is preempted: its pages and its slot are given back and it returns to the
+head of the queue, to be recomputed from its prompt plus the tokens it has
+already emitted (fixed-size state cannot be rewound).  Tokens that were
+emitted are never emitted twice, and a request that cannot fit the pool even
+alone ends with ``error``.
+"""
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from enum import Enum
+from typing import Callable, Optional, Sequence
+
+from ..cache import OutOfPages, OutOfSlots
+from ..sampling.params import SamplingParams
+from .step import StepEntry
+
+MAX_PREFILL_CHUNK = 2048        # src/scheduler/mod.rs:341
+
+
+class FinishReason(str, Enum):
+    STOP = "stop"
+    LENGTH = "length"
+    ERROR = "error"
+    CANCELLED = "cancelled"
+
+
+class SeqState(str, Enum):
+    WAITING = "waiting"
+    RUNNING = "running"
+    FINISHED = "finished"
+
+
+@dataclass
+class Sequence_:
+    id: int
+    prompt: list
+    params: SamplingParams
+    seed: int
+    submitted: int                                  # submission order
+    output: list = field(default_factory=list)
+    fed: int = 0                                    # tokens of prompt + output already in the cache
+    state: SeqState = SeqState.WAITING
+    finish: Optional[FinishReason] = None
+    error: Optional[str] = None
+    admitted: int = -1                              # admission order (for preemption)
+    preemptions: int = 0
+    cancelled: bool = False
+
+    @property
+    def tokens(self) -> list:
+        return self.prompt + self.output
+
+    @property
+    def remaining(self) -> int:
+        return len(self.prompt) + len(self.output) - self.fed
+
+    @property
+    def decoding(self) -> bool:
+        """One token left to feed, and it is one this request generated."""
+        return self.remaining == 1 and len(self.output) > 0
+
+
+@dataclass
+class StepOutput:
+    """Shape of the reference's ``BatchStepOutput`` (``src/scheduler/mod.rs:539-546``)
+    plus what was emitted and who finished."""
+    tokens_generated: int = 0
+    active_sequences: int = 0
+    prefill: tuple = (0.0, 0)                       # (seconds, prompt tokens)
+    decode: tuple = (0.0, 0)                        # (seconds, decoded tokens)
+    emitted: list = field(default_factory=list)     # (sequence id, token)
+    finished: list = field(default_factory=list)    # (sequence id, FinishReason)
+    preempted: list = field(default_factory=list)   # sequence ids
+
+
+class Scheduler:
+    def __init__(self, engine, sampler: Callable, max_batch_tokens: int = MAX_PREFILL_CHUNK,
+                 max_running: Optional[int] = None, eos_ids: Sequence[int] = (), seed: int = 0,
+                 on_token: Optional[Callable] = None):
+        """engine: ``open/close/step/can_run/max_context/max_requests``;
+        sampler: ``(logits, params, seeds, counters) -> token ids``."""
+        self.engine, self.sampler = engine, sampler
+        self.max_batch_tokens = max(1, int(max_batch_tokens))
+        self.max_running = min(int(max_running or engine.max_requests), engine.max_requests)
+        self.ctx = engine.max_context
+        self.eos_ids = set(int(e) for e in eos_ids)
+        self.seed = seed
+        self.on_token = on_token
+        self.waiting: deque = deque()
+        self.running: list = []
+        self.sequences: dict = {}
+        self._next_id = 0
+        self._admissions = 0
+        self.steps = 0
+
+    # -- submission --------------------------------------------------------------
+    def submit(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
+        params = params or SamplingParams()
+        prompt = [int(t) for t in prompt] or [1]
+        if len(prompt) >= self.ctx:
+            raise ValueError(f"a prompt of {len(prompt)} tokens does not fit the context of {self.ctx}")
+        max_new = min(params.max_new_tokens, self.ctx - len(prompt))
+        if max_new != params.max_new_tokens:
+            params = SamplingParams(**{**params.__dict__, "max_new_tokens": max_new})
+        sid = self._next_id
+        self._next_id += 1
+        seed = params.seed if params.seed is not None else (self.seed * 0x9E3779B1 + sid * 0x85EBCA77 + 1)
+        seq = Sequence_(sid, prompt, params, seed & ((1 << 64) - 1), submitted=sid)
+        self.sequences[sid] = seq
+        self.waiting.append(seq)
+        return sid
+
+    def cancel(self, sid: int) -> None:
+        """The client gave up: the request ends at the next step."""
+        self.sequences[sid].cancelled = True
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # -- internals ---------------------------------------------------------------
+    def _finish(self, seq: Sequence_, reason: FinishReason, out: StepOutput, error: Optional[str] = None):
+        if seq.state == SeqState.RUNNING:
+            self.engine.close(seq.id)
+            self.running.remove(seq)
+        elif seq in self.waiting:
+            self.waiting.remove(seq)
+        seq.state, seq.finish, seq.error = SeqState.FINISHED, reason, error
+        out.finished.append((seq.id, reason))
+
+    def _preempt(self, seq: Sequence_, out: StepOutput):
+        self.engine.close(seq.id)
+        self.running.remove(seq)
+        seq.state, seq.fed = SeqState.WAITING, 0
+        seq.preemptions += 1
+        self.waiting.appendleft(seq)
+        out.preempted.append(seq.id)
+
+    def _admit(self, budget: int, out: StepOutput):
+        while self.waiting and len(self.running) < self.max_running:
+            seq = self.waiting[0]
+            if seq.cancelled:
+                self._finish(seq, FinishReason.CANCELLED, out)
+                continue
+            try:
+                self.engine.open(seq.id)
+            except OutOfSlots:
+                break
+            first = min(seq.remaining, max(budget, 1))
+            # the running requests' next tokens are counted too, so that a request is not
+            # admitted only to be preempted in the same step
+            others = [StepEntry(s.id, s.tokens[s.fed:s.fed + 1]) for s in self.running if s.remaining > 0]
+            if not self.engine.can_run(others + [StepEntry(seq.id, seq.tokens[:first])]):
+                self.engine.close(seq.id)
+                if not self.running:
+                    # nothing else holds pages: this request can never start
+                    self.waiting.popleft()
+                    seq.state = SeqState.WAITING
+                    self._finish(seq, FinishReason.ERROR, out,
+                                 f"the cache pool cannot hold the first {first} tokens of this request")
+                    continue
+                break
+            self.waiting.popleft()
+            seq.state, seq.admitted = SeqState.RUNNING, self._admissions
+            self._admissions += 1
+            self.running.append(seq)
+
+    def _plan(self) -> list:
+        """(sequence, number of tokens) for this step."""
+        plan = [(s, 1) for s in self.running if s.decoding]
+        budget = max(self.max_batch_tokens - len(plan), 0)
+        prefilling = sorted((s for s in self.running if not s.decoding), key=lambda s: (s.remaining, s.submitted))
+        if not prefilling:
+            return plan
+        if budget == 0 and not plan:
+            budget = 1
+        oldest = min(prefilling, key=lambda s: s.submitted)
+        reserved = min(oldest.remaining, -(-budget // 2))
+        left = budget
+        for s in prefilling:
+            if s is oldest:
+                reserved = 0
+                avail = left
+            else:
+                avail = max(left - reserved, 0)
+            n = min(s.remaining, avail)
+            if n > 0:
+                plan.append((s, n))
+                left -= n
+        return plan
+
+    # -- one step ----------------------------------------------------------------
+    def step(self) -> StepOutput:
+        out = StepOutput()
+        self.steps += 1
+        for seq in [s for s in self.running if s.cancelled]:
+            self._finish(seq, FinishReason.CANCELLED, out)
+        decoding_now = sum(1 for s in self.running if s.decoding)
+        self._admit(max(self.max_batch_tokens - decoding_now, 1), out)
+
+        plan = self._plan()
+        # Pages: drop the most recently admitted request until the step fits.
+        while plan:
+            entries = [StepEntry(s.id, s.tokens[s.fed:s.fed + n]) for s, n in plan]
+            if self.engine.can_run(entries):
+                break
+            victim = max((s for s, _ in plan), key=lambda s: s.admitted)
+            if len(self.running) == 1:
+                self._finish(victim, FinishReason.ERROR, out,
+                             "the cache pool cannot hold this request even alone")
+            else:
+                # preempt the request admitted last, whether or not it is in this step's plan
+                victim = max(self.running, key=lambda s: s.admitted)
+                self._preempt(victim, out)
+            plan = [(s, n) for s, n in plan if s.state == SeqState.RUNNING]
+        if not plan:
+            out.active_sequences = len(self.running)
+            return out
+
+        entries, samplers = [], []
+        n_prefill = n_decode = 0
+        for s, n in plan:
+            last = s.fed + n == len(s.prompt) + len(s.output)
+            entries.append(StepEntry(s.id, s.tokens[s.fed:s.fed + n], [n - 1] if last else []))
+            if last:
+                samplers.append(s)
+            if s.decoding:
+                n_decode += 1
+            else:
+                n_prefill += n
+        t0 = time.perf_counter()
+        try:
+            logits = self.engine.step(entries)
+            picked = self.sampler(logits, [s.params for s in samplers], [s.seed for s in samplers],
+                                  [len(s.output) for s in samplers]) if samplers else []
+        except Exception as e:  # the step failed as a whole: its requests end with an error
+            if isinstance(e, (OutOfPages, KeyboardInterrupt)):
+                raise
+            for s, _ in plan:
+                self._finish(s, FinishReason.ERROR, out, f"step failed: {e}")
+            out.active_sequences = len(self.running)
+            return out
+        dt = time.perf_counter() - t0
+        for s, n in plan:
+            s.fed += n
+
+        for s, tok in zip(samplers, picked):
+            tok = int(tok)
+            if s.params.max_new_tokens == 0:
+                self._finish(s, FinishReason.LENGTH, out)
+                continue
+            if tok in self.eos_ids or tok in s.params.stop_ids:
+                self._finish(s, FinishReason.STOP, out)
+                continue
+            s.output.append(tok)
+            out.emitted.append((s.id, tok))
+            out.tokens_generated += 1
+            if self.on_token:
+                self.on_token(s.id, tok)
+            if len(s.prompt) + len(s.output) >= self.ctx or len(s.output) >= s.params.max_new_tokens:
+                self._finish(s, FinishReason.LENGTH, out)
+        total = max(n_prefill + n_decode, 1)
+        out.prefill = (dt * n_prefill / total, n_prefill)
+        out.decode = (dt * n_decode / total, n_decode)
+        out.active_sequences = len(self.running)
+        return out
+
+    # -- convenience -------------------------------------------------------------
+    def run(self, max_steps: Optional[int] = None) -> list:
+        """Step until nothing is left; returns the StepOutputs."""
+        outs = []
+        while self.has_work() and (max_steps is None or len(outs) < max_steps):
+            outs.append(self.step())
+        return outs
+
+    def generate(self, prompts: Sequence[Sequence[int]], params=None) -> list:
+        """Submit prompts, run to the end, return each one's generated ids."""
+        if params is None or isinstance(params, SamplingParams):
+            params = [params] * len(prompts)
+        ids = [self.submit(p, q) for p, q in zip(prompts, params)]
+        self.run()
+        return [list(self.sequences[i].output) for i in ids]

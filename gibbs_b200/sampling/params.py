@@ -1,0 +1,43 @@
+"""Per-request sampling controls.  Names, meanings and defaults follow
+MisterTK/gibbs ``SamplingParams`` and its constants
+(``src/scheduler/mod.rs:334-339, 405-446``; top-k 50: ``src/scheduler/mod.rs:178``)."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+DEFAULT_MAX_NEW_TOKENS = 64
+DEFAULT_TEMPERATURE = 1.0
+DEFAULT_TOP_P = 0.9
+DEFAULT_TOP_K = 50
+GREEDY_BELOW = 1e-4          # temperature at or below this is exact argmax (src/runtime/lm.rs:1073)
+MAX_TOP_K = 64               # src/runtime/lm.rs:1161
+
+
+@dataclass(frozen=True)
+class SamplingParams:
+    temperature: Optional[float] = None      # None: DEFAULT_TEMPERATURE; <= 0 is greedy
+    top_p: Optional[float] = None            # None: DEFAULT_TOP_P
+    top_k: int = DEFAULT_TOP_K               # 1..64
+    max_new_tokens: int = DEFAULT_MAX_NEW_TOKENS
+    seed: Optional[int] = None               # None: derived from the scheduler's seed and the request id
+    stop_ids: tuple = ()                     # besides the model's own end-of-sequence ids
+
+    def __post_init__(self):
+        if not 1 <= self.top_k <= MAX_TOP_K:
+            raise ValueError(f"top_k {self.top_k} outside 1..{MAX_TOP_K}")
+        if self.max_new_tokens < 0:
+            raise ValueError(f"max_new_tokens {self.max_new_tokens}")
+
+    @property
+    def resolved_temperature(self) -> float:
+        t = DEFAULT_TEMPERATURE if self.temperature is None else float(self.temperature)
+        return max(t, 0.0)
+
+    @property
+    def resolved_top_p(self) -> float:
+        return DEFAULT_TOP_P if self.top_p is None else float(self.top_p)
+
+    @property
+    def greedy(self) -> bool:
+        return self.resolved_temperature <= GREEDY_BELOW

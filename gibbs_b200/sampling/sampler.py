@@ -1,0 +1,58 @@
+"""Sampling on the device: one launch picks a token for every wanted logits
+row (greedy, or temperature with top-k and top-p; ``csrc/sampling.cu``).
+
+Randomness is counter based: the uniform number of a draw is SplitMix64 of
+(the request's seed, how many tokens it has drawn so far), so a run with a
+seed repeats, whatever the batching.  (The reference hashes the recent tokens
+instead, ``src/runtime/lm.rs:1125-1137``.)"""
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+
+from .. import ops
+from .params import SamplingParams
+
+_MASK = (1 << 64) - 1
+
+
+def uniform24(seed: int, counter: int) -> float:
+    """Host twin of the kernel's generator: a multiple of 2^-24 in [0, 1)."""
+    z = (seed + (counter + 1) * 0x9E3779B97F4A7C15) & _MASK
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _MASK
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _MASK
+    z ^= z >> 31
+    return (z >> 40) / float(1 << 24)
+
+
+def _signed(v: int) -> int:
+    v &= _MASK
+    return v - (1 << 64) if v >= (1 << 63) else v
+
+
+class Sampler:
+    def __init__(self, device):
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("the sampler is a CUDA kernel; there is no host path")
+
+    def __call__(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+                 counters: Sequence[int]) -> list[int]:
+        """One token id per row of ``logits`` ([rows, vocab] float32 on the device)."""
+        out = self.sample_device(logits, params, seeds, counters)
+        return out.tolist()
+
+    def sample_device(self, logits, params, seeds, counters) -> torch.Tensor:
+        rows = logits.shape[0]
+        out = torch.empty(rows, dtype=torch.int32, device=self.device)
+        if all(p.greedy for p in params):
+            return ops.sample(logits, out)
+        host = torch.tensor(
+            [[p.resolved_temperature if not p.greedy else 0.0, p.resolved_top_p] for p in params], dtype=torch.float32)
+        ints = torch.tensor([[p.top_k] for p in params], dtype=torch.int32)
+        longs = torch.tensor([[_signed(s), int(c)] for s, c in zip(seeds, counters)], dtype=torch.int64)
+        host, ints, longs = (t.to(self.device, non_blocking=True) for t in (host, ints, longs))
+        return ops.sample(logits, out, temperature=host[:, 0].contiguous(), top_k=ints[:, 0].contiguous(),
+                          top_p=host[:, 1].contiguous(), seed=longs[:, 0].contiguous(),
+                          counter=longs[:, 1].contiguous())

@@ -1,0 +1,75 @@
+"""An engine without a GPU for scheduler tests: the real cache manager on the
+host, and logits that are a pure function of the tokens a request has been
+fed, so that any rescheduling must reproduce them."""
+import torch
+
+from gibbs_b200.cache import CacheManager, OutOfPages
+from gibbs_b200.parts.base import PagedKV, SlotState
+
+
+def fake_next(tokens, vocab):
+    h = 17
+    for t in tokens:
+        h = (h * 31 + int(t) + 1) % 1000003
+    return h % vocab
+
+
+class FakeEngine:
+    def __init__(self, n_pages=64, page_size=4, max_requests=4, max_context=256, vocab=50, fail_on=None):
+        self.cache = CacheManager([([PagedKV(1, 2)], None), ([SlotState((2,))], None)], n_pages, page_size,
+                                  max_requests, torch.float32, "cpu", max_context)
+        self.max_requests, self.max_context, self.vocab = max_requests, max_context, vocab
+        self.fed = {}
+        self.log = []               # per step: [(request id, number of tokens, wanted?)]
+        self.fail_on = fail_on      # step index at which step() raises
+
+    def open(self, rid):
+        self.cache.open(rid)
+        self.fed[rid] = []
+
+    def close(self, rid):
+        self.cache.close(rid)
+        del self.fed[rid]
+
+    def can_run(self, entries):
+        need = 0
+        for e in entries:
+            rc = self.cache.live[e.request_id]
+            need += self.cache.pages_needed(rc.length + len(e.tokens)) - len(rc.block_tables[0])
+        return need <= self.cache.groups[0].pool.n_free
+
+    def step(self, entries):
+        if self.fail_on is not None and len(self.log) == self.fail_on:
+            self.log.append("failed")
+            raise RuntimeError("injected step failure")
+        if not self.can_run(entries):
+            raise OutOfPages("fake engine out of pages")
+        rows = []
+        for e in entries:
+            rc = self.cache.live[e.request_id]
+            self.cache.reserve(rc, rc.length + len(e.tokens))
+            self.cache.advance(rc, rc.length + len(e.tokens))
+            base = len(self.fed[e.request_id])
+            self.fed[e.request_id].extend(e.tokens)
+            for w in e.want:
+                row = torch.zeros(self.vocab)
+                row[fake_next(self.fed[e.request_id][:base + w + 1], self.vocab)] = 1.0
+                rows.append(row)
+        self.log.append([(e.request_id, len(e.tokens), bool(e.want)) for e in entries])
+        self.cache.check()
+        return torch.stack(rows) if rows else None
+
+
+def argmax_sampler(logits, params, seeds, counters):
+    return [int(torch.argmax(r)) for r in logits]
+
+
+def expected_greedy(prompt, n_new, vocab, eos=()):
+    toks, out = list(prompt), []
+    for _ in range(n_new):
+        t = fake_next(toks, vocab)
+        if t in eos:
+            break
+        toks.append(t)
+        out.append(t)
+    return out

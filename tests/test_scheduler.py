@@ -1,0 +1,186 @@
+"""The scheduler's decisions on a fake engine (no GPU).  The invariants follow
+the reference's own scheduler tests (MisterTK/gibbs src/scheduler/mod.rs:1632-1931):
+decoding never starves, a short prompt is not stuck behind a long one, a long
+prompt is not starved, max_new_tokens is exact, generation stops at the
+context's end, a cancelled request frees what it holds."""
+import pytest
+
+from fake_engine import FakeEngine, argmax_sampler, expected_greedy
+from gibbs_b200.engine.scheduler import FinishReason, Scheduler
+from gibbs_b200.sampling import SamplingParams
+
+GREEDY = SamplingParams(temperature=0.0, max_new_tokens=8)
+
+
+def _sched(engine, **kw):
+    return Scheduler(engine, argmax_sampler, **kw)
+
+
+def test_generate_matches_the_model_and_frees_everything():
+    eng = FakeEngine()
+    s = _sched(eng, max_batch_tokens=16)
+    prompts = [[3, 4, 5], list(range(1, 41)), [7]]
+    outs = s.generate(prompts, GREEDY)
+    assert outs == [expected_greedy(p, 8, eng.vocab) for p in prompts]
+    assert all(s.sequences[i].finish == FinishReason.LENGTH for i in range(3))
+    assert not eng.cache.live and eng.cache.free_pages() == [64] and eng.cache.slots.n_free == 4
+
+
+def test_token_budget_and_decodes_never_starve():
+    eng = FakeEngine(max_context=512)
+    s = _sched(eng, max_batch_tokens=10)
+    a = s.submit([1, 2], SamplingParams(temperature=0.0, max_new_tokens=30))
+    s.step()                                        # a is decoding from now on
+    b = s.submit(list(range(1, 101)), GREEDY)
+    while s.sequences[b].fed < 100:
+        before, left = len(s.sequences[a].output), 100 - s.sequences[b].fed
+        s.step()
+        step = eng.log[-1]
+        assert sum(n for _, n, _ in step) <= 10
+        if s.sequences[a].finish is None:
+            assert len(s.sequences[a].output) == before + 1      # one token every step
+            assert (a, 1, True) in step
+            assert dict((r, n) for r, n, _ in step)[b] == min(9, left)   # the rest of the budget goes to the prompt
+    s.run()
+    assert s.sequences[b].output == expected_greedy(list(range(1, 101)), 8, eng.vocab)
+
+
+def test_short_prompt_is_not_stuck_behind_a_long_one_and_long_is_not_starved():
+    eng = FakeEngine(max_context=512, n_pages=200)
+    s = _sched(eng, max_batch_tokens=16)
+    long_ = s.submit(list(range(1, 201)), GREEDY)
+    s.step()
+    short = s.submit([9, 9, 9], GREEDY)
+    s.step()
+    # the short prompt (shortest remaining first) got its three tokens and its first output
+    assert len(s.sequences[short].output) == 1
+    # the oldest prefilling request keeps at least half of the budget
+    assert dict((r, n) for r, n, _ in eng.log[-1])[long_] >= 8
+    for _ in range(40):
+        s.submit([5, 6], SamplingParams(temperature=0.0, max_new_tokens=1))
+    fed_before = s.sequences[long_].fed
+    for _ in range(6):
+        s.step()
+        assert dict((r, n) for r, n, _ in eng.log[-1]).get(long_, 0) >= 8 or s.sequences[long_].fed >= 200
+    assert s.sequences[long_].fed > fed_before
+    s.run()
+    assert s.sequences[long_].output == expected_greedy(list(range(1, 201)), 8, eng.vocab)
+
+
+def test_max_new_tokens_is_exact_and_zero_is_allowed():
+    eng = FakeEngine()
+    s = _sched(eng)
+    ids = [s.submit([1, 2, 3], SamplingParams(temperature=0.0, max_new_tokens=n)) for n in (0, 1, 5)]
+    s.run()
+    assert [len(s.sequences[i].output) for i in ids] == [0, 1, 5]
+    assert all(s.sequences[i].finish == FinishReason.LENGTH for i in ids)
+
+
+def test_stops_at_the_context_end_and_rejects_prompts_that_do_not_fit():
+    eng = FakeEngine(max_context=12)
+    s = _sched(eng)
+    i = s.submit(list(range(1, 9)), SamplingParams(temperature=0.0, max_new_tokens=100))
+    assert s.sequences[i].params.max_new_tokens == 4            # clamped at submission
+    s.run()
+    assert len(s.sequences[i].output) == 4 and s.sequences[i].finish == FinishReason.LENGTH
+    with pytest.raises(ValueError, match="context"):
+        s.submit(list(range(12)))
+    j = s.submit([])                                            # an empty prompt becomes token 1
+    assert s.sequences[j].prompt == [1]
+
+
+def test_stop_ids_are_not_emitted():
+    eng = FakeEngine()
+    want = expected_greedy([4, 4], 8, eng.vocab)
+    eos = want[3]
+    cut = want.index(eos)            # the id may occur earlier than the fourth token
+    s = _sched(eng, eos_ids=[eos])
+    i = s.submit([4, 4], GREEDY)
+    s.run()
+    assert s.sequences[i].output == want[:cut] and s.sequences[i].finish == FinishReason.STOP
+    s2 = _sched(FakeEngine())
+    j = s2.submit([4, 4], SamplingParams(temperature=0.0, max_new_tokens=8, stop_ids=(eos,)))
+    s2.run()
+    assert s2.sequences[j].output == want[:cut]
+
+
+def test_cancel_frees_pages_and_slot():
+    eng = FakeEngine()
+    s = _sched(eng, max_batch_tokens=8)
+    i = s.submit(list(range(1, 60)), GREEDY)
+    k = s.submit([1], GREEDY)
+    s.step()
+    assert eng.cache.free_pages()[0] < 64
+    s.cancel(i)
+    w = s.submit([2], GREEDY)
+    s.cancel(w)                                                # cancelled while still waiting
+    s.run()
+    assert s.sequences[i].finish == FinishReason.CANCELLED and s.sequences[w].finish == FinishReason.CANCELLED
+    assert s.sequences[k].finish == FinishReason.LENGTH
+    assert eng.cache.free_pages() == [64] and eng.cache.slots.n_free == 4 and not eng.cache.live
+
+
+def test_admission_waits_for_slots_first_come_first_served():
+    eng = FakeEngine(max_requests=2)
+    s = _sched(eng)
+    ids = [s.submit([i + 1], SamplingParams(temperature=0.0, max_new_tokens=3)) for i in range(5)]
+    order = []
+    while s.has_work():
+        out = s.step()
+        assert out.active_sequences <= 2 and len(eng.cache.live) <= 2
+        order += [i for i, _ in out.finished]
+    assert order == ids
+
+
+def test_pages_run_out_the_last_admitted_is_preempted_and_recomputed():
+    # 10 pages of 4 tokens; two requests that each grow to 28 tokens cannot both stay
+    eng = FakeEngine(n_pages=10, page_size=4, max_requests=4, max_context=64)
+    s = _sched(eng, max_batch_tokens=64)
+    p0, p1 = list(range(1, 13)), list(range(20, 32))
+    a = s.submit(p0, SamplingParams(temperature=0.0, max_new_tokens=16))
+    b = s.submit(p1, SamplingParams(temperature=0.0, max_new_tokens=16))
+    emitted, preempted = {a: [], b: []}, []
+    while s.has_work():
+        out = s.step()
+        for i, t in out.emitted:
+            emitted[i].append(t)
+        preempted += out.preempted
+        eng.cache.check()
+    assert preempted and set(preempted) == {b}                 # the one admitted last gives way
+    assert s.sequences[b].preemptions >= 1
+    # tokens are the same as without preemption, and none was emitted twice
+    assert emitted[a] == s.sequences[a].output == expected_greedy(p0, 16, eng.vocab)
+    assert emitted[b] == s.sequences[b].output == expected_greedy(p1, 16, eng.vocab)
+    assert eng.cache.free_pages() == [10] and not eng.cache.live
+
+
+def test_a_request_that_cannot_fit_alone_ends_with_an_error():
+    eng = FakeEngine(n_pages=2, page_size=4, max_context=64)
+    s = _sched(eng, max_batch_tokens=64)
+    big = s.submit(list(range(1, 20)), GREEDY)                 # first portion needs 5 pages
+    grow = s.submit([1, 2, 3], SamplingParams(temperature=0.0, max_new_tokens=30))   # outgrows 2 pages
+    s.run(max_steps=200)
+    assert s.sequences[big].finish == FinishReason.ERROR and "pool" in s.sequences[big].error
+    assert s.sequences[grow].finish == FinishReason.ERROR and len(s.sequences[grow].output) >= 5
+    assert eng.cache.free_pages() == [2] and not eng.cache.live
+
+
+def test_a_failing_step_ends_its_requests_with_an_error_and_the_loop_goes_on():
+    eng = FakeEngine(fail_on=1)
+    s = _sched(eng)
+    a = s.submit([1, 2, 3], GREEDY)
+    s.step()
+    out = s.step()
+    assert (a, FinishReason.ERROR) in out.finished and "injected" in s.sequences[a].error
+    assert not eng.cache.live
+    b = s.submit([1, 2, 3], GREEDY)
+    s.run()
+    assert s.sequences[b].output == expected_greedy([1, 2, 3], 8, eng.vocab)
+
+
+def test_seeds_are_per_request_and_reproducible():
+    s1, s2 = _sched(FakeEngine(), seed=5), _sched(FakeEngine(), seed=5)
+    ids1 = [s1.submit([1]), s1.submit([1], SamplingParams(seed=99))]
+    ids2 = [s2.submit([1]), s2.submit([1], SamplingParams(seed=99))]
+    assert [s1.sequences[i].seed for i in ids1] == [s2.sequences[i].seed for i in ids2]
+    assert s1.sequences[ids1[0]].seed != s1.sequences[ids1[1]].seed == 99
