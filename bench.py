@@ -1,0 +1,120 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the LFM2-1.2B shape on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B]
+
+Prints ONE JSON line.  ``value`` is decoded tokens a second at the given batch
+(device time over exactly K decode steps, CUDA events); ``e2e`` is the same
+through the Python entry point, with token ids coming from and going to the
+host every step; ``prefill`` times one whole prompt of 2,048 tokens; ``roofline``
+relates the decode step to the memory bandwidth; ``points`` holds batch 1 and 64.
+The model has random bfloat16 weights and uniform-random token ids (there is
+neither a checkpoint nor a dataset here).  Decode steps read 2.3 GB of
+weights each, far more than the L2 holds, so no flush is needed between steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# the benchmark configuration: layer sizes of the LFM2-1.2B shape
+LFM2_1P2B = dict(
+    architectures=["Lfm2ForCausalLM"], model_type="lfm2", hidden_size=2048, num_hidden_layers=16,
+    num_attention_heads=32, num_key_value_heads=8, head_dim=64, vocab_size=65536, intermediate_size=12288,
+    block_auto_adjust_ff_dim=True, block_ffn_dim_multiplier=1.0, block_multiple_of=256, conv_L_cache=3,
+    conv_bias=False, full_attn_idxs=[2, 5, 8, 10, 12, 14], rope_theta=1000000.0, norm_eps=1e-5, tie_embedding=True,
+    max_position_embeddings=4096,
+)
+SEED, PROMPT_LEN, CONTEXT = 2, 2048, 4096
+
+
+def reference_arm():
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "MisterTK/gibbs is a Rust crate with Apple Metal kernels: pip cannot install it "
+                      "(no setup.py or pyproject.toml), there is no cargo/rustc here, and it has no CUDA path"}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-points", action="store_true", help="skip batch 1 and 64")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        return reference_arm()
+    if a.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
+        return 2
+    a.warmup = max(a.warmup, 3)
+
+    import torch
+    from gibbs_b200 import Generator, Lfm2Config, random_model
+    from gibbs_b200.engine import benchmark as B
+
+    raw = dict(LFM2_1P2B)
+    full_layers = raw["num_hidden_layers"]
+    if a.layers is not None and a.layers < full_layers:
+        raw["num_hidden_layers"] = a.layers
+        raw["full_attn_idxs"] = [i for i in raw["full_attn_idxs"] if i < a.layers]
+    cfg = Lfm2Config.from_dict(raw)
+    peaks = B.load_peaks(ROOT)
+    torch.manual_seed(0)
+    model = random_model(cfg, SEED, dtype="bfloat16", device="cuda:0")
+
+    page_size = 16
+    max_batch = max(64, a.batch)
+    gen = Generator(model, ctx=CONTEXT, page_size=page_size, n_pages=max_batch * (CONTEXT // page_size),
+                    max_running=max_batch, max_batch_tokens=2048)
+    eng = gen.engine
+
+    pre = B.measure_prefill(eng, PROMPT_LEN, warmup=a.warmup, runs=5, seed=SEED)
+    pre_flops = B.prefill_flops(model, PROMPT_LEN)
+    pre["frac"] = pre_flops / (pre["ms"] / 1e3) / (peaks["bf16_tflops"] * 1e12)
+
+    with B.ClockSampler() as clocks:
+        dec = B.measure_decode(eng, a.batch, PROMPT_LEN, a.steps, a.warmup, seed=SEED)
+    e2e = B.measure_decode_e2e(gen, a.batch, PROMPT_LEN, a.steps, a.warmup, seed=SEED)
+    points = {}
+    if not a.skip_points:
+        for b in (1, 64):
+            if b != a.batch:
+                points[f"decode_b{b}"] = round(B.measure_decode(eng, b, PROMPT_LEN, a.steps, a.warmup, seed=SEED)["tok_s"], 1)
+
+    line = {
+        "metric": "LFM2-1.2B decode tok/s", "value": round(dec["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(dec["ms_per_step"], 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights N(0, 0.02) seed 2, uniform-random token ids",
+        "config": {
+            "model": "LFM2-1.2B shape", "global_batch": a.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN,
+            "parallelism": "none (1 GPU)", "layers": cfg.num_hidden_layers, "layers_full": full_layers,
+            "attention_layers": len(cfg.attention_layers), "hidden": cfg.hidden_size,
+            "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+            "ffn": cfg.ffn_dim, "vocab": cfg.vocab_size, "conv_L_cache": cfg.conv_L_cache, "page_size": page_size,
+            "l2": "step inputs (2.3 GB of weights) exceed L2; no flush",
+        },
+        "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items()},
+        "gpu_launches": dec["launches"],
+        "prefill": {"value": round(pre["value"], 1), "tokens": pre["tokens"], "ms": round(pre["ms"], 3),
+                    "frac": round(pre["frac"], 4)},
+        "roofline": {"bound": "hbm", "achieved": round(dec["gbs"], 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(dec["gbs"] / peaks["hbm_gbs"], 4), "peaks": peaks["source"]},
+        "points": points,
+        "clocks": clocks.summary(),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

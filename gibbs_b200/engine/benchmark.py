@@ -1,0 +1,230 @@
+"""Measurement of prefill and decode throughput, shared by ``bench.py`` and the
+command line's ``--bench``.
+
+Method after MisterTK/gibbs ``src/bench.rs:219-322``: warm-up, then timed
+decode steps; the roofline of a decode step is the bytes it must read (every
+weight once, and the cache of the live requests) over the memory bandwidth
+(``src/bench.rs:298-308``, ``src/graph/program.rs:330-341``).  Times are taken
+with CUDA events on the launching stream, after a synchronise.
+"""
+from __future__ import annotations
+
+import json
+import statistics
+import subprocess
+import threading
+import time
+from pathlib import Path
+from typing import Optional
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..sampling import Sampler, SamplingParams
+from .scheduler import Scheduler
+from .step import Engine, StepEntry
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def load_peaks(repo_root) -> dict:
+    """Measured copy bandwidth (GB/s) and bf16 matrix throughput (TFLOP/s) of
+    this pool's GPUs if a ``MEASURED_PEAKS.json`` lies at the repository root,
+    else the stated fallback figures."""
+    p = Path(repo_root) / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            out = {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+            if "bf16_tflops_sustained" in d:
+                out["bf16_tflops_sustained"] = float(d["bf16_tflops_sustained"])
+            return out
+        except (KeyError, ValueError, json.JSONDecodeError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed
+    region runs (reading only; nothing is set)."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0, period_ms: int = 200):
+        self.index, self.period_ms = index, period_ms
+        self.proc, self.lines = None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-i", str(self.index),
+                 "-lms", str(self.period_ms)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self._t = threading.Thread(target=self._read, daemon=True)
+            self._t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        mhz, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                mhz.append(float(f[0]))
+                mx = max(mx, float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def model_flops_per_token(model) -> int:
+    """Multiply-adds x2 of every projection a token passes through (the head
+    is counted separately, per wanted row)."""
+    head = model.head.proj.weight
+    total = 0
+    seen = {head.data_ptr()}
+    for b in model.blocks:
+        for holder in (b.mixer, b.ffn):
+            for v in vars(holder).values():
+                w = getattr(v, "weight", None)
+                if isinstance(w, torch.Tensor) and w.dim() == 2 and w.data_ptr() not in seen:
+                    seen.add(w.data_ptr())
+                    total += 2 * w.numel()
+    return total
+
+
+def prefill_flops(model, n_tokens: int, n_logit_rows: int = 1) -> int:
+    fl = model_flops_per_token(model) * n_tokens + 2 * model.head.proj.weight.numel() * n_logit_rows
+    for b in model.blocks:
+        m = b.mixer
+        if hasattr(m, "heads") and hasattr(m, "head_dim"):
+            # scores and weighted values over the causal half: 2 * 2 * hd * T(T+1)/2 per head
+            fl += 2 * m.heads * m.head_dim * n_tokens * (n_tokens + 1)
+    return fl
+
+
+def _events():
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def measure_prefill(engine: Engine, n_tokens: int, warmup: int = 3, runs: int = 5, seed: int = 0) -> dict:
+    """Time from the first token of a whole prompt to its last-row logits, one step."""
+    rng = np.random.default_rng(seed)
+    times = []
+    for i in range(warmup + runs):
+        ids = rng.integers(0, engine.vocab_size, n_tokens).tolist()
+        engine.open("prefill-bench")
+        torch.cuda.synchronize()
+        a, b = _events()
+        a.record()
+        engine.step([StepEntry("prefill-bench", ids, [n_tokens - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        engine.close("prefill-bench")
+        if i >= warmup:
+            times.append(a.elapsed_time(b))
+    ms = statistics.median(times)
+    return {"ms": ms, "tokens": n_tokens, "value": n_tokens / (ms / 1e3)}
+
+
+def fill_contexts(engine: Engine, batch: int, prompt_len: int, seed: int, chunk: int = 2048) -> list:
+    """Open ``batch`` requests and run their random prompts; returns the ids
+    picked greedily from the last prompt position of each."""
+    rng = np.random.default_rng(seed)
+    sampler = Sampler(engine.device)
+    first = []
+    for r in range(batch):
+        ids = rng.integers(0, engine.vocab_size, prompt_len).tolist()
+        engine.open(("bench", r))
+        for lo in range(0, prompt_len, chunk):
+            part = ids[lo:lo + chunk]
+            last = lo + chunk >= prompt_len
+            logits = engine.step([StepEntry(("bench", r), part, [len(part) - 1] if last else [])])
+        first.append(sampler(logits, [SamplingParams(temperature=0.0)], [0], [0])[0])
+    return first
+
+
+def measure_decode(engine: Engine, batch: int, prompt_len: int, steps: int, warmup: int, seed: int = 0) -> dict:
+    """``steps`` decode steps of ``batch`` requests whose contexts start at
+    ``prompt_len``: every step feeds each request its last token, takes the
+    logits and picks the next token greedily on the device."""
+    tokens = fill_contexts(engine, batch, prompt_len, seed)
+    sampler = Sampler(engine.device)
+    greedy = [SamplingParams(temperature=0.0)] * batch
+    zeros = [0] * batch
+
+    def one_step(tokens):
+        logits = engine.step([StepEntry(("bench", r), [tokens[r]], [0]) for r in range(batch)])
+        return sampler(logits, greedy, zeros, zeros)
+
+    for _ in range(warmup):
+        tokens = one_step(tokens)
+    launches0 = ops.launch_count()
+    torch.cuda.synchronize()
+    a, b = _events()
+    t0 = time.perf_counter()
+    a.record()
+    for _ in range(steps):
+        tokens = one_step(tokens)
+    b.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    ms = a.elapsed_time(b)
+    ctx = [engine.length(("bench", r)) for r in range(batch)]
+    bytes_step = engine.model.weight_bytes_per_step() + sum(ctx) * engine.cache.kv_bytes_per_token() \
+        + batch * engine.cache.slot_bytes
+    for r in range(batch):
+        engine.close(("bench", r))
+    return {"batch": batch, "steps": steps, "ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3),
+            "wall_ms_per_step": wall * 1e3 / steps, "bytes_per_step": bytes_step,
+            "gbs": bytes_step / (ms / steps / 1e3) / 1e9, "launches": ops.launch_count() - launches0,
+            "context": int(statistics.mean(ctx))}
+
+
+def measure_decode_e2e(generator, batch: int, prompt_len: int, steps: int, warmup: int, seed: int = 0) -> dict:
+    """The same through the public entry point's scheduler: token ids come from
+    host lists, every step copies its inputs from pinned host memory and reads
+    the picked ids back to the host."""
+    rng = np.random.default_rng(seed)
+    sched: Scheduler = generator.scheduler(stop_at_eos=False)
+    params = SamplingParams(temperature=0.0, max_new_tokens=warmup + steps + 4)
+    for _ in range(batch):
+        sched.submit(rng.integers(0, generator.engine.vocab_size, prompt_len).tolist(), params)
+    while any(not s.decoding for s in sched.sequences.values()):
+        sched.step()
+    for _ in range(warmup):
+        sched.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    n = 0
+    for _ in range(steps):
+        n += sched.step().tokens_generated
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    for sid in list(sched.sequences):
+        sched.cancel(sid)
+    sched.step()
+    meta_ints = 3 * 4 * ((batch + 3) // 4) + 6 * 4 * ((batch + 3) // 4) \
+        + len(generator.engine.cache.groups) * batch * generator.engine.cache.max_blocks
+    return {"value": n / dt, "unit": "tokens/s", "h2d_bytes_per_step": 4 * meta_ints, "d2h_bytes_per_step": 4 * batch,
+            "ms_per_step": dt * 1e3 / steps}

@@ -20,6 +20,20 @@ _DT = {torch.float32: F32, torch.bfloat16: BF16}
 _c_int, _c_ll, _c_float, _c_void = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
 
 
+_LAUNCHES = 0
+
+
+def _launched(n: int = 1) -> None:
+    global _LAUNCHES
+    _LAUNCHES += n
+
+
+def launch_count() -> int:
+    """Kernels of this package launched so far in this process (each wrapper
+    adds the number of kernels its call enqueues)."""
+    return _LAUNCHES
+
+
 def dtype_code(dt: torch.dtype) -> int:
     try:
         return _DT[dt]
@@ -71,6 +85,7 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Te
     if not table.is_contiguous() or table.shape[1] != dim or out.dtype != torch.float32 or not out.is_contiguous():
         raise KernelError("embed: table [vocab, dim] contiguous and out [n, dim] float32 contiguous expected")
     _i32(ids, "embed ids")
+    _launched(1)
     check(lib, lib.gb_embed(_ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out), _c_int(n), _c_int(dim),
                             _c_int(table.shape[0]), _stream()))
     return out
@@ -92,6 +107,7 @@ def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
         raise KernelError("rmsnorm: out has a different number of rows than x")
     _f32vec(gain, dim, "rmsnorm gain")
     _i32(rows, "rmsnorm rows")
+    _launched(1)
     check(lib, lib.gb_rmsnorm(_ptr(x), _c_ll(ldx), _ptr(gain), _ptr(out), dtype_code(out.dtype), _ptr(rows),
                               _c_int(n_rows), _c_int(dim), _c_float(eps), _stream()))
     return out
@@ -107,6 +123,7 @@ def linear_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
     if w.shape[1] != k or out.shape[0] != m or out.shape[1] != n:
         raise KernelError(f"linear: shapes a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} disagree")
     _f32vec(bias, n, "linear bias")
+    _launched(1)
     check(lib, lib.gb_linear_simt(
         _ptr(a), dtype_code(a.dtype), _c_ll(_rows(a, "linear a")), _ptr(w), dtype_code(w.dtype),
         _c_ll(_rows(w, "linear w")), _ptr(bias), _ptr(out), dtype_code(out.dtype), _c_ll(_rows(out, "linear out")),
@@ -133,6 +150,7 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     if gate_up.shape != (n, 2 * inner) or not gate_up.is_contiguous() or not out.is_contiguous() \
             or gate_up.dtype != out.dtype:
         raise KernelError("swiglu: gate_up [n, 2*inner] and out [n, inner], contiguous, same dtype expected")
+    _launched(1)
     check(lib, lib.gb_swiglu(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), _c_int(n), _c_int(inner), _stream()))
     return out
 
@@ -142,6 +160,7 @@ def cast(src: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     lib = library("core")
     if not src.is_contiguous() or not out.is_contiguous() or src.numel() != out.numel():
         raise KernelError("cast: contiguous tensors of equal size expected")
+    _launched(1)
     check(lib, lib.gb_cast(_ptr(src), dtype_code(src.dtype), _ptr(out), dtype_code(out.dtype),
                            _c_ll(src.numel()), _stream()))
     return out
@@ -164,6 +183,7 @@ def short_conv(bcx: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tenso
         raise KernelError(f"short_conv: state must be float32 [slots, {kk - 1}, {hidden}] with contiguous slots")
     for t, w in ((slot_ids, "slot_ids"), (tok_req, "tok_req"), (q_start, "q_start"), (q_len, "q_len")):
         _i32(t, "short_conv " + w)
+    _launched(2)
     check(lib, lib.gb_short_conv(
         _ptr(bcx), dtype_code(bcx.dtype), _c_ll(_rows(bcx, "short_conv bcx")), _ptr(taps), _ptr(bias), _ptr(state),
         _c_ll(state.stride(0)), _ptr(slot_ids), _ptr(tok_req), _ptr(q_start), _ptr(q_len), _ptr(out), _c_int(n),
@@ -205,6 +225,7 @@ def qk_norm_rope_store(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: i
     if write:
         _check_pages(k_pages, v_pages, kv_heads, head_dim, qkv.dtype, "qk_norm_rope_store")
         page_size, n_pages = k_pages.shape[2], k_pages.shape[0]
+    _launched(1)
     check(lib, lib.gb_qk_norm_rope_store(
         _ptr(qkv), dtype_code(qkv.dtype), _c_ll(_rows(qkv, "qkv")), _ptr(q_gain), _ptr(k_gain), _c_float(eps),
         _ptr(inv_freq), _c_int(rotary_dim), _c_int(1 if adjacent_pairs else 0), _ptr(tok_req), _ptr(tok_pos),
@@ -225,6 +246,7 @@ def paged_attention(q: torch.Tensor, heads: int, kv_heads: int, head_dim: int, k
         raise KernelError("paged_attention: q and out must be [n, heads*head_dim] of one dtype")
     _check_pages(k_pages, v_pages, kv_heads, head_dim, q.dtype, "paged_attention")
     _i32(tok_req, "tok_req"), _i32(tok_pos, "tok_pos"), _i32(block_table, "block_table"), _i32(status, "status")
+    _launched(1)
     check(lib, lib.gb_paged_attention(
         _ptr(q), dtype_code(q.dtype), _c_ll(_rows(q, "q")), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
         _c_int(block_table.shape[1]), _c_int(k_pages.shape[2]), _c_int(k_pages.shape[0]), _ptr(tok_req),
@@ -248,6 +270,7 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
     for t, w in ((seed, "seed"), (counter, "counter")):
         if t is not None and (t.dtype != torch.int64 or t.numel() != rows or not t.is_contiguous()):
             raise KernelError(f"sample {w}: expected {rows} int64 values")
+    _launched(1)
     check(lib, lib.gb_sample(_ptr(logits), _c_ll(_rows(logits, "logits")), _c_int(rows), _c_int(vocab),
                              _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(seed), _ptr(counter), _ptr(out),
                              _stream()))
