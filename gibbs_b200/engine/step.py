@@ -83,7 +83,7 @@ class Engine:
         self._staging_evt = [None] * 4
         self._turn = 0
         self._dev_meta = torch.empty(cap, dtype=torch.int32, device=self.device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.status = ops.device_status(self.device)
         self.steps_run = 0
 
     # -- request life ----------------------------------------------------------
@@ -227,5 +227,8 @@ class Engine:
         code = int(self.status.item())
         if code:
             self.status.zero_()
+            if code >= 16:
+                raise StepError(f"a bounded wait inside a tensor-core kernel ran out (code {code}); "
+                                "the kernel released what it held and returned, its output is invalid")
             raise StepError(f"a cache kernel met a page id outside its pool (code {code}); "
                             "the block tables and the pools disagree")

@@ -133,12 +133,65 @@ def linear_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
 
 def linear_libraries(weight_dtype: torch.dtype, compute_dtype: torch.dtype):
     """Kernel libraries a projection with these operand types launches from."""
+    if weight_dtype == torch.bfloat16 and compute_dtype == torch.bfloat16:
+        return ("core", "tensorcore")
     return ("core",)
+
+
+_STATUS: dict = {}
+
+
+def device_status(device) -> torch.Tensor:
+    """The int32 word of ``device`` that kernels set when a bounded wait ran
+    out or a page id was outside its pool (0: nothing happened)."""
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    t = _STATUS.get(key)
+    if t is None:
+        t = _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return t
+
+
+def linear_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+              accumulate: bool = False) -> torch.Tensor:
+    """out (+)= a @ w.T (+ bias) for bfloat16 a and w on the tensor cores (csrc/gemm_tc.cu)."""
+    _need_cuda(a, w, bias, out)
+    lib = library("tensorcore")
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape[0] != m or out.shape[1] != n:
+        raise KernelError(f"linear: shapes a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} disagree")
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("linear_tc: bfloat16 operands expected")
+    _f32vec(bias, n, "linear bias")
+    lib.gb_linear_tc_workspace.restype = ctypes.c_longlong
+    need = lib.gb_linear_tc_workspace(_c_int(m), _c_int(n), _c_int(k))
+    ws = torch.empty(need, dtype=torch.float32, device=a.device) if need else None
+    rc = lib.gb_linear_tc(
+        _ptr(a), _c_ll(_rows(a, "linear a")), _ptr(w), _c_ll(_rows(w, "linear w")), _ptr(bias), _ptr(out),
+        dtype_code(out.dtype), _c_ll(_rows(out, "linear out")), _c_int(1 if accumulate else 0), _c_int(m), _c_int(n),
+        _c_int(k), _ptr(ws), _ptr(device_status(a.device)), _stream())
+    if rc < 0:
+        check(lib, rc)
+    _launched(rc)
+    return out
+
+
+def linear_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.dim() != 2 or w.dim() != 2:
+        return False
+    k = a.shape[1]
+    return (k % 8 == 0 and a.stride(1) == 1 and w.stride(1) == 1 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
            accumulate: bool = False) -> torch.Tensor:
-    """out (+)= a @ w.T (+ bias); picks the matrix-product kernel for the operand types."""
+    """out (+)= a @ w.T (+ bias); picks the matrix-product kernel for the
+    operand types: tensor cores for bfloat16 x bfloat16, 32-bit FMA otherwise
+    (float32 operands, a weight kept in 32-bit, rows TMA cannot address)."""
+    if linear_tc_supported(a, w):
+        return linear_tc(a, w, bias, out, accumulate)
     return linear_simt(a, w, bias, out, accumulate)
 
 

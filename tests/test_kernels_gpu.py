@@ -1,0 +1,431 @@
+"""Each CUDA kernel alone against a plain float64 reference of the same
+operation written here, at sizes other than the engine's tiny models: widths
+and vocabularies that are no power of two, head sizes in steps of 16, odd
+numbers of heads and groups."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _dt(name):
+    return torch.bfloat16 if name == "bfloat16" else torch.float32
+
+
+def _close(got, want, dtype, scale=None):
+    got = got.detach().double().cpu()
+    want = want.double()
+    tol = 2e-2 if dtype == "bfloat16" else 2e-5
+    err = (got - want).abs().max().item()
+    ref = (scale if scale is not None else want.abs().max().item()) + 1e-30
+    assert err / ref < tol, f"max abs err {err:.3g} against scale {ref:.3g}"
+
+
+def _quant(t, dtype):
+    """Round to the kernel's storage dtype, return (device tensor, float64 copy of the rounded values)."""
+    d = t.to(_dt(dtype))
+    return d.to(DEV), d.double()
+
+
+# --------------------------------------------------------------------------- embed / norm / swiglu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embed(dtype):
+    from gibbs_b200 import ops
+    torch.manual_seed(0)
+    table, ref = _quant(torch.randn(1000, 96), dtype)
+    ids = torch.tensor([0, 999, 5, 5, 123], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 96, dtype=torch.float32, device=DEV)
+    ops.embed(table, ids, out)
+    assert torch.equal(out.cpu().double(), ref[ids.cpu().long()])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dim,eps", [(96, 1e-6), (2048, 1e-5), (1000, 1e-5), (7, 1e-3)])
+def test_rmsnorm_with_row_gather(dtype, dim, eps):
+    from gibbs_b200 import ops
+    torch.manual_seed(1)
+    x = torch.randn(9, dim) * 3
+    g = 1 + 0.1 * torch.randn(dim)
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32)
+    want = x.double() / torch.sqrt((x.double() ** 2).mean(-1, keepdim=True) + eps) * g.double()
+    out = torch.empty(9, dim, dtype=_dt(dtype), device=DEV)
+    ops.rmsnorm(x.to(DEV), g.to(DEV), eps, out)
+    _close(out, want, dtype)
+    out = torch.empty(3, dim, dtype=_dt(dtype), device=DEV)
+    ops.rmsnorm(x.to(DEV), g.to(DEV), eps, out, rows.to(DEV))
+    _close(out, want[rows.long()], dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_swiglu(dtype):
+    from gibbs_b200 import ops
+    torch.manual_seed(2)
+    gu, ref = _quant(torch.randn(13, 2 * 200) * 2, dtype)
+    out = torch.empty(13, 200, dtype=_dt(dtype), device=DEV)
+    ops.swiglu(gu, out)
+    g, u = ref[:, :200], ref[:, 200:]
+    _close(out, g / (1 + torch.exp(-g)) * u, dtype)
+
+
+# --------------------------------------------------------------------------- matrix products
+SHAPES = [(1, 64, 64), (3, 100, 72), (16, 192, 64), (17, 256, 96), (40, 1000, 200), (64, 2048, 2048),
+          (130, 384, 520), (300, 136, 1032), (8, 6144, 2048)]
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES)
+@pytest.mark.parametrize("pair", ["f32xf32", "bf16xbf16", "bf16xf32"])
+def test_linear_simt(m, n, k, pair):
+    from gibbs_b200 import ops
+    torch.manual_seed(m * 7 + n)
+    ad, wd = {"f32xf32": ("float32", "float32"), "bf16xbf16": ("bfloat16", "bfloat16"),
+              "bf16xf32": ("bfloat16", "float32")}[pair]
+    a, ar = _quant(torch.randn(m, k), ad)
+    w, wr = _quant(torch.randn(n, k) / math.sqrt(k), wd)
+    bias = torch.randn(n)
+    want = ar @ wr.T + bias.double()
+    out = torch.empty(m, n, dtype=_dt(ad), device=DEV)
+    ops.linear_simt(a, w, bias.to(DEV), out)
+    _close(out, want, ad)
+    res = torch.randn(m, n)
+    acc = res.clone().to(DEV)
+    ops.linear_simt(a, w, None, acc, accumulate=True)
+    _close(acc, res.double() + ar @ wr.T, "float32" if ad == "float32" else "float32", scale=want.abs().max().item())
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES + [(2048, 512, 2048), (1, 65536 // 8, 2048), (257, 130, 8)])
+def test_linear_tensor_cores(m, n, k):
+    """bf16 x bf16 on tcgen05: bf16 store, f32 store, f32 accumulate, with and
+    without bias, including the split-K sizes."""
+    from gibbs_b200 import ops
+    torch.manual_seed(m + n + k)
+    a, ar = _quant(torch.randn(m, k), "bfloat16")
+    w, wr = _quant(torch.randn(n, k) / math.sqrt(k), "bfloat16")
+    assert ops.linear_tc_supported(a, w)
+    bias = torch.randn(n)
+    exact = ar @ wr.T
+    scale = exact.abs().max().item()
+    out = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+    ops.linear_tc(a, w, None, out)
+    _close(out, exact, "float32", scale)            # f32 accumulation of exact bf16 products
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops.linear_tc(a, w, bias.to(DEV), out)
+    _close(out, exact + bias.double(), "bfloat16")
+    res = torch.randn(m, n)
+    acc = res.clone().to(DEV)
+    ops.linear_tc(a, w, bias.to(DEV), acc, accumulate=True)
+    _close(acc, res.double() + exact + bias.double(), "float32", scale + 3)
+    assert int(ops.device_status(DEV).item()) == 0
+
+
+def test_linear_tensor_cores_strided_rows():
+    """Operands that are column slices of wider rows (their row stride is not their width)."""
+    from gibbs_b200 import ops
+    torch.manual_seed(5)
+    wide, _ = _quant(torch.randn(50, 3 * 128), "bfloat16")
+    a = wide[:, 128:256]
+    w, wr = _quant(torch.randn(72, 128) / 11, "bfloat16")
+    out = torch.empty(50, 72, dtype=torch.float32, device=DEV)
+    ops.linear(a, w, None, out)
+    _close(out, a.double().cpu() @ wr.T, "float32")
+
+
+def test_linear_falls_back_when_tma_cannot_address_the_rows():
+    from gibbs_b200 import ops
+    a, ar = _quant(torch.randn(5, 36), "bfloat16")          # 36 % 8 != 0
+    w, wr = _quant(torch.randn(20, 36), "bfloat16")
+    assert not ops.linear_tc_supported(a, w)
+    out = torch.empty(5, 20, dtype=torch.bfloat16, device=DEV)
+    ops.linear(a, w, None, out)
+    _close(out, ar @ wr.T, "bfloat16")
+
+
+# --------------------------------------------------------------------------- short convolution
+def _plain_conv(bcx, taps, bias, state, q_lens):
+    """bcx [n, 3h] float64 rows of [B | C | x]; returns (out, new states)."""
+    h, k = taps.shape
+    outs, new_states, row = [], [], 0
+    for r, n in enumerate(q_lens):
+        b, c, x = (bcx[row:row + n, i * h:(i + 1) * h] for i in range(3))
+        win = torch.cat([state[r], b * x], 0)
+        cv = sum(win[j:j + n] * taps[:, j][None, :] for j in range(k))
+        if bias is not None:
+            cv = cv + bias[None, :]
+        outs.append(c * cv)
+        new_states.append(win[n:])
+        row += n
+    return torch.cat(outs, 0), torch.stack(new_states, 0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden,k,use_bias", [(96, 4, True), (200, 2, False), (64, 7, True)])
+def test_short_conv_ragged_batch(dtype, hidden, k, use_bias):
+    from gibbs_b200 import ops
+    torch.manual_seed(hidden + k)
+    q_lens = [1, 5, 2, 1, k - 1, 11]                       # decode tokens, portions shorter than the state, longer ones
+    n = sum(q_lens)
+    bcx, ref = _quant(torch.randn(n, 3 * hidden), dtype)
+    taps = torch.randn(hidden, k)
+    bias = torch.randn(hidden) if use_bias else None
+    n_slots = 9
+    state = torch.randn(n_slots, 2, k - 1, hidden)          # slot axis strided: [slots, 2 (another tenant), k-1, h]
+    slot_ids = [7, 0, 3, 8, 2, 5]
+    dev_state = state.to(DEV)
+    view = dev_state[:, 1]
+    q_start = np.cumsum([0] + q_lens[:-1]).astype(np.int32)
+    tok_req = np.repeat(np.arange(len(q_lens)), q_lens).astype(np.int32)
+    out = torch.empty(n, hidden, dtype=_dt(dtype), device=DEV)
+    t = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    ops.short_conv(bcx, taps.to(DEV), None if bias is None else bias.to(DEV), view, t(slot_ids), t(tok_req),
+                   t(q_start), t(q_lens), out)
+    want, new_state = _plain_conv(ref, taps.double(), None if bias is None else bias.double(),
+                                  state[slot_ids, 1].double(), q_lens)
+    _close(out, want, dtype)
+    got_state = dev_state.cpu()
+    assert torch.allclose(got_state[slot_ids, 1].double(), new_state, rtol=1e-6, atol=1e-6)
+    untouched = [s for s in range(n_slots) if s not in slot_ids]
+    assert torch.equal(got_state[untouched], state[untouched]) and torch.equal(got_state[:, 0], state[:, 0])
+
+
+def test_short_conv_refuses_wide_kernels():
+    from gibbs_b200 import ops
+    from gibbs_b200.ops import KernelError
+    z = lambda *s, d=torch.float32: torch.zeros(*s, dtype=d, device=DEV)
+    with pytest.raises(KernelError, match="outside 2..16"):
+        ops.short_conv(z(1, 24), z(8, 17), None, z(1, 16, 8), z(1, d=torch.int32), z(1, d=torch.int32),
+                       z(1, d=torch.int32), torch.ones(1, dtype=torch.int32, device=DEV), z(1, 8))
+
+
+# --------------------------------------------------------------------------- attention
+def _plain_rope(x, pos, inv, rd, adjacent):
+    out = x.clone()
+    ang = (pos.float()[:, None] * inv.float()[None, :]).double()[:, None, :]
+    c, s = torch.cos(ang), torch.sin(ang)
+    if adjacent:
+        a, b = x[..., 0:rd:2], x[..., 1:rd:2]
+        out[..., 0:rd:2], out[..., 1:rd:2] = a * c - b * s, a * s + b * c
+    else:
+        a, b = x[..., :rd // 2], x[..., rd // 2:rd]
+        out[..., :rd // 2], out[..., rd // 2:rd] = a * c - b * s, a * s + b * c
+    return out
+
+
+def _layout(lengths_before, q_lens, page_size, n_pages, seed):
+    """Random distinct pages for each request; returns metadata arrays."""
+    rng = np.random.default_rng(seed)
+    perm = rng.permutation(n_pages)
+    max_blocks = max(-(-(a + b) // page_size) for a, b in zip(lengths_before, q_lens)) + 1
+    bt = np.full((len(q_lens), max_blocks), -1, dtype=np.int32)
+    used = 0
+    for r, (a, b) in enumerate(zip(lengths_before, q_lens)):
+        nb = -(-(a + b) // page_size)
+        bt[r, :nb] = perm[used:used + nb]
+        used += nb
+    assert used <= n_pages
+    tok_req = np.repeat(np.arange(len(q_lens)), q_lens).astype(np.int32)
+    tok_pos = np.concatenate([np.arange(a, a + b) for a, b in zip(lengths_before, q_lens)]).astype(np.int32)
+    return bt, tok_req, tok_pos
+
+
+CASES = [
+    # heads, kv_heads, head_dim, rotary_dim, adjacent, page_size, window, norm
+    (4, 2, 16, 16, False, 16, 0, True),
+    (3, 1, 32, 32, False, 8, 0, True),
+    (6, 3, 48, 32, True, 4, 0, False),
+    (8, 2, 64, 64, False, 16, 0, True),
+    (5, 5, 80, 80, False, 32, 0, True),
+    (2, 1, 128, 64, False, 16, 0, False),
+    (4, 2, 16, 16, False, 8, 7, True),
+    (8, 8, 8, 8, False, 16, 0, True),
+]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,kvh,hd,rd,adjacent,ps,window,norm", CASES)
+def test_qk_norm_rope_store_then_attention(dtype, heads, kvh, hd, rd, adjacent, ps, window, norm):
+    """A ragged batch against earlier context: requests with 0, some and many
+    cached positions, portions and single tokens, pages in random order."""
+    from gibbs_b200 import ops
+    torch.manual_seed(heads * 100 + hd)
+    before = [0, 37, 5, 130, 64]
+    q_lens = [9, 1, 20, 1, 3]
+    n_pages = 96
+    bt, tok_req, tok_pos = _layout(before, q_lens, ps, n_pages, seed=hd)
+    n = sum(q_lens)
+    width = (heads + 2 * kvh) * hd
+    eps = 1e-5
+    qkv, ref = _quant(torch.randn(n, width), dtype)
+    qg, kg = (1 + 0.2 * torch.randn(hd), 1 + 0.2 * torch.randn(hd)) if norm else (None, None)
+    inv = torch.tensor([1.0 / (10000.0 ** (2 * j / rd)) for j in range(rd // 2)], dtype=torch.float32)
+    # earlier context: keys/values already in the pages (post-norm, post-rope values, arbitrary)
+    k_ctx = [torch.randn(b, kvh, hd) for b in before]
+    v_ctx = [torch.randn(b, kvh, hd) for b in before]
+    kp = torch.zeros(n_pages, kvh, ps, hd)
+    vp = torch.zeros(n_pages, kvh, ps, hd)
+    for r, b in enumerate(before):
+        for p in range(b):
+            kp[bt[r, p // ps], :, p % ps] = k_ctx[r][p]
+            vp[bt[r, p // ps], :, p % ps] = v_ctx[r][p]
+    kp_d, kp_ref = _quant(kp, dtype)
+    vp_d, vp_ref = _quant(vp, dtype)
+    t = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    dev = lambda x: None if x is None else x.to(DEV)
+    ops.qk_norm_rope_store(qkv, heads, kvh, hd, dev(qg), dev(kg), eps, inv.to(DEV), rd, adjacent, t(tok_req),
+                           t(tok_pos), t(bt), kp_d, vp_d, status)
+    # plain: norm, rope
+    q = ref[:, :heads * hd].reshape(n, heads, hd)
+    k = ref[:, heads * hd:(heads + kvh) * hd].reshape(n, kvh, hd)
+    v = ref[:, (heads + kvh) * hd:].reshape(n, kvh, hd)
+    if norm:
+        q = q / torch.sqrt((q * q).mean(-1, keepdim=True) + eps) * qg.double()
+        k = k / torch.sqrt((k * k).mean(-1, keepdim=True) + eps) * kg.double()
+    pos = torch.tensor(tok_pos)
+    q, k = _plain_rope(q, pos, inv, rd, adjacent), _plain_rope(k, pos, inv, rd, adjacent)
+    _close(qkv[:, :heads * hd], q.reshape(n, -1), dtype)
+    # the new keys and values landed in their pages; nothing else changed
+    kp_want, vp_want = kp_ref.clone(), vp_ref.clone()
+    for i in range(n):
+        r, p = tok_req[i], tok_pos[i]
+        kp_want[bt[r, p // ps], :, p % ps] = k[i]
+        vp_want[bt[r, p // ps], :, p % ps] = v[i]
+    _close(kp_d, kp_want, dtype)
+    _close(vp_d, vp_want, dtype)
+    touched = torch.zeros(n_pages, ps, dtype=torch.bool)
+    for i in range(n):
+        touched[bt[tok_req[i], tok_pos[i] // ps], tok_pos[i] % ps] = True
+    assert torch.equal(kp_d.cpu().double()[~touched[:, None, :].expand(-1, kvh, -1)],
+                       kp_ref[~touched[:, None, :].expand(-1, kvh, -1)])
+
+    # attention over the pages as the kernel left them (so rounding of stored keys is shared)
+    kp_now, vp_now = kp_d.cpu().double(), vp_d.cpu().double()
+    q_now = qkv[:, :heads * hd].cpu().double().reshape(n, heads, hd)
+    scale = 1.0 / math.sqrt(hd)
+    want = torch.zeros(n, heads, hd, dtype=torch.float64)
+    for i in range(n):
+        r, p = tok_req[i], int(tok_pos[i])
+        lo = max(0, p - window + 1) if window else 0
+        keys = torch.stack([kp_now[bt[r, j // ps], :, j % ps] for j in range(lo, p + 1)])     # [L, kvh, hd]
+        vals = torch.stack([vp_now[bt[r, j // ps], :, j % ps] for j in range(lo, p + 1)])
+        for h in range(heads):
+            g = h // (heads // kvh)
+            s = (keys[:, g] @ q_now[i, h]) * scale
+            w = torch.softmax(s, 0)
+            want[i, h] = w @ vals[:, g]
+    out = torch.empty(n, heads * hd, dtype=_dt(dtype), device=DEV)
+    ops.paged_attention(qkv[:, :heads * hd], heads, kvh, hd, kp_d, vp_d, t(bt), t(tok_req), t(tok_pos), scale,
+                        window, out, status)
+    _close(out, want.reshape(n, -1), dtype)
+    assert int(status.item()) == 0
+
+
+def test_attention_sees_one_far_key_among_hundreds():
+    """One key far back is made to dominate: if a page's edge or the lane
+    split drops it, the output is visibly wrong."""
+    from gibbs_b200 import ops
+    heads, kvh, hd, ps = 2, 2, 32, 16
+    for length, far in ((700, 0), (700, 15), (700, 16), (513, 511), (1000, 333)):
+        torch.manual_seed(far)
+        bt = np.arange(-(-length // ps), dtype=np.int32)[None, :]
+        kp = torch.randn(64, kvh, ps, hd) * 0.1
+        vp = torch.randn(64, kvh, ps, hd)
+        q = torch.randn(1, heads * hd) * 0.1
+        q[0, :hd] = 4.0                                       # head 0 looks for the far key
+        kp[far // ps, 0, far % ps] = 4.0
+        vp[far // ps, 0, far % ps] = 100.0
+        t = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        out = torch.empty(1, heads * hd, dtype=torch.float32, device=DEV)
+        ops.paged_attention(q.to(DEV), heads, kvh, hd, kp.to(DEV), vp.to(DEV), t(bt), t([0]), t([length - 1]),
+                            1.0, 0, out, status)
+        assert out[0, :hd].min().item() > 99.0, (length, far)
+        assert abs(out[0, hd:].mean().item()) < 1.0                 # the other kv head holds no such key
+
+
+def test_bad_page_id_is_reported_not_dereferenced():
+    from gibbs_b200 import ops
+    heads, kvh, hd, ps = 2, 1, 16, 4
+    t = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kp = torch.zeros(4, kvh, ps, hd, device=DEV)
+    out = torch.empty(1, heads * hd, device=DEV)
+    ops.paged_attention(torch.zeros(1, heads * hd, device=DEV), heads, kvh, hd, kp, kp.clone(), t([[0, 99, -1]]),
+                        t([0]), t([6]), 1.0, 0, out, status)
+    assert int(status.item()) == 2
+    status.zero_()
+    qkv = torch.zeros(1, (heads + 2 * kvh) * hd, device=DEV)
+    ops.qk_norm_rope_store(qkv, heads, kvh, hd, None, None, 1e-5, None, 0, False, t([0]), t([5]), t([[0, 4]]),
+                           kp, kp.clone(), status)
+    assert int(status.item()) == 1
+
+
+# --------------------------------------------------------------------------- sampling
+def test_argmax_first_maximum_and_nan():
+    from gibbs_b200 import ops
+    x = torch.randn(6, 1000)
+    x[0, 17] = x[0, 400] = 50.0                              # tie: the lower id
+    x[1, 3] = float("nan")
+    x[1, 900] = 60.0
+    x[2, :] = float("-inf")
+    x[2, 5] = -1e30
+    x[3, :] = float("nan")                                   # nothing can win: id 0
+    x[4, 999] = 70.0
+    x[5, 0] = 70.0
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    ops.sample(x.to(DEV), out)
+    assert out.tolist() == [17, 900, 5, 0, 999, 0]
+
+
+@pytest.mark.parametrize("vocab", [1000, 65536, 50257])
+def test_temperature_sampling_matches_the_plain_rule(vocab):
+    """For seeded cases the kernel must pick exactly the candidate the plain
+    rule picks with the same uniform number (the reference's test pattern,
+    src/runtime/lm.rs:1271-1400)."""
+    import plain_lfm2 as plain
+    from gibbs_b200 import ops
+    from gibbs_b200.sampling import uniform24
+    rng = np.random.default_rng(vocab)
+    rows = 40
+    logits = (rng.standard_normal((rows, vocab)) * 3).astype(np.float32)
+    logits[3, 10] = logits[3, 20] = logits[3].max() + 1       # a tie at the top
+    temp = rng.uniform(0.3, 1.5, rows).astype(np.float32)
+    temp[5] = 0.0                                             # greedy row among sampled ones
+    top_k = rng.integers(1, 65, rows).astype(np.int32)
+    top_p = rng.uniform(0.05, 1.0, rows).astype(np.float32)
+    seeds = rng.integers(0, 2 ** 62, rows)
+    counters = rng.integers(0, 1000, rows)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.sample(torch.from_numpy(logits).to(DEV), out, torch.from_numpy(temp).to(DEV),
+               torch.from_numpy(top_k).to(DEV), torch.from_numpy(top_p).to(DEV),
+               torch.from_numpy(seeds.astype(np.int64)).to(DEV), torch.from_numpy(counters.astype(np.int64)).to(DEV))
+    got = out.tolist()
+    for r in range(rows):
+        if temp[r] <= 1e-4:
+            assert got[r] == int(np.argmax(logits[r]))
+            continue
+        ids, probs = plain.nucleus_candidates(logits[r], float(temp[r]), int(top_k[r]), float(top_p[r]))
+        u = uniform24(int(seeds[r]), int(counters[r]))
+        cum = np.cumsum(probs)
+        target = u * cum[-1]
+        pick = int(ids[min(int(np.searchsorted(cum, target)), len(ids) - 1)])
+        if got[r] != pick:
+            # float32 against float64 may disagree only when the draw falls on a boundary
+            j = list(ids).index(got[r]) if got[r] in ids else None
+            assert j is not None and abs(cum[j - 1 if got[r] != ids[0] and cum[j] > target else j] - target) < 1e-5, r
+
+
+def test_sampling_distribution():
+    from gibbs_b200 import ops
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0] + [-20.0] * 60]).repeat(4000, 1)
+    rows = logits.shape[0]
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.sample(logits.to(DEV), out, torch.full((rows,), 1.0, device=DEV),
+               torch.full((rows,), 3, dtype=torch.int32, device=DEV), torch.full((rows,), 1.0, device=DEV),
+               torch.full((rows,), 1234, dtype=torch.int64, device=DEV), torch.arange(rows, device=DEV))
+    counts = np.bincount(out.cpu().numpy(), minlength=4)[:4] / rows
+    p = np.exp([2.0, 1.0, 0.0])
+    p /= p.sum()
+    assert counts[3] == 0 and np.abs(counts[:3] - p).max() < 0.03
