@@ -49,6 +49,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="measure one phase only (for short profiler captures); the line is then partial")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm()
@@ -77,6 +79,14 @@ def main():
                     max_running=max_batch, max_batch_tokens=2048)
     eng = gen.engine
 
+    if a.only == "prefill":
+        pre = B.measure_prefill(eng, PROMPT_LEN, warmup=a.warmup, runs=a.steps, seed=SEED)
+        print(json.dumps({"partial": "prefill", "prefill": pre}))
+        return 0
+    if a.only == "decode":
+        dec = B.measure_decode(eng, a.batch, PROMPT_LEN, a.steps, a.warmup, seed=SEED)
+        print(json.dumps({"partial": "decode", "decode": dec}))
+        return 0
     pre = B.measure_prefill(eng, PROMPT_LEN, warmup=a.warmup, runs=5, seed=SEED)
     pre_flops = B.prefill_flops(model, PROMPT_LEN)
     pre["frac"] = pre_flops / (pre["ms"] / 1e3) / (peaks["bf16_tflops"] * 1e12)

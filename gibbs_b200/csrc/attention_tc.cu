@@ -1,0 +1,396 @@
+// Causal grouped-query attention over the paged cache in bfloat16 on the
+// tensor cores, for a ragged batch: prompt portions and single decoded
+// tokens, each request reading its own pages through its block table.
+//
+// The rows of a CTA's tile are (token, query head of one kv group) pairs, so
+// the keys and values of a kv head are read from the pages once for all the
+// query heads that share them.  A CTA walks the visible keys in tiles of 64
+// absolute positions (cp.async into double-buffered shared memory, looked up
+// page by page), computes S = Q K^T and O += P V with mma.sync m16n8k16, and
+// keeps the softmax statistics (running maximum and sum) in 32-bit.
+//   NW = 4: 64 rows per CTA (prompt portions);  NW = 1: 16 rows (decoding).
+// With splits > 1 (decoding against long contexts) the key range is divided
+// among CTAs; each writes an unnormalised partial output with its maximum and
+// sum to a workspace and a second kernel merges them in split order.
+//
+// Formula: MisterTK/gibbs src/graph/cpu.rs:826-951 (keys j <= pos, optional
+// window j + w > pos, scale applied to the dot product, max-subtracted
+// softmax, query head h reads kv head h / (heads / kv_heads)).
+//
+// The tensor-core path here is warp-level mma.sync; the matrix products of
+// the projections use tcgen05 (gemm_tc.cu).  Attention is 2 % of a prompt's
+// arithmetic at these sizes.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int KT = 64;   // keys per tile
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, const void* smem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, const void* smem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct AttnParams {
+  const bf16* q; long long ldq;
+  const bf16* k_pages; const bf16* v_pages;
+  const int* block_table; int bt_stride; int page_size; int n_pages;
+  const int* q_start; const int* q_len; const int* start_pos;
+  bf16* out; long long ldo;
+  float* part_o; float* part_ml;     // [splits][n_tokens*heads][HD], [splits][n_tokens*heads][2]
+  int n_requests, n_tokens, heads, kv_heads, splits, window;
+  float scale_log2;                  // scale * log2(e)
+  int* status;
+};
+
+// Row stride of the shared tiles: HD bf16 plus one 16-byte chunk, an odd number
+// of chunks, so that the eight rows an ldmatrix phase reads fall in distinct banks.
+template <int HD> struct Tile {
+  static constexpr int CHUNKS = HD / 8;
+  static constexpr int STRIDE = HD + 8;   // in bf16
+};
+
+template <int HD, int NW>
+__global__ void __launch_bounds__(32 * NW)
+attention_tc_kernel(const AttnParams p) {
+  constexpr int BQ = 16 * NW;
+  constexpr int STRIDE = Tile<HD>::STRIDE, CHUNKS = Tile<HD>::CHUNKS;
+  constexpr int NT = 32 * NW;
+  extern __shared__ __align__(16) uint8_t smem[];
+  bf16* sq = reinterpret_cast<bf16*>(smem);                  // [BQ][STRIDE]
+  bf16* sk = sq + BQ * STRIDE;                               // [2][KT][STRIDE]
+  bf16* sv = sk + 2 * KT * STRIDE;                           // [2][KT][STRIDE]
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int group = p.heads / p.kv_heads;
+  const int tpt = BQ / group;                                // tokens per tile
+  const int kvh = blockIdx.y, z = blockIdx.z;
+
+  // which request and which of its tiles this CTA has
+  int r = 0, tile = (int)blockIdx.x, found = 0;
+  for (; r < p.n_requests; ++r) {
+    const int nt = (p.q_len[r] + tpt - 1) / tpt;
+    if (tile < nt) { found = 1; break; }
+    tile -= nt;
+  }
+  if (!found) return;
+  const int qlen = p.q_len[r], first_tok = tile * tpt;
+  const int n_tok = min(tpt, qlen - first_tok);             // tokens of this tile
+  const int row0 = p.q_start[r] + first_tok;                 // batch row of the tile's first token
+  const int pos0 = p.start_pos[r] + first_tok;               // its position
+  const int* bt = p.block_table + (size_t)r * p.bt_stride;
+
+  // key range: everything a row of this tile may see, in tiles of KT absolute positions
+  const int hi_all = pos0 + n_tok;                           // exclusive
+  const int lo_all = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
+  const int t_lo = lo_all / KT, t_hi = (hi_all + KT - 1) / KT;
+  const int per = (t_hi - t_lo + p.splits - 1) / p.splits;
+  const int t_begin = t_lo + z * per, t_end = min(t_hi, t_begin + per);
+
+  // Q tile: row = token_local * group + g
+  for (int idx = tid; idx < BQ * CHUNKS; idx += NT) {
+    const int row = idx / CHUNKS, c = idx - row * CHUNKS;
+    const int tl = row / group, g = row - tl * group;
+    const bool valid = tl < n_tok;
+    const bf16* src = p.q + (size_t)(row0 + (valid ? tl : 0)) * p.ldq + (size_t)(kvh * group + g) * HD + c * 8;
+    cp_async_16(sq + row * STRIDE + c * 8, src, valid);
+  }
+  auto load_kv = [&](int t, int buf) {
+    for (int idx = tid; idx < KT * CHUNKS; idx += NT) {
+      const int row = idx / CHUNKS, c = idx - row * CHUNKS;
+      const int j = t * KT + row;
+      bool valid = j < hi_all && j >= lo_all;
+      size_t off = 0;
+      if (valid) {
+        const int page = bt[j / p.page_size];
+        if (page < 0 || page >= p.n_pages) {
+          atomicExch(p.status, 2);
+          valid = false;
+        } else {
+          off = (((size_t)page * p.kv_heads + kvh) * p.page_size + j % p.page_size) * HD + c * 8;
+        }
+      }
+      cp_async_16(sk + (buf * KT + row) * STRIDE + c * 8, p.k_pages + off, valid);
+      cp_async_16(sv + (buf * KT + row) * STRIDE + c * 8, p.v_pages + off, valid);
+    }
+  };
+  if (t_begin < t_end) load_kv(t_begin, 0);
+  cp_async_commit();
+
+  // this thread's two rows: g0 = lane/4 and g0 + 8 of the warp's 16
+  const int rloc[2] = {warp * 16 + (lane >> 2), warp * 16 + (lane >> 2) + 8};
+  int rpos[2];
+  bool rvalid[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int tl = rloc[i] / group;
+    rvalid[i] = tl < n_tok;
+    rpos[i] = pos0 + tl;
+  }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
+
+  uint32_t qf[HD / 16][4];
+  for (int t = t_begin; t < t_end; ++t) {
+    const int buf = (t - t_begin) & 1;
+    if (t + 1 < t_end) load_kv(t + 1, buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    if (t == t_begin) {
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; ++kk)
+        ldmatrix_x4(qf[kk], sq + (warp * 16 + (lane & 15)) * STRIDE + kk * 16 + (lane >> 4) * 8);
+    }
+    // S = Q K^T for 64 keys
+    float s[KT / 8][4];
+#pragma unroll
+    for (int n = 0; n < KT / 8; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[n][i] = 0.f;
+    const bf16* kb = sk + buf * KT * STRIDE;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+#pragma unroll
+      for (int n2 = 0; n2 < KT / 16; ++n2) {
+        uint32_t b[4];
+        ldmatrix_x4(b, kb + (n2 * 16 + (lane & 7) + ((lane >> 4) << 3)) * STRIDE + kk * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16(s[2 * n2], qf[kk], b[0], b[1]);
+        mma_bf16(s[2 * n2 + 1], qf[kk], b[2], b[3]);
+      }
+    }
+    // scale, mask, running maximum
+    float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+    for (int n = 0; n < KT / 8; ++n) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int ri = i >> 1;
+        const int j = t * KT + n * 8 + (lane & 3) * 2 + (i & 1);
+        const bool vis = rvalid[ri] && j <= rpos[ri] && (p.window <= 0 || j + p.window > rpos[ri]);
+        const float v = vis ? s[n][i] * p.scale_log2 : -INFINITY;
+        s[n][i] = v;
+        m_new[ri] = fmaxf(m_new[ri], v);
+      }
+    }
+    float corr[2];
+#pragma unroll
+    for (int ri = 0; ri < 2; ++ri) {
+      m_new[ri] = fmaxf(m_new[ri], __shfl_xor_sync(0xffffffffu, m_new[ri], 1));
+      m_new[ri] = fmaxf(m_new[ri], __shfl_xor_sync(0xffffffffu, m_new[ri], 2));
+      corr[ri] = (m_new[ri] == -INFINITY) ? 1.f : exp2f(m_run[ri] - m_new[ri]);
+      m_run[ri] = m_new[ri];
+      l_run[ri] *= corr[ri];
+    }
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+      o[n][0] *= corr[0]; o[n][1] *= corr[0];
+      o[n][2] *= corr[1]; o[n][3] *= corr[1];
+    }
+    // P = exp2(S - m), O += P V
+    const bf16* vb = sv + buf * KT * STRIDE;
+#pragma unroll
+    for (int kk = 0; kk < KT / 16; ++kk) {
+      uint32_t a[4];
+      float pv[2][4];
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int ri = i >> 1;
+          const float e = (m_run[ri] == -INFINITY) ? 0.f : exp2f(s[2 * kk + h2][i] - m_run[ri]);
+          pv[h2][i] = e;
+          l_run[ri] += e;
+        }
+      a[0] = pack_bf16(pv[0][0], pv[0][1]);
+      a[1] = pack_bf16(pv[0][2], pv[0][3]);
+      a[2] = pack_bf16(pv[1][0], pv[1][1]);
+      a[3] = pack_bf16(pv[1][2], pv[1][3]);
+#pragma unroll
+      for (int n2 = 0; n2 < HD / 16; ++n2) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, vb + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + n2 * 16 + (lane >> 4) * 8);
+        mma_bf16(o[2 * n2], a, b[0], b[1]);
+        mma_bf16(o[2 * n2 + 1], a, b[2], b[3]);
+      }
+    }
+    __syncthreads();   // everyone is done with this buffer before it is refilled
+  }
+  cp_async_wait<0>();
+
+  // row sums across the four threads of a row
+#pragma unroll
+  for (int ri = 0; ri < 2; ++ri) {
+    l_run[ri] += __shfl_xor_sync(0xffffffffu, l_run[ri], 1);
+    l_run[ri] += __shfl_xor_sync(0xffffffffu, l_run[ri], 2);
+  }
+#pragma unroll
+  for (int ri = 0; ri < 2; ++ri) {
+    if (!rvalid[ri]) continue;
+    const int tl = rloc[ri] / group, g = rloc[ri] - tl * group;
+    const int trow = row0 + tl, h = kvh * group + g;
+    if (p.splits == 1) {
+      const float inv = l_run[ri] > 0.f ? 1.0f / l_run[ri] : 0.f;
+      bf16* dst = p.out + (size_t)trow * p.ldo + (size_t)h * HD + (lane & 3) * 2;
+#pragma unroll
+      for (int n = 0; n < HD / 8; ++n)
+        *reinterpret_cast<__nv_bfloat162*>(dst + n * 8) =
+            __floats2bfloat162_rn(o[n][2 * ri] * inv, o[n][2 * ri + 1] * inv);
+    } else {
+      const size_t prow = (size_t)z * p.n_tokens * p.heads + (size_t)trow * p.heads + h;
+      float* dst = p.part_o + prow * HD + (lane & 3) * 2;
+#pragma unroll
+      for (int n = 0; n < HD / 8; ++n)
+        *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][2 * ri], o[n][2 * ri + 1]);
+      if ((lane & 3) == 0) {
+        p.part_ml[prow * 2] = m_run[ri];
+        p.part_ml[prow * 2 + 1] = l_run[ri];
+      }
+    }
+  }
+}
+
+// out[row, :] = sum_z 2^(m_z - M) o_z / sum_z 2^(m_z - M) l_z, splits in ascending order.
+__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                       bf16* __restrict__ out, long long ldo, int n_tokens, int heads, int hd,
+                                       int splits) {
+  const int row = blockIdx.x;                         // token * heads + head
+  const size_t rows = (size_t)n_tokens * heads;
+  float M = -INFINITY;
+  for (int z = 0; z < splits; ++z) M = fmaxf(M, part_ml[(z * rows + row) * 2]);
+  float L = 0.f;
+  for (int z = 0; z < splits; ++z) {
+    const float m = part_ml[(z * rows + row) * 2];
+    if (m != -INFINITY) L += exp2f(m - M) * part_ml[(z * rows + row) * 2 + 1];
+  }
+  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  const int t = row / heads, h = row - t * heads;
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float acc = 0.f;
+    for (int z = 0; z < splits; ++z) {
+      const float m = part_ml[(z * rows + row) * 2];
+      if (m != -INFINITY) acc += exp2f(m - M) * part_o[(z * rows + row) * hd + d];
+    }
+    out[(size_t)t * ldo + (size_t)h * hd + d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+template <int HD, int NW>
+int launch(const AttnParams& p, int n_tiles, cudaStream_t stream) {
+  constexpr int smem = (16 * NW + 4 * KT) * Tile<HD>::STRIDE * 2;
+  static bool attr_set = false;
+  if (!attr_set && smem > 48 * 1024) {
+    GB_CUDA(cudaFuncSetAttribute(attention_tc_kernel<HD, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    attr_set = true;
+  }
+  dim3 grid(n_tiles, p.kv_heads, p.splits);
+  attention_tc_kernel<HD, NW><<<grid, 32 * NW, smem, stream>>>(p);
+  return GB_OK;
+}
+
+template <int NW>
+int dispatch_hd(const AttnParams& p, int hd, int n_tiles, cudaStream_t stream) {
+  switch (hd) {
+    case 16: return launch<16, NW>(p, n_tiles, stream);
+    case 32: return launch<32, NW>(p, n_tiles, stream);
+    case 48: return launch<48, NW>(p, n_tiles, stream);
+    case 64: return launch<64, NW>(p, n_tiles, stream);
+    case 80: return launch<80, NW>(p, n_tiles, stream);
+    case 96: return launch<96, NW>(p, n_tiles, stream);
+    case 112: return launch<112, NW>(p, n_tiles, stream);
+    case 128: return launch<128, NW>(p, n_tiles, stream);
+  }
+  GB_FAIL(GB_ERR_ARG, "gb_attention_tc: head_dim %d is not one of 16, 32, ..., 128", hd);
+}
+
+}  // namespace
+
+// 1 if gb_attention_tc takes this geometry.
+GB_API int gb_attention_tc_supported(int heads, int kv_heads, int hd, long long ldq, long long ldo) {
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0) return 0;
+  if (hd % 16 != 0 || hd < 16 || hd > 128) return 0;
+  if (heads / kv_heads > 64) return 0;
+  if (ldq % 8 != 0 || ldo % 2 != 0) return 0;
+  return 1;
+}
+
+// Number of 32-bit words of workspace for `splits` (0 when splits == 1).
+GB_API long long gb_attention_tc_workspace(int n_tokens, int heads, int hd, int splits) {
+  return splits > 1 ? (long long)splits * n_tokens * heads * (hd + 2) : 0;
+}
+
+// q: [n_tokens, heads*hd] bf16 with row stride ldq (16-byte aligned rows); out likewise with ldo.
+// max_q_len: the longest q_len of the batch (known on the host); it selects the tile height.
+// Returns the number of kernels launched, or a negative error code.
+GB_API int gb_attention_tc(const void* q, long long ldq, const void* k_pages, const void* v_pages,
+                           const int* block_table, int bt_stride, int page_size, int n_pages, const int* q_start,
+                           const int* q_len, const int* start_pos, void* out, long long ldo, int n_requests,
+                           int n_tokens, int max_q_len, int heads, int kv_heads, int hd, float scale, int window,
+                           int splits, float* workspace, int* status, cudaStream_t stream) {
+  if (n_tokens <= 0 || n_requests <= 0) return 0;
+  if (!gb_attention_tc_supported(heads, kv_heads, hd, ldq, ldo))
+    GB_FAIL(GB_ERR_ARG, "gb_attention_tc: %d heads / %d kv heads / head_dim %d (row strides %lld, %lld) not taken",
+            heads, kv_heads, hd, ldq, ldo);
+  if (((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
+    GB_FAIL(GB_ERR_ARG, "gb_attention_tc: q and the pages must be 16-byte aligned");
+  if (splits < 1) splits = 1;
+  if (splits > 1 && workspace == nullptr) GB_FAIL(GB_ERR_ARG, "gb_attention_tc: splits need a workspace");
+  const int group = heads / kv_heads;
+  const bool small = (long long)max_q_len * group <= 16 && group <= 16;
+  const int bq = small ? 16 : 64;
+  if (group > bq) GB_FAIL(GB_ERR_ARG, "gb_attention_tc: %d query heads per kv head", group);
+  const int tpt = bq / group;
+  // upper bound of the number of tiles: sum_r ceil(q_len_r / tpt) <= n_tokens / tpt + n_requests
+  const long long n_tiles = small ? n_requests : ((long long)n_tokens + tpt - 1) / tpt + n_requests;
+  if (!small) splits = 1;
+  AttnParams p;
+  p.q = (const bf16*)q; p.ldq = ldq; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
+  p.block_table = block_table; p.bt_stride = bt_stride; p.page_size = page_size; p.n_pages = n_pages;
+  p.q_start = q_start; p.q_len = q_len; p.start_pos = start_pos; p.out = (bf16*)out; p.ldo = ldo;
+  p.part_o = workspace;
+  p.part_ml = workspace ? workspace + (size_t)splits * n_tokens * heads * hd : nullptr;
+  p.n_requests = n_requests; p.n_tokens = n_tokens; p.heads = heads; p.kv_heads = kv_heads; p.splits = splits;
+  p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+  int rc = small ? dispatch_hd<1>(p, hd, (int)n_tiles, stream) : dispatch_hd<4>(p, hd, (int)n_tiles, stream);
+  if (rc != GB_OK) return rc;
+  GB_CHECK_LAUNCH("gb_attention_tc");
+  if (splits > 1) {
+    attention_merge_kernel<<<n_tokens * heads, hd <= 64 ? 64 : 128, 0, stream>>>(
+        p.part_o, p.part_ml, (bf16*)out, ldo, n_tokens, heads, hd, splits);
+    GB_CHECK_LAUNCH("gb_attention_tc (merge)");
+    return 2;
+  }
+  return 1;
+}

@@ -291,20 +291,58 @@ def paged_attention(q: torch.Tensor, heads: int, kv_heads: int, head_dim: int, k
                     v_pages: torch.Tensor, block_table: torch.Tensor, tok_req: torch.Tensor, tok_pos: torch.Tensor,
                     scale: float, window: int, out: torch.Tensor, status: torch.Tensor, hints=None) -> torch.Tensor:
     """out[t, h, :] = softmax over visible keys of (q.K)*scale, times V; q may be
-    a column slice of a wider row (its row stride is passed on)."""
+    a column slice of a wider row (its row stride is passed on).  ``hints`` is
+    the step's state (per-request starts and lengths and the longest portion):
+    with it, bfloat16 attention runs on the tensor cores."""
     _need_cuda(q, k_pages, v_pages, block_table, tok_req, tok_pos, out, status)
-    lib = library("core")
     n = q.shape[0]
     if q.shape[1] != heads * head_dim or out.shape != (n, heads * head_dim) or q.dtype != out.dtype:
         raise KernelError("paged_attention: q and out must be [n, heads*head_dim] of one dtype")
     _check_pages(k_pages, v_pages, kv_heads, head_dim, q.dtype, "paged_attention")
     _i32(tok_req, "tok_req"), _i32(tok_pos, "tok_pos"), _i32(block_table, "block_table"), _i32(status, "status")
+    if hints is not None and q.dtype == torch.bfloat16 and attention_tc_supported(q, out, heads, kv_heads, head_dim):
+        return _attention_tc(q, heads, kv_heads, head_dim, k_pages, v_pages, block_table, scale, window, out,
+                             status, hints)
+    lib = library("core")
     _launched(1)
     check(lib, lib.gb_paged_attention(
         _ptr(q), dtype_code(q.dtype), _c_ll(_rows(q, "q")), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
         _c_int(block_table.shape[1]), _c_int(k_pages.shape[2]), _c_int(k_pages.shape[0]), _ptr(tok_req),
         _ptr(tok_pos), _ptr(out), _c_ll(_rows(out, "out")), _c_int(n), _c_int(heads), _c_int(kv_heads),
         _c_int(head_dim), _c_float(scale), _c_int(window or 0), _ptr(status), _stream()))
+    return out
+
+
+def attention_tc_supported(q, out, heads, kv_heads, head_dim) -> bool:
+    return (head_dim % 16 == 0 and 16 <= head_dim <= 128 and heads % kv_heads == 0 and heads // kv_heads <= 64
+            and q.stride(0) % 8 == 0 and out.stride(0) % 2 == 0 and q.data_ptr() % 16 == 0)
+
+
+def attention_splits(n_requests: int, kv_heads: int, max_ctx_len: int) -> int:
+    """How many CTAs share the keys of one (request, kv head) when decoding:
+    enough to occupy the GPU, at least two tiles of 64 keys each."""
+    by_sm = max(1, 296 // max(1, n_requests * kv_heads))
+    by_len = max(1, -(-max_ctx_len // 128))
+    return max(1, min(32, by_sm, by_len))
+
+
+def _attention_tc(q, heads, kv_heads, head_dim, k_pages, v_pages, block_table, scale, window, out, status, step):
+    lib = library("tensorcore")
+    n, group = q.shape[0], heads // kv_heads
+    small = step.max_q_len * group <= 16 and group <= 16
+    splits = attention_splits(step.n_requests, kv_heads, step.max_ctx_len) if small else 1
+    ws = None
+    if splits > 1:
+        ws = torch.empty(splits * n * heads * (head_dim + 2), dtype=torch.float32, device=q.device)
+    rc = lib.gb_attention_tc(
+        _ptr(q), _c_ll(_rows(q, "q")), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), _c_int(block_table.shape[1]),
+        _c_int(k_pages.shape[2]), _c_int(k_pages.shape[0]), _ptr(step.q_start), _ptr(step.q_len),
+        _ptr(step.start_pos), _ptr(out), _c_ll(_rows(out, "out")), _c_int(step.n_requests), _c_int(n),
+        _c_int(step.max_q_len), _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_float(scale),
+        _c_int(window or 0), _c_int(splits), _ptr(ws), _ptr(status), _stream())
+    if rc < 0:
+        check(lib, rc)
+    _launched(rc)
     return out
 
 

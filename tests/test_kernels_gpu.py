@@ -429,3 +429,101 @@ def test_sampling_distribution():
     p = np.exp([2.0, 1.0, 0.0])
     p /= p.sum()
     assert counts[3] == 0 and np.abs(counts[:3] - p).max() < 0.03
+
+
+# --------------------------------------------------------------------------- tensor-core attention
+class _Hints:
+    def __init__(self, before, q_lens):
+        t = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+        self.q_start = t(np.cumsum([0] + list(q_lens[:-1])).tolist())
+        self.q_len, self.start_pos = t(q_lens), t(before)
+        self.n_requests, self.max_q_len = len(q_lens), max(q_lens)
+        self.max_ctx_len = max(a + b for a, b in zip(before, q_lens))
+
+
+def _plain_paged_attention(q, kp, vp, bt, tok_req, tok_pos, heads, kvh, hd, ps, scale, window):
+    n = q.shape[0]
+    q = q.reshape(n, heads, hd)
+    want = torch.zeros(n, heads, hd, dtype=torch.float64)
+    for i in range(n):
+        r, p = tok_req[i], int(tok_pos[i])
+        lo = max(0, p - window + 1) if window else 0
+        idx = torch.arange(lo, p + 1)
+        pages = torch.from_numpy(bt[r].astype(np.int64))[idx // ps]
+        keys, vals = kp[pages, :, idx % ps], vp[pages, :, idx % ps]          # [L, kvh, hd]
+        for h in range(heads):
+            g = h // (heads // kvh)
+            w = torch.softmax((keys[:, g] @ q[i, h]) * scale, 0)
+            want[i, h] = w @ vals[:, g]
+    return want.reshape(n, -1)
+
+
+TC_CASES = [
+    # heads, kv_heads, head_dim, page_size, window, lengths before, portion lengths
+    (4, 2, 16, 16, 0, [0, 37, 5, 130, 64], [9, 1, 20, 1, 3]),
+    (3, 1, 32, 8, 0, [0, 200, 63], [70, 2, 1]),
+    (6, 2, 48, 4, 0, [10, 0], [33, 64]),
+    (32, 8, 64, 16, 0, [0, 100], [150, 17]),
+    (5, 5, 80, 32, 0, [3, 300], [40, 1]),
+    (8, 1, 128, 16, 0, [0, 64], [65, 8]),
+    (4, 2, 16, 8, 7, [0, 50, 20], [30, 1, 12]),
+    (8, 2, 64, 16, 100, [500], [90]),
+    # decoding only: one token per request, long contexts, the key range is split among CTAs
+    (32, 8, 64, 16, 0, [2047, 5, 700, 64, 63], [1, 1, 1, 1, 1]),
+    (4, 1, 32, 16, 0, [1500], [1]),
+    (6, 3, 96, 16, 33, [400, 31, 32], [1, 1, 1]),
+    (16, 1, 64, 16, 0, [300, 1], [1, 1]),
+    (2, 1, 112, 64, 0, [129], [3]),
+]
+
+
+@pytest.mark.parametrize("heads,kvh,hd,ps,window,before,q_lens", TC_CASES)
+def test_attention_tensor_cores(heads, kvh, hd, ps, window, before, q_lens):
+    from gibbs_b200 import ops
+    torch.manual_seed(heads + hd + ps)
+    total = sum(a + b for a, b in zip(before, q_lens))
+    n_pages = total // ps + len(before) + 8
+    bt, tok_req, tok_pos = _layout(before, q_lens, ps, n_pages, seed=hd + ps)
+    n = sum(q_lens)
+    wide, _ = _quant(torch.randn(n, (heads + 2 * kvh) * hd), "bfloat16")
+    q = wide[:, :heads * hd]                                   # a column slice, as the engine passes it
+    kp_d, kp = _quant(torch.randn(n_pages, kvh, ps, hd), "bfloat16")
+    vp_d, vp = _quant(torch.randn(n_pages, kvh, ps, hd), "bfloat16")
+    scale = 1.0 / math.sqrt(hd)
+    want = _plain_paged_attention(q.double().cpu(), kp, vp, bt, tok_req, tok_pos, heads, kvh, hd, ps, scale, window)
+    t = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((n, heads * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    before_launches = ops.launch_count()
+    ops.paged_attention(q, heads, kvh, hd, kp_d, vp_d, t(bt), t(tok_req), t(tok_pos), scale, window, out, status,
+                        hints=_Hints(before, q_lens))
+    assert ops.attention_tc_supported(q, out, heads, kvh, hd)
+    _close(out, want, "bfloat16")
+    assert int(status.item()) == 0
+    if max(q_lens) == 1 and max(a + 1 for a in before) > 128:
+        assert ops.launch_count() - before_launches == 2        # split keys + merge
+
+
+def test_attention_tensor_cores_far_key_and_tile_edges():
+    """A dominant key at the edges of the 64-key tiles and of the splits."""
+    from gibbs_b200 import ops
+    heads, kvh, hd, ps = 4, 2, 64, 16
+    for length, far, q_len in ((700, 0, 1), (700, 63, 1), (700, 64, 1), (1025, 1023, 1), (1000, 333, 1),
+                               (300, 255, 40), (300, 256, 40), (129, 128, 129)):
+        torch.manual_seed(far)
+        nb = -(-length // ps)
+        bt = np.arange(nb, dtype=np.int32)[None, :]
+        kp = (torch.randn(nb, kvh, ps, hd) * 0.1).to(torch.bfloat16)
+        vp = torch.randn(nb, kvh, ps, hd).to(torch.bfloat16)
+        q = (torch.randn(q_len, heads * hd) * 0.1).to(torch.bfloat16)
+        q[-1, :hd] = 4.0
+        kp[far // ps, 0, far % ps] = 4.0
+        vp[far // ps, 0, far % ps] = 100.0
+        t = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        out = torch.empty(q_len, heads * hd, dtype=torch.bfloat16, device=DEV)
+        before = [length - q_len]
+        ops.paged_attention(q.to(DEV), heads, kvh, hd, kp.to(DEV), vp.to(DEV), t(bt), t([0] * q_len),
+                            t(list(range(length - q_len, length))), 1.0, 0, out, status, hints=_Hints(before, [q_len]))
+        assert out[-1, :hd].float().min().item() > 99.0, (length, far, q_len)
+        assert abs(out[-1, 2 * hd:].float().mean().item()) < 1.0
