@@ -75,18 +75,59 @@ __global__ void short_conv_state_kernel(const T* __restrict__ bcx, long long ld,
   }
 }
 
+// Every request brings exactly one token: output and state update in one pass,
+// one thread per request and channel (it alone reads and writes its state column).
+template <typename T>
+__global__ void short_conv_decode_kernel(const T* __restrict__ bcx, long long ld, const float* __restrict__ taps,
+                                         const float* __restrict__ bias, float* __restrict__ state,
+                                         long long slot_stride, const int* __restrict__ slot_ids,
+                                         const int* __restrict__ q_start, T* __restrict__ out, int n_requests,
+                                         int hidden, int K) {
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= (long long)n_requests * hidden) return;
+  const int r = (int)(gid / hidden), c = (int)(gid - (long long)r * hidden);
+  const int t = q_start[r];
+  const T* row = bcx + (size_t)t * ld;
+  const float bx = to_f32(row[c]) * to_f32(row[2 * hidden + c]);
+  float* st = state + (size_t)slot_ids[r] * slot_stride;
+  float acc = 0.f;
+  for (int j = 0; j < K - 1; ++j) {
+    const float v = st[(size_t)j * hidden + c];
+    acc = fmaf(taps[(size_t)c * K + j], v, acc);
+    if (j > 0) st[(size_t)(j - 1) * hidden + c] = v;      // shift the window by one
+  }
+  acc = fmaf(taps[(size_t)c * K + K - 1], bx, acc);
+  st[(size_t)(K - 2) * hidden + c] = bx;
+  if (bias) acc += bias[c];
+  out[(size_t)t * hidden + c] = from_f32<T>(to_f32(row[hidden + c]) * acc);
+}
+
 }  // namespace
 
 // bcx: [n_tokens, 3*hidden] rows of [B | C | x] with row stride ld; taps
 // [hidden, K] and bias [hidden] (optional) in 32-bit; state: 32-bit, slot s at
-// state + s*slot_stride holding [K-1, hidden]; out: [n_tokens, hidden].
+// state + s*slot_stride holding [K-1, hidden]; out: [n_tokens, hidden].  max_q_len: the longest
+// portion of the batch if the host knows it (0: unknown).  Returns the number of kernels launched.
 GB_API int gb_short_conv(const void* bcx, int dtype, long long ld, const float* taps, const float* bias,
                          float* state, long long slot_stride, const int* slot_ids, const int* tok_req,
                          const int* q_start, const int* q_len, void* out, int n_tokens, int n_requests, int hidden,
-                         int K, cudaStream_t stream) {
-  if (n_tokens <= 0) return GB_OK;
+                         int K, int max_q_len, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
   if (K < 2 || K > MAX_TAPS) GB_FAIL(GB_ERR_ARG, "gb_short_conv: kernel width %d outside 2..%d", K, MAX_TAPS);
   const int threads = 256;
+  if (max_q_len == 1 && n_tokens == n_requests) {           // one token per request
+    const long long total = (long long)n_requests * hidden;
+    if (dtype == GB_F32)
+      short_conv_decode_kernel<float><<<gb_div_up(total, threads), threads, 0, stream>>>(
+          (const float*)bcx, ld, taps, bias, state, slot_stride, slot_ids, q_start, (float*)out, n_requests, hidden, K);
+    else if (dtype == GB_BF16)
+      short_conv_decode_kernel<bf16><<<gb_div_up(total, threads), threads, 0, stream>>>(
+          (const bf16*)bcx, ld, taps, bias, state, slot_stride, slot_ids, q_start, (bf16*)out, n_requests, hidden, K);
+    else
+      GB_FAIL(GB_ERR_ARG, "gb_short_conv: unknown dtype %d", dtype);
+    GB_CHECK_LAUNCH("gb_short_conv (decode)");
+    return 1;
+  }
   const long long total = (long long)n_tokens * hidden;
   const long long total_s = (long long)n_requests * hidden;
   if (dtype == GB_F32) {
@@ -105,5 +146,5 @@ GB_API int gb_short_conv(const void* bcx, int dtype, long long ld, const float* 
     GB_FAIL(GB_ERR_ARG, "gb_short_conv: unknown dtype %d", dtype);
   }
   GB_CHECK_LAUNCH("gb_short_conv");
-  return GB_OK;
+  return 2;
 }

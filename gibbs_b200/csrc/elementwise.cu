@@ -37,35 +37,84 @@ GB_API int gb_embed(const void* table, int table_dtype, const int* ids, float* o
 // One block per output row.  `rows` (optional) gathers input rows.  The sum of
 // squares is taken in a fixed order, so a row's result does not depend on
 // what else is in the batch.
+//
+// `pend` (optional): partial sums [splits][n_src_rows][dim] (+ pend_bias) that a
+// split-K product left to be added to x.  They are added here, in split order,
+// before the statistics; without a row gather the sum is also written back to x
+// (the residual stream carries on from it).
 template <typename TOut>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ gain,
-                               TOut* __restrict__ out, const int* __restrict__ rows, int dim, float eps) {
+__global__ void rmsnorm_kernel(float* __restrict__ x, long long ldx, const float* __restrict__ gain,
+                               TOut* __restrict__ out, const int* __restrict__ rows, int dim, float eps,
+                               const float* __restrict__ pend, int splits, long long n_src_rows,
+                               const float* __restrict__ pend_bias) {
   __shared__ float scratch[32];
   const int r = blockIdx.x;
-  const float* src = x + (size_t)(rows ? rows[r] : r) * ldx;
+  const long long sr = rows ? rows[r] : r;
+  float* src = x + (size_t)sr * ldx;
+  const bool write_back = pend != nullptr && rows == nullptr;
   float ss = 0.f;
   for (int d = threadIdx.x; d < dim; d += blockDim.x) {
-    const float v = src[d];
+    float v = src[d];
+    if (pend) {
+      for (int s = 0; s < splits; ++s) v += pend[((size_t)s * n_src_rows + sr) * dim + d];
+      if (pend_bias) v += pend_bias[d];
+      if (write_back) src[d] = v;
+    }
     ss += v * v;
   }
   ss = block_sum(ss, scratch);
   const float scale = 1.0f / sqrtf(ss / (float)dim + eps);
   TOut* dst = out + (size_t)r * dim;
-  for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = from_f32<TOut>(src[d] * scale * gain[d]);
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    float v = src[d];                       // each thread re-reads what it wrote itself
+    if (pend && !write_back) {
+      for (int s = 0; s < splits; ++s) v += pend[((size_t)s * n_src_rows + sr) * dim + d];
+      if (pend_bias) v += pend_bias[d];
+    }
+    dst[d] = from_f32<TOut>(v * scale * gain[d]);
+  }
 }
 
-GB_API int gb_rmsnorm(const float* x, long long ldx, const float* gain, void* out, int out_dtype, const int* rows,
-                      int n_rows, int dim, float eps, cudaStream_t stream) {
+GB_API int gb_rmsnorm(float* x, long long ldx, const float* gain, void* out, int out_dtype, const int* rows,
+                      int n_rows, int dim, float eps, const float* pend, int splits, long long n_src_rows,
+                      const float* pend_bias, cudaStream_t stream) {
   if (n_rows <= 0) return GB_OK;
   int threads = 32;
   while (threads < 512 && threads * 4 < dim) threads <<= 1;
   if (out_dtype == GB_F32)
-    rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, ldx, gain, (float*)out, rows, dim, eps);
+    rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, ldx, gain, (float*)out, rows, dim, eps, pend, splits,
+                                                          n_src_rows, pend_bias);
   else if (out_dtype == GB_BF16)
-    rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, ldx, gain, (bf16*)out, rows, dim, eps);
+    rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, ldx, gain, (bf16*)out, rows, dim, eps, pend, splits,
+                                                         n_src_rows, pend_bias);
   else
     GB_FAIL(GB_ERR_ARG, "gb_rmsnorm: unknown output dtype %d", out_dtype);
   GB_CHECK_LAUNCH("gb_rmsnorm");
+  return GB_OK;
+}
+
+// x[m, :] += sum over splits of pend[s][m, :] (+ bias), in split order.
+__global__ void add_pending_kernel(float* __restrict__ x, long long ldx, const float* __restrict__ pend, int splits,
+                                   const float* __restrict__ bias, long long n_rows, int dim) {
+  const long long total = n_rows * dim;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long m = i / dim;
+    const int d = (int)(i - m * dim);
+    float v = x[(size_t)m * ldx + d];
+    for (int s = 0; s < splits; ++s) v += pend[(size_t)s * total + i];
+    if (bias) v += bias[d];
+    x[(size_t)m * ldx + d] = v;
+  }
+}
+
+GB_API int gb_add_pending(float* x, long long ldx, const float* pend, int splits, const float* bias,
+                          long long n_rows, int dim, cudaStream_t stream) {
+  const long long total = n_rows * dim;
+  if (total <= 0 || splits <= 0) return GB_OK;
+  const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  add_pending_kernel<<<blocks, 256, 0, stream>>>(x, ldx, pend, splits, bias, n_rows, dim);
+  GB_CHECK_LAUNCH("gb_add_pending");
   return GB_OK;
 }
 

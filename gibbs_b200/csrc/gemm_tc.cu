@@ -3,15 +3,29 @@
 // memory by TMA (128-byte swizzle) and the 32-bit accumulator in tensor memory.
 //
 // The weight matrix is always the 128-row side of the instruction and the
-// tokens are its N side (16 to 256 columns), so the same kernel serves a
+// tokens are its N side (16 to 128 columns), so the same kernel serves a
 // single decoded token and a 2,048-token prompt: D[n, m] = W[n, :] . X[m, :],
 // stored transposed.  One CTA computes one 128 x BN tile over a range of K:
 //   warp 0   one elected thread issues the TMA loads (producer),
 //   warp 1   allocates tensor memory; one elected thread issues the MMAs,
 //   warps 2-5 read the accumulator back (tcgen05.ld) and store the tile.
-// When there are too few tiles to fill the GPU (decode), K is split across
-// CTAs; the partial tiles go to a 32-bit workspace and a second kernel adds
-// them in a fixed order, so results do not depend on timing.
+//
+// Epilogues: store bf16 / store f32 / add into an f32 output (the residual
+// stream) / SwiGLU, for a weight whose rows alternate in blocks of 64 between
+// gate and up: lanes 0-63 of a tile then hold g, lanes 64-127 hold u of the
+// same 64 features, and the tile stores (g * sigmoid(g)) * u.
+//
+// When there are too few tiles to fill the GPU (decoding), K is split across
+// CTAs: every CTA writes its partial tile to a 32-bit workspace, and the
+// partial tiles are added in split order (so the result does not depend on
+// timing) either by a small second kernel here, or, for a product that adds
+// into the residual stream, by the normalisation kernel that reads the stream
+// next (the caller asks for that with `defer`).
+//
+// A decode step is bound by streaming the weights once: the weights are read
+// with an evict-first L2 hint.  A call may also name the weights of the NEXT
+// product, for which the CTAs then issue L2 prefetches while they work (off
+// by default: it did not pay in measurements so far).
 //
 // Sizes: any M, N; K a multiple of 8 (16-byte rows for TMA), all row strides
 // multiples of 8 elements, 16-byte aligned bases.  Ragged edges are zero-filled
@@ -33,33 +47,65 @@ constexpr int UMMA_K = 16;
 constexpr int W_TILE_BYTES = BM * BK * 2;
 constexpr int STATUS_TIMEOUT = 16;
 
-enum OutMode : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2, OUT_PARTIAL = 3 };
+enum OutMode : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2, OUT_SWIGLU = 3 };
 
 template <int BN> struct Cfg {
   static constexpr int X_TILE_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES;
-  static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 3 : (BN >= 64 ? 4 : 5));
+  static constexpr int STAGES = BN >= 128 ? 3 : (BN >= 64 ? 4 : 5);
   static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;   // + room to align to 1024
 };
 
+struct GemmParams {
+  const float* bias;
+  void* out; long long ldo;
+  int mode;                     // OutMode
+  int M, N;                     // tokens, weight rows (for SwiGLU: 2 * features)
+  int total_kb, kb_per_split, splits;
+  float* ws;                    // [splits][M][N] partial tiles (splits > 1)
+  const uint8_t* prefetch; long long prefetch_bytes;   // weights of the next product, or null
+  int stream_weights;           // 1: read W with an evict-first L2 hint
+  int* status;
+};
+
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  const float sig = 1.0f / (1.0f + expf(-g));
+  return (g * sig) * u;
+}
+
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Applies the epilogue to one finished value D[n][m] (n: weight row) and stores it.
+__device__ __forceinline__ void store_value(const GemmParams& p, int m, int n, float val) {
+  if (p.mode == OUT_BF16) {
+    ((bf16*)p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(val);
+  } else if (p.mode == OUT_F32) {
+    ((float*)p.out)[(size_t)m * p.ldo + n] = val;
+  } else {
+    float* o = (float*)p.out + (size_t)m * p.ldo + n;
+    *o = *o + val;
+  }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(192)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-               const float* __restrict__ bias, void* __restrict__ out, long long ldo, int mode, int M, int N,
-               int total_kb, int kb_per_split, int* __restrict__ status) {
+               const GemmParams p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t full_bar[C::STAGES], empty_bar[C::STAGES], tmem_full_bar;
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int abort_flag;
+  __shared__ float ubuf[64][17];                 // SwiGLU: u of one 16-column chunk, padded against bank conflicts
 
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN;
-  const int kb_begin = blockIdx.z * kb_per_split;
-  const int kb_end = min(kb_begin + kb_per_split, total_kb);
+  const int kb_begin = blockIdx.z * p.kb_per_split;
+  const int kb_end = min(kb_begin + p.kb_per_split, p.total_kb);
   const int nkb = kb_end - kb_begin;
+  const int M = p.M, N = p.N;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -85,18 +131,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 
   if (warp == 0) {
     if (elect_one()) {
+      uint64_t policy = 0;
+      if (p.stream_weights) asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
       for (int i = 0; i < nkb; ++i) {
         const int s = i % C::STAGES;
         const uint32_t ph = (i / C::STAGES) & 1;
         if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
           abort_flag = 1;
-          atomicExch(status, STATUS_TIMEOUT);
+          atomicExch(p.status, STATUS_TIMEOUT);
           break;
         }
         if (abort_flag) break;
         uint8_t* st = tiles + (size_t)s * C::STAGE_BYTES;
         mbar_arrive_expect_tx(&full_bar[s], C::STAGE_BYTES);
-        tma_load_2d(st, &tmap_w, (kb_begin + i) * BK, n0, &full_bar[s]);
+        if (p.stream_weights)
+          tma_load_2d_hint(st, &tmap_w, (kb_begin + i) * BK, n0, &full_bar[s], policy);
+        else
+          tma_load_2d(st, &tmap_w, (kb_begin + i) * BK, n0, &full_bar[s]);
         tma_load_2d(st + W_TILE_BYTES, &tmap_x, (kb_begin + i) * BK, m0, &full_bar[s]);
       }
     }
@@ -109,7 +160,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         const uint32_t ph = (i / C::STAGES) & 1;
         if (!mbar_wait(&full_bar[s], ph)) {
           abort_flag = 1;
-          atomicExch(status, STATUS_TIMEOUT + 1);
+          atomicExch(p.status, STATUS_TIMEOUT + 1);
           break;
         }
         if (abort_flag) break;
@@ -128,38 +179,80 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     }
     __syncwarp();
   } else {
+    // ---- epilogue warps (threads 64..191) ----
+    const int et = threadIdx.x - 64;            // 0..127
+    if (p.prefetch != nullptr) {
+      // this CTA's share of the next product's weights, in 4 KB pieces, towards L2
+      const long long n_cta = (long long)gridDim.x * gridDim.y * gridDim.z;
+      const long long cta = ((long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+      const long long pieces = (p.prefetch_bytes + 4095) / 4096;
+      for (long long i = cta * 128 + et; i < pieces; i += n_cta * 128) {
+        const long long off = i * 4096;
+        const uint32_t bytes = (uint32_t)((p.prefetch_bytes - off < 4096 ? p.prefetch_bytes - off : 4096) & ~15ll);
+        if (bytes) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.prefetch + off), "r"(bytes));
+      }
+    }
     const bool ok = mbar_wait(&tmem_full_bar, 0);
     if (!ok) {
       abort_flag = 1;
-      if (lane == 0) atomicExch(status, STATUS_TIMEOUT + 2);
+      if (lane == 0) atomicExch(p.status, STATUS_TIMEOUT + 2);
     }
     tc_fence_after();
-    if (ok && !abort_flag) {
-      const int q = warp & 3;                 // this warp may read tensor-memory lanes 32q .. 32q+31
-      const int n = n0 + 32 * q + lane;       // the weight row this thread holds
-      const float b = (bias != nullptr && mode != OUT_PARTIAL && n < N) ? bias[n] : 0.f;
+    epilogue_barrier();                          // abort_flag is seen by all epilogue threads
+    const bool good = !abort_flag;
+    const int q = warp & 3;                      // this warp may read tensor-memory lanes 32q .. 32q+31
+    const int row = 32 * q + lane;               // lane of the accumulator = weight row within the tile
+    const int n = n0 + row;
+    const bool split = p.splits > 1;
+    if (good && split) {
+      // partial tile -> workspace
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
-        if (m0 + c0 >= M) break;              // uniform over the warp
+        if (m0 + c0 >= M) break;
         float v[16];
         tmem_ld_16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, v);
         if (n < N) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int m = m0 + c0 + j;
-            if (m < M) {
-              const float val = v[j] + b;
-              if (mode == OUT_BF16) {
-                ((bf16*)out)[(size_t)m * ldo + n] = __float2bfloat16_rn(val);
-              } else if (mode == OUT_F32) {
-                ((float*)out)[(size_t)m * ldo + n] = val;
-              } else if (mode == OUT_F32_ACC) {
-                float* o = (float*)out + (size_t)m * ldo + n;
-                *o = *o + val;
-              } else {
-                ((float*)out)[((size_t)blockIdx.z * M + m) * (size_t)N + n] = v[j];
-              }
-            }
+            if (m < M) p.ws[((size_t)blockIdx.z * M + m) * (size_t)N + n] = v[j];
+          }
+        }
+      }
+    } else if (good && p.mode == OUT_SWIGLU) {
+      const float b = (p.bias && n < N) ? p.bias[n] : 0.f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        if (m0 + c0 >= M) break;
+        float v[16];
+        tmem_ld_16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, v);
+        if (row >= 64) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) ubuf[row - 64][j] = v[j] + b;
+        }
+        epilogue_barrier();
+        if (row < 64) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = m0 + c0 + j;
+            if (m < M)
+              ((bf16*)p.out)[(size_t)m * p.ldo + (n0 >> 1) + row] = __float2bfloat16_rn(silu_mul(v[j] + b, ubuf[row][j]));
+          }
+        }
+        epilogue_barrier();
+      }
+    } else if (good) {
+      const float b = (p.bias != nullptr && n < N) ? p.bias[n] : 0.f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        if (m0 + c0 >= M) break;                // uniform over the warp
+        float v[16];
+        tmem_ld_16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, v);
+        if (n < N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = m0 + c0 + j;
+            if (m < M) store_value(p, m, n, v[j] + b);
           }
         }
       }
@@ -175,20 +268,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
 
-// out = sum over splits of the partial tiles (+ bias), in split order.
+// out = epilogue(sum over splits of the partial tiles (+ bias)), in split order.
 __global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, const float* __restrict__ bias,
                                      void* __restrict__ out, long long ldo, int mode, int M, int N) {
   const long long total = (long long)M * N;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+  const int n_out = mode == OUT_SWIGLU ? N / 2 : N;
+  const long long work = (long long)M * n_out;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < work;
        i += (long long)gridDim.x * blockDim.x) {
-    const int m = (int)(i / N), n = (int)(i - (long long)m * N);
-    float acc = ws[i];
-    for (int s = 1; s < splits; ++s) acc += ws[(size_t)s * total + i];
-    if (bias) acc += bias[n];
-    const size_t o = (size_t)m * ldo + n;
-    if (mode == OUT_BF16) ((bf16*)out)[o] = __float2bfloat16_rn(acc);
-    else if (mode == OUT_F32) ((float*)out)[o] = acc;
-    else ((float*)out)[o] += acc;
+    const int m = (int)(i / n_out), c = (int)(i - (long long)m * n_out);
+    if (mode == OUT_SWIGLU) {
+      const int n = (c / 64) * 128 + (c % 64);          // gate row; its up row is 64 further
+      float g = 0.f, u = 0.f;
+      for (int s = 0; s < splits; ++s) {
+        g += ws[(size_t)s * total + (size_t)m * N + n];
+        u += ws[(size_t)s * total + (size_t)m * N + n + 64];
+      }
+      if (bias) {
+        g += bias[n];
+        u += bias[n + 64];
+      }
+      ((bf16*)out)[(size_t)m * ldo + c] = __float2bfloat16_rn(silu_mul(g, u));
+    } else {
+      float acc = 0.f;
+      for (int s = 0; s < splits; ++s) acc += ws[(size_t)s * total + (size_t)m * N + c];
+      if (bias) acc += bias[c];
+      const size_t o = (size_t)m * ldo + c;
+      if (mode == OUT_BF16) ((bf16*)out)[o] = __float2bfloat16_rn(acc);
+      else if (mode == OUT_F32) ((float*)out)[o] = acc;
+      else ((float*)out)[o] += acc;
+    }
   }
 }
 
@@ -248,7 +357,7 @@ void plan(int M, int N, int K, int* bn, int* splits, int* kb_per_split) {
   const int total_kb = gb_div_up(K, BK);
   const long long tiles = (long long)gb_div_up(N, BM) * gb_div_up(M, *bn);
   int s = 1;
-  if (tiles < 96 && M <= 128) {                  // too few CTAs to pull the weights at full bandwidth
+  if (tiles < 96 && M <= 128) {   // too few CTAs to pull the weights at full bandwidth
     s = (int)(148 / tiles);
     const int max_by_k = total_kb / 4;           // at least 4 k-blocks (256 columns of K) per split
     if (s > max_by_k) s = max_by_k;
@@ -260,17 +369,15 @@ void plan(int M, int N, int K, int* bn, int* splits, int* kb_per_split) {
 }
 
 template <int BN>
-int launch(const CUtensorMap& tw, const CUtensorMap& tx, const float* bias, void* out, long long ldo, int mode,
-           int M, int N, int total_kb, int kb_per_split, int splits, int* status, cudaStream_t stream) {
+int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
     GB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  Cfg<BN>::SMEM_BYTES));
     attr_set = true;
   }
-  dim3 grid(gb_div_up(N, BM), gb_div_up(M, BN), splits);
-  gemm_tc_kernel<BN><<<grid, 192, Cfg<BN>::SMEM_BYTES, stream>>>(tw, tx, bias, out, ldo, mode, M, N, total_kb,
-                                                               kb_per_split, status);
+  dim3 grid(gb_div_up(p.N, BM), gb_div_up(p.M, BN), p.splits);
+  gemm_tc_kernel<BN><<<grid, 192, Cfg<BN>::SMEM_BYTES, stream>>>(tw, tx, p);
   return GB_OK;
 }
 
@@ -283,29 +390,44 @@ GB_API long long gb_linear_tc_workspace(int M, int N, int K) {
   return splits > 1 ? (long long)splits * M * N : 0;
 }
 
+// Number of K splits gb_linear_tc uses for these sizes.
+GB_API int gb_linear_tc_splits(int M, int N, int K) {
+  int bn, splits, kbs;
+  plan(M, N, K, &bn, &splits, &kbs);
+  return splits;
+}
+
 // 1 if gb_linear_tc takes these operands, else 0 (the caller then uses the CUDA-core kernel).
 GB_API int gb_linear_tc_supported(const void* X, long long ldx, const void* W, long long ldw, int K) {
   return (K > 0 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ((uintptr_t)X & 15) == 0 && ((uintptr_t)W & 15) == 0)
              ? 1 : 0;
 }
 
-// X: [M, K] bf16 (row stride ldx), W: [N, K] bf16 (row stride ldw), bias: f32 [N] or null,
-// out: [M, N] bf16 or f32 (row stride ldo); accumulate adds into an f32 out.
+// X: [M, K] bf16 (row stride ldx), W: [N, K] bf16 (row stride ldw), bias: f32 [N] or null.
+// mode 0: out bf16 [M, N]; 1: out f32; 2: out f32 += ; 3: SwiGLU, W rows alternating in blocks of
+// 64 between gate and up (N = 2 * features, a multiple of 128), out bf16 [M, N / 2].
 // workspace: gb_linear_tc_workspace(M, N, K) floats (may be null when that is 0).
-// Returns the number of kernels launched (1 or 2), or a negative error code.
+// defer != 0 (mode 2 only): when K is split, leave the partial tiles in the workspace
+// ([splits][M][N], without bias) for the caller's next kernel to add; nothing is written to out.
+// prefetch / prefetch_bytes: the weights of the product that follows, or null / 0.
+// flags bit 0: read the weights with an evict-first hint.
+// Returns the number of kernels launched, or a negative error code.
 GB_API int gb_linear_tc(const void* X, long long ldx, const void* W, long long ldw, const float* bias, void* out,
-                        int out_dtype, long long ldo, int accumulate, int M, int N, int K, float* workspace,
-                        int* status, cudaStream_t stream) {
+                        int mode, long long ldo, int M, int N, int K, float* workspace, int defer,
+                        const void* prefetch, long long prefetch_bytes, int flags, int* status,
+                        cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (!gb_linear_tc_supported(X, ldx, W, ldw, K))
     GB_FAIL(GB_ERR_ARG, "gb_linear_tc: K = %d and the row strides (%lld, %lld) must be multiples of 8 and the bases "
             "16-byte aligned", K, ldx, ldw);
-  if (accumulate && out_dtype != GB_F32) GB_FAIL(GB_ERR_ARG, "gb_linear_tc: accumulation needs a 32-bit output");
-  if (out_dtype != GB_F32 && out_dtype != GB_BF16) GB_FAIL(GB_ERR_ARG, "gb_linear_tc: output dtype %d", out_dtype);
+  if (mode < OUT_BF16 || mode > OUT_SWIGLU) GB_FAIL(GB_ERR_ARG, "gb_linear_tc: output mode %d", mode);
+  if (mode == OUT_SWIGLU && N % 128 != 0)
+    GB_FAIL(GB_ERR_ARG, "gb_linear_tc: the SwiGLU epilogue needs 2 * features = %d to be a multiple of 128", N);
   if (gb_div_up(M, 16) > 65535) GB_FAIL(GB_ERR_ARG, "gb_linear_tc: M = %d is too large", M);
   int bn, splits, kb_per_split;
   plan(M, N, K, &bn, &splits, &kb_per_split);
   if (splits > 1 && workspace == nullptr) GB_FAIL(GB_ERR_ARG, "gb_linear_tc: these sizes need a workspace");
+  if (defer && mode != OUT_F32_ACC) GB_FAIL(GB_ERR_ARG, "gb_linear_tc: only an accumulating product can be deferred");
 
   CUtensorMap tw, tx;
   {
@@ -321,31 +443,36 @@ GB_API int gb_linear_tc(const void* X, long long ldx, const void* W, long long l
   }
   if (!make_tmap(&tx, X, M, K, ldx, bn)) GB_FAIL(GB_ERR_CUDA, "gb_linear_tc: cuTensorMapEncodeTiled failed (X)");
 
-  const int final_mode = out_dtype == GB_BF16 ? OUT_BF16 : (accumulate ? OUT_F32_ACC : OUT_F32);
-  const int mode = splits > 1 ? OUT_PARTIAL : final_mode;
-  void* dst = splits > 1 ? (void*)workspace : out;
-  const int total_kb = gb_div_up(K, BK);
+  GemmParams p;
+  p.bias = bias; p.out = out; p.ldo = ldo; p.mode = mode; p.M = M; p.N = N;
+  p.total_kb = gb_div_up(K, BK); p.kb_per_split = kb_per_split; p.splits = splits;
+  p.ws = workspace;
+  const bool decode_like = M <= 64;
+  p.prefetch = decode_like ? (const uint8_t*)prefetch : nullptr;
+  p.prefetch_bytes = decode_like ? (prefetch_bytes > (64ll << 20) ? (64ll << 20) : prefetch_bytes) : 0;
+  if (((uintptr_t)p.prefetch & 15) != 0) p.prefetch = nullptr;
+  p.stream_weights = (decode_like && (flags & 1)) ? 1 : 0;   // flags bit 0: evict-first hint for the weights
+  p.status = status;
   int rc;
   switch (bn) {
-    case 16: rc = launch<16>(tw, tx, bias, dst, ldo, mode, M, N, total_kb, kb_per_split, splits, status, stream); break;
-    case 32: rc = launch<32>(tw, tx, bias, dst, ldo, mode, M, N, total_kb, kb_per_split, splits, status, stream); break;
-    case 64: rc = launch<64>(tw, tx, bias, dst, ldo, mode, M, N, total_kb, kb_per_split, splits, status, stream); break;
-    default: rc = launch<128>(tw, tx, bias, dst, ldo, mode, M, N, total_kb, kb_per_split, splits, status, stream); break;
+    case 16: rc = launch<16>(tw, tx, p, stream); break;
+    case 32: rc = launch<32>(tw, tx, p, stream); break;
+    case 64: rc = launch<64>(tw, tx, p, stream); break;
+    default: rc = launch<128>(tw, tx, p, stream); break;
   }
   if (rc != GB_OK) return rc;
   GB_CHECK_LAUNCH("gb_linear_tc");
-  if (splits > 1) {
-    const long long total = (long long)M * N;
-    const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(workspace, splits, bias, out, ldo, final_mode, M, N);
+  if (splits > 1 && !defer) {
+    const long long work = (long long)M * (mode == OUT_SWIGLU ? N / 2 : N);
+    const int blocks = (int)((work + 255) / 256 < 148 * 8 ? (work + 255) / 256 : 148 * 8);
+    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(workspace, splits, bias, out, ldo, mode, M, N);
     GB_CHECK_LAUNCH("gb_linear_tc (split-K reduce)");
     return 2;
   }
   return 1;
 }
 
-// Forget the tensor maps of weights (call when weights are freed, so that a
-// later allocation at the same address with another shape gets a new map).
+// Forget the tensor maps of weights.
 GB_API void gb_linear_tc_forget() {
   std::lock_guard<std::mutex> lock(g_wmap_mutex);
   g_wmaps.clear();

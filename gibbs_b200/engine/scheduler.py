@@ -76,6 +76,15 @@ class Sequence_:
     def tokens(self) -> list:
         return self.prompt + self.output
 
+    def span(self, lo: int, hi: int) -> list:
+        """Tokens lo..hi-1 of prompt + output, without building the whole list."""
+        n = len(self.prompt)
+        if hi <= n:
+            return self.prompt[lo:hi]
+        if lo >= n:
+            return self.output[lo - n:hi - n]
+        return self.prompt[lo:] + self.output[:hi - n]
+
     @property
     def remaining(self) -> int:
         return len(self.prompt) + len(self.output) - self.fed
@@ -174,8 +183,8 @@ class Scheduler:
             first = min(seq.remaining, max(budget, 1))
             # the running requests' next tokens are counted too, so that a request is not
             # admitted only to be preempted in the same step
-            others = [StepEntry(s.id, s.tokens[s.fed:s.fed + 1]) for s in self.running if s.remaining > 0]
-            if not self.engine.can_run(others + [StepEntry(seq.id, seq.tokens[:first])]):
+            others = [StepEntry(s.id, s.span(s.fed, s.fed + 1)) for s in self.running if s.remaining > 0]
+            if not self.engine.can_run(others + [StepEntry(seq.id, seq.span(0, first))]):
                 self.engine.close(seq.id)
                 if not self.running:
                     # nothing else holds pages: this request can never start
@@ -226,7 +235,7 @@ class Scheduler:
         plan = self._plan()
         # Pages: drop the most recently admitted request until the step fits.
         while plan:
-            entries = [StepEntry(s.id, s.tokens[s.fed:s.fed + n]) for s, n in plan]
+            entries = [StepEntry(s.id, s.span(s.fed, s.fed + n)) for s, n in plan]
             if self.engine.can_run(entries):
                 break
             victim = max((s for s, _ in plan), key=lambda s: s.admitted)
@@ -246,7 +255,7 @@ class Scheduler:
         n_prefill = n_decode = 0
         for s, n in plan:
             last = s.fed + n == len(s.prompt) + len(s.output)
-            entries.append(StepEntry(s.id, s.tokens[s.fed:s.fed + n], [n - 1] if last else []))
+            entries.append(StepEntry(s.id, s.span(s.fed, s.fed + n), [n - 1] if last else []))
             if last:
                 samplers.append(s)
             if s.decoding:

@@ -63,7 +63,7 @@ class Engine:
     """A model, its cache and the step function over them."""
 
     def __init__(self, model: CausalLM, n_pages: int, page_size: int = 16, max_requests: int = 64,
-                 max_step_tokens: int = 8192, max_context: Optional[int] = None):
+                 max_step_tokens: int = 8192, max_context: Optional[int] = None, use_graphs: bool = True):
         self.model = model
         self.device = model.rt.device
         if self.device.type != "cuda":
@@ -85,6 +85,11 @@ class Engine:
         self._dev_meta = torch.empty(cap, dtype=torch.int32, device=self.device)
         self.status = ops.device_status(self.device)
         self.steps_run = 0
+        # decode steps are replayed from CUDA graphs, one per batch size, unless a part of the
+        # model cannot be captured (it reads host-side step data)
+        self.use_graphs = bool(use_graphs) and all(getattr(b.mixer, "capturable", True) for b in model.blocks)
+        self._graphs: dict = {}
+        self._graph_bufs: dict = {}
 
     # -- request life ----------------------------------------------------------
     def open(self, request_id) -> None:
@@ -149,7 +154,12 @@ class Engine:
         """Run one batch.  Returns float32 logits [number of wanted places,
         vocab] on the device, in the order of the entries and of each entry's
         ``want``; None when nothing is wanted.  Raises OutOfPages, before
-        anything changes, if the pools cannot hold the step."""
+        anything changes, if the pools cannot hold the step.
+
+        A step in which every request brings exactly one token and wants its
+        logits (a decode step) is replayed from a CUDA graph captured for that
+        batch size; its logits live in the graph's own buffer and are
+        overwritten by the next decode step of the same size."""
         entries = list(entries)
         n_tok = self._validate(entries)
         if not self.can_run(entries):
@@ -160,16 +170,47 @@ class Engine:
 
         n_req = len(entries)
         n_want = sum(len(e.want) for e in entries)
-        n_groups = len(self.cache.groups)
-        mb = self.cache.max_blocks
-        # layout of the metadata buffer (int32), every section 16-byte aligned
+        offs, total = self._layout(n_tok, n_req, n_want)
+        turn = self._fill_staging(entries, rcs, offs, n_tok, n_req, n_want)
+        decode = self.use_graphs and n_tok == n_req and n_want == n_req
+
+        if decode and n_req in self._graphs:
+            g = self._graphs[n_req]
+            g["meta"][:total].copy_(self._staging[turn][:total], non_blocking=True)
+            self._record(turn)
+            g["graph"].replay()
+            ops._launched(g["launches"])
+            logits = g["logits"]
+        else:
+            dev = self._graph_meta(n_req, total) if decode else self._dev_meta
+            dev[:total].copy_(self._staging[turn][:total], non_blocking=True)
+            self._record(turn)
+            step, caches = self._state(dev, offs, entries, rcs, n_tok, n_req, n_want, fixed=decode)
+            before = ops.launch_count()
+            logits = self.model.forward(step, caches)
+            if decode:
+                # this run was the real step; capture the same work for the next steps of this size
+                self._capture(n_req, dev, step, caches, ops.launch_count() - before)
+        for e, rc in zip(entries, rcs):
+            self.cache.advance(rc, rc.length + len(e.tokens))
+        self.steps_run += 1
+        return logits
+
+    # -- pieces of a step --------------------------------------------------------
+    def _layout(self, n_tok: int, n_req: int, n_want: int):
+        """Offsets (in int32) of the sections of the metadata buffer, each
+        16-byte aligned: token ids, token->request, token->position; per
+        request first row, count, length before, length after, slot; wanted
+        rows; one block table per group."""
+        n_groups, mb = len(self.cache.groups), self.cache.max_blocks
         sizes = [n_tok, n_tok, n_tok, n_req, n_req, n_req, n_req, n_req, max(n_want, 1), n_groups * n_req * mb]
         offs, o = [], 0
-        for s in sizes:
+        for sz in sizes:
             offs.append(o)
-            o += _align4(s)
-        total = o
+            o += _align4(sz)
+        return offs, o
 
+    def _fill_staging(self, entries, rcs, offs, n_tok, n_req, n_want) -> int:
         turn = self._turn
         self._turn = (turn + 1) % len(self._staging)
         if self._staging_evt[turn] is not None:
@@ -190,15 +231,22 @@ class Engine:
                 wr[w_i] = row + int(w)
                 w_i += 1
             row += n
+        n_groups, mb = len(self.cache.groups), self.cache.max_blocks
         if n_groups:
             bt = buf[offs[9]:offs[9] + n_groups * n_req * mb].reshape(n_groups, n_req, mb)
             self.cache.fill_block_tables(rcs, bt)
+        return turn
 
-        dev = self._dev_meta
-        dev[:total].copy_(self._staging[turn][:total], non_blocking=True)
+    def _record(self, turn: int) -> None:
         evt = torch.cuda.Event()
         evt.record()
         self._staging_evt[turn] = evt
+
+    def _state(self, dev, offs, entries, rcs, n_tok, n_req, n_want, fixed: bool = False):
+        """The step's state and cache views over the device metadata buffer
+        ``dev``.  ``fixed`` (graph capture): launch-sizing hints that do not
+        depend on the requests' current lengths."""
+        n_groups, mb = len(self.cache.groups), self.cache.max_blocks
 
         def view(i, n):
             return dev[offs[i]:offs[i] + n]
@@ -209,18 +257,28 @@ class Engine:
             q_start=view(3, n_req), q_len=view(4, n_req), start_pos=view(5, n_req), ctx_len=view(6, n_req),
             want_rows=view(8, n_want), status=self.status,
             max_q_len=max(len(e.tokens) for e in entries),
-            max_ctx_len=max(rc.length + len(e.tokens) for e, rc in zip(entries, rcs)),
-            host_q_start=[int(v) for v in qs], host_q_len=[int(v) for v in ql],
-            host_start_pos=[int(v) for v in sp],
+            max_ctx_len=self.max_context if fixed else max(rc.length + len(e.tokens) for e, rc in zip(entries, rcs)),
+            host_q_start=[] if fixed else [int(v) for v in np.cumsum([0] + [len(e.tokens) for e in entries[:-1]])],
+            host_q_len=[] if fixed else [len(e.tokens) for e in entries],
+            host_start_pos=[] if fixed else [rc.length for rc in rcs],
         )
         tables = [dev[offs[9] + g * n_req * mb: offs[9] + (g + 1) * n_req * mb].view(n_req, mb)
                   for g in range(n_groups)]
-        caches = self.cache.views(tables, view(7, n_req), [rc.slot for rc in rcs])
-        logits = self.model.forward(step, caches)
-        for e, rc in zip(entries, rcs):
-            self.cache.advance(rc, rc.length + len(e.tokens))
-        self.steps_run += 1
-        return logits
+        caches = self.cache.views(tables, view(7, n_req), [] if fixed else [rc.slot for rc in rcs])
+        return step, caches
+
+    def _graph_meta(self, batch: int, total: int) -> torch.Tensor:
+        buf = self._graph_bufs.get(batch)
+        if buf is None:
+            buf = self._graph_bufs[batch] = torch.empty(total, dtype=torch.int32, device=self.device)
+        return buf
+
+    def _capture(self, batch: int, dev, step, caches, launches: int) -> None:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(step, caches)
+        ops._launched(-launches)        # the wrappers counted the captured launches, which did not run
+        self._graphs[batch] = {"graph": graph, "meta": dev, "logits": logits, "launches": launches}
 
     def check_status(self) -> None:
         """Synchronise and raise if a kernel met a page id outside its pool."""

@@ -8,6 +8,7 @@ GPU or a kernel library is missing, the call raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -92,8 +93,10 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Te
 
 
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
-            rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[r, :] = x[rows[r] or r, :] * rsqrt(mean(x^2) + eps) * gain; x is 32-bit."""
+            rows: Optional[torch.Tensor] = None, pending=None) -> torch.Tensor:
+    """out[r, :] = x[rows[r] or r, :] * rsqrt(mean(x^2) + eps) * gain; x is 32-bit.
+    ``pending`` = (partials [splits, n, dim], bias or None): sums a split-K
+    product left to be added to x first (and, without ``rows``, written back)."""
     _need_cuda(x, gain, out, rows)
     lib = library("core")
     dim = x.shape[1]
@@ -107,10 +110,32 @@ def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
         raise KernelError("rmsnorm: out has a different number of rows than x")
     _f32vec(gain, dim, "rmsnorm gain")
     _i32(rows, "rmsnorm rows")
+    ws = pbias = None
+    splits = 0
+    if pending is not None:
+        ws, pbias = pending
+        splits = ws.shape[0]
+        if ws.dtype != torch.float32 or not ws.is_contiguous() or ws.shape[1:] != x.shape:
+            raise KernelError("rmsnorm: pending partial sums must be contiguous float32 [splits, n, dim]")
+        _f32vec(pbias, dim, "rmsnorm pending bias")
     _launched(1)
     check(lib, lib.gb_rmsnorm(_ptr(x), _c_ll(ldx), _ptr(gain), _ptr(out), dtype_code(out.dtype), _ptr(rows),
-                              _c_int(n_rows), _c_int(dim), _c_float(eps), _stream()))
+                              _c_int(n_rows), _c_int(dim), _c_float(eps), _ptr(ws), _c_int(splits),
+                              _c_ll(x.shape[0]), _ptr(pbias), _stream()))
     return out
+
+
+def add_pending(x: torch.Tensor, ws: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """x += sum over splits of ws[s] (+ bias), in split order."""
+    _need_cuda(x, ws, bias)
+    lib = library("core")
+    if x.dtype != torch.float32 or ws.dtype != torch.float32 or not ws.is_contiguous() or ws.shape[1:] != x.shape:
+        raise KernelError("add_pending: x float32 [n, dim] and partial sums float32 [splits, n, dim] expected")
+    _f32vec(bias, x.shape[1], "add_pending bias")
+    _launched(1)
+    check(lib, lib.gb_add_pending(_ptr(x), _c_ll(_rows(x, "x")), _ptr(ws), _c_int(ws.shape[0]), _ptr(bias),
+                                  _c_ll(x.shape[0]), _c_int(x.shape[1]), _stream()))
+    return x
 
 
 def linear_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
@@ -152,29 +177,58 @@ def device_status(device) -> torch.Tensor:
     return t
 
 
+# tuning switches of the tensor-core product: prefetch the next weight towards L2; evict-first hint
+_TC_PREFETCH = os.environ.get("GIBBS_B200_PREFETCH", "0") != "0"
+_TC_FLAGS = 1 if os.environ.get("GIBBS_B200_EVICT_FIRST", "1") != "0" else 0
+
+
 def linear_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-              accumulate: bool = False) -> torch.Tensor:
-    """out (+)= a @ w.T (+ bias) for bfloat16 a and w on the tensor cores (csrc/gemm_tc.cu)."""
-    _need_cuda(a, w, bias, out)
+              accumulate: bool = False, swiglu: bool = False, prefetch: Optional[torch.Tensor] = None,
+              defer: bool = False):
+    """out (+)= a @ w.T (+ bias) for bfloat16 a and w on the tensor cores
+    (csrc/gemm_tc.cu).  ``swiglu``: w holds gate and up rows alternating in
+    blocks of 64 and out [m, n/2] gets (g * sigmoid(g)) * u.  ``prefetch``:
+    the weight the next product will read, pulled towards L2 meanwhile.
+    ``defer`` (with ``accumulate``): when the kernel splits K, nothing is
+    added to ``out``; the partial sums [splits, m, n] are returned instead,
+    for the caller's next kernel to add (without the bias).  Otherwise
+    returns ``out``."""
+    _need_cuda(a, w, bias, out, prefetch)
     lib = library("tensorcore")
     m, k = a.shape
     n = w.shape[0]
-    if w.shape[1] != k or out.shape[0] != m or out.shape[1] != n:
+    n_out = n // 2 if swiglu else n
+    if w.shape[1] != k or out.shape[0] != m or out.shape[1] != n_out:
         raise KernelError(f"linear: shapes a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} disagree")
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("linear_tc: bfloat16 operands expected")
+    if swiglu:
+        if out.dtype != torch.bfloat16 or n % 128:
+            raise KernelError("linear_tc: the SwiGLU epilogue writes bfloat16 and needs 2*features % 128 == 0")
+        mode = 3
+    elif accumulate:
+        if out.dtype != torch.float32:
+            raise KernelError("linear_tc: accumulation needs a float32 output")
+        mode = 2
+    else:
+        mode = 0 if out.dtype == torch.bfloat16 else 1
+        dtype_code(out.dtype)
     _f32vec(bias, n, "linear bias")
-    lib.gb_linear_tc_workspace.restype = ctypes.c_longlong
-    need = lib.gb_linear_tc_workspace(_c_int(m), _c_int(n), _c_int(k))
-    ws = torch.empty(need, dtype=torch.float32, device=a.device) if need else None
+    splits = lib.gb_linear_tc_splits(_c_int(m), _c_int(n), _c_int(k))
+    ws = torch.empty((splits, m, n), dtype=torch.float32, device=a.device) if splits > 1 else None
+    defer = bool(defer and accumulate and splits > 1)
+    if not _TC_PREFETCH:
+        prefetch = None
+    pf_bytes = prefetch.numel() * prefetch.element_size() if prefetch is not None else 0
     rc = lib.gb_linear_tc(
         _ptr(a), _c_ll(_rows(a, "linear a")), _ptr(w), _c_ll(_rows(w, "linear w")), _ptr(bias), _ptr(out),
-        dtype_code(out.dtype), _c_ll(_rows(out, "linear out")), _c_int(1 if accumulate else 0), _c_int(m), _c_int(n),
-        _c_int(k), _ptr(ws), _ptr(device_status(a.device)), _stream())
+        _c_int(mode), _c_ll(_rows(out, "linear out")), _c_int(m), _c_int(n), _c_int(k), _ptr(ws),
+        _c_int(1 if defer else 0), _ptr(prefetch), _c_ll(pf_bytes), _c_int(_TC_FLAGS),
+        _ptr(device_status(a.device)), _stream())
     if rc < 0:
         check(lib, rc)
     _launched(rc)
-    return out
+    return ws if defer else out
 
 
 def linear_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
@@ -186,12 +240,12 @@ def linear_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-           accumulate: bool = False) -> torch.Tensor:
+           accumulate: bool = False, prefetch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out (+)= a @ w.T (+ bias); picks the matrix-product kernel for the
     operand types: tensor cores for bfloat16 x bfloat16, 32-bit FMA otherwise
     (float32 operands, a weight kept in 32-bit, rows TMA cannot address)."""
     if linear_tc_supported(a, w):
-        return linear_tc(a, w, bias, out, accumulate)
+        return linear_tc(a, w, bias, out, accumulate, prefetch=prefetch)
     return linear_simt(a, w, bias, out, accumulate)
 
 
@@ -221,7 +275,7 @@ def cast(src: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 
 def short_conv(bcx: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
                slot_ids: torch.Tensor, tok_req: torch.Tensor, q_start: torch.Tensor, q_len: torch.Tensor,
-               out: torch.Tensor) -> torch.Tensor:
+               out: torch.Tensor, max_q_len: int = 0) -> torch.Tensor:
     """Gated short convolution over a ragged batch; see csrc/conv.cu.
     state: float32 [n_slots, kernel-1, hidden] (the slot axis may be strided)."""
     _need_cuda(bcx, taps, bias, state, slot_ids, tok_req, q_start, q_len, out)
@@ -236,11 +290,13 @@ def short_conv(bcx: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tenso
         raise KernelError(f"short_conv: state must be float32 [slots, {kk - 1}, {hidden}] with contiguous slots")
     for t, w in ((slot_ids, "slot_ids"), (tok_req, "tok_req"), (q_start, "q_start"), (q_len, "q_len")):
         _i32(t, "short_conv " + w)
-    _launched(2)
-    check(lib, lib.gb_short_conv(
+    rc = lib.gb_short_conv(
         _ptr(bcx), dtype_code(bcx.dtype), _c_ll(_rows(bcx, "short_conv bcx")), _ptr(taps), _ptr(bias), _ptr(state),
         _c_ll(state.stride(0)), _ptr(slot_ids), _ptr(tok_req), _ptr(q_start), _ptr(q_len), _ptr(out), _c_int(n),
-        _c_int(q_len.numel()), _c_int(hidden), _c_int(kk), _stream()))
+        _c_int(q_len.numel()), _c_int(hidden), _c_int(kk), _c_int(max_q_len), _stream())
+    if rc < 0:
+        check(lib, rc)
+    _launched(rc)
     return out
 
 
@@ -321,7 +377,7 @@ def attention_tc_supported(q, out, heads, kv_heads, head_dim) -> bool:
 def attention_splits(n_requests: int, kv_heads: int, max_ctx_len: int) -> int:
     """How many CTAs share the keys of one (request, kv head) when decoding:
     enough to occupy the GPU, at least two tiles of 64 keys each."""
-    by_sm = max(1, 296 // max(1, n_requests * kv_heads))
+    by_sm = max(1, 592 // max(1, n_requests * kv_heads))
     by_len = max(1, -(-max_ctx_len // 128))
     return max(1, min(32, by_sm, by_len))
 

@@ -12,16 +12,18 @@ A part
 
 Categories and what each must implement:
 
-  norm        ``forward(x_f32 [N, dim], out=None, rows=None) -> [N or len(rows), dim]``
-              in the compute dtype.
+  norm        ``forward(x, out=None, rows=None) -> [N or len(rows), dim]`` in the
+              compute dtype; x is the ``Residual`` stream (or a float32 tensor).
   position    ``rotary() -> Rotary | None`` (tables a mixer's kernel applies)
               and ``embed(x_f32, step)`` (an in-place hook on the embedded
               tokens; default nothing).
   mixer       ``cache_needs() -> [PagedKV | SlotState, ...]`` and
-              ``forward(h, residual_f32, step, caches)`` which ADDS the mixer's
-              output into ``residual_f32``; ``caches`` holds one view per need.
-  feed_forward ``forward(h, residual_f32, step)``, adding likewise.
-  block       built from its four parts; ``forward(x_f32, step, caches)``.
+              ``forward(h, residual, step, caches)`` which ADDS the mixer's
+              output into the ``Residual`` stream (``residual.add_(y)``, or a
+              projection called with ``out=residual, accumulate=True``);
+              ``caches`` holds one view per need.
+  feed_forward ``forward(h, residual, step)``, adding likewise.
+  block       built from its four parts; ``forward(residual, step, caches)``.
   embedding   ``forward(ids_i32 [N]) -> x_f32 [N, dim]``.
   head        ``forward(z [R, dim]) -> logits_f32 [R, vocab]``.
 
@@ -77,6 +79,42 @@ class Runtime:
         return torch.empty(*shape, dtype=dtype or self.dtype, device=self.device)
 
 
+class Residual:
+    """The 32-bit residual stream of a step, [tokens, hidden], plus at most one
+    set of partial sums that a split-K product left to be added to it.  The
+    next norm adds them while it reads the stream (one kernel instead of
+    three); anything else that needs the values calls ``tensor()``."""
+
+    def __init__(self, x: torch.Tensor):
+        self.x = x
+        self.pending = None            # (partials [splits, tokens, hidden], bias or None)
+
+    def tensor(self) -> torch.Tensor:
+        """The stream with everything added."""
+        if self.pending is not None:
+            from .. import ops
+            ops.add_pending(self.x, *self.pending)
+            self.pending = None
+        return self.x
+
+    def defer(self, partials: torch.Tensor, bias) -> None:
+        self.tensor()
+        self.pending = (partials, bias)
+
+    def take_pending(self):
+        p, self.pending = self.pending, None
+        return p
+
+    def add_(self, y: torch.Tensor) -> "Residual":
+        """For parts written with tensor operations: stream += y."""
+        self.tensor().add_(y.to(torch.float32))
+        return self
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+
 class Part:
     category: str = ""
 
@@ -119,6 +157,9 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     category = "mixer"
+    # False for a mixer whose forward reads the step's host-side lists or otherwise cannot be
+    # recorded into a CUDA graph; the engine then runs decode steps without graphs.
+    capturable = True
 
     def cache_needs(self) -> list:
         return []

@@ -7,7 +7,7 @@ import torch
 
 from .. import ops
 from .base import FeedForward, TensorDecl, VECTOR, register_part
-from .linear import Linear
+from .linear import Linear, can_fuse_swiglu, interleave_gate_up
 
 
 class SwiGLU(FeedForward):
@@ -25,20 +25,28 @@ class SwiGLU(FeedForward):
         self.hidden, self.inner = int(params["hidden"]), int(params["inner"])
         if tensors["gate.weight"].dtype != tensors["up.weight"].dtype:
             raise ValueError("gate and up projections are stored in different dtypes")
-        w = torch.cat([tensors["gate.weight"], tensors["up.weight"]], 0)
+        self.fused = can_fuse_swiglu(tensors["gate.weight"], rt)
+        join = interleave_gate_up if self.fused else (lambda g, u: torch.cat([g, u], 0))
+        w = join(tensors["gate.weight"], tensors["up.weight"])
         b = None
         if params.get("bias"):
-            b = torch.cat([tensors["gate.bias"].to(torch.float32), tensors["up.bias"].to(torch.float32)], 0)
-        self.gate_up = Linear(w, b, rt)
+            b = join(tensors["gate.bias"].to(torch.float32), tensors["up.bias"].to(torch.float32))
+        self.gate_up = Linear(w, b, rt, swiglu=self.fused)
         self.down = Linear(tensors["down.weight"], tensors.get("down.bias"), rt)
 
     def kernel_libraries(self):
         return tuple(set(self.gate_up.kernel_libraries()) | set(self.down.kernel_libraries()) | {"core"})
 
+    def linears(self):
+        return [self.gate_up, self.down]
+
     def forward(self, h, residual, step):
-        gu = self.gate_up(h)
-        act = self.rt.empty(h.shape[0], self.inner)
-        ops.swiglu(gu, act)
+        if self.fused:
+            act = self.gate_up(h)
+        else:
+            gu = self.gate_up(h)
+            act = self.rt.empty(h.shape[0], self.inner)
+            ops.swiglu(gu, act)
         self.down(act, out=residual, accumulate=True)
 
 

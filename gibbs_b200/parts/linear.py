@@ -7,15 +7,23 @@ from typing import Optional
 import torch
 
 from .. import ops
-from .base import Runtime
+from .base import Residual, Runtime
 
 
 class Linear:
-    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor], rt: Runtime):
+    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor], rt: Runtime, swiglu: bool = False):
+        """``swiglu``: the weight holds gate and up rows alternating in blocks
+        of 64 and calls return (g * sigmoid(g)) * u (see ``interleave_gate_up``)."""
         self.weight = weight.contiguous()          # [out, in], as stored (bfloat16 or float32)
         self.bias = None if bias is None else bias.to(torch.float32).contiguous()
         self.out_features, self.in_features = self.weight.shape
+        if swiglu:
+            self.out_features //= 2
+        self.swiglu = swiglu
         self.rt = rt
+        # the weight of the product that runs after this one (set by the model once it is
+        # assembled); the tensor-core kernel pulls it towards L2 while it works
+        self.next_weight: Optional[torch.Tensor] = None
 
     def kernel_libraries(self):
         return ops.linear_libraries(self.weight.dtype, self.rt.dtype)
@@ -24,6 +32,34 @@ class Linear:
                  out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """out (+)= x W^T + b.  ``accumulate`` adds into a float32 ``out``
         (the residual stream)."""
+        if isinstance(out, Residual):
+            if not accumulate:
+                raise ValueError("a projection can only add into the residual stream")
+            if ops.linear_tc_supported(x, self.weight):
+                res = ops.linear_tc(x, self.weight, self.bias, out.tensor(), accumulate=True,
+                                    prefetch=self.next_weight, defer=True)
+                if res is not out.x:              # K was split: the next norm adds the partial sums
+                    out.defer(res, self.bias)
+                return out
+            ops.linear(x, self.weight, self.bias, out.tensor(), True)
+            return out
         if out is None:
             out = torch.empty(x.shape[0], self.out_features, dtype=out_dtype or self.rt.dtype, device=x.device)
-        return ops.linear(x, self.weight, self.bias, out, accumulate)
+        if self.swiglu:
+            return ops.linear_tc(x, self.weight, self.bias, out, swiglu=True, prefetch=self.next_weight)
+        return ops.linear(x, self.weight, self.bias, out, accumulate, prefetch=self.next_weight)
+
+
+def can_fuse_swiglu(gate: torch.Tensor, rt: Runtime) -> bool:
+    """Whether gate/up of this shape run as one product with the SwiGLU epilogue."""
+    inner, hidden = gate.shape
+    return gate.dtype == torch.bfloat16 and rt.dtype == torch.bfloat16 and inner % 64 == 0 and hidden % 8 == 0
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[gate rows 0..63; up rows 0..63; gate rows 64..127; up rows 64..127; ...]:
+    each 128-row tile of the product then holds g and u of the same 64 features."""
+    inner = gate.shape[0]
+    g = gate.reshape(inner // 64, 64, *gate.shape[1:])
+    u = up.reshape(inner // 64, 64, *up.shape[1:])
+    return torch.stack([g, u], 1).reshape(2 * inner, *gate.shape[1:]).contiguous()

@@ -8,7 +8,7 @@ from typing import Optional
 import torch
 
 from ..config.plan import ModelPlan, PartSpec
-from .base import Runtime, part_class
+from .base import Residual, Runtime, part_class
 
 
 def plan_parts(plan: ModelPlan):
@@ -28,6 +28,21 @@ class CausalLM:
         self.plan, self.rt = plan, rt
         self.embedding, self.blocks, self.final_norm, self.head = embedding, blocks, final_norm, head
         self.vocab_size, self.hidden_size = plan.vocab_size, plan.hidden_size
+        self._link_products()
+
+    def _link_products(self) -> None:
+        """Tell every projection which weight is read after its own, in the
+        order the plan runs the layers (the head wraps around to the first
+        layer of the next step).  Parts that expose no ``linears()`` are skipped."""
+        chain = []
+        for entry in self.plan.order:
+            block = self.blocks[entry.layer]
+            for part in (block.mixer, block.ffn):
+                chain += list(getattr(part, "linears", lambda: [])())
+        chain += list(getattr(self.head, "linears", lambda: [])())
+        for cur, nxt in zip(chain, chain[1:] + chain[:1]):
+            if cur is not nxt:
+                cur.next_weight = nxt.weight
 
     def entry_needs(self):
         """For each entry of the plan's order: (cache needs of its mixer, the
@@ -44,7 +59,7 @@ class CausalLM:
     def forward(self, step, caches) -> Optional[torch.Tensor]:
         """Run the step's tokens through every entry of the order; return the
         32-bit logits of the wanted rows, [n_want, vocab], or None."""
-        x = self.embedding.forward(step.token_ids)
+        x = Residual(self.embedding.forward(step.token_ids))
         for e, entry in enumerate(self.plan.order):
             self.blocks[entry.layer].forward(x, step, caches[e])
         if step.n_want == 0:

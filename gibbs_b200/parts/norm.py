@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .base import Norm, TensorDecl, VECTOR, register_part
+from .base import Norm, Residual, TensorDecl, VECTOR, register_part
 
 
 class RMSNorm(Norm):
@@ -19,10 +19,13 @@ class RMSNorm(Norm):
         self.gain = tensors["weight"].to(torch.float32).contiguous()
 
     def forward(self, x, out=None, rows=None):
+        pending = None
+        if isinstance(x, Residual):
+            pending, x = x.take_pending(), x.x
         n = x.shape[0] if rows is None else rows.numel()
         if out is None:
             out = self.rt.empty(n, self.dim)
-        return ops.rmsnorm(x, self.gain, self.eps, out, rows)
+        return ops.rmsnorm(x, self.gain, self.eps, out, rows, pending)
 
 
 register_part("norm", "rmsnorm", RMSNorm)

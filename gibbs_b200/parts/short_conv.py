@@ -42,6 +42,9 @@ class GatedShortConv(Mixer):
     def kernel_libraries(self):
         return tuple(set(self.in_proj.kernel_libraries()) | set(self.out_proj.kernel_libraries()) | {"core"})
 
+    def linears(self):
+        return [self.in_proj, self.out_proj]
+
     def cache_needs(self):
         return [SlotState((self.kernel - 1, self.hidden), torch.float32)]
 
@@ -50,7 +53,7 @@ class GatedShortConv(Mixer):
         bcx = self.in_proj(h)
         y = self.rt.empty(h.shape[0], self.hidden)
         ops.short_conv(bcx, self.taps, self.conv_bias, slot.state, slot.slot_ids, step.tok_req, step.q_start,
-                       step.q_len, y)
+                       step.q_len, y, max_q_len=step.max_q_len)
         self.out_proj(y, out=residual, accumulate=True)
 
 

@@ -190,6 +190,32 @@ def test_short_conv_ragged_batch(dtype, hidden, k, use_bias):
     assert torch.equal(got_state[untouched], state[untouched]) and torch.equal(got_state[:, 0], state[:, 0])
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden,k,use_bias", [(96, 4, True), (200, 2, False), (2048, 3, False)])
+def test_short_conv_one_token_per_request(dtype, hidden, k, use_bias):
+    """The fused path of decode steps, several steps in a row on the same slots."""
+    from gibbs_b200 import ops
+    torch.manual_seed(hidden * k)
+    n_req, n_slots = 5, 7
+    taps = torch.randn(hidden, k)
+    bias = torch.randn(hidden) if use_bias else None
+    state = torch.randn(n_slots, k - 1, hidden)
+    slot_ids = [6, 1, 0, 4, 2]
+    dev_state = state.to(DEV)
+    ref_state = state[slot_ids].double()
+    t = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    for step in range(k + 1):
+        bcx, ref = _quant(torch.randn(n_req, 3 * hidden), dtype)
+        out = torch.empty(n_req, hidden, dtype=_dt(dtype), device=DEV)
+        ops.short_conv(bcx, taps.to(DEV), None if bias is None else bias.to(DEV), dev_state, t(slot_ids),
+                       t(list(range(n_req))), t(list(range(n_req))), t([1] * n_req), out, max_q_len=1)
+        want, ref_state = _plain_conv(ref, taps.double(), None if bias is None else bias.double(), ref_state,
+                                      [1] * n_req)
+        _close(out, want, dtype)
+        assert torch.allclose(dev_state.cpu()[slot_ids].double(), ref_state, rtol=1e-6, atol=1e-6)
+    assert torch.equal(dev_state.cpu()[[3, 5]], state[[3, 5]])
+
+
 def test_short_conv_refuses_wide_kernels():
     from gibbs_b200 import ops
     from gibbs_b200.ops import KernelError
@@ -527,3 +553,71 @@ def test_attention_tensor_cores_far_key_and_tile_edges():
                             t(list(range(length - q_len, length))), 1.0, 0, out, status, hints=_Hints(before, [q_len]))
         assert out[-1, :hd].float().min().item() > 99.0, (length, far, q_len)
         assert abs(out[-1, 2 * hd:].float().mean().item()) < 1.0
+
+
+@pytest.mark.parametrize("m,f,k", [(1, 64, 64), (8, 192, 96), (8, 8192, 2048), (64, 256, 2048), (300, 448, 136),
+                                   (2, 128, 4096)])
+@pytest.mark.parametrize("use_bias", [False, True])
+def test_linear_tensor_cores_swiglu_epilogue(m, f, k, use_bias):
+    """gate and up as one product whose epilogue applies (g * sigmoid(g)) * u,
+    directly and through the split-K path."""
+    from gibbs_b200 import ops
+    from gibbs_b200.parts.linear import interleave_gate_up
+    torch.manual_seed(m + f + k)
+    a, ar = _quant(torch.randn(m, k), "bfloat16")
+    wg, wgr = _quant(torch.randn(f, k) / math.sqrt(k) * 2, "bfloat16")
+    wu, wur = _quant(torch.randn(f, k) / math.sqrt(k) * 2, "bfloat16")
+    bg, bu = torch.randn(f), torch.randn(f)
+    w = interleave_gate_up(wg, wu)
+    bias = interleave_gate_up(bg, bu).to(DEV) if use_bias else None
+    g = ar @ wgr.T + (bg.double() if use_bias else 0)
+    u = ar @ wur.T + (bu.double() if use_bias else 0)
+    want = g / (1 + torch.exp(-g)) * u
+    out = torch.full((m, f), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.linear_tc(a, w, bias, out, swiglu=True)
+    _close(out, want, "bfloat16")
+    assert int(ops.device_status(DEV).item()) == 0
+
+
+def test_linear_tensor_cores_with_prefetch_of_the_next_weight():
+    from gibbs_b200 import ops
+    torch.manual_seed(3)
+    a, ar = _quant(torch.randn(4, 512), "bfloat16")
+    w, wr = _quant(torch.randn(384, 512) / 20, "bfloat16")
+    nxt = torch.randn(1000, 333, device=DEV).to(torch.bfloat16)      # an odd number of bytes per 4 KB piece
+    out = torch.empty(4, 384, dtype=torch.float32, device=DEV)
+    ops.linear_tc(a, w, None, out, prefetch=nxt)
+    _close(out, ar @ wr.T, "float32")
+
+
+def test_deferred_split_k_and_norm_that_adds_the_partial_sums():
+    """A product into the residual stream that splits K leaves partial sums;
+    the norm adds them in split order, writes the stream back and normalises."""
+    from gibbs_b200 import ops
+    torch.manual_seed(11)
+    m, n, k, eps = 8, 256, 2048, 1e-5
+    a, ar = _quant(torch.randn(m, k), "bfloat16")
+    w, wr = _quant(torch.randn(n, k) / math.sqrt(k), "bfloat16")
+    bias, gain = torch.randn(n), 1 + 0.1 * torch.randn(n)
+    x0 = torch.randn(m, n)
+    x = x0.clone().to(DEV)
+    ws = ops.linear_tc(a, w, bias.to(DEV), x, accumulate=True, defer=True)
+    assert ws is not x and ws.shape[1:] == (m, n) and ws.shape[0] > 1
+    assert torch.equal(x.cpu(), x0)                                  # nothing was added yet
+    want_x = x0.double() + ar @ wr.T + bias.double()
+    want_h = want_x / torch.sqrt((want_x ** 2).mean(-1, keepdim=True) + eps) * gain.double()
+    # gathered rows: the stream itself stays as it was
+    rows = torch.tensor([5, 0, 5], dtype=torch.int32, device=DEV)
+    out = torch.empty(3, n, dtype=torch.float32, device=DEV)
+    ops.rmsnorm(x, gain.to(DEV), eps, out, rows, pending=(ws, bias.to(DEV)))
+    _close(out, want_h[[5, 0, 5]], "float32")
+    assert torch.equal(x.cpu(), x0)
+    # all rows: normalised output and the stream updated
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops.rmsnorm(x, gain.to(DEV), eps, out, None, pending=(ws, bias.to(DEV)))
+    _close(out, want_h, "bfloat16")
+    _close(x, want_x, "float32")
+    # and the plain way of adding them
+    x2 = x0.clone().to(DEV)
+    ops.add_pending(x2, ws, bias.to(DEV))
+    assert torch.equal(x2, x)
