@@ -32,6 +32,8 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, long long ld, con
                                           T* __restrict__ k_pages, T* __restrict__ v_pages, int n_pages,
                                           int n_tokens, int heads, int kv_heads, int hd, int write_kv,
                                           int* __restrict__ status) {
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int slots = heads + (write_kv ? 2 * kv_heads : 0);
   const long long idx = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -101,6 +103,8 @@ paged_attention_kernel(const T* __restrict__ q, long long ldq, const T* __restri
                        int page_size, int n_pages, const int* __restrict__ tok_req,
                        const int* __restrict__ tok_pos, T* __restrict__ out, long long ldo, int n_tokens,
                        int heads, int kv_heads, int hd, float scale, int window, int* __restrict__ status) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float qs[4][HD_MAX];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long idx = (long long)blockIdx.x * 4 + warp;
@@ -164,7 +168,7 @@ int launch_attention(const void* q, long long ldq, const void* k_pages, const vo
   const long long warps = (long long)n_tokens * heads;
   const int blocks = gb_div_up(warps, 4);
 #define GB_ATTN(HD)                                                                                              \
-  paged_attention_kernel<T, HD><<<blocks, 128, 0, stream>>>((const T*)q, ldq, (const T*)k_pages, (const T*)v_pages, \
+  gb_launch(paged_attention_kernel<T, HD>, dim3(blocks), dim3(128), 0, stream, (const T*)q, ldq, (const T*)k_pages, (const T*)v_pages, \
                                                             block_table, bt_stride, page_size, n_pages, tok_req, \
                                                             tok_pos, (T*)out, ldo, n_tokens, heads, kv_heads, hd, \
                                                             scale, window, status)
@@ -193,13 +197,11 @@ GB_API int gb_qk_norm_rope_store(void* qkv, int dtype, long long ld, const float
   const long long warps = (long long)n_tokens * slots;
   const int blocks = gb_div_up(warps, 4);
   if (dtype == GB_F32)
-    qk_norm_rope_store_kernel<float><<<blocks, 128, 0, stream>>>(
-        (float*)qkv, ld, q_gain, k_gain, eps, inv_freq, rotary_dim, adjacent, tok_req, tok_pos, block_table,
+    gb_launch(qk_norm_rope_store_kernel<float>, dim3(blocks), dim3(128), 0, stream, (float*)qkv, ld, q_gain, k_gain, eps, inv_freq, rotary_dim, adjacent, tok_req, tok_pos, block_table,
         bt_stride, page_size, (float*)k_pages, (float*)v_pages, n_pages, n_tokens, heads, kv_heads, hd, write_kv,
         status);
   else if (dtype == GB_BF16)
-    qk_norm_rope_store_kernel<bf16><<<blocks, 128, 0, stream>>>(
-        (bf16*)qkv, ld, q_gain, k_gain, eps, inv_freq, rotary_dim, adjacent, tok_req, tok_pos, block_table,
+    gb_launch(qk_norm_rope_store_kernel<bf16>, dim3(blocks), dim3(128), 0, stream, (bf16*)qkv, ld, q_gain, k_gain, eps, inv_freq, rotary_dim, adjacent, tok_req, tok_pos, block_table,
         bt_stride, page_size, (bf16*)k_pages, (bf16*)v_pages, n_pages, n_tokens, heads, kv_heads, hd, write_kv,
         status);
   else

@@ -81,6 +81,8 @@ template <int HD> struct Tile {
 template <int HD, int NW>
 __global__ void __launch_bounds__(32 * NW)
 attention_tc_kernel(const AttnParams p) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int BQ = 16 * NW;
   constexpr int STRIDE = Tile<HD>::STRIDE, CHUNKS = Tile<HD>::CHUNKS;
   constexpr int NT = 32 * NW;
@@ -286,6 +288,8 @@ attention_tc_kernel(const AttnParams p) {
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        bf16* __restrict__ out, long long ldo, int n_tokens, int heads, int hd,
                                        int splits) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;                         // token * heads + head
   const size_t rows = (size_t)n_tokens * heads;
   float M = -INFINITY;
@@ -316,7 +320,7 @@ int launch(const AttnParams& p, int n_tiles, cudaStream_t stream) {
     attr_set = true;
   }
   dim3 grid(n_tiles, p.kv_heads, p.splits);
-  attention_tc_kernel<HD, NW><<<grid, 32 * NW, smem, stream>>>(p);
+  gb_launch(attention_tc_kernel<HD, NW>, dim3(grid), dim3(32 * NW), smem, stream, p);
   return GB_OK;
 }
 
@@ -387,8 +391,7 @@ GB_API int gb_attention_tc(const void* q, long long ldq, const void* k_pages, co
   if (rc != GB_OK) return rc;
   GB_CHECK_LAUNCH("gb_attention_tc");
   if (splits > 1) {
-    attention_merge_kernel<<<n_tokens * heads, hd <= 64 ? 64 : 128, 0, stream>>>(
-        p.part_o, p.part_ml, (bf16*)out, ldo, n_tokens, heads, hd, splits);
+    gb_launch(attention_merge_kernel, dim3(n_tokens * heads), dim3(hd <= 64 ? 64 : 128), 0, stream, p.part_o, p.part_ml, (bf16*)out, ldo, n_tokens, heads, hd, splits);
     GB_CHECK_LAUNCH("gb_attention_tc (merge)");
     return 2;
   }

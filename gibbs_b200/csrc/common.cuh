@@ -78,3 +78,35 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 static inline int gb_div_up(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+// ---------------------------------------------------------------- launches
+// Programmatic dependent launch: a kernel launched through gb_launch may begin
+// (become resident, run its prologue) while the kernel before it on the stream
+// is still running.  Every kernel of this library therefore
+//   - calls pdl_trigger() first, which lets the kernel after it start early, and
+//   - calls pdl_wait() before it reads or writes anything an earlier kernel may
+//     still touch (activations, caches, state; weights and launch arguments are
+//     safe).  pdl_wait() returns when the earlier kernels have completed and
+//     their writes are visible.
+// Outside such a launch both are no-ops.  GIBBS_B200_PDL=0 turns the launch
+// attribute off (kernels then run strictly one after the other).
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+int gb_pdl_enabled();  // defined in errors.cu (one copy per shared library)
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t gb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = gb_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

@@ -26,6 +26,8 @@ __global__ void short_conv_out_kernel(const T* __restrict__ bcx, long long ld, c
                                       long long slot_stride, const int* __restrict__ slot_ids,
                                       const int* __restrict__ tok_req, const int* __restrict__ q_start,
                                       T* __restrict__ out, int n_tokens, int hidden, int K) {
+  pdl_trigger();
+  pdl_wait();
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= (long long)n_tokens * hidden) return;
   const int t = (int)(gid / hidden), c = (int)(gid - (long long)t * hidden);
@@ -54,6 +56,8 @@ __global__ void short_conv_state_kernel(const T* __restrict__ bcx, long long ld,
                                         long long slot_stride, const int* __restrict__ slot_ids,
                                         const int* __restrict__ q_start, const int* __restrict__ q_len,
                                         int n_requests, int hidden, int K) {
+  pdl_trigger();
+  pdl_wait();
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= (long long)n_requests * hidden) return;
   const int r = (int)(gid / hidden), c = (int)(gid - (long long)r * hidden);
@@ -83,6 +87,8 @@ __global__ void short_conv_decode_kernel(const T* __restrict__ bcx, long long ld
                                          long long slot_stride, const int* __restrict__ slot_ids,
                                          const int* __restrict__ q_start, T* __restrict__ out, int n_requests,
                                          int hidden, int K) {
+  pdl_trigger();
+  pdl_wait();
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= (long long)n_requests * hidden) return;
   const int r = (int)(gid / hidden), c = (int)(gid - (long long)r * hidden);
@@ -118,11 +124,9 @@ GB_API int gb_short_conv(const void* bcx, int dtype, long long ld, const float* 
   if (max_q_len == 1 && n_tokens == n_requests) {           // one token per request
     const long long total = (long long)n_requests * hidden;
     if (dtype == GB_F32)
-      short_conv_decode_kernel<float><<<gb_div_up(total, threads), threads, 0, stream>>>(
-          (const float*)bcx, ld, taps, bias, state, slot_stride, slot_ids, q_start, (float*)out, n_requests, hidden, K);
+      gb_launch(short_conv_decode_kernel<float>, dim3(gb_div_up(total, threads)), dim3(threads), 0, stream, (const float*)bcx, ld, taps, bias, state, slot_stride, slot_ids, q_start, (float*)out, n_requests, hidden, K);
     else if (dtype == GB_BF16)
-      short_conv_decode_kernel<bf16><<<gb_div_up(total, threads), threads, 0, stream>>>(
-          (const bf16*)bcx, ld, taps, bias, state, slot_stride, slot_ids, q_start, (bf16*)out, n_requests, hidden, K);
+      gb_launch(short_conv_decode_kernel<bf16>, dim3(gb_div_up(total, threads)), dim3(threads), 0, stream, (const bf16*)bcx, ld, taps, bias, state, slot_stride, slot_ids, q_start, (bf16*)out, n_requests, hidden, K);
     else
       GB_FAIL(GB_ERR_ARG, "gb_short_conv: unknown dtype %d", dtype);
     GB_CHECK_LAUNCH("gb_short_conv (decode)");
@@ -131,17 +135,13 @@ GB_API int gb_short_conv(const void* bcx, int dtype, long long ld, const float* 
   const long long total = (long long)n_tokens * hidden;
   const long long total_s = (long long)n_requests * hidden;
   if (dtype == GB_F32) {
-    short_conv_out_kernel<float><<<gb_div_up(total, threads), threads, 0, stream>>>(
-        (const float*)bcx, ld, taps, bias, state, slot_stride, slot_ids, tok_req, q_start, (float*)out, n_tokens,
+    gb_launch(short_conv_out_kernel<float>, dim3(gb_div_up(total, threads)), dim3(threads), 0, stream, (const float*)bcx, ld, taps, bias, state, slot_stride, slot_ids, tok_req, q_start, (float*)out, n_tokens,
         hidden, K);
-    short_conv_state_kernel<float><<<gb_div_up(total_s, threads), threads, 0, stream>>>(
-        (const float*)bcx, ld, state, slot_stride, slot_ids, q_start, q_len, n_requests, hidden, K);
+    gb_launch(short_conv_state_kernel<float>, dim3(gb_div_up(total_s, threads)), dim3(threads), 0, stream, (const float*)bcx, ld, state, slot_stride, slot_ids, q_start, q_len, n_requests, hidden, K);
   } else if (dtype == GB_BF16) {
-    short_conv_out_kernel<bf16><<<gb_div_up(total, threads), threads, 0, stream>>>(
-        (const bf16*)bcx, ld, taps, bias, state, slot_stride, slot_ids, tok_req, q_start, (bf16*)out, n_tokens,
+    gb_launch(short_conv_out_kernel<bf16>, dim3(gb_div_up(total, threads)), dim3(threads), 0, stream, (const bf16*)bcx, ld, taps, bias, state, slot_stride, slot_ids, tok_req, q_start, (bf16*)out, n_tokens,
         hidden, K);
-    short_conv_state_kernel<bf16><<<gb_div_up(total_s, threads), threads, 0, stream>>>(
-        (const bf16*)bcx, ld, state, slot_stride, slot_ids, q_start, q_len, n_requests, hidden, K);
+    gb_launch(short_conv_state_kernel<bf16>, dim3(gb_div_up(total_s, threads)), dim3(threads), 0, stream, (const bf16*)bcx, ld, state, slot_stride, slot_ids, q_start, q_len, n_requests, hidden, K);
   } else {
     GB_FAIL(GB_ERR_ARG, "gb_short_conv: unknown dtype %d", dtype);
   }

@@ -10,6 +10,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
                              int dim, int vocab) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   int id = ids[row];
   // Token ids are checked on the host before the step; a bad id reads row 0.
@@ -24,9 +26,9 @@ GB_API int gb_embed(const void* table, int table_dtype, const int* ids, float* o
   if (n <= 0) return GB_OK;
   const int threads = dim >= 1024 ? 256 : 128;
   if (table_dtype == GB_F32)
-    embed_kernel<float><<<n, threads, 0, stream>>>((const float*)table, ids, out, dim, vocab);
+    gb_launch(embed_kernel<float>, dim3(n), dim3(threads), 0, stream, (const float*)table, ids, out, dim, vocab);
   else if (table_dtype == GB_BF16)
-    embed_kernel<bf16><<<n, threads, 0, stream>>>((const bf16*)table, ids, out, dim, vocab);
+    gb_launch(embed_kernel<bf16>, dim3(n), dim3(threads), 0, stream, (const bf16*)table, ids, out, dim, vocab);
   else
     GB_FAIL(GB_ERR_ARG, "gb_embed: unknown table dtype %d", table_dtype);
   GB_CHECK_LAUNCH("gb_embed");
@@ -43,16 +45,82 @@ GB_API int gb_embed(const void* table, int table_dtype, const int* ids, float* o
 // before the statistics; without a row gather the sum is also written back to x
 // (the residual stream carries on from it).
 template <typename TOut>
+__device__ __forceinline__ void store4(TOut* dst, float4 v);
+template <>
+__device__ __forceinline__ void store4<float>(float* dst, float4 v) { *reinterpret_cast<float4*>(dst) = v; }
+template <>
+__device__ __forceinline__ void store4<bf16>(bf16* dst, float4 v) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<uint32_t*>(&lo);
+  u.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = u;
+}
+
+// VEC > 0: dim is a multiple of 4, rows are 16-byte aligned and each thread keeps its
+// VEC float4 of the row in registers (all loads of the row and of the partial sums are
+// issued together; the row is read once).  VEC == 0: any dim, two passes.
+template <typename TOut, int VEC>
 __global__ void rmsnorm_kernel(float* __restrict__ x, long long ldx, const float* __restrict__ gain,
                                TOut* __restrict__ out, const int* __restrict__ rows, int dim, float eps,
                                const float* __restrict__ pend, int splits, long long n_src_rows,
                                const float* __restrict__ pend_bias) {
   __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const long long sr = rows ? rows[r] : r;
   float* src = x + (size_t)sr * ldx;
   const bool write_back = pend != nullptr && rows == nullptr;
+  TOut* dst = out + (size_t)r * dim;
   float ss = 0.f;
+  if (VEC > 0) {
+    float4 v[VEC > 0 ? VEC : 1];
+    const int n4 = dim >> 2;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      v[i] = c < n4 ? reinterpret_cast<const float4*>(src)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (pend) {
+      for (int s = 0; s < splits; ++s) {
+        const float4* ps = reinterpret_cast<const float4*>(pend + ((size_t)s * n_src_rows + sr) * dim);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          const int c = threadIdx.x + i * blockDim.x;
+          if (c < n4) {
+            const float4 a = __ldcg(ps + c);
+            v[i].x += a.x; v[i].y += a.y; v[i].z += a.z; v[i].w += a.w;
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < n4) {
+          if (pend_bias) {
+            const float4 b = reinterpret_cast<const float4*>(pend_bias)[c];
+            v[i].x += b.x; v[i].y += b.y; v[i].z += b.z; v[i].w += b.w;
+          }
+          if (write_back) reinterpret_cast<float4*>(src)[c] = v[i];
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)dim + eps);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < n4) {
+        const float4 g = reinterpret_cast<const float4*>(gain)[c];
+        store4<TOut>(dst + 4 * c, make_float4(v[i].x * scale * g.x, v[i].y * scale * g.y, v[i].z * scale * g.z,
+                                              v[i].w * scale * g.w));
+      }
+    }
+    return;
+  }
   for (int d = threadIdx.x; d < dim; d += blockDim.x) {
     float v = src[d];
     if (pend) {
@@ -64,7 +132,6 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, long long ldx, const float
   }
   ss = block_sum(ss, scratch);
   const float scale = 1.0f / sqrtf(ss / (float)dim + eps);
-  TOut* dst = out + (size_t)r * dim;
   for (int d = threadIdx.x; d < dim; d += blockDim.x) {
     float v = src[d];                       // each thread re-reads what it wrote itself
     if (pend && !write_back) {
@@ -75,18 +142,41 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, long long ldx, const float
   }
 }
 
+template <typename TOut>
+void launch_rmsnorm(float* x, long long ldx, const float* gain, TOut* out, const int* rows, int n_rows, int dim,
+                    float eps, const float* pend, int splits, long long n_src_rows, const float* pend_bias,
+                    cudaStream_t stream) {
+  const bool vec_ok = dim % 4 == 0 && ldx % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)gain & 15) == 0 &&
+                      ((uintptr_t)out & 15) == 0 && ((uintptr_t)pend & 15) == 0 && ((uintptr_t)pend_bias & 15) == 0;
+  const int n4 = dim / 4;
+  if (vec_ok && n4 <= 2 * 1024) {
+    int threads = 32;
+    while (threads < 1024 && threads < n4) threads <<= 1;
+    if (threads > 256 && n4 <= 2 * 256) threads = 256;
+    if (n4 <= threads)
+      gb_launch(rmsnorm_kernel<TOut, 1>, dim3(n_rows), dim3(threads), 0, stream, x, ldx, gain, out, rows, dim, eps,
+                pend, splits, n_src_rows, pend_bias);
+    else
+      gb_launch(rmsnorm_kernel<TOut, 2>, dim3(n_rows), dim3(threads), 0, stream, x, ldx, gain, out, rows, dim, eps,
+                pend, splits, n_src_rows, pend_bias);
+    return;
+  }
+  int threads = 32;
+  while (threads < 512 && threads * 4 < dim) threads <<= 1;
+  gb_launch(rmsnorm_kernel<TOut, 0>, dim3(n_rows), dim3(threads), 0, stream, x, ldx, gain, out, rows, dim, eps, pend,
+            splits, n_src_rows, pend_bias);
+}
+
 GB_API int gb_rmsnorm(float* x, long long ldx, const float* gain, void* out, int out_dtype, const int* rows,
                       int n_rows, int dim, float eps, const float* pend, int splits, long long n_src_rows,
                       const float* pend_bias, cudaStream_t stream) {
   if (n_rows <= 0) return GB_OK;
-  int threads = 32;
-  while (threads < 512 && threads * 4 < dim) threads <<= 1;
   if (out_dtype == GB_F32)
-    rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, ldx, gain, (float*)out, rows, dim, eps, pend, splits,
-                                                          n_src_rows, pend_bias);
+    launch_rmsnorm<float>(x, ldx, gain, (float*)out, rows, n_rows, dim, eps, pend, splits, n_src_rows, pend_bias,
+                          stream);
   else if (out_dtype == GB_BF16)
-    rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, ldx, gain, (bf16*)out, rows, dim, eps, pend, splits,
-                                                         n_src_rows, pend_bias);
+    launch_rmsnorm<bf16>(x, ldx, gain, (bf16*)out, rows, n_rows, dim, eps, pend, splits, n_src_rows, pend_bias,
+                         stream);
   else
     GB_FAIL(GB_ERR_ARG, "gb_rmsnorm: unknown output dtype %d", out_dtype);
   GB_CHECK_LAUNCH("gb_rmsnorm");
@@ -96,6 +186,8 @@ GB_API int gb_rmsnorm(float* x, long long ldx, const float* gain, void* out, int
 // x[m, :] += sum over splits of pend[s][m, :] (+ bias), in split order.
 __global__ void add_pending_kernel(float* __restrict__ x, long long ldx, const float* __restrict__ pend, int splits,
                                    const float* __restrict__ bias, long long n_rows, int dim) {
+  pdl_trigger();
+  pdl_wait();
   const long long total = n_rows * dim;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -113,7 +205,7 @@ GB_API int gb_add_pending(float* x, long long ldx, const float* pend, int splits
   const long long total = n_rows * dim;
   if (total <= 0 || splits <= 0) return GB_OK;
   const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-  add_pending_kernel<<<blocks, 256, 0, stream>>>(x, ldx, pend, splits, bias, n_rows, dim);
+  gb_launch(add_pending_kernel, dim3(blocks), dim3(256), 0, stream, x, ldx, pend, splits, bias, n_rows, dim);
   GB_CHECK_LAUNCH("gb_add_pending");
   return GB_OK;
 }
@@ -122,6 +214,8 @@ GB_API int gb_add_pending(float* x, long long ldx, const float* pend, int splits
 // in: [n, 2*inner] rows of [gate | up]; out: [n, inner].
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int inner) {
+  pdl_trigger();
+  pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     const long long row = i / inner;
@@ -139,9 +233,9 @@ GB_API int gb_swiglu(const void* gu, void* out, int dtype, int n, int inner, cud
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == GB_F32)
-    swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, total, inner);
+    gb_launch(swiglu_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)gu, (float*)out, total, inner);
   else if (dtype == GB_BF16)
-    swiglu_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, total, inner);
+    gb_launch(swiglu_kernel<bf16>, dim3(blocks), dim3(threads), 0, stream, (const bf16*)gu, (bf16*)out, total, inner);
   else
     GB_FAIL(GB_ERR_ARG, "gb_swiglu: unknown dtype %d", dtype);
   GB_CHECK_LAUNCH("gb_swiglu");
@@ -151,6 +245,8 @@ GB_API int gb_swiglu(const void* gu, void* out, int dtype, int n, int inner, cud
 // ---------------------------------------------------------------- cast
 template <typename TIn, typename TOut>
 __global__ void cast_kernel(const TIn* __restrict__ in, TOut* __restrict__ out, long long total) {
+  pdl_trigger();
+  pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x)
     out[i] = from_f32<TOut>(to_f32(in[i]));
@@ -161,9 +257,9 @@ GB_API int gb_cast(const void* in, int in_dtype, void* out, int out_dtype, long 
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (in_dtype == GB_F32 && out_dtype == GB_BF16)
-    cast_kernel<float, bf16><<<blocks, threads, 0, stream>>>((const float*)in, (bf16*)out, total);
+    gb_launch(cast_kernel<float, bf16>, dim3(blocks), dim3(threads), 0, stream, (const float*)in, (bf16*)out, total);
   else if (in_dtype == GB_BF16 && out_dtype == GB_F32)
-    cast_kernel<bf16, float><<<blocks, threads, 0, stream>>>((const bf16*)in, (float*)out, total);
+    gb_launch(cast_kernel<bf16, float>, dim3(blocks), dim3(threads), 0, stream, (const bf16*)in, (float*)out, total);
   else
     GB_FAIL(GB_ERR_ARG, "gb_cast: unsupported conversion %d -> %d", in_dtype, out_dtype);
   GB_CHECK_LAUNCH("gb_cast");

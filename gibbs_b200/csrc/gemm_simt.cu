@@ -18,6 +18,8 @@ __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict__ W, long long ldw,
                  const float* __restrict__ bias, void* __restrict__ out, long long ldo, int out_dtype,
                  int accumulate, int M, int N, int K) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int BM = 16 * TM;
   __shared__ float As[BK][BM + 1];
   __shared__ float Ws[BK][BN + 1];
@@ -84,11 +86,11 @@ void launch(const void* A, long long lda, const void* W, long long ldw, const fl
             int out_dtype, int accumulate, int M, int N, int K, cudaStream_t stream) {
   if (M <= 16) {
     dim3 grid(gb_div_up(N, BN), gb_div_up(M, 16));
-    gemm_simt_kernel<TA, TW, 1><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, ldw, bias, out, ldo,
+    gb_launch(gemm_simt_kernel<TA, TW, 1>, dim3(grid), dim3(256), 0, stream, (const TA*)A, lda, (const TW*)W, ldw, bias, out, ldo,
                                                           out_dtype, accumulate, M, N, K);
   } else {
     dim3 grid(gb_div_up(N, BN), gb_div_up(M, 64));
-    gemm_simt_kernel<TA, TW, 4><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, ldw, bias, out, ldo,
+    gb_launch(gemm_simt_kernel<TA, TW, 4>, dim3(grid), dim3(256), 0, stream, (const TA*)A, lda, (const TW*)W, ldw, bias, out, ldo,
                                                           out_dtype, accumulate, M, N, K);
   }
 }

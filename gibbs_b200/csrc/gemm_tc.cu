@@ -92,6 +92,7 @@ template <int BN>
 __global__ void __launch_bounds__(192)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                const GemmParams p) {
+  pdl_trigger();   // the kernel after this one may start its prologue now
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t full_bar[C::STAGES], empty_bar[C::STAGES], tmem_full_bar;
@@ -133,7 +134,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     if (elect_one()) {
       uint64_t policy = 0;
       if (p.stream_weights) asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
-      for (int i = 0; i < nkb; ++i) {
+      auto load_w = [&](int i, int s) {
+        uint8_t* st = tiles + (size_t)s * C::STAGE_BYTES;
+        mbar_arrive_expect_tx(&full_bar[s], C::STAGE_BYTES);
+        if (p.stream_weights)
+          tma_load_2d_hint(st, &tmap_w, (kb_begin + i) * BK, n0, &full_bar[s], policy);
+        else
+          tma_load_2d(st, &tmap_w, (kb_begin + i) * BK, n0, &full_bar[s]);
+      };
+      auto load_x = [&](int i, int s) {
+        uint8_t* st = tiles + (size_t)s * C::STAGE_BYTES;
+        tma_load_2d(st + W_TILE_BYTES, &tmap_x, (kb_begin + i) * BK, m0, &full_bar[s]);
+      };
+      // The weights do not depend on the kernels before this one: their first tiles are
+      // requested at once.  The activations are read only after those kernels have finished.
+      const int head = nkb < C::STAGES ? nkb : C::STAGES;
+      for (int i = 0; i < head; ++i) load_w(i, i);
+      pdl_wait();
+      for (int i = 0; i < head; ++i) load_x(i, i);
+      for (int i = head; i < nkb; ++i) {
         const int s = i % C::STAGES;
         const uint32_t ph = (i / C::STAGES) & 1;
         if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
@@ -142,13 +161,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
           break;
         }
         if (abort_flag) break;
-        uint8_t* st = tiles + (size_t)s * C::STAGE_BYTES;
-        mbar_arrive_expect_tx(&full_bar[s], C::STAGE_BYTES);
-        if (p.stream_weights)
-          tma_load_2d_hint(st, &tmap_w, (kb_begin + i) * BK, n0, &full_bar[s], policy);
-        else
-          tma_load_2d(st, &tmap_w, (kb_begin + i) * BK, n0, &full_bar[s]);
-        tma_load_2d(st + W_TILE_BYTES, &tmap_x, (kb_begin + i) * BK, m0, &full_bar[s]);
+        load_w(i, s);
+        load_x(i, s);
       }
     }
     __syncwarp();
@@ -192,6 +206,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         if (bytes) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.prefetch + off), "r"(bytes));
       }
     }
+    pdl_wait();    // outputs (and the workspace) may still be read by the kernels before this one
     const bool ok = mbar_wait(&tmem_full_bar, 0);
     if (!ok) {
       abort_flag = 1;
@@ -271,6 +286,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 // out = epilogue(sum over splits of the partial tiles (+ bias)), in split order.
 __global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, const float* __restrict__ bias,
                                      void* __restrict__ out, long long ldo, int mode, int M, int N) {
+  pdl_trigger();
+  pdl_wait();
   const long long total = (long long)M * N;
   const int n_out = mode == OUT_SWIGLU ? N / 2 : N;
   const long long work = (long long)M * n_out;
@@ -377,7 +394,7 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cu
     attr_set = true;
   }
   dim3 grid(gb_div_up(p.N, BM), gb_div_up(p.M, BN), p.splits);
-  gemm_tc_kernel<BN><<<grid, 192, Cfg<BN>::SMEM_BYTES, stream>>>(tw, tx, p);
+  gb_launch(gemm_tc_kernel<BN>, dim3(grid), dim3(192), Cfg<BN>::SMEM_BYTES, stream, tw, tx, p);
   return GB_OK;
 }
 
@@ -465,7 +482,7 @@ GB_API int gb_linear_tc(const void* X, long long ldx, const void* W, long long l
   if (splits > 1 && !defer) {
     const long long work = (long long)M * (mode == OUT_SWIGLU ? N / 2 : N);
     const int blocks = (int)((work + 255) / 256 < 148 * 8 ? (work + 255) / 256 : 148 * 8);
-    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(workspace, splits, bias, out, ldo, mode, M, N);
+    gb_launch(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, workspace, splits, bias, out, ldo, mode, M, N);
     GB_CHECK_LAUNCH("gb_linear_tc (split-K reduce)");
     return 2;
   }

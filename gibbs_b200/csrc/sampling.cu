@@ -51,6 +51,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, long long ldv, i
                               const float* __restrict__ temperature, const int* __restrict__ top_k,
                               const float* __restrict__ top_p, const unsigned long long* __restrict__ seed,
                               const long long* __restrict__ counter, int* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ Cand warp_c[32];
   __shared__ Cand picked[MAX_K];
   __shared__ Cand prev;
@@ -146,7 +148,7 @@ GB_API int gb_sample(const float* logits, long long ldv, int rows, int vocab, co
   if (vocab <= 0) GB_FAIL(GB_ERR_ARG, "gb_sample: vocabulary of %d", vocab);
   int threads = 64;
   while (threads < 1024 && threads * 8 < vocab) threads <<= 1;
-  sample_kernel<<<rows, threads, 0, stream>>>(logits, ldv, vocab, temperature, top_k, top_p, seed, counter, out);
+  gb_launch(sample_kernel, dim3(rows), dim3(threads), 0, stream, logits, ldv, vocab, temperature, top_k, top_p, seed, counter, out);
   GB_CHECK_LAUNCH("gb_sample");
   return GB_OK;
 }

@@ -59,6 +59,109 @@ def _align4(n: int) -> int:
     return (n + 3) & ~3
 
 
+class StepBuilder:
+    """Packs a step's metadata (token ids, token->request, positions, per-request
+    starts and lengths, slots, wanted rows, block tables) into ONE pinned host
+    buffer, copies it to the device with one transfer and hands out the views
+    (``StepState`` and the cache views) the parts read.  The engine owns one;
+    tests build steps for a bare cache manager with it."""
+
+    def __init__(self, cache: CacheManager, device, max_requests: int, max_step_tokens: int, status=None):
+        self.cache, self.device = cache, torch.device(device)
+        self.max_requests, self.max_step_tokens = int(max_requests), int(max_step_tokens)
+        n_groups = len(cache.groups)
+        cap = 4 * _align4(self.max_step_tokens) + 5 * _align4(self.max_requests) \
+            + n_groups * self.max_requests * cache.max_blocks + 16
+        self._staging = [torch.empty(cap, dtype=torch.int32).pin_memory() for _ in range(4)]
+        self._staging_np = [t.numpy() for t in self._staging]
+        self._staging_evt = [None] * 4
+        self._turn = 0
+        self.dev_meta = torch.empty(cap, dtype=torch.int32, device=self.device)
+        self.status = status if status is not None else ops.device_status(self.device)
+        self.max_context = cache.max_context
+
+    def build(self, entries, rcs):
+        """(StepState, cache views) for entries (StepEntry) of live requests
+        ``rcs``, through the builder's own device buffer."""
+        n_tok = sum(len(e.tokens) for e in entries)
+        n_req, n_want = len(entries), sum(len(e.want) for e in entries)
+        offs, total = self._layout(n_tok, n_req, n_want)
+        turn = self._fill_staging(entries, rcs, offs, n_tok, n_req, n_want)
+        self.dev_meta[:total].copy_(self._staging[turn][:total], non_blocking=True)
+        self._record(turn)
+        return self._state(self.dev_meta, offs, entries, rcs, n_tok, n_req, n_want)
+
+    def _layout(self, n_tok: int, n_req: int, n_want: int):
+        """Offsets (in int32) of the sections of the metadata buffer, each
+        16-byte aligned: token ids, token->request, token->position; per
+        request first row, count, length before, length after, slot; wanted
+        rows; one block table per group."""
+        n_groups, mb = len(self.cache.groups), self.cache.max_blocks
+        sizes = [n_tok, n_tok, n_tok, n_req, n_req, n_req, n_req, n_req, max(n_want, 1), n_groups * n_req * mb]
+        offs, o = [], 0
+        for sz in sizes:
+            offs.append(o)
+            o += _align4(sz)
+        return offs, o
+
+    def _fill_staging(self, entries, rcs, offs, n_tok, n_req, n_want) -> int:
+        turn = self._turn
+        self._turn = (turn + 1) % len(self._staging)
+        if self._staging_evt[turn] is not None:
+            self._staging_evt[turn].synchronize()
+        buf = self._staging_np[turn]
+        ids, treq, tpos = (buf[offs[i]:offs[i] + n_tok] for i in range(3))
+        qs, ql, sp, cl, sl = (buf[offs[i]:offs[i] + n_req] for i in range(3, 8))
+        wr = buf[offs[8]:offs[8] + max(n_want, 1)]
+        row, w_i = 0, 0
+        for r, (e, rc) in enumerate(zip(entries, rcs)):
+            n = len(e.tokens)
+            ids[row:row + n] = e.tokens
+            treq[row:row + n] = r
+            tpos[row:row + n] = np.arange(rc.length, rc.length + n, dtype=np.int32)
+            qs[r], ql[r], sp[r], cl[r] = row, n, rc.length, rc.length + n
+            sl[r] = rc.slot if rc.slot is not None else -1
+            for w in e.want:
+                wr[w_i] = row + int(w)
+                w_i += 1
+            row += n
+        n_groups, mb = len(self.cache.groups), self.cache.max_blocks
+        if n_groups:
+            bt = buf[offs[9]:offs[9] + n_groups * n_req * mb].reshape(n_groups, n_req, mb)
+            self.cache.fill_block_tables(rcs, bt)
+        return turn
+
+    def _record(self, turn: int) -> None:
+        evt = torch.cuda.Event()
+        evt.record()
+        self._staging_evt[turn] = evt
+
+    def _state(self, dev, offs, entries, rcs, n_tok, n_req, n_want, fixed: bool = False):
+        """The step's state and cache views over the device metadata buffer
+        ``dev``.  ``fixed`` (graph capture): launch-sizing hints that do not
+        depend on the requests' current lengths."""
+        n_groups, mb = len(self.cache.groups), self.cache.max_blocks
+
+        def view(i, n):
+            return dev[offs[i]:offs[i] + n]
+
+        step = StepState(
+            n_tokens=n_tok, n_requests=n_req, n_want=n_want,
+            token_ids=view(0, n_tok), tok_req=view(1, n_tok), tok_pos=view(2, n_tok),
+            q_start=view(3, n_req), q_len=view(4, n_req), start_pos=view(5, n_req), ctx_len=view(6, n_req),
+            want_rows=view(8, n_want), status=self.status,
+            max_q_len=max(len(e.tokens) for e in entries),
+            max_ctx_len=self.max_context if fixed else max(rc.length + len(e.tokens) for e, rc in zip(entries, rcs)),
+            host_q_start=[] if fixed else [int(v) for v in np.cumsum([0] + [len(e.tokens) for e in entries[:-1]])],
+            host_q_len=[] if fixed else [len(e.tokens) for e in entries],
+            host_start_pos=[] if fixed else [rc.length for rc in rcs],
+        )
+        tables = [dev[offs[9] + g * n_req * mb: offs[9] + (g + 1) * n_req * mb].view(n_req, mb)
+                  for g in range(n_groups)]
+        caches = self.cache.views(tables, view(7, n_req), [] if fixed else [rc.slot for rc in rcs])
+        return step, caches
+
+
 class Engine:
     """A model, its cache and the step function over them."""
 
@@ -74,16 +177,8 @@ class Engine:
         self.cache = CacheManager(model.entry_needs(), n_pages, page_size, self.max_requests, model.rt.dtype,
                                   self.device, self.max_context)
         self.vocab_size = model.vocab_size
-        n_groups = len(self.cache.groups)
-        cap = 3 * _align4(self.max_step_tokens) + 5 * _align4(self.max_requests) + _align4(self.max_step_tokens) \
-            + n_groups * self.max_requests * self.cache.max_blocks + 16
-        self._cap = cap
-        self._staging = [torch.empty(cap, dtype=torch.int32).pin_memory() for _ in range(4)]
-        self._staging_np = [s.numpy() for s in self._staging]
-        self._staging_evt = [None] * 4
-        self._turn = 0
-        self._dev_meta = torch.empty(cap, dtype=torch.int32, device=self.device)
         self.status = ops.device_status(self.device)
+        self.builder = StepBuilder(self.cache, self.device, self.max_requests, self.max_step_tokens, self.status)
         self.steps_run = 0
         # decode steps are replayed from CUDA graphs, one per batch size, unless a part of the
         # model cannot be captured (it reads host-side step data)
@@ -170,22 +265,23 @@ class Engine:
 
         n_req = len(entries)
         n_want = sum(len(e.want) for e in entries)
-        offs, total = self._layout(n_tok, n_req, n_want)
-        turn = self._fill_staging(entries, rcs, offs, n_tok, n_req, n_want)
+        bld = self.builder
+        offs, total = bld._layout(n_tok, n_req, n_want)
+        turn = bld._fill_staging(entries, rcs, offs, n_tok, n_req, n_want)
         decode = self.use_graphs and n_tok == n_req and n_want == n_req
 
         if decode and n_req in self._graphs:
             g = self._graphs[n_req]
-            g["meta"][:total].copy_(self._staging[turn][:total], non_blocking=True)
-            self._record(turn)
+            g["meta"][:total].copy_(bld._staging[turn][:total], non_blocking=True)
+            bld._record(turn)
             g["graph"].replay()
             ops._launched(g["launches"])
             logits = g["logits"]
         else:
-            dev = self._graph_meta(n_req, total) if decode else self._dev_meta
-            dev[:total].copy_(self._staging[turn][:total], non_blocking=True)
-            self._record(turn)
-            step, caches = self._state(dev, offs, entries, rcs, n_tok, n_req, n_want, fixed=decode)
+            dev = self._graph_meta(n_req, total) if decode else bld.dev_meta
+            dev[:total].copy_(bld._staging[turn][:total], non_blocking=True)
+            bld._record(turn)
+            step, caches = bld._state(dev, offs, entries, rcs, n_tok, n_req, n_want, fixed=decode)
             before = ops.launch_count()
             logits = self.model.forward(step, caches)
             if decode:
@@ -195,77 +291,6 @@ class Engine:
             self.cache.advance(rc, rc.length + len(e.tokens))
         self.steps_run += 1
         return logits
-
-    # -- pieces of a step --------------------------------------------------------
-    def _layout(self, n_tok: int, n_req: int, n_want: int):
-        """Offsets (in int32) of the sections of the metadata buffer, each
-        16-byte aligned: token ids, token->request, token->position; per
-        request first row, count, length before, length after, slot; wanted
-        rows; one block table per group."""
-        n_groups, mb = len(self.cache.groups), self.cache.max_blocks
-        sizes = [n_tok, n_tok, n_tok, n_req, n_req, n_req, n_req, n_req, max(n_want, 1), n_groups * n_req * mb]
-        offs, o = [], 0
-        for sz in sizes:
-            offs.append(o)
-            o += _align4(sz)
-        return offs, o
-
-    def _fill_staging(self, entries, rcs, offs, n_tok, n_req, n_want) -> int:
-        turn = self._turn
-        self._turn = (turn + 1) % len(self._staging)
-        if self._staging_evt[turn] is not None:
-            self._staging_evt[turn].synchronize()
-        buf = self._staging_np[turn]
-        ids, treq, tpos = (buf[offs[i]:offs[i] + n_tok] for i in range(3))
-        qs, ql, sp, cl, sl = (buf[offs[i]:offs[i] + n_req] for i in range(3, 8))
-        wr = buf[offs[8]:offs[8] + max(n_want, 1)]
-        row, w_i = 0, 0
-        for r, (e, rc) in enumerate(zip(entries, rcs)):
-            n = len(e.tokens)
-            ids[row:row + n] = e.tokens
-            treq[row:row + n] = r
-            tpos[row:row + n] = np.arange(rc.length, rc.length + n, dtype=np.int32)
-            qs[r], ql[r], sp[r], cl[r] = row, n, rc.length, rc.length + n
-            sl[r] = rc.slot if rc.slot is not None else -1
-            for w in e.want:
-                wr[w_i] = row + int(w)
-                w_i += 1
-            row += n
-        n_groups, mb = len(self.cache.groups), self.cache.max_blocks
-        if n_groups:
-            bt = buf[offs[9]:offs[9] + n_groups * n_req * mb].reshape(n_groups, n_req, mb)
-            self.cache.fill_block_tables(rcs, bt)
-        return turn
-
-    def _record(self, turn: int) -> None:
-        evt = torch.cuda.Event()
-        evt.record()
-        self._staging_evt[turn] = evt
-
-    def _state(self, dev, offs, entries, rcs, n_tok, n_req, n_want, fixed: bool = False):
-        """The step's state and cache views over the device metadata buffer
-        ``dev``.  ``fixed`` (graph capture): launch-sizing hints that do not
-        depend on the requests' current lengths."""
-        n_groups, mb = len(self.cache.groups), self.cache.max_blocks
-
-        def view(i, n):
-            return dev[offs[i]:offs[i] + n]
-
-        step = StepState(
-            n_tokens=n_tok, n_requests=n_req, n_want=n_want,
-            token_ids=view(0, n_tok), tok_req=view(1, n_tok), tok_pos=view(2, n_tok),
-            q_start=view(3, n_req), q_len=view(4, n_req), start_pos=view(5, n_req), ctx_len=view(6, n_req),
-            want_rows=view(8, n_want), status=self.status,
-            max_q_len=max(len(e.tokens) for e in entries),
-            max_ctx_len=self.max_context if fixed else max(rc.length + len(e.tokens) for e, rc in zip(entries, rcs)),
-            host_q_start=[] if fixed else [int(v) for v in np.cumsum([0] + [len(e.tokens) for e in entries[:-1]])],
-            host_q_len=[] if fixed else [len(e.tokens) for e in entries],
-            host_start_pos=[] if fixed else [rc.length for rc in rcs],
-        )
-        tables = [dev[offs[9] + g * n_req * mb: offs[9] + (g + 1) * n_req * mb].view(n_req, mb)
-                  for g in range(n_groups)]
-        caches = self.cache.views(tables, view(7, n_req), [] if fixed else [rc.slot for rc in rcs])
-        return step, caches
 
     def _graph_meta(self, batch: int, total: int) -> torch.Tensor:
         buf = self._graph_bufs.get(batch)

@@ -1,0 +1,162 @@
+"""Generation through the public entry point and the command line."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm2 as plain
+from helpers import TINY, TOL, make_folder, plain_logits, random_ids, rel_err
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _gen(folder, dtype, **kw):
+    from gibbs_b200 import Generator
+    args = dict(dtype=dtype, device="cuda:0", ctx=512, page_size=16, n_pages=64, max_running=4)
+    args.update(kw)
+    return Generator(folder, **args)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_float32_equals_plain(tmp_path, name):
+    from gibbs_b200 import SamplingParams
+    folder = make_folder(tmp_path, name, std=0.05)
+    cfg, w = plain.load_folder(folder)
+    vocab = TINY[name][0]["vocab_size"]
+    prompts = [random_ids(5, 7, vocab), random_ids(6, 13, vocab), [3]]
+    gen = _gen(folder, "float32")
+    outs = gen.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=8), stop_at_eos=False)
+    for p, o in zip(prompts, outs):
+        assert o == plain.greedy(cfg, w, p, 8)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_follows_the_plain_logits(tmp_path, dtype):
+    """300 tokens decoded one by one (through CUDA graphs in steady state): every
+    token must be the plain model's choice given the same history; in bfloat16
+    a token may differ only where the plain logits are within rounding."""
+    from gibbs_b200 import SamplingParams
+    stored = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+    folder = make_folder(tmp_path, "A", stored=stored, std=0.05)
+    prompt = random_ids(9, 20, 512)
+    gen = _gen(folder, dtype)
+    out = gen.generate([prompt], SamplingParams(temperature=0.0, max_new_tokens=300), stop_at_eos=False)[0]
+    assert len(out) == 300
+    logits = plain_logits(folder, prompt + out)              # teacher forced on the engine's own tokens
+    for t, tok in enumerate(out):
+        row = logits[len(prompt) + t - 1]
+        if dtype == "float32":
+            assert tok == int(np.argmax(row)), t
+        else:
+            assert row.max() - row[tok] <= 0.02 * (row.max() - row.min()), t
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(tmp_path, dtype):
+    from gibbs_b200 import StepEntry
+    stored = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+    folder = make_folder(tmp_path, "B", stored=stored)
+    ids = random_ids(1, 6, 1000)
+    want = plain_logits(folder, ids)
+    eng = _gen(folder, dtype).engine
+    for cut in ([1, 1, 1, 1, 1, 1], [1, 2, 3], [2, 1, 3], [3, 3]):
+        eng.open("s")
+        got, pos = [], 0
+        for n in cut:
+            got.append(eng.step([StepEntry("s", ids[pos:pos + n], list(range(n)))]).cpu().numpy())
+            pos += n
+        eng.close("s")
+        assert rel_err(np.concatenate(got), want) < TOL[dtype], cut
+
+
+def test_temperature_sampling_is_seeded_and_stays_in_the_top_k(tmp_path):
+    from gibbs_b200 import SamplingParams
+    folder = make_folder(tmp_path, "A", std=0.08)
+    prompt = random_ids(2, 10, 512)
+    gen = _gen(folder, "float32")
+    p = SamplingParams(temperature=0.9, top_k=5, top_p=0.95, max_new_tokens=24, seed=123)
+    a = gen.generate([prompt], p, stop_at_eos=False)[0]
+    b = gen.generate([prompt], p, stop_at_eos=False)[0]
+    c = gen.generate([prompt], SamplingParams(temperature=0.9, top_k=5, top_p=0.95, max_new_tokens=24, seed=124),
+                     stop_at_eos=False)[0]
+    assert a == b and a != c
+    logits = plain_logits(folder, prompt + a)
+    for t, tok in enumerate(a):
+        row = logits[len(prompt) + t - 1]
+        assert tok in np.argsort(-row)[:5]
+    # same seed, other batch composition: a request's draws do not depend on its neighbours
+    d = gen.generate([random_ids(3, 4, 512), prompt], [SamplingParams(max_new_tokens=5), p], stop_at_eos=False)[1]
+    assert d == a
+
+
+def test_scheduler_preempts_and_recomputes_on_the_gpu(tmp_path):
+    """A pool too small for both requests at full length: the one admitted last
+    gives way and is recomputed; tokens equal an unconstrained run."""
+    from gibbs_b200 import SamplingParams
+    folder = make_folder(tmp_path, "B", std=0.05)
+    prompts = [random_ids(11, 30, 1000), random_ids(12, 28, 1000)]
+    p = SamplingParams(temperature=0.0, max_new_tokens=40)
+    roomy = _gen(folder, "float32", n_pages=64).generate(prompts, p, stop_at_eos=False)
+    gen = _gen(folder, "float32", n_pages=7, page_size=16, max_running=2)     # 112 positions for 138
+    sched = gen.scheduler(stop_at_eos=False)
+    ids = [sched.submit(q, p) for q in prompts]
+    preempted = []
+    while sched.has_work():
+        preempted += sched.step().preempted
+    assert preempted and [sched.sequences[i].output for i in ids] == roomy
+    assert gen.engine.cache.free_pages() == [7]
+
+
+def test_eos_from_config_stops_generation(tmp_path):
+    from gibbs_b200 import Lfm2Config, SamplingParams, write_random_model
+    raw = dict(TINY["A"][0])
+    cfg0, w0 = None, None
+    folder = make_folder(tmp_path, "A", std=0.05)
+    prompt = random_ids(4, 9, 512)
+    free = _gen(folder, "float32").generate([prompt], SamplingParams(temperature=0.0, max_new_tokens=12),
+                                            stop_at_eos=False)[0]
+    raw["eos_token_id"] = free[4]
+    cut = free.index(free[4])
+    folder2 = write_random_model(tmp_path / "with_eos", Lfm2Config.from_dict(raw), TINY["A"][1], gain_jitter=0.1,
+                                 std=0.05)
+    out = _gen(folder2, "float32").generate([prompt], SamplingParams(temperature=0.0, max_new_tokens=12))[0]
+    assert out == free[:cut]
+
+
+def test_command_line(tmp_path):
+    folder = make_folder(tmp_path, "A", std=0.05)
+    cfg, w = plain.load_folder(folder)
+    prompt = [5, 17, 42, 99]
+    run = lambda *args: subprocess.run([sys.executable, str(ROOT / "bin" / "gibbs-b200"), *args], text=True,
+                                       capture_output=True, timeout=600)
+    p = run("--model", str(folder), "--prompt-ids", ",".join(map(str, prompt)), "--max-tokens", "6",
+            "--temperature", "0", "--dtype", "float32", "--ctx", "64")
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = p.stdout.splitlines()
+    out = [int(t) for t in lines[lines.index("Output:") + 1].split(",")]
+    assert out == plain.greedy(cfg, w, prompt, 6)
+    assert any(l.startswith("Decode: 5 tokens") for l in lines) and any(l.startswith("Roofline:") for l in lines)
+    p = run("--model", str(folder), "--probe-top5", "5,17,42", "--dtype", "float32", "--ctx", "64")
+    top = json.loads(p.stdout.strip().splitlines()[-1])
+    want = plain.forward(cfg, w, [5, 17, 42])[-1].numpy()
+    assert top["ids"] == [int(i) for i in np.argsort(-want)[:5]]
+    p = run("--model", str(folder), "--arch-dump")
+    dump = json.loads(p.stdout)
+    assert dump["architecture"] == "Lfm2ForCausalLM" and dump["unconsumed"] == []
+    assert dump["config"]["ffn_dim (derived)"] == 192
+    (tmp_path / "cfg.json").write_text(json.dumps(TINY["B"][0]))
+    p = run("--random", str(tmp_path / "cfg.json"), "--seed", "1", "--save", str(tmp_path / "rnd"), "--dtype",
+            "float32")
+    assert p.returncode == 0 and (tmp_path / "rnd" / "model.safetensors").exists()
+    (tmp_path / "suite.json").write_text(json.dumps({"defaults": {"decode_tokens": 8, "prefill_tokens": 32, "runs": 1},
+                                                     "models": [{"id": str(folder)}]}))
+    p = run("--model", str(folder), "--bench", str(tmp_path / "suite.json"), "--dtype", "float32")
+    assert p.returncode == 0, p.stderr[-2000:]
+    rec = json.loads(p.stdout.strip().splitlines()[-1])
+    for key in ("decode_tok_s", "prefill_tok_s", "bytes_per_token", "roofline_pct", "wall_ms", "weights_ms"):
+        assert key in rec

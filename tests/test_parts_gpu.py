@@ -1,0 +1,338 @@
+"""Each part alone against the plain function of the same part; models put
+together from a hand-written plan (a layer run twice, a layer that reads
+another layer's cache, a windowed layer); and a toy mixer with state of its
+own that is defined here, registered, built and stepped without any change
+to the framework."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm2 as plain
+from helpers import TOL, rel_err
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _rt(dtype):
+    from gibbs_b200.parts import Runtime
+    return Runtime(torch.bfloat16 if dtype == "bfloat16" else torch.float32, torch.device(DEV))
+
+
+def _step_for(part_needs, before, q_lens, dtype, page_size=8, seed=0):
+    """A cache manager for one mixer and a step over requests that already hold
+    ``before`` positions and bring ``q_lens`` new ones."""
+    from gibbs_b200.cache import CacheManager
+    from gibbs_b200.engine.step import StepBuilder, StepEntry
+    total = sum(a + b for a, b in zip(before, q_lens))
+    cache = CacheManager([(part_needs, None)], n_pages=total // page_size + len(before) + 2, page_size=page_size,
+                         n_slots=len(before), dtype=_rt(dtype).dtype, device=DEV, max_context=512)
+    builder = StepBuilder(cache, DEV, max_requests=len(before), max_step_tokens=1024)
+    rcs = [cache.open(i) for i in range(len(before))]
+    return cache, builder, rcs
+
+
+def _run_mixer(mixer, tokens_h, cuts, dtype, hidden):
+    """Feed each request's rows of ``tokens_h`` ([n_r, hidden] float64 per
+    request) through the mixer in the portions ``cuts`` gives; returns what
+    the mixer added to a zero residual, per request."""
+    from gibbs_b200.engine.step import StepEntry
+    from gibbs_b200.parts import Residual
+    rt = _rt(dtype)
+    cache, builder, rcs = _step_for(mixer.cache_needs(), [0] * len(tokens_h), [len(t) for t in tokens_h], dtype)
+    outs = [[] for _ in tokens_h]
+    pos = [0] * len(tokens_h)
+    for step_cut in cuts:                                    # step_cut: {request: n tokens}
+        entries, rows = [], []
+        for r, n in step_cut.items():
+            entries.append(StepEntry(r, [0] * n, []))
+            rows.append(tokens_h[r][pos[r]:pos[r] + n])
+        live = [rcs[e.request_id] for e in entries]
+        for e, rc in zip(entries, live):
+            cache.reserve(rc, rc.length + len(e.tokens))
+        step, caches = builder.build(entries, live)
+        h = torch.cat(rows).to(rt.dtype).to(DEV)
+        res = Residual(torch.zeros(h.shape[0], hidden, dtype=torch.float32, device=DEV))
+        mixer.forward(h, res, step, caches[0])
+        got = res.tensor().cpu().double()
+        o = 0
+        for e, rc in zip(entries, live):
+            n = len(e.tokens)
+            outs[e.request_id].append(got[o:o + n])
+            o += n
+            pos[e.request_id] += n
+            cache.advance(rc, rc.length + n)
+    assert int(builder.status.item()) == 0
+    return [torch.cat(o) for o in outs]
+
+
+CUTS = [
+    [{0: 37, 1: 5, 2: 60}],                                                       # whole
+    [{0: 30, 2: 2}, {0: 1, 1: 2, 2: 40}, {0: 1, 1: 3}, {0: 5, 2: 17}, {2: 1}],     # portions beside single tokens
+]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_part_alone(dtype):
+    from gibbs_b200.config import PartSpec
+    from gibbs_b200.parts import part_class
+    torch.manual_seed(0)
+    hidden, heads, kvh, hd, eps = 80, 6, 2, 16, 1e-6
+    sizes = dict(hidden=hidden, heads=heads, kv_heads=kvh, head_dim=hd, eps=eps, theta=5e5)
+    w = {"q_proj.weight": torch.randn(heads * hd, hidden) / 9, "k_proj.weight": torch.randn(kvh * hd, hidden) / 9,
+         "v_proj.weight": torch.randn(kvh * hd, hidden) / 9, "out_proj.weight": torch.randn(hidden, heads * hd) / 9,
+         "q_norm.weight": 1 + 0.2 * torch.randn(hd), "k_norm.weight": 1 + 0.2 * torch.randn(hd),
+         "q_proj.bias": torch.randn(heads * hd) / 5, "k_proj.bias": torch.randn(kvh * hd) / 5,
+         "v_proj.bias": torch.randn(kvh * hd) / 5, "out_proj.bias": torch.randn(hidden) / 5}
+    rt = _rt(dtype)
+    if dtype == "bfloat16":
+        w = {k: (v.to(torch.bfloat16) if v.dim() == 2 else v) for k, v in w.items()}
+    params = {"hidden": hidden, "heads": heads, "kv_heads": kvh, "head_dim": hd, "bias": True, "qk_norm": True,
+              "qk_norm_eps": eps, "scale": 1 / math.sqrt(hd), "window": None,
+              "position": PartSpec("rope_half_split", {"head_dim": hd, "rotary_dim": hd, "theta": 5e5})}
+    mixer = part_class("mixer", "gqa_attention")(params, {k: v.to(DEV) for k, v in w.items()}, rt)
+    toks = [torch.randn(n, hidden, dtype=torch.float64) for n in (37, 5, 60)]
+    if dtype == "bfloat16":
+        toks = [t.to(torch.bfloat16).double() for t in toks]
+    plain_w = {"p." + k.replace("q_norm", "q_layernorm").replace("k_norm", "k_layernorm"): v.double()
+               for k, v in w.items()}
+    want = [plain.attention_mixer(t, plain_w, "p.", sizes, torch.arange(len(t))) for t in toks]
+    for cuts in CUTS:
+        got = _run_mixer(mixer, toks, cuts, dtype, hidden)
+        for g, wv in zip(got, want):
+            assert rel_err(g, wv.numpy()) < TOL[dtype] * (1 if dtype == "float32" else 2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kernel,bias", [(3, False), (5, True)])
+def test_short_conv_part_alone(dtype, kernel, bias):
+    from gibbs_b200.parts import part_class
+    torch.manual_seed(kernel)
+    hidden = 72
+    w = {"in_proj.weight": torch.randn(3 * hidden, hidden) / 8, "conv.weight": torch.randn(hidden, 1, kernel) / 2,
+         "out_proj.weight": torch.randn(hidden, hidden) / 8}
+    if bias:
+        w.update({"in_proj.bias": torch.randn(3 * hidden) / 4, "conv.bias": torch.randn(hidden) / 4,
+                  "out_proj.bias": torch.randn(hidden) / 4})
+    if dtype == "bfloat16":
+        w = {k: (v.to(torch.bfloat16) if k.endswith("proj.weight") else v) for k, v in w.items()}
+    tensors = {k: (v.reshape(hidden, kernel) if k == "conv.weight" else v).to(DEV) for k, v in w.items()}
+    mixer = part_class("mixer", "gated_short_conv")({"hidden": hidden, "kernel": kernel, "bias": bias}, tensors,
+                                                    _rt(dtype))
+    toks = [torch.randn(n, hidden, dtype=torch.float64) for n in (37, 5, 60)]
+    if dtype == "bfloat16":
+        toks = [t.to(torch.bfloat16).double() for t in toks]
+    plain_w = {"p." + k: v.double() for k, v in w.items()}
+    want = [plain.short_conv_mixer(t, plain_w, "p.", {"hidden": hidden, "conv_k": kernel}) for t in toks]
+    for cuts in CUTS:
+        got = _run_mixer(mixer, toks, cuts, dtype, hidden)
+        for g, wv in zip(got, want):
+            assert rel_err(g, wv.numpy()) < TOL[dtype] * (1 if dtype == "float32" else 2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("inner,bias", [(200, True), (192, False)])
+def test_swiglu_part_alone(dtype, inner, bias):
+    """inner = 192 takes the fused epilogue in bfloat16, 200 the separate kernel."""
+    from gibbs_b200.parts import Residual, part_class
+    torch.manual_seed(inner)
+    hidden = 88
+    w = {"gate.weight": torch.randn(inner, hidden) / 6, "up.weight": torch.randn(inner, hidden) / 6,
+         "down.weight": torch.randn(hidden, inner) / 6}
+    if bias:
+        w.update({"gate.bias": torch.randn(inner) / 3, "up.bias": torch.randn(inner) / 3,
+                  "down.bias": torch.randn(hidden) / 3})
+    if dtype == "bfloat16":
+        w = {k: (v.to(torch.bfloat16) if v.dim() == 2 else v) for k, v in w.items()}
+    ffn = part_class("feed_forward", "swiglu")({"hidden": hidden, "inner": inner, "bias": bias},
+                                               {k: v.to(DEV) for k, v in w.items()}, _rt(dtype))
+    assert ffn.fused == (dtype == "bfloat16" and inner % 64 == 0)
+    h = torch.randn(33, hidden, dtype=torch.float64)
+    if dtype == "bfloat16":
+        h = h.to(torch.bfloat16).double()
+    names = {"gate": "w1", "up": "w3", "down": "w2"}
+    plain_w = {"p." + names[k.split(".")[0]] + "." + k.split(".")[1]: v.double() for k, v in w.items()}
+    want = plain.swiglu_ffn(h, plain_w, "p.")
+    base = torch.randn(33, hidden)
+    res = Residual(base.clone().to(DEV))
+    ffn.forward(h.to(_rt(dtype).dtype).to(DEV), res, None)
+    assert rel_err(res.tensor().cpu().double() - base.double(), want.numpy()) < TOL[dtype] * (1 if dtype == "float32" else 2)
+
+
+def test_norm_and_position_parts_alone():
+    from gibbs_b200.parts import part_class
+    rt = _rt("float32")
+    g = 1 + 0.3 * torch.randn(100)
+    norm = part_class("norm", "rmsnorm")({"dim": 100, "eps": 1e-6}, {"weight": g.to(DEV)}, rt)
+    x = torch.randn(7, 100) * 5
+    want = plain.rms_norm(x.double(), g.double(), 1e-6)
+    assert rel_err(norm.forward(x.to(DEV)).cpu(), want.numpy()) < 1e-6
+    rows = torch.tensor([6, 2], dtype=torch.int32, device=DEV)
+    assert rel_err(norm.forward(x.to(DEV), rows=rows).cpu(), want[[6, 2]].numpy()) < 1e-6
+    for theta, hd in ((10000.0, 16), (1e6, 64), (5e5, 48)):
+        rope = part_class("position", "rope_half_split")({"head_dim": hd, "rotary_dim": hd, "theta": theta}, {}, rt)
+        r = rope.rotary()
+        assert not r.adjacent_pairs and r.rotary_dim == hd
+        assert torch.equal(r.inv_freq.cpu(), plain.rope_inv_freq(hd, theta, torch.float32))
+    assert part_class("position", "rope_adjacent")({"head_dim": 8, "theta": 1e4}, {}, rt).rotary().adjacent_pairs
+    assert part_class("position", "none")({}, {}, rt).rotary() is None
+    with pytest.raises(KeyError, match="known"):
+        part_class("mixer", "no_such_mixer")
+
+
+# ---------------------------------------------------------------------------
+# models from hand-written plans
+# ---------------------------------------------------------------------------
+
+class ToyDecayMixer:
+    """A mixer with state of its own, written with tensor operations: per
+    request a vector s (zero at the start); for every token s = a * s + W_in h,
+    and the mixer adds W_out s to the residual stream."""
+    category = "mixer"
+    capturable = False                      # reads the step's host-side lists
+
+    @classmethod
+    def declare(cls, params):
+        from gibbs_b200.parts import TensorDecl, VECTOR
+        h, d = params["hidden"], params["state"]
+        return {"w_in": TensorDecl.of(d, h), "w_out": TensorDecl.of(h, d), "decay": TensorDecl.of(d, role=VECTOR)}
+
+    def __init__(self, params, tensors, rt):
+        self.rt, self.d = rt, params["state"]
+        self.w_in, self.w_out = tensors["w_in"].float(), tensors["w_out"].float()
+        self.decay = tensors["decay"].float()
+
+    def kernel_libraries(self):
+        return ("core",)
+
+    def cache_needs(self):
+        from gibbs_b200.parts import SlotState
+        return [SlotState((self.d,), torch.float32)]
+
+    def forward(self, h, residual, step, caches):
+        slot = caches[0]
+        u = h.float() @ self.w_in.T
+        out = torch.empty(h.shape[0], self.w_out.shape[0], device=h.device)
+        for r, (start, n) in enumerate(zip(step.host_q_start, step.host_q_len)):
+            s = slot.state[slot.host_slot_ids[r]].clone()
+            for i in range(start, start + n):
+                s = self.decay * s + u[i]
+                out[i] = self.w_out @ s
+            slot.state[slot.host_slot_ids[r]] = s
+        residual.add_(out)
+
+
+def _plain_toy(h, w_in, w_out, decay):
+    s = torch.zeros(w_in.shape[0], dtype=torch.float64)
+    out = []
+    for i in range(h.shape[0]):
+        s = decay * s + w_in @ h[i]
+        out.append(w_out @ s)
+    return torch.stack(out)
+
+
+def _hand_plan(hidden=64, heads=4, kvh=2, hd=16, inner=128, vocab=300, eps=1e-5, window=24, state=10):
+    """Layers: 0 toy mixer, 1 attention (all keys), 2 attention with a window, 3 attention without
+    k/v of its own.  Order: 0, 1, 2, 1 again (its own cache), 3 reading the cache of entry 1."""
+    from gibbs_b200.config import LayerSpec, ModelPlan, OrderEntry, PartSpec
+
+    def norm(name):
+        return PartSpec("rmsnorm", {"dim": hidden, "eps": eps}, {"weight": name})
+
+    def ffn(i):
+        return PartSpec("swiglu", {"hidden": hidden, "inner": inner, "bias": False},
+                        {"gate.weight": f"l{i}.g", "up.weight": f"l{i}.u", "down.weight": f"l{i}.d"})
+
+    def attn(i, window=None, shares=False):
+        t = {"q_proj.weight": f"l{i}.q", "out_proj.weight": f"l{i}.o", "q_norm.weight": f"l{i}.qn"}
+        if not shares:
+            t.update({"k_proj.weight": f"l{i}.k", "v_proj.weight": f"l{i}.v", "k_norm.weight": f"l{i}.kn"})
+        return PartSpec("gqa_attention", {
+            "hidden": hidden, "heads": heads, "kv_heads": kvh, "head_dim": hd, "bias": False, "qk_norm": True,
+            "qk_norm_eps": eps, "scale": 1 / math.sqrt(hd), "window": window, "shares_kv": shares,
+            "position": PartSpec("rope_half_split", {"head_dim": hd, "rotary_dim": hd, "theta": 1e4})}, t)
+
+    toy = PartSpec("toy_decay", {"hidden": hidden, "state": state},
+                   {"w_in": "l0.win", "w_out": "l0.wout", "decay": "l0.decay"})
+    mixers = [toy, attn(1), attn(2, window=window), attn(3, shares=True)]
+    layers = tuple(LayerSpec("prenorm_residual", norm(f"l{i}.n1"), m, norm(f"l{i}.n2"), ffn(i))
+                   for i, m in enumerate(mixers))
+    order = (OrderEntry(0), OrderEntry(1), OrderEntry(2), OrderEntry(1), OrderEntry(3, reads_cache_of=1))
+    return ModelPlan("hand-made", vocab, hidden, 512, PartSpec("token_embedding", {"vocab": vocab, "dim": hidden},
+                                                                {"weight": "emb"}),
+                     layers, order, norm("fn"), PartSpec("lm_head", {"vocab": vocab, "dim": hidden}, {"weight": "emb"}))
+
+
+def _plain_hand_model(w, ids, hidden=64, heads=4, kvh=2, hd=16, eps=1e-5, window=24):
+    """The same model written out plainly (whole sequence, no cache)."""
+    n = len(ids)
+    pos = torch.arange(n)
+    x = w["emb"][torch.tensor(ids)]
+    inv = plain.rope_inv_freq(hd, 1e4, torch.float64)
+
+    def qkv(i, h, with_kv=True):
+        q = plain.rms_norm((h @ w[f"l{i}.q"].T).reshape(n, heads, hd), w[f"l{i}.qn"], eps)
+        q = plain.rope_half_split(q, pos, inv)
+        if not with_kv:
+            return q, None, None
+        k = plain.rms_norm((h @ w[f"l{i}.k"].T).reshape(n, kvh, hd), w[f"l{i}.kn"], eps)
+        return q, plain.rope_half_split(k, pos, inv), (h @ w[f"l{i}.v"].T).reshape(n, kvh, hd)
+
+    def ffn(i, x):
+        h = plain.rms_norm(x, w[f"l{i}.n2"], eps)
+        g, u = h @ w[f"l{i}.g"].T, h @ w[f"l{i}.u"].T
+        return x + (g / (1 + torch.exp(-g)) * u) @ w[f"l{i}.d"].T
+
+    kv_of_entry1 = None
+    for e, (layer, reads) in enumerate([(0, None), (1, None), (2, None), (1, None), (3, 1)]):
+        h = plain.rms_norm(x, w[f"l{layer}.n1"], eps)
+        if layer == 0:
+            a = _plain_toy(h, w["l0.win"], w["l0.wout"], w["l0.decay"])
+        else:
+            q, k, v = qkv(layer, h, with_kv=reads is None)
+            if e == 1:
+                kv_of_entry1 = (k, v)
+            if reads is not None:
+                k, v = kv_of_entry1
+            o = plain.causal_attention(q, k, v, 1 / math.sqrt(hd), window=window if layer == 2 else None)
+            a = o.reshape(n, heads * hd) @ w[f"l{layer}.o"].T
+        x = ffn(layer, x + a)
+    return plain.rms_norm(x, w["fn"], eps) @ w["emb"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_hand_made_model_with_toy_mixer_repeated_layer_shared_cache_and_window(dtype):
+    from gibbs_b200 import Engine, register_part
+    from gibbs_b200.parts import build_model
+    from gibbs_b200.weights import TensorDict, expected_tensors
+    from helpers import first_wrong, run_trace_on_engine, trace_mixed, trace_portions, trace_whole, random_ids
+    register_part("mixer", "toy_decay", ToyDecayMixer)
+    plan = _hand_plan()
+    torch.manual_seed(4)
+    tensors = {}
+    for name, decl in expected_tensors(plan).items():
+        shape = decl.shapes[0]
+        if name.endswith("decay"):
+            t = torch.rand(shape) * 0.5 + 0.4
+        elif len(shape) == 1:
+            t = 1 + 0.1 * torch.randn(shape)
+        else:
+            t = torch.randn(shape) * (0.3 if name == "emb" else 1.0 / math.sqrt(shape[-1]))
+        tensors[name] = t.to(torch.bfloat16) if (dtype == "bfloat16" and len(shape) == 2) else t
+    model = build_model(plan, TensorDict(tensors), torch.bfloat16 if dtype == "bfloat16" else torch.float32, DEV)
+    needs = model.entry_needs()
+    assert [len(n) for n, _ in needs] == [1, 1, 1, 1, 0] and needs[4][1] == 1
+    eng = Engine(model, n_pages={None: 40, 24: 40}, page_size=8, max_requests=4, max_step_tokens=512)
+    assert len(eng.cache.groups) == 2 and not eng.use_graphs                 # all keys; window of 24
+    w64 = {k: v.double() for k, v in tensors.items()}
+    reqs = {f"r{i}": random_ids(70 + i, n, 300) for i, n in enumerate([70, 33, 100, 5, 64])}
+    for steps in (trace_whole(reqs), trace_portions(reqs), trace_mixed(reqs, capacity_tokens=320, seed=2)):
+        got = run_trace_on_engine(eng, steps)
+        for rid, ids in reqs.items():
+            want = _plain_hand_model(w64, ids).numpy()
+            bad = first_wrong(got[rid], want, TOL[dtype] * (1 if dtype == "float32" else 2))
+            assert bad is None, f"{rid}: first wrong position {bad}"
+    # the windowed group gave pages back while requests were still running
+    assert eng.cache.free_pages() == [40, 40] and not eng.cache.live
