@@ -67,7 +67,7 @@ def build_dir() -> Path:
 
 def _fingerprint(sources: list[str]) -> str:
     h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
-    for name in sorted(sources) + sorted(p.name for p in HERE.glob("*.cuh")):
+    for name in sorted(sources) + sorted(p.name for p in list(HERE.glob("*.cuh")) + list(HERE.glob("*.h"))):
         h.update(name.encode())
         h.update((HERE / name).read_bytes())
     return h.hexdigest()

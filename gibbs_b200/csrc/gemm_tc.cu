@@ -494,3 +494,92 @@ GB_API void gb_linear_tc_forget() {
   std::lock_guard<std::mutex> lock(g_wmap_mutex);
   g_wmaps.clear();
 }
+
+// ---------------------------------------------------------------- no-allocation entry point
+// See gb_no_alloc.h.  The split-K partial tiles live in a fixed array inside this
+// library instead of a caller-provided workspace.
+#include "gb_no_alloc.h"
+
+namespace {
+
+// Every GPU that loads this library holds these 4 MiB until the process exits.
+static __device__ __align__(256) float g_static_workspace[GB_NO_ALLOC_MAX_WORKSPACE_FLOATS];
+
+constexpr int MAX_DEVICES = 64;
+std::mutex g_static_mutex;
+float* g_static_ptr[MAX_DEVICES] = {nullptr};
+
+// The device address of g_static_workspace on the current device.  In host code the
+// array's name is only a handle; the address a kernel can use comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+int static_workspace(float** out) {
+  int dev = -1;
+  GB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= MAX_DEVICES) GB_FAIL(GB_ERR_ARG, "gb_linear_tc_no_alloc: device index %d", dev);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    GB_CUDA(cudaGetSymbolAddress(&p, g_static_workspace));
+    g_static_ptr[dev] = (float*)p;
+  }
+  *out = g_static_ptr[dev];
+  return GB_OK;
+}
+
+}  // namespace
+
+GB_API long long gb_linear_tc_no_alloc_needs(int M, int N, int K) { return gb_linear_tc_workspace(M, N, K); }
+
+GB_API int gb_linear_tc_no_alloc(const void* X, long long ldx, const void* W, long long ldw, const float* bias,
+                                 void* out, int mode, long long ldo, int M, int N, int K, int* status,
+                                 cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (!gb_linear_tc_supported(X, ldx, W, ldw, K))
+    GB_FAIL(GB_ERR_ARG, "gb_linear_tc_no_alloc: K = %d and the row strides (%lld, %lld) must be multiples of 8 and "
+            "the bases 16-byte aligned", K, ldx, ldw);
+  if (mode < OUT_BF16 || mode > OUT_SWIGLU) GB_FAIL(GB_ERR_ARG, "gb_linear_tc_no_alloc: output mode %d", mode);
+  if (mode == OUT_SWIGLU && N % 128 != 0)
+    GB_FAIL(GB_ERR_ARG, "gb_linear_tc_no_alloc: the SwiGLU epilogue needs N = %d to be a multiple of 128", N);
+  if (status == nullptr) GB_FAIL(GB_ERR_ARG, "gb_linear_tc_no_alloc: a status word on the device is required");
+  if (gb_div_up(M, 16) > 65535) GB_FAIL(GB_ERR_ARG, "gb_linear_tc_no_alloc: M = %d is too large", M);
+  int bn, splits, kb_per_split;
+  plan(M, N, K, &bn, &splits, &kb_per_split);
+  const long long need = splits > 1 ? (long long)splits * M * N : 0;
+  if (need > GB_NO_ALLOC_MAX_WORKSPACE_FLOATS)
+    GB_FAIL(GB_ERR_ARG, "gb_linear_tc_no_alloc: M = %d, N = %d, K = %d split K %d ways and need %lld floats of "
+            "scratch; the built-in scratch holds %d (use gb_linear_tc with your own workspace)",
+            M, N, K, splits, need, GB_NO_ALLOC_MAX_WORKSPACE_FLOATS);
+  float* ws = nullptr;
+  if (splits > 1) {
+    const int rc = static_workspace(&ws);
+    if (rc != GB_OK) return rc;
+  }
+  CUtensorMap tw, tx;   // on the stack: no cache, nothing is kept between calls
+  if (!make_tmap(&tw, W, N, K, ldw, BM)) GB_FAIL(GB_ERR_CUDA, "gb_linear_tc_no_alloc: cuTensorMapEncodeTiled failed (W)");
+  if (!make_tmap(&tx, X, M, K, ldx, bn)) GB_FAIL(GB_ERR_CUDA, "gb_linear_tc_no_alloc: cuTensorMapEncodeTiled failed (X)");
+  GemmParams p;
+  p.bias = bias; p.out = out; p.ldo = ldo; p.mode = mode; p.M = M; p.N = N;
+  p.total_kb = gb_div_up(K, BK); p.kb_per_split = kb_per_split; p.splits = splits;
+  p.ws = ws;
+  p.prefetch = nullptr; p.prefetch_bytes = 0;
+  p.stream_weights = M <= 64 ? 1 : 0;
+  p.status = status;
+  int rc;
+  switch (bn) {
+    case 16: rc = launch<16>(tw, tx, p, stream); break;
+    case 32: rc = launch<32>(tw, tx, p, stream); break;
+    case 64: rc = launch<64>(tw, tx, p, stream); break;
+    default: rc = launch<128>(tw, tx, p, stream); break;
+  }
+  if (rc != GB_OK) return rc;
+  GB_CHECK_LAUNCH("gb_linear_tc_no_alloc");
+  if (splits > 1) {
+    const long long work = (long long)M * (mode == OUT_SWIGLU ? N / 2 : N);
+    const int blocks = (int)((work + 255) / 256 < 148 * 8 ? (work + 255) / 256 : 148 * 8);
+    gb_launch(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, (const float*)ws, splits, bias, out, ldo, mode,
+              M, N);
+    GB_CHECK_LAUNCH("gb_linear_tc_no_alloc (split-K reduce)");
+    return 2;
+  }
+  return 1;
+}
