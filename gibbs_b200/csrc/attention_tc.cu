@@ -90,6 +90,7 @@ attention_tc_kernel(const AttnParams p) {
   bf16* sq = reinterpret_cast<bf16*>(smem);                  // [BQ][STRIDE]
   bf16* sk = sq + BQ * STRIDE;                               // [2][KT][STRIDE]
   bf16* sv = sk + 2 * KT * STRIDE;                           // [2][KT][STRIDE]
+  __shared__ long long row_off[2][KT];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int group = p.heads / p.kv_heads;
@@ -125,25 +126,38 @@ attention_tc_kernel(const AttnParams p) {
     const bf16* src = p.q + (size_t)(row0 + (valid ? tl : 0)) * p.ldq + (size_t)(kvh * group + g) * HD + c * 8;
     cp_async_16(sq + row * STRIDE + c * 8, src, valid);
   }
+  // Where each of a tile's 64 keys lies in the pages (element offset of its row, -1: not
+  // visible) is worked out once per tile and row, not once per 16-byte piece: row_off[t & 1]
+  // belongs to tile t.  It is written one iteration before the tile's loads are issued; the
+  // barrier that ends every iteration makes it visible.
+  auto locate = [&](int t) {
+    for (int row = tid; row < KT; row += NT) {
+      const int j = t * KT + row;
+      long long off = -1;
+      if (j < hi_all && j >= lo_all) {
+        const int blk = j / p.page_size;
+        const int page = bt[blk];
+        if (page < 0 || page >= p.n_pages)
+          atomicExch(p.status, 2);
+        else
+          off = (((long long)page * p.kv_heads + kvh) * p.page_size + (j - blk * p.page_size)) * HD;
+      }
+      row_off[t & 1][row] = off;
+    }
+  };
   auto load_kv = [&](int t, int buf) {
     for (int idx = tid; idx < KT * CHUNKS; idx += NT) {
       const int row = idx / CHUNKS, c = idx - row * CHUNKS;
-      const int j = t * KT + row;
-      bool valid = j < hi_all && j >= lo_all;
-      size_t off = 0;
-      if (valid) {
-        const int page = bt[j / p.page_size];
-        if (page < 0 || page >= p.n_pages) {
-          atomicExch(p.status, 2);
-          valid = false;
-        } else {
-          off = (((size_t)page * p.kv_heads + kvh) * p.page_size + j % p.page_size) * HD + c * 8;
-        }
-      }
-      cp_async_16(sk + (buf * KT + row) * STRIDE + c * 8, p.k_pages + off, valid);
-      cp_async_16(sv + (buf * KT + row) * STRIDE + c * 8, p.v_pages + off, valid);
+      const long long off = row_off[t & 1][row];
+      const bool valid = off >= 0;
+      const size_t src = valid ? (size_t)off + c * 8 : 0;
+      cp_async_16(sk + (buf * KT + row) * STRIDE + c * 8, p.k_pages + src, valid);
+      cp_async_16(sv + (buf * KT + row) * STRIDE + c * 8, p.v_pages + src, valid);
     }
   };
+  if (t_begin < t_end) locate(t_begin);
+  if (t_begin + 1 < t_end) locate(t_begin + 1);
+  __syncthreads();
   if (t_begin < t_end) load_kv(t_begin, 0);
   cp_async_commit();
 
@@ -171,6 +185,8 @@ attention_tc_kernel(const AttnParams p) {
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
+    // row_off[t & 1] was last read when tile t was requested, before the barrier above
+    if (t + 2 < t_end) locate(t + 2);
     if (t == t_begin) {
 #pragma unroll
       for (int kk = 0; kk < HD / 16; ++kk)
