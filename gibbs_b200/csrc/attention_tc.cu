@@ -98,10 +98,13 @@ attention_tc_kernel(const AttnParams p) {
   const int kvh = blockIdx.y, z = blockIdx.z;
 
   // which request and which of its tiles this CTA has
-  int r = 0, tile = (int)blockIdx.x, found = 0;
-  for (; r < p.n_requests; ++r) {
+  // Blocks are handed out in descending order of work: requests from the last to the first and,
+  // within a request, from its last tile (which sees the most keys) to its first, so that the
+  // long tiles of a causal prompt do not form the tail of the launch.
+  int r = p.n_requests - 1, tile = (int)blockIdx.x, found = 0;
+  for (; r >= 0; --r) {
     const int nt = (p.q_len[r] + tpt - 1) / tpt;
-    if (tile < nt) { found = 1; break; }
+    if (tile < nt) { found = 1; tile = nt - 1 - tile; break; }
     tile -= nt;
   }
   if (!found) return;

@@ -51,6 +51,65 @@ __global__ void short_conv_out_kernel(const T* __restrict__ bcx, long long ld, c
   out[(size_t)t * hidden + c] = from_f32<T>(to_f32(bcx[(size_t)t * ld + hidden + c]) * acc);
 }
 
+// The same for bfloat16 rows whose width is a multiple of 8: one thread takes 8 neighbouring
+// channels of a token with 16-byte loads and stores.
+__global__ void short_conv_out_vec8_kernel(const bf16* __restrict__ bcx, long long ld, const float* __restrict__ taps,
+                                           const float* __restrict__ bias, const float* __restrict__ state,
+                                           long long slot_stride, const int* __restrict__ slot_ids,
+                                           const int* __restrict__ tok_req, const int* __restrict__ q_start,
+                                           bf16* __restrict__ out, int n_tokens, int hidden, int K) {
+  pdl_trigger();
+  pdl_wait();
+  const int groups = hidden >> 3;
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= (long long)n_tokens * groups) return;
+  const int t = (int)(gid / groups), c = (int)(gid - (long long)t * groups) << 3;
+  const int r = tok_req[t];
+  const int first = q_start[r];
+  const int i = t - first;
+  const float* st = state + (size_t)slot_ids[r] * slot_stride;
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  auto unpack = [](uint4 u, float* f) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 v = __bfloat1622float2(h[e]);
+      f[2 * e] = v.x;
+      f[2 * e + 1] = v.y;
+    }
+  };
+  for (int j = 0; j < K; ++j) {
+    const int src = i - (K - 1 - j);
+    float v[8];
+    if (src >= 0) {
+      const bf16* row = bcx + (size_t)(first + src) * ld;
+      float b[8], x[8];
+      unpack(*reinterpret_cast<const uint4*>(row + c), b);
+      unpack(*reinterpret_cast<const uint4*>(row + 2 * hidden + c), x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = b[e] * x[e];
+    } else {
+      const float4* sp = reinterpret_cast<const float4*>(st + (size_t)(K - 1 + src) * hidden + c);
+      const float4 s0 = sp[0], s1 = sp[1];
+      v[0] = s0.x; v[1] = s0.y; v[2] = s0.z; v[3] = s0.w; v[4] = s1.x; v[5] = s1.y; v[6] = s1.z; v[7] = s1.w;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = fmaf(taps[(size_t)(c + e) * K + j], v[e], acc[e]);
+  }
+  float g[8];
+  unpack(*reinterpret_cast<const uint4*>(bcx + (size_t)t * ld + hidden + c), g);
+  uint4 o;
+  __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float a0 = acc[2 * e] + (bias ? bias[c + 2 * e] : 0.f), a1 = acc[2 * e + 1] + (bias ? bias[c + 2 * e + 1] : 0.f);
+    oh[e] = __floats2bfloat162_rn(g[2 * e] * a0, g[2 * e + 1] * a1);
+  }
+  *reinterpret_cast<uint4*>(out + (size_t)t * hidden + c) = o;
+}
+
 template <typename T>
 __global__ void short_conv_state_kernel(const T* __restrict__ bcx, long long ld, float* __restrict__ state,
                                         long long slot_stride, const int* __restrict__ slot_ids,
@@ -139,7 +198,14 @@ GB_API int gb_short_conv(const void* bcx, int dtype, long long ld, const float* 
         hidden, K);
     gb_launch(short_conv_state_kernel<float>, dim3(gb_div_up(total_s, threads)), dim3(threads), 0, stream, (const float*)bcx, ld, state, slot_stride, slot_ids, q_start, q_len, n_requests, hidden, K);
   } else if (dtype == GB_BF16) {
-    gb_launch(short_conv_out_kernel<bf16>, dim3(gb_div_up(total, threads)), dim3(threads), 0, stream, (const bf16*)bcx, ld, taps, bias, state, slot_stride, slot_ids, tok_req, q_start, (bf16*)out, n_tokens,
+    const bool vec = hidden % 8 == 0 && ld % 8 == 0 && slot_stride % 4 == 0 && ((uintptr_t)bcx & 15) == 0 &&
+                     ((uintptr_t)out & 15) == 0 && ((uintptr_t)state & 15) == 0;
+    if (vec)
+      gb_launch(short_conv_out_vec8_kernel, dim3(gb_div_up(total / 8, threads)), dim3(threads), 0, stream,
+                (const bf16*)bcx, ld, taps, bias, (const float*)state, slot_stride, slot_ids, tok_req, q_start,
+                (bf16*)out, n_tokens, hidden, K);
+    else
+      gb_launch(short_conv_out_kernel<bf16>, dim3(gb_div_up(total, threads)), dim3(threads), 0, stream, (const bf16*)bcx, ld, taps, bias, state, slot_stride, slot_ids, tok_req, q_start, (bf16*)out, n_tokens,
         hidden, K);
     gb_launch(short_conv_state_kernel<bf16>, dim3(gb_div_up(total_s, threads)), dim3(threads), 0, stream, (const bf16*)bcx, ld, state, slot_stride, slot_ids, q_start, q_len, n_requests, hidden, K);
   } else {

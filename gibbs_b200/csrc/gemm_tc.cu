@@ -264,10 +264,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         float v[16];
         tmem_ld_16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, v);
         if (n < N) {
+          if (p.mode == OUT_F32_ACC) {
+            // read the 16 old values together (16 loads in flight), then add and store
+            float* base = (float*)p.out + (size_t)(m0 + c0) * p.ldo + n;
+            float old[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = m0 + c0 + j;
-            if (m < M) store_value(p, m, n, v[j] + b);
+            for (int j = 0; j < 16; ++j) old[j] = (m0 + c0 + j < M) ? __ldcg(base + (size_t)j * p.ldo) : 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (m0 + c0 + j < M) base[(size_t)j * p.ldo] = old[j] + (v[j] + b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int m = m0 + c0 + j;
+              if (m < M) store_value(p, m, n, v[j] + b);
+            }
           }
         }
       }

@@ -137,6 +137,39 @@ __global__ void sample_kernel(const float* __restrict__ logits, long long ldv, i
   out[row] = choice;
 }
 
+// All rows greedy: one pass, the first maximum of each row.
+__global__ void argmax_kernel(const float* __restrict__ logits, long long ldv, int vocab, int* __restrict__ out) {
+  __shared__ Cand warp_c[32];
+  pdl_trigger();
+  pdl_wait();
+  const float* x = logits + (size_t)blockIdx.x * ldv;
+  Cand best = {0.f, -1};
+  const bool vec = (ldv % 4 == 0) && (((uintptr_t)logits & 15) == 0);
+  const int n4 = vec ? vocab >> 2 : 0;
+  for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(x)[i];
+    const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const Cand c = {e[k], 4 * i + k};
+      if (e[k] == e[k] && better(c, best)) best = c;
+    }
+  }
+  for (int i = 4 * n4 + threadIdx.x; i < vocab; i += blockDim.x) {
+    const Cand c = {x[i], i};
+    if (c.v == c.v && better(c, best)) best = c;
+  }
+  best = warp_best(best);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  if (lane == 0) warp_c[warp] = best;
+  __syncthreads();
+  if (warp == 0) {
+    Cand c = lane < nwarps ? warp_c[lane] : Cand{0.f, -1};
+    c = warp_best(c);
+    if (lane == 0) out[blockIdx.x] = c.id < 0 ? 0 : c.id;
+  }
+}
+
 }  // namespace
 
 // logits: [rows, vocab] 32-bit with row stride ldv.  temperature / top_k /
@@ -148,6 +181,11 @@ GB_API int gb_sample(const float* logits, long long ldv, int rows, int vocab, co
   if (vocab <= 0) GB_FAIL(GB_ERR_ARG, "gb_sample: vocabulary of %d", vocab);
   int threads = 64;
   while (threads < 1024 && threads * 8 < vocab) threads <<= 1;
+  if (temperature == nullptr) {
+    gb_launch(argmax_kernel, dim3(rows), dim3(threads), 0, stream, logits, ldv, vocab, out);
+    GB_CHECK_LAUNCH("gb_sample (argmax)");
+    return GB_OK;
+  }
   gb_launch(sample_kernel, dim3(rows), dim3(threads), 0, stream, logits, ldv, vocab, temperature, top_k, top_p, seed, counter, out);
   GB_CHECK_LAUNCH("gb_sample");
   return GB_OK;
