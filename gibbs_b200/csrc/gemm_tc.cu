@@ -31,6 +31,8 @@
 // multiples of 8 elements, 16-byte aligned bases.  Ragged edges are zero-filled
 // by TMA on load and masked on store.  Every mbarrier wait is bounded; a wait
 // that runs out sets *status and the CTA drains and returns.
+#include <stdlib.h>
+
 #include <mutex>
 #include <unordered_map>
 
@@ -52,7 +54,7 @@ enum OutMode : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2, OUT_SWIGLU = 3 
 template <int BN> struct Cfg {
   static constexpr int X_TILE_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES;
-  static constexpr int STAGES = BN >= 128 ? 3 : (BN >= 64 ? 4 : 5);
+  static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 3 : (BN >= 64 ? 4 : 5));
   static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;   // + room to align to 1024
 };
@@ -66,6 +68,7 @@ struct GemmParams {
   float* ws;                    // [splits][M][N] partial tiles (splits > 1)
   const uint8_t* prefetch; long long prefetch_bytes;   // weights of the next product, or null
   int stream_weights;           // 1: read W with an evict-first L2 hint
+  int vec_store;                // 1: out rows are 16-byte aligned (base and row stride)
   int* status;
 };
 
@@ -234,6 +237,98 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
           }
         }
       }
+    } else if (good && BN >= 32 && p.vec_store && n0 + BM <= N) {
+      // Large tiles: the accumulator is transposed through shared memory (the pipeline's
+      // stages are free once the accumulator is complete) and leaves in 16-byte pieces,
+      // whole rows of the output at a time, instead of one element per thread and column.
+      const float b = p.bias ? p.bias[n] : 0.f;
+      const int cols = min(BN, M - m0);                      // token rows of this tile
+      if (p.mode == OUT_SWIGLU) {
+        float* ub = reinterpret_cast<float*>(tiles);                                   // [BN][64] u + bias
+        bf16* ob = reinterpret_cast<bf16*>(tiles + (size_t)BN * 64 * sizeof(float));   // [BN][64] result
+#pragma unroll 1
+        for (int c0 = 0; c0 < cols; c0 += 16) {
+          float v[16];
+          tmem_ld_16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, v);
+          if (row >= 64) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) ub[(c0 + j) * 64 + (row - 64)] = v[j] + b;
+          }
+        }
+        epilogue_barrier();
+        if (row < 64) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < cols; c0 += 16) {
+            float v[16];
+            tmem_ld_16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, v);
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              ob[(c0 + j) * 64 + row] = __float2bfloat16_rn(silu_mul(v[j] + b, ub[(c0 + j) * 64 + row]));
+          }
+        }
+        epilogue_barrier();
+        bf16* dst = (bf16*)p.out + (size_t)m0 * p.ldo + (n0 >> 1);
+        for (int idx = et; idx < cols * 8; idx += 128) {        // 8 pieces of 8 bf16 per row
+          const int mm = idx >> 3, piece = idx & 7;
+          *reinterpret_cast<uint4*>(dst + (size_t)mm * p.ldo + piece * 8) =
+              *reinterpret_cast<const uint4*>(ob + mm * 64 + piece * 8);
+        }
+      } else if (p.mode == OUT_BF16) {
+        bf16* ob = reinterpret_cast<bf16*>(tiles);                                     // [BN][128]
+#pragma unroll 1
+        for (int c0 = 0; c0 < cols; c0 += 16) {
+          float v[16];
+          tmem_ld_16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) ob[(c0 + j) * BM + row] = __float2bfloat16_rn(v[j] + b);
+        }
+        epilogue_barrier();
+        bf16* dst = (bf16*)p.out + (size_t)m0 * p.ldo + n0;
+        for (int idx = et; idx < cols * 16; idx += 128) {       // 16 pieces of 8 bf16 per row
+          const int mm = idx >> 4, piece = idx & 15;
+          *reinterpret_cast<uint4*>(dst + (size_t)mm * p.ldo + piece * 8) =
+              *reinterpret_cast<const uint4*>(ob + mm * BM + piece * 8);
+        }
+      } else {                                                // OUT_F32 / OUT_F32_ACC, 64 token rows at a time
+        float* fb = reinterpret_cast<float*>(tiles);                                   // [64][128]
+#pragma unroll 1
+        for (int h0 = 0; h0 < cols; h0 += 64) {
+          const int hc = min(64, cols - h0);
+#pragma unroll 1
+          for (int c0 = 0; c0 < hc; c0 += 16) {
+            float v[16];
+            tmem_ld_16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(h0 + c0), v);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) fb[(c0 + j) * BM + row] = v[j] + b;
+          }
+          epilogue_barrier();
+          float* dst = (float*)p.out + (size_t)(m0 + h0) * p.ldo + n0;
+          for (int idx = et; idx < hc * 32; idx += 128 * 4) {   // 32 pieces of 4 floats per row, 4 in flight
+            float4 nv[4], ov[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int id = idx + u * 128;
+              if (id < hc * 32) {
+                const int mm = id >> 5, piece = id & 31;
+                nv[u] = *reinterpret_cast<const float4*>(fb + mm * BM + piece * 4);
+                if (p.mode == OUT_F32_ACC)
+                  ov[u] = __ldcg(reinterpret_cast<const float4*>(dst + (size_t)mm * p.ldo + piece * 4));
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int id = idx + u * 128;
+              if (id < hc * 32) {
+                const int mm = id >> 5, piece = id & 31;
+                float4 r = nv[u];
+                if (p.mode == OUT_F32_ACC) { r.x += ov[u].x; r.y += ov[u].y; r.z += ov[u].z; r.w += ov[u].w; }
+                *reinterpret_cast<float4*>(dst + (size_t)mm * p.ldo + piece * 4) = r;
+              }
+            }
+          }
+          epilogue_barrier();
+        }
+      }
     } else if (good && p.mode == OUT_SWIGLU) {
       const float b = (p.bias && n < N) ? p.bias[n] : 0.f;
 #pragma unroll 1
@@ -292,6 +387,595 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   }
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------- persistent kernel (prompts)
+// For many tiles (prompt portions) one CTA per SM walks a list of tiles, so that the
+// set-up, the start of the TMA pipeline and the epilogue are paid once or hidden:
+//  - the producer runs ahead into the next tile while the MMAs of this one finish,
+//  - the accumulator is double-buffered in tensor memory (2 x BN columns): the epilogue
+//    warps drain tile i while the MMA thread fills tile i+1,
+//  - the epilogue transposes through a staging area in shared memory, releases the
+//    accumulator as soon as it has been read, and stores whole output rows in 16-byte pieces.
+// Tiles are numbered with the token tile fastest, so CTAs running at the same time share
+// the weight tiles in L2.  K is never split here.
+template <int BN> struct PCfg {
+  static constexpr int X_TILE_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES;
+  static constexpr int STAGES = 5;
+  static constexpr int STAGING_BYTES = BN * 64 * 4 + BN * 64 * 2;      // SwiGLU: u (f32) + result (bf16); others fit
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(192)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                          const GemmParams p) {
+  using C = PCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t full_bar[C::STAGES], empty_bar[C::STAGES], tmem_full_bar[2], tmem_empty_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int abort_flag;
+  pdl_trigger();
+
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* staging = tiles + (size_t)C::STAGES * C::STAGE_BYTES;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int M = p.M, N = p.N, nkb = p.total_kb;
+  const int tiles_m = (M + BN - 1) / BN, tiles_n = (N + BM - 1) / BM;
+  const int n_tiles = tiles_m * tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full_bar[a], 1);
+      mbar_init(&tmem_empty_bar[a], 1);
+    }
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      int it = 0;                                           // k-blocks requested so far, over all tiles
+      bool first = true;
+      for (int t = blockIdx.x; t < n_tiles && !abort_flag; t += gridDim.x) {
+        const int n0 = (t / tiles_m) * BM, m0 = (t % tiles_m) * BN;
+        int i = 0;
+        if (first) {
+          // The weights do not depend on earlier kernels: the first stages' weight tiles are
+          // requested at once, the activation tiles after those kernels have finished.
+          const int head = nkb < C::STAGES ? nkb : C::STAGES;
+          for (i = 0; i < head; ++i) {
+            mbar_arrive_expect_tx(&full_bar[i], C::STAGE_BYTES);
+            tma_load_2d(tiles + (size_t)i * C::STAGE_BYTES, &tmap_w, i * BK, n0, &full_bar[i]);
+          }
+          pdl_wait();
+          for (i = 0; i < head; ++i)
+            tma_load_2d(tiles + (size_t)i * C::STAGE_BYTES + W_TILE_BYTES, &tmap_x, i * BK, m0, &full_bar[i]);
+          it = head;
+          first = false;
+        }
+        for (; i < nkb; ++i, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
+            abort_flag = 1;
+            atomicExch(p.status, STATUS_TIMEOUT + 4);
+            break;
+          }
+          if (abort_flag) break;
+          uint8_t* st = tiles + (size_t)s * C::STAGE_BYTES;
+          mbar_arrive_expect_tx(&full_bar[s], C::STAGE_BYTES);
+          tma_load_2d(st, &tmap_w, i * BK, n0, &full_bar[s]);
+          tma_load_2d(st + W_TILE_BYTES, &tmap_x, i * BK, m0, &full_bar[s]);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = idesc_bf16_f32(BM, BN);
+      int it = 0, tile_i = 0;
+      for (int t = blockIdx.x; t < n_tiles && !abort_flag; t += gridDim.x, ++tile_i) {
+        const int a = tile_i & 1;
+        if (!mbar_wait(&tmem_empty_bar[a], ((tile_i >> 1) & 1) ^ 1)) {   // the epilogue has drained this buffer
+          abort_flag = 1;
+          atomicExch(p.status, STATUS_TIMEOUT + 5);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t acc = tmem_base + (uint32_t)(a * BN);
+        for (int i = 0; i < nkb; ++i, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], ph)) {
+            abort_flag = 1;
+            atomicExch(p.status, STATUS_TIMEOUT + 6);
+            break;
+          }
+          if (abort_flag) break;
+          tc_fence_after();
+          uint8_t* st = tiles + (size_t)s * C::STAGE_BYTES;
+          const uint64_t da = smem_desc_sw128(st);
+          const uint64_t db = smem_desc_sw128(st + W_TILE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (uint32_t)((i | k) != 0));
+          umma_commit(&empty_bar[s]);
+        }
+        umma_commit(&tmem_full_bar[a]);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int et = threadIdx.x - 64;
+    const int q = warp & 3, row = 32 * q + lane;
+    pdl_wait();
+    int tile_i = 0;
+    for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++tile_i) {
+      const int a = tile_i & 1;
+      const int n0 = (t / tiles_m) * BM, m0 = (t % tiles_m) * BN;
+      const int n = n0 + row;
+      const bool ok = mbar_wait(&tmem_full_bar[a], (tile_i >> 1) & 1);
+      if (!ok) {
+        abort_flag = 1;
+        if (lane == 0) atomicExch(p.status, STATUS_TIMEOUT + 7);
+      }
+      tc_fence_after();
+      epilogue_barrier();
+      if (abort_flag) break;
+      const uint32_t acc = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(a * BN);
+      const int cols = min(BN, M - m0);
+      const bool fast = p.vec_store && n0 + BM <= N;
+      const float b = (p.bias && n < N) ? p.bias[n] : 0.f;
+      if (fast && p.mode == OUT_SWIGLU) {
+        float* ub = reinterpret_cast<float*>(staging);
+        bf16* ob = reinterpret_cast<bf16*>(staging + (size_t)BN * 64 * sizeof(float));
+#pragma unroll 1
+        for (int c0 = 0; c0 < cols; c0 += 16) {
+          float v[16];
+          tmem_ld_16(acc + (uint32_t)c0, v);
+          if (row >= 64) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) ub[(c0 + j) * 64 + (row - 64)] = v[j] + b;
+          }
+        }
+        epilogue_barrier();
+        if (row < 64) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < cols; c0 += 16) {
+            float v[16];
+            tmem_ld_16(acc + (uint32_t)c0, v);
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              ob[(c0 + j) * 64 + row] = __float2bfloat16_rn(silu_mul(v[j] + b, ub[(c0 + j) * 64 + row]));
+          }
+        }
+        tc_fence_before();
+        epilogue_barrier();
+        if (et == 0) mbar_arrive(&tmem_empty_bar[a]);          // the accumulator may be overwritten
+        bf16* dst = (bf16*)p.out + (size_t)m0 * p.ldo + (n0 >> 1);
+        for (int idx = et; idx < cols * 8; idx += 128) {
+          const int mm = idx >> 3, piece = idx & 7;
+          *reinterpret_cast<uint4*>(dst + (size_t)mm * p.ldo + piece * 8) =
+              *reinterpret_cast<const uint4*>(ob + mm * 64 + piece * 8);
+        }
+        epilogue_barrier();                                    // staging is free again
+      } else if (fast && p.mode == OUT_BF16) {
+        bf16* ob = reinterpret_cast<bf16*>(staging);
+#pragma unroll 1
+        for (int c0 = 0; c0 < cols; c0 += 16) {
+          float v[16];
+          tmem_ld_16(acc + (uint32_t)c0, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) ob[(c0 + j) * BM + row] = __float2bfloat16_rn(v[j] + b);
+        }
+        tc_fence_before();
+        epilogue_barrier();
+        if (et == 0) mbar_arrive(&tmem_empty_bar[a]);
+        bf16* dst = (bf16*)p.out + (size_t)m0 * p.ldo + n0;
+        for (int idx = et; idx < cols * 16; idx += 128) {
+          const int mm = idx >> 4, piece = idx & 15;
+          *reinterpret_cast<uint4*>(dst + (size_t)mm * p.ldo + piece * 8) =
+              *reinterpret_cast<const uint4*>(ob + mm * BM + piece * 8);
+        }
+        epilogue_barrier();
+      } else if (fast) {                                       // OUT_F32 / OUT_F32_ACC, 64 token rows at a time
+        float* fb = reinterpret_cast<float*>(staging);
+#pragma unroll 1
+        for (int h0 = 0; h0 < cols; h0 += 64) {
+          const int hc = min(64, cols - h0);
+#pragma unroll 1
+          for (int c0 = 0; c0 < hc; c0 += 16) {
+            float v[16];
+            tmem_ld_16(acc + (uint32_t)(h0 + c0), v);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) fb[(c0 + j) * BM + row] = v[j] + b;
+          }
+          tc_fence_before();
+          epilogue_barrier();
+          if (h0 + 64 >= cols && et == 0) mbar_arrive(&tmem_empty_bar[a]);
+          float* dst = (float*)p.out + (size_t)(m0 + h0) * p.ldo + n0;
+          for (int idx = et; idx < hc * 32; idx += 128 * 4) {
+            float4 nv[4], ov[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int id = idx + u * 128;
+              if (id < hc * 32) {
+                const int mm = id >> 5, piece = id & 31;
+                nv[u] = *reinterpret_cast<const float4*>(fb + mm * BM + piece * 4);
+                if (p.mode == OUT_F32_ACC)
+                  ov[u] = __ldcg(reinterpret_cast<const float4*>(dst + (size_t)mm * p.ldo + piece * 4));
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int id = idx + u * 128;
+              if (id < hc * 32) {
+                const int mm = id >> 5, piece = id & 31;
+                float4 r = nv[u];
+                if (p.mode == OUT_F32_ACC) { r.x += ov[u].x; r.y += ov[u].y; r.z += ov[u].z; r.w += ov[u].w; }
+                *reinterpret_cast<float4*>(dst + (size_t)mm * p.ldo + piece * 4) = r;
+              }
+            }
+          }
+          epilogue_barrier();
+        }
+      } else {
+        // ragged edge or unaligned output: element by element
+        if (p.mode == OUT_SWIGLU) {
+          float* ub = reinterpret_cast<float*>(staging);
+#pragma unroll 1
+          for (int c0 = 0; c0 < cols; c0 += 16) {
+            float v[16];
+            tmem_ld_16(acc + (uint32_t)c0, v);
+            if (row >= 64) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) ub[(c0 + j) * 64 + (row - 64)] = v[j] + b;
+            }
+          }
+          epilogue_barrier();
+          if (row < 64) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < cols; c0 += 16) {
+              float v[16];
+              tmem_ld_16(acc + (uint32_t)c0, v);
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (c0 + j < cols)
+                  ((bf16*)p.out)[(size_t)(m0 + c0 + j) * p.ldo + (n0 >> 1) + row] =
+                      __float2bfloat16_rn(silu_mul(v[j] + b, ub[(c0 + j) * 64 + row]));
+            }
+          }
+        } else {
+#pragma unroll 1
+          for (int c0 = 0; c0 < cols; c0 += 16) {
+            float v[16];
+            tmem_ld_16(acc + (uint32_t)c0, v);
+            if (n < N) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (c0 + j < cols) store_value(p, m0 + c0 + j, n, v[j] + b);
+            }
+          }
+        }
+        tc_fence_before();
+        epilogue_barrier();
+        if (et == 0) mbar_arrive(&tmem_empty_bar[a]);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag && threadIdx.x == 0) {
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------- CTA-pair kernel (prompts)
+// Two CTAs of a cluster (two SMs) compute one 256 x 256 tile with tcgen05.mma.cta_group::2:
+// each CTA stages 128 weight rows (its half of A) and 128 token rows (its half of B) per
+// k-block, 32 KB for 128 x 256 x 64 multiply-adds of its own, half the shared-memory traffic
+// per flop of a lone CTA, so five stages cover the load latency.  The leader (cluster rank 0)
+// issues the MMAs for both; its "full" barriers count the bytes of both CTAs' TMA loads, its
+// commits release the stages and publish the accumulator in both CTAs.  Each CTA keeps the
+// 128 accumulator rows of its own weight rows in its tensor memory (2 x 256 columns, double
+// buffered) and runs its own epilogue.  Persistent: one pair per two SMs walks the tiles.
+struct PairCfg {
+  static constexpr int BNP = 256;                         // tokens per tile
+  static constexpr int X_TILE_BYTES = (BNP / 2) * BK * 2; // this CTA's half of the token rows
+  static constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES;
+  static constexpr int STAGES = 5;
+  static constexpr int STAGING_BYTES = 128 * 64 * 4 + 128 * 64 * 2;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024;
+};
+
+__global__ void __launch_bounds__(192)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                    const GemmParams p) {
+  using C = PairCfg;
+  constexpr int BNP = C::BNP;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t full_bar[C::STAGES], empty_bar[C::STAGES], tmem_full_bar[2], tmem_empty_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int abort_flag;
+  pdl_trigger();
+
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* staging = tiles + (size_t)C::STAGES * C::STAGE_BYTES;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();                // 0: leader
+  const int M = p.M, N = p.N, nkb = p.total_kb;
+  const int tiles_m = (M + BNP - 1) / BNP, tiles_n = (N + 2 * BM - 1) / (2 * BM);
+  const int n_tiles = tiles_m * tiles_n;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);       // the leader's producer arrives; both CTAs' loads add bytes
+      mbar_init(&empty_bar[s], 1);      // one multicast commit
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full_bar[a], 1);  // one multicast commit
+      mbar_init(&tmem_empty_bar[a], 2); // the epilogues of both CTAs (only the leader's copy is used)
+    }
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&tmem_slot, C::TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                   // both CTAs' barriers are initialised before anyone signals them
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      pdl_wait();
+      int it = 0;
+      for (int t = pair; t < n_tiles && !abort_flag; t += n_pairs) {
+        const int n0 = (t / tiles_m) * 2 * BM + (int)rank * BM;          // this CTA's weight rows
+        const int m0 = (t % tiles_m) * BNP + (int)rank * (BNP / 2);      // this CTA's half of the token rows
+        for (int i = 0; i < nkb; ++i, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
+            abort_flag = 1;
+            atomicExch(p.status, STATUS_TIMEOUT + 8);
+            break;
+          }
+          if (abort_flag) break;
+          uint8_t* st = tiles + (size_t)s * C::STAGE_BYTES;
+          if (rank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * C::STAGE_BYTES);
+          tma_load_2d_pair(st, &tmap_w, i * BK, n0, &full_bar[s]);
+          tma_load_2d_pair(st + W_TILE_BYTES, &tmap_x, i * BK, m0, &full_bar[s]);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (rank == 0 && elect_one()) {
+      constexpr uint32_t idesc = idesc_bf16_f32(2 * BM, BNP);
+      int it = 0, tile_i = 0;
+      for (int t = pair; t < n_tiles && !abort_flag; t += n_pairs, ++tile_i) {
+        const int a = tile_i & 1;
+        if (!mbar_wait(&tmem_empty_bar[a], ((tile_i >> 1) & 1) ^ 1)) {
+          abort_flag = 1;
+          atomicExch(p.status, STATUS_TIMEOUT + 9);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t acc = tmem_base + (uint32_t)(a * BNP);
+        for (int i = 0; i < nkb; ++i, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], ph)) {
+            abort_flag = 1;
+            atomicExch(p.status, STATUS_TIMEOUT + 10);
+            break;
+          }
+          if (abort_flag) break;
+          tc_fence_after();
+          uint8_t* st = tiles + (size_t)s * C::STAGE_BYTES;
+          const uint64_t da = smem_desc_sw128(st);
+          const uint64_t db = smem_desc_sw128(st + W_TILE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16_pair(acc, da + 2 * k, db + 2 * k, idesc, (uint32_t)((i | k) != 0));
+          umma_commit_pair(&empty_bar[s]);
+        }
+        umma_commit_pair(&tmem_full_bar[a]);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int et = threadIdx.x - 64;
+    const int q = warp & 3, row = 32 * q + lane;
+    pdl_wait();
+    int tile_i = 0;
+    for (int t = pair; t < n_tiles; t += n_pairs, ++tile_i) {
+      const int a = tile_i & 1;
+      const int n0 = (t / tiles_m) * 2 * BM + (int)rank * BM, m0 = (t % tiles_m) * BNP;
+      const int n = n0 + row;
+      const bool ok = mbar_wait(&tmem_full_bar[a], (tile_i >> 1) & 1);
+      if (!ok) {
+        abort_flag = 1;
+        if (lane == 0) atomicExch(p.status, STATUS_TIMEOUT + 11);
+      }
+      tc_fence_after();
+      epilogue_barrier();
+      if (abort_flag) break;
+      const uint32_t acc = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(a * BNP);
+      const int cols = max(0, min(BNP, M - m0));
+      const bool fast = p.vec_store && n0 + BM <= N;
+      const float b = (p.bias && n < N) ? p.bias[n] : 0.f;
+      const bool f32out = p.mode == OUT_F32 || p.mode == OUT_F32_ACC;
+      const int RC = (f32out || p.mode == OUT_SWIGLU) ? 64 : 128;   // token rows staged at a time
+      for (int h0 = 0; h0 < BNP; h0 += RC) {
+        const int hc = max(0, min(RC, cols - h0));
+        const bool last = h0 + RC >= BNP;
+        if (hc > 0 && fast && p.mode == OUT_SWIGLU) {
+          // g (accumulator rows 0-63) and u (rows 64-127) of 64 token rows go to shared memory
+          // in 32-bit; then all 128 threads share the 64 x 64 activations, two features each.
+          float* gs = reinterpret_cast<float*>(staging);          // [64][64]
+          float* us = gs + 64 * 64;                               // [64][64]
+          float* mine = row < 64 ? gs + row : us + (row - 64);
+#pragma unroll 1
+          for (int c0 = 0; c0 < hc; c0 += 16) {
+            float v[16];
+            tmem_ld_16(acc + (uint32_t)(h0 + c0), v);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) mine[(c0 + j) * 64] = v[j] + b;
+          }
+          tc_fence_before();
+          epilogue_barrier();
+          if (last && et == 0) mbar_arrive_leader(&tmem_empty_bar[a]);
+          bf16* dst = (bf16*)p.out + (size_t)(m0 + h0) * p.ldo + (n0 >> 1);
+          for (int idx = et; idx < hc * 32; idx += 128) {
+            const int mm = idx >> 5, f = (idx & 31) * 2;
+            const float2 g2 = *reinterpret_cast<const float2*>(gs + mm * 64 + f);
+            const float2 u2 = *reinterpret_cast<const float2*>(us + mm * 64 + f);
+            // the result is rounded to bfloat16: the fast exponential is exact enough here
+            const float r0 = g2.x / (1.0f + __expf(-g2.x)) * u2.x;
+            const float r1 = g2.y / (1.0f + __expf(-g2.y)) * u2.y;
+            *reinterpret_cast<__nv_bfloat162*>(dst + (size_t)mm * p.ldo + f) = __floats2bfloat162_rn(r0, r1);
+          }
+          epilogue_barrier();
+        } else if (hc > 0 && fast && p.mode == OUT_BF16) {
+          bf16* ob = reinterpret_cast<bf16*>(staging);
+#pragma unroll 1
+          for (int c0 = 0; c0 < hc; c0 += 16) {
+            float v[16];
+            tmem_ld_16(acc + (uint32_t)(h0 + c0), v);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) ob[(c0 + j) * BM + row] = __float2bfloat16_rn(v[j] + b);
+          }
+          tc_fence_before();
+          epilogue_barrier();
+          if (last && et == 0) mbar_arrive_leader(&tmem_empty_bar[a]);
+          bf16* dst = (bf16*)p.out + (size_t)(m0 + h0) * p.ldo + n0;
+          for (int idx = et; idx < hc * 16; idx += 128) {
+            const int mm = idx >> 4, piece = idx & 15;
+            *reinterpret_cast<uint4*>(dst + (size_t)mm * p.ldo + piece * 8) =
+                *reinterpret_cast<const uint4*>(ob + mm * BM + piece * 8);
+          }
+          epilogue_barrier();
+        } else if (hc > 0 && fast) {
+          float* fb = reinterpret_cast<float*>(staging);
+#pragma unroll 1
+          for (int c0 = 0; c0 < hc; c0 += 16) {
+            float v[16];
+            tmem_ld_16(acc + (uint32_t)(h0 + c0), v);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) fb[(c0 + j) * BM + row] = v[j] + b;
+          }
+          tc_fence_before();
+          epilogue_barrier();
+          if (last && et == 0) mbar_arrive_leader(&tmem_empty_bar[a]);
+          float* dst = (float*)p.out + (size_t)(m0 + h0) * p.ldo + n0;
+          for (int idx = et; idx < hc * 32; idx += 128 * 4) {
+            float4 nv[4], ov[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int id = idx + u * 128;
+              if (id < hc * 32) {
+                const int mm = id >> 5, piece = id & 31;
+                nv[u] = *reinterpret_cast<const float4*>(fb + mm * BM + piece * 4);
+                if (p.mode == OUT_F32_ACC)
+                  ov[u] = __ldcg(reinterpret_cast<const float4*>(dst + (size_t)mm * p.ldo + piece * 4));
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int id = idx + u * 128;
+              if (id < hc * 32) {
+                const int mm = id >> 5, piece = id & 31;
+                float4 r = nv[u];
+                if (p.mode == OUT_F32_ACC) { r.x += ov[u].x; r.y += ov[u].y; r.z += ov[u].z; r.w += ov[u].w; }
+                *reinterpret_cast<float4*>(dst + (size_t)mm * p.ldo + piece * 4) = r;
+              }
+            }
+          }
+          epilogue_barrier();
+        } else {
+          // nothing to store from this chunk, a ragged edge or an unaligned output: element by element
+          if (hc > 0 && p.mode == OUT_SWIGLU) {
+            float* ub = reinterpret_cast<float*>(staging);
+#pragma unroll 1
+            for (int c0 = 0; c0 < hc; c0 += 16) {
+              float v[16];
+              tmem_ld_16(acc + (uint32_t)(h0 + c0), v);
+              if (row >= 64) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) ub[(c0 + j) * 64 + (row - 64)] = v[j] + b;
+              }
+            }
+            epilogue_barrier();
+            if (row < 64 && n + 64 < N) {
+#pragma unroll 1
+              for (int c0 = 0; c0 < hc; c0 += 16) {
+                float v[16];
+                tmem_ld_16(acc + (uint32_t)(h0 + c0), v);
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                  if (c0 + j < hc)
+                    ((bf16*)p.out)[(size_t)(m0 + h0 + c0 + j) * p.ldo + (n0 >> 1) + row] =
+                        __float2bfloat16_rn(silu_mul(v[j] + b, ub[(c0 + j) * 64 + row]));
+              }
+            }
+          } else if (hc > 0) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < hc; c0 += 16) {
+              float v[16];
+              tmem_ld_16(acc + (uint32_t)(h0 + c0), v);
+              if (n < N) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                  if (c0 + j < hc) store_value(p, m0 + h0 + c0 + j, n, v[j] + b);
+              }
+            }
+          }
+          tc_fence_before();
+          epilogue_barrier();
+          if (last && et == 0) mbar_arrive_leader(&tmem_empty_bar[a]);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag && threadIdx.x == 0) {
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  __syncthreads();
+  cluster_sync_all();                   // nobody leaves while its partner may still use its memory
+  if (warp == 1) tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
 }
 
 // out = epilogue(sum over splits of the partial tiles (+ bias)), in split order.
@@ -373,11 +1057,22 @@ struct WKeyHash {
 std::mutex g_wmap_mutex;
 std::unordered_map<WKey, CUtensorMap, WKeyHash> g_wmaps;   // weights do not move: their maps are made once
 
+// GIBBS_B200_WIDE_TILES=1 puts prompts on 128 x 256 single-CTA tiles (for comparison runs; slower).
+int gb_wide_tiles() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("GIBBS_B200_WIDE_TILES");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v;
+}
+
 int pick_bn(int M) {
   if (M <= 16) return 16;
   if (M <= 32) return 32;
   if (M <= 64) return 64;
-  return 128;
+  if (M <= 128 || !gb_wide_tiles()) return 128;
+  return 256;
 }
 
 void plan(int M, int N, int K, int* bn, int* splits, int* kb_per_split) {
@@ -407,6 +1102,80 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cu
   dim3 grid(gb_div_up(p.N, BM), gb_div_up(p.M, BN), p.splits);
   gb_launch(gemm_tc_kernel<BN>, dim3(grid), dim3(192), Cfg<BN>::SMEM_BYTES, stream, tw, tx, p);
   return GB_OK;
+}
+
+template <int BN>
+int launch_persistent(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    GB_CUDA(cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 PCfg<BN>::SMEM_BYTES));
+    attr_set = true;
+  }
+  static int n_sm = 0;
+  if (n_sm == 0) {
+    int dev = 0;
+    GB_CUDA(cudaGetDevice(&dev));
+    GB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+  }
+  const long long tiles = (long long)gb_div_up(p.N, BM) * gb_div_up(p.M, BN);
+  const int grid = (int)(tiles < n_sm ? tiles : n_sm);
+  gb_launch(gemm_tc_persistent_kernel<BN>, dim3(grid), dim3(192), PCfg<BN>::SMEM_BYTES, stream, tw, tx, p);
+  return GB_OK;
+}
+
+int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    GB_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 PairCfg::SMEM_BYTES));
+    attr_set = true;
+  }
+  static int n_sm = 0;
+  if (n_sm == 0) {
+    int dev = 0;
+    GB_CUDA(cudaGetDevice(&dev));
+    GB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+  }
+  const long long tiles = (long long)gb_div_up(p.N, 2 * BM) * gb_div_up(p.M, PairCfg::BNP);
+  const int pairs = (int)(tiles < n_sm / 2 ? tiles : n_sm / 2);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = PairCfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = gb_pdl_enabled() ? 2 : 1;
+  GB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, tw, tx, p));
+  return GB_OK;
+}
+
+// GIBBS_B200_PAIR=0 keeps prompts off the CTA-pair kernel (for comparison runs).
+int gb_pair() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("GIBBS_B200_PAIR");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v;
+}
+
+// GIBBS_B200_PERSISTENT=1 lets the single-CTA persistent kernel take prompts the pair kernel
+// does not (for comparison runs; it measured slower than two one-tile CTAs per SM).
+int gb_persistent() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("GIBBS_B200_PERSISTENT");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v;
 }
 
 }  // namespace
@@ -480,13 +1249,23 @@ GB_API int gb_linear_tc(const void* X, long long ldx, const void* W, long long l
   p.prefetch_bytes = decode_like ? (prefetch_bytes > (64ll << 20) ? (64ll << 20) : prefetch_bytes) : 0;
   if (((uintptr_t)p.prefetch & 15) != 0) p.prefetch = nullptr;
   p.stream_weights = (decode_like && (flags & 1)) ? 1 : 0;   // flags bit 0: evict-first hint for the weights
+  p.vec_store = (((uintptr_t)out & 15) == 0 && (ldo * (mode == OUT_BF16 || mode == OUT_SWIGLU ? 2 : 4)) % 16 == 0) ? 1 : 0;
   p.status = status;
   int rc;
-  switch (bn) {
-    case 16: rc = launch<16>(tw, tx, p, stream); break;
-    case 32: rc = launch<32>(tw, tx, p, stream); break;
-    case 64: rc = launch<64>(tw, tx, p, stream); break;
-    default: rc = launch<128>(tw, tx, p, stream); break;
+  const long long n_tiles = (long long)gb_div_up(N, BM) * gb_div_up(M, bn);
+  const long long pair_tiles = (long long)gb_div_up(N, 2 * BM) * gb_div_up(M, PairCfg::BNP);
+  if (bn == 128 && splits == 1 && M >= 192 && pair_tiles >= 32 && gb_pair()) {
+    rc = launch_pair(tw, tx, p, stream);
+  } else if (bn == 128 && splits == 1 && n_tiles > 148 && gb_persistent()) {
+    rc = launch_persistent<128>(tw, tx, p, stream);
+  } else {
+    switch (bn) {
+      case 16: rc = launch<16>(tw, tx, p, stream); break;
+      case 32: rc = launch<32>(tw, tx, p, stream); break;
+      case 64: rc = launch<64>(tw, tx, p, stream); break;
+      case 256: rc = launch<256>(tw, tx, p, stream); break;
+      default: rc = launch<128>(tw, tx, p, stream); break;
+    }
   }
   if (rc != GB_OK) return rc;
   GB_CHECK_LAUNCH("gb_linear_tc");
@@ -574,12 +1353,14 @@ GB_API int gb_linear_tc_no_alloc(const void* X, long long ldx, const void* W, lo
   p.ws = ws;
   p.prefetch = nullptr; p.prefetch_bytes = 0;
   p.stream_weights = M <= 64 ? 1 : 0;
+  p.vec_store = (((uintptr_t)out & 15) == 0 && (ldo * (mode == OUT_BF16 || mode == OUT_SWIGLU ? 2 : 4)) % 16 == 0) ? 1 : 0;
   p.status = status;
   int rc;
   switch (bn) {
     case 16: rc = launch<16>(tw, tx, p, stream); break;
     case 32: rc = launch<32>(tw, tx, p, stream); break;
     case 64: rc = launch<64>(tw, tx, p, stream); break;
+    case 256: rc = launch<256>(tw, tx, p, stream); break;
     default: rc = launch<128>(tw, tx, p, stream); break;
   }
   if (rc != GB_OK) return rc;

@@ -207,7 +207,8 @@ def measure_decode_e2e(generator, batch: int, prompt_len: int, steps: int, warmu
     the picked ids back to the host."""
     rng = np.random.default_rng(seed)
     sched: Scheduler = generator.scheduler(stop_at_eos=False)
-    params = SamplingParams(temperature=0.0, max_new_tokens=warmup + steps + 4)
+    # prompts finish at different steps: leave room so that nobody reaches max_new_tokens while timed
+    params = SamplingParams(temperature=0.0, max_new_tokens=warmup + steps + 4 * batch + 16)
     for _ in range(batch):
         sched.submit(rng.integers(0, generator.engine.vocab_size, prompt_len).tolist(), params)
     while any(not s.decoding for s in sched.sequences.values()):

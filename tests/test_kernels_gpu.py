@@ -96,7 +96,9 @@ def test_linear_simt(m, n, k, pair):
     _close(acc, res.double() + ar @ wr.T, "float32" if ad == "float32" else "float32", scale=want.abs().max().item())
 
 
-@pytest.mark.parametrize("m,n,k", SHAPES + [(2048, 512, 2048), (1, 65536 // 8, 2048), (257, 130, 8)])
+# the last three have more than 148 tiles: the persistent kernel, with ragged edges in both directions
+@pytest.mark.parametrize("m,n,k", SHAPES + [(2048, 512, 2048), (1, 65536 // 8, 2048), (257, 130, 8),
+                                            (2048, 2048, 256), (1500, 1664, 200), (1281, 2050, 72)])
 def test_linear_tensor_cores(m, n, k):
     """bf16 x bf16 on tcgen05: bf16 store, f32 store, f32 accumulate, with and
     without bias, including the split-K sizes."""
@@ -556,7 +558,7 @@ def test_attention_tensor_cores_far_key_and_tile_edges():
 
 
 @pytest.mark.parametrize("m,f,k", [(1, 64, 64), (8, 192, 96), (8, 8192, 2048), (64, 256, 2048), (300, 448, 136),
-                                   (2, 128, 4096)])
+                                   (2, 128, 4096), (2048, 1280, 128), (1300, 1024, 200)])
 @pytest.mark.parametrize("use_bias", [False, True])
 def test_linear_tensor_cores_swiglu_epilogue(m, f, k, use_bias):
     """gate and up as one product whose epilogue applies (g * sigmoid(g)) * u,
