@@ -5,10 +5,10 @@
 // The rows of a CTA's tile are (token, query head of one kv group) pairs, so
 // the keys and values of a kv head are read from the pages once for all the
 // query heads that share them.  A CTA walks the visible keys in tiles of 64
-// absolute positions (cp.async into double-buffered shared memory, looked up
+// absolute positions (cp.async into multi-buffered shared memory, looked up
 // page by page), computes S = Q K^T and O += P V with mma.sync m16n8k16, and
 // keeps the softmax statistics (running maximum and sum) in 32-bit.
-//   NW = 4: 64 rows per CTA (prompt portions);  NW = 1: 16 rows (decoding).
+//   prompts: 64 rows per CTA, 16 per warp;  decoding: 16 rows per CTA, the four warps split each tile's keys.
 // With splits > 1 (decoding against long contexts) the key range is divided
 // among CTAs; each writes an unnormalised partial output with its maximum and
 // sum to a workspace and a second kernel merges them in split order.
@@ -71,26 +71,44 @@ struct AttnParams {
   int* status;
 };
 
-// Row stride of the shared tiles: HD bf16 plus one 16-byte chunk, an odd number
-// of chunks, so that the eight rows an ldmatrix phase reads fall in distinct banks.
+// Layout of the shared tiles.  Head sizes that are multiples of 64 store rows back to back
+// and XOR the 16-byte chunk index with the row (chunk ^ (row & 7)), others pad each row by
+// one chunk (an odd number of chunks per row); either way the eight rows an ldmatrix phase
+// reads fall in distinct banks.
 template <int HD> struct Tile {
   static constexpr int CHUNKS = HD / 8;
-  static constexpr int STRIDE = HD + 8;   // in bf16
+  static constexpr bool SWIZZLED = (HD % 64) == 0;
+  static constexpr int STRIDE = SWIZZLED ? HD : HD + 8;   // in bf16
+  // element offset of (row, col) for col a multiple of 8
+  __device__ static __forceinline__ int at(int row, int col) {
+    return SWIZZLED ? row * STRIDE + ((((col >> 3) ^ (row & 7)) << 3)) : row * STRIDE + col;
+  }
 };
 
-template <int HD, int NW>
+// Tiles of keys in flight: prompts double-buffer; decoding CTAs are a single warp that
+// waits on memory, so they keep one more tile on the way.
+template <bool KSPLIT> struct Depth { static constexpr int STAGES = KSPLIT ? 3 : 2; };
+
+// KSPLIT = false: NW warps, 16 query rows each, every warp walks all 64 keys of a tile.
+// KSPLIT = true (decoding): ONE 16-row query tile shared by the NW = 4 warps; warp w takes keys
+// 16w .. 16w+15 of every tile with its own running maximum, sum and output, and the four
+// partial states are merged through shared memory at the end.  The warps of an SM then have
+// something to overlap their memory waits with.
+template <int HD, int NW, bool KSPLIT>
 __global__ void __launch_bounds__(32 * NW)
 attention_tc_kernel(const AttnParams p) {
   pdl_trigger();
   pdl_wait();
-  constexpr int BQ = 16 * NW;
-  constexpr int STRIDE = Tile<HD>::STRIDE, CHUNKS = Tile<HD>::CHUNKS;
+  constexpr int BQ = KSPLIT ? 16 : 16 * NW;
+  constexpr int NN = KSPLIT ? 2 : KT / 8;                    // 8-key column tiles per warp and key tile
+  using TL = Tile<HD>;
+  constexpr int STRIDE = TL::STRIDE, CHUNKS = TL::CHUNKS, NS = Depth<KSPLIT>::STAGES;
   constexpr int NT = 32 * NW;
   extern __shared__ __align__(16) uint8_t smem[];
   bf16* sq = reinterpret_cast<bf16*>(smem);                  // [BQ][STRIDE]
-  bf16* sk = sq + BQ * STRIDE;                               // [2][KT][STRIDE]
-  bf16* sv = sk + 2 * KT * STRIDE;                           // [2][KT][STRIDE]
-  __shared__ long long row_off[2][KT];
+  bf16* sk = sq + BQ * STRIDE;                               // [NS][KT][STRIDE]
+  bf16* sv = sk + NS * KT * STRIDE;                          // [NS][KT][STRIDE]
+  __shared__ long long row_off[NS + 1][KT];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int group = p.heads / p.kv_heads;
@@ -127,45 +145,69 @@ attention_tc_kernel(const AttnParams p) {
     const int tl = row / group, g = row - tl * group;
     const bool valid = tl < n_tok;
     const bf16* src = p.q + (size_t)(row0 + (valid ? tl : 0)) * p.ldq + (size_t)(kvh * group + g) * HD + c * 8;
-    cp_async_16(sq + row * STRIDE + c * 8, src, valid);
+    cp_async_16(sq + TL::at(row, c * 8), src, valid);
   }
   // Where each of a tile's 64 keys lies in the pages (element offset of its row, -1: not
-  // visible) is worked out once per tile and row, not once per 16-byte piece: row_off[t & 1]
-  // belongs to tile t.  It is written one iteration before the tile's loads are issued; the
-  // barrier that ends every iteration makes it visible.
-  auto locate = [&](int t) {
-    for (int row = tid; row < KT; row += NT) {
+  // visible) is worked out once per tile and row, not once per 16-byte piece: slot t % (NS + 1)
+  // of row_off belongs to tile t.  It is written an iteration before the tile's loads are
+  // issued; the barrier that ends every iteration makes it visible.
+  // The page ids are read early (locate_begin) and turned into offsets late (locate_end), so
+  // that the block-table reads of a one-warp CTA overlap the work on the current tile.
+  constexpr int RPT = (KT + NT - 1) / NT;                    // rows per thread
+  int pending_page[RPT], pending_tile = -1;
+  auto locate_begin = [&](int t) {
+    pending_tile = t;
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+      const int row = tid + i * NT;
       const int j = t * KT + row;
-      long long off = -1;
-      if (j < hi_all && j >= lo_all) {
-        const int blk = j / p.page_size;
-        const int page = bt[blk];
-        if (page < 0 || page >= p.n_pages)
-          atomicExch(p.status, 2);
-        else
-          off = (((long long)page * p.kv_heads + kvh) * p.page_size + (j - blk * p.page_size)) * HD;
-      }
-      row_off[t & 1][row] = off;
+      pending_page[i] = (row < KT && j < hi_all && j >= lo_all) ? bt[j / p.page_size] : -2;   // -2: not visible
     }
+  };
+  auto locate_end = [&]() {
+    if (pending_tile < 0) return;
+    const int t = pending_tile;
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+      const int row = tid + i * NT;
+      if (row >= KT) continue;
+      const int j = t * KT + row;
+      const int page = pending_page[i];
+      long long off = -1;
+      if (page >= 0 && page < p.n_pages)
+        off = (((long long)page * p.kv_heads + kvh) * p.page_size + j % p.page_size) * HD;
+      else if (page != -2)
+        atomicExch(p.status, 2);
+      row_off[t % (NS + 1)][row] = off;
+    }
+    pending_tile = -1;
+  };
+  auto locate = [&](int t) {
+    locate_begin(t);
+    locate_end();
   };
   auto load_kv = [&](int t, int buf) {
     for (int idx = tid; idx < KT * CHUNKS; idx += NT) {
       const int row = idx / CHUNKS, c = idx - row * CHUNKS;
-      const long long off = row_off[t & 1][row];
+      const long long off = row_off[t % (NS + 1)][row];
       const bool valid = off >= 0;
       const size_t src = valid ? (size_t)off + c * 8 : 0;
-      cp_async_16(sk + (buf * KT + row) * STRIDE + c * 8, p.k_pages + src, valid);
-      cp_async_16(sv + (buf * KT + row) * STRIDE + c * 8, p.v_pages + src, valid);
+      cp_async_16(sk + buf * KT * STRIDE + TL::at(row, c * 8), p.k_pages + src, valid);
+      cp_async_16(sv + buf * KT * STRIDE + TL::at(row, c * 8), p.v_pages + src, valid);
     }
   };
-  if (t_begin < t_end) locate(t_begin);
-  if (t_begin + 1 < t_end) locate(t_begin + 1);
+  for (int i = 0; i < NS; ++i)
+    if (t_begin + i < t_end) locate(t_begin + i);
   __syncthreads();
-  if (t_begin < t_end) load_kv(t_begin, 0);
-  cp_async_commit();
+  for (int i = 0; i < NS - 1; ++i) {       // one commit group per tile, also for tiles that do not exist
+    if (t_begin + i < t_end) load_kv(t_begin + i, i);
+    cp_async_commit();
+  }
 
   // this thread's two rows: g0 = lane/4 and g0 + 8 of the warp's 16
-  const int rloc[2] = {warp * 16 + (lane >> 2), warp * 16 + (lane >> 2) + 8};
+  const int wrow = KSPLIT ? 0 : warp * 16;                   // first query row of this warp
+  const int kbase = KSPLIT ? warp * 16 : 0;                  // first key (within a tile) of this warp
+  const int rloc[2] = {wrow + (lane >> 2), wrow + (lane >> 2) + 8};
   int rpos[2];
   bool rvalid[2];
 #pragma unroll
@@ -183,31 +225,30 @@ attention_tc_kernel(const AttnParams p) {
 
   uint32_t qf[HD / 16][4];
   for (int t = t_begin; t < t_end; ++t) {
-    const int buf = (t - t_begin) & 1;
-    if (t + 1 < t_end) load_kv(t + 1, buf ^ 1);
+    const int buf = (t - t_begin) % NS;
+    if (t + NS - 1 < t_end) load_kv(t + NS - 1, (t - t_begin + NS - 1) % NS);
     cp_async_commit();
-    cp_async_wait<1>();
+    if (t + NS < t_end) locate_begin(t + NS);      // page ids of a later tile: needed after this tile's work
+    cp_async_wait<NS - 1>();               // all but the NS-1 newest groups: tile t (and Q) have landed
     __syncthreads();
-    // row_off[t & 1] was last read when tile t was requested, before the barrier above
-    if (t + 2 < t_end) locate(t + 2);
     if (t == t_begin) {
 #pragma unroll
       for (int kk = 0; kk < HD / 16; ++kk)
-        ldmatrix_x4(qf[kk], sq + (warp * 16 + (lane & 15)) * STRIDE + kk * 16 + (lane >> 4) * 8);
+        ldmatrix_x4(qf[kk], sq + TL::at(wrow + (lane & 15), kk * 16 + (lane >> 4) * 8));
     }
-    // S = Q K^T for 64 keys
-    float s[KT / 8][4];
+    // S = Q K^T for this warp's keys of the tile
+    float s[NN][4];
 #pragma unroll
-    for (int n = 0; n < KT / 8; ++n)
+    for (int n = 0; n < NN; ++n)
 #pragma unroll
       for (int i = 0; i < 4; ++i) s[n][i] = 0.f;
     const bf16* kb = sk + buf * KT * STRIDE;
 #pragma unroll
     for (int kk = 0; kk < HD / 16; ++kk) {
 #pragma unroll
-      for (int n2 = 0; n2 < KT / 16; ++n2) {
+      for (int n2 = 0; n2 < NN / 2; ++n2) {
         uint32_t b[4];
-        ldmatrix_x4(b, kb + (n2 * 16 + (lane & 7) + ((lane >> 4) << 3)) * STRIDE + kk * 16 + ((lane >> 3) & 1) * 8);
+        ldmatrix_x4(b, kb + TL::at(kbase + n2 * 16 + (lane & 7) + ((lane >> 4) << 3), kk * 16 + ((lane >> 3) & 1) * 8));
         mma_bf16(s[2 * n2], qf[kk], b[0], b[1]);
         mma_bf16(s[2 * n2 + 1], qf[kk], b[2], b[3]);
       }
@@ -215,11 +256,11 @@ attention_tc_kernel(const AttnParams p) {
     // scale, mask, running maximum
     float m_new[2] = {m_run[0], m_run[1]};
 #pragma unroll
-    for (int n = 0; n < KT / 8; ++n) {
+    for (int n = 0; n < NN; ++n) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int ri = i >> 1;
-        const int j = t * KT + n * 8 + (lane & 3) * 2 + (i & 1);
+        const int j = t * KT + kbase + n * 8 + (lane & 3) * 2 + (i & 1);
         const bool vis = rvalid[ri] && j <= rpos[ri] && (p.window <= 0 || j + p.window > rpos[ri]);
         const float v = vis ? s[n][i] * p.scale_log2 : -INFINITY;
         s[n][i] = v;
@@ -243,7 +284,7 @@ attention_tc_kernel(const AttnParams p) {
     // P = exp2(S - m), O += P V
     const bf16* vb = sv + buf * KT * STRIDE;
 #pragma unroll
-    for (int kk = 0; kk < KT / 16; ++kk) {
+    for (int kk = 0; kk < NN / 2; ++kk) {
       uint32_t a[4];
       float pv[2][4];
 #pragma unroll
@@ -262,12 +303,14 @@ attention_tc_kernel(const AttnParams p) {
 #pragma unroll
       for (int n2 = 0; n2 < HD / 16; ++n2) {
         uint32_t b[4];
-        ldmatrix_x4_trans(b, vb + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + n2 * 16 + (lane >> 4) * 8);
+        ldmatrix_x4_trans(b, vb + TL::at(kbase + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, n2 * 16 + (lane >> 4) * 8));
         mma_bf16(o[2 * n2], a, b[0], b[1]);
         mma_bf16(o[2 * n2 + 1], a, b[2], b[3]);
       }
     }
-    __syncthreads();   // everyone is done with this buffer before it is refilled
+    // slot (t + NS) % (NS + 1) held tile t - 1, whose loads were requested two barriers ago
+    locate_end();
+    __syncthreads();   // everyone is done with this buffer before it is refilled; offsets are visible
   }
   cp_async_wait<0>();
 
@@ -276,6 +319,54 @@ attention_tc_kernel(const AttnParams p) {
   for (int ri = 0; ri < 2; ++ri) {
     l_run[ri] += __shfl_xor_sync(0xffffffffu, l_run[ri], 1);
     l_run[ri] += __shfl_xor_sync(0xffffffffu, l_run[ri], 2);
+  }
+  if (KSPLIT) {
+    // merge the four warps' states: rows 0..15, in warp order
+    float* pm = reinterpret_cast<float*>(sk);                // [NW][16] maxima
+    float* pl = pm + NW * 16;                                // [NW][16] sums
+    float* po = pl + NW * 16;                                // [NW][16][HD] outputs
+    __syncthreads();                                         // the key tiles are no longer read
+#pragma unroll
+    for (int ri = 0; ri < 2; ++ri) {
+      const int rr = (lane >> 2) + 8 * ri;
+      if ((lane & 3) == 0) {
+        pm[warp * 16 + rr] = m_run[ri];
+        pl[warp * 16 + rr] = l_run[ri];
+      }
+#pragma unroll
+      for (int n = 0; n < HD / 8; ++n)
+        *reinterpret_cast<float2*>(po + ((size_t)warp * 16 + rr) * HD + n * 8 + (lane & 3) * 2) =
+            make_float2(o[n][2 * ri], o[n][2 * ri + 1]);
+    }
+    __syncthreads();
+    for (int idx = tid; idx < 16 * HD; idx += NT) {
+      const int rr = idx / HD, d = idx - rr * HD;
+      const int tl = rr / group, g = rr - tl * group;
+      if (tl >= n_tok) continue;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) M = fmaxf(M, pm[w * 16 + rr]);
+      float L = 0.f, acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+        const float mw = pm[w * 16 + rr];
+        const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+        L += f * pl[w * 16 + rr];
+        acc += f * po[((size_t)w * 16 + rr) * HD + d];
+      }
+      const int trow = row0 + tl, h = kvh * group + g;
+      if (p.splits == 1) {
+        p.out[(size_t)trow * p.ldo + (size_t)h * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+      } else {
+        const size_t prow = (size_t)z * p.n_tokens * p.heads + (size_t)trow * p.heads + h;
+        p.part_o[prow * HD + d] = acc;
+        if (d == 0) {
+          p.part_ml[prow * 2] = M;
+          p.part_ml[prow * 2 + 1] = L;
+        }
+      }
+    }
+    return;
   }
 #pragma unroll
   for (int ri = 0; ri < 2; ++ri) {
@@ -330,30 +421,32 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
   }
 }
 
-template <int HD, int NW>
+template <int HD, bool KSPLIT>
 int launch(const AttnParams& p, int n_tiles, cudaStream_t stream) {
-  constexpr int smem = (16 * NW + 4 * KT) * Tile<HD>::STRIDE * 2;
+  constexpr int NW = 4;
+  constexpr int smem = ((KSPLIT ? 16 : 64) + 2 * Depth<KSPLIT>::STAGES * KT) * Tile<HD>::STRIDE * 2;
   static bool attr_set = false;
   if (!attr_set && smem > 48 * 1024) {
-    GB_CUDA(cudaFuncSetAttribute(attention_tc_kernel<HD, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    GB_CUDA(cudaFuncSetAttribute(attention_tc_kernel<HD, NW, KSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 smem));
     attr_set = true;
   }
   dim3 grid(n_tiles, p.kv_heads, p.splits);
-  gb_launch(attention_tc_kernel<HD, NW>, dim3(grid), dim3(32 * NW), smem, stream, p);
+  gb_launch(attention_tc_kernel<HD, NW, KSPLIT>, dim3(grid), dim3(32 * NW), smem, stream, p);
   return GB_OK;
 }
 
-template <int NW>
+template <bool KSPLIT>
 int dispatch_hd(const AttnParams& p, int hd, int n_tiles, cudaStream_t stream) {
   switch (hd) {
-    case 16: return launch<16, NW>(p, n_tiles, stream);
-    case 32: return launch<32, NW>(p, n_tiles, stream);
-    case 48: return launch<48, NW>(p, n_tiles, stream);
-    case 64: return launch<64, NW>(p, n_tiles, stream);
-    case 80: return launch<80, NW>(p, n_tiles, stream);
-    case 96: return launch<96, NW>(p, n_tiles, stream);
-    case 112: return launch<112, NW>(p, n_tiles, stream);
-    case 128: return launch<128, NW>(p, n_tiles, stream);
+    case 16: return launch<16, KSPLIT>(p, n_tiles, stream);
+    case 32: return launch<32, KSPLIT>(p, n_tiles, stream);
+    case 48: return launch<48, KSPLIT>(p, n_tiles, stream);
+    case 64: return launch<64, KSPLIT>(p, n_tiles, stream);
+    case 80: return launch<80, KSPLIT>(p, n_tiles, stream);
+    case 96: return launch<96, KSPLIT>(p, n_tiles, stream);
+    case 112: return launch<112, KSPLIT>(p, n_tiles, stream);
+    case 128: return launch<128, KSPLIT>(p, n_tiles, stream);
   }
   GB_FAIL(GB_ERR_ARG, "gb_attention_tc: head_dim %d is not one of 16, 32, ..., 128", hd);
 }
@@ -406,7 +499,7 @@ GB_API int gb_attention_tc(const void* q, long long ldq, const void* k_pages, co
   p.part_ml = workspace ? workspace + (size_t)splits * n_tokens * heads * hd : nullptr;
   p.n_requests = n_requests; p.n_tokens = n_tokens; p.heads = heads; p.kv_heads = kv_heads; p.splits = splits;
   p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
-  int rc = small ? dispatch_hd<1>(p, hd, (int)n_tiles, stream) : dispatch_hd<4>(p, hd, (int)n_tiles, stream);
+  int rc = small ? dispatch_hd<true>(p, hd, (int)n_tiles, stream) : dispatch_hd<false>(p, hd, (int)n_tiles, stream);
   if (rc != GB_OK) return rc;
   GB_CHECK_LAUNCH("gb_attention_tc");
   if (splits > 1) {

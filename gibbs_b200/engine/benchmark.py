@@ -51,7 +51,7 @@ class ClockSampler:
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int = 0, period_ms: int = 200):
+    def __init__(self, index: int = 0, period_ms: int = 20):
         self.index, self.period_ms = index, period_ms
         self.proc, self.lines = None, []
 
