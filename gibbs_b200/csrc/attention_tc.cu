@@ -395,29 +395,45 @@ attention_tc_kernel(const AttnParams p) {
 }
 
 // out[row, :] = sum_z 2^(m_z - M) o_z / sum_z 2^(m_z - M) l_z, splits in ascending order.
+// One block per row (token, head); at most 32 splits.  The first warp reads all maxima and
+// sums at once and leaves the normalised weights in shared memory; then every thread adds
+// its column over the splits with the loads of several splits in flight.
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        bf16* __restrict__ out, long long ldo, int n_tokens, int heads, int hd,
                                        int splits) {
+  __shared__ float wgt[32];
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.x;                         // token * heads + head
   const size_t rows = (size_t)n_tokens * heads;
-  float M = -INFINITY;
-  for (int z = 0; z < splits; ++z) M = fmaxf(M, part_ml[(z * rows + row) * 2]);
-  float L = 0.f;
-  for (int z = 0; z < splits; ++z) {
-    const float m = part_ml[(z * rows + row) * 2];
-    if (m != -INFINITY) L += exp2f(m - M) * part_ml[(z * rows + row) * 2 + 1];
+  if (threadIdx.x < 32) {
+    const int z = threadIdx.x;
+    float m = -INFINITY, l = 0.f;
+    if (z < splits) {
+      const float2 ml = *reinterpret_cast<const float2*>(part_ml + ((size_t)z * rows + row) * 2);
+      m = ml.x;
+      l = ml.y;
+    }
+    const float M = warp_max(m);
+    const float f = (m == -INFINITY) ? 0.f : exp2f(m - M);
+    const float L = warp_sum(f * l);
+    wgt[z] = L > 0.f ? f / L : 0.f;
   }
-  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  __syncthreads();
   const int t = row / heads, h = row - t * heads;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float acc = 0.f;
-    for (int z = 0; z < splits; ++z) {
-      const float m = part_ml[(z * rows + row) * 2];
-      if (m != -INFINITY) acc += exp2f(m - M) * part_o[(z * rows + row) * hd + d];
+    int z = 0;
+    for (; z + 4 <= splits; z += 4) {
+      const float a0 = part_o[((size_t)z * rows + row) * hd + d], a1 = part_o[((size_t)(z + 1) * rows + row) * hd + d];
+      const float a2 = part_o[((size_t)(z + 2) * rows + row) * hd + d], a3 = part_o[((size_t)(z + 3) * rows + row) * hd + d];
+      acc += wgt[z] * a0;
+      acc += wgt[z + 1] * a1;
+      acc += wgt[z + 2] * a2;
+      acc += wgt[z + 3] * a3;
     }
-    out[(size_t)t * ldo + (size_t)h * hd + d] = __float2bfloat16_rn(acc * inv);
+    for (; z < splits; ++z) acc += wgt[z] * part_o[((size_t)z * rows + row) * hd + d];
+    out[(size_t)t * ldo + (size_t)h * hd + d] = __float2bfloat16_rn(acc);
   }
 }
 
@@ -482,6 +498,7 @@ GB_API int gb_attention_tc(const void* q, long long ldq, const void* k_pages, co
   if (((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
     GB_FAIL(GB_ERR_ARG, "gb_attention_tc: q and the pages must be 16-byte aligned");
   if (splits < 1) splits = 1;
+  if (splits > 32) GB_FAIL(GB_ERR_ARG, "gb_attention_tc: at most 32 splits, got %d", splits);
   if (splits > 1 && workspace == nullptr) GB_FAIL(GB_ERR_ARG, "gb_attention_tc: splits need a workspace");
   const int group = heads / kv_heads;
   const bool small = (long long)max_q_len * group <= 16 && group <= 16;

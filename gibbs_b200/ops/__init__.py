@@ -379,7 +379,7 @@ def attention_splits(n_requests: int, kv_heads: int, max_ctx_len: int) -> int:
     enough to occupy the GPU, at least two tiles of 64 keys each."""
     by_sm = max(1, 740 // max(1, n_requests * kv_heads))      # about five one-warp CTAs per SM
     by_len = max(1, -(-max_ctx_len // 128))
-    return max(1, min(32, by_sm, by_len))
+    return max(1, min(16, by_sm, by_len))
 
 
 def _attention_tc(q, heads, kv_heads, head_dim, k_pages, v_pages, block_table, scale, window, out, status, step):
