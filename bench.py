@@ -40,6 +40,38 @@ def reference_arm():
     return 0
 
 
+def other_workload(a):
+    """The two other workloads this project's configurations name: mixed serving at the
+    LFM2-700M shape, and a long context at the LFM2-2.6B shape."""
+    import torch
+    from gibbs_b200 import Generator, Lfm2Config, random_model
+    from gibbs_b200.engine import benchmark as B
+    base = dict(LFM2_1P2B)
+    if a.workload == "serve700m":
+        base.update(hidden_size=1536, num_attention_heads=24, intermediate_size=10240, max_position_embeddings=4096)
+        cfg = Lfm2Config.from_dict(base)
+        model = random_model(cfg, 3, dtype="bfloat16", device="cuda:0")
+        gen = Generator(model, ctx=2048 + 256 + 16, page_size=16, max_running=64, max_batch_tokens=512, seed=3)
+        B.measure_serving(gen, n_requests=64, min_len=16, max_len=2048, new_tokens=256, temperature=0.8, seed=1)  # warm-up
+        res = B.measure_serving(gen, n_requests=64, min_len=16, max_len=2048, new_tokens=256, temperature=0.8, seed=3)
+        res["workload"] = "LFM2-700M shape: 64 requests, prompts U[16, 2048], portions of 512 beside decode, 256 new tokens, T=0.8"
+    else:
+        base.update(num_hidden_layers=30, full_attn_idxs=[2, 6, 10, 14, 18, 22, 25, 28], intermediate_size=10752,
+                    max_position_embeddings=8192)
+        cfg = Lfm2Config.from_dict(base)
+        model = random_model(cfg, 4, dtype="bfloat16", device="cuda:0")
+        gen = Generator(model, ctx=8192, page_size=16, n_pages=64 * 80, max_running=64, max_batch_tokens=8192, seed=4)
+        pre = B.measure_prefill(gen.engine, 8000, warmup=2, runs=3, seed=4)
+        dec1 = B.measure_decode(gen.engine, 1, 8000, 64, 4, seed=4)
+        dec64 = B.measure_decode(gen.engine, 64, 1024, 64, 4, seed=4)
+        res = {"workload": "LFM2-2.6B shape (30 layers, FFN 7168): 8,000-token prompt, greedy decode at 8k, batch 64 at 1k",
+               "prefill_8000_ms": round(pre["ms"], 2), "prefill_tok_s": round(pre["value"], 1),
+               "decode_b1_ctx8000_tok_s": round(dec1["tok_s"], 1), "decode_b1_gbs": round(dec1["gbs"], 1),
+               "decode_b64_ctx1024_tok_s": round(dec64["tok_s"], 1), "decode_b64_gbs": round(dec64["gbs"], 1)}
+    print(json.dumps({k: (round(v, 2) if isinstance(v, float) else v) for k, v in res.items()}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -49,6 +81,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--workload", choices=["serve700m", "long2p6b"], default=None,
+                    help="run one of the other reference workloads instead (prints its own JSON line)")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="measure one phase only (for short profiler captures); the line is then partial")
     a = ap.parse_args()
@@ -63,6 +97,8 @@ def main():
     from gibbs_b200 import Generator, Lfm2Config, random_model
     from gibbs_b200.engine import benchmark as B
 
+    if a.workload:
+        return other_workload(a)
     raw = dict(LFM2_1P2B)
     full_layers = raw["num_hidden_layers"]
     if a.layers is not None and a.layers < full_layers:

@@ -229,3 +229,31 @@ def measure_decode_e2e(generator, batch: int, prompt_len: int, steps: int, warmu
         + len(generator.engine.cache.groups) * batch * generator.engine.cache.max_blocks
     return {"value": n / dt, "unit": "tokens/s", "h2d_bytes_per_step": 4 * meta_ints, "d2h_bytes_per_step": 4 * batch,
             "ms_per_step": dt * 1e3 / steps}
+
+
+def measure_serving(generator, n_requests: int, min_len: int, max_len: int, new_tokens: int, temperature: float,
+                    seed: int = 0) -> dict:
+    """Continuous batching end to end: ``n_requests`` prompts of uniform-random length arrive at
+    once, are prefilled in portions under the scheduler's token budget while earlier ones decode,
+    and each generates ``new_tokens`` tokens by temperature sampling."""
+    rng = np.random.default_rng(seed)
+    sched: Scheduler = generator.scheduler(stop_at_eos=False)
+    lens = rng.integers(min_len, max_len + 1, n_requests)
+    params = SamplingParams(temperature=temperature, max_new_tokens=new_tokens, seed=seed)
+    for n in lens:
+        sched.submit(rng.integers(0, generator.engine.vocab_size, int(n)).tolist(), params)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    steps = prefill_tokens = decoded = preempted = 0
+    while sched.has_work():
+        out = sched.step()
+        steps += 1
+        prefill_tokens += out.prefill[1]
+        decoded += out.tokens_generated
+        preempted += len(out.preempted)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    done = [s for s in sched.sequences.values() if s.finish is not None and s.finish.value == "length"]
+    return {"requests": n_requests, "finished_length": len(done), "prompt_tokens": int(lens.sum()),
+            "generated_tokens": decoded, "seconds": dt, "steps": steps, "preemptions": preempted,
+            "generated_tok_s": decoded / dt, "total_tok_s": (int(lens.sum()) + decoded) / dt}

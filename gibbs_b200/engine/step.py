@@ -184,6 +184,8 @@ class Engine:
         # model cannot be captured (it reads host-side step data)
         self.use_graphs = bool(use_graphs) and all(getattr(b.mixer, "capturable", True) for b in model.blocks)
         self._graphs: dict = {}
+        self._graph_pool = None
+        self._capture_stream = torch.cuda.Stream(device=self.device) if self.use_graphs else None
         self._graph_bufs: dict = {}
 
     # -- request life ----------------------------------------------------------
@@ -283,7 +285,8 @@ class Engine:
             bld._record(turn)
             step, caches = bld._state(dev, offs, entries, rcs, n_tok, n_req, n_want, fixed=decode)
             before = ops.launch_count()
-            logits = self.model.forward(step, caches)
+            with ops.launching_on():
+                logits = self.model.forward(step, caches)
             if decode:
                 # this run was the real step; capture the same work for the next steps of this size
                 self._capture(n_req, dev, step, caches, ops.launch_count() - before)
@@ -299,9 +302,24 @@ class Engine:
         return buf
 
     def _capture(self, batch: int, dev, step, caches, launches: int) -> None:
+        """Record the decode step of this batch size.  All graphs of an engine share one
+        memory pool, and the capture is begun and ended by hand: the context manager of
+        torch.cuda.graph collects garbage and empties the allocator's cache every time,
+        which costs more than a hundred milliseconds per batch size."""
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            logits = self.model.forward(step, caches)
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        torch.cuda.synchronize()
+        side = self._capture_stream
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            graph.capture_begin(pool=self._graph_pool)
+            try:
+                with ops.launching_on(side):
+                    logits = self.model.forward(step, caches)
+            finally:
+                graph.capture_end()
+        torch.cuda.current_stream().wait_stream(side)
         ops._launched(-launches)        # the wrappers counted the captured launches, which did not run
         self._graphs[batch] = {"graph": graph, "meta": dev, "logits": logits, "launches": launches}
 

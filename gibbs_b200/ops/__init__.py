@@ -46,8 +46,34 @@ def _ptr(t: Optional[torch.Tensor]):
     return _c_void(t.data_ptr()) if t is not None else _c_void(0)
 
 
+_STREAM = None      # handle of the stream kernels launch on while a `launching_on` block is active
+
+
 def _stream():
+    if _STREAM is not None:
+        return _STREAM
     return _c_void(torch.cuda.current_stream().cuda_stream)
+
+
+class launching_on:
+    """Within the block every kernel of this module launches on ``stream`` (default: the
+    current CUDA stream at entry) without asking torch for the current stream at every
+    launch, which costs more than the launch itself.  The caller must not switch streams
+    inside the block."""
+
+    def __init__(self, stream=None):
+        self.stream = stream
+
+    def __enter__(self):
+        global _STREAM
+        self.prev = _STREAM
+        st = self.stream if self.stream is not None else torch.cuda.current_stream()
+        _STREAM = _c_void(st.cuda_stream)
+        return self
+
+    def __exit__(self, *exc):
+        global _STREAM
+        _STREAM = self.prev
 
 
 def _need_cuda(*tensors):
@@ -164,6 +190,7 @@ def linear_libraries(weight_dtype: torch.dtype, compute_dtype: torch.dtype):
 
 
 _STATUS: dict = {}
+_SPLITS: dict = {}      # (m, n, k) -> number of K splits the tensor-core product uses
 
 
 def device_status(device) -> torch.Tensor:
@@ -214,7 +241,9 @@ def linear_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
         mode = 0 if out.dtype == torch.bfloat16 else 1
         dtype_code(out.dtype)
     _f32vec(bias, n, "linear bias")
-    splits = lib.gb_linear_tc_splits(_c_int(m), _c_int(n), _c_int(k))
+    splits = _SPLITS.get((m, n, k))
+    if splits is None:
+        splits = _SPLITS[(m, n, k)] = lib.gb_linear_tc_splits(_c_int(m), _c_int(n), _c_int(k))
     ws = torch.empty((splits, m, n), dtype=torch.float32, device=a.device) if splits > 1 else None
     defer = bool(defer and accumulate and splits > 1)
     if not _TC_PREFETCH:
