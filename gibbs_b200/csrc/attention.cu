@@ -92,6 +92,96 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, long long ld, con
   }
 }
 
+// The same for q, k, v given as the partial tiles of the split-K product that made them
+// (ws[split][token][cols], 32-bit, plus bias): the sums are rounded to bfloat16 where the
+// product's own reduction would have rounded them.  q goes to q_out [n_tokens, heads*hd].
+__global__ void qk_norm_rope_store_partials_kernel(const float* __restrict__ ws, int splits, const float* __restrict__ bias,
+                                                   bf16* __restrict__ q_out, const float* __restrict__ q_gain,
+                                                   const float* __restrict__ k_gain, float eps,
+                                                   const float* __restrict__ inv_freq, int rotary_dim, int adjacent,
+                                                   const int* __restrict__ tok_req, const int* __restrict__ tok_pos,
+                                                   const int* __restrict__ block_table, int bt_stride, int page_size,
+                                                   bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, int n_pages,
+                                                   int n_tokens, int heads, int kv_heads, int hd, int write_kv,
+                                                   int* __restrict__ status) {
+  extern __shared__ float staged[];                      // [warps of the block][hd]
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* mine = staged + (size_t)warp * hd;
+  const int slots = heads + (write_kv ? 2 * kv_heads : 0);
+  const int cols = slots * hd;
+  const long long idx = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (idx >= (long long)n_tokens * slots) return;
+  const int t = (int)(idx / slots), slot = (int)(idx - (long long)t * slots);
+  const int pos = tok_pos[t];
+  const bool is_q = slot < heads;
+  const bool is_k = !is_q && slot < heads + kv_heads;
+  const int kvh = is_q ? 0 : (is_k ? slot - heads : slot - heads - kv_heads);
+  bf16* dst;
+  if (is_q) {
+    dst = q_out + (size_t)t * heads * hd + (size_t)slot * hd;
+  } else {
+    const int page = block_table[(size_t)tok_req[t] * bt_stride + pos / page_size];
+    if (page < 0 || page >= n_pages) {
+      if (lane == 0) atomicExch(status, STATUS_BAD_PAGE_WRITE);
+      return;
+    }
+    dst = (is_k ? k_pages : v_pages) + (((size_t)page * kv_heads + kvh) * page_size + pos % page_size) * hd;
+  }
+  float ss = 0.f;
+  for (int d0 = 0; d0 < hd; d0 += 128) {                 // four columns per lane at a time
+    size_t at[4];
+    float v[4];
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+      const int d = d0 + lane + 32 * m;
+      at[m] = (size_t)t * cols + (size_t)slot * hd + (d < hd ? d : hd - 1);
+    }
+    sum_partials<4>(ws, splits, (size_t)n_tokens * cols, at, v);
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+      const int d = d0 + lane + 32 * m;
+      if (d < hd) {
+        if (bias) v[m] += bias[slot * hd + d];
+        const float x = to_f32(from_f32<bf16>(v[m]));
+        mine[d] = x;
+        ss += x * x;
+      }
+    }
+  }
+  __syncwarp();
+  if (!is_q && !is_k) {
+    for (int d = lane; d < hd; d += 32) dst[d] = __float2bfloat16_rn(mine[d]);
+    return;
+  }
+  const float* gain = is_q ? q_gain : k_gain;
+  float scale = 1.f;
+  if (gain) {
+    ss = warp_sum(ss);
+    scale = 1.0f / sqrtf(ss / (float)hd + eps);
+  }
+  const int half = inv_freq ? rotary_dim / 2 : 0;
+  for (int j = lane; j < half; j += 32) {
+    const int i0 = adjacent ? 2 * j : j;
+    const int i1 = adjacent ? 2 * j + 1 : j + half;
+    float a = mine[i0], b = mine[i1];
+    if (gain) {
+      a = a * scale * gain[i0];
+      b = b * scale * gain[i1];
+    }
+    const float ang = (float)pos * inv_freq[j];
+    const float c = cosf(ang), s = sinf(ang);
+    dst[i0] = __float2bfloat16_rn(a * c - b * s);
+    dst[i1] = __float2bfloat16_rn(a * s + b * c);
+  }
+  for (int d = 2 * half + lane; d < hd; d += 32) {
+    float a = mine[d];
+    if (gain) a = a * scale * gain[d];
+    dst[d] = __float2bfloat16_rn(a);
+  }
+}
+
 // One warp per (token, head).  Lane l takes the keys lo + l, lo + l + 32, ...
 // with its own running (max, sum, output); the 32 partial states are merged at
 // the end.  Which keys a lane takes depends on the query's position only, so
@@ -207,6 +297,31 @@ GB_API int gb_qk_norm_rope_store(void* qkv, int dtype, long long ld, const float
   else
     GB_FAIL(GB_ERR_ARG, "gb_qk_norm_rope_store: unknown dtype %d", dtype);
   GB_CHECK_LAUNCH("gb_qk_norm_rope_store");
+  return GB_OK;
+}
+
+// q, k, v as the `splits` partial tiles (32-bit [splits][n_tokens][cols], cols = (heads + 2*kv_heads) * hd,
+// or heads * hd without write_kv) of a split-K product, plus its bias or null; bfloat16 pages and q_out.
+GB_API int gb_qk_norm_rope_store_partials(const float* ws, int splits, const float* bias, void* q_out,
+                                          const float* q_gain, const float* k_gain, float eps, const float* inv_freq,
+                                          int rotary_dim, int adjacent, const int* tok_req, const int* tok_pos,
+                                          const int* block_table, int bt_stride, int page_size, void* k_pages,
+                                          void* v_pages, int n_pages, int n_tokens, int heads, int kv_heads, int hd,
+                                          int write_kv, int* status, cudaStream_t stream) {
+  if (n_tokens <= 0) return GB_OK;
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0)
+    GB_FAIL(GB_ERR_ARG, "gb_qk_norm_rope_store_partials: %d heads over %d kv heads", heads, kv_heads);
+  if (inv_freq && (rotary_dim % 2 != 0 || rotary_dim > hd || rotary_dim <= 0))
+    GB_FAIL(GB_ERR_ARG, "gb_qk_norm_rope_store_partials: rotary_dim %d for head_dim %d", rotary_dim, hd);
+  if (page_size <= 0) GB_FAIL(GB_ERR_ARG, "gb_qk_norm_rope_store_partials: page_size %d", page_size);
+  if (splits < 1 || hd <= 0 || hd > 2048) GB_FAIL(GB_ERR_ARG, "gb_qk_norm_rope_store_partials: %d splits, head_dim %d", splits, hd);
+  const int slots = heads + (write_kv ? 2 * kv_heads : 0);
+  const long long warps = (long long)n_tokens * slots;
+  gb_launch(qk_norm_rope_store_partials_kernel, dim3(gb_div_up(warps, 4)), dim3(128), (size_t)4 * hd * sizeof(float),
+            stream, ws, splits, bias, (bf16*)q_out, q_gain, k_gain, eps, inv_freq, rotary_dim, adjacent, tok_req,
+            tok_pos, block_table, bt_stride, page_size, (bf16*)k_pages, (bf16*)v_pages, n_pages, n_tokens, heads,
+            kv_heads, hd, write_kv, status);
+  GB_CHECK_LAUNCH("gb_qk_norm_rope_store_partials");
   return GB_OK;
 }
 

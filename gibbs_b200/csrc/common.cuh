@@ -77,6 +77,29 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return scratch[0];
 }
 
+// NV sums over the `splits` partial tiles a split-K product left in 32-bit ([split][row][col],
+// `stride` elements between splits), at the element offsets at[0..NV): the loads of four splits
+// are requested together and the terms are added in split order.
+template <int NV>
+__device__ __forceinline__ void sum_partials(const float* __restrict__ ws, int splits, size_t stride,
+                                             const size_t* at, float* acc) {
+#pragma unroll
+  for (int v = 0; v < NV; ++v) acc[v] = 0.f;
+  for (int s0 = 0; s0 < splits; s0 += 4) {
+    float a[4][NV];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int v = 0; v < NV; ++v) a[u][v] = (s0 + u < splits) ? __ldcg(ws + (size_t)(s0 + u) * stride + at[v]) : 0.f;
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (s0 + u < splits) {
+#pragma unroll
+        for (int v = 0; v < NV; ++v) acc[v] += a[u][v];
+      }
+  }
+}
+
 static inline int gb_div_up(long long a, long long b) { return (int)((a + b - 1) / b); }
 
 // ---------------------------------------------------------------- launches

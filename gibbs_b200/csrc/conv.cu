@@ -167,7 +167,63 @@ __global__ void short_conv_decode_kernel(const T* __restrict__ bcx, long long ld
   out[(size_t)t * hidden + c] = from_f32<T>(to_f32(row[hidden + c]) * acc);
 }
 
+// The same, reading [B | C | x] as the partial tiles of the split-K product that made it
+// (ws[split][token][3*hidden], 32-bit, plus in_bias): their sum is rounded to bfloat16 exactly
+// where the product's own reduction would have rounded it, then used as above.
+__global__ void short_conv_decode_partials_kernel(const float* __restrict__ ws, int splits, long long n_rows,
+                                                  const float* __restrict__ in_bias, const float* __restrict__ taps,
+                                                  const float* __restrict__ bias, float* __restrict__ state,
+                                                  long long slot_stride, const int* __restrict__ slot_ids,
+                                                  const int* __restrict__ q_start, bf16* __restrict__ out,
+                                                  int n_requests, int hidden, int K) {
+  pdl_trigger();
+  pdl_wait();
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= (long long)n_requests * hidden) return;
+  const int r = (int)(gid / hidden), c = (int)(gid - (long long)r * hidden);
+  const int t = q_start[r];
+  const size_t ld = (size_t)3 * hidden;
+  const size_t at[3] = {(size_t)t * ld + c, (size_t)t * ld + hidden + c, (size_t)t * ld + 2 * hidden + c};
+  float* st = state + (size_t)slot_ids[r] * slot_stride;
+  float old[MAX_TAPS];
+  for (int j = 0; j < K - 1; ++j) old[j] = st[(size_t)j * hidden + c];   // on their way while the sums are formed
+  float v[3];
+  sum_partials<3>(ws, splits, (size_t)n_rows * ld, at, v);
+  if (in_bias) {
+    v[0] += in_bias[c];
+    v[1] += in_bias[hidden + c];
+    v[2] += in_bias[2 * hidden + c];
+  }
+  const float bv = to_f32(from_f32<bf16>(v[0])), cv = to_f32(from_f32<bf16>(v[1])), xv = to_f32(from_f32<bf16>(v[2]));
+  const float bx = bv * xv;
+  float acc = 0.f;
+  for (int j = 0; j < K - 1; ++j) {
+    acc = fmaf(taps[(size_t)c * K + j], old[j], acc);
+    if (j > 0) st[(size_t)(j - 1) * hidden + c] = old[j];
+  }
+  acc = fmaf(taps[(size_t)c * K + K - 1], bx, acc);
+  st[(size_t)(K - 2) * hidden + c] = bx;
+  if (bias) acc += bias[c];
+  out[(size_t)t * hidden + c] = __float2bfloat16_rn(cv * acc);
+}
+
 }  // namespace
+
+// One token per request, with [B | C | x] given as the `splits` partial tiles of a split-K product
+// (ws: 32-bit [splits][n_rows][3*hidden], in_bias: its bias or null); out is bfloat16.
+GB_API int gb_short_conv_partials(const float* ws, int splits, long long n_rows, const float* in_bias,
+                                  const float* taps, const float* bias, float* state, long long slot_stride,
+                                  const int* slot_ids, const int* q_start, void* out, int n_requests, int hidden, int K,
+                                  cudaStream_t stream) {
+  if (n_requests <= 0) return 0;
+  if (K < 2 || K > MAX_TAPS) GB_FAIL(GB_ERR_ARG, "gb_short_conv_partials: kernel width %d outside 2..%d", K, MAX_TAPS);
+  if (splits < 1) GB_FAIL(GB_ERR_ARG, "gb_short_conv_partials: %d splits", splits);
+  const long long total = (long long)n_requests * hidden;
+  gb_launch(short_conv_decode_partials_kernel, dim3(gb_div_up(total, 128)), dim3(128), 0, stream, ws, splits, n_rows,
+            in_bias, taps, bias, state, slot_stride, slot_ids, q_start, (bf16*)out, n_requests, hidden, K);
+  GB_CHECK_LAUNCH("gb_short_conv_partials");
+  return 1;
+}
 
 // bcx: [n_tokens, 3*hidden] rows of [B | C | x] with row stride ld; taps
 // [hidden, K] and bias [hidden] (optional) in 32-bit; state: 32-bit, slot s at

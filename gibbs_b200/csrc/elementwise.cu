@@ -83,14 +83,30 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, long long ldx, const float
       v[i] = c < n4 ? reinterpret_cast<const float4*>(src)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     if (pend) {
-      for (int s = 0; s < splits; ++s) {
-        const float4* ps = reinterpret_cast<const float4*>(pend + ((size_t)s * n_src_rows + sr) * dim);
+      // the partial sums of up to eight splits are requested together (one trip to L2, not eight)
+      // and then added in split order
+      constexpr int G = 8;
+      const size_t split_stride = (size_t)n_src_rows * dim;
+      const float* p0 = pend + (size_t)sr * dim;
+      for (int s0 = 0; s0 < splits; s0 += G) {
+        float4 a[G][VEC > 0 ? VEC : 1];
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) {
-          const int c = threadIdx.x + i * blockDim.x;
-          if (c < n4) {
-            const float4 a = __ldcg(ps + c);
-            v[i].x += a.x; v[i].y += a.y; v[i].z += a.z; v[i].w += a.w;
+        for (int u = 0; u < G; ++u) {
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) {
+            const int c = threadIdx.x + i * blockDim.x;
+            a[u][i] = (s0 + u < splits && c < n4)
+                          ? __ldcg(reinterpret_cast<const float4*>(p0 + (size_t)(s0 + u) * split_stride) + c)
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < G; ++u) {
+          if (s0 + u < splits) {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+              v[i].x += a[u][i].x; v[i].y += a[u][i].y; v[i].z += a[u][i].z; v[i].w += a[u][i].w;
+            }
           }
         }
       }

@@ -1204,8 +1204,9 @@ GB_API int gb_linear_tc_supported(const void* X, long long ldx, const void* W, l
 // mode 0: out bf16 [M, N]; 1: out f32; 2: out f32 += ; 3: SwiGLU, W rows alternating in blocks of
 // 64 between gate and up (N = 2 * features, a multiple of 128), out bf16 [M, N / 2].
 // workspace: gb_linear_tc_workspace(M, N, K) floats (may be null when that is 0).
-// defer != 0 (mode 2 only): when K is split, leave the partial tiles in the workspace
-// ([splits][M][N], without bias) for the caller's next kernel to add; nothing is written to out.
+// defer != 0 (modes 0 and 2): when K is split, leave the partial tiles in the workspace
+// ([splits][M][N], without bias) for the caller's next kernel to add (mode 0: and to round to
+// bfloat16); nothing is written to out.
 // prefetch / prefetch_bytes: the weights of the product that follows, or null / 0.
 // flags bit 0: read the weights with an evict-first hint.
 // Returns the number of kernels launched, or a negative error code.
@@ -1224,7 +1225,8 @@ GB_API int gb_linear_tc(const void* X, long long ldx, const void* W, long long l
   int bn, splits, kb_per_split;
   plan(M, N, K, &bn, &splits, &kb_per_split);
   if (splits > 1 && workspace == nullptr) GB_FAIL(GB_ERR_ARG, "gb_linear_tc: these sizes need a workspace");
-  if (defer && mode != OUT_F32_ACC) GB_FAIL(GB_ERR_ARG, "gb_linear_tc: only an accumulating product can be deferred");
+  if (defer && mode != OUT_F32_ACC && mode != OUT_BF16)
+    GB_FAIL(GB_ERR_ARG, "gb_linear_tc: only a plain bfloat16 or an accumulating product can be deferred");
 
   CUtensorMap tw, tx;
   {

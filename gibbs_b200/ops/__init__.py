@@ -216,10 +216,10 @@ def linear_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     (csrc/gemm_tc.cu).  ``swiglu``: w holds gate and up rows alternating in
     blocks of 64 and out [m, n/2] gets (g * sigmoid(g)) * u.  ``prefetch``:
     the weight the next product will read, pulled towards L2 meanwhile.
-    ``defer`` (with ``accumulate``): when the kernel splits K, nothing is
-    added to ``out``; the partial sums [splits, m, n] are returned instead,
-    for the caller's next kernel to add (without the bias).  Otherwise
-    returns ``out``."""
+    ``defer`` (with ``accumulate``, or for a plain bfloat16 product): when
+    the kernel splits K, nothing is written to ``out``; the partial sums
+    [splits, m, n] are returned instead, for the caller's next kernel to add
+    (without the bias).  Otherwise returns ``out``."""
     _need_cuda(a, w, bias, out, prefetch)
     lib = library("tensorcore")
     m, k = a.shape
@@ -245,7 +245,7 @@ def linear_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     if splits is None:
         splits = _SPLITS[(m, n, k)] = lib.gb_linear_tc_splits(_c_int(m), _c_int(n), _c_int(k))
     ws = torch.empty((splits, m, n), dtype=torch.float32, device=a.device) if splits > 1 else None
-    defer = bool(defer and accumulate and splits > 1)
+    defer = bool(defer and (accumulate or mode == 0) and splits > 1)
     if not _TC_PREFETCH:
         prefetch = None
     pf_bytes = prefetch.numel() * prefetch.element_size() if prefetch is not None else 0
@@ -258,6 +258,26 @@ def linear_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
         check(lib, rc)
     _launched(rc)
     return ws if defer else out
+
+
+class Partials:
+    """What a split-K product left for its consumer: the 32-bit partial tiles
+    [splits, m, n] (to be added in split order), the product's bias (not yet
+    added) or None, and the dtype the sum is to be rounded to."""
+
+    def __init__(self, ws: torch.Tensor, bias: Optional[torch.Tensor], dtype: torch.dtype):
+        self.ws, self.bias, self.dtype = ws, bias, dtype
+        self.shape = tuple(ws.shape[1:])
+
+
+def linear_tc_partials(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]):
+    """a @ w.T on the tensor cores for a consumer that can add split-K partial
+    tiles itself: returns ``Partials`` when the kernel splits K for these sizes
+    (no reduction kernel runs), else the finished bfloat16 product."""
+    m, n = a.shape[0], w.shape[0]
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
+    res = linear_tc(a, w, bias, out, defer=True)
+    return Partials(res, bias, torch.bfloat16) if res is not out else out
 
 
 def linear_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
@@ -329,6 +349,37 @@ def short_conv(bcx: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tenso
     return out
 
 
+def short_conv_partials(bcx: Partials, taps: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
+                        slot_ids: torch.Tensor, q_start: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """The gated short convolution of one token per request, reading [B | C | x]
+    as the partial tiles of the product that made it (no reduction kernel in between)."""
+    _need_cuda(bcx.ws, bcx.bias, taps, bias, state, slot_ids, q_start, out)
+    lib = library("core")
+    n, hidden = out.shape
+    kk = taps.shape[1]
+    ws = bcx.ws
+    if ws.dtype != torch.float32 or not ws.is_contiguous() or ws.shape[1:] != (n, 3 * hidden) \
+            or out.dtype != torch.bfloat16 or not out.is_contiguous() or bcx.dtype != torch.bfloat16:
+        raise KernelError("short_conv_partials: partial tiles [splits, n, 3*hidden] float32 and out [n, hidden] "
+                          "bfloat16 expected")
+    if q_start.numel() != n:
+        raise KernelError("short_conv_partials: one token per request expected")
+    _f32vec(taps, hidden * kk, "short_conv taps")
+    _f32vec(bias, hidden, "short_conv bias")
+    _f32vec(bcx.bias, 3 * hidden, "short_conv in_proj bias")
+    if state.dtype != torch.float32 or state.shape[1:] != (kk - 1, hidden) or state[0].stride() != (hidden, 1):
+        raise KernelError(f"short_conv: state must be float32 [slots, {kk - 1}, {hidden}] with contiguous slots")
+    _i32(slot_ids, "short_conv slot_ids"), _i32(q_start, "short_conv q_start")
+    rc = lib.gb_short_conv_partials(
+        _ptr(ws), _c_int(ws.shape[0]), _c_ll(n), _ptr(bcx.bias), _ptr(taps), _ptr(bias), _ptr(state),
+        _c_ll(state.stride(0)), _ptr(slot_ids), _ptr(q_start), _ptr(out), _c_int(n), _c_int(hidden), _c_int(kk),
+        _stream())
+    if rc < 0:
+        check(lib, rc)
+    _launched(rc)
+    return out
+
+
 def _check_pages(k_pages, v_pages, kv_heads, hd, dtype, what):
     for p in (k_pages, v_pages):
         if p.dim() != 4 or p.shape[1] != kv_heads or p.shape[3] != hd or not p.is_contiguous() or p.dtype != dtype:
@@ -370,6 +421,45 @@ def qk_norm_rope_store(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: i
         _ptr(block_table), _c_int(block_table.shape[1] if block_table.dim() == 2 else 0), _c_int(page_size),
         _ptr(k_pages), _ptr(v_pages), _c_int(n_pages), _c_int(n), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
         _c_int(1 if write else 0), _ptr(status), _stream()))
+
+
+def qk_norm_rope_store_partials(qkv: Partials, q_out: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
+                                q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], eps: float,
+                                inv_freq: Optional[torch.Tensor], rotary_dim: int, adjacent_pairs: bool,
+                                tok_req: torch.Tensor, tok_pos: torch.Tensor, block_table: torch.Tensor,
+                                k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+                                status: torch.Tensor) -> torch.Tensor:
+    """As ``qk_norm_rope_store`` for q, k, v given as the partial tiles of their
+    split-K product; q (normed and rotated) goes to ``q_out`` [n, heads*head_dim]."""
+    _need_cuda(qkv.ws, qkv.bias, q_out, q_gain, k_gain, inv_freq, tok_req, tok_pos, block_table, k_pages, v_pages,
+               status)
+    lib = library("core")
+    ws = qkv.ws
+    n = ws.shape[1]
+    write = k_pages is not None
+    cols = (heads + (2 * kv_heads if write else 0)) * head_dim
+    if ws.dtype != torch.float32 or not ws.is_contiguous() or ws.shape[2] != cols or qkv.dtype != torch.bfloat16:
+        raise KernelError(f"qk_norm_rope_store_partials: partial tiles [splits, n, {cols}] float32 expected")
+    if q_out.shape != (n, heads * head_dim) or q_out.dtype != torch.bfloat16 or not q_out.is_contiguous():
+        raise KernelError("qk_norm_rope_store_partials: q_out must be contiguous bfloat16 [n, heads*head_dim]")
+    _f32vec(qkv.bias, cols, "qkv bias")
+    _f32vec(q_gain, head_dim, "q gain")
+    _f32vec(k_gain, head_dim, "k gain")
+    if inv_freq is not None:
+        _f32vec(inv_freq, rotary_dim // 2, "inv_freq")
+    _i32(tok_req, "tok_req"), _i32(tok_pos, "tok_pos"), _i32(block_table, "block_table"), _i32(status, "status")
+    page_size, n_pages = 1, 0
+    if write:
+        _check_pages(k_pages, v_pages, kv_heads, head_dim, torch.bfloat16, "qk_norm_rope_store_partials")
+        page_size, n_pages = k_pages.shape[2], k_pages.shape[0]
+    _launched(1)
+    check(lib, lib.gb_qk_norm_rope_store_partials(
+        _ptr(ws), _c_int(ws.shape[0]), _ptr(qkv.bias), _ptr(q_out), _ptr(q_gain), _ptr(k_gain), _c_float(eps),
+        _ptr(inv_freq), _c_int(rotary_dim), _c_int(1 if adjacent_pairs else 0), _ptr(tok_req), _ptr(tok_pos),
+        _ptr(block_table), _c_int(block_table.shape[1] if block_table.dim() == 2 else 0), _c_int(page_size),
+        _ptr(k_pages), _ptr(v_pages), _c_int(n_pages), _c_int(n), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
+        _c_int(1 if write else 0), _ptr(status), _stream()))
+    return q_out
 
 
 def paged_attention(q: torch.Tensor, heads: int, kv_heads: int, head_dim: int, k_pages: torch.Tensor,

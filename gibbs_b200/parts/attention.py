@@ -76,16 +76,23 @@ class GQAAttention(Mixer):
         kv = caches[0]
         if not self.shares_kv and not kv.writable:
             raise RuntimeError("an attention layer with k/v projections was given a read-only cache")
-        qkv = self.qkv(h)
+        qkv = self.qkv.partials(h)
         rot = self.rotary
-        ops.qk_norm_rope_store(
-            qkv, self.heads, self.kv_heads, self.head_dim, self.q_gain, self.k_gain, self.eps,
-            None if rot is None else rot.inv_freq, 0 if rot is None else rot.rotary_dim,
-            False if rot is None else rot.adjacent_pairs, step.tok_req, step.tok_pos, kv.block_table,
-            None if self.shares_kv else kv.k_pages, None if self.shares_kv else kv.v_pages, step.status)
+        rope = (None if rot is None else rot.inv_freq, 0 if rot is None else rot.rotary_dim,
+                False if rot is None else rot.adjacent_pairs)
+        pages = (None if self.shares_kv else kv.k_pages, None if self.shares_kv else kv.v_pages)
         a = self.heads * self.head_dim
+        if isinstance(qkv, ops.Partials):
+            # K was split: this kernel adds the partial tiles itself (no reduction kernel in between)
+            q = ops.qk_norm_rope_store_partials(
+                qkv, self.rt.empty(qkv.shape[0], a), self.heads, self.kv_heads, self.head_dim, self.q_gain,
+                self.k_gain, self.eps, *rope, step.tok_req, step.tok_pos, kv.block_table, *pages, step.status)
+        else:
+            ops.qk_norm_rope_store(qkv, self.heads, self.kv_heads, self.head_dim, self.q_gain, self.k_gain, self.eps,
+                                   *rope, step.tok_req, step.tok_pos, kv.block_table, *pages, step.status)
+            q = qkv[:, :a]
         out = self.rt.empty(qkv.shape[0], a)
-        ops.paged_attention(qkv[:, :a], self.heads, self.kv_heads, self.head_dim, kv.k_pages, kv.v_pages,
+        ops.paged_attention(q, self.heads, self.kv_heads, self.head_dim, kv.k_pages, kv.v_pages,
                             kv.block_table, step.tok_req, step.tok_pos, self.scale, self.window or 0, out,
                             step.status, hints=step)
         self.out_proj(out, out=residual, accumulate=True)

@@ -28,6 +28,14 @@ class Linear:
     def kernel_libraries(self):
         return ops.linear_libraries(self.weight.dtype, self.rt.dtype)
 
+    def partials(self, x: torch.Tensor):
+        """x W^T + b for a consumer that can add split-K partial tiles itself:
+        ``ops.Partials`` when the product runs on the tensor cores with K split
+        (then no reduction kernel runs), else the finished product."""
+        if not self.swiglu and self.rt.dtype == torch.bfloat16 and ops.linear_tc_supported(x, self.weight):
+            return ops.linear_tc_partials(x, self.weight, self.bias)
+        return self(x)
+
     def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False,
                  out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """out (+)= x W^T + b.  ``accumulate`` adds into a float32 ``out``

@@ -50,10 +50,14 @@ class GatedShortConv(Mixer):
 
     def forward(self, h, residual, step, caches):
         slot = caches[0]
-        bcx = self.in_proj(h)
         y = self.rt.empty(h.shape[0], self.hidden)
-        ops.short_conv(bcx, self.taps, self.conv_bias, slot.state, slot.slot_ids, step.tok_req, step.q_start,
-                       step.q_len, y, max_q_len=step.max_q_len)
+        one_each = step.max_q_len == 1 and step.n_tokens == step.n_requests
+        bcx = self.in_proj.partials(h) if one_each else self.in_proj(h)
+        if isinstance(bcx, ops.Partials):
+            ops.short_conv_partials(bcx, self.taps, self.conv_bias, slot.state, slot.slot_ids, step.q_start, y)
+        else:
+            ops.short_conv(bcx, self.taps, self.conv_bias, slot.state, slot.slot_ids, step.tok_req, step.q_start,
+                           step.q_len, y, max_q_len=step.max_q_len)
         self.out_proj(y, out=residual, accumulate=True)
 
 

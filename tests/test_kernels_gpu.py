@@ -623,3 +623,95 @@ def test_deferred_split_k_and_norm_that_adds_the_partial_sums():
     x2 = x0.clone().to(DEV)
     ops.add_pending(x2, ws, bias.to(DEV))
     assert torch.equal(x2, x)
+
+
+# --------------------------------------------------------------------------- consumers of split-K partial tiles
+def _split_partials(full: torch.Tensor, splits: int, seed: int):
+    """Random 32-bit partial tiles [splits, m, n] whose sum in split order is what a reduction
+    kernel would compute; returns (tiles on the device, their bfloat16-rounded sum)."""
+    g = torch.Generator().manual_seed(seed)
+    parts = torch.randn(splits, *full.shape, generator=g) * 0.3
+    parts[0] = full - parts[1:].sum(0)
+    acc = torch.zeros_like(full)
+    for s in range(splits):                     # the order the kernels add in
+        acc = acc + parts[s]
+    return parts.to(DEV), acc
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("hidden,k,splits,use_bias", [(96, 4, 3, True), (200, 2, 1, False), (2048, 3, 9, False)])
+def test_short_conv_from_partial_tiles_equals_the_two_kernel_way(hidden, k, splits, use_bias):
+    from gibbs_b200 import ops
+    torch.manual_seed(hidden + splits)
+    n_req, n_slots = 5, 7
+    taps, bias = torch.randn(hidden, k), (torch.randn(hidden) if use_bias else None)
+    in_bias = torch.randn(3 * hidden) if use_bias else None
+    state = torch.randn(n_slots, k - 1, hidden)
+    slot_ids = [6, 1, 0, 4, 2]
+    t = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    dev = lambda x: None if x is None else x.to(DEV)
+    st_a, st_b = state.to(DEV), state.to(DEV)
+    for step in range(3):
+        ws, total = _split_partials(torch.randn(n_req, 3 * hidden), splits, seed=step)
+        if in_bias is not None:
+            total = total + in_bias
+        bcx = total.to(torch.bfloat16).to(DEV)                        # what the reduction kernel would have written
+        want = torch.empty(n_req, hidden, dtype=torch.bfloat16, device=DEV)
+        ops.short_conv(bcx, dev(taps), dev(bias), st_a, t(slot_ids), t(list(range(n_req))), t(list(range(n_req))),
+                       t([1] * n_req), want, max_q_len=1)
+        got = torch.empty_like(want)
+        ops.short_conv_partials(ops.Partials(ws, dev(in_bias), torch.bfloat16), dev(taps), dev(bias), st_b,
+                                t(slot_ids), t(list(range(n_req))), got)
+        assert torch.equal(got, want)
+        assert torch.equal(st_a, st_b)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("heads,kvh,hd,rd,adjacent,norm,splits,write_kv",
+                         [(4, 2, 16, 16, False, True, 2, True), (3, 1, 32, 16, True, False, 5, True),
+                          (32, 8, 64, 64, False, True, 6, True), (2, 2, 128, 128, False, True, 1, False),
+                          (5, 5, 80, 40, False, True, 3, True)])
+def test_qk_norm_rope_store_from_partial_tiles_equals_the_two_kernel_way(heads, kvh, hd, rd, adjacent, norm, splits,
+                                                                         write_kv):
+    from gibbs_b200 import ops
+    torch.manual_seed(heads * 10 + hd)
+    before, q_lens, ps, n_pages = [0, 37, 5], [4, 1, 1], 8, 40
+    bt, tok_req, tok_pos = _layout(before, q_lens, ps, n_pages, seed=hd)
+    n = sum(q_lens)
+    cols = (heads + (2 * kvh if write_kv else 0)) * hd
+    bias = torch.randn(cols)
+    ws, total = _split_partials(torch.randn(n, cols), splits, seed=3)
+    qkv = (total + bias).to(torch.bfloat16).to(DEV)
+    qg, kg = ((1 + 0.2 * torch.randn(hd)).to(DEV), (1 + 0.2 * torch.randn(hd)).to(DEV)) if norm else (None, None)
+    inv = torch.tensor([1.0 / (10000.0 ** (2 * j / rd)) for j in range(rd // 2)], dtype=torch.float32, device=DEV)
+    t = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    pages = lambda: (torch.zeros(n_pages, kvh, ps, hd, dtype=torch.bfloat16, device=DEV) if write_kv else None)
+    kp_a, vp_a, kp_b, vp_b = pages(), pages(), pages(), pages()
+    ops.qk_norm_rope_store(qkv, heads, kvh, hd, qg, kg, 1e-5, inv, rd, adjacent, t(tok_req), t(tok_pos), t(bt),
+                           kp_a, vp_a, status)
+    q = torch.empty(n, heads * hd, dtype=torch.bfloat16, device=DEV)
+    ops.qk_norm_rope_store_partials(ops.Partials(ws, bias.to(DEV), torch.bfloat16), q, heads, kvh, hd, qg, kg, 1e-5,
+                                    inv, rd, adjacent, t(tok_req), t(tok_pos), t(bt), kp_b, vp_b, status)
+    assert torch.equal(q, qkv[:, :heads * hd])
+    if write_kv:
+        assert torch.equal(kp_a, kp_b) and torch.equal(vp_a, vp_b)
+        assert kp_a.abs().sum() > 0
+    assert int(status.item()) == 0
+
+
+@pytest.mark.gpu
+def test_linear_partials_returns_tiles_only_when_k_is_split():
+    from gibbs_b200 import ops
+    torch.manual_seed(5)
+    a, ar = _quant(torch.randn(8, 2048), "bfloat16")
+    w, wr = _quant(torch.randn(384, 2048) / 45.0, "bfloat16")        # 3 tiles of weight rows: K is split
+    bias = torch.randn(384, device=DEV)
+    p = ops.linear_tc_partials(a, w, bias)
+    assert isinstance(p, ops.Partials) and p.ws.shape[0] > 1 and p.shape == (8, 384)
+    _close(p.ws.sum(0) + bias, ar @ wr.T + bias.cpu().double(), "float32")
+    w2, w2r = _quant(torch.randn(128 * 100, 64) / 8.0, "bfloat16")   # many tiles: no split, finished product
+    a2, a2r = _quant(torch.randn(8, 64), "bfloat16")
+    out = ops.linear_tc_partials(a2, w2, None)
+    assert isinstance(out, torch.Tensor) and out.dtype == torch.bfloat16
+    _close(out, a2r @ w2r.T, "bfloat16")
