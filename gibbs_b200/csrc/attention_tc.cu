@@ -113,13 +113,13 @@ attention_tc_kernel(const AttnParams p) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int group = p.heads / p.kv_heads;
   const int tpt = BQ / group;                                // tokens per tile
-  const int kvh = blockIdx.y, z = blockIdx.z;
+  const int kvh = blockIdx.x, z = blockIdx.z;          // x (dispatched fastest) is the kv head: heavy tiles of every head first
 
   // which request and which of its tiles this CTA has
   // Blocks are handed out in descending order of work: requests from the last to the first and,
   // within a request, from its last tile (which sees the most keys) to its first, so that the
   // long tiles of a causal prompt do not form the tail of the launch.
-  int r = p.n_requests - 1, tile = (int)blockIdx.x, found = 0;
+  int r = p.n_requests - 1, tile = (int)blockIdx.y, found = 0;
   for (; r >= 0; --r) {
     const int nt = (p.q_len[r] + tpt - 1) / tpt;
     if (tile < nt) { found = 1; tile = nt - 1 - tile; break; }
@@ -447,7 +447,7 @@ int launch(const AttnParams& p, int n_tiles, cudaStream_t stream) {
                                  smem));
     attr_set = true;
   }
-  dim3 grid(n_tiles, p.kv_heads, p.splits);
+  dim3 grid(p.kv_heads, n_tiles, p.splits);
   gb_launch(attention_tc_kernel<HD, NW, KSPLIT>, dim3(grid), dim3(32 * NW), smem, stream, p);
   return GB_OK;
 }
@@ -508,6 +508,7 @@ GB_API int gb_attention_tc(const void* q, long long ldq, const void* k_pages, co
   // upper bound of the number of tiles: sum_r ceil(q_len_r / tpt) <= n_tokens / tpt + n_requests
   const long long n_tiles = small ? n_requests : ((long long)n_tokens + tpt - 1) / tpt + n_requests;
   if (!small) splits = 1;
+  if (n_tiles > 65535) GB_FAIL(GB_ERR_ARG, "gb_attention_tc: %lld tiles in one launch", n_tiles);
   AttnParams p;
   p.q = (const bf16*)q; p.ldq = ldq; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
   p.block_table = block_table; p.bt_stride = bt_stride; p.page_size = page_size; p.n_pages = n_pages;

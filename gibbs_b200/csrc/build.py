@@ -26,7 +26,7 @@ HERE = Path(__file__).resolve().parent
 # it computes in bfloat16.
 LIBRARIES = {
     "core": ["errors.cu", "elementwise.cu", "gemm_simt.cu", "conv.cu", "attention.cu", "sampling.cu"],
-    "tensorcore": ["errors.cu", "gemm_tc.cu", "attention_tc.cu"],
+    "tensorcore": ["errors.cu", "gemm_tc.cu", "attention_tc.cu", "attention_tcgen05.cu"],
 }
 
 NVCC_FLAGS = [

@@ -501,10 +501,27 @@ def attention_splits(n_requests: int, kv_heads: int, max_ctx_len: int) -> int:
     return max(1, min(16, by_sm, by_len))
 
 
+# prompt portions on tcgen05 (csrc/attention_tcgen05.cu); 0: keep them on the mma.sync kernel
+_ATTN_TCGEN05 = os.environ.get("GIBBS_B200_ATTN_TCGEN05", "1") != "0"
+
+
 def _attention_tc(q, heads, kv_heads, head_dim, k_pages, v_pages, block_table, scale, window, out, status, step):
     lib = library("tensorcore")
     n, group = q.shape[0], heads // kv_heads
     small = step.max_q_len * group <= 16 and group <= 16
+    if not small and _ATTN_TCGEN05 and lib.gb_attention_tcgen05_supported(
+            _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(k_pages.shape[2]), _c_ll(_rows(q, "q")),
+            _c_ll(_rows(out, "out"))) and out.data_ptr() % 16 == 0 and scale > 0:
+        rc = lib.gb_attention_tcgen05(
+            _ptr(q), _c_ll(_rows(q, "q")), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+            _c_int(block_table.shape[1]), _c_int(k_pages.shape[2]), _c_int(k_pages.shape[0]), _ptr(step.q_start),
+            _ptr(step.q_len), _ptr(step.start_pos), _ptr(out), _c_ll(_rows(out, "out")), _c_int(step.n_requests),
+            _c_int(n), _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_float(scale), _c_int(window or 0),
+            _ptr(status), _stream())
+        if rc < 0:
+            check(lib, rc)
+        _launched(rc)
+        return out
     splits = attention_splits(step.n_requests, kv_heads, step.max_ctx_len) if small else 1
     ws = None
     if splits > 1:

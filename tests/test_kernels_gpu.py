@@ -502,6 +502,14 @@ TC_CASES = [
     (6, 3, 96, 16, 33, [400, 31, 32], [1, 1, 1]),
     (16, 1, 64, 16, 0, [300, 1], [1, 1]),
     (2, 1, 112, 64, 0, [129], [3]),
+    # prompt portions at head sizes 64 and 128 (the tcgen05 kernel): every group size, page sizes 8 to 128,
+    # windows within a tile and across tiles, decoded tokens beside a portion
+    (16, 1, 64, 32, 0, [0, 300], [200, 5]),
+    (4, 4, 64, 128, 0, [100], [260]),
+    (8, 4, 128, 8, 150, [1000, 0], [40, 300]),
+    (32, 8, 64, 16, 0, [2047, 5, 300], [1, 1, 500]),
+    (8, 2, 64, 64, 257, [600], [700]),
+    (2, 1, 64, 16, 0, [0], [1000]),
 ]
 
 
