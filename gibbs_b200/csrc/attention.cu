@@ -92,6 +92,96 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, long long ld, con
   }
 }
 
+// Prompt portions in bfloat16 at head sizes 32, 64 and 128 with the half-split rotation over the
+// whole head: one block per token.  The token's cosines and sines are worked out once (not once
+// per head) into shared memory; then hd/8 threads share a head, each with 8 neighbouring values
+// in one 16-byte load, the sum of squares and the rotation partner (hd/2 further) coming from the
+// neighbouring threads by shuffles.  Same arithmetic as the kernel above, value by value.
+__global__ void qk_norm_rope_store_vec_kernel(bf16* __restrict__ qkv, long long ld, const float* __restrict__ q_gain,
+                                              const float* __restrict__ k_gain, float eps,
+                                              const float* __restrict__ inv_freq, const int* __restrict__ tok_req,
+                                              const int* __restrict__ tok_pos, const int* __restrict__ block_table,
+                                              int bt_stride, int page_size, bf16* __restrict__ k_pages,
+                                              bf16* __restrict__ v_pages, int n_pages, int heads, int kv_heads, int hd,
+                                              int write_kv, int* __restrict__ status) {
+  __shared__ float cs[64], sn[64];                       // hd / 2 <= 64
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int pos = tok_pos[t];
+  const int half = hd >> 1;
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    const float ang = (float)pos * inv_freq[j];
+    cs[j] = cosf(ang);
+    sn[j] = sinf(ang);
+  }
+  __syncthreads();
+  const int tps = hd >> 3;                               // threads per head: 4, 8 or 16
+  const int slots = heads + (write_kv ? 2 * kv_heads : 0);
+  int page = 0;
+  if (write_kv) {
+    page = block_table[(size_t)tok_req[t] * bt_stride + pos / page_size];
+    if (page < 0 || page >= n_pages) {
+      if (threadIdx.x == 0) atomicExch(status, STATUS_BAD_PAGE_WRITE);
+      write_kv = 0;                                      // q is still processed
+    }
+  }
+  const int total = slots * tps;                         // a multiple of 4; the block is padded to whole warps
+  for (int idx0 = 0; idx0 < total; idx0 += blockDim.x) {
+    const int idx = idx0 + threadIdx.x;
+    const bool active = idx < total;
+    const int slot = active ? idx / tps : 0, sub = active ? idx - slot * tps : 0;
+    const bool is_q = slot < heads;
+    const bool is_k = !is_q && slot < heads + kv_heads;
+    const int kvh = is_q ? 0 : (is_k ? slot - heads : slot - heads - kv_heads);
+    bf16* src = qkv + (size_t)t * ld + (size_t)slot * hd + sub * 8;
+    float v[8];
+    {
+      const uint4 raw = active ? *reinterpret_cast<const uint4*>(src) : make_uint4(0, 0, 0, 0);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        v[2 * e] = f.x;
+        v[2 * e + 1] = f.y;
+      }
+    }
+    bf16* dst = src;
+    if (!is_q) dst = (is_k ? k_pages : v_pages) + (((size_t)page * kv_heads + kvh) * page_size + pos % page_size) * hd + sub * 8;
+    const bool store = active && (is_q || write_kv);
+    const float* gain = is_q ? q_gain : (is_k ? k_gain : nullptr);
+    // every lane takes part in the shuffles; a head's threads are neighbours within a warp
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+    for (int o = tps >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (gain) {
+      const float scale = 1.0f / sqrtf(ss / (float)hd + eps);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = v[e] * scale * gain[sub * 8 + e];
+    }
+    float w[8];                                          // the partner's values: hd/2 further (or back)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) w[e] = __shfl_xor_sync(0xffffffffu, v[e], tps >> 1);
+    if (is_q || is_k) {
+      const bool lower = sub < (tps >> 1);
+      const int j0 = (lower ? sub : sub - (tps >> 1)) * 8;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float c = cs[j0 + e], sv = sn[j0 + e];
+        v[e] = lower ? (v[e] * c - w[e] * sv) : (w[e] * sv + v[e] * c);
+      }
+    }
+    if (store) {
+      uint4 o;
+      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) oh[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+      *reinterpret_cast<uint4*>(dst) = o;
+    }
+  }
+}
+
 // The same for q, k, v given as the partial tiles of the split-K product that made them
 // (ws[split][token][cols], 32-bit, plus bias): the sums are rounded to bfloat16 where the
 // product's own reduction would have rounded them.  q goes to q_out [n_tokens, heads*hd].
@@ -284,6 +374,17 @@ GB_API int gb_qk_norm_rope_store(void* qkv, int dtype, long long ld, const float
     GB_FAIL(GB_ERR_ARG, "gb_qk_norm_rope_store: rotary_dim %d for head_dim %d", rotary_dim, hd);
   if (page_size <= 0) GB_FAIL(GB_ERR_ARG, "gb_qk_norm_rope_store: page_size %d", page_size);
   const int slots = heads + (write_kv ? 2 * kv_heads : 0);
+  if (dtype == GB_BF16 && n_tokens >= 32 && (hd == 32 || hd == 64 || hd == 128) && inv_freq != nullptr && !adjacent &&
+      rotary_dim == hd && ld % 8 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_pages & 15) == 0 &&
+      ((uintptr_t)v_pages & 15) == 0) {
+    int threads = slots * (hd / 8);
+    threads = threads > 512 ? 512 : ((threads + 31) / 32) * 32;
+    gb_launch(qk_norm_rope_store_vec_kernel, dim3(n_tokens), dim3(threads), 0, stream, (bf16*)qkv, ld, q_gain, k_gain,
+              eps, inv_freq, tok_req, tok_pos, block_table, bt_stride, page_size, (bf16*)k_pages, (bf16*)v_pages,
+              n_pages, heads, kv_heads, hd, write_kv, status);
+    GB_CHECK_LAUNCH("gb_qk_norm_rope_store (vector)");
+    return GB_OK;
+  }
   const long long warps = (long long)n_tokens * slots;
   const int blocks = gb_div_up(warps, 4);
   if (dtype == GB_F32)

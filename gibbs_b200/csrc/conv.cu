@@ -110,6 +110,101 @@ __global__ void short_conv_out_vec8_kernel(const bf16* __restrict__ bcx, long lo
   *reinterpret_cast<uint4*>(out + (size_t)t * hidden + c) = o;
 }
 
+// The same for narrow filters (K <= 4), eight consecutive tokens per thread: the products B*x a
+// filter position needs are kept in registers while the window slides along the tokens, so every
+// row of [B | C | x] is read once instead of K times and the taps once per thread.  Where the run
+// crosses into another request the window restarts from that request's state.  The terms are
+// added in the order of the kernels above (oldest tap first), so the results are the same bits.
+template <int K>
+__global__ void short_conv_out_run_kernel(const bf16* __restrict__ bcx, long long ld, const float* __restrict__ taps,
+                                          const float* __restrict__ bias, const float* __restrict__ state,
+                                          long long slot_stride, const int* __restrict__ slot_ids,
+                                          const int* __restrict__ tok_req, const int* __restrict__ q_start,
+                                          bf16* __restrict__ out, int n_tokens, int hidden) {
+  constexpr int RUN = 8;
+  pdl_trigger();
+  pdl_wait();
+  const int groups = hidden >> 3;
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long n_runs = ((long long)n_tokens + RUN - 1) / RUN;
+  if (gid >= n_runs * groups) return;
+  const int run = (int)(gid / groups), c = (int)(gid - (long long)run * groups) << 3;
+  auto unpack = [](uint4 u, float* f) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 v = __bfloat1622float2(h[e]);
+      f[2 * e] = v.x;
+      f[2 * e + 1] = v.y;
+    }
+  };
+  float tap[K][8], bs[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+#pragma unroll
+    for (int j = 0; j < K; ++j) tap[j][e] = taps[(size_t)(c + e) * K + j];
+    bs[e] = bias ? bias[c + e] : 0.f;
+  }
+  float win[K][8];                                           // win[j]: the product that meets tap j for the current token
+  int cur_req = -1, first = 0;
+  const int t0 = run * RUN, t1 = min(t0 + RUN, n_tokens);
+  for (int t = t0; t < t1; ++t) {
+    const int r = tok_req[t];
+    bool restart = r != cur_req;
+    if (restart) {
+      cur_req = r;
+      first = q_start[r];
+    }
+    const int i = t - first;
+    const bf16* row = bcx + (size_t)t * ld;
+    float b[8], x[8], g[8];
+    unpack(*reinterpret_cast<const uint4*>(row + c), b);
+    unpack(*reinterpret_cast<const uint4*>(row + 2 * hidden + c), x);
+    unpack(*reinterpret_cast<const uint4*>(row + hidden + c), g);
+    if (restart) {
+      // the K-1 older positions: earlier tokens of this request in the batch, or its state
+      const float* st = state + (size_t)slot_ids[r] * slot_stride;
+#pragma unroll
+      for (int j = 0; j < K - 1; ++j) {
+        const int src = i - (K - 1 - j);
+        if (src >= 0) {
+          const bf16* prow = bcx + (size_t)(first + src) * ld;
+          float pb[8], px[8];
+          unpack(*reinterpret_cast<const uint4*>(prow + c), pb);
+          unpack(*reinterpret_cast<const uint4*>(prow + 2 * hidden + c), px);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) win[j][e] = pb[e] * px[e];
+        } else {
+          const float4* sp = reinterpret_cast<const float4*>(st + (size_t)(K - 1 + src) * hidden + c);
+          const float4 s0 = sp[0], s1 = sp[1];
+          win[j][0] = s0.x; win[j][1] = s0.y; win[j][2] = s0.z; win[j][3] = s0.w;
+          win[j][4] = s1.x; win[j][5] = s1.y; win[j][6] = s1.z; win[j][7] = s1.w;
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) win[K - 1][e] = b[e] * x[e];
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float a = 0.f;
+#pragma unroll
+      for (int j = 0; j < K; ++j) a = fmaf(tap[j][e], win[j][e], a);
+      acc[e] = a + bs[e];
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) oh[e] = __floats2bfloat162_rn(g[2 * e] * acc[2 * e], g[2 * e + 1] * acc[2 * e + 1]);
+    *reinterpret_cast<uint4*>(out + (size_t)t * hidden + c) = o;
+    // slide: the next token's tap j meets what tap j+1 met now
+#pragma unroll
+    for (int j = 0; j < K - 1; ++j)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) win[j][e] = win[j + 1][e];
+  }
+}
+
 template <typename T>
 __global__ void short_conv_state_kernel(const T* __restrict__ bcx, long long ld, float* __restrict__ state,
                                         long long slot_stride, const int* __restrict__ slot_ids,
@@ -256,7 +351,19 @@ GB_API int gb_short_conv(const void* bcx, int dtype, long long ld, const float* 
   } else if (dtype == GB_BF16) {
     const bool vec = hidden % 8 == 0 && ld % 8 == 0 && slot_stride % 4 == 0 && ((uintptr_t)bcx & 15) == 0 &&
                      ((uintptr_t)out & 15) == 0 && ((uintptr_t)state & 15) == 0;
-    if (vec)
+    if (vec && K <= 4) {
+      const long long work = (((long long)n_tokens + 7) / 8) * (hidden / 8);
+      const dim3 grid(gb_div_up(work, 128)), block(128);
+      if (K == 2)
+        gb_launch(short_conv_out_run_kernel<2>, grid, block, 0, stream, (const bf16*)bcx, ld, taps, bias,
+                  (const float*)state, slot_stride, slot_ids, tok_req, q_start, (bf16*)out, n_tokens, hidden);
+      else if (K == 3)
+        gb_launch(short_conv_out_run_kernel<3>, grid, block, 0, stream, (const bf16*)bcx, ld, taps, bias,
+                  (const float*)state, slot_stride, slot_ids, tok_req, q_start, (bf16*)out, n_tokens, hidden);
+      else
+        gb_launch(short_conv_out_run_kernel<4>, grid, block, 0, stream, (const bf16*)bcx, ld, taps, bias,
+                  (const float*)state, slot_stride, slot_ids, tok_req, q_start, (bf16*)out, n_tokens, hidden);
+    } else if (vec)
       gb_launch(short_conv_out_vec8_kernel, dim3(gb_div_up(total / 8, threads)), dim3(threads), 0, stream,
                 (const bf16*)bcx, ld, taps, bias, (const float*)state, slot_stride, slot_ids, tok_req, q_start,
                 (bf16*)out, n_tokens, hidden, K);

@@ -1256,7 +1256,12 @@ GB_API int gb_linear_tc(const void* X, long long ldx, const void* W, long long l
   int rc;
   const long long n_tiles = (long long)gb_div_up(N, BM) * gb_div_up(M, bn);
   const long long pair_tiles = (long long)gb_div_up(N, 2 * BM) * gb_div_up(M, PairCfg::BNP);
-  if (bn == 128 && splits == 1 && M >= 192 && pair_tiles >= 32 && gb_pair()) {
+  // Products with no more 256 x 256 tiles than there are CTA pairs would run one tile per pair,
+  // start-up, pipeline fill and epilogue all exposed; two 128 x 128 CTAs per SM do those a little
+  // faster.  GIBBS_B200_PAIR_MIN_TILES moves the threshold (for comparison runs).
+  static int pair_min = -1;
+  if (pair_min < 0) { const char* e = getenv("GIBBS_B200_PAIR_MIN_TILES"); pair_min = e ? atoi(e) : 65; }
+  if (bn == 128 && splits == 1 && M >= 192 && pair_tiles >= pair_min && gb_pair()) {
     rc = launch_pair(tw, tx, p, stream);
   } else if (bn == 128 && splits == 1 && n_tiles > 148 && gb_persistent()) {
     rc = launch_persistent<128>(tw, tx, p, stream);

@@ -268,6 +268,11 @@ CASES = [
     (2, 1, 128, 64, False, 16, 0, False),
     (4, 2, 16, 16, False, 8, 7, True),
     (8, 8, 8, 8, False, 16, 0, True),
+    # bfloat16 portions of 32 tokens and more at head sizes 32, 64, 128 with the whole head rotated take the
+    # vector kernel (one block per token); more slots than a block has threads, and no per-head norm
+    (32, 8, 64, 64, False, 16, 0, True),
+    (40, 40, 128, 128, False, 16, 0, True),
+    (2, 1, 128, 128, False, 32, 0, False),
 ]
 
 
