@@ -22,6 +22,12 @@ _c_int, _c_ll, _c_float, _c_void = ctypes.c_int, ctypes.c_longlong, ctypes.c_flo
 
 
 _LAUNCHES = 0
+_LIBS: dict = {}        # kernel libraries already loaded, by name
+
+
+def _lib(name: str):
+    lib = _LIBS[name] = library(name)
+    return lib
 
 
 def _launched(n: int = 1) -> None:
@@ -123,19 +129,32 @@ def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
     """out[r, :] = x[rows[r] or r, :] * rsqrt(mean(x^2) + eps) * gain; x is 32-bit.
     ``pending`` = (partials [splits, n, dim], bias or None): sums a split-K
     product left to be added to x first (and, without ``rows``, written back)."""
-    _need_cuda(x, gain, out, rows)
-    lib = library("core")
-    dim = x.shape[1]
+    lib = _LIBS.get("core") or _lib("core")
+    n_x, dim = x.shape
+    if not (x.is_cuda and gain.is_cuda and out.is_cuda):
+        _need_cuda(x, gain, out)
     if x.dtype != torch.float32:
         raise KernelError("rmsnorm: the input (the residual stream) is float32")
-    ldx = _rows(x, "rmsnorm x")
+    if dim > 1 and x.stride(1) != 1:
+        raise KernelError("rmsnorm x: expected a 2-d tensor with contiguous rows")
     n_rows = out.shape[0]
     if not out.is_contiguous() or out.shape[1] != dim:
         raise KernelError("rmsnorm: out must be contiguous [rows, dim]")
-    if rows is None and n_rows != x.shape[0]:
-        raise KernelError("rmsnorm: out has a different number of rows than x")
-    _f32vec(gain, dim, "rmsnorm gain")
-    _i32(rows, "rmsnorm rows")
+    if rows is None:
+        if n_rows != n_x:
+            raise KernelError("rmsnorm: out has a different number of rows than x")
+    else:
+        _need_cuda(rows)
+        _i32(rows, "rmsnorm rows")
+    if gain.dtype != torch.float32 or gain.numel() != dim or not gain.is_contiguous():
+        _f32vec(gain, dim, "rmsnorm gain")
+    odt = out.dtype
+    if odt == torch.bfloat16:
+        code = BF16
+    elif odt == torch.float32:
+        code = F32
+    else:
+        raise KernelError(f"kernels take float32 and bfloat16 tensors, not {odt}")
     ws = pbias = None
     splits = 0
     if pending is not None:
@@ -143,11 +162,18 @@ def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
         splits = ws.shape[0]
         if ws.dtype != torch.float32 or not ws.is_contiguous() or ws.shape[1:] != x.shape:
             raise KernelError("rmsnorm: pending partial sums must be contiguous float32 [splits, n, dim]")
-        _f32vec(pbias, dim, "rmsnorm pending bias")
+        if pbias is not None:
+            _need_cuda(pbias)
+            _f32vec(pbias, dim, "rmsnorm pending bias")
     _launched(1)
-    check(lib, lib.gb_rmsnorm(_ptr(x), _c_ll(ldx), _ptr(gain), _ptr(out), dtype_code(out.dtype), _ptr(rows),
-                              _c_int(n_rows), _c_int(dim), _c_float(eps), _ptr(ws), _c_int(splits),
-                              _c_ll(x.shape[0]), _ptr(pbias), _stream()))
+    rc = lib.gb_rmsnorm(_c_void(x.data_ptr()), _c_ll(x.stride(0) if n_x > 1 else max(x.stride(0), dim)),
+                        _c_void(gain.data_ptr()), _c_void(out.data_ptr()), _c_int(code),
+                        _NULL if rows is None else _c_void(rows.data_ptr()), _c_int(n_rows), _c_int(dim), _c_float(eps),
+                        _NULL if ws is None else _c_void(ws.data_ptr()), _c_int(splits), _c_ll(n_x),
+                        _NULL if pbias is None else _c_void(pbias.data_ptr()),
+                        _STREAM if _STREAM is not None else _stream())
+    if rc:
+        check(lib, rc)
     return out
 
 
@@ -201,7 +227,18 @@ def device_status(device) -> torch.Tensor:
     t = _STATUS.get(key)
     if t is None:
         t = _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+        _STATUS_PTR[key] = _c_void(t.data_ptr())
     return t
+
+
+_STATUS_PTR: dict = {}
+_NULL, _ZERO, _ONE = _c_void(0), _c_int(0), _c_int(1)
+
+
+def _status_ptr(t: torch.Tensor):
+    """The status word of the device ``t`` lives on, as a C pointer."""
+    p = _STATUS_PTR.get(t.device.index)
+    return p if p is not None else _c_void(device_status(t.device).data_ptr())
 
 
 # tuning switches of the tensor-core product: prefetch the next weight towards L2; evict-first hint
@@ -220,40 +257,56 @@ def linear_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     the kernel splits K, nothing is written to ``out``; the partial sums
     [splits, m, n] are returned instead, for the caller's next kernel to add
     (without the bias).  Otherwise returns ``out``."""
-    _need_cuda(a, w, bias, out, prefetch)
-    lib = library("tensorcore")
+    # (this wrapper runs some seventy times a step: its checks are the cheap ones)
+    lib = _LIBS.get("tensorcore") or _lib("tensorcore")
     m, k = a.shape
-    n = w.shape[0]
+    n, kw = w.shape
     n_out = n // 2 if swiglu else n
-    if w.shape[1] != k or out.shape[0] != m or out.shape[1] != n_out:
+    if not (a.is_cuda and w.is_cuda and out.is_cuda):
+        _need_cuda(a, w, out)
+    if kw != k or out.shape[0] != m or out.shape[1] != n_out:
         raise KernelError(f"linear: shapes a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} disagree")
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("linear_tc: bfloat16 operands expected")
+    if a.stride(1) != 1 or w.stride(1) != 1 or (n_out > 1 and out.stride(1) != 1):
+        raise KernelError("linear: expected 2-d tensors with contiguous rows")
+    odt = out.dtype
     if swiglu:
-        if out.dtype != torch.bfloat16 or n % 128:
+        if odt != torch.bfloat16 or n % 128:
             raise KernelError("linear_tc: the SwiGLU epilogue writes bfloat16 and needs 2*features % 128 == 0")
         mode = 3
     elif accumulate:
-        if out.dtype != torch.float32:
+        if odt != torch.float32:
             raise KernelError("linear_tc: accumulation needs a float32 output")
         mode = 2
+    elif odt == torch.bfloat16:
+        mode = 0
+    elif odt == torch.float32:
+        mode = 1
     else:
-        mode = 0 if out.dtype == torch.bfloat16 else 1
-        dtype_code(out.dtype)
-    _f32vec(bias, n, "linear bias")
-    splits = _SPLITS.get((m, n, k))
+        raise KernelError(f"kernels take float32 and bfloat16 tensors, not {odt}")
+    if bias is not None:
+        _need_cuda(bias)
+        _f32vec(bias, n, "linear bias")
+    key = (m, n, k)
+    splits = _SPLITS.get(key)
     if splits is None:
-        splits = _SPLITS[(m, n, k)] = lib.gb_linear_tc_splits(_c_int(m), _c_int(n), _c_int(k))
+        splits = _SPLITS[key] = lib.gb_linear_tc_splits(_c_int(m), _c_int(n), _c_int(k))
     ws = torch.empty((splits, m, n), dtype=torch.float32, device=a.device) if splits > 1 else None
     defer = bool(defer and (accumulate or mode == 0) and splits > 1)
+    pf_bytes = 0
     if not _TC_PREFETCH:
         prefetch = None
-    pf_bytes = prefetch.numel() * prefetch.element_size() if prefetch is not None else 0
+    elif prefetch is not None:
+        _need_cuda(prefetch)
+        pf_bytes = prefetch.numel() * prefetch.element_size()
     rc = lib.gb_linear_tc(
-        _ptr(a), _c_ll(_rows(a, "linear a")), _ptr(w), _c_ll(_rows(w, "linear w")), _ptr(bias), _ptr(out),
-        _c_int(mode), _c_ll(_rows(out, "linear out")), _c_int(m), _c_int(n), _c_int(k), _ptr(ws),
-        _c_int(1 if defer else 0), _ptr(prefetch), _c_ll(pf_bytes), _c_int(_TC_FLAGS),
-        _ptr(device_status(a.device)), _stream())
+        _c_void(a.data_ptr()), _c_ll(a.stride(0) if m > 1 else max(a.stride(0), k)), _c_void(w.data_ptr()),
+        _c_ll(w.stride(0) if n > 1 else max(w.stride(0), k)), _NULL if bias is None else _c_void(bias.data_ptr()),
+        _c_void(out.data_ptr()), _c_int(mode), _c_ll(out.stride(0) if m > 1 else max(out.stride(0), n_out)), _c_int(m),
+        _c_int(n), _c_int(k), _NULL if ws is None else _c_void(ws.data_ptr()), _ONE if defer else _ZERO,
+        _NULL if prefetch is None else _c_void(prefetch.data_ptr()), _c_ll(pf_bytes), _c_int(_TC_FLAGS),
+        _status_ptr(a), _STREAM if _STREAM is not None else _stream())
     if rc < 0:
         check(lib, rc)
     _launched(rc)
