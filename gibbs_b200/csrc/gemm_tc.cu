@@ -51,10 +51,14 @@ constexpr int STATUS_TIMEOUT = 16;
 
 enum OutMode : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2, OUT_SWIGLU = 3 };
 
-template <int BN> struct Cfg {
+// DEEP (64-token tiles): a launch with no more CTAs than SMs (every decode product but the head)
+// has one CTA per SM anyway; it then takes most of the SM's shared memory for its pipeline, so
+// that as many weight bytes are on their way as with the narrower tiles.
+template <int BN, bool DEEP = false> struct Cfg {
   static constexpr int X_TILE_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES;
-  static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 3 : (BN >= 64 ? 4 : 5));
+  static constexpr int STAGES = DEEP ? (BN >= 64 ? 8 : (BN >= 32 ? 9 : 10))
+                                     : (BN >= 256 ? 4 : (BN >= 128 ? 3 : (BN >= 64 ? 4 : 5)));
   static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;   // + room to align to 1024
 };
@@ -91,12 +95,12 @@ __device__ __forceinline__ void store_value(const GemmParams& p, int m, int n, f
   }
 }
 
-template <int BN>
+template <int BN, bool DEEP>
 __global__ void __launch_bounds__(192)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                const GemmParams p) {
   pdl_trigger();   // the kernel after this one may start its prologue now
-  using C = Cfg<BN>;
+  using C = Cfg<BN, DEEP>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t full_bar[C::STAGES], empty_bar[C::STAGES], tmem_full_bar;
   __shared__ uint32_t tmem_slot;
@@ -1091,17 +1095,42 @@ void plan(int M, int N, int K, int* bn, int* splits, int* kb_per_split) {
   *splits = gb_div_up(total_kb, *kb_per_split);
 }
 
-template <int BN>
-int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
+// GIBBS_B200_DEEP_PIPELINE=0 keeps one-wave launches on the short pipeline (for comparison runs).
+int gb_deep() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("GIBBS_B200_DEEP_PIPELINE");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v;
+}
+
+template <int BN, bool DEEP>
+int launch_as(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, dim3 grid, cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
-    GB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 Cfg<BN>::SMEM_BYTES));
+    GB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<BN, DEEP>::SMEM_BYTES));
     attr_set = true;
   }
-  dim3 grid(gb_div_up(p.N, BM), gb_div_up(p.M, BN), p.splits);
-  gb_launch(gemm_tc_kernel<BN>, dim3(grid), dim3(192), Cfg<BN>::SMEM_BYTES, stream, tw, tx, p);
+  gb_launch(gemm_tc_kernel<BN, DEEP>, dim3(grid), dim3(192), Cfg<BN, DEEP>::SMEM_BYTES, stream, tw, tx, p);
   return GB_OK;
+}
+
+template <int BN>
+int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
+  dim3 grid(gb_div_up(p.N, BM), gb_div_up(p.M, BN), p.splits);
+  if (BN == 64) {   // (measured: narrower tiles gain nothing from the deeper pipeline and lose the overlap with the next launch)
+    static int n_sm = 0;
+    if (n_sm == 0) {
+      int dev = 0;
+      GB_CUDA(cudaGetDevice(&dev));
+      GB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+    }
+    if ((long long)grid.x * grid.y * grid.z <= n_sm && gb_deep())
+      return launch_as<BN, (BN == 64)>(tw, tx, p, grid, stream);
+  }
+  return launch_as<BN, false>(tw, tx, p, grid, stream);
 }
 
 template <int BN>

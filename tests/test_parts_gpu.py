@@ -336,3 +336,149 @@ def test_hand_made_model_with_toy_mixer_repeated_layer_shared_cache_and_window(d
             assert bad is None, f"{rid}: first wrong position {bad}"
     # the windowed group gave pages back while requests were still running
     assert eng.cache.free_pages() == [40, 40] and not eng.cache.live
+
+
+# ---------------------------------------------------------------------------
+# a feed-forward with routing and another position encoding, both defined here
+# ---------------------------------------------------------------------------
+
+class ToyRoutedFFN:
+    """Top-1 routing among a few small experts, written with tensor operations:
+    p = softmax(router h); e = argmax p; out = p[e] * W_out[e] relu(W_in[e] h)."""
+    category = "feed_forward"
+
+    @classmethod
+    def declare(cls, params):
+        from gibbs_b200.parts import TensorDecl
+        h, f, e = params["hidden"], params["inner"], params["experts"]
+        return {"router": TensorDecl.of(e, h), "w_in": TensorDecl.of(e * f, h), "w_out": TensorDecl.of(e * h, f)}
+
+    def __init__(self, params, tensors, rt):
+        self.rt = rt
+        self.h, self.f, self.e = params["hidden"], params["inner"], params["experts"]
+        self.router = tensors["router"].float()
+        self.w_in = tensors["w_in"].float().reshape(self.e, self.f, self.h)
+        self.w_out = tensors["w_out"].float().reshape(self.e, self.h, self.f)
+
+    def kernel_libraries(self):
+        return ("core",)
+
+    def forward(self, h, residual, step):
+        x = h.float()
+        p = torch.softmax(x @ self.router.T, -1)                       # router logits and softmax in 32-bit
+        top, choice = p.max(-1)
+        hidden = torch.relu(torch.einsum("efh,nh->nef", self.w_in, x))
+        every = torch.einsum("ehf,nef->neh", self.w_out, hidden)        # all experts; the toy keeps the chosen one
+        picked = every[torch.arange(x.shape[0], device=x.device), choice]
+        residual.add_(top[:, None] * picked)
+
+
+def _toy_scaled_rope():
+    from gibbs_b200.parts import PositionEncoding, Rotary
+
+    class ToyScaledRope(PositionEncoding):
+        """Half-split rotation of the first ``rotary_dim`` columns with every frequency divided by
+        ``factor`` (positions stretched), the rest of the head left as it is."""
+
+        def __init__(self, params, tensors, rt):
+            super().__init__(params, tensors, rt)
+            rd = int(params["rotary_dim"])
+            inv = plain.rope_inv_freq(rd, float(params["theta"]), torch.float32) / float(params["factor"])
+            self.inv_freq, self.rd = inv.to(rt.device), rd
+
+        def rotary(self):
+            return Rotary(self.inv_freq, self.rd, False)
+
+    return ToyScaledRope
+
+
+def _toy_plan(hidden=48, heads=3, kvh=1, hd=32, rd=16, factor=4.0, inner=64, experts=3, vocab=200, eps=1e-6):
+    from gibbs_b200.config import LayerSpec, ModelPlan, OrderEntry, PartSpec
+
+    def norm(name):
+        return PartSpec("rmsnorm", {"dim": hidden, "eps": eps}, {"weight": name})
+
+    attn = PartSpec("gqa_attention", {
+        "hidden": hidden, "heads": heads, "kv_heads": kvh, "head_dim": hd, "bias": False, "qk_norm": False,
+        "scale": 1 / math.sqrt(hd), "window": None,
+        "position": PartSpec("toy_scaled_rope", {"rotary_dim": rd, "theta": 1e4, "factor": factor})},
+        {"q_proj.weight": "a.q", "k_proj.weight": "a.k", "v_proj.weight": "a.v", "out_proj.weight": "a.o"})
+    routed = PartSpec("toy_routed", {"hidden": hidden, "inner": inner, "experts": experts},
+                      {"router": "f.r", "w_in": "f.in", "w_out": "f.out"})
+    conv = PartSpec("gated_short_conv", {"hidden": hidden, "kernel": 3, "bias": False},
+                    {"in_proj.weight": "c.in", "conv.weight": "c.taps", "out_proj.weight": "c.out"})
+    dense = PartSpec("swiglu", {"hidden": hidden, "inner": 64, "bias": False},
+                     {"gate.weight": "d.g", "up.weight": "d.u", "down.weight": "d.d"})
+    layers = (LayerSpec("prenorm_residual", norm("n0"), attn, norm("n1"), routed),
+              LayerSpec("prenorm_residual", norm("n2"), conv, norm("n3"), dense))
+    emb = PartSpec("token_embedding", {"vocab": vocab, "dim": hidden}, {"weight": "emb"})
+    return ModelPlan("toy-routed", vocab, hidden, 256, emb, layers, (OrderEntry(0), OrderEntry(1)), norm("fn"),
+                     PartSpec("lm_head", {"vocab": vocab, "dim": hidden}, {"weight": "head"}))
+
+
+def _plain_toy_model(w, ids, hidden=48, heads=3, kvh=1, hd=32, rd=16, factor=4.0, inner=64, experts=3, eps=1e-6):
+    n = len(ids)
+    pos = torch.arange(n)
+    x = w["emb"][torch.tensor(ids)]
+    # layer 0: attention with the stretched partial rotation, then the routed feed-forward
+    h = plain.rms_norm(x, w["n0"], eps)
+    inv = plain.rope_inv_freq(rd, 1e4, torch.float64) / factor
+    q = (h @ w["a.q"].T).reshape(n, heads, hd).clone()
+    k = (h @ w["a.k"].T).reshape(n, kvh, hd).clone()
+    v = (h @ w["a.v"].T).reshape(n, kvh, hd)
+    q[..., :rd] = plain.rope_half_split(q[..., :rd], pos, inv)
+    k[..., :rd] = plain.rope_half_split(k[..., :rd], pos, inv)
+    o = plain.causal_attention(q, k, v, 1 / math.sqrt(hd))
+    x = x + o.reshape(n, heads * hd) @ w["a.o"].T
+    h = plain.rms_norm(x, w["n1"], eps)
+    p = torch.softmax(h @ w["f.r"].T, -1)
+    out = torch.zeros_like(x)
+    for i in range(n):
+        e = int(p[i].argmax())
+        w_in = w["f.in"].reshape(experts, inner, hidden)[e]
+        w_out = w["f.out"].reshape(experts, hidden, inner)[e]
+        out[i] = p[i, e] * (w_out @ torch.relu(w_in @ h[i]))
+    x = x + out
+    # layer 1: the built-in short convolution and SwiGLU
+    h = plain.rms_norm(x, w["n2"], eps)
+    bcx = h @ w["c.in"].T
+    b, c, xx = bcx[:, :hidden], bcx[:, hidden:2 * hidden], bcx[:, 2 * hidden:]
+    x = x + (c * plain.causal_conv1d(b * xx, w["c.taps"])) @ w["c.out"].T
+    h = plain.rms_norm(x, w["n3"], eps)
+    g, u = h @ w["d.g"].T, h @ w["d.u"].T
+    x = x + (g / (1 + torch.exp(-g)) * u) @ w["d.d"].T
+    return plain.rms_norm(x, w["fn"], eps) @ w["head"].T
+
+
+def test_routed_feed_forward_and_another_position_encoding_defined_in_the_test():
+    """A feed-forward that routes and a position encoding of another kind are registered from
+    here, built from a hand-written plan beside built-in parts and stepped in portions; nothing
+    in the framework's files knows them."""
+    from gibbs_b200 import Engine, register_part
+    from gibbs_b200.parts import build_model
+    from gibbs_b200.weights import TensorDict, expected_tensors
+    from helpers import first_wrong, run_trace_on_engine, trace_portions, trace_tail_decoded, trace_whole, random_ids
+    register_part("feed_forward", "toy_routed", ToyRoutedFFN)
+    register_part("position", "toy_scaled_rope", _toy_scaled_rope())
+    plan = _toy_plan()
+    torch.manual_seed(9)
+    tensors = {}
+    for name, decl in expected_tensors(plan).items():
+        shape = decl.shapes[0]
+        if len(shape) == 1:
+            tensors[name] = 1 + 0.1 * torch.randn(shape)
+        elif name == "f.r":
+            tensors[name] = torch.randn(shape) * 2.0          # decisive routing: no near-ties between experts
+        else:
+            tensors[name] = torch.randn(shape) * (0.3 if name == "emb" else 1.0 / math.sqrt(shape[-1]))
+    model = build_model(plan, TensorDict(tensors), torch.float32, DEV)
+    eng = Engine(model, n_pages=48, page_size=8, max_requests=4, max_step_tokens=256, use_graphs=False)
+    w64 = {k: v.double() for k, v in tensors.items()}
+    reqs = {f"r{i}": random_ids(30 + i, n, 200) for i, n in enumerate([50, 9, 77])}
+    for steps in (trace_whole(reqs), trace_portions(reqs), trace_tail_decoded(reqs, tail=8)):
+        got = run_trace_on_engine(eng, steps)
+        for rid, ids in reqs.items():
+            want = _plain_toy_model(w64, ids).numpy()
+            bad = first_wrong(got[rid], want, 2e-5)
+            assert bad is None, f"{rid}: first wrong position {bad}"
+    assert not eng.cache.live
