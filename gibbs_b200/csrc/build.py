@@ -23,10 +23,12 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 
 # library name -> sources.  A model needs "core" always and "tensorcore" when
-# it computes in bfloat16.
+# it computes in bfloat16; "runtime" holds no kernels: it walks a step's list of operations
+# and calls into the other two.
 LIBRARIES = {
     "core": ["errors.cu", "elementwise.cu", "gemm_simt.cu", "conv.cu", "attention.cu", "sampling.cu"],
     "tensorcore": ["errors.cu", "gemm_tc.cu", "attention_tc.cu", "attention_tcgen05.cu"],
+    "runtime": ["errors.cu", "step_plan.cu"],
 }
 
 NVCC_FLAGS = [

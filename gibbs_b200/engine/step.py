@@ -19,7 +19,9 @@ import torch
 
 from .. import ops
 from ..cache import CacheManager, OutOfPages
+from ..parts.base import NotPlannable
 from ..parts.model import CausalLM
+from . import plan as step_plan
 
 
 class StepError(RuntimeError):
@@ -166,7 +168,8 @@ class Engine:
     """A model, its cache and the step function over them."""
 
     def __init__(self, model: CausalLM, n_pages: int, page_size: int = 16, max_requests: int = 64,
-                 max_step_tokens: int = 8192, max_context: Optional[int] = None, use_graphs: bool = True):
+                 max_step_tokens: int = 8192, max_context: Optional[int] = None, use_graphs: bool = True,
+                 use_plan: bool = True):
         self.model = model
         self.device = model.rt.device
         if self.device.type != "cuda":
@@ -187,6 +190,15 @@ class Engine:
         self._graph_pool = None
         self._capture_stream = torch.cuda.Stream(device=self.device) if self.use_graphs else None
         self._graph_bufs: dict = {}
+        # The host work of a step as a list of operations walked by one C call (engine/plan.py), when
+        # every part of the model can be written that way; otherwise the parts' forward methods run.
+        self.plan = None
+        self.plan_refusal: Optional[str] = None
+        if use_plan and step_plan.ENABLED:
+            try:
+                self.plan = step_plan.build_step_plan(model, self.cache, self.max_step_tokens, self.max_requests)
+            except NotPlannable as e:
+                self.plan_refusal = str(e)
 
     # -- request life ----------------------------------------------------------
     def open(self, request_id) -> None:
@@ -283,13 +295,21 @@ class Engine:
             dev = self._graph_meta(n_req, total) if decode else bld.dev_meta
             dev[:total].copy_(bld._staging[turn][:total], non_blocking=True)
             bld._record(turn)
-            step, caches = bld._state(dev, offs, entries, rcs, n_tok, n_req, n_want, fixed=decode)
             before = ops.launch_count()
-            with ops.launching_on():
-                logits = self.model.forward(step, caches)
+            if self.plan is not None:
+                args = (n_tok, n_req, n_want, max(len(e.tokens) for e in entries), dev.data_ptr(), offs)
+                max_ctx = self.max_context if decode else max(rc.length + len(e.tokens) for e, rc in zip(entries, rcs))
+                with ops.launching_on():
+                    logits = self._run_plan(*args, max_ctx)
+                step = caches = None
+            else:
+                args = None
+                step, caches = bld._state(dev, offs, entries, rcs, n_tok, n_req, n_want, fixed=decode)
+                with ops.launching_on():
+                    logits = self.model.forward(step, caches)
             if decode:
                 # this run was the real step; capture the same work for the next steps of this size
-                self._capture(n_req, dev, step, caches, ops.launch_count() - before)
+                self._capture(n_req, dev, step, caches, ops.launch_count() - before, args)
         for e, rc in zip(entries, rcs):
             self.cache.advance(rc, rc.length + len(e.tokens))
         self.steps_run += 1
@@ -301,7 +321,14 @@ class Engine:
             buf = self._graph_bufs[batch] = torch.empty(total, dtype=torch.int32, device=self.device)
         return buf
 
-    def _capture(self, batch: int, dev, step, caches, launches: int) -> None:
+    def _run_plan(self, n_tok, n_req, n_want, max_q_len, meta_ptr, offs, max_ctx) -> Optional[torch.Tensor]:
+        """One call into the step plan; the logits get a buffer of their own."""
+        logits = torch.empty((n_want, self.vocab_size), dtype=torch.float32, device=self.device) if n_want else None
+        self.plan.run(n_tok, n_req, n_want, max_q_len, max_ctx, meta_ptr, offs, self.cache.max_blocks,
+                      logits.data_ptr() if n_want else 0)
+        return logits
+
+    def _capture(self, batch: int, dev, step, caches, launches: int, plan_args=None) -> None:
         """Record the decode step of this batch size.  All graphs of an engine share one
         memory pool, and the capture is begun and ended by hand: the context manager of
         torch.cuda.graph collects garbage and empties the allocator's cache every time,
@@ -316,7 +343,10 @@ class Engine:
             graph.capture_begin(pool=self._graph_pool)
             try:
                 with ops.launching_on(side):
-                    logits = self.model.forward(step, caches)
+                    if plan_args is not None:
+                        logits = self._run_plan(*plan_args, self.max_context)
+                    else:
+                        logits = self.model.forward(step, caches)
             finally:
                 graph.capture_end()
         torch.cuda.current_stream().wait_stream(side)

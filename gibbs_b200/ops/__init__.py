@@ -546,10 +546,13 @@ def attention_tc_supported(q, out, heads, kv_heads, head_dim) -> bool:
             and q.stride(0) % 8 == 0 and out.stride(0) % 2 == 0 and q.data_ptr() % 16 == 0)
 
 
+_ATTN_CTAS = int(os.environ.get("GIBBS_B200_ATTN_CTAS", "740"))
+
+
 def attention_splits(n_requests: int, kv_heads: int, max_ctx_len: int) -> int:
     """How many CTAs share the keys of one (request, kv head) when decoding:
     enough to occupy the GPU, at least two tiles of 64 keys each."""
-    by_sm = max(1, 740 // max(1, n_requests * kv_heads))      # about five one-warp CTAs per SM
+    by_sm = max(1, _ATTN_CTAS // max(1, n_requests * kv_heads))      # about five CTAs per SM
     by_len = max(1, -(-max_ctx_len // 128))
     return max(1, min(16, by_sm, by_len))
 

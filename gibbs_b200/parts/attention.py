@@ -97,5 +97,17 @@ class GQAAttention(Mixer):
                             step.status, hints=step)
         self.out_proj(out, out=residual, accumulate=True)
 
+    def plan_ops(self, plan, h, caches):
+        kv = caches[0]
+        if not self.shares_kv and not kv.writable:
+            raise RuntimeError("an attention layer with k/v projections was given a read-only cache")
+        qkv = plan.linear(h, self.qkv.weight, self.qkv.bias, plan.buffer("qkv", self.qkv.out_features), "plain",
+                          partials="always")
+        plan.qk_norm_rope_store(qkv, self.heads, self.kv_heads, self.head_dim, self.q_gain, self.k_gain, self.eps,
+                                self.rotary, kv, not self.shares_kv, plan.bt_stride)
+        out = plan.attention(self.heads, self.kv_heads, self.head_dim, self.scale, self.window or 0, kv,
+                             plan.bt_stride)
+        plan.linear(out, self.out_proj.weight, self.out_proj.bias, None, "residual")
+
 
 register_part("mixer", "gqa_attention", GQAAttention)

@@ -24,6 +24,10 @@ Categories and what each must implement:
               ``caches`` holds one view per need.
   feed_forward ``forward(h, residual, step)``, adding likewise.
   block       built from its four parts; ``forward(residual, step, caches)``.
+  Optionally every part has ``plan_ops(plan, ...)`` with the arguments of its
+  ``forward`` minus the step and the residual: it appends the same work as
+  operations of a step plan (``engine/plan.py``), which the engine then runs
+  with one call per step instead of one per kernel.
   embedding   ``forward(ids_i32 [N]) -> x_f32 [N, dim]``.
   head        ``forward(z [R, dim]) -> logits_f32 [R, vocab]``.
 
@@ -115,6 +119,21 @@ class Residual:
         return self.x.shape
 
 
+class NotPlannable(Exception):
+    """Raised while a step plan is built when a part (or one of its sizes)
+    cannot be written as operations of the plan; the engine then runs the
+    parts' ``forward`` methods from Python."""
+
+
+def plan_ops_of(part):
+    """``part.plan_ops``, or NotPlannable for a part that has none (parts need
+    not derive from the classes below)."""
+    fn = getattr(part, "plan_ops", None)
+    if fn is None:
+        raise NotPlannable(f"{type(part).__name__} has no plan operations")
+    return fn
+
+
 class Part:
     category: str = ""
 
@@ -128,6 +147,12 @@ class Part:
     def kernel_libraries(self) -> Sequence[str]:
         """Kernel libraries this part launches from (built before the first step)."""
         return ("core",)
+
+    def plan_ops(self, plan, *args):
+        """Append to ``plan`` (an ``engine.plan.PlanBuilder``) the operations
+        that do what ``forward`` does, for any step.  Optional: a model with a
+        part that lacks it is run through the ``forward`` methods."""
+        raise NotPlannable(f"{type(self).__name__} has no plan operations")
 
 
 class Norm(Part):
@@ -183,6 +208,9 @@ class Block:
 
     def forward(self, x: torch.Tensor, step, caches: list) -> None:
         raise NotImplementedError
+
+    def plan_ops(self, plan, caches: list) -> None:
+        raise NotPlannable(f"{type(self).__name__} has no plan operations")
 
 
 # ---------------------------------------------------------------------------

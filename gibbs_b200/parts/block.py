@@ -1,7 +1,7 @@
 """Arrangements of norm, mixer and feed-forward around the residual stream."""
 from __future__ import annotations
 
-from .base import Block, register_part
+from .base import Block, plan_ops_of, register_part
 
 
 class PreNormResidual(Block):
@@ -13,6 +13,12 @@ class PreNormResidual(Block):
         self.mixer.forward(h, x, step, caches)
         h = self.ffn_norm.forward(x)
         self.ffn.forward(h, x, step)
+
+    def plan_ops(self, plan, caches):
+        h = plan_ops_of(self.mixer_norm)(plan)
+        plan_ops_of(self.mixer)(plan, h, caches)
+        h = plan_ops_of(self.ffn_norm)(plan)
+        plan_ops_of(self.ffn)(plan, h)
 
 
 register_part("block", "prenorm_residual", PreNormResidual)

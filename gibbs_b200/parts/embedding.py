@@ -25,6 +25,9 @@ class TokenEmbedding(Part):
         out = self.rt.empty(ids.numel(), self.dim, dtype=torch.float32)
         return ops.embed(self.table, ids, out)
 
+    def plan_ops(self, plan):
+        plan.embed(self.table)
+
 
 class LMHead(Part):
     """logits = z W^T in 32-bit, no scale and no soft cap
@@ -49,6 +52,10 @@ class LMHead(Part):
 
     def forward(self, z: torch.Tensor) -> torch.Tensor:
         return self.proj(z, out_dtype=torch.float32)
+
+    def plan_ops(self, plan, z, logits: int):
+        """``logits``: the plan's symbol for where the step's float32 logits go."""
+        plan.linear(z, self.proj.weight, self.proj.bias, logits, "plain", rows_symbol=plan.WANTED)
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)

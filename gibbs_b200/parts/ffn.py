@@ -49,5 +49,14 @@ class SwiGLU(FeedForward):
             ops.swiglu(gu, act)
         self.down(act, out=residual, accumulate=True)
 
+    def plan_ops(self, plan, h):
+        gu = self.gate_up
+        if self.fused:
+            act = plan.linear(h, gu.weight, gu.bias, plan.buffer("act", self.inner), "swiglu")
+        else:
+            both = plan.linear(h, gu.weight, gu.bias, plan.buffer("gate_up", 2 * self.inner), "plain")
+            act = plan.swiglu(both, self.inner)
+        plan.linear(act, self.down.weight, self.down.bias, None, "residual")
+
 
 register_part("feed_forward", "swiglu", SwiGLU)

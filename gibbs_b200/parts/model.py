@@ -8,7 +8,7 @@ from typing import Optional
 import torch
 
 from ..config.plan import ModelPlan, PartSpec
-from .base import Residual, Runtime, part_class
+from .base import Residual, Runtime, part_class, plan_ops_of
 
 
 def plan_parts(plan: ModelPlan):
@@ -66,6 +66,15 @@ class CausalLM:
             return None
         z = self.final_norm.forward(x, rows=step.want_rows)
         return self.head.forward(z)
+
+    def plan_ops(self, plan, caches) -> None:
+        """Append everything ``forward`` does to a step plan; raises
+        NotPlannable if a part cannot be written as operations."""
+        plan_ops_of(self.embedding)(plan)
+        for e, entry in enumerate(self.plan.order):
+            plan_ops_of(self.blocks[entry.layer])(plan, caches[e])
+        z = plan_ops_of(self.final_norm)(plan, wanted_rows=True)
+        plan_ops_of(self.head)(plan, z, plan.LOGITS)
 
     def weight_bytes_per_step(self) -> int:
         """Bytes of weights one step reads when each is read once: every

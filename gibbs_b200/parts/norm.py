@@ -28,4 +28,8 @@ class RMSNorm(Norm):
         return ops.rmsnorm(x, self.gain, self.eps, out, rows, pending)
 
 
+    def plan_ops(self, plan, wanted_rows: bool = False):
+        return plan.rmsnorm(self.gain, self.eps, wanted_rows)
+
+
 register_part("norm", "rmsnorm", RMSNorm)

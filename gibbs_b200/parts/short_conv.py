@@ -60,5 +60,11 @@ class GatedShortConv(Mixer):
                            step.q_len, y, max_q_len=step.max_q_len)
         self.out_proj(y, out=residual, accumulate=True)
 
+    def plan_ops(self, plan, h, caches):
+        bcx = plan.linear(h, self.in_proj.weight, self.in_proj.bias, plan.buffer("bcx", 3 * self.hidden), "plain",
+                          partials="one_each")
+        y = plan.short_conv(bcx, self.taps, self.conv_bias, caches[0], self.hidden, self.kernel)
+        plan.linear(y, self.out_proj.weight, self.out_proj.bias, None, "residual")
+
 
 register_part("mixer", "gated_short_conv", GatedShortConv)
