@@ -92,3 +92,27 @@ def test_mixed_batches_with_page_reuse(tmp_path_factory, name, dtype):
     # every page and slot was handed out more than once
     assert sum(len(v) for v in reqs.values()) > capacity
     print(f"mixed {name} {dtype}: worst rel err {worst:.3g}, {len(steps)} steps")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_step_plan_gives_the_same_bits_as_the_parts_forward(tmp_path_factory, name, dtype):
+    """The same model stepped through the C walker of its plan and through the parts' forward
+    methods: one sequence of kernels either way, so the logits are equal bit for bit, under mixed
+    batches and decoding (graphs on in both)."""
+    from gibbs_b200 import Engine
+    folder, model = _setup(tmp_path_factory, name, dtype)
+    reqs = _requests(name, [90, 37, 128, 61, 150, 2], seed=7)
+    got = []
+    for use_plan in (True, False):
+        eng = Engine(model, n_pages=28, page_size=16, max_requests=4, use_plan=use_plan)
+        assert (eng.plan is not None) == use_plan, eng.plan_refusal
+        a = run_trace_on_engine(eng, trace_mixed(reqs, capacity_tokens=448, max_live=4, seed=5))
+        b = run_trace_on_engine(eng, trace_tail_decoded({k: v for k, v in list(reqs.items())[:2]}, tail=20))
+        got.append((a, b))
+        assert not eng.cache.live
+    for (pa, pb), (fa, fb) in [(got[0], got[1])]:
+        for rid in pa:
+            assert np.array_equal(pa[rid], fa[rid]), rid
+        for rid in pb:
+            assert np.array_equal(pb[rid], fb[rid]), rid

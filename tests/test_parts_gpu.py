@@ -326,6 +326,7 @@ def test_hand_made_model_with_toy_mixer_repeated_layer_shared_cache_and_window(d
     assert [len(n) for n, _ in needs] == [1, 1, 1, 1, 0] and needs[4][1] == 1
     eng = Engine(model, n_pages={None: 40, 24: 40}, page_size=8, max_requests=4, max_step_tokens=512)
     assert len(eng.cache.groups) == 2 and not eng.use_graphs                 # all keys; window of 24
+    assert eng.plan is None and "ToyDecayMixer" in eng.plan_refusal          # no plan operations: forward methods run
     w64 = {k: v.double() for k, v in tensors.items()}
     reqs = {f"r{i}": random_ids(70 + i, n, 300) for i, n in enumerate([70, 33, 100, 5, 64])}
     for steps in (trace_whole(reqs), trace_portions(reqs), trace_mixed(reqs, capacity_tokens=320, seed=2)):
