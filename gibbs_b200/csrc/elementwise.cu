@@ -60,7 +60,9 @@ __device__ __forceinline__ void store4<bf16>(bf16* dst, float4 v) {
 // VEC > 0: dim is a multiple of 4, rows are 16-byte aligned and each thread keeps its
 // VEC float4 of the row in registers (all loads of the row and of the partial sums are
 // issued together; the row is read once).  VEC == 0: any dim, two passes.
-template <typename TOut, int VEC>
+// PEND: instantiated apart so that rows without partial sums (prompts) do not pay for the
+// registers that hold eight splits' worth of loads.
+template <typename TOut, int VEC, bool PEND>
 __global__ void rmsnorm_kernel(float* __restrict__ x, long long ldx, const float* __restrict__ gain,
                                TOut* __restrict__ out, const int* __restrict__ rows, int dim, float eps,
                                const float* __restrict__ pend, int splits, long long n_src_rows,
@@ -82,7 +84,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, long long ldx, const float
       const int c = threadIdx.x + i * blockDim.x;
       v[i] = c < n4 ? reinterpret_cast<const float4*>(src)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    if (pend) {
+    if (PEND && pend) {
       // the partial sums of up to eight splits are requested together (one trip to L2, not eight)
       // and then added in split order
       constexpr int G = 8;
@@ -169,18 +171,16 @@ void launch_rmsnorm(float* x, long long ldx, const float* gain, TOut* out, const
     int threads = 32;
     while (threads < 1024 && threads < n4) threads <<= 1;
     if (threads > 256 && n4 <= 2 * 256) threads = 256;
-    if (n4 <= threads)
-      gb_launch(rmsnorm_kernel<TOut, 1>, dim3(n_rows), dim3(threads), 0, stream, x, ldx, gain, out, rows, dim, eps,
-                pend, splits, n_src_rows, pend_bias);
-    else
-      gb_launch(rmsnorm_kernel<TOut, 2>, dim3(n_rows), dim3(threads), 0, stream, x, ldx, gain, out, rows, dim, eps,
-                pend, splits, n_src_rows, pend_bias);
+    auto kernel = n4 <= threads ? (pend ? rmsnorm_kernel<TOut, 1, true> : rmsnorm_kernel<TOut, 1, false>)
+                                : (pend ? rmsnorm_kernel<TOut, 2, true> : rmsnorm_kernel<TOut, 2, false>);
+    gb_launch(kernel, dim3(n_rows), dim3(threads), 0, stream, x, ldx, gain, out, rows, dim, eps, pend, splits,
+              n_src_rows, pend_bias);
     return;
   }
   int threads = 32;
   while (threads < 512 && threads * 4 < dim) threads <<= 1;
-  gb_launch(rmsnorm_kernel<TOut, 0>, dim3(n_rows), dim3(threads), 0, stream, x, ldx, gain, out, rows, dim, eps, pend,
-            splits, n_src_rows, pend_bias);
+  gb_launch(rmsnorm_kernel<TOut, 0, true>, dim3(n_rows), dim3(threads), 0, stream, x, ldx, gain, out, rows, dim, eps,
+            pend, splits, n_src_rows, pend_bias);
 }
 
 GB_API int gb_rmsnorm(float* x, long long ldx, const float* gain, void* out, int out_dtype, const int* rows,

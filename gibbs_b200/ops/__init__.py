@@ -546,7 +546,7 @@ def attention_tc_supported(q, out, heads, kv_heads, head_dim) -> bool:
             and q.stride(0) % 8 == 0 and out.stride(0) % 2 == 0 and q.data_ptr() % 16 == 0)
 
 
-_ATTN_CTAS = int(os.environ.get("GIBBS_B200_ATTN_CTAS", "740"))
+_ATTN_CTAS = int(os.environ.get("GIBBS_B200_ATTN_CTAS", "592"))   # about four CTAs per SM
 
 
 def attention_splits(n_requests: int, kv_heads: int, max_ctx_len: int) -> int:
