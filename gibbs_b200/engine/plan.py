@@ -215,11 +215,11 @@ class StepPlan:
     """A finished plan: the operation list (host memory, read by the C walker), its buffers,
     and ``run``."""
 
-    _bound = False
+    _bound = None      # None: nothing bound yet; False: the core library only; True: the tensor-core library as well
 
     def __init__(self, b: PlanBuilder, n_groups: int):
         self.lib = library("runtime")
-        self._bind()
+        self._bind(b.tc)
         self.table = np.stack(b.ops) if b.ops else np.zeros(0, dtype=OP)
         if self.table.dtype.itemsize != self.lib.gb_plan_op_bytes():
             raise KernelError("the plan's record layout does not match the library")
@@ -237,19 +237,21 @@ class StepPlan:
         r.status = ops.device_status(b.device).data_ptr()
         r.attn_ctas, r.tc_flags, r.use_tcgen05 = ops._ATTN_CTAS, ops._TC_FLAGS, int(ops._ATTN_TCGEN05)
 
-    def _bind(self) -> None:
-        if StepPlan._bound:
+    def _bind(self, need_tensorcore: bool) -> None:
+        """Hand the walker the entry points of the kernel libraries; those of the tensor-core
+        library only once a model needs it (a float32 model never builds that library)."""
+        if StepPlan._bound is True or (StepPlan._bound is False and not need_tensorcore):
             return
         fns = (ctypes.c_void_p * len(_FUNCTIONS))()
         for i, (lib_name, fn) in enumerate(_FUNCTIONS):
-            try:
+            if lib_name == "tensorcore" and not need_tensorcore:
+                fns[i] = None
+            else:
                 fns[i] = ctypes.cast(getattr(library(lib_name), fn), ctypes.c_void_p).value
-            except KernelError:
-                fns[i] = None                      # a library this model does not need
         rc = self.lib.gb_plan_bind(fns, ctypes.c_int(len(_FUNCTIONS)))
         if rc != 0:
             ops.check(self.lib, rc)
-        StepPlan._bound = True
+        StepPlan._bound = bool(need_tensorcore)
 
     def run(self, n_tokens: int, n_requests: int, n_want: int, max_q_len: int, max_ctx_len: int, meta_ptr: int, offs,
             mb: int, logits_ptr: int) -> int:
