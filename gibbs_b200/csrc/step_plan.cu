@@ -127,6 +127,7 @@ int run_op(Walk& w, const PlanOp& o) {
       // a0 x (f32), a1 its row stride, a2 gain, a3 out, a4 out dtype, a5 gather the wanted rows (0/1), a6 dim; f0 eps
       const bool gather = a[5] != 0;
       const int n_rows = gather ? W : N;
+      if (n_rows <= 0) return 0;                               // (a step that wants no logits)
       const float* pend = w.pend_splits > 0 ? w.ws : nullptr;
       PLAN_CALL(w, F_RMSNORM, ((RmsnormFn)g_fn[F_RMSNORM])(
           ptr<float>(w, a[0]), a[1], ptr<const float>(w, a[2]), ptr<void>(w, a[3]), (int)a[4],
