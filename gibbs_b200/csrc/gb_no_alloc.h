@@ -31,7 +31,7 @@
 //    (cudaGetSymbolAddress, with that device current) and keeps it.  Make that
 //    first call outside any stream capture.
 //
-// Arguments are those of gb_linear_tc without workspace, prefetch and flags:
+// Arguments are those of gb_linear_tc without workspace and flags:
 // X [M, K] bf16 (row stride ldx), W [N, K] bf16 (row stride ldw), bias f32 [N]
 // or null; mode 0: out bf16 [M, N], 1: out f32, 2: out f32 +=, 3: SwiGLU over
 // gate/up rows alternating in blocks of 64 (out bf16 [M, N / 2]); status: an

@@ -23,9 +23,8 @@
 // next (the caller asks for that with `defer`).
 //
 // A decode step is bound by streaming the weights once: the weights are read
-// with an evict-first L2 hint.  A call may also name the weights of the NEXT
-// product, for which the CTAs then issue L2 prefetches while they work (off
-// by default: it did not pay in measurements so far).
+// with an evict-first L2 hint.  (Asking L2 for the next product's weights ahead of time was
+// measured in several forms and always lost; it is not done.)
 //
 // Sizes: any M, N; K a multiple of 8 (16-byte rows for TMA), all row strides
 // multiples of 8 elements, 16-byte aligned bases.  Ragged edges are zero-filled
@@ -58,7 +57,7 @@ template <int BN, bool DEEP = false> struct Cfg {
   static constexpr int X_TILE_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES;
   static constexpr int STAGES = DEEP ? (BN >= 64 ? 8 : (BN >= 32 ? 9 : 10))
-                                     : (BN >= 256 ? 4 : (BN >= 128 ? 3 : (BN >= 64 ? 4 : 5)));
+                                     : (BN >= 128 ? 3 : (BN >= 64 ? 4 : 5));
   static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;   // + room to align to 1024
 };
@@ -70,7 +69,6 @@ struct GemmParams {
   int M, N;                     // tokens, weight rows (for SwiGLU: 2 * features)
   int total_kb, kb_per_split, splits;
   float* ws;                    // [splits][M][N] partial tiles (splits > 1)
-  const uint8_t* prefetch; long long prefetch_bytes;   // weights of the next product, or null
   int stream_weights;           // 1: read W with an evict-first L2 hint
   int vec_store;                // 1: out rows are 16-byte aligned (base and row stride)
   int* status;
@@ -202,17 +200,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   } else {
     // ---- epilogue warps (threads 64..191) ----
     const int et = threadIdx.x - 64;            // 0..127
-    if (p.prefetch != nullptr) {
-      // this CTA's share of the next product's weights, in 4 KB pieces, towards L2
-      const long long n_cta = (long long)gridDim.x * gridDim.y * gridDim.z;
-      const long long cta = ((long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-      const long long pieces = (p.prefetch_bytes + 4095) / 4096;
-      for (long long i = cta * 128 + et; i < pieces; i += n_cta * 128) {
-        const long long off = i * 4096;
-        const uint32_t bytes = (uint32_t)((p.prefetch_bytes - off < 4096 ? p.prefetch_bytes - off : 4096) & ~15ll);
-        if (bytes) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.prefetch + off), "r"(bytes));
-      }
-    }
     pdl_wait();    // outputs (and the workspace) may still be read by the kernels before this one
     const bool ok = mbar_wait(&tmem_full_bar, 0);
     if (!ok) {
@@ -387,307 +374,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   __syncthreads();
   if (abort_flag && threadIdx.x == 0) {
     // give copies that are still in flight time to land before the shared memory is released
-    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
-  }
-  __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
-}
-
-// ---------------------------------------------------------------- persistent kernel (prompts)
-// For many tiles (prompt portions) one CTA per SM walks a list of tiles, so that the
-// set-up, the start of the TMA pipeline and the epilogue are paid once or hidden:
-//  - the producer runs ahead into the next tile while the MMAs of this one finish,
-//  - the accumulator is double-buffered in tensor memory (2 x BN columns): the epilogue
-//    warps drain tile i while the MMA thread fills tile i+1,
-//  - the epilogue transposes through a staging area in shared memory, releases the
-//    accumulator as soon as it has been read, and stores whole output rows in 16-byte pieces.
-// Tiles are numbered with the token tile fastest, so CTAs running at the same time share
-// the weight tiles in L2.  K is never split here.
-template <int BN> struct PCfg {
-  static constexpr int X_TILE_BYTES = BN * BK * 2;
-  static constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES;
-  static constexpr int STAGES = 5;
-  static constexpr int STAGING_BYTES = BN * 64 * 4 + BN * 64 * 2;      // SwiGLU: u (f32) + result (bf16); others fit
-  static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024;
-};
-
-template <int BN>
-__global__ void __launch_bounds__(192)
-gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                          const GemmParams p) {
-  using C = PCfg<BN>;
-  extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t full_bar[C::STAGES], empty_bar[C::STAGES], tmem_full_bar[2], tmem_empty_bar[2];
-  __shared__ uint32_t tmem_slot;
-  __shared__ volatile int abort_flag;
-  pdl_trigger();
-
-  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* staging = tiles + (size_t)C::STAGES * C::STAGE_BYTES;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int M = p.M, N = p.N, nkb = p.total_kb;
-  const int tiles_m = (M + BN - 1) / BN, tiles_n = (N + BM - 1) / BM;
-  const int n_tiles = tiles_m * tiles_n;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < C::STAGES; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
-    }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(&tmem_full_bar[a], 1);
-      mbar_init(&tmem_empty_bar[a], 1);
-    }
-    abort_flag = 0;
-    fence_barrier_init();
-  }
-  if (warp == 0 && lane == 0) {
-    tma_prefetch_desc(&tmap_w);
-    tma_prefetch_desc(&tmap_x);
-  }
-  if (warp == 1) {
-    tmem_alloc(&tmem_slot, C::TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = tmem_slot;
-
-  if (warp == 0) {
-    if (elect_one()) {
-      int it = 0;                                           // k-blocks requested so far, over all tiles
-      bool first = true;
-      for (int t = blockIdx.x; t < n_tiles && !abort_flag; t += gridDim.x) {
-        const int n0 = (t / tiles_m) * BM, m0 = (t % tiles_m) * BN;
-        int i = 0;
-        if (first) {
-          // The weights do not depend on earlier kernels: the first stages' weight tiles are
-          // requested at once, the activation tiles after those kernels have finished.
-          const int head = nkb < C::STAGES ? nkb : C::STAGES;
-          for (i = 0; i < head; ++i) {
-            mbar_arrive_expect_tx(&full_bar[i], C::STAGE_BYTES);
-            tma_load_2d(tiles + (size_t)i * C::STAGE_BYTES, &tmap_w, i * BK, n0, &full_bar[i]);
-          }
-          pdl_wait();
-          for (i = 0; i < head; ++i)
-            tma_load_2d(tiles + (size_t)i * C::STAGE_BYTES + W_TILE_BYTES, &tmap_x, i * BK, m0, &full_bar[i]);
-          it = head;
-          first = false;
-        }
-        for (; i < nkb; ++i, ++it) {
-          const int s = it % C::STAGES;
-          const uint32_t ph = (it / C::STAGES) & 1;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
-            abort_flag = 1;
-            atomicExch(p.status, STATUS_TIMEOUT + 4);
-            break;
-          }
-          if (abort_flag) break;
-          uint8_t* st = tiles + (size_t)s * C::STAGE_BYTES;
-          mbar_arrive_expect_tx(&full_bar[s], C::STAGE_BYTES);
-          tma_load_2d(st, &tmap_w, i * BK, n0, &full_bar[s]);
-          tma_load_2d(st + W_TILE_BYTES, &tmap_x, i * BK, m0, &full_bar[s]);
-        }
-      }
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    if (elect_one()) {
-      constexpr uint32_t idesc = idesc_bf16_f32(BM, BN);
-      int it = 0, tile_i = 0;
-      for (int t = blockIdx.x; t < n_tiles && !abort_flag; t += gridDim.x, ++tile_i) {
-        const int a = tile_i & 1;
-        if (!mbar_wait(&tmem_empty_bar[a], ((tile_i >> 1) & 1) ^ 1)) {   // the epilogue has drained this buffer
-          abort_flag = 1;
-          atomicExch(p.status, STATUS_TIMEOUT + 5);
-          break;
-        }
-        tc_fence_after();
-        const uint32_t acc = tmem_base + (uint32_t)(a * BN);
-        for (int i = 0; i < nkb; ++i, ++it) {
-          const int s = it % C::STAGES;
-          const uint32_t ph = (it / C::STAGES) & 1;
-          if (!mbar_wait(&full_bar[s], ph)) {
-            abort_flag = 1;
-            atomicExch(p.status, STATUS_TIMEOUT + 6);
-            break;
-          }
-          if (abort_flag) break;
-          tc_fence_after();
-          uint8_t* st = tiles + (size_t)s * C::STAGE_BYTES;
-          const uint64_t da = smem_desc_sw128(st);
-          const uint64_t db = smem_desc_sw128(st + W_TILE_BYTES);
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (uint32_t)((i | k) != 0));
-          umma_commit(&empty_bar[s]);
-        }
-        umma_commit(&tmem_full_bar[a]);
-      }
-    }
-    __syncwarp();
-  } else {
-    const int et = threadIdx.x - 64;
-    const int q = warp & 3, row = 32 * q + lane;
-    pdl_wait();
-    int tile_i = 0;
-    for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++tile_i) {
-      const int a = tile_i & 1;
-      const int n0 = (t / tiles_m) * BM, m0 = (t % tiles_m) * BN;
-      const int n = n0 + row;
-      const bool ok = mbar_wait(&tmem_full_bar[a], (tile_i >> 1) & 1);
-      if (!ok) {
-        abort_flag = 1;
-        if (lane == 0) atomicExch(p.status, STATUS_TIMEOUT + 7);
-      }
-      tc_fence_after();
-      epilogue_barrier();
-      if (abort_flag) break;
-      const uint32_t acc = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(a * BN);
-      const int cols = min(BN, M - m0);
-      const bool fast = p.vec_store && n0 + BM <= N;
-      const float b = (p.bias && n < N) ? p.bias[n] : 0.f;
-      if (fast && p.mode == OUT_SWIGLU) {
-        float* ub = reinterpret_cast<float*>(staging);
-        bf16* ob = reinterpret_cast<bf16*>(staging + (size_t)BN * 64 * sizeof(float));
-#pragma unroll 1
-        for (int c0 = 0; c0 < cols; c0 += 16) {
-          float v[16];
-          tmem_ld_16(acc + (uint32_t)c0, v);
-          if (row >= 64) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) ub[(c0 + j) * 64 + (row - 64)] = v[j] + b;
-          }
-        }
-        epilogue_barrier();
-        if (row < 64) {
-#pragma unroll 1
-          for (int c0 = 0; c0 < cols; c0 += 16) {
-            float v[16];
-            tmem_ld_16(acc + (uint32_t)c0, v);
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              ob[(c0 + j) * 64 + row] = __float2bfloat16_rn(silu_mul(v[j] + b, ub[(c0 + j) * 64 + row]));
-          }
-        }
-        tc_fence_before();
-        epilogue_barrier();
-        if (et == 0) mbar_arrive(&tmem_empty_bar[a]);          // the accumulator may be overwritten
-        bf16* dst = (bf16*)p.out + (size_t)m0 * p.ldo + (n0 >> 1);
-        for (int idx = et; idx < cols * 8; idx += 128) {
-          const int mm = idx >> 3, piece = idx & 7;
-          *reinterpret_cast<uint4*>(dst + (size_t)mm * p.ldo + piece * 8) =
-              *reinterpret_cast<const uint4*>(ob + mm * 64 + piece * 8);
-        }
-        epilogue_barrier();                                    // staging is free again
-      } else if (fast && p.mode == OUT_BF16) {
-        bf16* ob = reinterpret_cast<bf16*>(staging);
-#pragma unroll 1
-        for (int c0 = 0; c0 < cols; c0 += 16) {
-          float v[16];
-          tmem_ld_16(acc + (uint32_t)c0, v);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) ob[(c0 + j) * BM + row] = __float2bfloat16_rn(v[j] + b);
-        }
-        tc_fence_before();
-        epilogue_barrier();
-        if (et == 0) mbar_arrive(&tmem_empty_bar[a]);
-        bf16* dst = (bf16*)p.out + (size_t)m0 * p.ldo + n0;
-        for (int idx = et; idx < cols * 16; idx += 128) {
-          const int mm = idx >> 4, piece = idx & 15;
-          *reinterpret_cast<uint4*>(dst + (size_t)mm * p.ldo + piece * 8) =
-              *reinterpret_cast<const uint4*>(ob + mm * BM + piece * 8);
-        }
-        epilogue_barrier();
-      } else if (fast) {                                       // OUT_F32 / OUT_F32_ACC, 64 token rows at a time
-        float* fb = reinterpret_cast<float*>(staging);
-#pragma unroll 1
-        for (int h0 = 0; h0 < cols; h0 += 64) {
-          const int hc = min(64, cols - h0);
-#pragma unroll 1
-          for (int c0 = 0; c0 < hc; c0 += 16) {
-            float v[16];
-            tmem_ld_16(acc + (uint32_t)(h0 + c0), v);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) fb[(c0 + j) * BM + row] = v[j] + b;
-          }
-          tc_fence_before();
-          epilogue_barrier();
-          if (h0 + 64 >= cols && et == 0) mbar_arrive(&tmem_empty_bar[a]);
-          float* dst = (float*)p.out + (size_t)(m0 + h0) * p.ldo + n0;
-          for (int idx = et; idx < hc * 32; idx += 128 * 4) {
-            float4 nv[4], ov[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int id = idx + u * 128;
-              if (id < hc * 32) {
-                const int mm = id >> 5, piece = id & 31;
-                nv[u] = *reinterpret_cast<const float4*>(fb + mm * BM + piece * 4);
-                if (p.mode == OUT_F32_ACC)
-                  ov[u] = __ldcg(reinterpret_cast<const float4*>(dst + (size_t)mm * p.ldo + piece * 4));
-              }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int id = idx + u * 128;
-              if (id < hc * 32) {
-                const int mm = id >> 5, piece = id & 31;
-                float4 r = nv[u];
-                if (p.mode == OUT_F32_ACC) { r.x += ov[u].x; r.y += ov[u].y; r.z += ov[u].z; r.w += ov[u].w; }
-                *reinterpret_cast<float4*>(dst + (size_t)mm * p.ldo + piece * 4) = r;
-              }
-            }
-          }
-          epilogue_barrier();
-        }
-      } else {
-        // ragged edge or unaligned output: element by element
-        if (p.mode == OUT_SWIGLU) {
-          float* ub = reinterpret_cast<float*>(staging);
-#pragma unroll 1
-          for (int c0 = 0; c0 < cols; c0 += 16) {
-            float v[16];
-            tmem_ld_16(acc + (uint32_t)c0, v);
-            if (row >= 64) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) ub[(c0 + j) * 64 + (row - 64)] = v[j] + b;
-            }
-          }
-          epilogue_barrier();
-          if (row < 64) {
-#pragma unroll 1
-            for (int c0 = 0; c0 < cols; c0 += 16) {
-              float v[16];
-              tmem_ld_16(acc + (uint32_t)c0, v);
-#pragma unroll
-              for (int j = 0; j < 16; ++j)
-                if (c0 + j < cols)
-                  ((bf16*)p.out)[(size_t)(m0 + c0 + j) * p.ldo + (n0 >> 1) + row] =
-                      __float2bfloat16_rn(silu_mul(v[j] + b, ub[(c0 + j) * 64 + row]));
-            }
-          }
-        } else {
-#pragma unroll 1
-          for (int c0 = 0; c0 < cols; c0 += 16) {
-            float v[16];
-            tmem_ld_16(acc + (uint32_t)c0, v);
-            if (n < N) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j)
-                if (c0 + j < cols) store_value(p, m0 + c0 + j, n, v[j] + b);
-            }
-          }
-        }
-        tc_fence_before();
-        epilogue_barrier();
-        if (et == 0) mbar_arrive(&tmem_empty_bar[a]);
-      }
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (abort_flag && threadIdx.x == 0) {
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
   }
   __syncthreads();
@@ -1061,22 +747,11 @@ struct WKeyHash {
 std::mutex g_wmap_mutex;
 std::unordered_map<WKey, CUtensorMap, WKeyHash> g_wmaps;   // weights do not move: their maps are made once
 
-// GIBBS_B200_WIDE_TILES=1 puts prompts on 128 x 256 single-CTA tiles (for comparison runs; slower).
-int gb_wide_tiles() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("GIBBS_B200_WIDE_TILES");
-    v = (e && e[0] == '1') ? 1 : 0;
-  }
-  return v;
-}
-
 int pick_bn(int M) {
   if (M <= 16) return 16;
   if (M <= 32) return 32;
   if (M <= 64) return 64;
-  if (M <= 128 || !gb_wide_tiles()) return 128;
-  return 256;
+  return 128;
 }
 
 void plan(int M, int N, int K, int* bn, int* splits, int* kb_per_split) {
@@ -1133,26 +808,6 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cu
   return launch_as<BN, false>(tw, tx, p, grid, stream);
 }
 
-template <int BN>
-int launch_persistent(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    GB_CUDA(cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 PCfg<BN>::SMEM_BYTES));
-    attr_set = true;
-  }
-  static int n_sm = 0;
-  if (n_sm == 0) {
-    int dev = 0;
-    GB_CUDA(cudaGetDevice(&dev));
-    GB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-  }
-  const long long tiles = (long long)gb_div_up(p.N, BM) * gb_div_up(p.M, BN);
-  const int grid = (int)(tiles < n_sm ? tiles : n_sm);
-  gb_launch(gemm_tc_persistent_kernel<BN>, dim3(grid), dim3(192), PCfg<BN>::SMEM_BYTES, stream, tw, tx, p);
-  return GB_OK;
-}
-
 int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
@@ -1196,17 +851,6 @@ int gb_pair() {
   return v;
 }
 
-// GIBBS_B200_PERSISTENT=1 lets the single-CTA persistent kernel take prompts the pair kernel
-// does not (for comparison runs; it measured slower than two one-tile CTAs per SM).
-int gb_persistent() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("GIBBS_B200_PERSISTENT");
-    v = (e && e[0] == '1') ? 1 : 0;
-  }
-  return v;
-}
-
 }  // namespace
 
 // 32-bit words of workspace gb_linear_tc needs for these sizes (0: none).
@@ -1236,13 +880,11 @@ GB_API int gb_linear_tc_supported(const void* X, long long ldx, const void* W, l
 // defer != 0 (modes 0 and 2): when K is split, leave the partial tiles in the workspace
 // ([splits][M][N], without bias) for the caller's next kernel to add (mode 0: and to round to
 // bfloat16); nothing is written to out.
-// prefetch / prefetch_bytes: the weights of the product that follows, or null / 0.
 // flags bit 0: read the weights with an evict-first hint.
 // Returns the number of kernels launched, or a negative error code.
 GB_API int gb_linear_tc(const void* X, long long ldx, const void* W, long long ldw, const float* bias, void* out,
                         int mode, long long ldo, int M, int N, int K, float* workspace, int defer,
-                        const void* prefetch, long long prefetch_bytes, int flags, int* status,
-                        cudaStream_t stream) {
+                        int flags, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (!gb_linear_tc_supported(X, ldx, W, ldw, K))
     GB_FAIL(GB_ERR_ARG, "gb_linear_tc: K = %d and the row strides (%lld, %lld) must be multiples of 8 and the bases "
@@ -1276,9 +918,6 @@ GB_API int gb_linear_tc(const void* X, long long ldx, const void* W, long long l
   p.total_kb = gb_div_up(K, BK); p.kb_per_split = kb_per_split; p.splits = splits;
   p.ws = workspace;
   const bool decode_like = M <= 64;
-  p.prefetch = decode_like ? (const uint8_t*)prefetch : nullptr;
-  p.prefetch_bytes = decode_like ? (prefetch_bytes > (64ll << 20) ? (64ll << 20) : prefetch_bytes) : 0;
-  if (((uintptr_t)p.prefetch & 15) != 0) p.prefetch = nullptr;
   p.stream_weights = (decode_like && (flags & 1)) ? 1 : 0;   // flags bit 0: evict-first hint for the weights
   p.vec_store = (((uintptr_t)out & 15) == 0 && (ldo * (mode == OUT_BF16 || mode == OUT_SWIGLU ? 2 : 4)) % 16 == 0) ? 1 : 0;
   p.status = status;
@@ -1292,14 +931,11 @@ GB_API int gb_linear_tc(const void* X, long long ldx, const void* W, long long l
   if (pair_min < 0) { const char* e = getenv("GIBBS_B200_PAIR_MIN_TILES"); pair_min = e ? atoi(e) : 65; }
   if (bn == 128 && splits == 1 && M >= 192 && pair_tiles >= pair_min && gb_pair()) {
     rc = launch_pair(tw, tx, p, stream);
-  } else if (bn == 128 && splits == 1 && n_tiles > 148 && gb_persistent()) {
-    rc = launch_persistent<128>(tw, tx, p, stream);
   } else {
     switch (bn) {
       case 16: rc = launch<16>(tw, tx, p, stream); break;
       case 32: rc = launch<32>(tw, tx, p, stream); break;
       case 64: rc = launch<64>(tw, tx, p, stream); break;
-      case 256: rc = launch<256>(tw, tx, p, stream); break;
       default: rc = launch<128>(tw, tx, p, stream); break;
     }
   }
@@ -1387,7 +1023,6 @@ GB_API int gb_linear_tc_no_alloc(const void* X, long long ldx, const void* W, lo
   p.bias = bias; p.out = out; p.ldo = ldo; p.mode = mode; p.M = M; p.N = N;
   p.total_kb = gb_div_up(K, BK); p.kb_per_split = kb_per_split; p.splits = splits;
   p.ws = ws;
-  p.prefetch = nullptr; p.prefetch_bytes = 0;
   p.stream_weights = M <= 64 ? 1 : 0;
   p.vec_store = (((uintptr_t)out & 15) == 0 && (ldo * (mode == OUT_BF16 || mode == OUT_SWIGLU ? 2 : 4)) % 16 == 0) ? 1 : 0;
   p.status = status;
@@ -1396,7 +1031,6 @@ GB_API int gb_linear_tc_no_alloc(const void* X, long long ldx, const void* W, lo
     case 16: rc = launch<16>(tw, tx, p, stream); break;
     case 32: rc = launch<32>(tw, tx, p, stream); break;
     case 64: rc = launch<64>(tw, tx, p, stream); break;
-    case 256: rc = launch<256>(tw, tx, p, stream); break;
     default: rc = launch<128>(tw, tx, p, stream); break;
   }
   if (rc != GB_OK) return rc;

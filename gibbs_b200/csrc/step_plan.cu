@@ -27,7 +27,7 @@ typedef int (*RmsnormFn)(float*, long long, const float*, void*, int, const int*
 typedef int (*LinearSimtFn)(const void*, int, long long, const void*, int, long long, const float*, void*, int,
                             long long, int, int, int, int, cudaStream_t);
 typedef int (*LinearTcFn)(const void*, long long, const void*, long long, const float*, void*, int, long long, int, int,
-                          int, float*, int, const void*, long long, int, int*, cudaStream_t);
+                          int, float*, int, int, int*, cudaStream_t);
 typedef int (*LinearTcSplitsFn)(int, int, int);
 typedef int (*ShortConvFn)(const void*, int, long long, const float*, const float*, float*, long long, const int*,
                            const int*, const int*, const int*, void*, int, int, int, int, int, cudaStream_t);
@@ -151,7 +151,7 @@ int run_op(Walk& w, const PlanOp& o) {
         const bool defer = wants && splits > 1 && (a[11] == 0 || a[11] == 2);
         PLAN_CALL(w, F_LINEAR_TC, ((LinearTcFn)g_fn[F_LINEAR_TC])(
             ptr<const void>(w, a[0]), a[1], ptr<const void>(w, a[2]), a[3], bias, ptr<void>(w, a[5]), (int)a[11], a[6],
-            M, n, k, splits > 1 ? w.ws : nullptr, defer ? 1 : 0, nullptr, 0, w.tc_flags, w.status, w.stream));
+            M, n, k, splits > 1 ? w.ws : nullptr, defer ? 1 : 0, w.tc_flags, w.status, w.stream));
         if (o.flags & LF_RESIDUAL) {
           w.pend_splits = defer ? splits : 0;
           w.pend_bias = bias;

@@ -241,18 +241,15 @@ def _status_ptr(t: torch.Tensor):
     return p if p is not None else _c_void(device_status(t.device).data_ptr())
 
 
-# tuning switches of the tensor-core product: prefetch the next weight towards L2; evict-first hint
-_TC_PREFETCH = os.environ.get("GIBBS_B200_PREFETCH", "0") != "0"
+# tuning switch of the tensor-core product: evict-first hint on the weights of decode-sized products
 _TC_FLAGS = 1 if os.environ.get("GIBBS_B200_EVICT_FIRST", "1") != "0" else 0
 
 
 def linear_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-              accumulate: bool = False, swiglu: bool = False, prefetch: Optional[torch.Tensor] = None,
-              defer: bool = False):
+              accumulate: bool = False, swiglu: bool = False, defer: bool = False):
     """out (+)= a @ w.T (+ bias) for bfloat16 a and w on the tensor cores
     (csrc/gemm_tc.cu).  ``swiglu``: w holds gate and up rows alternating in
-    blocks of 64 and out [m, n/2] gets (g * sigmoid(g)) * u.  ``prefetch``:
-    the weight the next product will read, pulled towards L2 meanwhile.
+    blocks of 64 and out [m, n/2] gets (g * sigmoid(g)) * u.
     ``defer`` (with ``accumulate``, or for a plain bfloat16 product): when
     the kernel splits K, nothing is written to ``out``; the partial sums
     [splits, m, n] are returned instead, for the caller's next kernel to add
@@ -294,18 +291,12 @@ def linear_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
         splits = _SPLITS[key] = lib.gb_linear_tc_splits(_c_int(m), _c_int(n), _c_int(k))
     ws = torch.empty((splits, m, n), dtype=torch.float32, device=a.device) if splits > 1 else None
     defer = bool(defer and (accumulate or mode == 0) and splits > 1)
-    pf_bytes = 0
-    if not _TC_PREFETCH:
-        prefetch = None
-    elif prefetch is not None:
-        _need_cuda(prefetch)
-        pf_bytes = prefetch.numel() * prefetch.element_size()
     rc = lib.gb_linear_tc(
         _c_void(a.data_ptr()), _c_ll(a.stride(0) if m > 1 else max(a.stride(0), k)), _c_void(w.data_ptr()),
         _c_ll(w.stride(0) if n > 1 else max(w.stride(0), k)), _NULL if bias is None else _c_void(bias.data_ptr()),
         _c_void(out.data_ptr()), _c_int(mode), _c_ll(out.stride(0) if m > 1 else max(out.stride(0), n_out)), _c_int(m),
         _c_int(n), _c_int(k), _NULL if ws is None else _c_void(ws.data_ptr()), _ONE if defer else _ZERO,
-        _NULL if prefetch is None else _c_void(prefetch.data_ptr()), _c_ll(pf_bytes), _c_int(_TC_FLAGS),
+        _c_int(_TC_FLAGS),
         _status_ptr(a), _STREAM if _STREAM is not None else _stream())
     if rc < 0:
         check(lib, rc)
@@ -342,12 +333,12 @@ def linear_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-           accumulate: bool = False, prefetch: Optional[torch.Tensor] = None) -> torch.Tensor:
+           accumulate: bool = False) -> torch.Tensor:
     """out (+)= a @ w.T (+ bias); picks the matrix-product kernel for the
     operand types: tensor cores for bfloat16 x bfloat16, 32-bit FMA otherwise
     (float32 operands, a weight kept in 32-bit, rows TMA cannot address)."""
     if linear_tc_supported(a, w):
-        return linear_tc(a, w, bias, out, accumulate, prefetch=prefetch)
+        return linear_tc(a, w, bias, out, accumulate)
     return linear_simt(a, w, bias, out, accumulate)
 
 

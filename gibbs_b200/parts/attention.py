@@ -66,9 +66,6 @@ class GQAAttention(Mixer):
     def kernel_libraries(self):
         return tuple(set(self.qkv.kernel_libraries()) | set(self.out_proj.kernel_libraries()) | {"core"})
 
-    def linears(self):
-        return [self.qkv, self.out_proj]
-
     def cache_needs(self):
         return [] if self.shares_kv else [PagedKV(self.kv_heads, self.head_dim, self.window)]
 

@@ -47,9 +47,6 @@ class LMHead(Part):
     def kernel_libraries(self):
         return self.proj.kernel_libraries()
 
-    def linears(self):
-        return [self.proj]
-
     def forward(self, z: torch.Tensor) -> torch.Tensor:
         return self.proj(z, out_dtype=torch.float32)
 

@@ -37,9 +37,6 @@ class SwiGLU(FeedForward):
     def kernel_libraries(self):
         return tuple(set(self.gate_up.kernel_libraries()) | set(self.down.kernel_libraries()) | {"core"})
 
-    def linears(self):
-        return [self.gate_up, self.down]
-
     def forward(self, h, residual, step):
         if self.fused:
             act = self.gate_up(h)

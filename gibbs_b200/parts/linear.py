@@ -21,9 +21,6 @@ class Linear:
             self.out_features //= 2
         self.swiglu = swiglu
         self.rt = rt
-        # the weight of the product that runs after this one (set by the model once it is
-        # assembled); the tensor-core kernel pulls it towards L2 while it works
-        self.next_weight: Optional[torch.Tensor] = None
 
     def kernel_libraries(self):
         return ops.linear_libraries(self.weight.dtype, self.rt.dtype)
@@ -45,7 +42,7 @@ class Linear:
                 raise ValueError("a projection can only add into the residual stream")
             if ops.linear_tc_supported(x, self.weight):
                 res = ops.linear_tc(x, self.weight, self.bias, out.tensor(), accumulate=True,
-                                    prefetch=self.next_weight, defer=True)
+                                    defer=True)
                 if res is not out.x:              # K was split: the next norm adds the partial sums
                     out.defer(res, self.bias)
                 return out
@@ -54,8 +51,8 @@ class Linear:
         if out is None:
             out = torch.empty(x.shape[0], self.out_features, dtype=out_dtype or self.rt.dtype, device=x.device)
         if self.swiglu:
-            return ops.linear_tc(x, self.weight, self.bias, out, swiglu=True, prefetch=self.next_weight)
-        return ops.linear(x, self.weight, self.bias, out, accumulate, prefetch=self.next_weight)
+            return ops.linear_tc(x, self.weight, self.bias, out, swiglu=True)
+        return ops.linear(x, self.weight, self.bias, out, accumulate)
 
 
 def can_fuse_swiglu(gate: torch.Tensor, rt: Runtime) -> bool:

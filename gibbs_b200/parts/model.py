@@ -28,21 +28,6 @@ class CausalLM:
         self.plan, self.rt = plan, rt
         self.embedding, self.blocks, self.final_norm, self.head = embedding, blocks, final_norm, head
         self.vocab_size, self.hidden_size = plan.vocab_size, plan.hidden_size
-        self._link_products()
-
-    def _link_products(self) -> None:
-        """Tell every projection which weight is read after its own, in the
-        order the plan runs the layers (the head wraps around to the first
-        layer of the next step).  Parts that expose no ``linears()`` are skipped."""
-        chain = []
-        for entry in self.plan.order:
-            block = self.blocks[entry.layer]
-            for part in (block.mixer, block.ffn):
-                chain += list(getattr(part, "linears", lambda: [])())
-        chain += list(getattr(self.head, "linears", lambda: [])())
-        for cur, nxt in zip(chain, chain[1:] + chain[:1]):
-            if cur is not nxt:
-                cur.next_weight = nxt.weight
 
     def entry_needs(self):
         """For each entry of the plan's order: (cache needs of its mixer, the

@@ -42,9 +42,6 @@ class GatedShortConv(Mixer):
     def kernel_libraries(self):
         return tuple(set(self.in_proj.kernel_libraries()) | set(self.out_proj.kernel_libraries()) | {"core"})
 
-    def linears(self):
-        return [self.in_proj, self.out_proj]
-
     def cache_needs(self):
         return [SlotState((self.kernel - 1, self.hidden), torch.float32)]
 

@@ -594,17 +594,6 @@ def test_linear_tensor_cores_swiglu_epilogue(m, f, k, use_bias):
     assert int(ops.device_status(DEV).item()) == 0
 
 
-def test_linear_tensor_cores_with_prefetch_of_the_next_weight():
-    from gibbs_b200 import ops
-    torch.manual_seed(3)
-    a, ar = _quant(torch.randn(4, 512), "bfloat16")
-    w, wr = _quant(torch.randn(384, 512) / 20, "bfloat16")
-    nxt = torch.randn(1000, 333, device=DEV).to(torch.bfloat16)      # an odd number of bytes per 4 KB piece
-    out = torch.empty(4, 384, dtype=torch.float32, device=DEV)
-    ops.linear_tc(a, w, None, out, prefetch=nxt)
-    _close(out, ar @ wr.T, "float32")
-
-
 def test_deferred_split_k_and_norm_that_adds_the_partial_sums():
     """A product into the residual stream that splits K leaves partial sums;
     the norm adds them in split order, writes the stream back and normalises."""
