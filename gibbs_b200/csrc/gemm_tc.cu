@@ -537,24 +537,34 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           float* us = gs + 64 * 64;                               // [64][64]
           float* mine = row < 64 ? gs + row : us + (row - 64);
 #pragma unroll 1
-          for (int c0 = 0; c0 < hc; c0 += 16) {
-            float v[16];
-            tmem_ld_16(acc + (uint32_t)(h0 + c0), v);
+          for (int c0 = 0; c0 < hc; c0 += 32) {
+            float v[32];
+            tmem_ld_32(acc + (uint32_t)(h0 + c0), v);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) mine[(c0 + j) * 64] = v[j] + b;
+            for (int j = 0; j < 32; ++j)
+              if (c0 + j < hc) mine[(c0 + j) * 64] = v[j] + b;
           }
           tc_fence_before();
           epilogue_barrier();
           if (last && et == 0) mbar_arrive_leader(&tmem_empty_bar[a]);
           bf16* dst = (bf16*)p.out + (size_t)(m0 + h0) * p.ldo + (n0 >> 1);
-          for (int idx = et; idx < hc * 32; idx += 128) {
-            const int mm = idx >> 5, f = (idx & 31) * 2;
-            const float2 g2 = *reinterpret_cast<const float2*>(gs + mm * 64 + f);
-            const float2 u2 = *reinterpret_cast<const float2*>(us + mm * 64 + f);
-            // the result is rounded to bfloat16: the fast exponential is exact enough here
-            const float r0 = g2.x / (1.0f + __expf(-g2.x)) * u2.x;
-            const float r1 = g2.y / (1.0f + __expf(-g2.y)) * u2.y;
-            *reinterpret_cast<__nv_bfloat162*>(dst + (size_t)mm * p.ldo + f) = __floats2bfloat162_rn(r0, r1);
+          // The epilogue warps are what this product waits for (they issue several times the
+          // instructions of everything else in the kernel), so every instruction counts: four
+          // features per thread and step, the fast exponential and the fast division (the result
+          // is rounded to bfloat16, which hides both).
+          for (int idx = et; idx < hc * 16; idx += 128) {
+            const int mm = idx >> 4, f = (idx & 15) * 4;
+            const float4 g4 = *reinterpret_cast<const float4*>(gs + mm * 64 + f);
+            const float4 u4 = *reinterpret_cast<const float4*>(us + mm * 64 + f);
+            const float r0 = __fdividef(g4.x, 1.0f + __expf(-g4.x)) * u4.x;
+            const float r1 = __fdividef(g4.y, 1.0f + __expf(-g4.y)) * u4.y;
+            const float r2 = __fdividef(g4.z, 1.0f + __expf(-g4.z)) * u4.z;
+            const float r3 = __fdividef(g4.w, 1.0f + __expf(-g4.w)) * u4.w;
+            __nv_bfloat162 lo = __floats2bfloat162_rn(r0, r1), hi = __floats2bfloat162_rn(r2, r3);
+            uint2 packed;
+            packed.x = *reinterpret_cast<uint32_t*>(&lo);
+            packed.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(dst + (size_t)mm * p.ldo + f) = packed;
           }
           epilogue_barrier();
         } else if (hc > 0 && fast && p.mode == OUT_BF16) {
