@@ -60,9 +60,10 @@ __device__ __forceinline__ void store4<bf16>(bf16* dst, float4 v) {
 // VEC > 0: dim is a multiple of 4, rows are 16-byte aligned and each thread keeps its
 // VEC float4 of the row in registers (all loads of the row and of the partial sums are
 // issued together; the row is read once).  VEC == 0: any dim, two passes.
-// PEND: instantiated apart so that rows without partial sums (prompts) do not pay for the
-// registers that hold eight splits' worth of loads.
-template <typename TOut, int VEC, bool PEND>
+// PEND: how many splits' loads are requested together (0: the kernel takes no partial sums).
+// Instantiated apart so that rows without partial sums, or with one tile set (prompts), do not
+// pay for the registers that hold eight splits' worth of loads.
+template <typename TOut, int VEC, int PEND>
 __global__ void rmsnorm_kernel(float* __restrict__ x, long long ldx, const float* __restrict__ gain,
                                TOut* __restrict__ out, const int* __restrict__ rows, int dim, float eps,
                                const float* __restrict__ pend, int splits, long long n_src_rows,
@@ -84,10 +85,10 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, long long ldx, const float
       const int c = threadIdx.x + i * blockDim.x;
       v[i] = c < n4 ? reinterpret_cast<const float4*>(src)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    if (PEND && pend) {
+    if (PEND > 0 && pend) {
       // the partial sums of up to eight splits are requested together (one trip to L2, not eight)
       // and then added in split order
-      constexpr int G = 8;
+      constexpr int G = PEND > 0 ? PEND : 1;
       const size_t split_stride = (size_t)n_src_rows * dim;
       const float* p0 = pend + (size_t)sr * dim;
       for (int s0 = 0; s0 < splits; s0 += G) {
@@ -171,15 +172,17 @@ void launch_rmsnorm(float* x, long long ldx, const float* gain, TOut* out, const
     int threads = 32;
     while (threads < 1024 && threads < n4) threads <<= 1;
     if (threads > 256 && n4 <= 2 * 256) threads = 256;
-    auto kernel = n4 <= threads ? (pend ? rmsnorm_kernel<TOut, 1, true> : rmsnorm_kernel<TOut, 1, false>)
-                                : (pend ? rmsnorm_kernel<TOut, 2, true> : rmsnorm_kernel<TOut, 2, false>);
+    const int g = pend ? (splits > 1 ? 8 : 1) : 0;
+    auto kernel = n4 <= threads
+                      ? (g == 8 ? rmsnorm_kernel<TOut, 1, 8> : (g == 1 ? rmsnorm_kernel<TOut, 1, 1> : rmsnorm_kernel<TOut, 1, 0>))
+                      : (g == 8 ? rmsnorm_kernel<TOut, 2, 8> : (g == 1 ? rmsnorm_kernel<TOut, 2, 1> : rmsnorm_kernel<TOut, 2, 0>));
     gb_launch(kernel, dim3(n_rows), dim3(threads), 0, stream, x, ldx, gain, out, rows, dim, eps, pend, splits,
               n_src_rows, pend_bias);
     return;
   }
   int threads = 32;
   while (threads < 512 && threads * 4 < dim) threads <<= 1;
-  gb_launch(rmsnorm_kernel<TOut, 0, true>, dim3(n_rows), dim3(threads), 0, stream, x, ldx, gain, out, rows, dim, eps,
+  gb_launch(rmsnorm_kernel<TOut, 0, 8>, dim3(n_rows), dim3(threads), 0, stream, x, ldx, gain, out, rows, dim, eps,
             pend, splits, n_src_rows, pend_bias);
 }
 

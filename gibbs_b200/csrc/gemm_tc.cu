@@ -570,11 +570,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         } else if (hc > 0 && fast && p.mode == OUT_BF16) {
           bf16* ob = reinterpret_cast<bf16*>(staging);
 #pragma unroll 1
-          for (int c0 = 0; c0 < hc; c0 += 16) {
-            float v[16];
-            tmem_ld_16(acc + (uint32_t)(h0 + c0), v);
+          for (int c0 = 0; c0 < hc; c0 += 32) {
+            float v[32];
+            tmem_ld_32(acc + (uint32_t)(h0 + c0), v);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) ob[(c0 + j) * BM + row] = __float2bfloat16_rn(v[j] + b);
+            for (int j = 0; j < 32; ++j)
+              if (c0 + j < hc) ob[(c0 + j) * BM + row] = __float2bfloat16_rn(v[j] + b);
           }
           tc_fence_before();
           epilogue_barrier();
@@ -589,11 +590,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         } else if (hc > 0 && fast) {
           float* fb = reinterpret_cast<float*>(staging);
 #pragma unroll 1
-          for (int c0 = 0; c0 < hc; c0 += 16) {
-            float v[16];
-            tmem_ld_16(acc + (uint32_t)(h0 + c0), v);
+          for (int c0 = 0; c0 < hc; c0 += 32) {
+            float v[32];
+            tmem_ld_32(acc + (uint32_t)(h0 + c0), v);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) fb[(c0 + j) * BM + row] = v[j] + b;
+            for (int j = 0; j < 32; ++j)
+              if (c0 + j < hc) fb[(c0 + j) * BM + row] = v[j] + b;
           }
           tc_fence_before();
           epilogue_barrier();
@@ -889,7 +891,10 @@ GB_API int gb_linear_tc_supported(const void* X, long long ldx, const void* W, l
 // workspace: gb_linear_tc_workspace(M, N, K) floats (may be null when that is 0).
 // defer != 0 (modes 0 and 2): when K is split, leave the partial tiles in the workspace
 // ([splits][M][N], without bias) for the caller's next kernel to add (mode 0: and to round to
-// bfloat16); nothing is written to out.
+// bfloat16); nothing is written to out.  defer == 2 (mode 2): the same also when K is not split:
+// the whole product goes to the workspace as one "partial" tile set, so that a large product into
+// the residual stream only stores (the norm that reads the stream next adds it while it reads)
+// instead of reading and rewriting 32-bit rows from its epilogue.
 // flags bit 0: read the weights with an evict-first hint.
 // Returns the number of kernels launched, or a negative error code.
 GB_API int gb_linear_tc(const void* X, long long ldx, const void* W, long long ldw, const float* bias, void* out,
@@ -923,6 +928,15 @@ GB_API int gb_linear_tc(const void* X, long long ldx, const void* W, long long l
   }
   if (!make_tmap(&tx, X, M, K, ldx, bn)) GB_FAIL(GB_ERR_CUDA, "gb_linear_tc: cuTensorMapEncodeTiled failed (X)");
 
+  if (defer == 2 && splits == 1) {
+    if (mode != OUT_F32_ACC || workspace == nullptr)
+      GB_FAIL(GB_ERR_ARG, "gb_linear_tc: an unsplit product is deferred only when it adds into a 32-bit output and has "
+              "a workspace");
+    mode = OUT_F32;            // plain stores of the product, without the bias, into the workspace
+    out = workspace;
+    ldo = N;
+    bias = nullptr;
+  }
   GemmParams p;
   p.bias = bias; p.out = out; p.ldo = ldo; p.mode = mode; p.M = M; p.N = N;
   p.total_kb = gb_div_up(K, BK); p.kb_per_split = kb_per_split; p.splits = splits;
@@ -934,11 +948,11 @@ GB_API int gb_linear_tc(const void* X, long long ldx, const void* W, long long l
   int rc;
   const long long n_tiles = (long long)gb_div_up(N, BM) * gb_div_up(M, bn);
   const long long pair_tiles = (long long)gb_div_up(N, 2 * BM) * gb_div_up(M, PairCfg::BNP);
-  // Products with no more 256 x 256 tiles than there are CTA pairs would run one tile per pair,
-  // start-up, pipeline fill and epilogue all exposed; two 128 x 128 CTAs per SM do those a little
-  // faster.  GIBBS_B200_PAIR_MIN_TILES moves the threshold (for comparison runs).
+  // Below this many 256 x 256 tiles the one-tile CTAs take the product (two per SM; they ask L2 for
+  // twice the bytes per flop, so they lose as soon as the pairs have enough tiles).
+  // GIBBS_B200_PAIR_MIN_TILES moves the threshold (for comparison runs).
   static int pair_min = -1;
-  if (pair_min < 0) { const char* e = getenv("GIBBS_B200_PAIR_MIN_TILES"); pair_min = e ? atoi(e) : 65; }
+  if (pair_min < 0) { const char* e = getenv("GIBBS_B200_PAIR_MIN_TILES"); pair_min = e ? atoi(e) : 32; }
   if (bn == 128 && splits == 1 && M >= 192 && pair_tiles >= pair_min && gb_pair()) {
     rc = launch_pair(tw, tx, p, stream);
   } else {

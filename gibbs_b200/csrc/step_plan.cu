@@ -81,6 +81,7 @@ struct Walk {
   int attn_ctas;             // how many CTAs the decode attention aims for
   int tc_flags;              // flags of the tensor-core product (evict-first hint)
   int use_tcgen05;
+  int defer_whole_rows;      // from this many rows on, an unsplit product into the residual is deferred whole
   // what the operation before left for the one after it
   int pend_splits; const float* pend_bias;     // partial sums to be added to the residual by the next norm
   int part_splits; const float* part_bias;     // partial tiles of a product whose consumer adds them itself
@@ -148,10 +149,13 @@ int run_op(Walk& w, const PlanOp& o) {
         const int splits = ((LinearTcSplitsFn)g_fn[F_LINEAR_TC_SPLITS])(M, n, k);
         const bool wants = (o.flags & LF_RESIDUAL) || (o.flags & LF_PARTIALS) ||
                            ((o.flags & LF_PARTIALS_IF_ONE_EACH) && one_each);
-        const bool defer = wants && splits > 1 && (a[11] == 0 || a[11] == 2);
+        // a large unsplit product into the residual stream is deferred as a whole (ops.DEFER_WHOLE_ROWS)
+        const bool whole = (o.flags & LF_RESIDUAL) && splits == 1 && M >= w.defer_whole_rows;
+        const bool defer = (wants && splits > 1 && (a[11] == 0 || a[11] == 2)) || whole;
         PLAN_CALL(w, F_LINEAR_TC, ((LinearTcFn)g_fn[F_LINEAR_TC])(
             ptr<const void>(w, a[0]), a[1], ptr<const void>(w, a[2]), a[3], bias, ptr<void>(w, a[5]), (int)a[11], a[6],
-            M, n, k, splits > 1 ? w.ws : nullptr, defer ? 1 : 0, w.tc_flags, w.status, w.stream));
+            M, n, k, (splits > 1 || whole) ? w.ws : nullptr, whole ? 2 : (defer ? 1 : 0), w.tc_flags, w.status,
+            w.stream));
         if (o.flags & LF_RESIDUAL) {
           w.pend_splits = defer ? splits : 0;
           w.pend_bias = bias;
@@ -273,7 +277,7 @@ struct GbPlanRun {
   const void* ops; int n_ops;
   const long long* sym; int n_sym;
   float* ws; float* attn_ws; int* status;
-  int attn_ctas, tc_flags, use_tcgen05;
+  int attn_ctas, tc_flags, use_tcgen05, defer_whole_rows;
   int failed_lib;            // out: 0 core, 1 tensor cores, 2 this library (where the message of a failure lies)
 };
 
@@ -284,6 +288,7 @@ GB_API int gb_plan_run(GbPlanRun* r, cudaStream_t stream) {
   memset(&w, 0, sizeof(w));
   w.sym = r->sym; w.stream = stream; w.status = r->status; w.ws = r->ws; w.attn_ws = r->attn_ws;
   w.attn_ctas = r->attn_ctas; w.tc_flags = r->tc_flags; w.use_tcgen05 = r->use_tcgen05;
+  w.defer_whole_rows = r->defer_whole_rows;
   w.failed_lib = 2;
   const PlanOp* ops = (const PlanOp*)r->ops;
   for (int i = 0; i < r->n_ops; ++i) {

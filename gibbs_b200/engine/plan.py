@@ -64,7 +64,7 @@ class _Run(ctypes.Structure):
     _fields_ = [("ops", ctypes.c_void_p), ("n_ops", ctypes.c_int), ("sym", ctypes.c_void_p), ("n_sym", ctypes.c_int),
                 ("ws", ctypes.c_void_p), ("attn_ws", ctypes.c_void_p), ("status", ctypes.c_void_p),
                 ("attn_ctas", ctypes.c_int), ("tc_flags", ctypes.c_int), ("use_tcgen05", ctypes.c_int),
-                ("failed_lib", ctypes.c_int)]
+                ("defer_whole_rows", ctypes.c_int), ("failed_lib", ctypes.c_int)]
 
 
 class PlanBuilder:
@@ -164,6 +164,8 @@ class PlanBuilder:
                 s = lib.gb_linear_tc_splits(ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(k))
                 if s > 1:
                     self.ws_floats = max(self.ws_floats, s * 128 * n)
+            if mode == "residual":
+                self.ws_floats = max(self.ws_floats, self.cap * n)     # large products are deferred whole
         self.emit(P_LINEAR, [x.data_ptr(), x.stride(0), self.keep(weight), weight.stride(0), self.keep(bias),
                              out if isinstance(out, int) else out.data_ptr(),
                              n if isinstance(out, int) else out.stride(0), sym(rows_symbol), n, k, 0 if use_tc else 1,
@@ -236,6 +238,7 @@ class StepPlan:
         r.ws, r.attn_ws = self.ws.data_ptr(), self.attn_ws.data_ptr()
         r.status = ops.device_status(b.device).data_ptr()
         r.attn_ctas, r.tc_flags, r.use_tcgen05 = ops._ATTN_CTAS, ops._TC_FLAGS, int(ops._ATTN_TCGEN05)
+        r.defer_whole_rows = ops.DEFER_WHOLE_ROWS
 
     def _bind(self, need_tensorcore: bool) -> None:
         """Hand the walker the entry points of the kernel libraries; those of the tensor-core

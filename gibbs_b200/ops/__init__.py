@@ -245,6 +245,13 @@ def _status_ptr(t: torch.Tensor):
 _TC_FLAGS = 1 if os.environ.get("GIBBS_B200_EVICT_FIRST", "1") != "0" else 0
 
 
+# From this many rows on, a product that adds into the 32-bit residual stream does not read and
+# rewrite the stream from its epilogue: it stores its result as one set of "partial" tiles, which
+# the norm that reads the stream next adds (measured on 2,048-token prompts: the read-modify-write
+# epilogue was what those products waited for).  The step walker (csrc/step_plan.cu) has the same rule.
+DEFER_WHOLE_ROWS = 256
+
+
 def linear_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
               accumulate: bool = False, swiglu: bool = False, defer: bool = False):
     """out (+)= a @ w.T (+ bias) for bfloat16 a and w on the tensor cores
@@ -289,13 +296,16 @@ def linear_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     splits = _SPLITS.get(key)
     if splits is None:
         splits = _SPLITS[key] = lib.gb_linear_tc_splits(_c_int(m), _c_int(n), _c_int(k))
-    ws = torch.empty((splits, m, n), dtype=torch.float32, device=a.device) if splits > 1 else None
-    defer = bool(defer and (accumulate or mode == 0) and splits > 1)
+    # a large unsplit product into the residual stream is deferred as a whole (see DEFER_WHOLE_ROWS)
+    whole = bool(defer and accumulate and splits == 1 and m >= DEFER_WHOLE_ROWS)
+    ws = torch.empty((splits, m, n), dtype=torch.float32, device=a.device) if (splits > 1 or whole) else None
+    defer = bool(defer and (accumulate or mode == 0) and splits > 1) or whole
     rc = lib.gb_linear_tc(
         _c_void(a.data_ptr()), _c_ll(a.stride(0) if m > 1 else max(a.stride(0), k)), _c_void(w.data_ptr()),
         _c_ll(w.stride(0) if n > 1 else max(w.stride(0), k)), _NULL if bias is None else _c_void(bias.data_ptr()),
         _c_void(out.data_ptr()), _c_int(mode), _c_ll(out.stride(0) if m > 1 else max(out.stride(0), n_out)), _c_int(m),
-        _c_int(n), _c_int(k), _NULL if ws is None else _c_void(ws.data_ptr()), _ONE if defer else _ZERO,
+        _c_int(n), _c_int(k), _NULL if ws is None else _c_void(ws.data_ptr()),
+        _c_int(2) if whole else (_ONE if defer else _ZERO),
         _c_int(_TC_FLAGS),
         _status_ptr(a), _STREAM if _STREAM is not None else _stream())
     if rc < 0:
