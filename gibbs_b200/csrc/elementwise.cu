@@ -35,6 +35,27 @@ GB_API int gb_embed(const void* table, int table_dtype, const int* ids, float* o
   return GB_OK;
 }
 
+// ---------------------------------------------------------------- token feedback
+// ids[t] = picked[from[t]] where from[t] >= 0: the tokens a step's sampler picked feed the
+// next step's gather without a trip through the host (the reference's Metal stream does
+// the same with the id its argmax head wrote, src/backend/metal/program.rs:458-544).
+__global__ void feed_tokens_kernel(int* __restrict__ ids, const int* __restrict__ picked,
+                                   const int* __restrict__ from, int n, int n_picked) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n) return;
+  const int f = from[t];
+  if (f >= 0 && f < n_picked) ids[t] = picked[f];
+}
+
+GB_API int gb_feed_tokens(int* ids, const int* picked, const int* from, int n, int n_picked, cudaStream_t stream) {
+  if (n <= 0) return GB_OK;
+  gb_launch(feed_tokens_kernel, dim3(gb_div_up(n, 128)), dim3(128), 0, stream, ids, picked, from, n, n_picked);
+  GB_CHECK_LAUNCH("gb_feed_tokens");
+  return GB_OK;
+}
+
 // ---------------------------------------------------------------- RMSNorm
 // One block per output row.  `rows` (optional) gathers input rows.  The sum of
 // squares is taken in a fixed order, so a row's result does not depend on

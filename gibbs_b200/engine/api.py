@@ -56,10 +56,12 @@ class Generator:
         self.eos_ids = tuple(getattr(conf, "eos_token_ids", ()) or ())
         self.max_batch_tokens, self.max_running, self.seed = max_batch_tokens, max_running, seed
 
-    def scheduler(self, on_token=None, stop_at_eos: bool = True) -> Scheduler:
+    def scheduler(self, on_token=None, stop_at_eos: bool = True, overlap: bool = True) -> Scheduler:
+        """``overlap``: decode steps are launched on the ids the device picked, one step
+        before the host reads them (see ``engine/scheduler.py``)."""
         return Scheduler(self.engine, self.sampler, max_batch_tokens=self.max_batch_tokens,
                          max_running=self.max_running, eos_ids=self.eos_ids if stop_at_eos else (), seed=self.seed,
-                         on_token=on_token)
+                         on_token=on_token, overlap=overlap)
 
     def generate(self, prompts: Sequence[Sequence[int]], params=None, stop_at_eos: bool = True) -> list:
         """Generated token ids for each prompt (lists of ids in, lists of ids out)."""

@@ -166,16 +166,22 @@ def fill_contexts(engine: Engine, batch: int, prompt_len: int, seed: int, chunk:
 
 def measure_decode(engine: Engine, batch: int, prompt_len: int, steps: int, warmup: int, seed: int = 0) -> dict:
     """``steps`` decode steps of ``batch`` requests whose contexts start at
-    ``prompt_len``: every step feeds each request its last token, takes the
-    logits and picks the next token greedily on the device."""
-    tokens = fill_contexts(engine, batch, prompt_len, seed)
+    ``prompt_len``: every step feeds each request the token the step before
+    picked for it (the ids stay on the device, as in the scheduler's
+    overlapped loop), takes the logits and picks the next token greedily on
+    the device.  The host copies each step's metadata and launches; it waits
+    for nothing inside the timed region."""
+    first = fill_contexts(engine, batch, prompt_len, seed)
     sampler = Sampler(engine.device)
     greedy = [SamplingParams(temperature=0.0)] * batch
     zeros = [0] * batch
+    places = list(range(batch))
+    entries = [StepEntry(("bench", r), [0], [0]) for r in range(batch)]
+    tokens = torch.tensor(first, dtype=torch.int32, device=engine.device)
 
     def one_step(tokens):
-        logits = engine.step([StepEntry(("bench", r), [tokens[r]], [0]) for r in range(batch)])
-        return sampler(logits, greedy, zeros, zeros)
+        logits = engine.step(entries, feed=(tokens, places))
+        return sampler.sample_device(logits, greedy, zeros, zeros)
 
     for _ in range(warmup):
         tokens = one_step(tokens)
@@ -202,16 +208,18 @@ def measure_decode(engine: Engine, batch: int, prompt_len: int, steps: int, warm
 
 
 def measure_decode_e2e(generator, batch: int, prompt_len: int, steps: int, warmup: int, seed: int = 0) -> dict:
-    """The same through the public entry point's scheduler: token ids come from
-    host lists, every step copies its inputs from pinned host memory and reads
-    the picked ids back to the host."""
+    """The same through the public entry point's scheduler: prompts come from host
+    lists, every step copies its metadata (positions, block tables, places of the fed
+    ids) from pinned host memory and the picked ids go back to pinned host memory, from
+    where they are emitted; a decode step is launched on the ids the device picked one
+    step before the host reads them."""
     rng = np.random.default_rng(seed)
     sched: Scheduler = generator.scheduler(stop_at_eos=False)
     # prompts finish at different steps: leave room so that nobody reaches max_new_tokens while timed
     params = SamplingParams(temperature=0.0, max_new_tokens=warmup + steps + 4 * batch + 16)
     for _ in range(batch):
         sched.submit(rng.integers(0, generator.engine.vocab_size, prompt_len).tolist(), params)
-    while any(not s.decoding for s in sched.sequences.values()):
+    while any(not s.output for s in sched.sequences.values()):
         sched.step()
     for _ in range(warmup):
         sched.step()
@@ -225,7 +233,7 @@ def measure_decode_e2e(generator, batch: int, prompt_len: int, steps: int, warmu
     for sid in list(sched.sequences):
         sched.cancel(sid)
     sched.step()
-    meta_ints = 3 * 4 * ((batch + 3) // 4) + 6 * 4 * ((batch + 3) // 4) \
+    meta_ints = 4 * 4 * ((batch + 3) // 4) + 6 * 4 * ((batch + 3) // 4) \
         + len(generator.engine.cache.groups) * batch * generator.engine.cache.max_blocks
     return {"value": n / dt, "unit": "tokens/s", "h2d_bytes_per_step": 4 * meta_ints, "d2h_bytes_per_step": 4 * batch,
             "ms_per_step": dt * 1e3 / steps}

@@ -27,6 +27,20 @@ head of the queue, to be recomputed from its prompt plus the tokens it has
 already emitted (fixed-size state cannot be rewound).  Tokens that were
 emitted are never emitted twice, and a request that cannot fit the pool even
 alone ends with ``error``.
+
+Token feedback (``overlap=True``).  The reference's Metal stream feeds the id
+its argmax head picked to the next token's queued commands on the device, so
+that the host never idles the GPU (``src/backend/metal/program.rs:458-544``).
+Here a step whose every entry picks a token leaves its ids on the device and
+on their way to pinned host memory; the next call launches the following
+decode step on the device's ids *before* it waits for the host's copy, and
+then reads, emits and finishes for the step before.  A request that ends on
+an id nobody could foresee (end of sequence, a stop id) has then run one
+token too far: the token is dropped and its pages go back like the others.
+Ends by length are foreseen and leave the batch on time.  Whenever the next
+step needs the host's decisions first (a request waits for admission, one
+was cancelled, the pages would not suffice), the step in flight is read
+before anything else happens, and the scheduler goes on as without overlap.
 """
 from __future__ import annotations
 
@@ -108,13 +122,30 @@ class StepOutput:
     preempted: list = field(default_factory=list)   # sequence ids
 
 
+@dataclass
+class _InFlight:
+    """A launched step whose picked ids the host has not read yet."""
+    seqs: list                                      # whose token it picks, in the order of the ids
+    pending: object                                 # ``device_ids`` and ``wait() -> list of ids``
+    launched: float
+    n_prefill: int
+    n_decode: int
+
+
 class Scheduler:
     def __init__(self, engine, sampler: Callable, max_batch_tokens: int = MAX_PREFILL_CHUNK,
                  max_running: Optional[int] = None, eos_ids: Sequence[int] = (), seed: int = 0,
-                 on_token: Optional[Callable] = None):
+                 on_token: Optional[Callable] = None, overlap: bool = False):
         """engine: ``open/close/step/can_run/max_context/max_requests``;
-        sampler: ``(logits, params, seeds, counters) -> token ids``."""
+        sampler: ``(logits, params, seeds, counters) -> token ids``.
+        ``overlap`` needs ``sampler.sample_async(...)`` (ids that stay on the
+        device, with ``wait()`` for the host's copy) and an engine whose
+        ``step`` takes ``feed``."""
         self.engine, self.sampler = engine, sampler
+        self.overlap = bool(overlap)
+        if self.overlap and not hasattr(sampler, "sample_async"):
+            raise ValueError("overlap needs a sampler with sample_async")
+        self._inflight: Optional[_InFlight] = None
         self.max_batch_tokens = max(1, int(max_batch_tokens))
         self.max_running = min(int(max_running or engine.max_requests), engine.max_requests)
         self.ctx = engine.max_context
@@ -150,7 +181,7 @@ class Scheduler:
         self.sequences[sid].cancelled = True
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self.waiting or self.running or self._inflight is not None)
 
     # -- internals ---------------------------------------------------------------
     def _finish(self, seq: Sequence_, reason: FinishReason, out: StepOutput, error: Optional[str] = None):
@@ -227,6 +258,17 @@ class Scheduler:
     def step(self) -> StepOutput:
         out = StepOutput()
         self.steps += 1
+        prev = self._inflight
+        if prev is not None:
+            # the next decode step goes out on the device's ids before the host reads this one's
+            self._inflight = self._launch_fed(prev)
+            self._collect(prev, out)
+            if self._inflight is not None and all(s.state != SeqState.RUNNING for s in self._inflight.seqs):
+                self._inflight = None               # everybody in it has ended meanwhile
+            for seq in [s for s in self.running if s.cancelled]:
+                self._finish(seq, FinishReason.CANCELLED, out)
+            out.active_sequences = len(self.running)
+            return out
         for seq in [s for s in self.running if s.cancelled]:
             self._finish(seq, FinishReason.CANCELLED, out)
         decoding_now = sum(1 for s in self.running if s.decoding)
@@ -262,11 +304,18 @@ class Scheduler:
                 n_decode += 1
             else:
                 n_prefill += n
+        # ids may stay on the device when every request of the step picks one
+        # (and none only ran to fill its cache, max_new_tokens == 0)
+        lag = self.overlap and len(samplers) == len(plan) and all(s.params.max_new_tokens > 0 for s in samplers)
         t0 = time.perf_counter()
         try:
             logits = self.engine.step(entries)
-            picked = self.sampler(logits, [s.params for s in samplers], [s.seed for s in samplers],
-                                  [len(s.output) for s in samplers]) if samplers else []
+            args = (logits, [s.params for s in samplers], [s.seed for s in samplers],
+                    [len(s.output) for s in samplers])
+            if lag:
+                pending, picked = self.sampler.sample_async(*args), []
+            else:
+                pending, picked = None, (self.sampler(*args) if samplers else [])
         except Exception as e:  # the step failed as a whole: its requests end with an error
             if isinstance(e, (OutOfPages, KeyboardInterrupt)):
                 raise
@@ -274,11 +323,22 @@ class Scheduler:
                 self._finish(s, FinishReason.ERROR, out, f"step failed: {e}")
             out.active_sequences = len(self.running)
             return out
-        dt = time.perf_counter() - t0
         for s, n in plan:
             s.fed += n
+        if pending is not None:
+            self._inflight = _InFlight(samplers, pending, t0, n_prefill, n_decode)
+            out.active_sequences = len(self.running)
+            return out
+        self._emit(samplers, picked, out)
+        self._account(out, time.perf_counter() - t0, n_prefill, n_decode)
+        out.active_sequences = len(self.running)
+        return out
 
+    def _emit(self, samplers, picked, out: StepOutput) -> None:
+        """What the picked ids mean for their requests: emitted, or the end."""
         for s, tok in zip(samplers, picked):
+            if s.state != SeqState.RUNNING:
+                continue                            # it ended while this step was in flight
             tok = int(tok)
             if s.params.max_new_tokens == 0:
                 self._finish(s, FinishReason.LENGTH, out)
@@ -293,11 +353,52 @@ class Scheduler:
                 self.on_token(s.id, tok)
             if len(s.prompt) + len(s.output) >= self.ctx or len(s.output) >= s.params.max_new_tokens:
                 self._finish(s, FinishReason.LENGTH, out)
+
+    @staticmethod
+    def _account(out: StepOutput, dt: float, n_prefill: int, n_decode: int) -> None:
         total = max(n_prefill + n_decode, 1)
         out.prefill = (dt * n_prefill / total, n_prefill)
         out.decode = (dt * n_decode / total, n_decode)
-        out.active_sequences = len(self.running)
-        return out
+
+    # -- token feedback -----------------------------------------------------------
+    def _collect(self, flight: _InFlight, out: StepOutput) -> None:
+        """Wait for the ids of a launched step and do what they ask for."""
+        self._emit(flight.seqs, flight.pending.wait(), out)
+        self._account(out, time.perf_counter() - flight.launched, flight.n_prefill, flight.n_decode)
+
+    def _launch_fed(self, prev: _InFlight) -> Optional[_InFlight]:
+        """The decode step after ``prev``, launched on the ids ``prev`` left on the
+        device; None when the host has to decide something first."""
+        if self.waiting or any(s.cancelled for s in self.running):
+            return None
+        if sum(1 for s in prev.seqs if s.state == SeqState.RUNNING) != len(self.running):
+            return None                             # somebody runs who is not in the step in flight
+        seqs, places = [], []
+        for i, s in enumerate(prev.seqs):
+            if s.state != SeqState.RUNNING:
+                continue                            # it ended on an id of the step before
+            new = len(s.output) + 1                 # with the id that is on its way
+            if new >= s.params.max_new_tokens or len(s.prompt) + new >= self.ctx:
+                continue                            # it ends by length when that id is read
+            seqs.append(s)
+            places.append(i)
+        if not seqs:
+            return None
+        entries = [StepEntry(s.id, [0], [0]) for s in seqs]
+        if not self.engine.can_run(entries):
+            return None                             # preemption is decided with every id known
+        t0 = time.perf_counter()
+        try:
+            logits = self.engine.step(entries, feed=(prev.pending.device_ids, places))
+            pending = self.sampler.sample_async(logits, [s.params for s in seqs], [s.seed for s in seqs],
+                                                [len(s.output) + 1 for s in seqs])
+        except KeyboardInterrupt:
+            raise
+        except Exception:
+            return None                             # the step is tried again, and judged, with every id known
+        for s in seqs:
+            s.fed += 1
+        return _InFlight(seqs, pending, t0, 0, len(seqs))
 
     # -- convenience -------------------------------------------------------------
     def run(self, max_steps: Optional[int] = None) -> list:

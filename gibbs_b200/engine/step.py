@@ -72,7 +72,7 @@ class StepBuilder:
         self.cache, self.device = cache, torch.device(device)
         self.max_requests, self.max_step_tokens = int(max_requests), int(max_step_tokens)
         n_groups = len(cache.groups)
-        cap = 4 * _align4(self.max_step_tokens) + 5 * _align4(self.max_requests) \
+        cap = 5 * _align4(self.max_step_tokens) + 5 * _align4(self.max_requests) \
             + n_groups * self.max_requests * cache.max_blocks + 16
         self._staging = [torch.empty(cap, dtype=torch.int32).pin_memory() for _ in range(4)]
         self._staging_np = [t.numpy() for t in self._staging]
@@ -93,20 +93,22 @@ class StepBuilder:
         self._record(turn)
         return self._state(self.dev_meta, offs, entries, rcs, n_tok, n_req, n_want)
 
-    def _layout(self, n_tok: int, n_req: int, n_want: int):
+    def _layout(self, n_tok: int, n_req: int, n_want: int, fed: bool = False):
         """Offsets (in int32) of the sections of the metadata buffer, each
         16-byte aligned: token ids, token->request, token->position; per
         request first row, count, length before, length after, slot; wanted
-        rows; one block table per group."""
+        rows; one block table per group; and, when ``fed``, for each token the
+        place among the ids picked on the device that it comes from (or -1)."""
         n_groups, mb = len(self.cache.groups), self.cache.max_blocks
-        sizes = [n_tok, n_tok, n_tok, n_req, n_req, n_req, n_req, n_req, max(n_want, 1), n_groups * n_req * mb]
+        sizes = [n_tok, n_tok, n_tok, n_req, n_req, n_req, n_req, n_req, max(n_want, 1), n_groups * n_req * mb,
+                 n_tok if fed else 0]
         offs, o = [], 0
         for sz in sizes:
             offs.append(o)
             o += _align4(sz)
         return offs, o
 
-    def _fill_staging(self, entries, rcs, offs, n_tok, n_req, n_want) -> int:
+    def _fill_staging(self, entries, rcs, offs, n_tok, n_req, n_want, fed_from=None) -> int:
         turn = self._turn
         self._turn = (turn + 1) % len(self._staging)
         if self._staging_evt[turn] is not None:
@@ -131,6 +133,12 @@ class StepBuilder:
         if n_groups:
             bt = buf[offs[9]:offs[9] + n_groups * n_req * mb].reshape(n_groups, n_req, mb)
             self.cache.fill_block_tables(rcs, bt)
+        if fed_from is not None:
+            src = buf[offs[10]:offs[10] + n_tok]
+            src[:] = -1
+            for r, f in enumerate(fed_from):
+                if f >= 0:
+                    src[qs[r]] = f
         return turn
 
     def _record(self, turn: int) -> None:
@@ -183,6 +191,7 @@ class Engine:
         self.status = ops.device_status(self.device)
         self.builder = StepBuilder(self.cache, self.device, self.max_requests, self.max_step_tokens, self.status)
         self.steps_run = 0
+        self.fed_steps = 0          # steps some of whose tokens came from ids on the device
         # decode steps are replayed from CUDA graphs, one per batch size, unless a part of the
         # model cannot be captured (it reads host-side step data)
         self.use_graphs = bool(use_graphs) and all(getattr(b.mixer, "capturable", True) for b in model.blocks)
@@ -259,11 +268,17 @@ class Engine:
             raise StepError(f"{total} tokens in one step; the engine was made for {self.max_step_tokens}")
         return total
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], feed=None) -> Optional[torch.Tensor]:
         """Run one batch.  Returns float32 logits [number of wanted places,
         vocab] on the device, in the order of the entries and of each entry's
         ``want``; None when nothing is wanted.  Raises OutOfPages, before
         anything changes, if the pools cannot hold the step.
+
+        ``feed`` = (picked, places): ``picked`` are int32 token ids on the
+        device (what a sampler wrote after an earlier step), ``places`` has
+        one number per entry: the index in ``picked`` of the entry's single
+        token, or -1 for an entry whose tokens are the given ones.  The host
+        then need not have read the ids before it launches the step.
 
         A step in which every request brings exactly one token and wants its
         logits (a decode step) is replayed from a CUDA graph captured for that
@@ -271,6 +286,15 @@ class Engine:
         overwritten by the next decode step of the same size."""
         entries = list(entries)
         n_tok = self._validate(entries)
+        fed_from = None
+        if feed is not None:
+            picked, fed_from = feed[0], [int(f) for f in feed[1]]
+            if len(fed_from) != len(entries):
+                raise StepError("feed: one place per entry expected")
+            for e, f in zip(entries, fed_from):
+                if f >= 0 and (len(e.tokens) != 1 or f >= picked.numel()):
+                    raise StepError(f"request {e.request_id!r}: a token fed from the device stands alone in its "
+                                    f"entry and its place lies among the {picked.numel()} picked ids")
         if not self.can_run(entries):
             raise OutOfPages(f"the step needs more pages than are free {self.cache.free_pages()}")
         rcs = [self.cache.live[e.request_id] for e in entries]
@@ -280,14 +304,20 @@ class Engine:
         n_req = len(entries)
         n_want = sum(len(e.want) for e in entries)
         bld = self.builder
-        offs, total = bld._layout(n_tok, n_req, n_want)
-        turn = bld._fill_staging(entries, rcs, offs, n_tok, n_req, n_want)
+        offs, total = bld._layout(n_tok, n_req, n_want, fed_from is not None)
+        turn = bld._fill_staging(entries, rcs, offs, n_tok, n_req, n_want, fed_from)
         decode = self.use_graphs and n_tok == n_req and n_want == n_req
+
+        def fed(dev):
+            if fed_from is not None:
+                self.fed_steps += 1
+                ops.feed_tokens(dev[offs[0]:offs[0] + n_tok], picked, dev[offs[10]:offs[10] + n_tok])
 
         if decode and n_req in self._graphs:
             g = self._graphs[n_req]
             g["meta"][:total].copy_(bld._staging[turn][:total], non_blocking=True)
             bld._record(turn)
+            fed(g["meta"])
             g["graph"].replay()
             ops._launched(g["launches"])
             logits = g["logits"]
@@ -295,6 +325,7 @@ class Engine:
             dev = self._graph_meta(n_req, total) if decode else bld.dev_meta
             dev[:total].copy_(bld._staging[turn][:total], non_blocking=True)
             bld._record(turn)
+            fed(dev)
             before = ops.launch_count()
             if self.plan is not None:
                 args = (n_tok, n_req, n_want, max(len(e.tokens) for e in entries), dev.data_ptr(), offs)
@@ -318,7 +349,9 @@ class Engine:
     def _graph_meta(self, batch: int, total: int) -> torch.Tensor:
         buf = self._graph_bufs.get(batch)
         if buf is None:
-            buf = self._graph_bufs[batch] = torch.empty(total, dtype=torch.int32, device=self.device)
+            # with room for the feedback section, whether or not the first step of this size has one
+            size = self.builder._layout(batch, batch, batch, True)[1]
+            buf = self._graph_bufs[batch] = torch.empty(max(size, total), dtype=torch.int32, device=self.device)
         return buf
 
     def _run_plan(self, n_tok, n_req, n_want, max_q_len, meta_ptr, offs, max_ctx) -> Optional[torch.Tensor]:

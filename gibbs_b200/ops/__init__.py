@@ -124,6 +124,20 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Te
     return out
 
 
+def feed_tokens(ids: torch.Tensor, picked: torch.Tensor, source: torch.Tensor) -> torch.Tensor:
+    """ids[t] = picked[source[t]] wherever source[t] >= 0 (all int32, on the device)."""
+    _need_cuda(ids, picked, source)
+    lib = library("core")
+    for t, what in ((ids, "feed_tokens ids"), (picked, "feed_tokens picked"), (source, "feed_tokens source")):
+        _i32(t, what)
+    if source.numel() != ids.numel():
+        raise KernelError("feed_tokens: one source index per token id expected")
+    _launched(1)
+    check(lib, lib.gb_feed_tokens(_ptr(ids), _ptr(picked), _ptr(source), _c_int(ids.numel()),
+                                  _c_int(picked.numel()), _stream()))
+    return ids
+
+
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
             rows: Optional[torch.Tensor] = None, pending=None) -> torch.Tensor:
     """out[r, :] = x[rows[r] or r, :] * rsqrt(mean(x^2) + eps) * gain; x is 32-bit.

@@ -31,11 +31,40 @@ def _signed(v: int) -> int:
     return v - (1 << 64) if v >= (1 << 63) else v
 
 
+class PendingIds:
+    """Token ids that were picked on the device and are on their way to the
+    host: ``device_ids`` can feed the next step at once, ``wait()`` gives the
+    host's copy when the transfer has ended."""
+
+    def __init__(self, device_ids: torch.Tensor, host: torch.Tensor, event):
+        self.device_ids, self._host, self._event = device_ids, host, event
+
+    def wait(self) -> list:
+        self._event.synchronize()
+        return self._host.tolist()
+
+
 class Sampler:
     def __init__(self, device):
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise RuntimeError("the sampler is a CUDA kernel; there is no host path")
+        self._pinned: list = []
+        self._turn = 0
+
+    def sample_async(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+                     counters: Sequence[int]) -> PendingIds:
+        """Pick on the device and start the copy to pinned host memory; nothing waits."""
+        out = self.sample_device(logits, params, seeds, counters)
+        rows = out.numel()
+        if not self._pinned or self._pinned[0].numel() < rows:
+            self._pinned = [torch.empty(max(rows, 64), dtype=torch.int32).pin_memory() for _ in range(4)]
+        host = self._pinned[self._turn][:rows]
+        self._turn = (self._turn + 1) % len(self._pinned)
+        host.copy_(out, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return PendingIds(out, host, event)
 
     def __call__(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                  counters: Sequence[int]) -> list[int]:

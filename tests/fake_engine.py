@@ -21,6 +21,7 @@ class FakeEngine:
         self.max_requests, self.max_context, self.vocab = max_requests, max_context, vocab
         self.fed = {}
         self.log = []               # per step: [(request id, number of tokens, wanted?)]
+        self.events = []            # "launch", "launch fed", and "read" from LaggingSampler
         self.fail_on = fail_on      # step index at which step() raises
 
     def open(self, rid):
@@ -38,7 +39,15 @@ class FakeEngine:
             need += self.cache.pages_needed(rc.length + len(e.tokens)) - len(rc.block_tables[0])
         return need <= self.cache.groups[0].pool.n_free
 
-    def step(self, entries):
+    def step(self, entries, feed=None):
+        if feed is not None:
+            # ids that a sampler left "on the device": the fake reads them where the real engine's kernel would
+            picked, places = feed
+            self.events.append("launch fed")
+            entries = [type(e)(e.request_id, [picked[f]] if f >= 0 else e.tokens, e.want)
+                       for e, f in zip(entries, places)]
+        else:
+            self.events.append("launch")
         if self.fail_on is not None and len(self.log) == self.fail_on:
             self.log.append("failed")
             raise RuntimeError("injected step failure")
@@ -62,6 +71,30 @@ class FakeEngine:
 
 def argmax_sampler(logits, params, seeds, counters):
     return [int(torch.argmax(r)) for r in logits]
+
+
+class LaggingSampler:
+    """argmax whose ids "stay on the device": ``sample_async`` hands out a list
+    at once, ``wait()`` notes in the engine's event list when the host read it."""
+
+    def __init__(self, engine):
+        self.engine = engine
+
+    def __call__(self, logits, params, seeds, counters):
+        self.engine.events.append("read")
+        return argmax_sampler(logits, params, seeds, counters)
+
+    def sample_async(self, logits, params, seeds, counters):
+        ids, events = argmax_sampler(logits, params, seeds, counters), self.engine.events
+
+        class Pending:
+            device_ids = ids
+
+            def wait(self):
+                events.append("read")
+                return list(ids)
+
+        return Pending()
 
 
 def expected_greedy(prompt, n_new, vocab, eos=()):

@@ -116,3 +116,48 @@ def test_step_plan_gives_the_same_bits_as_the_parts_forward(tmp_path_factory, na
             assert np.array_equal(pa[rid], fa[rid]), rid
         for rid in pb:
             assert np.array_equal(pb[rid], fb[rid]), rid
+
+
+@pytest.mark.parametrize("use_graphs", [True, False])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_tokens_fed_from_the_device_equal_tokens_given_by_the_host(tmp_path_factory, dtype, use_graphs):
+    """``Engine.step(..., feed=...)``: ids that lie on the device (where a sampler wrote them) stand
+    in for the host's; entries may be fed from any place, beside entries with tokens of their own."""
+    from gibbs_b200 import Engine
+    from gibbs_b200.engine.step import StepEntry, StepError
+    folder, model = _setup(tmp_path_factory, "B", dtype)
+    reqs = _requests("B", [20, 9, 33], seed=3)
+    picked_host = [17, 999, 4, 321]
+    picked = torch.tensor(picked_host, dtype=torch.int32, device="cuda:0")
+    out = []
+    for fed in (False, True):
+        eng = Engine(model, n_pages=24, page_size=16, max_requests=4, use_graphs=use_graphs)
+        rows = []
+        for rid in reqs:
+            eng.open(rid)
+        eng.step([StepEntry(rid, toks) for rid, toks in reqs.items()])
+        rids = list(reqs)
+        for turn in range(3):       # the second and third turn replay the decode graph
+            places = [(turn + 2 * i) % 4 for i in range(3)]
+            if fed:
+                entries = [StepEntry(r, [0], [0]) for r in rids]
+                rows.append(eng.step(entries, feed=(picked, places)).clone())
+            else:
+                rows.append(eng.step([StepEntry(r, [picked_host[p]], [0]) for r, p in zip(rids, places)]).clone())
+        # a prompt portion with tokens of its own beside two fed tokens
+        portion = random_ids(8, 5, 1000)
+        if fed:
+            entries = [StepEntry(rids[0], [0], [0]), StepEntry(rids[1], portion, [1, 4]), StepEntry(rids[2], [0], [0])]
+            rows.append(eng.step(entries, feed=(picked, [3, -1, 1])).clone())
+            with pytest.raises(StepError, match="stands alone"):
+                eng.step([StepEntry(rids[0], [1, 2], [0])], feed=(picked, [0]))
+            with pytest.raises(StepError, match="stands alone"):
+                eng.step([StepEntry(rids[0], [0], [0])], feed=(picked, [4]))
+        else:
+            entries = [StepEntry(rids[0], [picked_host[3]], [0]), StepEntry(rids[1], portion, [1, 4]),
+                       StepEntry(rids[2], [picked_host[1]], [0])]
+            rows.append(eng.step(entries).clone())
+        eng.check_status()
+        out.append(rows)
+    for a, b in zip(*out):
+        assert torch.equal(a, b)

@@ -112,6 +112,42 @@ def test_scheduler_preempts_and_recomputes_on_the_gpu(tmp_path):
     assert gen.engine.cache.free_pages() == [7]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_token_feedback_emits_the_tokens_of_the_plain_loop(tmp_path, dtype):
+    """Decode steps launched on the ids the device picked, one step before the host reads
+    them, against the loop that reads every id first: the same tokens and finish reasons,
+    with greedy and seeded temperature requests, ends by length at different steps and (in
+    32-bit, where a changed batch cannot move a choice) an end on a stop id."""
+    from gibbs_b200 import SamplingParams
+    stored = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+    folder = make_folder(tmp_path, "B", stored=stored, std=0.05)
+    gen = _gen(folder, dtype)
+    prompts = [random_ids(21, 33, 1000), random_ids(22, 5, 1000), random_ids(23, 18, 1000), [7]]
+    free = gen.generate([prompts[3]], SamplingParams(temperature=0.0, max_new_tokens=31), stop_at_eos=False)[0]
+    stop = (free[12],) if dtype == "float32" else ()
+    params = [SamplingParams(temperature=0.0, max_new_tokens=40),
+              SamplingParams(temperature=0.8, top_k=8, top_p=0.9, seed=5, max_new_tokens=25),
+              SamplingParams(temperature=0.0, max_new_tokens=3),
+              SamplingParams(temperature=0.0, max_new_tokens=31, stop_ids=stop)]
+    got = []
+    for overlap in (False, True):
+        sched = gen.scheduler(stop_at_eos=False, overlap=overlap)
+        ids = [sched.submit(p, q) for p, q in zip(prompts, params)]
+        before = gen.engine.fed_steps
+        emitted = {i: [] for i in ids}
+        while sched.has_work():
+            for i, t in sched.step().emitted:
+                emitted[i].append(t)
+        fed = gen.engine.fed_steps - before
+        assert (fed >= 30) if overlap else (fed == 0)
+        assert all(emitted[i] == sched.sequences[i].output for i in ids)
+        got.append([(sched.sequences[i].output, sched.sequences[i].finish) for i in ids])
+        assert not gen.engine.cache.live
+    assert got[0] == got[1]
+    if stop:
+        assert got[1][3][0] == free[:free.index(stop[0])] and got[1][3][1] == "stop"
+
+
 def test_eos_from_config_stops_generation(tmp_path):
     from gibbs_b200 import Lfm2Config, SamplingParams, write_random_model
     raw = dict(TINY["A"][0])

@@ -5,7 +5,9 @@ prompt is not starved, max_new_tokens is exact, generation stops at the
 context's end, a cancelled request frees what it holds."""
 import pytest
 
-from fake_engine import FakeEngine, argmax_sampler, expected_greedy
+import random
+
+from fake_engine import FakeEngine, LaggingSampler, argmax_sampler, expected_greedy
 from gibbs_b200.engine.scheduler import FinishReason, Scheduler
 from gibbs_b200.sampling import SamplingParams
 
@@ -184,3 +186,107 @@ def test_seeds_are_per_request_and_reproducible():
     ids2 = [s2.submit([1]), s2.submit([1], SamplingParams(seed=99))]
     assert [s1.sequences[i].seed for i in ids1] == [s2.sequences[i].seed for i in ids2]
     assert s1.sequences[ids1[0]].seed != s1.sequences[ids1[1]].seed == 99
+
+
+# ---------------------------------------------------------------- token feedback (overlap)
+def _lagging(engine, **kw):
+    return Scheduler(engine, LaggingSampler(engine), overlap=True, **kw)
+
+
+def test_overlap_launches_the_next_decode_step_before_it_reads_the_last():
+    eng = FakeEngine()
+    s = _lagging(eng, max_batch_tokens=16)
+    prompts = [[3, 4, 5], list(range(1, 31)), [7]]
+    outs = s.generate(prompts, GREEDY)
+    assert outs == [expected_greedy(p, 8, eng.vocab) for p in prompts]
+    ev = eng.events
+    fed = [i for i, e in enumerate(ev) if e == "launch fed"]
+    assert len(fed) >= 6
+    # every fed launch went out while the ids of the step before were still unread
+    for i in fed:
+        assert ev[:i].count("read") == sum(1 for e in ev[:i] if e.startswith("launch")) - 1
+    assert not eng.cache.live and eng.cache.free_pages() == [64] and eng.cache.slots.n_free == 4
+
+
+def test_overlap_drops_the_token_after_an_unforeseen_end_and_foresees_ends_by_length():
+    eng = FakeEngine()
+    want = expected_greedy([4, 4], 12, eng.vocab)
+    eos = want[5]
+    cut = want.index(eos)
+    s = _lagging(eng, eos_ids=[eos])
+    i = s.submit([4, 4], SamplingParams(temperature=0.0, max_new_tokens=12))
+    j = s.submit([9, 1, 1], SamplingParams(temperature=0.0, max_new_tokens=3))
+    emitted = {i: [], j: []}
+    while s.has_work():
+        for k, t in s.step().emitted:
+            emitted[k].append(t)
+    assert emitted[i] == s.sequences[i].output == want[:cut] and s.sequences[i].finish == FinishReason.STOP
+    want_j = expected_greedy([9, 1, 1], 3, eng.vocab, eos=[eos])
+    assert emitted[j] == s.sequences[j].output == want_j
+    # the request that ends by length was fed exactly its prompt and its tokens but the last
+    assert eng.events.count("launch fed") >= 2
+    assert not eng.cache.live and eng.cache.free_pages() == [64] and eng.cache.slots.n_free == 4
+
+
+def test_overlap_gives_way_to_admission_cancellation_and_preemption():
+    # the preemption scenario of the test above, with ids that lag
+    eng = FakeEngine(n_pages=10, page_size=4, max_requests=4, max_context=64)
+    s = _lagging(eng, max_batch_tokens=64)
+    p0, p1 = list(range(1, 13)), list(range(20, 32))
+    a = s.submit(p0, SamplingParams(temperature=0.0, max_new_tokens=16))
+    b = s.submit(p1, SamplingParams(temperature=0.0, max_new_tokens=16))
+    emitted, preempted = {a: [], b: []}, []
+    while s.has_work():
+        out = s.step()
+        for i, t in out.emitted:
+            emitted[i].append(t)
+        preempted += out.preempted
+        eng.cache.check()
+    assert set(preempted) == {b}
+    assert emitted[a] == expected_greedy(p0, 16, eng.vocab) and emitted[b] == expected_greedy(p1, 16, eng.vocab)
+    assert eng.cache.free_pages() == [10] and not eng.cache.live
+    # a request that arrives while a step is in flight is admitted at the next step
+    eng = FakeEngine()
+    s = _lagging(eng)
+    a = s.submit([1, 2, 3], SamplingParams(temperature=0.0, max_new_tokens=20))
+    for _ in range(4):
+        s.step()
+    b = s.submit([5, 6], GREEDY)
+    s.step()
+    s.step()
+    assert eng.is_open(b) if hasattr(eng, "is_open") else b in eng.cache.live
+    s.cancel(a)
+    s.run()
+    assert s.sequences[a].finish == FinishReason.CANCELLED
+    assert s.sequences[a].output == expected_greedy([1, 2, 3], 20, eng.vocab)[:len(s.sequences[a].output)]
+    assert s.sequences[b].output == expected_greedy([5, 6], 8, eng.vocab)
+    assert not eng.cache.live and eng.cache.free_pages() == [64]
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_overlap_emits_what_the_plain_loop_emits_under_random_traffic(seed):
+    def run(overlap):
+        rng = random.Random(seed)
+        eng = FakeEngine(n_pages=rng.choice([14, 24, 64]), page_size=4, max_requests=3, max_context=48, vocab=11)
+        sampler = LaggingSampler(eng)
+        s = Scheduler(eng, sampler, max_batch_tokens=rng.choice([6, 16]), eos_ids=[3], overlap=overlap)
+        ids, emitted = [], {}
+        for step in range(400):
+            if step < 60 and rng.random() < 0.3:
+                prompt = [rng.randrange(11) for _ in range(rng.randint(1, 14))]
+                ids.append(s.submit(prompt, SamplingParams(temperature=0.0, max_new_tokens=rng.randint(0, 12))))
+            if not s.has_work():
+                if step >= 60:
+                    break
+                continue
+            for i, t in s.step().emitted:
+                emitted.setdefault(i, []).append(t)
+            eng.cache.check()
+        assert not s.has_work() and not eng.cache.live
+        assert all(emitted.get(i, []) == s.sequences[i].output for i in ids)
+        return [(s.sequences[i].output, s.sequences[i].finish) for i in ids], eng.events.count("launch fed")
+
+    plain, none_fed = run(False)
+    lagging, fed = run(True)
+    assert none_fed == 0 and fed > 0
+    assert plain == lagging
