@@ -766,6 +766,24 @@ int pick_bn(int M) {
   return 128;
 }
 
+// Below this many 256 x 256 tiles the one-tile CTAs take the product (two per SM; they ask L2 for
+// twice the bytes per flop, so they lose as soon as the pairs have enough tiles).
+// GIBBS_B200_PAIR_MIN_TILES moves the threshold (for comparison runs).
+int gb_pair_min() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("GIBBS_B200_PAIR_MIN_TILES"); v = e ? atoi(e) : 32; }
+  return v;
+}
+
+int gb_pair();
+
+// Whether the product runs on CTA pairs (256 x 256 tiles; they never split K: with K split four
+// ways a pair per tile and split was measured slower than the one-tile CTAs below, at every size).
+bool runs_on_pairs(int M, int N) {
+  const long long pair_tiles = (long long)gb_div_up(N, 2 * BM) * gb_div_up(M, 256);
+  return M >= 192 && pair_tiles >= gb_pair_min() && gb_pair();
+}
+
 void plan(int M, int N, int K, int* bn, int* splits, int* kb_per_split) {
   *bn = pick_bn(M);
   const int total_kb = gb_div_up(K, BK);
@@ -776,6 +794,15 @@ void plan(int M, int N, int K, int* bn, int* splits, int* kb_per_split) {
     const int max_by_k = total_kb / 4;           // at least 4 k-blocks (256 columns of K) per split
     if (s > max_by_k) s = max_by_k;
     if (s > 16) s = 16;
+    if (s < 1) s = 1;
+  } else if (M > 128 && tiles < 148 && (tiles <= 74 || total_kb >= 64) && !runs_on_pairs(M, N)) {
+    // Prompt portions of a few hundred tokens against a narrow weight: a CTA alone walks K at the
+    // pace of its own loads (about 75 GB/s), so an under-filled launch takes as long as K is deep,
+    // whatever the number of tokens.  Split K until two CTAs per SM are busy.
+    s = (int)(296 / tiles);
+    const int max_by_k = total_kb / 8;           // at least 8 k-blocks (512 columns of K) per split
+    if (s > max_by_k) s = max_by_k;
+    if (s > 8) s = 8;
     if (s < 1) s = 1;
   }
   *kb_per_split = gb_div_up(total_kb, s);
@@ -947,13 +974,7 @@ GB_API int gb_linear_tc(const void* X, long long ldx, const void* W, long long l
   p.status = status;
   int rc;
   const long long n_tiles = (long long)gb_div_up(N, BM) * gb_div_up(M, bn);
-  const long long pair_tiles = (long long)gb_div_up(N, 2 * BM) * gb_div_up(M, PairCfg::BNP);
-  // Below this many 256 x 256 tiles the one-tile CTAs take the product (two per SM; they ask L2 for
-  // twice the bytes per flop, so they lose as soon as the pairs have enough tiles).
-  // GIBBS_B200_PAIR_MIN_TILES moves the threshold (for comparison runs).
-  static int pair_min = -1;
-  if (pair_min < 0) { const char* e = getenv("GIBBS_B200_PAIR_MIN_TILES"); pair_min = e ? atoi(e) : 32; }
-  if (bn == 128 && splits == 1 && M >= 192 && pair_tiles >= pair_min && gb_pair()) {
+  if (bn == 128 && splits == 1 && runs_on_pairs(M, N)) {
     rc = launch_pair(tw, tx, p, stream);
   } else {
     switch (bn) {
@@ -1030,7 +1051,13 @@ GB_API int gb_linear_tc_no_alloc(const void* X, long long ldx, const void* W, lo
   if (gb_div_up(M, 16) > 65535) GB_FAIL(GB_ERR_ARG, "gb_linear_tc_no_alloc: M = %d is too large", M);
   int bn, splits, kb_per_split;
   plan(M, N, K, &bn, &splits, &kb_per_split);
-  const long long need = splits > 1 ? (long long)splits * M * N : 0;
+  long long need = splits > 1 ? (long long)splits * M * N : 0;
+  if (M > 128 && need > GB_NO_ALLOC_MAX_WORKSPACE_FLOATS) {
+    // above 128 rows the split is for speed only: without the scratch for it, K stays whole
+    splits = 1;
+    kb_per_split = gb_div_up(K, BK);
+    need = 0;
+  }
   if (need > GB_NO_ALLOC_MAX_WORKSPACE_FLOATS)
     GB_FAIL(GB_ERR_ARG, "gb_linear_tc_no_alloc: M = %d, N = %d, K = %d split K %d ways and need %lld floats of "
             "scratch; the built-in scratch holds %d (use gb_linear_tc with your own workspace)",

@@ -158,12 +158,14 @@ class PlanBuilder:
             if partials and use_tc and out.dtype == torch.bfloat16:
                 flags |= LF_PARTIALS if partials == "always" else LF_PARTIALS_IF_ONE_EACH
         if use_tc:
-            # K is split only for 128 rows or fewer; the tile width changes at 16, 32 and 64 rows
+            # how K is split changes with the tile width (at 16, 32 and 64 rows) and then with
+            # the number of 128-row tiles
             lib = library("tensorcore")
-            for m in (1, 17, 33, 65, 128):
+            for m in sorted({1, 17, 33, 65, 128, *range(256, self.cap + 128, 128)}):
+                m = min(m, self.cap)
                 s = lib.gb_linear_tc_splits(ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(k))
                 if s > 1:
-                    self.ws_floats = max(self.ws_floats, s * 128 * n)
+                    self.ws_floats = max(self.ws_floats, s * m * n)
             if mode == "residual":
                 self.ws_floats = max(self.ws_floats, self.cap * n)     # large products are deferred whole
         self.emit(P_LINEAR, [x.data_ptr(), x.stride(0), self.keep(weight), weight.stride(0), self.keep(bias),

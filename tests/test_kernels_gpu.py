@@ -96,9 +96,11 @@ def test_linear_simt(m, n, k, pair):
     _close(acc, res.double() + ar @ wr.T, "float32" if ad == "float32" else "float32", scale=want.abs().max().item())
 
 
-# the last three have more than 148 tiles: the persistent kernel, with ragged edges in both directions
+# the last two split K above 128 rows (few tiles, deep K); the three before them are walked by CTA pairs,
+# with ragged edges in both directions
 @pytest.mark.parametrize("m,n,k", SHAPES + [(2048, 512, 2048), (1, 65536 // 8, 2048), (257, 130, 8),
-                                            (2048, 2048, 256), (1500, 1664, 200), (1281, 2050, 72)])
+                                            (2048, 2048, 256), (1500, 1664, 200), (1281, 2050, 72),
+                                            (300, 256, 1024), (520, 392, 4104)])
 def test_linear_tensor_cores(m, n, k):
     """bf16 x bf16 on tcgen05: bf16 store, f32 store, f32 accumulate, with and
     without bias, including the split-K sizes."""
@@ -625,6 +627,27 @@ def test_deferred_split_k_and_norm_that_adds_the_partial_sums():
     x2 = x0.clone().to(DEV)
     ops.add_pending(x2, ws, bias.to(DEV))
     assert torch.equal(x2, x)
+
+
+def test_split_k_above_128_rows_is_left_to_the_norm_too():
+    """A prompt portion against a narrow, deep weight splits K as well (few tiles would leave most
+    SMs idle); its partial tiles reach the norm like the decode sizes' do."""
+    from gibbs_b200 import ops
+    torch.manual_seed(12)
+    m, n, k, eps = 300, 256, 4096, 1e-5
+    a, ar = _quant(torch.randn(m, k), "bfloat16")
+    w, wr = _quant(torch.randn(n, k) / math.sqrt(k), "bfloat16")
+    gain = 1 + 0.1 * torch.randn(n)
+    x0 = torch.randn(m, n)
+    x = x0.clone().to(DEV)
+    ws = ops.linear_tc(a, w, None, x, accumulate=True, defer=True)
+    assert ws is not x and ws.shape == (8, m, n)
+    want_x = x0.double() + ar @ wr.T
+    want_h = want_x / torch.sqrt((want_x ** 2).mean(-1, keepdim=True) + eps) * gain.double()
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops.rmsnorm(x, gain.to(DEV), eps, out, None, pending=(ws, None))
+    _close(out, want_h, "bfloat16")
+    _close(x, want_x, "float32", scale=want_x.abs().max().item())
 
 
 # --------------------------------------------------------------------------- consumers of split-K partial tiles
