@@ -24,7 +24,7 @@
 // Formula: MisterTK/gibbs src/graph/cpu.rs:826-951 (keys j <= pos, optional window j + w > pos,
 // scale on the dot product, max-subtracted softmax, query head h reads kv head h / group).
 //
-// Taken: bfloat16, head_dim 64 or 128, group 1, 2, 4, 8 or 16, page sizes 8..128 that divide 128.
+// Taken: bfloat16, head_dim 64 or 128, groups of 1 to 16 query heads, page sizes 8..128 that divide 128.
 // Every wait is bounded; a wait that runs out sets *status and the CTA drains and returns.
 #include <mutex>
 #include <unordered_map>
@@ -122,6 +122,18 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     tmem_alloc(&tmem_slot, C::TMEM_COLS);
     tmem_relinquish();
   }
+  if (group * tpt < ROWS) {
+    // A group that does not divide 128 (3, 5, 6, 7, ...) leaves the tile's last rows without a
+    // (token, head): the q box does not reach them.  They are zeroed so that the tensor core reads
+    // numbers there; nothing of these rows is stored.
+    const int spare = ROWS - group * tpt;                      // < group <= 16 rows of 128 bytes per sub-tile
+    for (int i = threadIdx.x; i < C::SUB * spare * 8; i += blockDim.x) {
+      const int sub = i / (spare * 8), rest = i - sub * spare * 8;
+      *reinterpret_cast<uint4*>(sq + (size_t)sub * ROWS * 128 + (size_t)(group * tpt + rest / 8) * 128 + (rest & 7) * 16) =
+          make_uint4(0u, 0u, 0u, 0u);
+    }
+    fence_proxy_async();
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -131,7 +143,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // ---- producer ----
     pdl_wait();                                                // q and the pages are written by the kernels before
     if (lane == 0) {
-      mbar_arrive_expect_tx(&q_full, C::Q_BYTES);
+      mbar_arrive_expect_tx(&q_full, (uint32_t)(C::SUB * group * tpt * 128));   // the box: tpt tokens x group heads
       for (int sub = 0; sub < C::SUB; ++sub)
         tma_load_3d(sq + (size_t)sub * ROWS * 128, &map_q, sub * 64, kvh * group, row0, &q_full);
     }
@@ -453,7 +465,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
 GB_API int gb_attention_tcgen05_supported(int heads, int kv_heads, int hd, int page_size, long long ldq, long long ldo) {
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0) return 0;
   const int group = heads / kv_heads;
-  if (group > 16 || (group & (group - 1)) != 0) return 0;
+  if (group > 16) return 0;
   if (hd != 64 && hd != 128) return 0;
   if (page_size < 8 || page_size > 128 || 128 % page_size != 0) return 0;
   if (ldq % 8 != 0 || ldo % 8 != 0) return 0;

@@ -517,6 +517,12 @@ TC_CASES = [
     (32, 8, 64, 16, 0, [2047, 5, 300], [1, 1, 500]),
     (8, 2, 64, 64, 257, [600], [700]),
     (2, 1, 64, 16, 0, [0], [1000]),
+    # groups that do not divide the 128 rows of a tile (its last rows stay without a token)
+    (24, 8, 64, 16, 0, [0, 1000, 37], [480, 1, 90]),
+    (5, 1, 64, 16, 0, [10], [300]),
+    (12, 2, 128, 32, 100, [200, 0], [150, 43]),
+    (7, 1, 64, 8, 0, [0, 129], [130, 19]),
+    (12, 1, 64, 64, 0, [5], [77]),
 ]
 
 
