@@ -54,6 +54,12 @@ __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x by the special-function unit (relative error 2^-22; -inf gives 0)
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -216,7 +222,10 @@ attention_tc_kernel(const AttnParams p) {
     rvalid[i] = tl < n_tok;
     rpos[i] = pos0 + tl;
   }
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  // rows 8..15 of the warp's 16 hold no token when the tile is a decoded token of a group of 8 or fewer
+  // heads (then all warps share the rows): their half of the softmax is skipped
+  const bool upper = n_tok * group > wrow + 8;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // the maximum in use and the sum under it
   float o[HD / 8][4];
 #pragma unroll
   for (int n = 0; n < HD / 8; ++n)
@@ -253,33 +262,56 @@ attention_tc_kernel(const AttnParams p) {
         mma_bf16(s[2 * n2 + 1], qf[kk], b[2], b[3]);
       }
     }
-    // scale, mask, running maximum
-    float m_new[2] = {m_run[0], m_run[1]};
+    // scale, mask, the tile's maximum.  A tile that lies below the diagonal (and inside the window) for
+    // every row of the CTA needs no mask: rows without a token have q = 0 there, finite and never stored.
+    const bool full = t * KT + KT - 1 <= pos0 && (p.window <= 0 || t * KT + p.window > pos0 + n_tok - 1);
+    float m_tile[2] = {-INFINITY, -INFINITY};
+    if (full) {
 #pragma unroll
-    for (int n = 0; n < NN; ++n) {
+      for (int n = 0; n < NN; ++n) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int ri = i >> 1;
-        const int j = t * KT + kbase + n * 8 + (lane & 3) * 2 + (i & 1);
-        const bool vis = rvalid[ri] && j <= rpos[ri] && (p.window <= 0 || j + p.window > rpos[ri]);
-        const float v = vis ? s[n][i] * p.scale_log2 : -INFINITY;
-        s[n][i] = v;
-        m_new[ri] = fmaxf(m_new[ri], v);
+        for (int i = 0; i < 4; ++i) {
+          if ((i >> 1) == 1 && !upper) continue;
+          const float v = s[n][i] * p.scale_log2;
+          s[n][i] = v;
+          m_tile[i >> 1] = fmaxf(m_tile[i >> 1], v);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int n = 0; n < NN; ++n) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int ri = i >> 1;
+          if (ri == 1 && !upper) continue;
+          const int j = t * KT + kbase + n * 8 + (lane & 3) * 2 + (i & 1);
+          const bool vis = rvalid[ri] && j <= rpos[ri] && (p.window <= 0 || j + p.window > rpos[ri]);
+          const float v = vis ? s[n][i] * p.scale_log2 : -INFINITY;
+          s[n][i] = v;
+          m_tile[ri] = fmaxf(m_tile[ri], v);
+        }
       }
     }
-    float corr[2];
+    // The maximum in use follows the tile's only when it would fall behind by more than 2^8 (P then
+    // stays below 256, far inside bfloat16's range); most tiles leave O and the sum as they are.
+    float corr[2] = {1.f, 1.f};
 #pragma unroll
     for (int ri = 0; ri < 2; ++ri) {
-      m_new[ri] = fmaxf(m_new[ri], __shfl_xor_sync(0xffffffffu, m_new[ri], 1));
-      m_new[ri] = fmaxf(m_new[ri], __shfl_xor_sync(0xffffffffu, m_new[ri], 2));
-      corr[ri] = (m_new[ri] == -INFINITY) ? 1.f : exp2f(m_run[ri] - m_new[ri]);
-      m_run[ri] = m_new[ri];
-      l_run[ri] *= corr[ri];
+      if (ri == 1 && !upper) continue;
+      m_tile[ri] = fmaxf(m_tile[ri], __shfl_xor_sync(0xffffffffu, m_tile[ri], 1));
+      m_tile[ri] = fmaxf(m_tile[ri], __shfl_xor_sync(0xffffffffu, m_tile[ri], 2));
+      if (m_tile[ri] > m_run[ri] + 8.f || (m_run[ri] == -INFINITY && m_tile[ri] > -INFINITY)) {
+        corr[ri] = ex2_approx(m_run[ri] - m_tile[ri]);         // 0 when nothing was seen before
+        m_run[ri] = m_tile[ri];
+        l_run[ri] *= corr[ri];
+      }
     }
+    if (corr[0] != 1.f || corr[1] != 1.f) {
 #pragma unroll
-    for (int n = 0; n < HD / 8; ++n) {
-      o[n][0] *= corr[0]; o[n][1] *= corr[0];
-      o[n][2] *= corr[1]; o[n][3] *= corr[1];
+      for (int n = 0; n < HD / 8; ++n) {
+        o[n][0] *= corr[0]; o[n][1] *= corr[0];
+        o[n][2] *= corr[1]; o[n][3] *= corr[1];
+      }
     }
     // P = exp2(S - m), O += P V
     const bf16* vb = sv + buf * KT * STRIDE;
@@ -292,9 +324,12 @@ attention_tc_kernel(const AttnParams p) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int ri = i >> 1;
-          const float e = (m_run[ri] == -INFINITY) ? 0.f : exp2f(s[2 * kk + h2][i] - m_run[ri]);
+          float e = 0.f;
+          if (ri == 0 || upper) {
+            e = (m_run[ri] == -INFINITY) ? 0.f : ex2_approx(s[2 * kk + h2][i] - m_run[ri]);
+            l_run[ri] += e;
+          }
           pv[h2][i] = e;
-          l_run[ri] += e;
         }
       a[0] = pack_bf16(pv[0][0], pv[0][1]);
       a[1] = pack_bf16(pv[0][2], pv[0][3]);
