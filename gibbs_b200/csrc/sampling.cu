@@ -39,12 +39,63 @@ __device__ __forceinline__ Cand warp_best(Cand c) {
   return c;
 }
 
+// f(value, id) for every element of a row, each thread taking every blockDim-th group of four
+// (or single element when the row cannot be read in 16-byte pieces).  Eight loads are requested
+// before the first is used: a thread that waits for each load in turn spends the row's sixteen
+// memory latencies one after the other.
+template <typename F>
+__device__ __forceinline__ void for_each_logit(const float* __restrict__ x, int vocab, bool vec, F f) {
+  const int T = blockDim.x;
+  const int n4 = vec ? vocab >> 2 : 0;
+  for (int i0 = threadIdx.x; i0 < n4; i0 += 8 * T) {
+    float4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      if (i0 + u * T < n4) v[u] = reinterpret_cast<const float4*>(x)[i0 + u * T];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * T;
+      if (i < n4) {
+        f(v[u].x, 4 * i);
+        f(v[u].y, 4 * i + 1);
+        f(v[u].z, 4 * i + 2);
+        f(v[u].w, 4 * i + 3);
+      }
+    }
+  }
+  for (int i0 = 4 * n4 + threadIdx.x; i0 < vocab; i0 += 8 * T) {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      if (i0 + u * T < vocab) v[u] = x[i0 + u * T];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      if (i0 + u * T < vocab) f(v[u], i0 + u * T);
+  }
+}
+
 __device__ __forceinline__ float uniform24(unsigned long long seed, unsigned long long counter) {
   unsigned long long z = seed + (counter + 1ull) * 0x9E3779B97F4A7C15ull;
   z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
   z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
   z ^= z >> 31;
   return (float)(z >> 40) * (1.0f / 16777216.0f);
+}
+
+// ---- the top k of a row without k passes over it ----------------------------------------
+// 1. every thread keeps the best of its own elements (one pass);
+// 2. L = the k-th largest of these per-thread maxima (radix select in shared memory): k threads hold an
+//    element >= L, so the k-th largest element of the row is >= L and all of the top k are >= L;
+// 3. the elements >= L are collected (second pass; at most k - 1 threads hold elements above L, so they are
+//    few unless values tie) and sorted by (logit descending, id ascending);
+// 4. the first k are the candidates.  If more than SEL_CAP elements pass (thousands of equal values at the
+//    threshold), the row falls back to k passes: never a wrong result.
+constexpr int SEL_CAP = 4096;
+
+// larger float <-> larger unsigned; 0 stands for "no element" (below -inf's key)
+__device__ __forceinline__ unsigned ordered_key(float v) {
+  const unsigned b = __float_as_uint(v);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
 __global__ void sample_kernel(const float* __restrict__ logits, long long ldv, int vocab,
@@ -56,6 +107,11 @@ __global__ void sample_kernel(const float* __restrict__ logits, long long ldv, i
   __shared__ Cand warp_c[32];
   __shared__ Cand picked[MAX_K];
   __shared__ Cand prev;
+  __shared__ Cand cand[SEL_CAP];
+  __shared__ unsigned local_key[1024];
+  __shared__ int hist[256];
+  __shared__ unsigned sel_prefix;
+  __shared__ int sel_need, n_cand;
   const int row = blockIdx.x;
   const float* x = logits + (size_t)row * ldv;
   const float temp = temperature ? temperature[row] : 0.f;
@@ -64,32 +120,117 @@ __global__ void sample_kernel(const float* __restrict__ logits, long long ldv, i
   k = k < 1 ? 1 : (k > MAX_K ? MAX_K : k);
   if (k > vocab) k = vocab;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int T = blockDim.x;
+  const bool vec = (ldv % 4 == 0) && (((uintptr_t)logits & 15) == 0);
 
-  int len = 0;
-  for (int round = 0; round < k; ++round) {
-    Cand best = {0.f, -1};
-    const Cand p = prev;  // meaningful from round 1 on
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-      const float v = x[i];
-      if (v != v) continue;  // NaN never wins
-      if (round > 0 && !(v < p.v || (v == p.v && i > p.id))) continue;
-      const Cand c = {v, i};
-      if (better(c, best)) best = c;
-    }
-    best = warp_best(best);
-    if (lane == 0) warp_c[warp] = best;
+  // 1. this thread's best element
+  Cand mine = {0.f, -1};
+  for_each_logit(x, vocab, vec, [&](float v, int id) {
+    const Cand c = {v, id};
+    if (v == v && better(c, mine)) mine = c;                 // NaN never wins
+  });
+  local_key[threadIdx.x] = mine.id >= 0 ? ordered_key(mine.v) : 0u;
+  if (threadIdx.x == 0) {
+    sel_prefix = 0u;
+    sel_need = k;
+    n_cand = 0;
+  }
+  // 2. the k-th largest of the T keys, eight bits at a time from the top
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int i = threadIdx.x; i < 256; i += T) hist[i] = 0;
+    __syncthreads();
+    const unsigned key = local_key[threadIdx.x], pre = sel_prefix;
+    const unsigned above = shift == 24 ? 0u : (0xFFFFFFFFu << (shift + 8));
+    if ((key & above) == (pre & above)) atomicAdd(&hist[(key >> shift) & 255u], 1);
     __syncthreads();
     if (warp == 0) {
-      Cand c = lane < nwarps ? warp_c[lane] : Cand{0.f, -1};
-      c = warp_best(c);
-      if (lane == 0) {
-        prev = c;
-        if (c.id >= 0) picked[round] = c;
+      // lane l owns bins 255 - 8l down to 248 - 8l; find the bin in which the count from the top reaches `need`
+      int mine8 = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mine8 += hist[255 - 8 * lane - j];
+      int incl = mine8;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+      }
+      const int need = sel_need, before = incl - mine8;
+      if (before < need && need <= incl) {                 // exactly one lane
+        int cum = before;
+        for (int j = 0; j < 8; ++j) {
+          const int bin = 255 - 8 * lane - j;
+          if (cum + hist[bin] >= need) {
+            sel_prefix = pre | ((unsigned)bin << shift);
+            sel_need = need - cum;
+            break;
+          }
+          cum += hist[bin];
+        }
       }
     }
     __syncthreads();
-    if (prev.id < 0) break;
-    len = round + 1;
+  }
+  const unsigned l_key = sel_prefix;                         // 0 when fewer than k threads hold an element
+  // 3. everything >= L
+  for_each_logit(x, vocab, vec, [&](float v, int id) {
+    if (v == v && ordered_key(v) >= l_key) {
+      const int at = atomicAdd(&n_cand, 1);
+      if (at < SEL_CAP) cand[at] = Cand{v, id};
+    }
+  });
+  __syncthreads();
+  const int n = n_cand;
+  int len = 0;
+  if (n <= SEL_CAP) {
+    // sort the candidates, best first (bitonic over the next power of two, padded with "none")
+    int n2 = 1;
+    while (n2 < n) n2 <<= 1;
+    for (int i = n + threadIdx.x; i < n2; i += T) cand[i] = Cand{0.f, -1};
+    __syncthreads();
+    for (int size = 2; size <= n2; size <<= 1) {
+      for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        for (int idx = threadIdx.x; idx < (n2 >> 1); idx += T) {
+          const int i = 2 * idx - (idx & (stride - 1)), j = i + stride;
+          const bool first_best = (i & size) == 0;
+          const Cand a = cand[i], b2 = cand[j];
+          if (better(b2, a) == first_best) {
+            cand[i] = b2;
+            cand[j] = a;
+          }
+        }
+        __syncthreads();
+      }
+    }
+    len = n < k ? n : k;
+    if (threadIdx.x < len) picked[threadIdx.x] = cand[threadIdx.x];
+    __syncthreads();
+  } else {
+    // k passes: each takes the best element that is worse than the one before
+    for (int round = 0; round < k; ++round) {
+      Cand best = {0.f, -1};
+      const Cand p = prev;  // meaningful from round 1 on
+      for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = x[i];
+        if (v != v) continue;  // NaN never wins
+        if (round > 0 && !(v < p.v || (v == p.v && i > p.id))) continue;
+        const Cand c = {v, i};
+        if (better(c, best)) best = c;
+      }
+      best = warp_best(best);
+      if (lane == 0) warp_c[warp] = best;
+      __syncthreads();
+      if (warp == 0) {
+        Cand c = lane < nwarps ? warp_c[lane] : Cand{0.f, -1};
+        c = warp_best(c);
+        if (lane == 0) {
+          prev = c;
+          if (c.id >= 0) picked[round] = c;
+        }
+      }
+      __syncthreads();
+      if (prev.id < 0) break;
+      len = round + 1;
+    }
   }
 
   if (threadIdx.x != 0) return;
@@ -145,20 +286,10 @@ __global__ void argmax_kernel(const float* __restrict__ logits, long long ldv, i
   const float* x = logits + (size_t)blockIdx.x * ldv;
   Cand best = {0.f, -1};
   const bool vec = (ldv % 4 == 0) && (((uintptr_t)logits & 15) == 0);
-  const int n4 = vec ? vocab >> 2 : 0;
-  for (int i = threadIdx.x; i < n4; i += blockDim.x) {
-    const float4 v = reinterpret_cast<const float4*>(x)[i];
-    const float e[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const Cand c = {e[k], 4 * i + k};
-      if (e[k] == e[k] && better(c, best)) best = c;
-    }
-  }
-  for (int i = 4 * n4 + threadIdx.x; i < vocab; i += blockDim.x) {
-    const Cand c = {x[i], i};
-    if (c.v == c.v && better(c, best)) best = c;
-  }
+  for_each_logit(x, vocab, vec, [&](float v, int id) {
+    const Cand c = {v, id};
+    if (v == v && better(c, best)) best = c;
+  });
   best = warp_best(best);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   if (lane == 0) warp_c[warp] = best;

@@ -452,6 +452,46 @@ def test_temperature_sampling_matches_the_plain_rule(vocab):
             assert j is not None and abs(cum[j - 1 if got[r] != ids[0] and cum[j] > target else j] - target) < 1e-5, r
 
 
+def test_top_k_selection_with_ties_and_few_finite_values():
+    """The candidates are the first k in (logit descending, id ascending) order whatever the row holds:
+    thousands of equal values at the threshold (the selection gives way to k passes), equal values
+    that still fit, fewer finite values than k, NaNs.  With top_p = 1 and k candidates of equal logit
+    the draw u picks candidate floor(u * k), the floor(u * k)-th smallest id."""
+    from gibbs_b200 import ops
+    from gibbs_b200.sampling import uniform24
+    vocab, k = 65536, 37
+    rows = []
+    a = torch.full((vocab,), -5.0); a[1000:9000] = 2.5                        # 8000 ties above everything else
+    b = torch.randn(vocab); b[[7, 77, 777, 7777, 60000]] = 9.0; b[123] = 8.0  # ties that fit; then one more
+    c = torch.full((vocab,), float("-inf")); c[[5, 50, 500]] = torch.tensor([1.0, 3.0, 2.0])
+    d = torch.randn(vocab); d[::2] = float("nan"); d[40001] = 50.0
+    e = torch.zeros(vocab)                                                   # everything ties
+    logits = torch.stack([a, b, c, d, e]).to(DEV)
+    n = logits.shape[0]
+    for seed in range(12):
+        out = torch.empty(n, dtype=torch.int32, device=DEV)
+        seeds = torch.full((n,), seed, dtype=torch.int64, device=DEV)
+        ctr = torch.arange(n, dtype=torch.int64, device=DEV)
+        ops.sample(logits, out, torch.full((n,), 1.0, device=DEV), torch.full((n,), k, dtype=torch.int32, device=DEV),
+                   torch.full((n,), 1.0, device=DEV), seeds, ctr)
+        got = out.tolist()
+        u = [uniform24(seed, i) for i in range(n)]
+        assert got[0] == 1000 + min(int(u[0] * k), k - 1) or abs(u[0] * k - round(u[0] * k)) < 1e-4
+        assert got[4] == min(int(u[4] * k), k - 1) or abs(u[4] * k - round(u[4] * k)) < 1e-4
+        assert got[2] in (5, 50, 500) and got[3] % 2 == 1
+        # row b: five candidates of logit 9 (weight 1 each), then 8.0 (weight 1/e), then the random rest
+        ids_b = [7, 77, 777, 7777, 60000, 123]
+        if u[1] < 0.5:
+            assert got[1] in ids_b
+    # greedy rows through the same kernel (a sampled row beside them): the smallest id of the maxima
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    temp = torch.zeros(n, device=DEV); temp[2] = 1.0
+    ops.sample(logits, out, temp, torch.full((n,), k, dtype=torch.int32, device=DEV), torch.full((n,), 1.0, device=DEV),
+               torch.zeros(n, dtype=torch.int64, device=DEV), torch.zeros(n, dtype=torch.int64, device=DEV))
+    got = out.tolist()
+    assert got[0] == 1000 and got[1] == 7 and got[3] == 40001 and got[4] == 0
+
+
 def test_sampling_distribution():
     from gibbs_b200 import ops
     logits = torch.tensor([[2.0, 1.0, 0.0, -1.0] + [-20.0] * 60]).repeat(4000, 1)
