@@ -156,7 +156,7 @@ attention_tc_kernel(const AttnParams p) {
   // Where each of a tile's 64 keys lies in the pages (element offset of its row, -1: not
   // visible) is worked out once per tile and row, not once per 16-byte piece: slot t % (NS + 1)
   // of row_off belongs to tile t.  It is written an iteration before the tile's loads are
-  // issued; the barrier that ends every iteration makes it visible.
+  // issued; the barrier at the head of every iteration makes it visible.
   // The page ids are read early (locate_begin) and turned into offsets late (locate_end), so
   // that the block-table reads of a one-warp CTA overlap the work on the current tile.
   constexpr int RPT = (KT + NT - 1) / NT;                    // rows per thread
@@ -235,11 +235,13 @@ attention_tc_kernel(const AttnParams p) {
   uint32_t qf[HD / 16][4];
   for (int t = t_begin; t < t_end; ++t) {
     const int buf = (t - t_begin) % NS;
+    cp_async_wait<NS - 2>();               // all but the NS-2 newest groups: tile t (and Q) have landed
+    // The one barrier of an iteration: tile t is visible to every warp, every warp has left tile t - 1
+    // (whose buffer the next loads overwrite), and the offsets written a tile ago are visible.
+    __syncthreads();
     if (t + NS - 1 < t_end) load_kv(t + NS - 1, (t - t_begin + NS - 1) % NS);
     cp_async_commit();
     if (t + NS < t_end) locate_begin(t + NS);      // page ids of a later tile: needed after this tile's work
-    cp_async_wait<NS - 1>();               // all but the NS-1 newest groups: tile t (and Q) have landed
-    __syncthreads();
     if (t == t_begin) {
 #pragma unroll
       for (int kk = 0; kk < HD / 16; ++kk)
@@ -343,9 +345,9 @@ attention_tc_kernel(const AttnParams p) {
         mma_bf16(o[2 * n2 + 1], a, b[2], b[3]);
       }
     }
-    // slot (t + NS) % (NS + 1) held tile t - 1, whose loads were requested two barriers ago
+    // slot (t + NS) % (NS + 1) held tile t - 1, whose loads were requested an iteration ago; the next
+    // iteration's barrier makes these offsets visible before they are used
     locate_end();
-    __syncthreads();   // everyone is done with this buffer before it is refilled; offsets are visible
   }
   cp_async_wait<0>();
 
