@@ -202,8 +202,13 @@ class PlanBuilder:
     def attention(self, heads: int, kv_heads: int, hd: int, scale: float, window: int, kv_view, bt_stride: int):
         out = self.buffer("mixed", heads * hd)
         kp, vp = kv_view.k_pages, kv_view.v_pages
-        # the decode kernel's key splits: at most 16 splits of at most max_requests * 16 rows
-        self.attn_ws_floats = max(self.attn_ws_floats, 16 * self.max_requests * 16 * heads * (hd + 2))
+        # the decode kernel's key splits: every split leaves (head_dim + 2) floats per (token, head); a
+        # request brings at most 16 // group tokens to that kernel, and the more requests the fewer splits
+        group = max(1, heads // kv_heads)
+        per_request = max(1, 16 // group) * heads * (hd + 2)
+        need = max(ops.attention_splits(n, kv_heads, 1 << 30) * n * per_request
+                   for n in range(1, self.max_requests + 1))
+        self.attn_ws_floats = max(self.attn_ws_floats, need)
         self.emit(P_ATTENTION, [out.data_ptr(), out.stride(0), self.keep(kp), self.keep(vp), kv_view.block_table.group,
                                 kp.shape[2], kp.shape[0], heads, kv_heads, hd, int(window or 0),
                                 ops.dtype_code(out.dtype), bt_stride], [scale])
