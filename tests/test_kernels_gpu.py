@@ -696,6 +696,48 @@ def test_split_k_above_128_rows_is_left_to_the_norm_too():
     _close(x, want_x, "float32", scale=want_x.abs().max().item())
 
 
+@pytest.mark.parametrize("before,q_len,window,far", [
+    (1499, 1, 0, 0), (1499, 1, 0, 15), (1499, 1, 0, 16), (1499, 1, 0, 767), (1499, 1, 0, 1499),   # decode, key splits
+    (1499, 1, 300, 1200), (1499, 1, 300, 1199),                    # the window's first key, and the one before it
+    (1000, 200, 0, 3), (1000, 200, 0, 1127), (1000, 200, 0, 1128),  # a portion: tile and page edges
+    (1000, 200, 150, 1000), (0, 333, 64, 130),                      # a window that some rows of the portion have left
+])
+def test_tensor_core_attention_sees_one_far_key_and_the_windows_edge(before, q_len, window, far):
+    """bfloat16 kernels (key splits when decoding, tcgen05 for the portion): one key is made to
+    dominate head 0 of every query row.  A row sees it exactly when the key is not after the row
+    and inside its window; a key lost at a page's, a tile's or a split's edge, or let in from
+    outside the window, shows as 100 against about 0."""
+    from gibbs_b200 import ops
+    heads, kvh, hd, ps = 8, 2, 64, 16
+    torch.manual_seed(far + window)
+    total = before + q_len
+    n_pages = total // ps + 6
+    bt, tok_req, tok_pos = _layout([before], [q_len], ps, n_pages, seed=far)
+    kp = torch.randn(n_pages, kvh, ps, hd) * 0.05
+    vp = torch.randn(n_pages, kvh, ps, hd) * 0.5
+    kp[bt[0, far // ps], 0, far % ps] = 4.0
+    vp[bt[0, far // ps], 0, far % ps] = 100.0
+    q = torch.randn(q_len, heads * hd) * 0.05
+    q[:, :hd] = 4.0                                            # head 0 (kv head 0) of every row looks for the key
+    t = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((q_len, heads * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.paged_attention(q.to(DEV).to(torch.bfloat16), heads, kvh, hd, kp.to(DEV).to(torch.bfloat16),
+                        vp.to(DEV).to(torch.bfloat16), t(bt), t(tok_req), t(tok_pos), 1.0 / 8, window, out, status,
+                        hints=_Hints([before], [q_len]))
+    assert int(status.item()) == 0
+    got = out.float().cpu()
+    for i in range(q_len):
+        pos = before + i
+        visible = far <= pos and (window == 0 or far + window > pos)
+        head0 = got[i, :hd]
+        if visible:
+            assert head0.min().item() > 99.0, (i, pos)
+        else:
+            assert head0.abs().max().item() < 3.0, (i, pos)
+        assert got[i, hd:].abs().max().item() < 3.0              # no other head holds such a key
+
+
 # --------------------------------------------------------------------------- consumers of split-K partial tiles
 def _split_partials(full: torch.Tensor, splits: int, seed: int):
     """Random 32-bit partial tiles [splits, m, n] whose sum in split order is what a reduction
