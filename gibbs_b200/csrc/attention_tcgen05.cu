@@ -68,7 +68,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   pdl_trigger();
   using C = Cfg<HD>;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t q_full, kv_full[RING], kv_empty[RING], s_full, p_full, o_full;
+  __shared__ uint64_t q_full, kv_full[RING], kv_empty[RING], s_full, s_free, p_full, o_full;
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int abort_flag;
   __shared__ volatile int alive_vote;
@@ -108,6 +108,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       mbar_init(&kv_empty[s], 1);
     }
     mbar_init(&s_full, 1);
+    mbar_init(&s_free, 4);                                     // one arrival per softmax warp
     mbar_init(&p_full, 4);                                     // one arrival per softmax warp
     mbar_init(&o_full, 1);
     abort_flag = 0;
@@ -191,30 +192,39 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       constexpr uint32_t idesc_s = idesc_bf16_f32(ROWS, KEYS);
       constexpr uint32_t idesc_o = idesc_bf16_f32_b_mn(ROWS, HD);
       bool ok = mbar_wait(&q_full, 0);
-      int it = 0;
+      // Order in the tensor pipe: S_0, then for every tile S_{j+1} before O += P_j V_j.  The softmax
+      // warps keep the row of S_j in registers, so S_{j+1} may overwrite it as soon as they have read
+      // it (s_free) and is ready when they come back from writing P_j: the products stay out of the
+      // softmax warps' way, which set the pace.  Ring items are K_j = 2j and V_j = 2j + 1.
+      auto issue_s = [&](int j) {
+        const int item = 2 * j, s = item % RING;
+        if (!mbar_wait(&kv_full[s], (item / RING) & 1)) return false;
+        tc_fence_after();
+        const uint8_t* kt = skv + (size_t)s * C::KV_BYTES;
+#pragma unroll
+        for (int sub = 0; sub < C::SUB; ++sub) {
+          const uint64_t da = smem_desc_sw128(sq + (size_t)sub * ROWS * 128);
+          const uint64_t db = smem_desc_sw128(kt + (size_t)sub * KEYS * 128);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma_bf16(tmem_s, da + 2 * k, db + 2 * k, idesc_s, (uint32_t)((sub | k) != 0));
+        }
+        umma_commit(&kv_empty[s]);
+        umma_commit(&s_full);
+        return true;
+      };
+      if (ok && n_tiles > 0) ok = issue_s(0);
       for (int j = 0; j < n_tiles && ok && !abort_flag; ++j) {
-        // S = Q K^T
-        {
-          const int s = it % RING;
-          ok = mbar_wait(&kv_full[s], (it / RING) & 1);
+        if (j + 1 < n_tiles) {
+          ok = mbar_wait(&s_free, j & 1);
           if (!ok) break;
           tc_fence_after();
-          const uint8_t* kt = skv + (size_t)s * C::KV_BYTES;
-#pragma unroll
-          for (int sub = 0; sub < C::SUB; ++sub) {
-            const uint64_t da = smem_desc_sw128(sq + (size_t)sub * ROWS * 128);
-            const uint64_t db = smem_desc_sw128(kt + (size_t)sub * KEYS * 128);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) umma_bf16(tmem_s, da + 2 * k, db + 2 * k, idesc_s, (uint32_t)((sub | k) != 0));
-          }
-          umma_commit(&kv_empty[s]);
-          umma_commit(&s_full);
-          ++it;
+          ok = issue_s(j + 1);
+          if (!ok) break;
         }
         // O += P V
         {
-          const int s = it % RING;
-          ok = mbar_wait(&p_full, j & 1) && mbar_wait(&kv_full[s], (it / RING) & 1);
+          const int item = 2 * j + 1, s = item % RING;
+          ok = mbar_wait(&p_full, j & 1) && mbar_wait(&kv_full[s], (item / RING) & 1);
           if (!ok) break;
           tc_fence_after();
           const uint8_t* vt = skv + (size_t)s * C::KV_BYTES;
@@ -233,7 +243,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           }
           umma_commit(&kv_empty[s]);
           umma_commit(&o_full);
-          ++it;
         }
       }
       if (!ok) {
@@ -274,6 +283,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       const unsigned span = hi_c >= lo_c ? (unsigned)(hi_c - lo_c) : 0u;
       const bool none = hi_c < lo_c;                           // (then `span` is not used)
       tmem_ld_wait_128(v);
+      // the row is in registers: the next tile's first product may overwrite S
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free);
       if (!full) {
 #pragma unroll
         for (int i = 0; i < KEYS; ++i) v[i] = (!none && (unsigned)(i - lo_c) <= span) ? v[i] : -INFINITY;
