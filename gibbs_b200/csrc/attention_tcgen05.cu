@@ -152,8 +152,27 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int pages_per_tile = KEYS / p.page_size;
     const int page_bytes = p.page_size * 128;                  // of one 64-column sub-tile
     const int first_page = bt[lo_all / p.page_size];
+    // Lane i brings page slot i of every tile (at most 16 slots).  Its page id for the next tile is
+    // read from the block table while this tile's copies are requested, and serves K and V alike: the
+    // table is not read between a buffer falling free and its copy going out.
+    constexpr int OUTSIDE = -0x7fffffff;
+    auto lookup = [&](int t) {
+      if (lane >= pages_per_tile) return OUTSIDE;
+      const int j0 = t * KEYS + lane * p.page_size;            // first key of this page slot
+      return (j0 < hi_all && j0 + p.page_size > lo_all) ? bt[j0 / p.page_size] : OUTSIDE;
+    };
+    int page_cur = t_lo < t_hi ? lookup(t_lo) : OUTSIDE;
     int it = 0;
     for (int t = t_lo; t < t_hi && !abort_flag; ++t) {
+      const int page_next = t + 1 < t_hi ? lookup(t + 1) : OUTSIDE;
+      // Slots past the visible range still get data (the products read the whole buffer); any
+      // page of the request will do, the mask gives those keys a weight of exactly zero.
+      int page = page_cur == OUTSIDE ? first_page : page_cur;
+      if (page < 0 || page >= p.n_pages) {
+        if (lane < pages_per_tile) atomicExch(p.status, 2);
+        page = 0;
+      }
+      const int row = (page * p.kv_heads + kvh) * p.page_size;
       for (int kv = 0; kv < 2; ++kv, ++it) {                   // K_t, then V_t
         const int s = it % RING;
         bool ok = true;
@@ -169,21 +188,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) break;
         uint8_t* dst = skv + (size_t)s * C::KV_BYTES;
-        for (int i = lane; i < pages_per_tile; i += 32) {
-          const int j0 = t * KEYS + i * p.page_size;           // first key of this page slot
-          // Slots past the visible range still get data (the products read the whole buffer); any
-          // page of the request will do, the mask gives those keys a weight of exactly zero.
-          int page = (j0 < hi_all && j0 + p.page_size > lo_all) ? bt[j0 / p.page_size] : first_page;
-          if (page < 0 || page >= p.n_pages) {
-            atomicExch(p.status, 2);
-            page = 0;
-          }
-          const int row = (page * p.kv_heads + kvh) * p.page_size;
+        if (lane < pages_per_tile) {
           for (int sub = 0; sub < C::SUB; ++sub)
-            tma_load_2d(dst + (size_t)sub * KEYS * 128 + (size_t)i * page_bytes, kv == 0 ? &map_k : &map_v, sub * 64, row,
-                        &kv_full[s]);
+            tma_load_2d(dst + (size_t)sub * KEYS * 128 + (size_t)lane * page_bytes, kv == 0 ? &map_k : &map_v, sub * 64,
+                        row, &kv_full[s]);
         }
       }
+      page_cur = page_next;
     }
     __syncwarp();
   } else if (warp == 1) {
