@@ -55,6 +55,34 @@ def other_workload(a):
         B.measure_serving(gen, n_requests=64, min_len=16, max_len=2048, new_tokens=256, temperature=0.8, seed=1)  # warm-up
         res = B.measure_serving(gen, n_requests=64, min_len=16, max_len=2048, new_tokens=256, temperature=0.8, seed=3)
         res["workload"] = "LFM2-700M shape: 64 requests, prompts U[16, 2048], portions of 512 beside decode, 256 new tokens, T=0.8"
+    elif a.workload == "sweep":
+        # the benchmark's shape at other batch sizes, contexts and prompt lengths: one JSON line per point
+        from gibbs_b200 import Engine
+        base.update(max_position_embeddings=32768 + 256)
+        model = random_model(Lfm2Config.from_dict(base), SEED, dtype="bfloat16", device="cuda:0")
+        pk = B.load_peaks(ROOT)
+        hbm, tensor = pk["hbm_gbs"], pk["bf16_tflops"]
+        for ctx in (512, 2048, 8192, 32768):
+            for batch in (1, 8, 64):
+                if batch * ctx > 600_000:
+                    continue
+                eng = Engine(model, n_pages=batch * (ctx // 16 + 8), page_size=16, max_requests=batch,
+                             max_step_tokens=2048, max_context=ctx + 128)
+                d = B.measure_decode(eng, batch, ctx, 32, 4, seed=SEED)
+                print(json.dumps({"decode_batch": batch, "context": d["context"], "ms_per_step": round(d["ms_per_step"], 4),
+                                  "tok_s": round(d["tok_s"], 1), "gbs": round(d["gbs"], 1),
+                                  "hbm_frac": round(d["gbs"] / hbm, 3)}), flush=True)
+                del eng
+                torch.cuda.empty_cache()
+        for n in (128, 512, 2048, 8192):
+            eng = Engine(model, n_pages=n // 16 + 8, page_size=16, max_requests=1, max_step_tokens=n, max_context=n + 16)
+            pre = B.measure_prefill(eng, n, warmup=2, runs=3, seed=SEED)
+            frac = B.prefill_flops(model, n) / (pre["ms"] / 1e3) / (tensor * 1e12)
+            print(json.dumps({"prompt_tokens": n, "ms": round(pre["ms"], 3), "tok_s": round(pre["value"], 1),
+                              "tensor_frac": round(frac, 3)}), flush=True)
+            del eng
+            torch.cuda.empty_cache()
+        return 0
     else:
         base.update(num_hidden_layers=30, full_attn_idxs=[2, 6, 10, 14, 18, 22, 25, 28], intermediate_size=10752,
                     max_position_embeddings=8192)
@@ -81,7 +109,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="skip batch 1 and 64")
-    ap.add_argument("--workload", choices=["serve700m", "long2p6b"], default=None,
+    ap.add_argument("--workload", choices=["serve700m", "long2p6b", "sweep"], default=None,
                     help="run one of the other reference workloads instead (prints its own JSON line)")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="measure one phase only (for short profiler captures); the line is then partial")

@@ -56,7 +56,7 @@ enum OutMode : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2, OUT_SWIGLU = 3 
 template <int BN, bool DEEP = false> struct Cfg {
   static constexpr int X_TILE_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES;
-  static constexpr int STAGES = DEEP ? (BN >= 64 ? 8 : (BN >= 32 ? 9 : 10))
+  static constexpr int STAGES = DEEP ? (BN >= 128 ? 6 : (BN >= 64 ? 8 : (BN >= 32 ? 9 : 10)))
                                      : (BN >= 128 ? 3 : (BN >= 64 ? 4 : 5));
   static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;   // + room to align to 1024
@@ -781,7 +781,10 @@ int gb_pair();
 // ways a pair per tile and split was measured slower than the one-tile CTAs below, at every size).
 bool runs_on_pairs(int M, int N) {
   const long long pair_tiles = (long long)gb_div_up(N, 2 * BM) * gb_div_up(M, 256);
-  return M >= 192 && pair_tiles >= gb_pair_min() && gb_pair();
+  if (pair_tiles < gb_pair_min() || !gb_pair()) return false;
+  // From 96 tokens on a single wave of pairs beats the one-tile CTAs (gate+up at 128 tokens: 19 us
+  // against 26 us); with several waves of half-empty token tiles it does not (the head: 65 against 60 us).
+  return M >= 192 || (M >= 96 && pair_tiles <= 74);
 }
 
 void plan(int M, int N, int K, int* bn, int* splits, int* kb_per_split) {
@@ -834,7 +837,7 @@ int launch_as(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p,
 template <int BN>
 int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
   dim3 grid(gb_div_up(p.N, BM), gb_div_up(p.M, BN), p.splits);
-  if (BN == 64) {   // (measured: narrower tiles gain nothing from the deeper pipeline and lose the overlap with the next launch)
+  if (BN >= 64) {   // (measured: narrower tiles gain nothing from the deeper pipeline and lose the overlap with the next launch)
     static int n_sm = 0;
     if (n_sm == 0) {
       int dev = 0;
@@ -842,7 +845,7 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cu
       GB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
     }
     if ((long long)grid.x * grid.y * grid.z <= n_sm && gb_deep())
-      return launch_as<BN, (BN == 64)>(tw, tx, p, grid, stream);
+      return launch_as<BN, (BN >= 64)>(tw, tx, p, grid, stream);
   }
   return launch_as<BN, false>(tw, tx, p, grid, stream);
 }
