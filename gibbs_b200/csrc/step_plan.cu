@@ -108,8 +108,12 @@ int attention_splits(const Walk& w, int n_requests, int kv_heads, int max_ctx_le
   if (by_sm < 1) by_sm = 1;
   int by_len = (max_ctx_len + 127) / 128;
   if (by_len < 1) by_len = 1;
-  int s = by_sm < by_len ? by_sm : by_len;
-  if (s > 16) s = 16;
+  // up to 16 splits of at least two tiles; beyond that (up to the merge kernel's 32) only with 1,024 keys a split
+  int s = by_len < 16 ? by_len : 16;
+  int by_long = max_ctx_len / 1024;
+  if (by_long > 32) by_long = 32;
+  if (by_long > s) s = by_long;
+  if (s > by_sm) s = by_sm;
   return s < 1 ? 1 : s;
 }
 

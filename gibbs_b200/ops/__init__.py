@@ -567,9 +567,10 @@ _ATTN_CTAS = int(os.environ.get("GIBBS_B200_ATTN_CTAS", "592"))   # about four C
 def attention_splits(n_requests: int, kv_heads: int, max_ctx_len: int) -> int:
     """How many CTAs share the keys of one (request, kv head) when decoding:
     enough to occupy the GPU, at least two tiles of 64 keys each."""
-    by_sm = max(1, _ATTN_CTAS // max(1, n_requests * kv_heads))      # about five CTAs per SM
+    by_sm = max(1, _ATTN_CTAS // max(1, n_requests * kv_heads))      # about four CTAs per SM
     by_len = max(1, -(-max_ctx_len // 128))
-    return max(1, min(16, by_sm, by_len))
+    # up to 16 splits of at least two tiles; beyond that (up to the merge kernel's 32) only with 1,024 keys a split
+    return max(1, min(by_sm, max(min(16, by_len), min(32, max_ctx_len // 1024))))
 
 
 # prompt portions on tcgen05 (csrc/attention_tcgen05.cu); 0: keep them on the mma.sync kernel
