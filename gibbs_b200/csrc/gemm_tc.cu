@@ -784,6 +784,8 @@ bool runs_on_pairs(int M, int N) {
   if (pair_tiles < gb_pair_min() || !gb_pair()) return false;
   // From 96 tokens on a single wave of pairs beats the one-tile CTAs (gate+up at 128 tokens: 19 us
   // against 26 us); with several waves of half-empty token tiles it does not (the head: 65 against 60 us).
+  // Below 96 tokens (decode batches) a pair gains 8 % alone but the step loses 3 %: a pair holds its SMs'
+  // shared and tensor memory whole, so the products before and after it cannot start under it.
   return M >= 192 || (M >= 96 && pair_tiles <= 74);
 }
 
@@ -956,7 +958,8 @@ GB_API int gb_linear_tc(const void* X, long long ldx, const void* W, long long l
       tw = it->second;
     }
   }
-  if (!make_tmap(&tx, X, M, K, ldx, bn)) GB_FAIL(GB_ERR_CUDA, "gb_linear_tc: cuTensorMapEncodeTiled failed (X)");
+  const bool pairs = splits == 1 && runs_on_pairs(M, N);    // each CTA of a pair stages 128 token rows
+  if (!make_tmap(&tx, X, M, K, ldx, pairs ? 128 : bn)) GB_FAIL(GB_ERR_CUDA, "gb_linear_tc: cuTensorMapEncodeTiled failed (X)");
 
   if (defer == 2 && splits == 1) {
     if (mode != OUT_F32_ACC || workspace == nullptr)
@@ -977,7 +980,7 @@ GB_API int gb_linear_tc(const void* X, long long ldx, const void* W, long long l
   p.status = status;
   int rc;
   const long long n_tiles = (long long)gb_div_up(N, BM) * gb_div_up(M, bn);
-  if (bn == 128 && splits == 1 && runs_on_pairs(M, N)) {
+  if (pairs) {
     rc = launch_pair(tw, tx, p, stream);
   } else {
     switch (bn) {
