@@ -208,7 +208,7 @@ __global__ void sample_kernel(const float* __restrict__ logits, long long ldv, i
     // k passes: each takes the best element that is worse than the one before
     for (int round = 0; round < k; ++round) {
       Cand best = {0.f, -1};
-      const Cand p = prev;  // meaningful from round 1 on
+      const Cand p = prev;  // meaningful from the second pass on
       for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
         const float v = x[i];
         if (v != v) continue;  // NaN never wins
