@@ -148,6 +148,46 @@ def test_token_feedback_emits_the_tokens_of_the_plain_loop(tmp_path, dtype):
         assert got[1][3][0] == free[:free.index(stop[0])] and got[1][3][1] == "stop"
 
 
+@pytest.mark.parametrize("seed", [2, 4, 8])
+def test_token_feedback_under_random_traffic_and_page_pressure(tmp_path, seed):
+    """Requests arrive while others run, greedy and sampled, with end-of-sequence ids that do end
+    some of them and pools so small that requests are preempted: with ids that lag a step the
+    scheduler emits what the plain loop emits (32-bit, where a changed batch cannot move a choice)."""
+    import random
+    from gibbs_b200 import SamplingParams
+    folder = make_folder(tmp_path, "B", std=0.05)
+    vocab = TINY["B"][0]["vocab_size"]
+    rng = random.Random(seed)
+    gen = _gen(folder, "float32", ctx=128, n_pages=rng.choice([10, 14, 40]), max_running=rng.choice([2, 4]),
+               max_batch_tokens=rng.choice([16, 48]))
+    eos = {rng.randrange(vocab) for _ in range(40)}
+
+    def run(overlap):
+        r = random.Random(seed + 1000)
+        sched = gen.scheduler(stop_at_eos=False, overlap=overlap)
+        sched.eos_ids = set(eos)
+        ids, before = [], gen.engine.fed_steps
+        for step in range(2000):
+            if step < 40 and r.random() < 0.35:
+                prompt = [r.randrange(vocab) for _ in range(r.randint(1, 50))]
+                params = SamplingParams(temperature=r.choice([0.0, 0.9]), top_k=r.choice([1, 5, 50]),
+                                        top_p=r.choice([0.5, 1.0]), seed=r.randrange(1 << 30),
+                                        max_new_tokens=r.randint(0, 60))
+                ids.append(sched.submit(prompt, params))
+            if not sched.has_work():
+                if step >= 40:
+                    break
+                continue
+            sched.step()
+        assert not sched.has_work() and not gen.engine.cache.live
+        return [(sched.sequences[i].output, sched.sequences[i].finish) for i in ids], gen.engine.fed_steps - before
+
+    plain_loop, none_fed = run(False)
+    lagging, fed = run(True)
+    assert none_fed == 0 and fed > 5
+    assert plain_loop == lagging
+
+
 def test_eos_from_config_stops_generation(tmp_path):
     from gibbs_b200 import Lfm2Config, SamplingParams, write_random_model
     raw = dict(TINY["A"][0])
