@@ -159,35 +159,68 @@ class CacheManager:
             return 0
         return max(0, start_pos - group.window + 1) // self.page_size
 
+    def pages_wanted(self, wants) -> list[int]:
+        """Pages each group's pool must still give for ``wants``, a list of
+        (request cache, new length), once every request of the list has given
+        back the pages its window has passed."""
+        need = [0] * len(self.groups)
+        for rc, new_length in wants:
+            for g, group in enumerate(self.groups):
+                table = rc.block_tables[g]
+                first = self._first_needed_page(group, rc.length)
+                freed = sum(1 for p in table[:first] if p >= 0)
+                need[g] += max(self.pages_needed(new_length) - len(table), 0) - freed
+        return need
+
+    def can_reserve_all(self, wants) -> bool:
+        return all(n <= g.pool.n_free for n, g in zip(self.pages_wanted(wants), self.groups))
+
     def can_reserve(self, rc: RequestCache, new_length: int) -> bool:
-        for g, group in enumerate(self.groups):
-            table = rc.block_tables[g]
-            first = self._first_needed_page(group, rc.length)
-            freed = sum(1 for p in table[:first] if p >= 0)
-            want = self.pages_needed(new_length) - len(table)
-            if want > group.pool.n_free + freed:
-                return False
-        return True
+        return self.can_reserve_all([(rc, new_length)])
+
+    def reserve_all(self, wants) -> None:
+        """Make room for positions rc.length .. new_length-1 of every (request
+        cache, new length) of ``wants`` in every group, all or nothing: first
+        EVERY request gives back the pages its window has passed, then the new
+        pages are taken, so that one request's returns cover another's needs
+        whatever their order.  Takes nothing and raises OutOfPages when a pool
+        cannot cover the whole list."""
+        for rc, new_length in wants:
+            if new_length > self.max_context:
+                raise ValueError(f"request {rc.request_id!r} would reach {new_length} positions; "
+                                 f"the cache is laid out for {self.max_context}")
+        if not self.can_reserve_all(wants):
+            raise OutOfPages(f"requests {[rc.request_id for rc, _ in wants]!r} need {self.pages_wanted(wants)} more "
+                             f"pages per group; free: {self.free_pages()}")
+        for rc, _ in wants:
+            for g, group in enumerate(self.groups):
+                table = rc.block_tables[g]
+                first = self._first_needed_page(group, rc.length)
+                for i in range(min(first, len(table))):
+                    if table[i] >= 0:
+                        group.pool.give_back(table[i])
+                        table[i] = -1
+        for rc, new_length in wants:
+            for g, group in enumerate(self.groups):
+                table = rc.block_tables[g]
+                while len(table) < self.pages_needed(new_length):
+                    table.append(group.pool.take())
 
     def reserve(self, rc: RequestCache, new_length: int) -> None:
-        """Make room for positions rc.length .. new_length-1 in every group:
-        pages the window has passed are given back first, then new pages are
-        taken.  Takes nothing and raises OutOfPages when a pool cannot cover it."""
-        if new_length > self.max_context:
-            raise ValueError(f"request {rc.request_id!r} would reach {new_length} positions; "
-                             f"the cache is laid out for {self.max_context}")
-        if not self.can_reserve(rc, new_length):
-            raise OutOfPages(f"request {rc.request_id!r} needs pages for {new_length} positions; "
-                             f"free pages per group: {self.free_pages()}")
+        """``reserve_all`` for one request."""
+        self.reserve_all([(rc, new_length)])
+
+    def unreserve(self, rc: RequestCache) -> None:
+        """Give back the pages beyond the request's written length: what a
+        ``reserve`` took for a step that then did not run.  (Pages a window had
+        passed stay given back; no later step reads them.)"""
+        keep = self.pages_needed(rc.length)
         for g, group in enumerate(self.groups):
             table = rc.block_tables[g]
-            first = self._first_needed_page(group, rc.length)
-            for i in range(min(first, len(table))):
-                if table[i] >= 0:
-                    group.pool.give_back(table[i])
-                    table[i] = -1
-            while len(table) < self.pages_needed(new_length):
-                table.append(group.pool.take())
+            while len(table) > keep:
+                p = table.pop()
+                if p >= 0:
+                    group.pool.give_back(p)
 
     def advance(self, rc: RequestCache, new_length: int) -> None:
         """Record that positions up to new_length-1 are written."""

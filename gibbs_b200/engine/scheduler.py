@@ -132,6 +132,14 @@ class _InFlight:
     n_decode: int
 
 
+@dataclass
+class _FailedLaunch:
+    """A fed step that raised: its requests end with ``error`` once the ids of
+    the step before it have been read and emitted."""
+    seqs: list
+    error: str
+
+
 class Scheduler:
     def __init__(self, engine, sampler: Callable, max_batch_tokens: int = MAX_PREFILL_CHUNK,
                  max_running: Optional[int] = None, eos_ids: Sequence[int] = (), seed: int = 0,
@@ -261,8 +269,15 @@ class Scheduler:
         prev = self._inflight
         if prev is not None:
             # the next decode step goes out on the device's ids before the host reads this one's
-            self._inflight = self._launch_fed(prev)
+            nxt = self._launch_fed(prev)
+            self._inflight = nxt if isinstance(nxt, _InFlight) else None
             self._collect(prev, out)
+            if isinstance(nxt, _FailedLaunch):
+                # as a failing step ends its requests without overlap (below); a decode error
+                # ends the sequences of that step only (src/scheduler/mod.rs:1491-1499)
+                for seq in nxt.seqs:
+                    if seq.state == SeqState.RUNNING:
+                        self._finish(seq, FinishReason.ERROR, out, f"step failed: {nxt.error}")
             if self._inflight is not None and all(s.state != SeqState.RUNNING for s in self._inflight.seqs):
                 self._inflight = None               # everybody in it has ended meanwhile
             for seq in [s for s in self.running if s.cancelled]:
@@ -366,9 +381,12 @@ class Scheduler:
         self._emit(flight.seqs, flight.pending.wait(), out)
         self._account(out, time.perf_counter() - flight.launched, flight.n_prefill, flight.n_decode)
 
-    def _launch_fed(self, prev: _InFlight) -> Optional[_InFlight]:
+    def _launch_fed(self, prev: _InFlight):
         """The decode step after ``prev``, launched on the ids ``prev`` left on the
-        device; None when the host has to decide something first."""
+        device: an ``_InFlight``; None when the host has to decide something
+        first; a ``_FailedLaunch`` when the step raised.  A step that raises
+        has given back the pages it took, but state of fixed size may already
+        have moved, so its requests cannot simply be stepped again."""
         if self.waiting or any(s.cancelled for s in self.running):
             return None
         if sum(1 for s in prev.seqs if s.state == SeqState.RUNNING) != len(self.running):
@@ -390,14 +408,17 @@ class Scheduler:
         t0 = time.perf_counter()
         try:
             logits = self.engine.step(entries, feed=(prev.pending.device_ids, places))
+        except OutOfPages:
+            return None                             # nothing changed; preemption is decided with every id known
+        except Exception as e:
+            return _FailedLaunch(seqs, str(e))
+        for s in seqs:
+            s.fed += 1                              # the engine has advanced, whatever the sampler does now
+        try:
             pending = self.sampler.sample_async(logits, [s.params for s in seqs], [s.seed for s in seqs],
                                                 [len(s.output) + 1 for s in seqs])
-        except KeyboardInterrupt:
-            raise
-        except Exception:
-            return None                             # the step is tried again, and judged, with every id known
-        for s in seqs:
-            s.fed += 1
+        except Exception as e:
+            return _FailedLaunch(seqs, str(e))
         return _InFlight(seqs, pending, t0, 0, len(seqs))
 
     # -- convenience -------------------------------------------------------------

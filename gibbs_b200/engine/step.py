@@ -224,17 +224,12 @@ class Engine:
 
     # -- the step ---------------------------------------------------------------
     def can_run(self, entries: Sequence[StepEntry]) -> bool:
-        """Whether the pools have the pages this step would take."""
-        need = [0] * len(self.cache.groups)
-        for e in entries:
-            rc = self.cache.live[e.request_id]
-            new_len = rc.length + len(e.tokens)
-            for g, group in enumerate(self.cache.groups):
-                table = rc.block_tables[g]
-                first = self.cache._first_needed_page(group, rc.length)
-                freed = sum(1 for p in table[:first] if p >= 0)
-                need[g] += self.cache.pages_needed(new_len) - len(table) - freed
-        return all(n <= g.pool.n_free for n, g in zip(need, self.cache.groups))
+        """Whether the pools have the pages this step would take (what the
+        requests' windows have passed counts as free, as ``reserve_all`` gives
+        it back first)."""
+        live = self.cache.live
+        return self.cache.can_reserve_all([(live[e.request_id], live[e.request_id].length + len(e.tokens))
+                                           for e in entries])
 
     def _validate(self, entries):
         if not entries:
@@ -295,12 +290,23 @@ class Engine:
                 if f >= 0 and (len(e.tokens) != 1 or f >= picked.numel()):
                     raise StepError(f"request {e.request_id!r}: a token fed from the device stands alone in its "
                                     f"entry and its place lies among the {picked.numel()} picked ids")
-        if not self.can_run(entries):
-            raise OutOfPages(f"the step needs more pages than are free {self.cache.free_pages()}")
         rcs = [self.cache.live[e.request_id] for e in entries]
+        self.cache.reserve_all([(rc, rc.length + len(e.tokens)) for e, rc in zip(entries, rcs)])
+        try:
+            logits = self._launch(entries, rcs, n_tok, fed_from, picked if fed_from is not None else None)
+        except BaseException:
+            # nothing was advanced: the pages taken for this step go back, and the caller sees
+            # the requests as they stood before it
+            for rc in rcs:
+                self.cache.unreserve(rc)
+            raise
         for e, rc in zip(entries, rcs):
-            self.cache.reserve(rc, rc.length + len(e.tokens))
+            self.cache.advance(rc, rc.length + len(e.tokens))
+        self.steps_run += 1
+        return logits
 
+    def _launch(self, entries, rcs, n_tok, fed_from, picked):
+        """Metadata, transfer and kernels of one step whose pages are reserved."""
         n_req = len(entries)
         n_want = sum(len(e.want) for e in entries)
         bld = self.builder
@@ -341,9 +347,6 @@ class Engine:
             if decode:
                 # this run was the real step; capture the same work for the next steps of this size
                 self._capture(n_req, dev, step, caches, ops.launch_count() - before, args)
-        for e, rc in zip(entries, rcs):
-            self.cache.advance(rc, rc.length + len(e.tokens))
-        self.steps_run += 1
         return logits
 
     def _graph_meta(self, batch: int, total: int) -> torch.Tensor:

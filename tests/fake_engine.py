@@ -33,11 +33,9 @@ class FakeEngine:
         del self.fed[rid]
 
     def can_run(self, entries):
-        need = 0
-        for e in entries:
-            rc = self.cache.live[e.request_id]
-            need += self.cache.pages_needed(rc.length + len(e.tokens)) - len(rc.block_tables[0])
-        return need <= self.cache.groups[0].pool.n_free
+        live = self.cache.live
+        return self.cache.can_reserve_all([(live[e.request_id], live[e.request_id].length + len(e.tokens))
+                                           for e in entries])
 
     def step(self, entries, feed=None):
         if feed is not None:
@@ -48,15 +46,17 @@ class FakeEngine:
                        for e, f in zip(entries, places)]
         else:
             self.events.append("launch")
+        rcs = [self.cache.live[e.request_id] for e in entries]
+        self.cache.reserve_all([(rc, rc.length + len(e.tokens)) for e, rc in zip(entries, rcs)])
         if self.fail_on is not None and len(self.log) == self.fail_on:
+            # as the real engine: a launch that raises gives back what the step reserved
             self.log.append("failed")
+            for rc in rcs:
+                self.cache.unreserve(rc)
             raise RuntimeError("injected step failure")
-        if not self.can_run(entries):
-            raise OutOfPages("fake engine out of pages")
         rows = []
         for e in entries:
             rc = self.cache.live[e.request_id]
-            self.cache.reserve(rc, rc.length + len(e.tokens))
             self.cache.advance(rc, rc.length + len(e.tokens))
             base = len(self.fed[e.request_id])
             self.fed[e.request_id].extend(e.tokens)

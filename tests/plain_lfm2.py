@@ -146,7 +146,7 @@ def causal_attention(q, k, v, scale, window=None):
     n, heads, hd = q.shape
     rep = heads // k.shape[1]
     out = torch.zeros_like(q)
-    idx = torch.arange(n)
+    idx = torch.arange(n, device=q.device)
     mask = idx[None, :] <= idx[:, None]
     if window is not None:
         mask &= idx[None, :] + window > idx[:, None]
@@ -171,7 +171,7 @@ def attention_mixer(h, w, prefix, sizes, positions):
     v = linear(h, w[prefix + "v_proj.weight"], w.get(prefix + "v_proj.bias")).reshape(n, kvh, hd)
     q = rms_norm(q, w[prefix + "q_layernorm.weight"], sizes["eps"])
     k = rms_norm(k, w[prefix + "k_layernorm.weight"], sizes["eps"])
-    inv = rope_inv_freq(hd, sizes["theta"], h.dtype)
+    inv = rope_inv_freq(hd, sizes["theta"], h.dtype).to(h.device)
     q = rope_half_split(q, positions, inv)
     k = rope_half_split(k, positions, inv)
     o = causal_attention(q, k, v, 1.0 / math.sqrt(hd))
@@ -185,7 +185,7 @@ def causal_conv1d(bx, taps, bias=None):
     (arch/families/lfm2.json5:53), adds to the conv output."""
     n, _ = bx.shape
     kk = taps.shape[1]
-    pad = torch.cat([torch.zeros(kk - 1, bx.shape[1], dtype=bx.dtype), bx], 0)
+    pad = torch.cat([torch.zeros(kk - 1, bx.shape[1], dtype=bx.dtype, device=bx.device), bx], 0)
     out = torch.zeros_like(bx)
     for j in range(kk):
         out = out + pad[j : j + n] * taps[:, j][None, :]
@@ -212,15 +212,18 @@ def swiglu_ffn(h, w, prefix):
     return linear((g * sig) * u, w[prefix + "w2.weight"], w.get(prefix + "w2.bias"))
 
 
-def forward(cfg: dict, weights: dict, ids, dtype=torch.float64) -> torch.Tensor:
+def forward(cfg: dict, weights: dict, ids, dtype=torch.float64, rows=None, device="cpu") -> torch.Tensor:
     """Logits [n, vocab] of one whole sequence at positions 0..n-1
     (layer loop: arch/families/lfm2.json5:73-92).  A layer is a conv layer
     when the checkpoint has its ``conv.in_proj.weight``
-    (arch/families/lfm2.json5:78-80)."""
+    (arch/families/lfm2.json5:78-80).  ``rows``: only these positions pass
+    through the final norm and the head (the reference's ``head: 'last'``,
+    arch/lib/transformer.json5:190, for any rows).  ``device``: where torch
+    computes; the formulas are the same anywhere."""
     sizes = resolve_sizes(cfg)
-    w = {k: v.to(dtype) for k, v in weights.items()}
-    ids = torch.as_tensor(ids, dtype=torch.long)
-    positions = torch.arange(len(ids))
+    w = {k: v.to(device=device, dtype=dtype) for k, v in weights.items()}
+    ids = torch.as_tensor(ids, dtype=torch.long, device=device)
+    positions = torch.arange(len(ids), device=device)
     x = w["model.embed_tokens.weight"][ids]
     for i in range(sizes["layers"]):
         p = f"model.layers.{i}."
@@ -232,6 +235,8 @@ def forward(cfg: dict, weights: dict, ids, dtype=torch.float64) -> torch.Tensor:
         x = x + a
         h = rms_norm(x, w[p + "ffn_norm.weight"], sizes["eps"])
         x = x + swiglu_ffn(h, w, p + "feed_forward.")
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), dtype=torch.long, device=device)]
     z = rms_norm(x, w["model.embedding_norm.weight"], sizes["eps"])
     head = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
     return linear(z, head)

@@ -131,3 +131,34 @@ def test_random_orders_of_requests(seed):
         m.close(rid)
     m.check()
     assert m.free_pages() == [12] and m.slots.n_free == 4
+
+
+def test_windowed_requests_on_an_exactly_full_pool_reserve_all_or_nothing():
+    """Two windowed requests fill the pool to the last page.  Their next step fits only because
+    each gives back the page its window has passed; a step's requests are reserved together
+    (every give-back before any take), so the order of the entries does not matter and a step
+    that does not fit takes nothing."""
+    m = _manager(n_pages=4, page_size=4, window=4, max_context=64)
+    a, b = m.open("a"), m.open("b")
+    m.reserve_all([(a, 8), (b, 8)])
+    m.advance(a, 8), m.advance(b, 8)
+    assert m.free_pages() == [0]
+    # positions 8..11 need a third page each; page 0 of each request (positions 0..3) has left the window
+    assert m.can_reserve_all([(a, 12), (b, 12)]) and m.can_reserve_all([(b, 12), (a, 12)])
+    before = ([list(t) for t in a.block_tables], [list(t) for t in b.block_tables])
+    # a step that does not fit (b would need two more pages) changes nothing
+    assert not m.can_reserve_all([(a, 12), (b, 16)])
+    with pytest.raises(OutOfPages):
+        m.reserve_all([(a, 12), (b, 16)])
+    assert ([list(t) for t in a.block_tables], [list(t) for t in b.block_tables]) == before and m.free_pages() == [0]
+    m.check()
+    m.reserve_all([(b, 12), (a, 12)])
+    assert a.block_tables[0][0] == -1 and b.block_tables[0][0] == -1 and m.free_pages() == [0]
+    m.check()
+    # a step that is not run gives back what it took; pages the window had passed stay given back
+    m.unreserve(a)
+    assert len(a.block_tables[0]) == 2 and m.free_pages() == [1]
+    m.check()
+    m.close("a"), m.close("b")
+    m.check()
+    assert m.free_pages() == [4]

@@ -290,3 +290,56 @@ def test_overlap_emits_what_the_plain_loop_emits_under_random_traffic(seed):
     lagging, fed = run(True)
     assert none_fed == 0 and fed > 0
     assert plain == lagging
+
+
+@pytest.mark.parametrize("fail_on", [1, 2, 3, 5])
+def test_a_failing_fed_step_ends_its_requests_like_a_failing_plain_step(fail_on):
+    """The same engine step fails with and without token feedback: the same requests end with
+    ``error`` after the same tokens, nothing stays reserved, and the loop goes on."""
+    def run(overlap):
+        eng = FakeEngine(fail_on=fail_on, n_pages=16, page_size=4)
+        s = Scheduler(eng, LaggingSampler(eng), overlap=overlap)
+        a = s.submit([1, 2, 3], SamplingParams(temperature=0.0, max_new_tokens=12))
+        b = s.submit([5, 6, 7, 8, 9], SamplingParams(temperature=0.0, max_new_tokens=12))
+        emitted = {a: [], b: []}
+        while s.has_work():
+            for i, t in s.step().emitted:
+                emitted[i].append(t)
+            eng.cache.check()
+        assert not eng.cache.live and eng.cache.free_pages() == [16] and eng.cache.slots.n_free == 4
+        assert emitted == {i: s.sequences[i].output for i in (a, b)}
+        for i in (a, b):
+            assert s.sequences[i].finish == FinishReason.ERROR and "injected" in s.sequences[i].error
+        # the loop goes on with a new request
+        c = s.submit([4, 4], GREEDY)
+        s.run()
+        assert s.sequences[c].output == expected_greedy([4, 4], 8, eng.vocab)
+        return [(s.sequences[i].output, s.sequences[i].finish) for i in (a, b)], eng.events.count("launch fed")
+
+    plain, none_fed = run(False)
+    lagging, fed = run(True)
+    assert none_fed == 0 and (fed > 0 or fail_on < 2)
+    assert plain == lagging
+
+
+def test_a_sampler_that_fails_after_a_fed_step_ends_the_requests():
+    """The engine has advanced when the sampler raises: the requests cannot be stepped again at
+    the old position, so they end with ``error`` and give everything back."""
+    eng = FakeEngine()
+
+    class Flaky(LaggingSampler):
+        calls = 0
+
+        def sample_async(self, *a):
+            Flaky.calls += 1
+            if Flaky.calls == 3:
+                raise RuntimeError("sampler fell over")
+            return super().sample_async(*a)
+
+    s = Scheduler(eng, Flaky(eng), overlap=True)
+    a = s.submit([1, 2, 3], SamplingParams(temperature=0.0, max_new_tokens=12))
+    s.run()
+    assert s.sequences[a].finish == FinishReason.ERROR and "fell over" in s.sequences[a].error
+    assert s.sequences[a].output == expected_greedy([1, 2, 3], 12, eng.vocab)[:len(s.sequences[a].output)]
+    assert len(s.sequences[a].output) >= 2
+    assert not eng.cache.live and eng.cache.free_pages() == [64]
