@@ -16,7 +16,7 @@ import math
 from dataclasses import dataclass, asdict
 from typing import Iterable, Optional
 
-from .plan import LayerSpec, ModelPlan, OrderEntry, PartSpec
+from .plan import ModelPlan, OrderEntry, PartSpec, prenorm_layer
 
 
 class ConfigError(ValueError):
@@ -235,8 +235,7 @@ class Lfm2Config:
                            "down.weight": fstems["w2"] + ".weight"},
                           {"gate": fstems["w1"], "up": fstems["w3"], "down": fstems["w2"]}, self.ffn_bias),
             )
-            layers.append(LayerSpec("prenorm_residual", norm(f"{p}.operator_norm.weight"), mixer,
-                                    norm(f"{p}.ffn_norm.weight"), ffn))
+            layers.append(prenorm_layer(norm(f"{p}.operator_norm.weight"), mixer, norm(f"{p}.ffn_norm.weight"), ffn))
 
         table = "model.embed_tokens.weight"
         plan = ModelPlan(

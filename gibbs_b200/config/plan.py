@@ -26,14 +26,38 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """A block: how norm, mixer and feed-forward are arranged (``block``) and
-    the four parts it is made of."""
+    """A block: the registry kind of its arrangement (``block``), the parts it
+    is made of as (role, category, PartSpec) in the arrangement's own order,
+    and the arrangement's constants.  Which roles there are is the
+    arrangement's business: pre-norm residual has a norm before the mixer and
+    one before the feed-forward; another may add norms after them, share one
+    norm between two parallel branches, or have no feed-forward at all."""
 
     block: str
-    mixer_norm: PartSpec
-    mixer: PartSpec
-    ffn_norm: PartSpec
-    ffn: PartSpec
+    parts: tuple[tuple[str, str, PartSpec], ...]
+    params: dict[str, Any] = field(default_factory=dict)
+
+    def part(self, role: str) -> PartSpec:
+        for r, _, spec in self.parts:
+            if r == role:
+                return spec
+        raise KeyError(f"the '{self.block}' layer has no part in the role '{role}'; it has "
+                       f"{[r for r, _, _ in self.parts]}")
+
+    def __getattr__(self, role: str) -> PartSpec:
+        # layer.mixer, layer.ffn, ...: the part in that role
+        if role.startswith("_") or role in ("block", "parts", "params"):
+            raise AttributeError(role)
+        try:
+            return self.part(role)
+        except KeyError as e:
+            raise AttributeError(str(e)) from None
+
+
+def prenorm_layer(mixer_norm: PartSpec, mixer: PartSpec, ffn_norm: PartSpec, ffn: PartSpec) -> LayerSpec:
+    """The arrangement x += mixer(norm(x)); x += ffn(norm(x))."""
+    return LayerSpec("prenorm_residual", (("mixer_norm", "norm", mixer_norm), ("mixer", "mixer", mixer),
+                                          ("ffn_norm", "norm", ffn_norm), ("ffn", "feed_forward", ffn)))
 
 
 @dataclass(frozen=True)

@@ -104,7 +104,7 @@ def model_flops_per_token(model) -> int:
     total = 0
     seen = {head.data_ptr()}
     for b in model.blocks:
-        for holder in (b.mixer, b.ffn):
+        for holder in b.parts.values():
             for v in vars(holder).values():
                 w = getattr(v, "weight", None)
                 if isinstance(w, torch.Tensor) and w.dim() == 2 and w.data_ptr() not in seen:
@@ -116,10 +116,11 @@ def model_flops_per_token(model) -> int:
 def prefill_flops(model, n_tokens: int, n_logit_rows: int = 1) -> int:
     fl = model_flops_per_token(model) * n_tokens + 2 * model.head.proj.weight.numel() * n_logit_rows
     for b in model.blocks:
-        m = b.mixer
-        if hasattr(m, "heads") and hasattr(m, "head_dim"):
-            # scores and weighted values over the causal half: 2 * 2 * hd * T(T+1)/2 per head
-            fl += 2 * m.heads * m.head_dim * n_tokens * (n_tokens + 1)
+        for m in b.parts.values():
+            # a part that attends says how many flops its scores and weighted values cost
+            extra = getattr(m, "attention_flops", None)
+            if extra is not None:
+                fl += int(extra(n_tokens))
     return fl
 
 

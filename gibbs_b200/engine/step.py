@@ -194,7 +194,7 @@ class Engine:
         self.fed_steps = 0          # steps some of whose tokens came from ids on the device
         # decode steps are replayed from CUDA graphs, one per batch size, unless a part of the
         # model cannot be captured (it reads host-side step data)
-        self.use_graphs = bool(use_graphs) and all(getattr(b.mixer, "capturable", True) for b in model.blocks)
+        self.use_graphs = bool(use_graphs) and all(b.capturable for b in model.blocks)
         self._graphs: dict = {}
         self._graph_pool = None
         self._capture_stream = torch.cuda.Stream(device=self.device) if self.use_graphs else None

@@ -69,6 +69,14 @@ class GQAAttention(Mixer):
     def cache_needs(self):
         return [] if self.shares_kv else [PagedKV(self.kv_heads, self.head_dim, self.window)]
 
+    def attention_flops(self, n_tokens: int) -> int:
+        """Scores and weighted values of a whole prompt over the causal half (or the
+        window): 2 * 2 * head_dim multiply-adds per visible (query, key) pair and head."""
+        pairs = n_tokens * (n_tokens + 1) // 2
+        if self.window and n_tokens > self.window:
+            pairs -= (n_tokens - self.window) * (n_tokens - self.window + 1) // 2
+        return 4 * self.heads * self.head_dim * pairs
+
     def forward(self, h, residual, step, caches):
         kv = caches[0]
         if not self.shares_kv and not kv.writable:

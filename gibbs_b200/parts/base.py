@@ -23,7 +23,12 @@ Categories and what each must implement:
               projection called with ``out=residual, accumulate=True``);
               ``caches`` holds one view per need.
   feed_forward ``forward(h, residual, step)``, adding likewise.
-  block       built from its four parts; ``forward(residual, step, caches)``.
+  block       an arrangement of parts around the residual stream.  Its class
+              names the roles it is made of (``ROLES``: (role, category) pairs);
+              a plan's layer gives one part per role; the block is built from
+              ``{role: part}`` and implements ``forward(residual, step, caches)``.
+              ``caches`` holds the views of all its parts' cache needs, in the
+              order of the roles (``caches_of(role, caches)`` picks a part's).
   Optionally every part has ``plan_ops(plan, ...)`` with the arguments of its
   ``forward`` minus the step and the residual: it appends the same work as
   operations of a step plan (``engine/plan.py``), which the engine then runs
@@ -200,11 +205,74 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
-class Block:
-    category = "block"
+def tensor_bytes(obj, seen: set) -> int:
+    """Bytes of the floating-point tensors an object (and the helpers it
+    holds) keeps, each tensor counted once across calls that share ``seen``."""
+    total = 0
+    if id(obj) in seen:
+        return 0
+    seen.add(id(obj))
+    values = obj.values() if isinstance(obj, dict) else vars(obj).values() if hasattr(obj, "__dict__") else ()
+    for v in values:
+        if isinstance(v, torch.Tensor):
+            if v.is_floating_point() and v.data_ptr() not in seen:
+                seen.add(v.data_ptr())
+                total += v.numel() * v.element_size()
+        elif isinstance(v, (list, tuple)):
+            total += sum(tensor_bytes(u, seen) for u in v if hasattr(u, "__dict__") or isinstance(u, dict))
+        elif (hasattr(v, "__dict__") or isinstance(v, dict)) and not isinstance(v, (Runtime, type)):
+            total += tensor_bytes(v, seen)
+    return total
 
-    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, ffn: FeedForward, rt: Runtime):
-        self.mixer_norm, self.mixer, self.ffn_norm, self.ffn, self.rt = mixer_norm, mixer, ffn_norm, ffn, rt
+
+def step_weight_bytes(part, n_tokens: int, seen: set) -> int:
+    """Bytes of weights ``part`` reads in a step of ``n_tokens`` tokens when
+    each is read once.  A part whose step reads only some of its weights (a
+    feed-forward that routes among experts) says so with a method
+    ``step_weight_bytes(n_tokens, seen)`` of its own; for every other part it
+    is all its floating-point tensors."""
+    own = getattr(part, "step_weight_bytes", None)
+    if own is not None:
+        return int(own(n_tokens, seen))
+    return tensor_bytes(part, seen)
+
+
+class Block:
+    """An arrangement of parts around the residual stream.  ``ROLES`` names
+    what it is made of; ``build_model`` checks a plan's layer against it and
+    hands the parts over as ``{role: part}`` (also reachable as attributes)."""
+    category = "block"
+    ROLES: tuple = ()
+
+    def __init__(self, parts: dict, rt: Runtime, params: Optional[dict] = None):
+        self.parts, self.rt, self.params = dict(parts), rt, dict(params or {})
+        for role, part in self.parts.items():
+            setattr(self, role, part)
+        self._cache_slices: dict = {}
+        at = 0
+        for role, part in self.parts.items():
+            needs = getattr(part, "cache_needs", None)
+            n = len(needs()) if needs is not None else 0
+            self._cache_slices[role] = (at, at + n)
+            at += n
+
+    def cache_needs(self) -> list:
+        """The cache needs of all parts of the block, in the order of its roles."""
+        out = []
+        for part in self.parts.values():
+            needs = getattr(part, "cache_needs", None)
+            if needs is not None:
+                out += list(needs())
+        return out
+
+    def caches_of(self, role: str, caches: list) -> list:
+        lo, hi = self._cache_slices[role]
+        return caches[lo:hi]
+
+    @property
+    def capturable(self) -> bool:
+        """Whether a decode step through this block can be recorded into a CUDA graph."""
+        return all(getattr(p, "capturable", True) for p in self.parts.values())
 
     def forward(self, x: torch.Tensor, step, caches: list) -> None:
         raise NotImplementedError

@@ -8,17 +8,15 @@ from typing import Optional
 import torch
 
 from ..config.plan import ModelPlan, PartSpec
-from .base import Residual, Runtime, part_class, plan_ops_of
+from .base import Residual, Runtime, part_class, plan_ops_of, step_weight_bytes
 
 
 def plan_parts(plan: ModelPlan):
     """Every (category, spec) of a plan, in build order."""
     yield "embedding", plan.embedding
     for layer in plan.layers:
-        yield "norm", layer.mixer_norm
-        yield "mixer", layer.mixer
-        yield "norm", layer.ffn_norm
-        yield "feed_forward", layer.ffn
+        for _, category, spec in layer.parts:
+            yield category, spec
     yield "norm", plan.final_norm
     yield "head", plan.head
 
@@ -32,12 +30,12 @@ class CausalLM:
     def entry_needs(self):
         """For each entry of the plan's order: (cache needs of its mixer, the
         entry whose cache it reads instead, or None)."""
-        return [(self.blocks[e.layer].mixer.cache_needs(), e.reads_cache_of) for e in self.plan.order]
+        return [(self.blocks[e.layer].cache_needs(), e.reads_cache_of) for e in self.plan.order]
 
     def kernel_libraries(self) -> set[str]:
         libs = {"core"}
         for part in [self.embedding, self.final_norm, self.head] + \
-                [p for b in self.blocks for p in (b.mixer_norm, b.mixer, b.ffn_norm, b.ffn)]:
+                [p for b in self.blocks for p in b.parts.values()]:
             libs |= set(part.kernel_libraries())
         return libs
 
@@ -61,28 +59,17 @@ class CausalLM:
         z = plan_ops_of(self.final_norm)(plan, wanted_rows=True)
         plan_ops_of(self.head)(plan, z, plan.LOGITS)
 
-    def weight_bytes_per_step(self) -> int:
-        """Bytes of weights one step reads when each is read once: every
-        projection matrix (a tied table once, as the head) and the small
-        vectors; the embedding rows a step gathers are not counted."""
-        seen, total = set(), 0
-
-        def visit(obj):
-            nonlocal total
-            for v in vars(obj).values():
-                if isinstance(v, torch.Tensor):
-                    if v.data_ptr() not in seen and v.is_floating_point():
-                        seen.add(v.data_ptr())
-                        total += v.numel() * v.element_size()
-                elif hasattr(v, "__dict__") and not isinstance(v, (Runtime, type)) and id(v) not in seen:
-                    seen.add(id(v))
-                    visit(v)
-
+    def weight_bytes_per_step(self, n_tokens: int = 1) -> int:
+        """Bytes of weights a step of ``n_tokens`` tokens reads when each is
+        read once: every projection matrix (a tied table once, as the head)
+        and the small vectors; the embedding rows a step gathers are not
+        counted.  Each part answers for itself (``parts.base.step_weight_bytes``)."""
+        seen: set = set()
+        total = 0
         for b in self.blocks:
-            visit(b)
-        visit(self.final_norm)
-        visit(self.head)
-        return total
+            for part in b.parts.values():
+                total += step_weight_bytes(part, n_tokens, seen)
+        return total + step_weight_bytes(self.final_norm, n_tokens, seen) + step_weight_bytes(self.head, n_tokens, seen)
 
 
 def build_model(plan: ModelPlan, source, dtype: torch.dtype, device) -> CausalLM:
@@ -101,10 +88,15 @@ def build_model(plan: ModelPlan, source, dtype: torch.dtype, device) -> CausalLM
 
     embedding = make("embedding", plan.embedding)
     blocks = []
-    for layer in plan.layers:
+    for i, layer in enumerate(plan.layers):
         block_cls = part_class("block", layer.block)
-        blocks.append(block_cls(make("norm", layer.mixer_norm), make("mixer", layer.mixer),
-                                make("norm", layer.ffn_norm), make("feed_forward", layer.ffn), rt))
+        given = tuple((role, category) for role, category, _ in layer.parts)
+        wanted = tuple(getattr(block_cls, "ROLES", ()))
+        if wanted and given != wanted:
+            raise ValueError(f"layer {i}: the '{layer.block}' arrangement is made of {list(wanted)}; "
+                             f"the plan gives {list(given)}")
+        blocks.append(block_cls({role: make(category, spec) for role, category, spec in layer.parts}, rt,
+                                layer.params))
     final_norm = make("norm", plan.final_norm)
     head = make("head", plan.head)
     binder.release()

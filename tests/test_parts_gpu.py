@@ -236,7 +236,7 @@ def _plain_toy(h, w_in, w_out, decay):
 def _hand_plan(hidden=64, heads=4, kvh=2, hd=16, inner=128, vocab=300, eps=1e-5, window=24, state=10):
     """Layers: 0 toy mixer, 1 attention (all keys), 2 attention with a window, 3 attention without
     k/v of its own.  Order: 0, 1, 2, 1 again (its own cache), 3 reading the cache of entry 1."""
-    from gibbs_b200.config import LayerSpec, ModelPlan, OrderEntry, PartSpec
+    from gibbs_b200.config import ModelPlan, OrderEntry, PartSpec, prenorm_layer
 
     def norm(name):
         return PartSpec("rmsnorm", {"dim": hidden, "eps": eps}, {"weight": name})
@@ -257,8 +257,7 @@ def _hand_plan(hidden=64, heads=4, kvh=2, hd=16, inner=128, vocab=300, eps=1e-5,
     toy = PartSpec("toy_decay", {"hidden": hidden, "state": state},
                    {"w_in": "l0.win", "w_out": "l0.wout", "decay": "l0.decay"})
     mixers = [toy, attn(1), attn(2, window=window), attn(3, shares=True)]
-    layers = tuple(LayerSpec("prenorm_residual", norm(f"l{i}.n1"), m, norm(f"l{i}.n2"), ffn(i))
-                   for i, m in enumerate(mixers))
+    layers = tuple(prenorm_layer(norm(f"l{i}.n1"), m, norm(f"l{i}.n2"), ffn(i)) for i, m in enumerate(mixers))
     order = (OrderEntry(0), OrderEntry(1), OrderEntry(2), OrderEntry(1), OrderEntry(3, reads_cache_of=1))
     return ModelPlan("hand-made", vocab, hidden, 512, PartSpec("token_embedding", {"vocab": vocab, "dim": hidden},
                                                                 {"weight": "emb"}),
@@ -394,7 +393,7 @@ def _toy_scaled_rope():
 
 
 def _toy_plan(hidden=48, heads=3, kvh=1, hd=32, rd=16, factor=4.0, inner=64, experts=3, vocab=200, eps=1e-6):
-    from gibbs_b200.config import LayerSpec, ModelPlan, OrderEntry, PartSpec
+    from gibbs_b200.config import ModelPlan, OrderEntry, PartSpec, prenorm_layer
 
     def norm(name):
         return PartSpec("rmsnorm", {"dim": hidden, "eps": eps}, {"weight": name})
@@ -410,8 +409,7 @@ def _toy_plan(hidden=48, heads=3, kvh=1, hd=32, rd=16, factor=4.0, inner=64, exp
                     {"in_proj.weight": "c.in", "conv.weight": "c.taps", "out_proj.weight": "c.out"})
     dense = PartSpec("swiglu", {"hidden": hidden, "inner": 64, "bias": False},
                      {"gate.weight": "d.g", "up.weight": "d.u", "down.weight": "d.d"})
-    layers = (LayerSpec("prenorm_residual", norm("n0"), attn, norm("n1"), routed),
-              LayerSpec("prenorm_residual", norm("n2"), conv, norm("n3"), dense))
+    layers = (prenorm_layer(norm("n0"), attn, norm("n1"), routed), prenorm_layer(norm("n2"), conv, norm("n3"), dense))
     emb = PartSpec("token_embedding", {"vocab": vocab, "dim": hidden}, {"weight": "emb"})
     return ModelPlan("toy-routed", vocab, hidden, 256, emb, layers, (OrderEntry(0), OrderEntry(1)), norm("fn"),
                      PartSpec("lm_head", {"vocab": vocab, "dim": hidden}, {"weight": "head"}))
