@@ -7,7 +7,9 @@ Prints ONE JSON line.  ``value`` is decoded tokens a second at the given batch
 (device time over exactly K decode steps, CUDA events); ``e2e`` is the same
 through the Python entry point, with token ids coming from and going to the
 host every step; ``prefill`` times one whole prompt of 2,048 tokens; ``roofline``
-relates the decode step to the memory bandwidth; ``points`` holds batch 1 and 64.
+relates the decode step to the memory bandwidth; ``points`` holds batch 1 and 64.  The region of K decode steps is timed five times
+back to back; ``value`` and ``e2e`` are the median region's, with the spread
+((slowest - fastest) / median) beside them.
 The model has random bfloat16 weights and uniform-random token ids (there is
 neither a checkpoint nor a dataset here).  Decode steps read 2.3 GB of
 weights each, far more than the L2 holds, so no flush is needed between steps.
@@ -31,6 +33,7 @@ LFM2_1P2B = dict(
     max_position_embeddings=4096,
 )
 SEED, PROMPT_LEN, CONTEXT = 2, 2048, 4096
+REPEATS = 5             # regions of K decode steps timed back to back; the median is reported
 
 
 def reference_arm():
@@ -60,7 +63,7 @@ def other_workload(a):
         from gibbs_b200 import Engine
         base.update(max_position_embeddings=32768 + 256)
         model = random_model(Lfm2Config.from_dict(base), SEED, dtype="bfloat16", device="cuda:0")
-        pk = B.load_peaks(ROOT)
+        pk = B.load_peaks(os.path.join(ROOT, "MEASURED_PEAKS.json"))
         hbm, tensor = pk["hbm_gbs"], pk["bf16_tflops"]
         for ctx in (512, 2048, 8192, 32768):
             for batch in (1, 8, 64):
@@ -133,7 +136,7 @@ def main():
         raw["num_hidden_layers"] = a.layers
         raw["full_attn_idxs"] = [i for i in raw["full_attn_idxs"] if i < a.layers]
     cfg = Lfm2Config.from_dict(raw)
-    peaks = B.load_peaks(ROOT)
+    peaks = B.load_peaks(os.path.join(ROOT, "MEASURED_PEAKS.json"))
     torch.manual_seed(0)
     model = random_model(cfg, SEED, dtype="bfloat16", device="cuda:0")
 
@@ -155,18 +158,22 @@ def main():
     pre_flops = B.prefill_flops(model, PROMPT_LEN)
     pre["frac"] = pre_flops / (pre["ms"] / 1e3) / (peaks["bf16_tflops"] * 1e12)
 
+    # as many regions as the context has room for after the prompt (five by default)
+    repeats = max(1, min(REPEATS, (CONTEXT - PROMPT_LEN - a.warmup - 4 * max_batch - 32) // max(a.steps, 1)))
     with B.ClockSampler() as clocks:
-        dec = B.measure_decode(eng, a.batch, PROMPT_LEN, a.steps, a.warmup, seed=SEED)
-    e2e = B.measure_decode_e2e(gen, a.batch, PROMPT_LEN, a.steps, a.warmup, seed=SEED)
+        dec = B.measure_decode(eng, a.batch, PROMPT_LEN, a.steps, a.warmup, seed=SEED, repeats=repeats)
+    e2e = B.measure_decode_e2e(gen, a.batch, PROMPT_LEN, a.steps, a.warmup, seed=SEED, repeats=repeats)
     points = {}
     if not a.skip_points:
         for b in (1, 64):
             if b != a.batch:
-                points[f"decode_b{b}"] = round(B.measure_decode(eng, b, PROMPT_LEN, a.steps, a.warmup, seed=SEED)["tok_s"], 1)
+                points[f"decode_b{b}"] = round(B.measure_decode(eng, b, PROMPT_LEN, a.steps, a.warmup, seed=SEED,
+                                                                 repeats=min(3, repeats))["tok_s"], 1)
 
     line = {
         "metric": "LFM2-1.2B decode tok/s", "value": round(dec["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1,
         "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(dec["ms_per_step"], 4),
+        "repeats": dec["repeats"], "spread": round(dec["spread"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights N(0, 0.02) seed 2, uniform-random token ids",
         "config": {
@@ -177,7 +184,7 @@ def main():
             "ffn": cfg.ffn_dim, "vocab": cfg.vocab_size, "conv_L_cache": cfg.conv_L_cache, "page_size": page_size,
             "l2": "step inputs (2.3 GB of weights) exceed L2; no flush",
         },
-        "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items()},
+        "e2e": {k: (round(v, 4 if k == "spread" else 1) if isinstance(v, float) else v) for k, v in e2e.items()},
         "gpu_launches": dec["launches"],
         "prefill": {"value": round(pre["value"], 1), "tokens": pre["tokens"], "ms": round(pre["ms"], 3),
                     "frac": round(pre["frac"], 4)},

@@ -73,11 +73,17 @@ class RequestCache:
 
 
 class CacheManager:
+    GUARD_BYTE = 0x5A
+
     def __init__(self, entry_needs, n_pages, page_size: int, n_slots: int, dtype: torch.dtype, device,
-                 max_context: int):
+                 max_context: int, guard: bool = False):
         """entry_needs: for each entry of the model's order, (list of needs,
         entry whose cache it reads instead or None).  n_pages: an int (for
-        every group) or a dict from window (None = all keys) to a count."""
+        every group) or a dict from window (None = all keys) to a count.
+        ``guard``: one page before and after every page tensor, one slot row
+        before and after the slots and 16 bytes behind every slot are filled
+        with a pattern that ``check`` looks at: a kernel that writes outside
+        the page or slot it was given is then found where it happened."""
         if page_size <= 0:
             raise ValueError(f"page_size {page_size}")
         self.page_size, self.n_slots, self.dtype = page_size, n_slots, dtype
@@ -85,6 +91,8 @@ class CacheManager:
         self.max_context = max_context
         self.max_blocks = -(-max_context // page_size)
         self.entry_needs = entry_needs
+        self.guard = bool(guard)
+        self._guards: list[torch.Tensor] = []
         self.groups: list[_Group] = []
         self._group_of: dict[tuple[int, int], int] = {}
         self._pages: dict[tuple[int, int], tuple[torch.Tensor, torch.Tensor]] = {}
@@ -103,9 +111,9 @@ class CacheManager:
                     g = by_window[need.window]
                     self.groups[g].entries.append((e, k))
                     self._group_of[(e, k)] = g
-                    shape = (self.groups[g].pool.size, need.kv_heads, page_size, need.head_dim)
-                    self._pages[(e, k)] = (torch.zeros(shape, dtype=dtype, device=self.device),
-                                           torch.zeros(shape, dtype=dtype, device=self.device))
+                    shape = (self.groups[g].pool.size, need.kv_heads, page_size)
+                    self._pages[(e, k)] = (self._page_tensor(shape + (need.head_dim,), dtype),
+                                           self._page_tensor(shape + (need.value_dim,), dtype))
                 elif isinstance(need, SlotState):
                     nbytes = int(torch.tensor([], dtype=need.dtype).element_size())
                     for s in need.shape:
@@ -117,19 +125,43 @@ class CacheManager:
                     raise TypeError(f"entry {e} asks for a cache of unknown kind {need!r}")
         self.slot_bytes = -(-slot_bytes // 16) * 16
         self.slots = IdPool(n_slots if self.slot_bytes else 0, "slot")
-        self._slot_mem = torch.zeros((n_slots, self.slot_bytes), dtype=torch.uint8, device=self.device) \
-            if self.slot_bytes else None
+        self._slot_mem = None
+        if self.slot_bytes and not self.guard:
+            self._slot_mem = torch.zeros((n_slots, self.slot_bytes), dtype=torch.uint8, device=self.device)
+        elif self.slot_bytes:
+            whole = torch.full((n_slots + 2, self.slot_bytes + 16), self.GUARD_BYTE, dtype=torch.uint8, device=self.device)
+            self._slot_mem = whole[1:-1, :self.slot_bytes]
+            self._slot_mem.zero_()
+            self._guards += [whole[0], whole[-1], whole[1:-1, self.slot_bytes:]]
         self._slot_views: dict[tuple[int, int], torch.Tensor] = {}
         for key, (start, nbytes, need) in self._slot_ranges.items():
             flat = self._slot_mem[:, start:start + nbytes].view(need.dtype)
             self._slot_views[key] = flat.unflatten(1, tuple(need.shape))
         self.live: dict[object, RequestCache] = {}
 
+    def _page_tensor(self, shape, dtype) -> torch.Tensor:
+        """A zeroed page tensor; with guards, the inner pages of a tensor that is two pages longer."""
+        if not self.guard:
+            return torch.zeros(shape, dtype=dtype, device=self.device)
+        whole = torch.zeros((shape[0] + 2,) + tuple(shape[1:]), dtype=dtype, device=self.device)
+        for edge in (whole[0], whole[-1]):
+            edge.view(torch.uint8).fill_(self.GUARD_BYTE)
+            self._guards.append(edge.view(torch.uint8))
+        return whole[1:-1]
+
+    def check_guards(self) -> None:
+        """Raise if anything wrote into the guard pages, guard slots or the bytes behind a slot."""
+        for i, g in enumerate(self._guards):
+            if not bool((g == self.GUARD_BYTE).all()):
+                bad = int((g != self.GUARD_BYTE).sum())
+                raise PoolError(f"guard region {i} of the cache was written to ({bad} bytes changed): a kernel wrote "
+                                "outside the page or slot it was given")
+
     # -- sizes ---------------------------------------------------------------
     def kv_bytes_per_token(self) -> int:
         total = 0
-        for (e, k), (kp, _) in self._pages.items():
-            total += 2 * kp.shape[1] * kp.shape[3] * kp.element_size()
+        for (e, k), (kp, vp) in self._pages.items():
+            total += kp.shape[1] * (kp.shape[3] + vp.shape[3]) * kp.element_size()
         return total
 
     def pages_needed(self, length: int) -> int:
@@ -255,6 +287,8 @@ class CacheManager:
         held = [rc.slot for rc in self.live.values() if rc.slot is not None]
         if len(held) != len(set(held)) or len(held) != self.slots.n_used:
             raise PoolError("slots held by requests and slots out of the pool differ")
+        if self.guard:
+            self.check_guards()
 
     # -- views for one step --------------------------------------------------
     def fill_block_tables(self, rcs: list, out) -> None:

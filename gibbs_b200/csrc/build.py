@@ -27,14 +27,14 @@ HERE = Path(__file__).resolve().parent
 # and calls into the other two.
 LIBRARIES = {
     "core": ["errors.cu", "elementwise.cu", "gemm_simt.cu", "conv.cu", "attention.cu", "sampling.cu"],
-    "tensorcore": ["errors.cu", "gemm_tc.cu", "attention_tc.cu", "attention_tcgen05.cu"],
+    "tensorcore": ["errors.cu", "gemm_tc.cu", "gemm_tc_decode.cu", "attention_tc.cu", "attention_tcgen05.cu"],
     "runtime": ["errors.cu", "step_plan.cu"],
 }
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",
-]
+] + os.environ.get("GIBBS_B200_NVCC_FLAGS", "").split()      # e.g. -DGB_DECODE_TRACE for a build that stamps times
 
 
 class BuildError(RuntimeError):

@@ -2,9 +2,9 @@
 // mbarrier, TMA (cp.async.bulk.tensor), tcgen05 (alloc, mma, commit, ld) and
 // the shared-memory / instruction descriptors of tcgen05.mma.
 //
-// Every wait is bounded: gb_mbar_wait gives up after a fixed number of
-// polls and reports it, so that a kernel can record the failure, release what
-// it holds and return instead of hanging the GPU.
+// Every wait is bounded: mbar_wait gives up after a fixed time and reports
+// it, so that a kernel can record the failure, release what it holds and
+// return instead of hanging the GPU.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -35,22 +35,32 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One poll: true if the phase of the given parity has completed.  The thread may be suspended
+// until then, for about a microsecond at most (the instruction's time hint; without one the limit
+// is system-defined and was found to be far too long for a wait that is meant to give up).
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
+  const uint32_t hint_ns = 1000;
   asm volatile(
-      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}\n"
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.b32 %0, 1, 0, p;\n\t}\n"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
       : "memory");
   return ok != 0;
 }
-// Waits for the phase of the given parity; false if it did not complete within
-// the poll limit (each poll itself blocks for a hardware-defined time slice).
-constexpr uint32_t MBAR_POLL_LIMIT = 1u << 22;
+// Waits for the phase of the given parity; false if it did not complete within about
+// LIMIT_US microseconds (measured on the SM's cycle counter at a nominal 2 GHz, so a lower
+// clock makes the limit longer, never shorter).  Two seconds by default: thousands of times
+// what any wait of these kernels takes when all is well.
+constexpr uint32_t MBAR_WAIT_LIMIT_US = 2000000;
+template <uint32_t LIMIT_US = MBAR_WAIT_LIMIT_US>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < MBAR_POLL_LIMIT; ++i)
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
-  return false;
+    if (clock64() - t0 > (long long)LIMIT_US * 2000) return false;
+  }
 }
 
 // ---------------------------------------------------------------- TMA

@@ -13,10 +13,18 @@
 //
 // The kernels live in the other libraries; their entry points are handed over once as a table of
 // function pointers (gb_plan_bind), so this file launches nothing by itself and knows no model.
+//
+// Operations beyond the built-in ones are registered by name at run time (gb_plan_register_op): a
+// part that brings kernels of its own hands over one C function per operation, gets an id back,
+// and emits records with that id; the walker calls the function with the record's operands
+// (symbols already replaced by the step's values) and the stream.  Nothing here is edited for it.
 #include <stdlib.h>
 #include <string.h>
 
+#include <vector>
+
 #include "common.cuh"
+#include "gb_plan_op.h"
 
 namespace {
 
@@ -49,20 +57,36 @@ typedef int (*AttentionTcgen05Fn)(const void*, long long, const void*, const voi
                                   int, int*, cudaStream_t);
 typedef int (*AttentionTcgen05SupportedFn)(int, int, int, int, long long, long long);
 typedef int (*SwigluFn)(const void*, void*, int, int, int, cudaStream_t);
+typedef int (*LinearDecodeFn)(const void*, long long, int, const float*, float, const int*, const float*, int,
+                              long long, const void*, long long, const float*, void*, int, long long, int, int, int,
+                              float*, long long, int, int*, cudaStream_t);
+typedef int (*LinearDecodePartsFn)(int, int);
+typedef int (*LinearDecodeSupportedFn)(int, const void*, long long, int);
+typedef int (*LinearDecodeNormedOkFn)(int, int, int);
+typedef int (*AddPendingFn)(float*, long long, const float*, int, const float*, long long, int, cudaStream_t);
 
 enum Fn : int { F_EMBED = 0, F_RMSNORM, F_LINEAR_SIMT, F_LINEAR_TC, F_LINEAR_TC_SPLITS, F_SHORT_CONV,
                 F_SHORT_CONV_PARTIALS, F_QKROPE, F_QKROPE_PARTIALS, F_PAGED_ATTENTION, F_ATTENTION_TC,
-                F_ATTENTION_TCGEN05, F_ATTENTION_TCGEN05_SUPPORTED, F_SWIGLU, F_COUNT };
+                F_ATTENTION_TCGEN05, F_ATTENTION_TCGEN05_SUPPORTED, F_SWIGLU, F_LINEAR_DECODE, F_LINEAR_DECODE_PARTS,
+                F_LINEAR_DECODE_SUPPORTED, F_ADD_PENDING, F_LINEAR_DECODE_NORMED_OK, F_COUNT };
 // which library an entry point belongs to (0: core, 1: tensor cores), for the caller to fetch the message
-const int FN_LIB[F_COUNT] = {0, 0, 0, 1, 1, 0, 0, 0, 0, 0, 1, 1, 1, 0};
+const int FN_LIB[F_COUNT] = {0, 0, 0, 1, 1, 0, 0, 0, 0, 0, 1, 1, 1, 0, 1, 1, 1, 0, 1};
 void* g_fn[F_COUNT];
 
 enum Op : int { P_EMBED = 1, P_RMSNORM = 2, P_LINEAR = 3, P_SHORT_CONV = 4, P_QKROPE = 5, P_ATTENTION = 6, P_SWIGLU = 7 };
-enum Sym : int { S_N = 0, S_R, S_W, S_MAXQ, S_MAXCTX, S_ONE_EACH, S_TOKEN_IDS, S_TOK_REQ, S_TOK_POS, S_Q_START, S_Q_LEN,
-                 S_START_POS, S_CTX_LEN, S_SLOT_IDS, S_WANT_ROWS, S_LOGITS, S_BLOCK_TABLE0, S_COUNT = 32 };
+// the step's symbols (gb_plan_op.h gives their meaning), under the short names used below
+enum Sym : int { S_N = GB_SYM_TOKENS, S_R = GB_SYM_REQUESTS, S_W = GB_SYM_WANTED, S_MAXQ = GB_SYM_MAX_PORTION,
+                 S_MAXCTX = GB_SYM_MAX_CONTEXT, S_ONE_EACH = GB_SYM_ONE_EACH, S_TOKEN_IDS = GB_SYM_TOKEN_IDS,
+                 S_TOK_REQ = GB_SYM_TOKEN_REQUEST, S_TOK_POS = GB_SYM_TOKEN_POSITION, S_Q_START = GB_SYM_PORTION_START,
+                 S_Q_LEN = GB_SYM_PORTION_LENGTH, S_START_POS = GB_SYM_LENGTH_BEFORE, S_CTX_LEN = GB_SYM_LENGTH_AFTER,
+                 S_SLOT_IDS = GB_SYM_SLOT_IDS, S_WANT_ROWS = GB_SYM_WANTED_ROWS, S_LOGITS = GB_SYM_LOGITS,
+                 S_BLOCK_TABLE0 = GB_SYM_BLOCK_TABLE0, S_COUNT = GB_SYM_COUNT };
 constexpr long long SYM_BIT = 1ll << 62;
 
-enum LinearFlag : int { LF_RESIDUAL = 1, LF_PARTIALS_IF_ONE_EACH = 2, LF_PARTIALS = 4 };
+enum LinearFlag : int { LF_RESIDUAL = 1, LF_PARTIALS_IF_ONE_EACH = 2, LF_PARTIALS = 4, LF_NORMED = 8 };
+enum NormFlag : int { NF_LAZY = 1 };      // the product after it may run the norm itself (up to 64 rows)
+constexpr int FIRST_REGISTERED_OP = 64;
+constexpr int MAX_REGISTERED_OPS = 64;
 
 struct PlanOp {              // 224 bytes; the meaning of a[] per operation is given where it is executed
   int op;
@@ -86,6 +110,12 @@ struct Walk {
   int pend_splits; const float* pend_bias;     // partial sums to be added to the residual by the next norm
   int part_splits; const float* part_bias;     // partial tiles of a product whose consumer adds them itself
   const void* q; long long ldq;                // where the rotated queries lie
+  // products of decode size (csrc/gemm_tc_decode.cu)
+  float* residual; long long residual_ld;      // the stream itself (for operations that need it whole)
+  int decode_products;                         // products of up to this many rows run on the decode kernel (0: none)
+  float* ssq;                                  // partial sums of squares of the stream's rows [parts][N]
+  int ssq_parts;                               // > 0: ssq describes the stream as it stands
+  const struct PlanOp* lazy_norm;              // a norm that was not launched: the next product runs it
   int launches;
   int failed_lib;
 };
@@ -117,22 +147,31 @@ int attention_splits(const Walk& w, int n_requests, int kv_heads, int max_ctx_le
   return s < 1 ? 1 : s;
 }
 
-int run_op(Walk& w, const PlanOp& o) {
+int run_registered(Walk& w, const PlanOp& o);
+
+int run_op(Walk& w, const PlanOp& o, bool force = false) {
   const long long* a = o.a;
   const int N = (int)w.sym[S_N], R = (int)w.sym[S_R], W = (int)w.sym[S_W];
   const int one_each = (int)w.sym[S_ONE_EACH];
   switch (o.op) {
     case P_EMBED: {
       // a0 table, a1 its dtype, a2 out (f32 [., dim]), a3 dim, a4 vocabulary
+      w.ssq_parts = 0;
       PLAN_CALL(w, F_EMBED, ((EmbedFn)g_fn[F_EMBED])(ptr<const void>(w, a[0]), (int)a[1], ptr<const int>(w, SYM_BIT | S_TOKEN_IDS),
                                                       ptr<float>(w, a[2]), N, (int)a[3], (int)a[4], w.stream));
       return 0;
     }
     case P_RMSNORM: {
-      // a0 x (f32), a1 its row stride, a2 gain, a3 out, a4 out dtype, a5 gather the wanted rows (0/1), a6 dim; f0 eps
+      // a0 x (f32), a1 its row stride, a2 gain, a3 out, a4 out dtype, a5 gather the wanted rows (0/1), a6 dim,
+      // a7, a8 (with NF_LAZY) n and k of the product that reads the rows; f0 eps
       const bool gather = a[5] != 0;
       const int n_rows = gather ? W : N;
       if (n_rows <= 0) return 0;                               // (a step that wants no logits)
+      if ((o.flags & NF_LAZY) && !force && n_rows <= w.decode_products && w.pend_splits == 0 && a[4] == GB_BF16 &&
+          ((LinearDecodeNormedOkFn)g_fn[F_LINEAR_DECODE_NORMED_OK])(n_rows, (int)a[7], (int)a[8])) {
+        w.lazy_norm = &o;                                      // the product that reads these rows normalises them
+        return 0;
+      }
       const float* pend = w.pend_splits > 0 ? w.ws : nullptr;
       PLAN_CALL(w, F_RMSNORM, ((RmsnormFn)g_fn[F_RMSNORM])(
           ptr<float>(w, a[0]), a[1], ptr<const float>(w, a[2]), ptr<void>(w, a[3]), (int)a[4],
@@ -148,6 +187,44 @@ int run_op(Walk& w, const PlanOp& o) {
       const int M = (int)val(w, a[7]);
       if (M <= 0) return 0;
       const float* bias = ptr<const float>(w, a[4]);
+      const PlanOp* lazy = (o.flags & LF_NORMED) ? w.lazy_norm : nullptr;
+      w.lazy_norm = nullptr;
+      if (a[10] == 0 && M <= w.decode_products &&
+          ((LinearDecodeSupportedFn)g_fn[F_LINEAR_DECODE_SUPPORTED])(M, ptr<const void>(w, a[2]), a[3], (int)a[9])) {
+        // up to 64 rows: K is split inside a cluster, and a norm that was left out runs inside the product
+        const int n = (int)a[8], k = (int)a[9];
+        const bool residual = (o.flags & LF_RESIDUAL) != 0;
+        const void* x = ptr<const void>(w, a[0]);
+        long long ldx = a[1];
+        const float* gain = nullptr;
+        const int* rows = nullptr;
+        float eps = 0.f;
+        if (lazy) {
+          x = ptr<const void>(w, lazy->a[0]);
+          ldx = lazy->a[1];
+          gain = ptr<const float>(w, lazy->a[2]);
+          eps = (float)lazy->f[0];
+          rows = lazy->a[5] != 0 ? ptr<const int>(w, SYM_BIT | S_WANT_ROWS) : nullptr;
+        }
+        const int parts = residual ? ((LinearDecodePartsFn)g_fn[F_LINEAR_DECODE_PARTS])(n, k) : 0;
+        PLAN_CALL(w, F_LINEAR_DECODE, ((LinearDecodeFn)g_fn[F_LINEAR_DECODE])(
+            x, ldx, lazy ? 1 : 0, gain, eps, rows, (lazy && w.ssq_parts > 0) ? w.ssq : nullptr, w.ssq_parts,
+            (long long)N, ptr<const void>(w, a[2]), a[3], bias, ptr<void>(w, a[5]), (int)a[11], a[6], M, n, k,
+            residual ? w.ssq : nullptr, (long long)N, w.tc_flags, w.status, w.stream));
+        if (residual) {
+          w.pend_splits = 0;
+          w.ssq_parts = parts;
+        } else {
+          w.part_splits = 0;
+        }
+        return 0;
+      }
+      if (lazy) {
+        // the product cannot take the norm in: run it after all
+        const int rc = run_op(w, *lazy, true);
+        if (rc < 0) return rc;
+      }
+      if (o.flags & LF_RESIDUAL) w.ssq_parts = 0;
       if (a[10] == 0) {
         const int n = (int)a[8], k = (int)a[9];
         const int splits = ((LinearTcSplitsFn)g_fn[F_LINEAR_TC_SPLITS])(M, n, k);
@@ -261,12 +338,83 @@ int run_op(Walk& w, const PlanOp& o) {
       return 0;
     }
   }
+  if (o.op >= FIRST_REGISTERED_OP) return run_registered(w, o);
   snprintf(gb_error_buffer(), 512, "gb_plan_run: unknown operation %d", o.op);
   w.failed_lib = 2;
   return GB_ERR_ARG;
 }
 
+// ---- operations registered from outside ----
+struct Registered {
+  char name[64];
+  GbPlanOpFn fn;
+};
+Registered g_registered[MAX_REGISTERED_OPS];
+int g_n_registered = 0;
+
+int run_registered(Walk& w, const PlanOp& o) {
+  const int i = o.op - FIRST_REGISTERED_OP;
+  if (i < 0 || i >= g_n_registered) {
+    snprintf(gb_error_buffer(), 512, "gb_plan_run: operation %d is not registered", o.op);
+    w.failed_lib = 2;
+    return GB_ERR_ARG;
+  }
+  // such an operation sees the stream whole: what a product left to be added is added first, and
+  // what this file remembers about the stream no longer holds afterwards
+  if (w.pend_splits > 0) {
+    const int N = (int)w.sym[S_N];
+    PLAN_CALL(w, F_ADD_PENDING, ((AddPendingFn)g_fn[F_ADD_PENDING])(
+        w.residual, w.residual_ld, w.ws, w.pend_splits, w.pend_bias, (long long)N, (int)w.residual_ld, w.stream));
+    w.pend_splits = 0;
+  }
+  w.ssq_parts = 0;
+  w.lazy_norm = nullptr;
+  w.part_splits = 0;
+  long long a[24];
+  for (int j = 0; j < 24; ++j) a[j] = val(w, o.a[j]);
+  GbPlanCtx ctx;
+  ctx.stream = w.stream;
+  ctx.status = w.status;
+  ctx.sym = w.sym;
+  ctx.n_sym = S_COUNT;
+  const int rc = g_registered[i].fn(&ctx, a, o.f, o.flags);
+  if (rc < 0) {
+    snprintf(gb_error_buffer(), 512, "gb_plan_run: the registered operation '%s' failed with code %d",
+             g_registered[i].name, rc);
+    w.failed_lib = 2;
+    return rc;
+  }
+  w.launches += rc;
+  return 0;
+}
+
 }  // namespace
+
+// Register an operation under a name; returns its id (the same id when the name is registered
+// again, with the new function), or a negative error code.  The function gets the record's
+// operands with symbols replaced by the step's values and returns the number of kernels it
+// launched (on ctx->stream), or a negative code.
+GB_API int gb_plan_register_op(const char* name, GbPlanOpFn fn) {
+  if (name == nullptr || fn == nullptr || strlen(name) == 0 || strlen(name) >= sizeof(g_registered[0].name))
+    GB_FAIL(GB_ERR_ARG, "gb_plan_register_op: a name of 1 to 63 characters and a function are needed");
+  for (int i = 0; i < g_n_registered; ++i)
+    if (strcmp(g_registered[i].name, name) == 0) {
+      g_registered[i].fn = fn;
+      return FIRST_REGISTERED_OP + i;
+    }
+  if (g_n_registered == MAX_REGISTERED_OPS)
+    GB_FAIL(GB_ERR_ARG, "gb_plan_register_op: all %d places are taken", MAX_REGISTERED_OPS);
+  strcpy(g_registered[g_n_registered].name, name);
+  g_registered[g_n_registered].fn = fn;
+  return FIRST_REGISTERED_OP + g_n_registered++;
+}
+
+// The id of a registered operation, or -1.
+GB_API int gb_plan_op_id(const char* name) {
+  for (int i = 0; i < g_n_registered; ++i)
+    if (strcmp(g_registered[i].name, name) == 0) return FIRST_REGISTERED_OP + i;
+  return -1;
+}
 
 // The table of entry points, in the order of the enumeration above (null where a library is not loaded).
 GB_API int gb_plan_bind(void* const* fns, int n) {
@@ -283,6 +431,12 @@ struct GbPlanRun {
   float* ws; float* attn_ws; int* status;
   int attn_ctas, tc_flags, use_tcgen05, defer_whole_rows;
   int failed_lib;            // out: 0 core, 1 tensor cores, 2 this library (where the message of a failure lies)
+  float* ssq; int decode_products;
+  float* residual; long long residual_ld;
+  // timing != 0: every operation is bracketed by CUDA events (which also keeps operations from
+  // overlapping) and its time is added to label_ms[a[23]] of its record; for measurements only
+  int timing; int n_labels;
+  float* label_ms; int* label_count;
 };
 
 // Launches the kernels of one step.  Returns the number of kernels launched, or a negative error code.
@@ -293,14 +447,42 @@ GB_API int gb_plan_run(GbPlanRun* r, cudaStream_t stream) {
   w.sym = r->sym; w.stream = stream; w.status = r->status; w.ws = r->ws; w.attn_ws = r->attn_ws;
   w.attn_ctas = r->attn_ctas; w.tc_flags = r->tc_flags; w.use_tcgen05 = r->use_tcgen05;
   w.defer_whole_rows = r->defer_whole_rows;
+  w.ssq = r->ssq; w.decode_products = g_fn[F_LINEAR_DECODE] != nullptr ? r->decode_products : 0;
+  w.residual = r->residual; w.residual_ld = r->residual_ld;
   w.failed_lib = 2;
   const PlanOp* ops = (const PlanOp*)r->ops;
+  static std::vector<cudaEvent_t> events;      // timing mode: two per operation, made once
+  if (r->timing) {
+    while ((int)events.size() < 2 * r->n_ops) {
+      cudaEvent_t e;
+      GB_CUDA(cudaEventCreate(&e));
+      events.push_back(e);
+    }
+  }
   for (int i = 0; i < r->n_ops; ++i) {
+    if (r->timing) GB_CUDA(cudaEventRecord(events[2 * i], stream));
     const int rc = run_op(w, ops[i]);
     if (rc < 0) {
       r->failed_lib = w.failed_lib;
       return rc;
     }
+    if (r->timing) GB_CUDA(cudaEventRecord(events[2 * i + 1], stream));
+  }
+  if (r->timing) {
+    GB_CUDA(cudaStreamSynchronize(stream));
+    for (int i = 0; i < r->n_ops; ++i) {
+      const long long label = ops[i].a[23];
+      float ms = 0.f;
+      if (label >= 0 && label < r->n_labels && cudaEventElapsedTime(&ms, events[2 * i], events[2 * i + 1]) == cudaSuccess) {
+        r->label_ms[label] += ms;
+        r->label_count[label] += 1;
+      }
+    }
+  }
+  if (w.lazy_norm != nullptr) {
+    snprintf(gb_error_buffer(), 512, "gb_plan_run: a norm was left to a product that never came");
+    r->failed_lib = 2;
+    return GB_ERR_ARG;
   }
   return w.launches;
 }

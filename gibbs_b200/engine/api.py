@@ -22,6 +22,9 @@ from .scheduler import MAX_PREFILL_CHUNK, Scheduler
 from .step import Engine
 
 
+DEFAULT_MAX_CONTEXT = 4096
+
+
 def pages_for(model: CausalLM, page_size: int, max_running: int, ctx: int, memory_fraction: float = 0.8) -> int:
     """Pages to allocate per group: enough for ``max_running`` requests of
     ``ctx`` tokens, or what ``memory_fraction`` of the free device memory
@@ -31,7 +34,8 @@ def pages_for(model: CausalLM, page_size: int, max_running: int, ctx: int, memor
         if reads is None:
             for need in needs:
                 if hasattr(need, "kv_heads"):
-                    per_token += 2 * need.kv_heads * need.head_dim * (2 if model.rt.dtype == torch.bfloat16 else 4)
+                    per_token += need.kv_heads * (need.head_dim + need.value_dim) \
+                        * (2 if model.rt.dtype == torch.bfloat16 else 4)
     want = max_running * -(-ctx // page_size)
     if per_token == 0:
         return 1
@@ -46,7 +50,10 @@ class Generator:
                  max_running: int = 64, max_batch_tokens: int = MAX_PREFILL_CHUNK, seed: int = 0,
                  arch: Optional[str] = None):
         self.model = model if isinstance(model, CausalLM) else load_model(model, dtype=dtype, device=device, arch=arch)
-        ctx = int(ctx or self.model.plan.max_context)
+        # as the reference: the context is max_position_embeddings, at most 4096, unless it is given
+        # (MisterTK/gibbs arch/families/lfm2.json5:51); a checkpoint that allows 128k positions would
+        # otherwise size every step's block tables, and the pools, for 128k
+        ctx = int(ctx or min(self.model.plan.max_context, DEFAULT_MAX_CONTEXT))
         if n_pages is None:
             n_pages = pages_for(self.model, page_size, max_running, ctx)
         self.engine = Engine(self.model, n_pages=n_pages, page_size=page_size, max_requests=max_running,

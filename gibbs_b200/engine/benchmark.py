@@ -28,12 +28,16 @@ from .step import Engine, StepEntry
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
-def load_peaks(repo_root) -> dict:
-    """Measured copy bandwidth (GB/s) and bf16 matrix throughput (TFLOP/s) of
-    this pool's GPUs if a ``MEASURED_PEAKS.json`` lies at the repository root,
-    else the stated fallback figures."""
-    p = Path(repo_root) / "MEASURED_PEAKS.json"
-    if p.exists():
+def load_peaks(path=None) -> dict:
+    """Copy bandwidth (GB/s) and bf16 matrix throughput (TFLOP/s) to relate
+    measurements to: from the JSON file ``path`` (keys ``hbm_gbs``,
+    ``bf16_tflops``, optionally ``bf16_tflops_sustained``; a folder stands for
+    its ``MEASURED_PEAKS.json``) when it exists, else the stated fallback
+    figures."""
+    p = Path(path) if path is not None else None
+    if p is not None and p.is_dir():
+        p = p / "MEASURED_PEAKS.json"
+    if p is not None and p.exists():
         try:
             d = json.loads(p.read_text())
             out = {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
@@ -165,13 +169,16 @@ def fill_contexts(engine: Engine, batch: int, prompt_len: int, seed: int, chunk:
     return first
 
 
-def measure_decode(engine: Engine, batch: int, prompt_len: int, steps: int, warmup: int, seed: int = 0) -> dict:
+def measure_decode(engine: Engine, batch: int, prompt_len: int, steps: int, warmup: int, seed: int = 0,
+                   repeats: int = 1) -> dict:
     """``steps`` decode steps of ``batch`` requests whose contexts start at
     ``prompt_len``: every step feeds each request the token the step before
     picked for it (the ids stay on the device, as in the scheduler's
     overlapped loop), takes the logits and picks the next token greedily on
     the device.  The host copies each step's metadata and launches; it waits
-    for nothing inside the timed region."""
+    for nothing inside the timed region.  The region of ``steps`` steps is
+    timed ``repeats`` times back to back; the figures are those of the median
+    region, ``spread`` is (slowest - fastest) / median."""
     first = fill_contexts(engine, batch, prompt_len, seed)
     sampler = Sampler(engine.device)
     greedy = [SamplingParams(temperature=0.0)] * batch
@@ -186,58 +193,71 @@ def measure_decode(engine: Engine, batch: int, prompt_len: int, steps: int, warm
 
     for _ in range(warmup):
         tokens = one_step(tokens)
-    launches0 = ops.launch_count()
-    torch.cuda.synchronize()
-    a, b = _events()
-    t0 = time.perf_counter()
-    a.record()
-    for _ in range(steps):
-        tokens = one_step(tokens)
-    b.record()
-    torch.cuda.synchronize()
-    wall = time.perf_counter() - t0
-    ms = a.elapsed_time(b)
-    ctx = [engine.length(("bench", r)) for r in range(batch)]
-    bytes_step = engine.model.weight_bytes_per_step() + sum(ctx) * engine.cache.kv_bytes_per_token() \
+    regions = []
+    for _ in range(max(1, repeats)):
+        launches0 = ops.launch_count()
+        torch.cuda.synchronize()
+        a, b = _events()
+        t0 = time.perf_counter()
+        a.record()
+        for _ in range(steps):
+            tokens = one_step(tokens)
+        b.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        ctx = [engine.length(("bench", r)) - steps // 2 for r in range(batch)]      # mid-region contexts
+        regions.append((a.elapsed_time(b), wall, ctx, ops.launch_count() - launches0))
+    regions.sort(key=lambda r: r[0])
+    ms, wall, ctx, launches = regions[len(regions) // 2]
+    spread = (regions[-1][0] - regions[0][0]) / ms
+    bytes_step = engine.model.weight_bytes_per_step(batch) + sum(ctx) * engine.cache.kv_bytes_per_token() \
         + batch * engine.cache.slot_bytes
     for r in range(batch):
         engine.close(("bench", r))
     return {"batch": batch, "steps": steps, "ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3),
             "wall_ms_per_step": wall * 1e3 / steps, "bytes_per_step": bytes_step,
-            "gbs": bytes_step / (ms / steps / 1e3) / 1e9, "launches": ops.launch_count() - launches0,
-            "context": int(statistics.mean(ctx))}
+            "gbs": bytes_step / (ms / steps / 1e3) / 1e9, "launches": launches,
+            "context": int(statistics.mean(ctx)), "repeats": len(regions), "spread": spread}
 
 
-def measure_decode_e2e(generator, batch: int, prompt_len: int, steps: int, warmup: int, seed: int = 0) -> dict:
+def measure_decode_e2e(generator, batch: int, prompt_len: int, steps: int, warmup: int, seed: int = 0,
+                       repeats: int = 1) -> dict:
     """The same through the public entry point's scheduler: prompts come from host
     lists, every step copies its metadata (positions, block tables, places of the fed
     ids) from pinned host memory and the picked ids go back to pinned host memory, from
     where they are emitted; a decode step is launched on the ids the device picked one
-    step before the host reads them."""
+    step before the host reads them.  ``repeats`` regions of ``steps`` steps are timed back
+    to back; the figures are the median region's, ``spread`` is (slowest - fastest) / median."""
     rng = np.random.default_rng(seed)
     sched: Scheduler = generator.scheduler(stop_at_eos=False)
+    repeats = max(1, repeats)
     # prompts finish at different steps: leave room so that nobody reaches max_new_tokens while timed
-    params = SamplingParams(temperature=0.0, max_new_tokens=warmup + steps + 4 * batch + 16)
+    params = SamplingParams(temperature=0.0, max_new_tokens=warmup + repeats * steps + 4 * batch + 16)
     for _ in range(batch):
         sched.submit(rng.integers(0, generator.engine.vocab_size, prompt_len).tolist(), params)
     while any(not s.output for s in sched.sequences.values()):
         sched.step()
     for _ in range(warmup):
         sched.step()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    n = 0
-    for _ in range(steps):
-        n += sched.step().tokens_generated
-    torch.cuda.synchronize()
-    dt = time.perf_counter() - t0
+    regions = []
+    for _ in range(repeats):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        n = 0
+        for _ in range(steps):
+            n += sched.step().tokens_generated
+        torch.cuda.synchronize()
+        regions.append((time.perf_counter() - t0, n))
+    regions.sort(key=lambda r: r[0] / max(r[1], 1))
+    dt, n = regions[len(regions) // 2]
+    spread = (regions[-1][0] - regions[0][0]) / dt
     for sid in list(sched.sequences):
         sched.cancel(sid)
     sched.step()
     meta_ints = 4 * 4 * ((batch + 3) // 4) + 6 * 4 * ((batch + 3) // 4) \
         + len(generator.engine.cache.groups) * batch * generator.engine.cache.max_blocks
     return {"value": n / dt, "unit": "tokens/s", "h2d_bytes_per_step": 4 * meta_ints, "d2h_bytes_per_step": 4 * batch,
-            "ms_per_step": dt * 1e3 / steps}
+            "ms_per_step": dt * 1e3 / steps, "repeats": repeats, "spread": spread}
 
 
 def measure_serving(generator, n_requests: int, min_len: int, max_len: int, new_tokens: int, temperature: float,

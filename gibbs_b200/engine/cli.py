@@ -26,7 +26,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--prompt", help="prompt text (needs tokenizer.json in the model folder)")
     ap.add_argument("--prompt-ids", help="prompt as comma-separated token ids")
     ap.add_argument("--max-tokens", type=int, default=None, help="most tokens to generate (default 64)")
-    ap.add_argument("--ctx", type=int, default=None, help="context length (default: the model's)")
+    ap.add_argument("--ctx", type=int, default=None,
+                    help="context length (default: the model's max_position_embeddings, at most 4096)")
     ap.add_argument("--temperature", type=float, default=None, help="default 0.7 for --prompt; <= 0 is greedy")
     ap.add_argument("--top-p", type=float, default=None, help="default 0.9")
     ap.add_argument("--top-k", type=int, default=50, help="1..64, default 50")
@@ -41,6 +42,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--random", help="config.json to make random weights for (with --save)")
     ap.add_argument("--save", help="folder to write the random-weights model to")
     ap.add_argument("--device", default="cuda:0")
+    ap.add_argument("--peaks", help="JSON file with the memory bandwidth (hbm_gbs) and bf16 throughput (bf16_tflops) "
+                                    "that roofline figures are related to (default: built-in figures for a B200)")
     return ap
 
 
@@ -82,8 +85,7 @@ def bench_suite(path: Path, a) -> int:
     from .api import Generator
     suite = json.loads(path.read_text())
     defaults = suite.get("defaults") or {}
-    root = Path(__file__).resolve().parents[2]
-    peaks = B.load_peaks(root)
+    peaks = B.load_peaks(a.peaks)
     for m in suite["models"]:
         folder = Path(m["id"]) if Path(m["id"]).is_absolute() else path.parent / m["id"]
         decode_tokens = int(m.get("decode_tokens", defaults.get("decode_tokens", 128)))
@@ -142,8 +144,10 @@ def main(argv=None) -> int:
         gen.engine.open("probe")
         logits = gen.engine.step([StepEntry("probe", ids, [len(ids) - 1])])[0]
         gen.engine.close("probe")
-        top = logits.topk(5)
-        print(json.dumps({"ids": top.indices.tolist(), "logits": [round(v, 6) for v in top.values.tolist()]}))
+        row = logits.cpu().numpy()                  # the row goes to the host and is sorted there
+        import numpy as np
+        top = np.lexsort((np.arange(row.size), -row.astype(np.float64)))[:5]      # logit descending, id ascending
+        print(json.dumps({"ids": [int(i) for i in top], "logits": [round(float(row[i]), 6) for i in top]}))
         return 0
     tok = None
     if a.prompt_ids:
@@ -177,7 +181,7 @@ def main(argv=None) -> int:
     tok_s = passes / max(t2 - t1, 1e-9)
     print(f"Decode: {passes} tokens in {(t2 - t1) * 1e3:.2f}ms ({tok_s:.1f} tok/s) on {torch.cuda.get_device_name()}")
     from . import benchmark as B
-    peaks = B.load_peaks(Path(__file__).resolve().parents[2])
+    peaks = B.load_peaks(a.peaks)
     bytes_per_token = gen.model.weight_bytes_per_step() \
         + (len(prompt) + len(seq.output)) * gen.engine.cache.kv_bytes_per_token() + gen.engine.cache.slot_bytes
     roof = peaks["hbm_gbs"] / (bytes_per_token / 1e9)

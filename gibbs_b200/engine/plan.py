@@ -30,7 +30,8 @@ from ..parts.base import NotPlannable
 OP = np.dtype([("op", "<i4"), ("flags", "<i4"), ("a", "<i8", (24,)), ("f", "<f8", (3,))])
 
 P_EMBED, P_RMSNORM, P_LINEAR, P_SHORT_CONV, P_QKROPE, P_ATTENTION, P_SWIGLU = range(1, 8)
-LF_RESIDUAL, LF_PARTIALS_IF_ONE_EACH, LF_PARTIALS = 1, 2, 4
+LF_RESIDUAL, LF_PARTIALS_IF_ONE_EACH, LF_PARTIALS, LF_NORMED = 1, 2, 4, 8
+NF_LAZY = 1
 
 SYM_BIT = 1 << 62
 (S_N, S_R, S_W, S_MAXQ, S_MAXCTX, S_ONE_EACH, S_TOKEN_IDS, S_TOK_REQ, S_TOK_POS, S_Q_START, S_Q_LEN, S_START_POS,
@@ -46,7 +47,24 @@ _FUNCTIONS = [("core", "gb_embed"), ("core", "gb_rmsnorm"), ("core", "gb_linear_
               ("tensorcore", "gb_linear_tc_splits"), ("core", "gb_short_conv"), ("core", "gb_short_conv_partials"),
               ("core", "gb_qk_norm_rope_store"), ("core", "gb_qk_norm_rope_store_partials"),
               ("core", "gb_paged_attention"), ("tensorcore", "gb_attention_tc"), ("tensorcore", "gb_attention_tcgen05"),
-              ("tensorcore", "gb_attention_tcgen05_supported"), ("core", "gb_swiglu")]
+              ("tensorcore", "gb_attention_tcgen05_supported"), ("core", "gb_swiglu"),
+              ("tensorcore", "gb_linear_decode"), ("tensorcore", "gb_linear_decode_parts"),
+              ("tensorcore", "gb_linear_decode_supported"), ("core", "gb_add_pending"),
+              ("tensorcore", "gb_linear_decode_normed_ok")]
+
+
+def register_op(name: str, function) -> int:
+    """Make an operation of a part's own kernel library known to the step walker:
+    ``function`` is a C function ``int f(const GbPlanCtx*, const long long* a, const
+    double* f, int flags)`` (a ctypes function pointer, or its address) that launches the
+    operation's kernels on ``ctx->stream`` and returns how many it launched.  Returns the
+    id to pass to ``PlanBuilder.emit``."""
+    lib = library("runtime")
+    address = function if isinstance(function, int) else ctypes.cast(function, ctypes.c_void_p).value
+    rc = lib.gb_plan_register_op(name.encode(), ctypes.c_void_p(address))
+    if rc < 0:
+        ops.check(lib, rc)
+    return rc
 
 
 class TableRef:
@@ -64,7 +82,10 @@ class _Run(ctypes.Structure):
     _fields_ = [("ops", ctypes.c_void_p), ("n_ops", ctypes.c_int), ("sym", ctypes.c_void_p), ("n_sym", ctypes.c_int),
                 ("ws", ctypes.c_void_p), ("attn_ws", ctypes.c_void_p), ("status", ctypes.c_void_p),
                 ("attn_ctas", ctypes.c_int), ("tc_flags", ctypes.c_int), ("use_tcgen05", ctypes.c_int),
-                ("defer_whole_rows", ctypes.c_int), ("failed_lib", ctypes.c_int)]
+                ("defer_whole_rows", ctypes.c_int), ("failed_lib", ctypes.c_int), ("ssq", ctypes.c_void_p),
+                ("decode_products", ctypes.c_int), ("residual", ctypes.c_void_p), ("residual_ld", ctypes.c_longlong),
+                ("timing", ctypes.c_int), ("n_labels", ctypes.c_int), ("label_ms", ctypes.c_void_p),
+                ("label_count", ctypes.c_void_p)]
 
 
 class PlanBuilder:
@@ -82,6 +103,9 @@ class PlanBuilder:
         self._keep: list = []
         self.ws_floats = 1
         self.attn_ws_floats = 1
+        self.ssq_floats = 1
+        self._lazy = None           # (index of a norm's record, its output buffer): the next product may take it in
+        self.labels: list = []      # names under which the operations' times are added up in timing mode
         self.bt_stride = 0
         self.LOGITS, self.WANTED = sym(S_LOGITS), S_W          # what a head writes to, and how many rows
         self.residual = self.buffer("residual", hidden, torch.float32)
@@ -104,10 +128,19 @@ class PlanBuilder:
         self._keep.append(t)
         return t.data_ptr()
 
-    def emit(self, op: int, a, f=(), flags: int = 0) -> None:
+    def emit(self, op: int, a, f=(), flags: int = 0, label: str = "") -> None:
+        """Append one record: a built-in operation (P_...) or the id ``register_op`` gave.
+        ``label``: the name its time is added up under in timing mode (operand 23 is kept for it)."""
+        self._lazy = None
+        if len(a) > 23:
+            raise NotPlannable("an operation has 23 integer operands")
+        label = label or f"op{op}"
+        if label not in self.labels:
+            self.labels.append(label)
         rec = np.zeros((), dtype=OP)
         rec["op"], rec["flags"] = op, flags
         rec["a"][:len(a)] = a
+        rec["a"][23] = self.labels.index(label)
         rec["f"][:len(f)] = f
         self.ops.append(rec)
 
@@ -116,21 +149,25 @@ class PlanBuilder:
         if not table.is_contiguous() or table.shape[1] != self.hidden:
             raise NotPlannable("the embedding table must be contiguous [vocab, hidden]")
         self.emit(P_EMBED, [self.keep(table), ops.dtype_code(table.dtype), self.residual.data_ptr(), self.hidden,
-                            table.shape[0]])
+                            table.shape[0]], label="embed")
 
-    def rmsnorm(self, gain: torch.Tensor, eps: float, wanted_rows: bool = False) -> torch.Tensor:
+    def rmsnorm(self, gain: torch.Tensor, eps: float, wanted_rows: bool = False, lazy: bool = False) -> torch.Tensor:
         """rmsnorm(residual (+ what the product before left to be added)) * gain; with
-        ``wanted_rows`` only the step's wanted rows, gathered."""
+        ``wanted_rows`` only the step's wanted rows, gathered.  ``lazy``: the caller hands the
+        result to ``linear`` next and nothing else reads it; steps of up to 64 rows then run
+        the norm inside that product."""
         dim = self.hidden
         if gain.dtype != torch.float32 or gain.numel() != dim or not gain.is_contiguous():
             raise NotPlannable("a norm's gain is a contiguous float32 vector of the residual width")
         out = self.buffer("normed_wanted" if wanted_rows else "normed", dim)
         self.emit(P_RMSNORM, [self.residual.data_ptr(), dim, self.keep(gain), out.data_ptr(),
-                              ops.dtype_code(out.dtype), int(wanted_rows), dim], [eps])
+                              ops.dtype_code(out.dtype), int(wanted_rows), dim], [eps], label="rmsnorm")
+        if lazy:
+            self._lazy = (len(self.ops) - 1, out)
         return out
 
     def linear(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out, mode: str,
-               rows_symbol: int = S_N, partials: str = "") -> torch.Tensor:
+               rows_symbol: int = S_N, partials: str = "", role: str = "") -> torch.Tensor:
         """out (+)= x W^T + b.  mode: 'plain' (out in its own dtype), 'residual' (adds into the
         float32 residual; partial sums may be left to the next norm) or 'swiglu'.  ``partials``:
         '' | 'one_each' | 'always': when K is split, leave the partial tiles to the next
@@ -144,6 +181,11 @@ class PlanBuilder:
                   and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
                   and weight.data_ptr() % 16 == 0)
         flags = 0
+        lazy, self._lazy = self._lazy, None
+        if lazy is not None and x is lazy[1] and use_tc and ops.DECODE_NORM_INSIDE and ops.linear_decode_supported(1, weight):
+            self.ops[lazy[0]]["flags"] = int(self.ops[lazy[0]]["flags"]) | NF_LAZY
+            self.ops[lazy[0]]["a"][7:9] = (n, k)
+            flags |= LF_NORMED
         if mode == "residual":
             out, code = self.residual, 2
             flags |= LF_RESIDUAL
@@ -168,11 +210,15 @@ class PlanBuilder:
                     self.ws_floats = max(self.ws_floats, s * m * n)
             if mode == "residual":
                 self.ws_floats = max(self.ws_floats, self.cap * n)     # large products are deferred whole
+                if ops.linear_decode_supported(1, weight):
+                    self.ssq_floats = max(self.ssq_floats, 64 * lib.gb_linear_decode_parts(ctypes.c_int(n),
+                                                                                           ctypes.c_int(k)))
         self.emit(P_LINEAR, [x.data_ptr(), x.stride(0), self.keep(weight), weight.stride(0), self.keep(bias),
                              out if isinstance(out, int) else out.data_ptr(),
                              n if isinstance(out, int) else out.stride(0), sym(rows_symbol), n, k, 0 if use_tc else 1,
                              code, ops.dtype_code(x.dtype), ops.dtype_code(weight.dtype),
-                             ops.F32 if isinstance(out, int) else ops.dtype_code(out.dtype)], flags=flags)
+                             ops.F32 if isinstance(out, int) else ops.dtype_code(out.dtype)], flags=flags,
+                  label="linear:" + (role or mode))
         return out
 
     def short_conv(self, bcx: torch.Tensor, taps: torch.Tensor, bias, slot_view, hidden: int, kernel: int):
@@ -183,7 +229,8 @@ class PlanBuilder:
         out = self.buffer("mixed", hidden)
         self._keep.append(state)
         self.emit(P_SHORT_CONV, [bcx.data_ptr(), bcx.stride(0), self.keep(taps), self.keep(bias), state.data_ptr(),
-                                 state.stride(0), out.data_ptr(), hidden, kernel, ops.dtype_code(bcx.dtype)])
+                                 state.stride(0), out.data_ptr(), hidden, kernel, ops.dtype_code(bcx.dtype)],
+                  label="short_conv")
         return out
 
     def qk_norm_rope_store(self, qkv: torch.Tensor, heads: int, kv_heads: int, hd: int, q_gain, k_gain, eps: float,
@@ -197,7 +244,8 @@ class PlanBuilder:
                    self.keep(None if rotary is None else rotary.inv_freq), 0 if rotary is None else rotary.rotary_dim,
                    0 if rotary is None else int(rotary.adjacent_pairs), kv_view.block_table.group, kp.shape[2],
                    self.keep(kp) if write_kv else 0, self.keep(vp) if write_kv else 0, kp.shape[0] if write_kv else 0,
-                   heads, kv_heads, hd, int(write_kv), ops.dtype_code(qkv.dtype), q_out.data_ptr(), bt_stride], [eps])
+                   heads, kv_heads, hd, int(write_kv), ops.dtype_code(qkv.dtype), q_out.data_ptr(), bt_stride], [eps],
+                  label="qk_rope")
 
     def attention(self, heads: int, kv_heads: int, hd: int, scale: float, window: int, kv_view, bt_stride: int):
         out = self.buffer("mixed", heads * hd)
@@ -211,12 +259,12 @@ class PlanBuilder:
         self.attn_ws_floats = max(self.attn_ws_floats, need)
         self.emit(P_ATTENTION, [out.data_ptr(), out.stride(0), self.keep(kp), self.keep(vp), kv_view.block_table.group,
                                 kp.shape[2], kp.shape[0], heads, kv_heads, hd, int(window or 0),
-                                ops.dtype_code(out.dtype), bt_stride], [scale])
+                                ops.dtype_code(out.dtype), bt_stride], [scale], label="attention")
         return out
 
     def swiglu(self, gate_up: torch.Tensor, inner: int) -> torch.Tensor:
         out = self.buffer("act", inner)
-        self.emit(P_SWIGLU, [gate_up.data_ptr(), out.data_ptr(), ops.dtype_code(out.dtype), inner])
+        self.emit(P_SWIGLU, [gate_up.data_ptr(), out.data_ptr(), ops.dtype_code(out.dtype), inner], label="swiglu")
         return out
 
 
@@ -236,6 +284,7 @@ class StepPlan:
         self._keep = (b._keep, b._buffers)
         self.ws = torch.empty(b.ws_floats, dtype=torch.float32, device=b.device)
         self.attn_ws = torch.empty(b.attn_ws_floats, dtype=torch.float32, device=b.device)
+        self.ssq = torch.empty(b.ssq_floats, dtype=torch.float32, device=b.device)
         self.symbols = np.zeros(N_SYMBOLS, dtype=np.int64)
         self.n_groups = n_groups
         self.cap, self.max_requests = b.cap, b.max_requests
@@ -246,6 +295,27 @@ class StepPlan:
         r.status = ops.device_status(b.device).data_ptr()
         r.attn_ctas, r.tc_flags, r.use_tcgen05 = ops._ATTN_CTAS, ops._TC_FLAGS, int(ops._ATTN_TCGEN05)
         r.defer_whole_rows = ops.DEFER_WHOLE_ROWS
+        r.ssq, r.decode_products = self.ssq.data_ptr(), (ops.DECODE_ROWS if b.tc else 0)
+        r.residual, r.residual_ld = b.residual.data_ptr(), b.residual.stride(0)
+        self.labels = list(b.labels)
+        self.label_ms = np.zeros(max(len(self.labels), 1), dtype=np.float32)
+        self.label_count = np.zeros(max(len(self.labels), 1), dtype=np.int32)
+        r.timing, r.n_labels = 0, len(self.labels)
+        r.label_ms, r.label_count = self.label_ms.ctypes.data, self.label_count.ctypes.data
+
+    def set_timing(self, on: bool) -> None:
+        """Timing mode: the walker brackets every operation with CUDA events, waits for the step
+        and adds each operation's time to its label (see ``timing_table``).  Operations then run
+        one after the other, so the times are those of kernels that do not overlap: good for
+        shares, not for the step's own duration.  Not for use inside a CUDA graph."""
+        self._run.timing = 1 if on else 0
+        self.label_ms[:] = 0
+        self.label_count[:] = 0
+
+    def timing_table(self) -> dict:
+        """{label: (operations timed, milliseconds in total)} since ``set_timing(True)``."""
+        return {name: (int(self.label_count[i]), float(self.label_ms[i])) for i, name in enumerate(self.labels)
+                if self.label_count[i]}
 
     def _bind(self, need_tensorcore: bool) -> None:
         """Hand the walker the entry points of the kernel libraries; those of the tensor-core

@@ -11,6 +11,7 @@ is an error (``src/runtime/lm.rs:531-544``).
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
@@ -177,7 +178,10 @@ class Engine:
 
     def __init__(self, model: CausalLM, n_pages: int, page_size: int = 16, max_requests: int = 64,
                  max_step_tokens: int = 8192, max_context: Optional[int] = None, use_graphs: bool = True,
-                 use_plan: bool = True):
+                 use_plan: bool = True, guard_cache: bool = False, timing: Optional[bool] = None):
+        """``timing`` (default: the environment variable GIBBS_B200_TIMING=1): every operation of
+        a step is timed with CUDA events and added up per kind (``timing_table``); steps then run
+        without CUDA graphs and their kernels do not overlap."""
         self.model = model
         self.device = model.rt.device
         if self.device.type != "cuda":
@@ -186,7 +190,7 @@ class Engine:
         self.max_context = int(max_context or model.plan.max_context)
         self.max_requests, self.max_step_tokens = int(max_requests), int(max_step_tokens)
         self.cache = CacheManager(model.entry_needs(), n_pages, page_size, self.max_requests, model.rt.dtype,
-                                  self.device, self.max_context)
+                                  self.device, self.max_context, guard=guard_cache)
         self.vocab_size = model.vocab_size
         self.status = ops.device_status(self.device)
         self.builder = StepBuilder(self.cache, self.device, self.max_requests, self.max_step_tokens, self.status)
@@ -194,7 +198,8 @@ class Engine:
         self.fed_steps = 0          # steps some of whose tokens came from ids on the device
         # decode steps are replayed from CUDA graphs, one per batch size, unless a part of the
         # model cannot be captured (it reads host-side step data)
-        self.use_graphs = bool(use_graphs) and all(b.capturable for b in model.blocks)
+        self.timing = bool(os.environ.get("GIBBS_B200_TIMING", "0") == "1" if timing is None else timing)
+        self.use_graphs = bool(use_graphs) and all(b.capturable for b in model.blocks) and not self.timing
         self._graphs: dict = {}
         self._graph_pool = None
         self._capture_stream = torch.cuda.Stream(device=self.device) if self.use_graphs else None
@@ -208,6 +213,17 @@ class Engine:
                 self.plan = step_plan.build_step_plan(model, self.cache, self.max_step_tokens, self.max_requests)
             except NotPlannable as e:
                 self.plan_refusal = str(e)
+        if self.timing and self.plan is not None:
+            self.plan.set_timing(True)
+
+    def timing_table(self) -> dict:
+        """In timing mode: {kind of operation: (count, milliseconds)} over the steps so far
+        (embed, rmsnorm, linear:<role>, short_conv, qk_rope, attention, swiglu, ...), the
+        per-kernel-class table the reference prints with GIBBS_PROFILE_KERNELS=1
+        (MisterTK/gibbs src/graph/metal.rs:143-148)."""
+        if self.plan is None or not self.timing:
+            return {}
+        return self.plan.timing_table()
 
     # -- request life ----------------------------------------------------------
     def open(self, request_id) -> None:

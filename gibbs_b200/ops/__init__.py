@@ -328,6 +328,133 @@ def linear_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     return ws if defer else out
 
 
+# Products of up to this many rows run on the cluster kernel (csrc/gemm_tc_decode.cu, which takes up to 64:
+# K split inside a thread-block cluster, the norm in front of a product inside it for up to 16 rows).
+# 0 (the default): all products on the general kernel, whose split-K partial tiles the next kernel adds.
+# Measured on a B200 at batch 8, 2,048-token contexts: 0.835 ms a step by default, 0.918 ms with the
+# cluster kernel and the norms as kernels of their own, 1.07 ms with the norms inside the products (the
+# exchange through distributed shared memory and the cluster barrier cost every product about 2 us more
+# than a partial tile costs its consumer, and normalising the rows in every CTA costs more instructions
+# on the critical path than the norm kernel's launch).
+DECODE_ROWS = max(0, min(64, int(os.environ.get("GIBBS_B200_DECODE_ROWS", "0"))))
+DECODE_PRODUCTS = DECODE_ROWS > 0
+# 0: the norm in front of a decode product stays a kernel of its own (for comparison)
+DECODE_NORM_INSIDE = os.environ.get("GIBBS_B200_DECODE_NORM_INSIDE", "1") != "0"
+
+
+def linear_decode_supported(m: int, w: torch.Tensor) -> bool:
+    """Whether ``linear_decode`` takes a product of ``m`` rows with this weight."""
+    return (1 <= m <= 64 and w.dtype == torch.bfloat16 and w.dim() == 2 and w.stride(1) == 1 and w.shape[1] % 8 == 0
+            and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0)
+
+
+def linear_decode_normed_ok(m: int, n: int, k: int) -> bool:
+    """Whether a decode product of these sizes can run the norm of its rows itself."""
+    lib = _LIBS.get("tensorcore") or _lib("tensorcore")
+    return bool(lib.gb_linear_decode_normed_ok(_c_int(m), _c_int(n), _c_int(k)))
+
+
+class NormedRows:
+    """Rows of the 32-bit residual stream that a product is to read through an
+    RMSNorm: ``x`` float32 [n, dim], ``gain``, ``eps``; ``rows`` (int32, optional)
+    picks and orders the rows; ``ssq`` (optional) are partial sums of squares
+    [parts, n] of the rows of ``x``, as a product into the stream left them."""
+
+    def __init__(self, x: torch.Tensor, gain: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None,
+                 ssq: Optional[torch.Tensor] = None):
+        self.x, self.gain, self.eps, self.rows, self.ssq = x, gain, float(eps), rows, ssq
+        self.n_rows = x.shape[0] if rows is None else rows.numel()
+        self.shape = (self.n_rows, x.shape[1])
+        self.device, self.dtype = x.device, torch.bfloat16
+
+    def tensor(self) -> torch.Tensor:
+        """The normalised rows as a bfloat16 tensor (the norm as a kernel of its own)."""
+        out = torch.empty(self.shape, dtype=torch.bfloat16, device=self.x.device)
+        return rmsnorm(self.x, self.gain, self.eps, out, self.rows)
+
+
+_PARTS: dict = {}       # (n, k) -> partial sums of squares per row a product into the stream leaves
+
+
+def linear_decode(a, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, accumulate: bool = False,
+                  swiglu: bool = False, want_ssq: bool = False):
+    """out (+)= a @ w.T (+ bias) for up to 64 rows (csrc/gemm_tc_decode.cu): K is
+    split inside a thread-block cluster and added through distributed shared
+    memory, so nothing but ``out`` is written.  ``a`` is a bfloat16 tensor, or
+    ``NormedRows`` (the RMSNorm then runs inside the product).  With
+    ``accumulate`` and ``want_ssq`` the partial sums of squares of the new rows
+    of ``out`` are returned ([parts, m] float32), else None."""
+    lib = _LIBS.get("tensorcore") or _lib("tensorcore")
+    normed = isinstance(a, NormedRows)
+    m, k = a.shape
+    n, kw = w.shape
+    n_out = n // 2 if swiglu else n
+    if kw != k or out.shape[0] != m or out.shape[1] != n_out:
+        raise KernelError(f"linear: shapes a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} disagree")
+    if not linear_decode_supported(m, w):
+        raise KernelError("linear_decode: 1 to 64 rows and a bfloat16 weight with 16-byte aligned rows expected")
+    if n_out > 1 and out.stride(1) != 1:
+        raise KernelError("linear: expected 2-d tensors with contiguous rows")
+    odt = out.dtype
+    if swiglu:
+        if odt != torch.bfloat16 or n % 128:
+            raise KernelError("linear_decode: the SwiGLU epilogue writes bfloat16 and needs 2*features % 128 == 0")
+        mode = 3
+    elif accumulate:
+        if odt != torch.float32:
+            raise KernelError("linear_decode: accumulation needs a float32 output")
+        mode = 2
+    elif odt == torch.bfloat16:
+        mode = 0
+    elif odt == torch.float32:
+        mode = 1
+    else:
+        raise KernelError(f"kernels take float32 and bfloat16 tensors, not {odt}")
+    if bias is not None:
+        _need_cuda(bias)
+        _f32vec(bias, n, "linear bias")
+    gain = rows = ssq_in = _NULL
+    eps, parts_in, ld_in = 0.0, 0, 0
+    if normed:
+        x = a.x
+        _need_cuda(x, a.gain, a.rows, a.ssq, w, out)
+        if x.dtype != torch.float32 or x.stride(1) != 1 or x.stride(0) % 4 or x.data_ptr() % 16:
+            raise KernelError("linear_decode: normalised rows are float32 with 16-byte aligned rows")
+        _f32vec(a.gain, k, "rmsnorm gain")
+        gain, eps = _c_void(a.gain.data_ptr()), a.eps
+        if a.rows is not None:
+            rows = _c_void(_i32(a.rows, "rmsnorm rows").data_ptr())
+        if a.ssq is not None:
+            if a.ssq.dtype != torch.float32 or not a.ssq.is_contiguous() or a.ssq.shape[1] != x.shape[0]:
+                raise KernelError("linear_decode: partial sums of squares are contiguous float32 [parts, rows of x]")
+            ssq_in, parts_in, ld_in = _c_void(a.ssq.data_ptr()), a.ssq.shape[0], a.ssq.shape[1]
+        ldx = x.stride(0) if x.shape[0] > 1 else max(x.stride(0), k)
+    else:
+        x = a
+        if not (x.is_cuda and w.is_cuda and out.is_cuda):
+            _need_cuda(x, w, out)
+        if x.dtype != torch.bfloat16 or x.stride(1) != 1:
+            raise KernelError("linear_decode: bfloat16 rows expected")
+        ldx = x.stride(0) if m > 1 else max(x.stride(0), k)
+    ssq = None
+    if want_ssq and mode == 2:
+        parts = _PARTS.get((n, k))
+        if parts is None:
+            parts = _PARTS[(n, k)] = lib.gb_linear_decode_parts(_c_int(n), _c_int(k))
+        ssq = torch.empty((parts, m), dtype=torch.float32, device=out.device)
+    rc = lib.gb_linear_decode(
+        _c_void(x.data_ptr()), _c_ll(ldx), _c_int(1 if normed else 0), gain, _c_float(eps), rows, ssq_in,
+        _c_int(parts_in), _c_ll(ld_in), _c_void(w.data_ptr()), _c_ll(w.stride(0) if n > 1 else max(w.stride(0), k)),
+        _NULL if bias is None else _c_void(bias.data_ptr()), _c_void(out.data_ptr()), _c_int(mode),
+        _c_ll(out.stride(0) if m > 1 else max(out.stride(0), n_out)), _c_int(m), _c_int(n), _c_int(k),
+        _NULL if ssq is None else _c_void(ssq.data_ptr()), _c_ll(m), _c_int(_TC_FLAGS), _status_ptr(out),
+        _STREAM if _STREAM is not None else _stream())
+    if rc < 0:
+        check(lib, rc)
+    _launched(rc)
+    return ssq
+
+
 class Partials:
     """What a split-K product left for its consumer: the 32-bit partial tiles
     [splits, m, n] (to be added in split order), the product's bias (not yet

@@ -18,6 +18,8 @@ from .linear import Linear
 
 
 class GQAAttention(Mixer):
+    fuses_norm = True          # its input goes straight into a product (parts.linear.Linear)
+
     @classmethod
     def declare(cls, params):
         h, hd = params["hidden"], params["head_dim"]
@@ -107,12 +109,12 @@ class GQAAttention(Mixer):
         if not self.shares_kv and not kv.writable:
             raise RuntimeError("an attention layer with k/v projections was given a read-only cache")
         qkv = plan.linear(h, self.qkv.weight, self.qkv.bias, plan.buffer("qkv", self.qkv.out_features), "plain",
-                          partials="always")
+                          partials="always", role="qkv")
         plan.qk_norm_rope_store(qkv, self.heads, self.kv_heads, self.head_dim, self.q_gain, self.k_gain, self.eps,
                                 self.rotary, kv, not self.shares_kv, plan.bt_stride)
         out = plan.attention(self.heads, self.kv_heads, self.head_dim, self.scale, self.window or 0, kv,
                              plan.bt_stride)
-        plan.linear(out, self.out_proj.weight, self.out_proj.bias, None, "residual")
+        plan.linear(out, self.out_proj.weight, self.out_proj.bias, None, "residual", role="out_proj")
 
 
 register_part("mixer", "gqa_attention", GQAAttention)

@@ -65,10 +65,16 @@ class TensorDecl:
 @dataclass(frozen=True)
 class PagedKV:
     """Keys and values of every position (or of the last ``window`` positions)
-    in pages: [n_pages, kv_heads, page_size, head_dim] each."""
+    in pages: keys [n_pages, kv_heads, page_size, head_dim], values
+    [n_pages, kv_heads, page_size, v_head_dim] (``v_head_dim`` None: as the keys)."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)
@@ -97,9 +103,12 @@ class Residual:
     def __init__(self, x: torch.Tensor):
         self.x = x
         self.pending = None            # (partials [splits, tokens, hidden], bias or None)
+        self.ssq = None                # partial sums of squares of the rows as they stand [parts, tokens], or None
 
     def tensor(self) -> torch.Tensor:
-        """The stream with everything added."""
+        """The stream with everything added (the caller may change it: what was known
+        about its rows' sums of squares is dropped)."""
+        self.ssq = None
         if self.pending is not None:
             from .. import ops
             ops.add_pending(self.x, *self.pending)
@@ -166,6 +175,12 @@ class Norm(Part):
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
+
+    def lazy(self, x, rows: Optional[torch.Tensor] = None):
+        """For a consumer that says ``fuses_norm``: the normalised rows, or an object that
+        a product can read *through* the norm (``ops.NormedRows``), so that no kernel runs
+        for the norm alone.  By default the norm simply runs."""
+        return self.forward(x, rows=rows)
 
 
 @dataclass(frozen=True)
@@ -266,6 +281,12 @@ class Block:
         return out
 
     def caches_of(self, role: str, caches: list) -> list:
+        """The views that belong to the part in ``role``.  A block with one part that keeps
+        a cache hands it everything it was given (an entry that reads another entry's cache
+        gets that entry's views, whatever its own needs are)."""
+        holders = [r for r, p in self.parts.items() if getattr(p, "cache_needs", None) is not None]
+        if holders == [role]:
+            return caches
         lo, hi = self._cache_slices[role]
         return caches[lo:hi]
 

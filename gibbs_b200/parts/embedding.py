@@ -34,6 +34,7 @@ class LMHead(Part):
     (MisterTK/gibbs arch/lib/transformer.json5:170-175).  A tied head is given
     the embedding table's tensor and shares its memory."""
     category = "head"
+    fuses_norm = True          # its input goes straight into a product (parts.linear.Linear)
 
     @classmethod
     def declare(cls, params):
@@ -52,7 +53,7 @@ class LMHead(Part):
 
     def plan_ops(self, plan, z, logits: int):
         """``logits``: the plan's symbol for where the step's float32 logits go."""
-        plan.linear(z, self.proj.weight, self.proj.bias, logits, "plain", rows_symbol=plan.WANTED)
+        plan.linear(z, self.proj.weight, self.proj.bias, logits, "plain", rows_symbol=plan.WANTED, role="lm_head")
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)

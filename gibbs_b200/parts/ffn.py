@@ -11,6 +11,8 @@ from .linear import Linear, can_fuse_swiglu, interleave_gate_up
 
 
 class SwiGLU(FeedForward):
+    fuses_norm = True          # its input goes straight into a product (parts.linear.Linear)
+
     @classmethod
     def declare(cls, params):
         h, f = params["hidden"], params["inner"]
@@ -49,11 +51,11 @@ class SwiGLU(FeedForward):
     def plan_ops(self, plan, h):
         gu = self.gate_up
         if self.fused:
-            act = plan.linear(h, gu.weight, gu.bias, plan.buffer("act", self.inner), "swiglu")
+            act = plan.linear(h, gu.weight, gu.bias, plan.buffer("act", self.inner), "swiglu", role="gate_up")
         else:
-            both = plan.linear(h, gu.weight, gu.bias, plan.buffer("gate_up", 2 * self.inner), "plain")
+            both = plan.linear(h, gu.weight, gu.bias, plan.buffer("gate_up", 2 * self.inner), "plain", role="gate_up")
             act = plan.swiglu(both, self.inner)
-        plan.linear(act, self.down.weight, self.down.bias, None, "residual")
+        plan.linear(act, self.down.weight, self.down.bias, None, "residual", role="down")
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

@@ -25,10 +25,23 @@ class Linear:
     def kernel_libraries(self):
         return ops.linear_libraries(self.weight.dtype, self.rt.dtype)
 
-    def partials(self, x: torch.Tensor):
+    def _decode(self, x) -> bool:
+        """Whether this call runs on the decode kernel (up to 64 rows, cluster split-K)."""
+        if self.rt.dtype != torch.bfloat16 or x.shape[0] > ops.DECODE_ROWS \
+                or not ops.linear_decode_supported(x.shape[0], self.weight):
+            return False
+        if isinstance(x, ops.NormedRows):
+            return True                 # (whether the norm runs inside is asked in __call__)
+        return (x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
+
+    def partials(self, x):
         """x W^T + b for a consumer that can add split-K partial tiles itself:
         ``ops.Partials`` when the product runs on the tensor cores with K split
         (then no reduction kernel runs), else the finished product."""
+        if self._decode(x):
+            return self(x)
+        if isinstance(x, ops.NormedRows):
+            x = x.tensor()
         if not self.swiglu and self.rt.dtype == torch.bfloat16 and ops.linear_tc_supported(x, self.weight):
             return ops.linear_tc_partials(x, self.weight, self.bias)
         return self(x)
@@ -37,9 +50,16 @@ class Linear:
                  out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """out (+)= x W^T + b.  ``accumulate`` adds into a float32 ``out``
         (the residual stream)."""
+        decode = self._decode(x)
+        if isinstance(x, ops.NormedRows) and not (decode and ops.linear_decode_normed_ok(x.shape[0], *self.weight.shape)):
+            x = x.tensor()                      # this product cannot take the norm in: the norm runs by itself
+            decode = self._decode(x)
         if isinstance(out, Residual):
             if not accumulate:
                 raise ValueError("a projection can only add into the residual stream")
+            if decode:
+                out.ssq = ops.linear_decode(x, self.weight, self.bias, out.tensor(), accumulate=True, want_ssq=True)
+                return out
             if ops.linear_tc_supported(x, self.weight):
                 res = ops.linear_tc(x, self.weight, self.bias, out.tensor(), accumulate=True,
                                     defer=True)
@@ -50,6 +70,9 @@ class Linear:
             return out
         if out is None:
             out = torch.empty(x.shape[0], self.out_features, dtype=out_dtype or self.rt.dtype, device=x.device)
+        if decode:
+            ops.linear_decode(x, self.weight, self.bias, out, accumulate=accumulate, swiglu=self.swiglu)
+            return out
         if self.swiglu:
             return ops.linear_tc(x, self.weight, self.bias, out, swiglu=True)
         return ops.linear(x, self.weight, self.bias, out, accumulate)

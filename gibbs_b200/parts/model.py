@@ -47,7 +47,10 @@ class CausalLM:
             self.blocks[entry.layer].forward(x, step, caches[e])
         if step.n_want == 0:
             return None
-        z = self.final_norm.forward(x, rows=step.want_rows)
+        if getattr(self.head, "fuses_norm", False):
+            z = self.final_norm.lazy(x, rows=step.want_rows)
+        else:
+            z = self.final_norm.forward(x, rows=step.want_rows)
         return self.head.forward(z)
 
     def plan_ops(self, plan, caches) -> None:
@@ -56,7 +59,13 @@ class CausalLM:
         plan_ops_of(self.embedding)(plan)
         for e, entry in enumerate(self.plan.order):
             plan_ops_of(self.blocks[entry.layer])(plan, caches[e])
-        z = plan_ops_of(self.final_norm)(plan, wanted_rows=True)
+        if getattr(self.head, "fuses_norm", False) and getattr(self.final_norm, "lazy", None) is not None:
+            try:
+                z = plan_ops_of(self.final_norm)(plan, wanted_rows=True, lazy=True)
+            except TypeError:            # a norm from outside whose plan_ops knows no such option
+                z = plan_ops_of(self.final_norm)(plan, wanted_rows=True)
+        else:
+            z = plan_ops_of(self.final_norm)(plan, wanted_rows=True)
         plan_ops_of(self.head)(plan, z, plan.LOGITS)
 
     def weight_bytes_per_step(self, n_tokens: int = 1) -> int:

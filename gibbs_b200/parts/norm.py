@@ -27,9 +27,19 @@ class RMSNorm(Norm):
             out = self.rt.empty(n, self.dim)
         return ops.rmsnorm(x, self.gain, self.eps, out, rows, pending)
 
+    def lazy(self, x, rows=None):
+        """Up to 16 rows of the stream in bfloat16: the product that reads them runs the
+        norm itself (csrc/gemm_tc_decode.cu), with the sums of squares the product before
+        left when there are some."""
+        n = (x.shape[0] if rows is None else rows.numel())
+        if (isinstance(x, Residual) and x.pending is None and ops.DECODE_PRODUCTS and ops.DECODE_NORM_INSIDE and self.rt.dtype == torch.bfloat16
+                and n <= min(16, ops.DECODE_ROWS) and self.dim % 8 == 0 and x.x.stride(1) == 1 and x.x.stride(0) % 4 == 0
+                and x.x.data_ptr() % 16 == 0):
+            return ops.NormedRows(x.x, self.gain, self.eps, rows, x.ssq)
+        return self.forward(x, rows=rows)
 
-    def plan_ops(self, plan, wanted_rows: bool = False):
-        return plan.rmsnorm(self.gain, self.eps, wanted_rows)
+    def plan_ops(self, plan, wanted_rows: bool = False, lazy: bool = False):
+        return plan.rmsnorm(self.gain, self.eps, wanted_rows, lazy=lazy)
 
 
 register_part("norm", "rmsnorm", RMSNorm)

@@ -14,6 +14,8 @@ from .linear import Linear
 
 
 class GatedShortConv(Mixer):
+    fuses_norm = True          # its input goes straight into a product (parts.linear.Linear)
+
     @classmethod
     def declare(cls, params):
         h, k = params["hidden"], params["kernel"]
@@ -59,9 +61,9 @@ class GatedShortConv(Mixer):
 
     def plan_ops(self, plan, h, caches):
         bcx = plan.linear(h, self.in_proj.weight, self.in_proj.bias, plan.buffer("bcx", 3 * self.hidden), "plain",
-                          partials="one_each")
+                          partials="one_each", role="in_proj")
         y = plan.short_conv(bcx, self.taps, self.conv_bias, caches[0], self.hidden, self.kernel)
-        plan.linear(y, self.out_proj.weight, self.out_proj.bias, None, "residual")
+        plan.linear(y, self.out_proj.weight, self.out_proj.bias, None, "residual", role="out_proj")
 
 
 register_part("mixer", "gated_short_conv", GatedShortConv)

@@ -29,7 +29,16 @@ TINY_B = dict(
     full_attn_idxs=[0, 2, 5], rope_theta=1000000.0, norm_eps=1e-6,
     tie_embedding=False, max_position_embeddings=512,
 )
-TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1)}
+# Head size 64 (the tensor-core attention kernels and the tcgen05 prompt kernel), two layers of
+# attention around a short convolution; used with sharpened attention (see ``sharpen_attention``).
+TINY_C = dict(
+    architectures=["Lfm2ForCausalLM"], model_type="lfm2",
+    hidden_size=128, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+    vocab_size=640, intermediate_size=256, block_auto_adjust_ff_dim=False, conv_L_cache=3, conv_bias=False,
+    layer_types=["full_attention", "conv", "full_attention"], rope_theta=10000.0, norm_eps=1e-5,
+    tie_embedding=True, max_position_embeddings=512,
+)
+TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2)}
 
 
 def make_folder(tmp, name: str, stored=torch.float32, gain_jitter=0.1, std=0.02):
@@ -37,6 +46,31 @@ def make_folder(tmp, name: str, stored=torch.float32, gain_jitter=0.1, std=0.02)
     cfg = Lfm2Config.from_dict(raw)
     return write_random_model(Path(tmp) / f"tiny{name}_{str(stored).split('.')[-1]}", cfg, seed, dtype=stored,
                               gain_jitter=gain_jitter, std=std)
+
+
+def sharpen_attention(folder, factor: float = 2.5):
+    """Multiply the per-head q and k norm gains of a model folder by ``factor``: the scores'
+    spread grows with its square, so that the softmax is peaked and a lost key, page or
+    window edge changes the logits by far more than rounding."""
+    from gibbs_b200.weights.safetensors_io import write_safetensors
+    path = Path(folder) / "model.safetensors"
+    raw = path.read_bytes()
+    import struct
+    (hlen,) = struct.unpack("<Q", raw[:8])
+    header = json.loads(raw[8:8 + hlen])
+    dtypes = {"F32": torch.float32, "BF16": torch.bfloat16}
+    tensors = []
+    for name, info in header.items():
+        if name == "__metadata__":
+            continue
+        lo, hi = info["data_offsets"]
+        t = torch.frombuffer(bytearray(raw[8 + hlen + lo:8 + hlen + hi]), dtype=dtypes[info["dtype"]])
+        t = t.reshape(info["shape"]).clone()
+        if name.endswith(("q_layernorm.weight", "k_layernorm.weight")):
+            t = (t.float() * factor).to(t.dtype)
+        tensors.append((name, t))
+    write_safetensors(path, iter(tensors), metadata=header.get("__metadata__", {}))
+    return folder
 
 
 def plain_logits(folder, ids) -> np.ndarray:

@@ -162,3 +162,41 @@ def test_windowed_requests_on_an_exactly_full_pool_reserve_all_or_nothing():
     m.close("a"), m.close("b")
     m.check()
     assert m.free_pages() == [4]
+
+
+def test_values_may_be_narrower_or_wider_than_keys():
+    """A mixer may keep values of another width than its keys: the two page tensors of an entry
+    then differ in their last axis and are indexed by the same page ids."""
+    needs = [([PagedKV(2, 8, None, v_head_dim=12)], None), ([PagedKV(1, 16)], None)]
+    m = CacheManager(needs, 6, 4, 2, torch.float32, "cpu", 32)
+    assert len(m.groups) == 1
+    rc = m.open("a")
+    m.reserve(rc, 9)
+    views = m.views([torch.zeros(1, m.max_blocks, dtype=torch.int32)], torch.zeros(1, dtype=torch.int32), [0])
+    assert views[0][0].k_pages.shape == (6, 2, 4, 8) and views[0][0].v_pages.shape == (6, 2, 4, 12)
+    assert views[1][0].k_pages.shape == views[1][0].v_pages.shape == (6, 1, 4, 16)
+    assert m.kv_bytes_per_token() == (2 * (8 + 12) + 1 * (16 + 16)) * 4
+    m.close("a")
+    m.check()
+
+
+def test_guards_catch_a_write_outside_a_page_or_a_slot():
+    m = CacheManager([([PagedKV(1, 4)], None), ([SlotState((3,))], None)], 4, 2, 2, torch.float32, "cpu", 16,
+                     guard=True)
+    rc = m.open("a")
+    m.reserve(rc, 3)
+    kp, vp = m._pages[(0, 0)]
+    assert kp.shape == (4, 1, 2, 4) and kp.is_contiguous()
+    kp.fill_(1.0), vp.fill_(2.0)                       # everything inside the pages may be written
+    m._slot_views[(1, 0)].fill_(3.0)
+    m.check()
+    flat = kp.view(-1)
+    flat.as_strided((1,), (1,), flat.storage_offset() + flat.numel())[0] = 9.0     # one element past the last page
+    with pytest.raises(PoolError, match="guard"):
+        m.check()
+    m2 = CacheManager([([SlotState((3,))], None)], 1, 2, 2, torch.float32, "cpu", 16, guard=True)
+    view = m2._slot_views[(0, 0)]
+    assert view.shape == (2, 3) and view.stride(0) > 3                            # guard bytes behind every slot
+    view.as_strided((1,), (1,), view.storage_offset() + 4)[0] = 1.0               # one float behind slot 0 (its 12 bytes are padded to 16)
+    with pytest.raises(PoolError, match="guard"):
+        m2.check()

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from helpers import (TINY, TOL, first_wrong, make_folder, plain_logits, random_ids, rel_err, run_trace_on_engine,
-                     trace_mixed, trace_portions, trace_tail_decoded, trace_whole)
+                     sharpen_attention, trace_mixed, trace_portions, trace_tail_decoded, trace_whole)
 
 pytestmark = pytest.mark.gpu
 
@@ -20,11 +20,16 @@ def _stored(dtype):
 
 
 def _setup(tmp_path_factory, name, dtype):
-    """(folder, model) for a tiny configuration, built once per session."""
+    """(folder, model) for a tiny configuration, built once per session.  Configuration C
+    (head size 64) gets wider weights and sharpened attention."""
     key = (name, dtype)
     if key not in _cache:
         from gibbs_b200 import load_model
-        folder = make_folder(tmp_path_factory.mktemp("models"), name, stored=_stored(dtype))
+        if name == "C":
+            folder = sharpen_attention(make_folder(tmp_path_factory.mktemp("models"), name, stored=_stored(dtype),
+                                                   std=0.06))
+        else:
+            folder = make_folder(tmp_path_factory.mktemp("models"), name, stored=_stored(dtype))
         _cache[key] = (folder, load_model(folder, dtype=dtype, device="cuda:0"))
     return _cache[key]
 
@@ -57,34 +62,38 @@ def test_whole_prompt(tmp_path_factory, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_last_32_tokens_one_by_one(tmp_path_factory, name, dtype):
     from gibbs_b200 import Engine
     folder, model = _setup(tmp_path_factory, name, dtype)
-    eng = Engine(model, n_pages=16, page_size=16)
+    eng = Engine(model, n_pages=16, page_size=16, guard_cache=True)
+    assert eng.plan is not None, eng.plan_refusal
     reqs = _requests(name, [33, 100, 177], seed=1)
     worst = _compare(folder, reqs, run_trace_on_engine(eng, trace_tail_decoded(reqs)), dtype)
     print(f"tail {name} {dtype}: worst rel err {worst:.3g}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_portions_of_changing_size(tmp_path_factory, name, dtype):
     from gibbs_b200 import Engine
     folder, model = _setup(tmp_path_factory, name, dtype)
-    eng = Engine(model, n_pages=26, page_size=8)
+    eng = Engine(model, n_pages=26, page_size=8, guard_cache=True)
     reqs = _requests(name, [5, 64, 131, 200], seed=2)
     worst = _compare(folder, reqs, run_trace_on_engine(eng, trace_portions(reqs)), dtype)
     print(f"portions {name} {dtype}: worst rel err {worst:.3g}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_mixed_batches_with_page_reuse(tmp_path_factory, name, dtype):
+    """Guard pages around every page tensor and guard bytes behind every state slot are checked
+    after every step: a write one row past a page or slot is found in the step that made it."""
     from gibbs_b200 import Engine
     folder, model = _setup(tmp_path_factory, name, dtype)
     capacity = 448
-    eng = Engine(model, n_pages=capacity // 16, page_size=16, max_requests=4)
+    eng = Engine(model, n_pages=capacity // 16, page_size=16, max_requests=4, guard_cache=True)
+    assert eng.plan is not None and eng.cache.guard, eng.plan_refusal
     reqs = _requests(name, [90, 37, 128, 61, 150, 2, 75, 100, 33, 119], seed=3)
     steps = trace_mixed(reqs, capacity_tokens=capacity, max_live=4, seed=5)
     assert max(len(s["entries"]) for s in steps) >= 3
@@ -95,7 +104,7 @@ def test_mixed_batches_with_page_reuse(tmp_path_factory, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_step_plan_gives_the_same_bits_as_the_parts_forward(tmp_path_factory, name, dtype):
     """The same model stepped through the C walker of its plan and through the parts' forward
     methods: one sequence of kernels either way, so the logits are equal bit for bit, under mixed
@@ -161,3 +170,29 @@ def test_tokens_fed_from_the_device_equal_tokens_given_by_the_host(tmp_path_fact
         out.append(rows)
     for a, b in zip(*out):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_cluster_products_with_the_norm_inside_give_the_plain_logits(tmp_path_factory, name, monkeypatch):
+    """The other way of running decode-sized products (GIBBS_B200_DECODE_ROWS=16: K split inside a
+    thread-block cluster, the norm in front of a product run by the product itself), switched on for
+    this test: mixed batches and token-by-token decoding against the plain implementation, and the
+    step plan against the parts' forward methods bit for bit."""
+    from gibbs_b200 import Engine, ops
+    monkeypatch.setattr(ops, "DECODE_ROWS", 16)
+    monkeypatch.setattr(ops, "DECODE_PRODUCTS", True)
+    folder, model = _setup(tmp_path_factory, name, "bfloat16")
+    reqs = _requests(name, [90, 37, 128, 61, 150, 2], seed=11)
+    got = []
+    for use_plan in (True, False):
+        eng = Engine(model, n_pages=28, page_size=16, max_requests=4, use_plan=use_plan, guard_cache=True)
+        assert (eng.plan is not None) == use_plan, eng.plan_refusal
+        before = ops.launch_count()
+        a = run_trace_on_engine(eng, trace_mixed(reqs, capacity_tokens=448, max_live=4, seed=5))
+        b = run_trace_on_engine(eng, trace_tail_decoded({k: v for k, v in list(reqs.items())[:2]}, tail=20))
+        _compare(folder, reqs, a, "bfloat16")
+        _compare(folder, {k: v for k, v in list(reqs.items())[:2]}, b, "bfloat16")
+        got.append((a, b))
+    for x, y in zip(got[0], got[1]):
+        for rid in x:
+            assert np.array_equal(x[rid], y[rid]), rid

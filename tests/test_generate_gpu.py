@@ -236,3 +236,91 @@ def test_command_line(tmp_path):
     rec = json.loads(p.stdout.strip().splitlines()[-1])
     for key in ("decode_tok_s", "prefill_tok_s", "bytes_per_token", "roofline_pct", "wall_ms", "weights_ms"):
         assert key in rec
+
+
+@pytest.mark.parametrize("name,ctx", [("A", 64), ("B", 128)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_generation_stops_at_the_contexts_end_and_a_step_past_it_is_refused(tmp_path, name, ctx, dtype):
+    """The tiny configurations with the context lengths their descriptions give (64 and 128; the
+    other tests give them 512 positions): generation into the context's end finishes with
+    ``length`` at exactly ctx tokens (MisterTK/gibbs src/scheduler/mod.rs:1366-1371, 1521-1525),
+    the tokens up to there are the plain model's, and a step that would write position ctx is an
+    error before anything changes (src/runtime/lm.rs:538-544)."""
+    import json as _json
+    from gibbs_b200 import Generator, SamplingParams, StepEntry
+    from gibbs_b200.engine.scheduler import FinishReason
+    from gibbs_b200.engine.step import StepError
+    stored = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+    folder = make_folder(tmp_path, name, stored=stored, std=0.08)
+    cfg_path = Path(folder) / "config.json"
+    raw = _json.loads(cfg_path.read_text())
+    raw["max_position_embeddings"] = ctx
+    cfg_path.write_text(_json.dumps(raw))
+    gen = Generator(folder, dtype=dtype, page_size=16, max_running=2)        # ctx from config.json
+    assert gen.engine.max_context == ctx
+    vocab = TINY[name][0]["vocab_size"]
+    prompt = random_ids(3, ctx - 20, vocab)
+    sched = gen.scheduler(stop_at_eos=False)
+    sid = sched.submit(prompt, SamplingParams(temperature=0.0, max_new_tokens=1000))
+    sched.run()
+    seq = sched.sequences[sid]
+    assert seq.finish == FinishReason.LENGTH and len(prompt) + len(seq.output) == ctx
+    logits = plain_logits(folder, prompt + seq.output)
+    for t, tok in enumerate(seq.output):
+        row = logits[len(prompt) + t - 1]
+        if dtype == "float32":
+            assert tok == int(np.argmax(row)), t
+        else:
+            assert row.max() - row[tok] <= 0.02 * (row.max() - row.min()), t
+    assert not gen.engine.cache.live
+    with pytest.raises(ValueError, match="does not fit the context"):
+        sched.submit(random_ids(4, ctx, vocab))
+    # the step function itself: the last position is fine, one more is refused and changes nothing
+    eng = gen.engine
+    eng.open("edge")
+    ids = random_ids(5, ctx, vocab)
+    out = eng.step([StepEntry("edge", ids, [ctx - 1])])
+    want = plain_logits(folder, ids)[-1:]
+    assert rel_err(out.cpu().numpy(), want) < TOL[dtype]
+    free = eng.cache.free_pages()
+    with pytest.raises(StepError, match="the context is"):
+        eng.step([StepEntry("edge", [1], [0])])
+    assert eng.length("edge") == ctx and eng.cache.free_pages() == free
+    eng.close("edge")
+    eng.cache.check()
+
+
+def test_timing_mode_adds_up_the_operations_of_a_step_by_kind(tmp_path):
+    """GIBBS_B200_TIMING=1 / Engine(timing=True): the step walker brackets every operation with
+    CUDA events and adds the times up per kind (the reference's per-kernel-class table,
+    MisterTK/gibbs src/graph/metal.rs:143-148).  The counts are exact, the logits are the
+    same bits as without timing."""
+    from gibbs_b200 import Engine, StepEntry, load_model
+    folder = make_folder(tmp_path, "A", stored=torch.bfloat16, std=0.05)
+    model = load_model(folder, dtype="bfloat16")
+    ids = random_ids(4, 40, 512)
+    outs = []
+    for timing in (False, True):
+        eng = Engine(model, n_pages=8, page_size=16, max_requests=2, max_step_tokens=64, timing=timing)
+        assert eng.plan is not None and eng.use_graphs == (not timing)
+        eng.open("t")
+        rows = [eng.step([StepEntry("t", ids[:37], [36])]).clone()]
+        for t in ids[37:]:
+            rows.append(eng.step([StepEntry("t", [t], [0])]).clone())
+        outs.append(torch.cat(rows))
+        if timing:
+            table = eng.timing_table()
+        else:
+            assert eng.timing_table() == {}
+        eng.close("t")
+    assert torch.equal(outs[0], outs[1])
+    steps, conv_layers, attn_layers = 4, 2, 2                    # tiny A: [conv, attention, conv, attention]
+    want = {"embed": steps, "rmsnorm": steps * (2 * 4 + 1), "linear:in_proj": steps * conv_layers,
+            "short_conv": steps * conv_layers, "linear:qkv": steps * attn_layers, "qk_rope": steps * attn_layers,
+            "attention": steps * attn_layers, "linear:out_proj": steps * 4, "linear:gate_up": steps * 4,
+            "linear:down": steps * 4, "linear:lm_head": steps}
+    assert {k: n for k, (n, _) in table.items()} == want
+    # a norm that the product after it ran itself (decode steps) took no time of its own; everything else did
+    assert all(ms > 0 for k, (_, ms) in table.items() if k != "rmsnorm")
+    total = sum(ms for _, ms in table.values())
+    assert 0 < total < 1000

@@ -828,3 +828,166 @@ def test_linear_partials_returns_tiles_only_when_k_is_split():
     out = ops.linear_tc_partials(a2, w2, None)
     assert isinstance(out, torch.Tensor) and out.dtype == torch.bfloat16
     _close(out, a2r @ w2r.T, "bfloat16")
+
+
+# --------------------------------------------------------------------------- decode products (cluster split-K, fused norm)
+DECODE_SHAPES = [(1, 64, 64), (8, 2048, 2048), (8, 6144, 2048), (8, 3072, 2048), (8, 2048, 8192), (3, 100, 72),
+                 (16, 192, 64), (17, 256, 96), (40, 1000, 200), (64, 2048, 2048), (64, 1536, 6912), (33, 136, 1032),
+                 (1, 65536 // 8, 2048), (5, 4608, 1536)]
+
+
+@pytest.mark.parametrize("m,n,k", DECODE_SHAPES)
+def test_linear_decode_against_float64(m, n, k):
+    """Every store of the decode product, with K split inside a cluster where the weight has few
+    tiles (1 to 8 ranks, slices of rows that do not divide 128), ragged edges in n and k."""
+    from gibbs_b200 import ops
+    torch.manual_seed(m + n + k)
+    a, ar = _quant(torch.randn(m, k), "bfloat16")
+    w, wr = _quant(torch.randn(n, k) / math.sqrt(k), "bfloat16")
+    assert ops.linear_decode_supported(m, w)
+    bias = torch.randn(n)
+    exact = ar @ wr.T
+    scale = exact.abs().max().item()
+    out = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+    ops.linear_decode(a, w, None, out)
+    _close(out, exact, "float32", scale)
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.linear_decode(a, w, bias.to(DEV), out)
+    _close(out, exact + bias.double(), "bfloat16")
+    # into the residual stream, with the partial sums of squares of the new rows
+    x0 = torch.randn(m, n)
+    x = x0.clone().to(DEV)
+    ssq = ops.linear_decode(a, w, bias.to(DEV), x, accumulate=True, want_ssq=True)
+    want_x = x0.double() + exact + bias.double()
+    _close(x, want_x, "float32", scale=want_x.abs().max().item())
+    assert ssq.shape[1] == m
+    got_ss = ssq.double().sum(0).cpu()
+    want_ss = (want_x ** 2).sum(-1)
+    assert ((got_ss - want_ss).abs() / want_ss).max().item() < 1e-5
+    assert int(ops.device_status(DEV).item()) == 0
+
+
+@pytest.mark.parametrize("m,n,k,gather", [(1, 256, 64, False), (8, 6144, 2048, False), (8, 3072, 2048, False),
+                                          (8, 8192, 2048, True), (3, 200, 72, True), (16, 1000, 200, False),
+                                          (12, 4608, 1536, False), (16, 384, 2048, True), (8, 16384, 2048, False),
+                                          (5, 256, 4096, False)])
+@pytest.mark.parametrize("with_ssq", [False, True])
+def test_linear_decode_with_the_norm_inside(m, n, k, gather, with_ssq):
+    """x_mode 1: the product reads the 32-bit stream through an RMSNorm of its own (scale from the
+    row or from partial sums of squares), with and without a row gather."""
+    from gibbs_b200 import ops
+    torch.manual_seed(m * 3 + n + k)
+    eps = 1e-5
+    n_src = m + 3 if gather else m
+    x = torch.randn(n_src, k) * 2
+    gain = 1 + 0.1 * torch.randn(k)
+    w, wr = _quant(torch.randn(n, k) / math.sqrt(k), "bfloat16")
+    rows = torch.randperm(n_src)[:m].to(torch.int32) if gather else None
+    src = x[rows.long()] if gather else x
+    h = src.double() / torch.sqrt((src.double() ** 2).mean(-1, keepdim=True) + eps) * gain.double()
+    h_bf = h.to(torch.bfloat16).double()                       # what the kernel's operand is rounded to
+    want = h_bf @ wr.T
+    ssq = None
+    if with_ssq:
+        # partial sums over three uneven column ranges, as a product before would have left them
+        cuts = [0, k // 3, k // 2, k]
+        ssq = torch.stack([(x[:, a:b] ** 2).sum(-1) for a, b in zip(cuts[:-1], cuts[1:])]).contiguous().to(DEV)
+    a = ops.NormedRows(x.to(DEV), gain.to(DEV), eps, None if rows is None else rows.to(DEV), ssq)
+    assert ops.linear_decode_normed_ok(m, n, k) and not ops.linear_decode_normed_ok(17, n, k)
+    assert not ops.linear_decode_normed_ok(m, 65536, k)          # more tiles than one wave of CTAs: the norm runs by itself
+    out = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+    ops.linear_decode(a, w, None, out)
+    # the operand's rounding to bfloat16 may fall the other way for values at a rounding edge
+    _close(out, want, "float32", scale=want.abs().max().item() * 200)
+    _close(out, h @ wr.T, "bfloat16")
+    assert int(ops.device_status(DEV).item()) == 0
+
+
+@pytest.mark.parametrize("m,f,k", [(1, 64, 64), (8, 8192, 2048), (8, 192, 96), (64, 256, 2048), (2, 128, 4096),
+                                   (33, 448, 136)])
+@pytest.mark.parametrize("normed", [False, True])
+def test_linear_decode_swiglu(m, f, k, normed):
+    from gibbs_b200 import ops
+    from gibbs_b200.parts.linear import interleave_gate_up
+    if normed and m > 16:
+        pytest.skip("the norm runs inside the product for up to 16 rows")
+    torch.manual_seed(m + f + k)
+    wg, wgr = _quant(torch.randn(f, k) / math.sqrt(k) * 2, "bfloat16")
+    wu, wur = _quant(torch.randn(f, k) / math.sqrt(k) * 2, "bfloat16")
+    bg, bu = torch.randn(f), torch.randn(f)
+    w = interleave_gate_up(wg, wu)
+    bias = interleave_gate_up(bg, bu).to(DEV)
+    if normed:
+        x = torch.randn(m, k) * 3
+        gain = 1 + 0.1 * torch.randn(k)
+        ar = (x.double() / torch.sqrt((x.double() ** 2).mean(-1, keepdim=True) + 1e-6) * gain.double())
+        a = ops.NormedRows(x.to(DEV), gain.to(DEV), 1e-6)
+    else:
+        a, ar = _quant(torch.randn(m, k), "bfloat16")
+    g = ar @ wgr.T + bg.double()
+    u = ar @ wur.T + bu.double()
+    want = g / (1 + torch.exp(-g)) * u
+    out = torch.full((m, f), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.linear_decode(a, w, bias, out, swiglu=True)
+    _close(out, want, "bfloat16")
+    assert int(ops.device_status(DEV).item()) == 0
+
+
+# --------------------------------------------------------------------------- a bounded wait that runs out
+BOUNDED_WAIT_SOURCE = r'''
+#include "sm100.cuh"
+
+// One thread waits, with a limit of a millisecond, for a phase of an mbarrier that nobody ever arrives
+// at (no copy is in flight, no tensor memory is held); the wait gives up, the kernel records a code
+// in the status word as the tensor-core kernels do, and returns.
+__global__ void bounded_wait_kernel(int* status, int* polls_done) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    sm100::mbar_init(&bar, 1);
+    sm100::fence_barrier_init();
+    const bool ok = sm100::mbar_wait<1000>(&bar, 0);
+    *polls_done = ok ? 0 : 1;
+    if (!ok) atomicExch(status, 16 + 7);
+  }
+}
+
+extern "C" __attribute__((visibility("default")))
+int bounded_wait_probe(int* status, int* polls_done, cudaStream_t stream) {
+  bounded_wait_kernel<<<1, 32, 0, stream>>>(status, polls_done);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+'''
+
+
+def test_a_bounded_wait_that_runs_out_sets_the_status_word_and_the_engine_reports_it(tmp_path):
+    """Every mbarrier wait of the tensor-core kernels is bounded (csrc/sm100.cuh); here one runs out
+    on purpose, in a kernel of the test's own that holds nothing: the kernel returns, the context
+    stays usable, the status word carries the code and the engine turns it into an error."""
+    import ctypes
+    import subprocess
+    from gibbs_b200 import Engine, Lfm2Config, ops, random_model
+    from gibbs_b200.csrc import build
+    from gibbs_b200.engine.step import StepEntry, StepError
+    from helpers import TINY_A
+    src, so = tmp_path / "bounded_wait.cu", tmp_path / "libbounded_wait.so"
+    src.write_text(BOUNDED_WAIT_SOURCE)
+    subprocess.run([build.find_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-shared", "-Xcompiler",
+                    "-fPIC", "-I", str(build.HERE), str(src), "-o", str(so)], check=True)
+    lib = ctypes.CDLL(str(so))
+    eng = Engine(random_model(Lfm2Config.from_dict(TINY_A), 0, dtype="float32"), n_pages=4, page_size=16,
+                 max_requests=1, max_step_tokens=16)
+    status = ops.device_status(DEV)
+    gave_up = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert int(status.item()) == 0
+    assert lib.bounded_wait_probe(ctypes.c_void_p(status.data_ptr()), ctypes.c_void_p(gave_up.data_ptr()),
+                                  ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
+    torch.cuda.synchronize()                                   # the kernel returned by itself
+    assert int(gave_up.item()) == 1 and int(status.item()) == 23
+    with pytest.raises(StepError, match="bounded wait.*ran out.*23"):
+        eng.check_status()
+    assert int(status.item()) == 0                             # reported once, then cleared
+    # the context is as usable as before
+    eng.open("r")
+    assert eng.step([StepEntry("r", [1, 2, 3], [2])]).shape == (1, TINY_A["vocab_size"])
+    eng.check_status()
+    eng.close("r")

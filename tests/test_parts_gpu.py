@@ -481,3 +481,261 @@ def test_routed_feed_forward_and_another_position_encoding_defined_in_the_test()
             bad = first_wrong(got[rid], want, 2e-5)
             assert bad is None, f"{rid}: first wrong position {bad}"
     assert not eng.cache.live
+
+
+# ---------------------------------------------------------------------------
+# another arrangement of a block, defined here
+# ---------------------------------------------------------------------------
+
+def _sandwich_block():
+    from gibbs_b200.parts import Block, Residual
+
+    class SandwichBlock(Block):
+        """x += post(mixer(pre(x))); x += scale * ffn(pre2(x)): a norm after the mixer as well
+        (MisterTK/gibbs arch/lib/transformer.json5:159-163, 'sandwich'), and a constant of the
+        arrangement's own on the second branch."""
+        ROLES = (("pre", "norm"), ("mixer", "mixer"), ("post", "norm"), ("pre2", "norm"), ("ffn", "feed_forward"))
+
+        def _branch(self, x):
+            return Residual(torch.zeros_like(x.tensor()))
+
+        def forward(self, x, step, caches):
+            branch = self._branch(x)
+            self.mixer.forward(self.pre.forward(x), branch, step, self.caches_of("mixer", caches))
+            x.add_(self.post.forward(branch))
+            branch = self._branch(x)
+            self.ffn.forward(self.pre2.forward(x), branch, step)
+            x.add_(branch.tensor() * float(self.params["ffn_scale"]))
+
+    return SandwichBlock
+
+
+def test_block_arrangement_defined_in_the_test():
+    """A block with five roles (a norm after the mixer) and a constant of its own is registered
+    from here and built from a plan whose layers name their parts by role; a layer that gives
+    other roles than the arrangement asks for is refused by name."""
+    from gibbs_b200 import Engine, register_part
+    from gibbs_b200.config import LayerSpec, ModelPlan, OrderEntry, PartSpec
+    from gibbs_b200.parts import build_model
+    from gibbs_b200.weights import TensorDict, expected_tensors
+    from helpers import first_wrong, run_trace_on_engine, trace_portions, trace_tail_decoded, trace_whole, random_ids
+    register_part("block", "toy_sandwich", _sandwich_block())
+    hidden, vocab, eps, kernel, inner, scale = 40, 150, 1e-6, 3, 64, 0.5
+
+    def norm(name):
+        return PartSpec("rmsnorm", {"dim": hidden, "eps": eps}, {"weight": name})
+
+    conv = PartSpec("gated_short_conv", {"hidden": hidden, "kernel": kernel, "bias": False},
+                    {"in_proj.weight": "c.in", "conv.weight": "c.taps", "out_proj.weight": "c.out"})
+    ffn = PartSpec("swiglu", {"hidden": hidden, "inner": inner, "bias": False},
+                   {"gate.weight": "f.g", "up.weight": "f.u", "down.weight": "f.d"})
+    layer = LayerSpec("toy_sandwich", (("pre", "norm", norm("n.pre")), ("mixer", "mixer", conv),
+                                       ("post", "norm", norm("n.post")), ("pre2", "norm", norm("n.pre2")),
+                                       ("ffn", "feed_forward", ffn)), {"ffn_scale": scale})
+    emb = PartSpec("token_embedding", {"vocab": vocab, "dim": hidden}, {"weight": "emb"})
+    head = PartSpec("lm_head", {"vocab": vocab, "dim": hidden}, {"weight": "emb"})
+    plan = ModelPlan("toy-sandwich", vocab, hidden, 256, emb, (layer,), (OrderEntry(0), OrderEntry(0)), norm("fn"), head)
+    assert layer.post.tensors == {"weight": "n.post"} and layer.part("mixer") is conv
+    torch.manual_seed(21)
+    tensors = {}
+    for name, decl in expected_tensors(plan).items():
+        shape = decl.shapes[0]
+        tensors[name] = 1 + 0.1 * torch.randn(shape) if name.startswith(("n.", "fn")) else \
+            torch.randn(shape) * (0.3 if name == "emb" else 1.0 / math.sqrt(shape[-1]))
+    model = build_model(plan, TensorDict(tensors), torch.float32, DEV)
+    assert [len(n) for n, _ in model.entry_needs()] == [1, 1]            # the layer runs twice, each run with its own state
+    eng = Engine(model, n_pages=8, page_size=8, max_requests=3, max_step_tokens=256)
+    assert eng.plan is None and "SandwichBlock" in eng.plan_refusal     # no plan operations: its forward runs
+
+    def plain_model(ids):
+        w = {k: v.double() for k, v in tensors.items()}
+        x = w["emb"][torch.tensor(ids)]
+        for _ in range(2):
+            h = plain.rms_norm(x, w["n.pre"], eps)
+            bcx = h @ w["c.in"].T
+            b, c, xx = bcx[:, :hidden], bcx[:, hidden:2 * hidden], bcx[:, 2 * hidden:]
+            a = (c * plain.causal_conv1d(b * xx, w["c.taps"].reshape(hidden, kernel))) @ w["c.out"].T
+            x = x + plain.rms_norm(a, w["n.post"], eps)
+            h = plain.rms_norm(x, w["n.pre2"], eps)
+            g, u = h @ w["f.g"].T, h @ w["f.u"].T
+            x = x + scale * ((g / (1 + torch.exp(-g)) * u) @ w["f.d"].T)
+        return (plain.rms_norm(x, w["fn"], eps) @ w["emb"].T).numpy()
+
+    reqs = {f"r{i}": random_ids(50 + i, n, vocab) for i, n in enumerate([40, 7, 66])}
+    for steps in (trace_whole(reqs), trace_portions(reqs), trace_tail_decoded(reqs, tail=6)):
+        got = run_trace_on_engine(eng, steps)
+        for rid, ids in reqs.items():
+            bad = first_wrong(got[rid], plain_model(ids), 2e-5)
+            assert bad is None, f"{rid}: first wrong position {bad}"
+    # a layer that does not give the arrangement's roles is refused, naming both lists
+    wrong = LayerSpec("toy_sandwich", layer.parts[:2] + layer.parts[3:], {"ffn_scale": 1.0})
+    bad_plan = ModelPlan("toy-sandwich", vocab, hidden, 256, emb, (wrong,), (OrderEntry(0),), norm("fn"), head)
+    with pytest.raises(ValueError, match="is made of"):
+        build_model(bad_plan, TensorDict({k: v for k, v in tensors.items() if k != "n.post"}), torch.float32, DEV)
+
+
+# ---------------------------------------------------------------------------
+# a mixer with a CUDA kernel of its own that joins the step plan
+# ---------------------------------------------------------------------------
+
+TOY_KERNEL_SOURCE = r'''
+#include <cuda_bf16.h>
+#include "gb_plan_op.h"
+
+// One block per request: s = decay * s + W_in h_t; residual_t += W_out s, over the request's tokens in order.
+template <typename T>
+__global__ void toy_decay_kernel(const T* h, long long ldh, float* residual, long long ldr, const float* w_in,
+                                 const float* w_out, const float* decay, float* state, long long slot_stride,
+                                 const int* slot_ids, const int* q_start, const int* q_len, int hidden, int d) {
+  extern __shared__ float s[];                 // [d]
+  const int r = blockIdx.x;
+  float* st = state + (long long)slot_ids[r] * slot_stride;
+  for (int j = threadIdx.x; j < d; j += blockDim.x) s[j] = st[j];
+  __syncthreads();
+  for (int t = q_start[r]; t < q_start[r] + q_len[r]; ++t) {
+    if (threadIdx.x < d) {
+      float u = 0.f;
+      for (int c = 0; c < hidden; ++c) u += w_in[threadIdx.x * hidden + c] * (float)h[t * ldh + c];
+      s[threadIdx.x] = decay[threadIdx.x] * s[threadIdx.x] + u;
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      float y = 0.f;
+      for (int j = 0; j < d; ++j) y += w_out[c * d + j] * s[j];
+      residual[t * ldr + c] += y;
+    }
+    __syncthreads();
+  }
+  for (int j = threadIdx.x; j < d; j += blockDim.x) st[j] = s[j];
+}
+
+// operands: a0 h, a1 its row stride, a2 h is bfloat16 (0/1), a3 residual, a4 its row stride, a5 w_in, a6 w_out,
+// a7 decay, a8 state of slot 0, a9 floats between slots, a10 slot ids, a11 first rows, a12 portion lengths,
+// a13 requests, a14 hidden, a15 state size
+extern "C" __attribute__((visibility("default")))
+int toy_decay_op(const GbPlanCtx* ctx, const long long* a, const double* f, int flags) {
+  const int requests = (int)a[13], hidden = (int)a[14], d = (int)a[15];
+  if (requests <= 0) return 0;
+  if (d > 128) return -1;
+  if (a[2])
+    toy_decay_kernel<__nv_bfloat16><<<requests, 128, d * sizeof(float), ctx->stream>>>(
+        (const __nv_bfloat16*)a[0], a[1], (float*)a[3], a[4], (const float*)a[5], (const float*)a[6],
+        (const float*)a[7], (float*)a[8], a[9], (const int*)a[10], (const int*)a[11], (const int*)a[12], hidden, d);
+  else
+    toy_decay_kernel<float><<<requests, 128, d * sizeof(float), ctx->stream>>>(
+        (const float*)a[0], a[1], (float*)a[3], a[4], (const float*)a[5], (const float*)a[6], (const float*)a[7],
+        (float*)a[8], a[9], (const int*)a[10], (const int*)a[11], (const int*)a[12], hidden, d);
+  return cudaGetLastError() == cudaSuccess ? 1 : -2;
+}
+'''
+
+
+def _toy_kernel_library(tmp_path):
+    """Compile the toy kernel with nvcc against the package's public header; returns the ctypes library."""
+    import ctypes
+    import subprocess
+    from gibbs_b200.csrc import build
+    src = tmp_path / "toy_decay.cu"
+    src.write_text(TOY_KERNEL_SOURCE)
+    so = tmp_path / "libtoy_decay.so"
+    subprocess.run([build.find_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-shared", "-Xcompiler",
+                    "-fPIC", "-I", str(build.HERE), str(src), "-o", str(so)], check=True)
+    return ctypes.CDLL(str(so))
+
+
+def _kernel_backed_toy_mixer(lib):
+    import ctypes
+    from gibbs_b200.engine import plan as step_plan
+    from gibbs_b200.parts import Mixer, SlotState, TensorDecl, VECTOR
+
+    class ToyKernelMixer(Mixer):
+        """The toy recurrent mixer on a CUDA kernel of its own.  ``forward`` calls the kernel's
+        operation function directly; ``plan_ops`` emits the same call as a record of the step plan
+        under the id the walker gave the function.  Both are graph-capturable: nothing reads the host."""
+        op_id = step_plan.register_op("toy_decay", lib.toy_decay_op)
+
+        @classmethod
+        def declare(cls, params):
+            h, d = params["hidden"], params["state"]
+            return {"w_in": TensorDecl.of(d, h, role=VECTOR), "w_out": TensorDecl.of(h, d, role=VECTOR),
+                    "decay": TensorDecl.of(d, role=VECTOR)}
+
+        def __init__(self, params, tensors, rt):
+            super().__init__(params, tensors, rt)
+            self.hidden, self.d = params["hidden"], params["state"]
+            self.w_in, self.w_out, self.decay = (tensors[k].float().contiguous() for k in ("w_in", "w_out", "decay"))
+
+        def cache_needs(self):
+            return [SlotState((self.d,), torch.float32)]
+
+        def _operands(self, h_ptr, h_ld, h_bf16, res_ptr, res_ld, state, slot_ids, q_start, q_len, n_req):
+            return [h_ptr, h_ld, int(h_bf16), res_ptr, res_ld, self.w_in.data_ptr(), self.w_out.data_ptr(),
+                    self.decay.data_ptr(), state.data_ptr(), state.stride(0), slot_ids, q_start, q_len, n_req,
+                    self.hidden, self.d]
+
+        def forward(self, h, residual, step, caches):
+            class Ctx(ctypes.Structure):
+                _fields_ = [("stream", ctypes.c_void_p), ("status", ctypes.c_void_p), ("sym", ctypes.c_void_p),
+                            ("n_sym", ctypes.c_int)]
+            slot, x = caches[0], residual.tensor()
+            a = (ctypes.c_longlong * 24)(*self._operands(
+                h.data_ptr(), h.stride(0), h.dtype == torch.bfloat16, x.data_ptr(), x.stride(0), slot.state,
+                slot.slot_ids.data_ptr(), step.q_start.data_ptr(), step.q_len.data_ptr(), step.n_requests))
+            ctx = Ctx(torch.cuda.current_stream().cuda_stream, step.status.data_ptr(), None, 0)
+            assert lib.toy_decay_op(ctypes.byref(ctx), a, (ctypes.c_double * 3)(), 0) == 1
+
+        def plan_ops(self, plan, h, caches):
+            S = step_plan
+            state = caches[0].state
+            plan.keep(state), plan.keep(self.w_in), plan.keep(self.w_out), plan.keep(self.decay)
+            plan.emit(self.op_id, self._operands(
+                h.data_ptr(), h.stride(0), h.dtype == torch.bfloat16, plan.residual.data_ptr(), plan.residual.stride(0),
+                state, S.sym(S.S_SLOT_IDS), S.sym(S.S_Q_START), S.sym(S.S_Q_LEN), S.sym(S.S_R)))
+
+    return ToyKernelMixer
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_mixer_with_a_kernel_of_its_own_joins_the_step_plan(tmp_path, dtype):
+    """A part outside the package compiles a kernel, registers its operation with the step walker and
+    emits it from plan_ops: the model is plannable (one C call per step, CUDA graphs for decode steps)
+    and nothing in the package's files names the operation.  The plan and the forward methods give
+    the same bits, and both agree with the plain model."""
+    from gibbs_b200 import Engine, register_part
+    from gibbs_b200.parts import build_model
+    from gibbs_b200.weights import TensorDict, expected_tensors
+    from helpers import first_wrong, run_trace_on_engine, trace_mixed, trace_tail_decoded, trace_whole, random_ids
+    register_part("mixer", "toy_decay", _kernel_backed_toy_mixer(_toy_kernel_library(tmp_path)))
+    plan = _hand_plan()
+    torch.manual_seed(4)
+    tensors = {}
+    for name, decl in expected_tensors(plan).items():
+        shape = decl.shapes[0]
+        if name.endswith("decay"):
+            t = torch.rand(shape) * 0.5 + 0.4
+        elif len(shape) == 1:
+            t = 1 + 0.1 * torch.randn(shape)
+        else:
+            t = torch.randn(shape) * (0.3 if name == "emb" else 1.0 / math.sqrt(shape[-1]))
+        tensors[name] = t.to(torch.bfloat16) if (dtype == "bfloat16" and len(shape) == 2 and ".w" not in name) else t
+    model = build_model(plan, TensorDict(tensors), torch.bfloat16 if dtype == "bfloat16" else torch.float32, DEV)
+    w64 = {k: v.double() for k, v in tensors.items()}
+    reqs = {f"r{i}": random_ids(70 + i, n, 300) for i, n in enumerate([70, 33, 100, 5, 64])}
+    got = {}
+    for use_plan in (True, False):
+        eng = Engine(model, n_pages={None: 40, 24: 40}, page_size=8, max_requests=4, max_step_tokens=512,
+                     use_plan=use_plan)
+        assert eng.use_graphs and (eng.plan is not None) == use_plan, eng.plan_refusal
+        runs = [run_trace_on_engine(eng, steps) for steps in
+                (trace_whole(reqs), trace_mixed(reqs, capacity_tokens=320, seed=2), trace_tail_decoded(reqs, tail=12))]
+        assert eng._graphs                                   # decode steps were replayed from CUDA graphs
+        got[use_plan] = runs
+        for run in runs:
+            for rid, ids in reqs.items():
+                want = _plain_hand_model(w64, ids).numpy()
+                bad = first_wrong(run[rid], want, TOL[dtype] * (1 if dtype == "float32" else 2))
+                assert bad is None, f"{rid}: first wrong position {bad} (plan {use_plan})"
+        assert eng.cache.free_pages() == [40, 40] and not eng.cache.live
+    for a, b in zip(got[True], got[False]):
+        for rid in a:
+            assert np.array_equal(a[rid], b[rid]), rid
