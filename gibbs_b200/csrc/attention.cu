@@ -27,8 +27,8 @@ template <typename T>
 __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, long long ld, const float* __restrict__ q_gain,
                                           const float* __restrict__ k_gain, float eps,
                                           const float* __restrict__ inv_freq, int rotary_dim, int adjacent,
-                                          const int* __restrict__ tok_req, const int* __restrict__ tok_pos,
-                                          const int* __restrict__ block_table, int bt_stride, int page_size,
+                                          const int* tok_req, const int* tok_pos,
+                                          const int* block_table, int bt_stride, int page_size,
                                           T* __restrict__ k_pages, T* __restrict__ v_pages, int n_pages,
                                           int n_tokens, int heads, int kv_heads, int hd, int write_kv,
                                           int* __restrict__ status) {
@@ -99,8 +99,8 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, long long ld, con
 // neighbouring threads by shuffles.  Same arithmetic as the kernel above, value by value.
 __global__ void qk_norm_rope_store_vec_kernel(bf16* __restrict__ qkv, long long ld, const float* __restrict__ q_gain,
                                               const float* __restrict__ k_gain, float eps,
-                                              const float* __restrict__ inv_freq, const int* __restrict__ tok_req,
-                                              const int* __restrict__ tok_pos, const int* __restrict__ block_table,
+                                              const float* __restrict__ inv_freq, const int* tok_req,
+                                              const int* tok_pos, const int* block_table,
                                               int bt_stride, int page_size, bf16* __restrict__ k_pages,
                                               bf16* __restrict__ v_pages, int n_pages, int heads, int kv_heads, int hd,
                                               int write_kv, int* __restrict__ status) {
@@ -185,12 +185,12 @@ __global__ void qk_norm_rope_store_vec_kernel(bf16* __restrict__ qkv, long long 
 // The same for q, k, v given as the partial tiles of the split-K product that made them
 // (ws[split][token][cols], 32-bit, plus bias): the sums are rounded to bfloat16 where the
 // product's own reduction would have rounded them.  q goes to q_out [n_tokens, heads*hd].
-__global__ void qk_norm_rope_store_partials_kernel(const float* __restrict__ ws, int splits, const float* __restrict__ bias,
+__global__ void qk_norm_rope_store_partials_kernel(const float* ws, int splits, const float* __restrict__ bias,
                                                    bf16* __restrict__ q_out, const float* __restrict__ q_gain,
                                                    const float* __restrict__ k_gain, float eps,
                                                    const float* __restrict__ inv_freq, int rotary_dim, int adjacent,
-                                                   const int* __restrict__ tok_req, const int* __restrict__ tok_pos,
-                                                   const int* __restrict__ block_table, int bt_stride, int page_size,
+                                                   const int* tok_req, const int* tok_pos,
+                                                   const int* block_table, int bt_stride, int page_size,
                                                    bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, int n_pages,
                                                    int n_tokens, int heads, int kv_heads, int hd, int write_kv,
                                                    int* __restrict__ status) {
@@ -278,10 +278,10 @@ __global__ void qk_norm_rope_store_partials_kernel(const float* __restrict__ ws,
 // the result is the same however the batch was cut.
 template <typename T, int HD_MAX>
 __global__ void __launch_bounds__(128)
-paged_attention_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k_pages,
-                       const T* __restrict__ v_pages, const int* __restrict__ block_table, int bt_stride,
-                       int page_size, int n_pages, const int* __restrict__ tok_req,
-                       const int* __restrict__ tok_pos, T* __restrict__ out, long long ldo, int n_tokens,
+paged_attention_kernel(const T* q, long long ldq, const T* k_pages,
+                       const T* v_pages, const int* block_table, int bt_stride,
+                       int page_size, int n_pages, const int* tok_req,
+                       const int* tok_pos, T* __restrict__ out, long long ldo, int n_tokens,
                        int heads, int kv_heads, int hd, float scale, int window, int* __restrict__ status) {
   pdl_trigger();
   pdl_wait();

@@ -435,7 +435,7 @@ attention_tc_kernel(const AttnParams p) {
 // One block per row (token, head); at most 32 splits.  The first warp reads all maxima and
 // sums at once and leaves the normalised weights in shared memory; then every thread adds
 // its column over the splits with the loads of several splits in flight.
-__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+__global__ void attention_merge_kernel(const float* part_o, const float* part_ml,
                                        bf16* __restrict__ out, long long ldo, int n_tokens, int heads, int hd,
                                        int splits) {
   __shared__ float wgt[32];

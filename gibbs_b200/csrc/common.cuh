@@ -113,6 +113,12 @@ static inline int gb_div_up(long long a, long long b) { return (int)((a + b - 1)
 //     their writes are visible.
 // Outside such a launch both are no-ops.  GIBBS_B200_PDL=0 turns the launch
 // attribute off (kernels then run strictly one after the other).
+//
+// Pointers to anything an earlier kernel writes (activations, cache pages, state, a step's
+// metadata) are NOT declared `const ... __restrict__`: the compiler takes loads through such a
+// pointer for invariant and may move them above pdl_wait() (it did, in a kernel that fetched its
+// first tile right after the wait).  Only what never changes while a model runs (weights, gains,
+// taps, biases, tables) keeps the qualifier.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 

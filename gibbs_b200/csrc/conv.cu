@@ -21,10 +21,10 @@ namespace {
 constexpr int MAX_TAPS = 16;
 
 template <typename T>
-__global__ void short_conv_out_kernel(const T* __restrict__ bcx, long long ld, const float* __restrict__ taps,
-                                      const float* __restrict__ bias, const float* __restrict__ state,
-                                      long long slot_stride, const int* __restrict__ slot_ids,
-                                      const int* __restrict__ tok_req, const int* __restrict__ q_start,
+__global__ void short_conv_out_kernel(const T* bcx, long long ld, const float* __restrict__ taps,
+                                      const float* __restrict__ bias, const float* state,
+                                      long long slot_stride, const int* slot_ids,
+                                      const int* tok_req, const int* q_start,
                                       T* __restrict__ out, int n_tokens, int hidden, int K) {
   pdl_trigger();
   pdl_wait();
@@ -53,10 +53,10 @@ __global__ void short_conv_out_kernel(const T* __restrict__ bcx, long long ld, c
 
 // The same for bfloat16 rows whose width is a multiple of 8: one thread takes 8 neighbouring
 // channels of a token with 16-byte loads and stores.
-__global__ void short_conv_out_vec8_kernel(const bf16* __restrict__ bcx, long long ld, const float* __restrict__ taps,
-                                           const float* __restrict__ bias, const float* __restrict__ state,
-                                           long long slot_stride, const int* __restrict__ slot_ids,
-                                           const int* __restrict__ tok_req, const int* __restrict__ q_start,
+__global__ void short_conv_out_vec8_kernel(const bf16* bcx, long long ld, const float* __restrict__ taps,
+                                           const float* __restrict__ bias, const float* state,
+                                           long long slot_stride, const int* slot_ids,
+                                           const int* tok_req, const int* q_start,
                                            bf16* __restrict__ out, int n_tokens, int hidden, int K) {
   pdl_trigger();
   pdl_wait();
@@ -116,10 +116,10 @@ __global__ void short_conv_out_vec8_kernel(const bf16* __restrict__ bcx, long lo
 // crosses into another request the window restarts from that request's state.  The terms are
 // added in the order of the kernels above (oldest tap first), so the results are the same bits.
 template <int K>
-__global__ void short_conv_out_run_kernel(const bf16* __restrict__ bcx, long long ld, const float* __restrict__ taps,
-                                          const float* __restrict__ bias, const float* __restrict__ state,
-                                          long long slot_stride, const int* __restrict__ slot_ids,
-                                          const int* __restrict__ tok_req, const int* __restrict__ q_start,
+__global__ void short_conv_out_run_kernel(const bf16* bcx, long long ld, const float* __restrict__ taps,
+                                          const float* __restrict__ bias, const float* state,
+                                          long long slot_stride, const int* slot_ids,
+                                          const int* tok_req, const int* q_start,
                                           bf16* __restrict__ out, int n_tokens, int hidden) {
   constexpr int RUN = 8;
   pdl_trigger();
@@ -206,9 +206,9 @@ __global__ void short_conv_out_run_kernel(const bf16* __restrict__ bcx, long lon
 }
 
 template <typename T>
-__global__ void short_conv_state_kernel(const T* __restrict__ bcx, long long ld, float* __restrict__ state,
-                                        long long slot_stride, const int* __restrict__ slot_ids,
-                                        const int* __restrict__ q_start, const int* __restrict__ q_len,
+__global__ void short_conv_state_kernel(const T* bcx, long long ld, float* __restrict__ state,
+                                        long long slot_stride, const int* slot_ids,
+                                        const int* q_start, const int* q_len,
                                         int n_requests, int hidden, int K) {
   pdl_trigger();
   pdl_wait();
@@ -236,10 +236,10 @@ __global__ void short_conv_state_kernel(const T* __restrict__ bcx, long long ld,
 // Every request brings exactly one token: output and state update in one pass,
 // one thread per request and channel (it alone reads and writes its state column).
 template <typename T>
-__global__ void short_conv_decode_kernel(const T* __restrict__ bcx, long long ld, const float* __restrict__ taps,
+__global__ void short_conv_decode_kernel(const T* bcx, long long ld, const float* __restrict__ taps,
                                          const float* __restrict__ bias, float* __restrict__ state,
-                                         long long slot_stride, const int* __restrict__ slot_ids,
-                                         const int* __restrict__ q_start, T* __restrict__ out, int n_requests,
+                                         long long slot_stride, const int* slot_ids,
+                                         const int* q_start, T* __restrict__ out, int n_requests,
                                          int hidden, int K) {
   pdl_trigger();
   pdl_wait();
@@ -265,11 +265,11 @@ __global__ void short_conv_decode_kernel(const T* __restrict__ bcx, long long ld
 // The same, reading [B | C | x] as the partial tiles of the split-K product that made it
 // (ws[split][token][3*hidden], 32-bit, plus in_bias): their sum is rounded to bfloat16 exactly
 // where the product's own reduction would have rounded it, then used as above.
-__global__ void short_conv_decode_partials_kernel(const float* __restrict__ ws, int splits, long long n_rows,
+__global__ void short_conv_decode_partials_kernel(const float* ws, int splits, long long n_rows,
                                                   const float* __restrict__ in_bias, const float* __restrict__ taps,
                                                   const float* __restrict__ bias, float* __restrict__ state,
-                                                  long long slot_stride, const int* __restrict__ slot_ids,
-                                                  const int* __restrict__ q_start, bf16* __restrict__ out,
+                                                  long long slot_stride, const int* slot_ids,
+                                                  const int* q_start, bf16* __restrict__ out,
                                                   int n_requests, int hidden, int K) {
   pdl_trigger();
   pdl_wait();

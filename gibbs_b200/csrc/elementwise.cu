@@ -8,7 +8,7 @@
 
 // ---------------------------------------------------------------- embedding
 template <typename T>
-__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
+__global__ void embed_kernel(const T* __restrict__ table, const int* ids, float* __restrict__ out,
                              int dim, int vocab) {
   pdl_trigger();
   pdl_wait();
@@ -39,8 +39,8 @@ GB_API int gb_embed(const void* table, int table_dtype, const int* ids, float* o
 // ids[t] = picked[from[t]] where from[t] >= 0: the tokens a step's sampler picked feed the
 // next step's gather without a trip through the host (the reference's Metal stream does
 // the same with the id its argmax head wrote, src/backend/metal/program.rs:458-544).
-__global__ void feed_tokens_kernel(int* __restrict__ ids, const int* __restrict__ picked,
-                                   const int* __restrict__ from, int n, int n_picked) {
+__global__ void feed_tokens_kernel(int* __restrict__ ids, const int* picked,
+                                   const int* from, int n, int n_picked) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
@@ -86,8 +86,8 @@ __device__ __forceinline__ void store4<bf16>(bf16* dst, float4 v) {
 // pay for the registers that hold eight splits' worth of loads.
 template <typename TOut, int VEC, int PEND>
 __global__ void rmsnorm_kernel(float* __restrict__ x, long long ldx, const float* __restrict__ gain,
-                               TOut* __restrict__ out, const int* __restrict__ rows, int dim, float eps,
-                               const float* __restrict__ pend, int splits, long long n_src_rows,
+                               TOut* __restrict__ out, const int* rows, int dim, float eps,
+                               const float* pend, int splits, long long n_src_rows,
                                const float* __restrict__ pend_bias) {
   __shared__ float scratch[32];
   pdl_trigger();
@@ -224,7 +224,7 @@ GB_API int gb_rmsnorm(float* x, long long ldx, const float* gain, void* out, int
 }
 
 // x[m, :] += sum over splits of pend[s][m, :] (+ bias), in split order.
-__global__ void add_pending_kernel(float* __restrict__ x, long long ldx, const float* __restrict__ pend, int splits,
+__global__ void add_pending_kernel(float* __restrict__ x, long long ldx, const float* pend, int splits,
                                    const float* __restrict__ bias, long long n_rows, int dim) {
   pdl_trigger();
   pdl_wait();
@@ -253,7 +253,7 @@ GB_API int gb_add_pending(float* x, long long ldx, const float* pend, int splits
 // ---------------------------------------------------------------- SwiGLU
 // in: [n, 2*inner] rows of [gate | up]; out: [n, inner].
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int inner) {
+__global__ void swiglu_kernel(const T* gu, T* __restrict__ out, long long total, int inner) {
   pdl_trigger();
   pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -284,7 +284,7 @@ GB_API int gb_swiglu(const void* gu, void* out, int dtype, int n, int inner, cud
 
 // ---------------------------------------------------------------- cast
 template <typename TIn, typename TOut>
-__global__ void cast_kernel(const TIn* __restrict__ in, TOut* __restrict__ out, long long total) {
+__global__ void cast_kernel(const TIn* in, TOut* __restrict__ out, long long total) {
   pdl_trigger();
   pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;

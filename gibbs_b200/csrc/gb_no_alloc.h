@@ -15,10 +15,13 @@
 //  - The array holds GB_NO_ALLOC_MAX_WORKSPACE_FLOATS floats (4 MiB).  Every GPU
 //    on which a process loads this library carries it until the process exits,
 //    whether or not this function is ever called.
-//  - A product whose split-K partial tiles (splits * M * N floats, see
-//    gb_linear_tc_no_alloc_needs) do not fit is refused with GB_ERR_ARG and a
-//    message that names the sizes; nothing is launched.  Products that do not
-//    split K need no scratch and are always taken.
+//  - A product of up to 128 rows whose split-K partial tiles (splits * M * N
+//    floats, see gb_linear_tc_no_alloc_needs) do not fit is refused with
+//    GB_ERR_ARG and a message that names the sizes; nothing is launched.
+//    Products that do not split K need no scratch and are always taken.  Above
+//    128 rows K is split for speed only: such a product whose partial tiles
+//    would not fit runs with K whole instead (slower, same result up to the
+//    order of the additions), and gb_linear_tc_no_alloc_needs says 0 for it.
 //  - The function itself allocates nothing: no cudaMalloc, no cudaFree, no
 //    library that allocates.  Inputs, the output and the status word are the
 //    caller's.  The tensor maps it builds live on its stack.
@@ -30,6 +33,15 @@
 //  - The first call on each device looks up the array's device address
 //    (cudaGetSymbolAddress, with that device current) and keeps it.  Make that
 //    first call outside any stream capture.
+//  - W must be complete when the kernel starts.  The kernel asks for its first
+//    weight tiles before it waits for the kernels ahead of it on the stream (it
+//    is launched with programmatic stream serialization, so that a kernel
+//    before it that signals griddepcontrol.launch_dependents lets it start
+//    early).  After an ordinary kernel or copy this cannot matter; but if the
+//    kernel right before it signals its dependents early AND writes W, put
+//    something else between the two.  X, bias and out may come from that kernel.
+//  - Launch limits (shared-memory size, SM count) are looked up once per process,
+//    for the device that is current then: use it on GPUs of one kind.
 //
 // Arguments are those of gb_linear_tc without workspace and flags:
 // X [M, K] bf16 (row stride ldx), W [N, K] bf16 (row stride ldw), bias f32 [N]

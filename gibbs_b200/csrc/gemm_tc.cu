@@ -681,7 +681,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
 }
 
 // out = epilogue(sum over splits of the partial tiles (+ bias)), in split order.
-__global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, const float* __restrict__ bias,
+__global__ void splitk_reduce_kernel(const float* ws, int splits, const float* __restrict__ bias,
                                      void* __restrict__ out, long long ldo, int mode, int M, int N) {
   pdl_trigger();
   pdl_wait();
@@ -1041,7 +1041,12 @@ int static_workspace(float** out) {
 
 }  // namespace
 
-GB_API long long gb_linear_tc_no_alloc_needs(int M, int N, int K) { return gb_linear_tc_workspace(M, N, K); }
+// What the product will really use of the built-in scratch: 0 also for a product of more than
+// 128 rows whose partial tiles would not fit (it runs with K whole).
+GB_API long long gb_linear_tc_no_alloc_needs(int M, int N, int K) {
+  const long long need = gb_linear_tc_workspace(M, N, K);
+  return (M > 128 && need > GB_NO_ALLOC_MAX_WORKSPACE_FLOATS) ? 0 : need;
+}
 
 GB_API int gb_linear_tc_no_alloc(const void* X, long long ldx, const void* W, long long ldw, const float* bias,
                                  void* out, int mode, long long ldo, int M, int N, int K, int* status,

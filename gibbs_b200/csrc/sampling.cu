@@ -44,7 +44,7 @@ __device__ __forceinline__ Cand warp_best(Cand c) {
 // before the first is used: a thread that waits for each load in turn spends the row's sixteen
 // memory latencies one after the other.
 template <typename F>
-__device__ __forceinline__ void for_each_logit(const float* __restrict__ x, int vocab, bool vec, F f) {
+__device__ __forceinline__ void for_each_logit(const float* x, int vocab, bool vec, F f) {
   const int T = blockDim.x;
   const int n4 = vec ? vocab >> 2 : 0;
   for (int i0 = threadIdx.x; i0 < n4; i0 += 8 * T) {
@@ -98,9 +98,9 @@ __device__ __forceinline__ unsigned ordered_key(float v) {
   return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
-__global__ void sample_kernel(const float* __restrict__ logits, long long ldv, int vocab,
-                              const float* __restrict__ temperature, const int* __restrict__ top_k,
-                              const float* __restrict__ top_p, const unsigned long long* __restrict__ seed,
+__global__ void sample_kernel(const float* logits, long long ldv, int vocab,
+                              const float* temperature, const int* top_k,
+                              const float* top_p, const unsigned long long* __restrict__ seed,
                               const long long* __restrict__ counter, int* __restrict__ out) {
   pdl_trigger();
   pdl_wait();
@@ -279,7 +279,7 @@ __global__ void sample_kernel(const float* __restrict__ logits, long long ldv, i
 }
 
 // All rows greedy: one pass, the first maximum of each row.
-__global__ void argmax_kernel(const float* __restrict__ logits, long long ldv, int vocab, int* __restrict__ out) {
+__global__ void argmax_kernel(const float* logits, long long ldv, int vocab, int* __restrict__ out) {
   __shared__ Cand warp_c[32];
   pdl_trigger();
   pdl_wait();

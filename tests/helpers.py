@@ -48,10 +48,12 @@ def make_folder(tmp, name: str, stored=torch.float32, gain_jitter=0.1, std=0.02)
                               gain_jitter=gain_jitter, std=std)
 
 
-def sharpen_attention(folder, factor: float = 2.5):
+def sharpen_attention(folder, factor: float = 1.2):
     """Multiply the per-head q and k norm gains of a model folder by ``factor``: the scores'
-    spread grows with its square, so that the softmax is peaked and a lost key, page or
-    window edge changes the logits by far more than rounding."""
+    spread grows with its square (1.44 times at the default: scores of several units, a few keys
+    carry most of the weight), so that a lost key, page or window edge changes the logits by
+    far more than rounding.  The factor is kept moderate: rounding errors of the scores grow
+    with the scores themselves, in 32-bit and above all in bfloat16."""
     from gibbs_b200.weights.safetensors_io import write_safetensors
     path = Path(folder) / "model.safetensors"
     raw = path.read_bytes()

@@ -242,3 +242,60 @@ def test_two_layers_at_benchmark_widths_whole_cut_and_decoded(tmp_path, name):
         assert rel_err(b16, want) < TOL["bfloat16"]
         # the walker and the Python wrappers launch the same kernels with the same arguments
         assert np.array_equal(b16, got["bfloat16", False, how]), (name, how)
+
+
+# --------------------------------------------------------------------------- the whole benchmark model and its 32-bit twin
+def test_full_size_model_in_bfloat16_against_its_float32_twin():
+    """All 16 layers of the LFM2-1.2B shape with random bfloat16 weights: the bfloat16 engine against
+    the float32 engine on the same (rounded) weights, which is its exact twin: a 512-token prompt
+    whole, the same in portions, and 32 tokens decoded one by one."""
+    from gibbs_b200 import Engine, Lfm2Config, StepEntry
+    from gibbs_b200.parts import build_model
+    from gibbs_b200.weights import TensorDict, random_tensors
+    raw = dict(architectures=["Lfm2ForCausalLM"], hidden_size=2048, num_hidden_layers=16, num_attention_heads=32,
+               num_key_value_heads=8, head_dim=64, vocab_size=65536, intermediate_size=12288,
+               block_auto_adjust_ff_dim=True, block_ffn_dim_multiplier=1.0, block_multiple_of=256, conv_L_cache=3,
+               full_attn_idxs=[2, 5, 8, 10, 12, 14], rope_theta=1000000.0, norm_eps=1e-5, tie_embedding=True,
+               max_position_embeddings=4096)
+    cfg = Lfm2Config.from_dict(raw)
+    plan = cfg.plan()
+    tensors = TensorDict(dict(random_tensors(plan, 2, torch.bfloat16, gain_jitter=0.1)))
+    prompt, tail = 512, 32
+    ids = random_ids(21, prompt + tail, 65536)
+    want_rows = [0, 255, 256, 511]
+
+    def run(eng, portions):
+        eng.open("r")
+        rows, pos = [], 0
+        for n in portions:
+            want = [r - pos for r in want_rows if pos <= r < pos + n]
+            out = eng.step([StepEntry("r", ids[pos:pos + n], want)])
+            if want:
+                rows.append(out.clone())
+            pos += n
+        for t in range(tail):
+            rows.append(eng.step([StepEntry("r", [ids[prompt + t]], [0])]).clone())
+        eng.close("r")
+        eng.check_status()
+        return torch.cat(rows).cpu().numpy()
+
+    got = {}
+    for dtype in (torch.float32, torch.bfloat16):
+        model = build_model(plan, tensors, dtype, DEV)
+        eng = Engine(model, n_pages=(prompt + tail) // 16 + 2, page_size=16, max_requests=1, max_step_tokens=prompt)
+        got[dtype, "whole"] = run(eng, (prompt,))
+        got[dtype, "cut"] = run(eng, (200, 2, 310))
+        del eng, model
+        torch.cuda.empty_cache()
+    f32, b16 = got[torch.float32, "whole"], got[torch.bfloat16, "whole"]
+    assert rel_err(got[torch.float32, "cut"], f32) < 2e-5
+    # The bound of the tiny models (4 and 6 layers) holds for their depth: every layer rounds its
+    # activations to bfloat16 anew, independent errors add in quadrature, so 16 layers carry about
+    # sqrt(16 / 4) = 2 times the error of 4 (measured: 2.3e-2 against 5e-3 to 7e-3).
+    bound = TOL["bfloat16"] * math.sqrt(16 / 4)
+    assert rel_err(b16, f32) < bound, rel_err(b16, f32)
+    assert rel_err(got[torch.bfloat16, "cut"], f32) < bound
+    # greedy choices agree wherever the 32-bit logits are not within rounding of a tie
+    for row32, row16 in zip(f32, b16):
+        top = int(np.argmax(row16))
+        assert row32.max() - row32[top] <= 0.02 * (row32.max() - row32.min())

@@ -26,8 +26,7 @@ def _setup(tmp_path_factory, name, dtype):
     if key not in _cache:
         from gibbs_b200 import load_model
         if name == "C":
-            folder = sharpen_attention(make_folder(tmp_path_factory.mktemp("models"), name, stored=_stored(dtype),
-                                                   std=0.06))
+            folder = sharpen_attention(make_folder(tmp_path_factory.mktemp("models"), name, stored=_stored(dtype)))
         else:
             folder = make_folder(tmp_path_factory.mktemp("models"), name, stored=_stored(dtype))
         _cache[key] = (folder, load_model(folder, dtype=dtype, device="cuda:0"))

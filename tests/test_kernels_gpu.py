@@ -991,3 +991,24 @@ def test_a_bounded_wait_that_runs_out_sets_the_status_word_and_the_engine_report
     assert eng.step([StepEntry("r", [1, 2, 3], [2])]).shape == (1, TINY_A["vocab_size"])
     eng.check_status()
     eng.close("r")
+
+
+@pytest.mark.parametrize("pair", ["f32xf32", "bf16xf32"])
+def test_linear_simt_gives_the_same_bits_however_the_rows_are_cut(pair):
+    """The 32-bit product has three kernels (128 x 128 tiles for prompts, 16-column tiles for a few
+    rows, a general one): every output is one accumulator walking k upwards in each of them, so a row
+    has the same bits whether it comes alone, among 16, among 64 or among 200."""
+    from gibbs_b200 import ops
+    torch.manual_seed(3)
+    ad = "float32" if pair == "f32xf32" else "bfloat16"
+    m, n, k = 200, 392, 2048
+    a, ar = _quant(torch.randn(m, k), ad)
+    w, wr = _quant(torch.randn(n, k) / math.sqrt(k), "float32")
+    bias = torch.randn(n).to(DEV)
+    whole = torch.empty(m, n, dtype=torch.float32, device=DEV)
+    ops.linear_simt(a, w, bias, whole)
+    _close(whole, ar @ wr.T + bias.double().cpu(), "float32")
+    for lo, hi in ((0, 1), (1, 17), (17, 81), (81, 200), (5, 13)):
+        part = torch.empty(hi - lo, n, dtype=torch.float32, device=DEV)
+        ops.linear_simt(a[lo:hi], w, bias, part)
+        assert torch.equal(part, whole[lo:hi]), (lo, hi)

@@ -40,8 +40,20 @@ def _call(lib, a, w, bias, out, mode, status):
         ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
 
 
+def _float64_product(a, w, bias, base, mode):
+    """The same product restated in float64 (on the device, with the library's float64 matmul)."""
+    y = a.double() @ w.double().T + bias.double()
+    if mode == 3:                                   # gate and up rows alternate in blocks of 64
+        y = y.reshape(y.shape[0], -1, 2, 64)
+        g, u = y[:, :, 0, :].reshape(y.shape[0], -1), y[:, :, 1, :].reshape(y.shape[0], -1)
+        return g / (1 + torch.exp(-g)) * u
+    return y + base.double() if mode == 2 else y
+
+
+# the last shape is one of more than 128 rows whose split (8 x 520 x 392 floats) would not fit the
+# built-in scratch: it runs with K whole, and the ordinary entry point (which splits) is its witness
 @pytest.mark.parametrize("m,n,k,mode", [(8, 2048, 2048, 2), (1, 3072, 2048, 0), (16, 2048, 8192, 1), (4, 256, 4096, 3),
-                                        (300, 384, 520, 0)])
+                                        (300, 384, 520, 0), (520, 392, 4104, 1)])
 def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row(m, n, k, mode):
     from gibbs_b200 import ops
     lib = _lib()
@@ -55,6 +67,11 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row(m, n, k, m
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     needs = lib.gb_linear_tc_no_alloc_needs(ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(k))
     assert needs <= MAX_FLOATS
+    if m > 128:
+        lib.gb_linear_tc_workspace.restype = ctypes.c_longlong
+        would = lib.gb_linear_tc_workspace(ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(k))
+        assert (needs == 0) == (would > MAX_FLOATS or would == 0)
+    exact = _float64_product(a, w, bias, base, mode)
     for round_ in range(2):
         if round_ == 1:
             # another product in between leaves its own partial sums in the shared scratch
@@ -73,6 +90,8 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row(m, n, k, m
         tol = 2e-2 if out_dtype == torch.bfloat16 else 2e-5
         scale = want.float().abs().max().item()
         assert (got.float() - want.float()).abs().max().item() <= tol * scale
+        # and against the float64 restatement of the product itself
+        assert (got.double() - exact).abs().max().item() <= tol * exact.abs().max().item()
         assert int(status.item()) == 0
 
 
