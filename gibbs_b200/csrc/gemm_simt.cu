@@ -42,7 +42,7 @@ constexpr int LK = 16;
 constexpr int LPAD = 4;
 
 template <typename TA, typename TW>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 gemm_simt_tile128_kernel(const TA* A, long long lda, const TW* __restrict__ W, long long ldw,
                          const float* __restrict__ bias, void* __restrict__ out, long long ldo, int out_dtype,
                          int accumulate, int M, int N, int K) {

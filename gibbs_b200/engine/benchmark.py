@@ -220,6 +220,32 @@ def measure_decode(engine: Engine, batch: int, prompt_len: int, steps: int, warm
             "context": int(statistics.mean(ctx)), "repeats": len(regions), "spread": spread}
 
 
+def decode_kind_shares(engine: Engine, batch: int, prompt_len: int, steps: int = 8, seed: int = 0) -> dict:
+    """Which kinds of operation a decode step's time goes to: ``steps`` decode steps of ``batch``
+    requests run in the engine's timing mode (every operation bracketed by CUDA events, no CUDA
+    graph, operations one after the other), and each kind's share of the summed time is returned
+    ({"linear:gate_up": 0.31, "rmsnorm": 0.12, ...}; the reference's per-kernel-class table,
+    MisterTK/gibbs src/graph/metal.rs:143-148).  Empty when the model has no step plan."""
+    if engine.plan is None:
+        return {}
+    first = fill_contexts(engine, batch, prompt_len, seed)
+    entries = [StepEntry(("bench", r), [t], [0]) for r, t in enumerate(first)]
+    graphs, timing = engine.use_graphs, engine.timing
+    engine.use_graphs, engine.timing = False, True
+    engine.plan.set_timing(True)
+    try:
+        for _ in range(steps):
+            engine.step(entries)
+        table = engine.plan.timing_table()
+    finally:
+        engine.plan.set_timing(False)
+        engine.use_graphs, engine.timing = graphs, timing
+        for r in range(batch):
+            engine.close(("bench", r))
+    total = sum(ms for _, ms in table.values()) or 1.0
+    return {k: round(ms / total, 4) for k, (_, ms) in sorted(table.items(), key=lambda kv: -kv[1][1])}
+
+
 def measure_decode_e2e(generator, batch: int, prompt_len: int, steps: int, warmup: int, seed: int = 0,
                        repeats: int = 1) -> dict:
     """The same through the public entry point's scheduler: prompts come from host

@@ -80,7 +80,8 @@ def arch_dump(folder: Path, arch) -> dict:
 def bench_suite(path: Path, a) -> int:
     """One JSON line per model, with the reference's field names
     (``src/bench.rs:80-116``): decode_tok_s, prefill_tok_s, bytes_per_token,
-    roofline_tok_s, roofline_pct, wall_ms, weights_ms, ceiling_gbps."""
+    roofline_tok_s, roofline_pct, wall_ms, weights_ms, ceiling_gbps; and
+    ``kernel_time_shares``, the share of a decode step's kernel time by kind of operation."""
     from . import benchmark as B
     from .api import Generator
     suite = json.loads(path.read_text())
@@ -98,6 +99,7 @@ def bench_suite(path: Path, a) -> int:
         pre = B.measure_prefill(gen.engine, prefill_tokens, warmup=3, runs=runs)
         decs = [B.measure_decode(gen.engine, batch, prefill_tokens, decode_tokens, 3, seed=r) for r in range(runs)]
         dec = sorted(decs, key=lambda d: d["tok_s"])[len(decs) // 2]
+        shares = B.decode_kind_shares(gen.engine, batch, prefill_tokens)
         bytes_per_token = dec["bytes_per_step"] // batch
         roof = peaks["hbm_gbs"] / (dec["bytes_per_step"] / 1e9) * batch
         print(json.dumps({
@@ -108,7 +110,7 @@ def bench_suite(path: Path, a) -> int:
             "host_ms": round(max(dec["wall_ms_per_step"] - dec["ms_per_step"], 0.0), 4),
             "dispatches": dec["launches"] / dec["steps"],
             "weights_ms": round(dec["bytes_per_step"] / (peaks["hbm_gbs"] * 1e9) * 1e3, 4),
-            "prefill_tok_s": round(pre["value"], 1), "batch": batch}), flush=True)
+            "prefill_tok_s": round(pre["value"], 1), "batch": batch, "kernel_time_shares": shares}), flush=True)
     return 0
 
 

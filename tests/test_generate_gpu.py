@@ -236,6 +236,15 @@ def test_command_line(tmp_path):
     rec = json.loads(p.stdout.strip().splitlines()[-1])
     for key in ("decode_tok_s", "prefill_tok_s", "bytes_per_token", "roofline_pct", "wall_ms", "weights_ms"):
         assert key in rec
+    shares = rec["kernel_time_shares"]
+    assert {"linear:gate_up", "linear:down", "attention", "short_conv", "rmsnorm"} <= set(shares)
+    assert abs(sum(shares.values()) - 1.0) < 0.01
+    # the peaks that roofline figures relate to come from --peaks, else the built-in figures
+    (tmp_path / "peaks.json").write_text(json.dumps({"hbm_gbs": 1234.5, "bf16_tflops": 100.0}))
+    p = run("--model", str(folder), "--bench", str(tmp_path / "suite.json"), "--dtype", "float32", "--peaks",
+            str(tmp_path / "peaks.json"))
+    assert p.returncode == 0 and json.loads(p.stdout.strip().splitlines()[-1])["ceiling_gbps"] == 1234.5
+    assert rec["ceiling_gbps"] == 6650.0
 
 
 @pytest.mark.parametrize("name,ctx", [("A", 64), ("B", 128)])
