@@ -114,8 +114,10 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--workload", choices=["serve700m", "long2p6b", "sweep"], default=None,
                     help="run one of the other reference workloads instead (prints its own JSON line)")
-    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
-                    help="measure one phase only (for short profiler captures); the line is then partial")
+    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "trace"], default=None,
+                    help="measure one phase only (for short profiler captures; the line is then partial); "
+                         "'timeline': the kernels of one decode step inside its graph, from CUPTI; 'trace': time "
+                         "stamps from inside the cluster product kernels (a -DGB_DECODE_TRACE build)")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm()
@@ -149,6 +151,12 @@ def main():
     if a.only == "prefill":
         pre = B.measure_prefill(eng, PROMPT_LEN, warmup=a.warmup, runs=a.steps, seed=SEED)
         print(json.dumps({"partial": "prefill", "prefill": pre}))
+        return 0
+    if a.only == "timeline":
+        print(B.format_timeline(B.decode_timeline(eng, a.batch, PROMPT_LEN, seed=SEED)))
+        return 0
+    if a.only == "trace":
+        print(B.decode_kernel_trace(eng, a.batch, PROMPT_LEN, seed=SEED))
         return 0
     if a.only == "decode":
         dec = B.measure_decode(eng, a.batch, PROMPT_LEN, a.steps, a.warmup, seed=SEED)

@@ -4,9 +4,14 @@
 //  gb_qk_norm_rope_store: per-head RMSNorm of q and k (optional), rotary
 //    position encoding of q and k (optional; half-split or adjacent pairs),
 //    q rewritten in place, k and v written into the pages of their positions.
+//    The rotary table `inv_freq` holds rotary_dim / 2 frequencies followed by
+//    ONE more value, the factor the cosines and sines are multiplied by (the
+//    reference's rope mscale, src/graph/cpu.rs:674-675; 1 for LFM2).
 //  gb_paged_attention: for every (token, head) softmax((q.K_j)*scale) V_j over
 //    the visible keys j <= pos (and j > pos - window), read through the
-//    request's block table.
+//    request's block table; with softcap > 0 the scaled scores pass through
+//    cap * tanh(s / cap) first (the reference's soft_cap,
+//    arch/lib/transformer.json5:69-75).
 //
 // Formulas (MisterTK/gibbs): per-head norm arch/lib/transformer.json5:22-24,
 // 55-58; RoPE src/graph/cpu.rs:632-697 (angle = (float)pos * inv_freq[j] in
@@ -72,6 +77,7 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, long long ld, con
     scale = 1.0f / sqrtf(ss / (float)hd + eps);
   }
   const int half = inv_freq ? rotary_dim / 2 : 0;
+  const float mscale = inv_freq ? inv_freq[half] : 1.f;
   for (int j = lane; j < half; j += 32) {
     const int i0 = adjacent ? 2 * j : j;
     const int i1 = adjacent ? 2 * j + 1 : j + half;
@@ -81,7 +87,7 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, long long ld, con
       b = b * scale * gain[i1];
     }
     const float ang = (float)pos * inv_freq[j];
-    const float c = cosf(ang), s = sinf(ang);
+    const float c = cosf(ang) * mscale, s = sinf(ang) * mscale;
     dst[i0] = from_f32<T>(a * c - b * s);
     dst[i1] = from_f32<T>(a * s + b * c);
   }
@@ -110,10 +116,11 @@ __global__ void qk_norm_rope_store_vec_kernel(bf16* __restrict__ qkv, long long 
   const int t = blockIdx.x;
   const int pos = tok_pos[t];
   const int half = hd >> 1;
+  const float mscale = inv_freq[half];
   for (int j = threadIdx.x; j < half; j += blockDim.x) {
     const float ang = (float)pos * inv_freq[j];
-    cs[j] = cosf(ang);
-    sn[j] = sinf(ang);
+    cs[j] = cosf(ang) * mscale;
+    sn[j] = sinf(ang) * mscale;
   }
   __syncthreads();
   const int tps = hd >> 3;                               // threads per head: 4, 8 or 16
@@ -252,6 +259,7 @@ __global__ void qk_norm_rope_store_partials_kernel(const float* ws, int splits, 
     scale = 1.0f / sqrtf(ss / (float)hd + eps);
   }
   const int half = inv_freq ? rotary_dim / 2 : 0;
+  const float mscale = inv_freq ? inv_freq[half] : 1.f;
   for (int j = lane; j < half; j += 32) {
     const int i0 = adjacent ? 2 * j : j;
     const int i1 = adjacent ? 2 * j + 1 : j + half;
@@ -261,7 +269,7 @@ __global__ void qk_norm_rope_store_partials_kernel(const float* ws, int splits, 
       b = b * scale * gain[i1];
     }
     const float ang = (float)pos * inv_freq[j];
-    const float c = cosf(ang), s = sinf(ang);
+    const float c = cosf(ang) * mscale, s = sinf(ang) * mscale;
     dst[i0] = __float2bfloat16_rn(a * c - b * s);
     dst[i1] = __float2bfloat16_rn(a * s + b * c);
   }
@@ -282,7 +290,8 @@ paged_attention_kernel(const T* q, long long ldq, const T* k_pages,
                        const T* v_pages, const int* block_table, int bt_stride,
                        int page_size, int n_pages, const int* tok_req,
                        const int* tok_pos, T* __restrict__ out, long long ldo, int n_tokens,
-                       int heads, int kv_heads, int hd, float scale, int window, int* __restrict__ status) {
+                       int heads, int kv_heads, int hd, float scale, float softcap, int window,
+                       int* __restrict__ status) {
   pdl_trigger();
   pdl_wait();
   __shared__ float qs[4][HD_MAX];
@@ -315,7 +324,8 @@ paged_attention_kernel(const T* q, long long ldq, const T* k_pages,
 #pragma unroll
     for (int d = 0; d < HD_MAX; ++d)
       if (d < hd) dot = fmaf(qs[warp][d], to_f32(kp[d]), dot);
-    const float s = dot * scale;
+    float s = dot * scale;
+    if (softcap > 0.f) s = softcap * tanhf(s / softcap);       // scores squashed into (-cap, cap)
     const float m_new = fmaxf(m, s);
     const float corr = expf(m - m_new);
     const float p = expf(s - m_new);
@@ -343,15 +353,15 @@ paged_attention_kernel(const T* q, long long ldq, const T* k_pages,
 template <typename T>
 int launch_attention(const void* q, long long ldq, const void* k_pages, const void* v_pages, const int* block_table,
                      int bt_stride, int page_size, int n_pages, const int* tok_req, const int* tok_pos, void* out,
-                     long long ldo, int n_tokens, int heads, int kv_heads, int hd, float scale, int window,
-                     int* status, cudaStream_t stream) {
+                     long long ldo, int n_tokens, int heads, int kv_heads, int hd, float scale, float softcap,
+                     int window, int* status, cudaStream_t stream) {
   const long long warps = (long long)n_tokens * heads;
   const int blocks = gb_div_up(warps, 4);
 #define GB_ATTN(HD)                                                                                              \
   gb_launch(paged_attention_kernel<T, HD>, dim3(blocks), dim3(128), 0, stream, (const T*)q, ldq, (const T*)k_pages, (const T*)v_pages, \
                                                             block_table, bt_stride, page_size, n_pages, tok_req, \
                                                             tok_pos, (T*)out, ldo, n_tokens, heads, kv_heads, hd, \
-                                                            scale, window, status)
+                                                            scale, softcap, window, status)
   if (hd <= 32) GB_ATTN(32);
   else if (hd <= 64) GB_ATTN(64);
   else if (hd <= 128) GB_ATTN(128);
@@ -429,7 +439,7 @@ GB_API int gb_qk_norm_rope_store_partials(const float* ws, int splits, const flo
 GB_API int gb_paged_attention(const void* q, int dtype, long long ldq, const void* k_pages, const void* v_pages,
                               const int* block_table, int bt_stride, int page_size, int n_pages, const int* tok_req,
                               const int* tok_pos, void* out, long long ldo, int n_tokens, int heads, int kv_heads,
-                              int hd, float scale, int window, int* status, cudaStream_t stream) {
+                              int hd, float scale, float softcap, int window, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return GB_OK;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0)
     GB_FAIL(GB_ERR_ARG, "gb_paged_attention: %d heads over %d kv heads", heads, kv_heads);
@@ -437,10 +447,10 @@ GB_API int gb_paged_attention(const void* q, int dtype, long long ldq, const voi
   if (page_size <= 0) GB_FAIL(GB_ERR_ARG, "gb_paged_attention: page_size %d", page_size);
   if (dtype == GB_F32)
     launch_attention<float>(q, ldq, k_pages, v_pages, block_table, bt_stride, page_size, n_pages, tok_req, tok_pos,
-                            out, ldo, n_tokens, heads, kv_heads, hd, scale, window, status, stream);
+                            out, ldo, n_tokens, heads, kv_heads, hd, scale, softcap, window, status, stream);
   else if (dtype == GB_BF16)
     launch_attention<bf16>(q, ldq, k_pages, v_pages, block_table, bt_stride, page_size, n_pages, tok_req, tok_pos,
-                           out, ldo, n_tokens, heads, kv_heads, hd, scale, window, status, stream);
+                           out, ldo, n_tokens, heads, kv_heads, hd, scale, softcap, window, status, stream);
   else
     GB_FAIL(GB_ERR_ARG, "gb_paged_attention: unknown dtype %d", dtype);
   GB_CHECK_LAUNCH("gb_paged_attention");

@@ -282,6 +282,29 @@ GB_API int gb_swiglu(const void* gu, void* out, int dtype, int n, int inner, cud
   return GB_OK;
 }
 
+// ---------------------------------------------------------------- logits: scale and soft cap
+// x <- x * scale, then (cap > 0) x <- cap * tanh(x / cap), in place on 32-bit logits
+// (MisterTK/gibbs arch/lib/transformer.json5:170-175: divided by logit_scale, then soft-capped).
+__global__ void scale_softcap_kernel(float* x, long long total, float scale, float cap) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    float v = x[i] * scale;
+    if (cap > 0.f) v = cap * tanhf(v / cap);
+    x[i] = v;
+  }
+}
+
+GB_API int gb_scale_softcap(float* x, long long total, float scale, float cap, cudaStream_t stream) {
+  if (total <= 0) return GB_OK;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  gb_launch(scale_softcap_kernel, dim3(blocks), dim3(threads), 0, stream, x, total, scale, cap);
+  GB_CHECK_LAUNCH("gb_scale_softcap");
+  return GB_OK;
+}
+
 // ---------------------------------------------------------------- cast
 template <typename TIn, typename TOut>
 __global__ void cast_kernel(const TIn* in, TOut* __restrict__ out, long long total) {

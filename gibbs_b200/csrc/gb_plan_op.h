@@ -44,6 +44,7 @@ enum GbPlanSymbol : int {
   GB_SYM_SLOT_IDS,           // [requests] state slot of the request
   GB_SYM_WANTED_ROWS,        // [wanted]
   GB_SYM_LOGITS,             // float32 [wanted, vocabulary]
-  GB_SYM_BLOCK_TABLE0,       // + g: block table of cache group g, [requests, entries per request]
+  GB_SYM_BLOCK_TABLE0,       // + g (g < 15): block table of cache group g, [requests, GB_SYM_TABLE_STRIDE entries]
+  GB_SYM_TABLE_STRIDE = 31,  // entries per request in this step's block tables (a value)
   GB_SYM_COUNT = 32
 };

@@ -301,7 +301,105 @@ __global__ void argmax_kernel(const float* logits, long long ldv, int vocab, int
   }
 }
 
+// What a row's distribution says about a picked token (MisterTK/gibbs logprob_info,
+// src/scheduler/mod.rs:272-315): the picked token's probability, the exact entropy of
+// softmax(logits) (terms below 1e-12 dropped, as there) and the k most probable tokens, by (logit
+// descending, id ascending).  One block per row; the candidates are found one after the other (k
+// block-wide maxima): the report is asked for a handful of tokens, not for speed.
+constexpr int MAX_LOGPROBS = 32;
+
+__global__ void logprob_info_kernel(const float* logits, long long ldv, int vocab, const int* chosen, int k,
+                                    float* __restrict__ chosen_prob, float* __restrict__ entropy,
+                                    int* __restrict__ top_ids, float* __restrict__ top_probs) {
+  __shared__ Cand warp_c[32];
+  __shared__ float warp_f[32];
+  __shared__ float bcast[2];
+  __shared__ int taken[MAX_LOGPROBS];
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x;
+  const float* x = logits + (size_t)row * ldv;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  auto block_best = [&](Cand c) {
+    c = warp_best(c);
+    __syncthreads();
+    if (lane == 0) warp_c[warp] = c;
+    __syncthreads();
+    Cand b = lane < nwarps ? warp_c[lane] : Cand{0.f, -1};
+    return warp_best(b);                      // (every warp computes the same result)
+  };
+  auto block_sum_f = [&](float v) {
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) warp_f[warp] = v;
+    __syncthreads();
+    float t = lane < nwarps ? warp_f[lane] : 0.f;
+    return warp_sum(t);
+  };
+  // the k best, one after the other
+  for (int j = 0; j < k; ++j) {
+    Cand best = {0.f, -1};
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      const float v = x[i];
+      bool free_ = v == v;
+      for (int t = 0; t < j; ++t) free_ = free_ && taken[t] != i;
+      const Cand c = {v, i};
+      if (free_ && better(c, best)) best = c;
+    }
+    best = block_best(best);
+    if (threadIdx.x == 0) {
+      taken[j] = best.id;
+      if (j == 0) bcast[0] = best.id >= 0 ? best.v : 0.f;     // the row's maximum
+    }
+    __syncthreads();
+  }
+  const float max_l = bcast[0];
+  float se = 0.f;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float v = x[i];
+    if (v == v) se += expf(v - max_l);
+  }
+  se = block_sum_f(se);
+  const float lse = max_l + logf(se);
+  float ent = 0.f;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float v = x[i];
+    if (v == v) {
+      const float p = expf(v - lse);
+      if (p > 1e-12f) ent += p * (v - lse);
+    }
+  }
+  ent = block_sum_f(ent);
+  if (threadIdx.x == 0) {
+    entropy[row] = -ent;
+    const int c = chosen[row];
+    const float lc = (c >= 0 && c < vocab) ? x[c] : max_l;
+    chosen_prob[row] = fminf(expf(lc - lse), 1.0f);
+  }
+  if (threadIdx.x < k) {
+    const int id = taken[threadIdx.x];
+    top_ids[(size_t)row * k + threadIdx.x] = id;
+    top_probs[(size_t)row * k + threadIdx.x] = id >= 0 ? expf(x[id] - lse) : 0.f;
+  }
+}
+
 }  // namespace
+
+// For each row: the probability of chosen[row] under softmax(logits[row]), the entropy of that
+// distribution, and its k most probable tokens with their probabilities ([rows, k] each; -1 / 0 where
+// a row has fewer than k numbers).  k in 1..32.
+GB_API int gb_logprob_info(const float* logits, long long ldv, int rows, int vocab, const int* chosen, int k,
+                           float* chosen_prob, float* entropy, int* top_ids, float* top_probs, cudaStream_t stream) {
+  if (rows <= 0) return GB_OK;
+  if (vocab <= 0) GB_FAIL(GB_ERR_ARG, "gb_logprob_info: vocabulary of %d", vocab);
+  if (k < 1 || k > MAX_LOGPROBS) GB_FAIL(GB_ERR_ARG, "gb_logprob_info: %d candidates outside 1..%d", k, MAX_LOGPROBS);
+  int threads = 64;
+  while (threads < 1024 && threads * 8 < vocab) threads <<= 1;
+  gb_launch(logprob_info_kernel, dim3(rows), dim3(threads), 0, stream, logits, ldv, vocab, chosen, k, chosen_prob,
+            entropy, top_ids, top_probs);
+  GB_CHECK_LAUNCH("gb_logprob_info");
+  return GB_OK;
+}
 
 // logits: [rows, vocab] 32-bit with row stride ldv.  temperature / top_k /
 // top_p / seed / counter are per row (null: greedy, 50, 0.9, 0, 0).

@@ -47,8 +47,9 @@ typedef int (*QkRopePartialsFn)(const float*, int, const float*, void*, const fl
                                 int, int, const int*, const int*, const int*, int, int, void*, void*, int, int, int, int,
                                 int, int, int*, cudaStream_t);
 typedef int (*PagedAttentionFn)(const void*, int, long long, const void*, const void*, const int*, int, int, int,
-                                const int*, const int*, void*, long long, int, int, int, int, float, int, int*,
+                                const int*, const int*, void*, long long, int, int, int, int, float, float, int, int*,
                                 cudaStream_t);
+typedef int (*ScaleSoftcapFn)(float*, long long, float, float, cudaStream_t);
 typedef int (*AttentionTcFn)(const void*, long long, const void*, const void*, const int*, int, int, int, const int*,
                              const int*, const int*, void*, long long, int, int, int, int, int, int, float, int, int,
                              float*, int*, cudaStream_t);
@@ -68,19 +69,20 @@ typedef int (*AddPendingFn)(float*, long long, const float*, int, const float*, 
 enum Fn : int { F_EMBED = 0, F_RMSNORM, F_LINEAR_SIMT, F_LINEAR_TC, F_LINEAR_TC_SPLITS, F_SHORT_CONV,
                 F_SHORT_CONV_PARTIALS, F_QKROPE, F_QKROPE_PARTIALS, F_PAGED_ATTENTION, F_ATTENTION_TC,
                 F_ATTENTION_TCGEN05, F_ATTENTION_TCGEN05_SUPPORTED, F_SWIGLU, F_LINEAR_DECODE, F_LINEAR_DECODE_PARTS,
-                F_LINEAR_DECODE_SUPPORTED, F_ADD_PENDING, F_LINEAR_DECODE_NORMED_OK, F_COUNT };
+                F_LINEAR_DECODE_SUPPORTED, F_ADD_PENDING, F_LINEAR_DECODE_NORMED_OK, F_SCALE_SOFTCAP, F_COUNT };
 // which library an entry point belongs to (0: core, 1: tensor cores), for the caller to fetch the message
-const int FN_LIB[F_COUNT] = {0, 0, 0, 1, 1, 0, 0, 0, 0, 0, 1, 1, 1, 0, 1, 1, 1, 0, 1};
+const int FN_LIB[F_COUNT] = {0, 0, 0, 1, 1, 0, 0, 0, 0, 0, 1, 1, 1, 0, 1, 1, 1, 0, 1, 0};
 void* g_fn[F_COUNT];
 
-enum Op : int { P_EMBED = 1, P_RMSNORM = 2, P_LINEAR = 3, P_SHORT_CONV = 4, P_QKROPE = 5, P_ATTENTION = 6, P_SWIGLU = 7 };
+enum Op : int { P_EMBED = 1, P_RMSNORM = 2, P_LINEAR = 3, P_SHORT_CONV = 4, P_QKROPE = 5, P_ATTENTION = 6, P_SWIGLU = 7,
+                P_SCALE_SOFTCAP = 8 };
 // the step's symbols (gb_plan_op.h gives their meaning), under the short names used below
 enum Sym : int { S_N = GB_SYM_TOKENS, S_R = GB_SYM_REQUESTS, S_W = GB_SYM_WANTED, S_MAXQ = GB_SYM_MAX_PORTION,
                  S_MAXCTX = GB_SYM_MAX_CONTEXT, S_ONE_EACH = GB_SYM_ONE_EACH, S_TOKEN_IDS = GB_SYM_TOKEN_IDS,
                  S_TOK_REQ = GB_SYM_TOKEN_REQUEST, S_TOK_POS = GB_SYM_TOKEN_POSITION, S_Q_START = GB_SYM_PORTION_START,
                  S_Q_LEN = GB_SYM_PORTION_LENGTH, S_START_POS = GB_SYM_LENGTH_BEFORE, S_CTX_LEN = GB_SYM_LENGTH_AFTER,
                  S_SLOT_IDS = GB_SYM_SLOT_IDS, S_WANT_ROWS = GB_SYM_WANTED_ROWS, S_LOGITS = GB_SYM_LOGITS,
-                 S_BLOCK_TABLE0 = GB_SYM_BLOCK_TABLE0, S_COUNT = GB_SYM_COUNT };
+                 S_BLOCK_TABLE0 = GB_SYM_BLOCK_TABLE0, S_TABLE_STRIDE = GB_SYM_TABLE_STRIDE, S_COUNT = GB_SYM_COUNT };
 constexpr long long SYM_BIT = 1ll << 62;
 
 enum LinearFlag : int { LF_RESIDUAL = 1, LF_PARTIALS_IF_ONE_EACH = 2, LF_PARTIALS = 4, LF_NORMED = 8 };
@@ -279,7 +281,7 @@ int run_op(Walk& w, const PlanOp& o, bool force = false) {
         PLAN_CALL(w, F_QKROPE_PARTIALS, ((QkRopePartialsFn)g_fn[F_QKROPE_PARTIALS])(
             w.ws, w.part_splits, w.part_bias, ptr<void>(w, a[17]), ptr<const float>(w, a[2]), ptr<const float>(w, a[3]),
             (float)o.f[0], ptr<const float>(w, a[4]), (int)a[5], (int)a[6], ptr<const int>(w, SYM_BIT | S_TOK_REQ),
-            ptr<const int>(w, SYM_BIT | S_TOK_POS), bt, (int)a[18], (int)a[8], ptr<void>(w, a[9]), ptr<void>(w, a[10]),
+            ptr<const int>(w, SYM_BIT | S_TOK_POS), bt, (int)val(w, a[18]), (int)a[8], ptr<void>(w, a[9]), ptr<void>(w, a[10]),
             (int)a[11], N, (int)a[12], (int)a[13], (int)a[14], (int)a[15], w.status, w.stream));
         w.q = ptr<const void>(w, a[17]);
         w.ldq = a[12] * a[14];
@@ -287,7 +289,7 @@ int run_op(Walk& w, const PlanOp& o, bool force = false) {
         PLAN_CALL(w, F_QKROPE, ((QkRopeFn)g_fn[F_QKROPE])(
             ptr<void>(w, a[0]), (int)a[16], a[1], ptr<const float>(w, a[2]), ptr<const float>(w, a[3]), (float)o.f[0],
             ptr<const float>(w, a[4]), (int)a[5], (int)a[6], ptr<const int>(w, SYM_BIT | S_TOK_REQ),
-            ptr<const int>(w, SYM_BIT | S_TOK_POS), bt, (int)a[18], (int)a[8], ptr<void>(w, a[9]), ptr<void>(w, a[10]),
+            ptr<const int>(w, SYM_BIT | S_TOK_POS), bt, (int)val(w, a[18]), (int)a[8], ptr<void>(w, a[9]), ptr<void>(w, a[10]),
             (int)a[11], N, (int)a[12], (int)a[13], (int)a[14], (int)a[15], w.status, w.stream));
         w.q = ptr<const void>(w, a[0]);
         w.ldq = a[1];
@@ -297,19 +299,20 @@ int run_op(Walk& w, const PlanOp& o, bool force = false) {
     }
     case P_ATTENTION: {
       // a0 out, a1 its row stride, a2 k pages, a3 v pages, a4 block-table group, a5 page size, a6 pages, a7 heads,
-      // a8 kv heads, a9 head_dim, a10 window, a11 dtype, a12 entries per request in a block table; f0 scale
+      // a8 kv heads, a9 head_dim, a10 window, a11 dtype, a12 entries per request in a block table; f0 scale,
+      // f1 soft cap of the scores (0: none; only the generic kernel applies one)
       const int heads = (int)a[7], kvh = (int)a[8], hd = (int)a[9], page_size = (int)a[5];
       const int group = heads / kvh;
       const int* bt = ptr<const int>(w, SYM_BIT | (S_BLOCK_TABLE0 + a[4]));
-      const float scale = (float)o.f[0];
+      const float scale = (float)o.f[0], softcap = (float)o.f[1];
       void* out = ptr<void>(w, a[0]);
-      const bool tc = a[11] == GB_BF16 && g_fn[F_ATTENTION_TC] != nullptr && hd % 16 == 0 && hd >= 16 && hd <= 128 &&
+      const bool tc = softcap <= 0.f && a[11] == GB_BF16 && g_fn[F_ATTENTION_TC] != nullptr && hd % 16 == 0 && hd >= 16 && hd <= 128 &&
                       heads % kvh == 0 && group <= 64 && w.ldq % 8 == 0 && a[1] % 2 == 0 && ((uintptr_t)w.q & 15) == 0;
       if (!tc) {
         PLAN_CALL(w, F_PAGED_ATTENTION, ((PagedAttentionFn)g_fn[F_PAGED_ATTENTION])(
-            w.q, (int)a[11], w.ldq, ptr<const void>(w, a[2]), ptr<const void>(w, a[3]), bt, (int)a[12], page_size,
+            w.q, (int)a[11], w.ldq, ptr<const void>(w, a[2]), ptr<const void>(w, a[3]), bt, (int)val(w, a[12]), page_size,
             (int)a[6], ptr<const int>(w, SYM_BIT | S_TOK_REQ), ptr<const int>(w, SYM_BIT | S_TOK_POS), out, a[1], N,
-            heads, kvh, hd, scale, (int)a[10], w.status, w.stream));
+            heads, kvh, hd, scale, softcap, (int)a[10], w.status, w.stream));
         return 0;
       }
       const int max_q = (int)w.sym[S_MAXQ];
@@ -317,7 +320,7 @@ int run_op(Walk& w, const PlanOp& o, bool force = false) {
       if (!small && w.use_tcgen05 && scale > 0.f && ((uintptr_t)out & 15) == 0 &&
           ((AttentionTcgen05SupportedFn)g_fn[F_ATTENTION_TCGEN05_SUPPORTED])(heads, kvh, hd, page_size, w.ldq, a[1])) {
         PLAN_CALL(w, F_ATTENTION_TCGEN05, ((AttentionTcgen05Fn)g_fn[F_ATTENTION_TCGEN05])(
-            w.q, w.ldq, ptr<const void>(w, a[2]), ptr<const void>(w, a[3]), bt, (int)a[12], page_size, (int)a[6],
+            w.q, w.ldq, ptr<const void>(w, a[2]), ptr<const void>(w, a[3]), bt, (int)val(w, a[12]), page_size, (int)a[6],
             ptr<const int>(w, SYM_BIT | S_Q_START), ptr<const int>(w, SYM_BIT | S_Q_LEN),
             ptr<const int>(w, SYM_BIT | S_START_POS), out, a[1], R, N, heads, kvh, hd, scale, (int)a[10], w.status,
             w.stream));
@@ -325,10 +328,18 @@ int run_op(Walk& w, const PlanOp& o, bool force = false) {
       }
       const int splits = small ? attention_splits(w, R, kvh, (int)w.sym[S_MAXCTX]) : 1;
       PLAN_CALL(w, F_ATTENTION_TC, ((AttentionTcFn)g_fn[F_ATTENTION_TC])(
-          w.q, w.ldq, ptr<const void>(w, a[2]), ptr<const void>(w, a[3]), bt, (int)a[12], page_size, (int)a[6],
+          w.q, w.ldq, ptr<const void>(w, a[2]), ptr<const void>(w, a[3]), bt, (int)val(w, a[12]), page_size, (int)a[6],
           ptr<const int>(w, SYM_BIT | S_Q_START), ptr<const int>(w, SYM_BIT | S_Q_LEN),
           ptr<const int>(w, SYM_BIT | S_START_POS), out, a[1], R, N, max_q, heads, kvh, hd, scale, (int)a[10], splits,
           splits > 1 ? w.attn_ws : nullptr, w.status, w.stream));
+      return 0;
+    }
+    case P_SCALE_SOFTCAP: {
+      // a0 the values (f32; the step's logits when it names that symbol), a1 columns, a2 rows (a symbol); f0 scale, f1 cap
+      const long long rows = val(w, a[2]);
+      if (rows <= 0) return 0;
+      PLAN_CALL(w, F_SCALE_SOFTCAP, ((ScaleSoftcapFn)g_fn[F_SCALE_SOFTCAP])(ptr<float>(w, a[0]), rows * a[1], (float)o.f[0],
+                                                                            (float)o.f[1], w.stream));
       return 0;
     }
     case P_SWIGLU: {

@@ -18,7 +18,7 @@ import torch
 from ..parts.model import CausalLM
 from ..sampling import Sampler, SamplingParams
 from .loading import load_model
-from .scheduler import MAX_PREFILL_CHUNK, Scheduler
+from .scheduler import MAX_PREFILL_CHUNK, PrefillTuner, Scheduler
 from .step import Engine
 
 
@@ -48,7 +48,9 @@ class Generator:
     def __init__(self, model: Union[str, Path, CausalLM], dtype: str = "bfloat16", device: str = "cuda:0",
                  ctx: Optional[int] = None, page_size: int = 16, n_pages: Optional[int] = None,
                  max_running: int = 64, max_batch_tokens: int = MAX_PREFILL_CHUNK, seed: int = 0,
-                 arch: Optional[str] = None):
+                 arch: Optional[str] = None, tune_prefill: bool = False):
+        """``tune_prefill``: size each step's prompt budget from measured costs (the
+        reference's ``PrefillTuner``) instead of the fixed ``max_batch_tokens``."""
         self.model = model if isinstance(model, CausalLM) else load_model(model, dtype=dtype, device=device, arch=arch)
         # as the reference: the context is max_position_embeddings, at most 4096, unless it is given
         # (MisterTK/gibbs arch/families/lfm2.json5:51); a checkpoint that allows 128k positions would
@@ -62,13 +64,14 @@ class Generator:
         conf = getattr(self.model, "config", None)
         self.eos_ids = tuple(getattr(conf, "eos_token_ids", ()) or ())
         self.max_batch_tokens, self.max_running, self.seed = max_batch_tokens, max_running, seed
+        self.tune_prefill = bool(tune_prefill)
 
     def scheduler(self, on_token=None, stop_at_eos: bool = True, overlap: bool = True) -> Scheduler:
         """``overlap``: decode steps are launched on the ids the device picked, one step
         before the host reads them (see ``engine/scheduler.py``)."""
         return Scheduler(self.engine, self.sampler, max_batch_tokens=self.max_batch_tokens,
                          max_running=self.max_running, eos_ids=self.eos_ids if stop_at_eos else (), seed=self.seed,
-                         on_token=on_token, overlap=overlap)
+                         on_token=on_token, overlap=overlap, tuner=PrefillTuner() if self.tune_prefill else None)
 
     def generate(self, prompts: Sequence[Sequence[int]], params=None, stop_at_eos: bool = True) -> list:
         """Generated token ids for each prompt (lists of ids in, lists of ids out)."""

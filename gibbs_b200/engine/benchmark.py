@@ -246,6 +246,115 @@ def decode_kind_shares(engine: Engine, batch: int, prompt_len: int, steps: int =
     return {k: round(ms / total, 4) for k, (_, ms) in sorted(table.items(), key=lambda kv: -kv[1][1])}
 
 
+def _decode_stepper(engine: Engine, batch: int, prompt_len: int, seed: int):
+    """Requests with ``prompt_len``-token contexts and a function that runs one fed decode step."""
+    first = fill_contexts(engine, batch, prompt_len, seed)
+    sampler = Sampler(engine.device)
+    greedy, zeros, places = [SamplingParams(temperature=0.0)] * batch, [0] * batch, list(range(batch))
+    entries = [StepEntry(("bench", r), [0], [0]) for r in range(batch)]
+    state = {"tokens": torch.tensor(first, dtype=torch.int32, device=engine.device)}
+
+    def one_step():
+        logits = engine.step(entries, feed=(state["tokens"], places))
+        state["tokens"] = sampler.sample_device(logits, greedy, zeros, zeros)
+
+    def close():
+        for r in range(batch):
+            engine.close(("bench", r))
+
+    return one_step, close
+
+
+def decode_timeline(engine: Engine, batch: int, prompt_len: int, seed: int = 0) -> list:
+    """Start and duration of every kernel of ONE decode step as it runs inside the replayed CUDA
+    graph, overlapping as programmatic dependent launch lets them (kernel records from CUPTI,
+    through torch.profiler).  Returns rows (name, grid, start_us, dur_us, adds_us): ``adds`` is how
+    far the kernel's end lies behind the latest end before it, i.e. what it adds to the chain of
+    dependent launches.  A measurement aid: the profiler slows the step down a little, so the
+    shares are what to read, not the sum."""
+    from torch.profiler import ProfilerActivity, profile
+    import tempfile
+    one_step, close = _decode_stepper(engine, batch, prompt_len, seed)
+    for _ in range(6):
+        one_step()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+        for _ in range(4):
+            one_step()
+        torch.cuda.synchronize()
+    close()
+    with tempfile.TemporaryDirectory() as tmp:
+        path = Path(tmp) / "trace.json"
+        prof.export_chrome_trace(str(path))
+        events = [e for e in json.loads(path.read_text())["traceEvents"] if e.get("cat") == "kernel"]
+    events.sort(key=lambda e: e["ts"])
+    marks = [i for i, e in enumerate(events) if "feed_tokens" in e["name"]]       # the first kernel of a fed step
+    step = events[marks[2]:marks[3]]
+    t0 = prev_end = step[0]["ts"]
+    rows = []
+    for e in step:
+        end = e["ts"] + e["dur"]
+        rows.append((e["name"], tuple(e["args"].get("grid", ())), e["ts"] - t0, e["dur"], end - prev_end))
+        prev_end = max(prev_end, end)
+    return rows
+
+
+def format_timeline(rows) -> str:
+    short = lambda n: n.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0]
+    span = max(r[2] + r[3] for r in rows)
+    out = [f"one decode step: {len(rows)} kernels, {span:.1f} us from the first kernel's start to the last one's end",
+           "by kernel: launches, sum of durations (they overlap), sum added to the chain of dependent launches"]
+    agg: dict = {}
+    for name, grid, _, dur, adds in rows:
+        a = agg.setdefault((short(name), grid), [0, 0.0, 0.0])
+        a[0] += 1
+        a[1] += dur
+        a[2] += adds
+    for (name, grid), (n, dur, adds) in sorted(agg.items(), key=lambda kv: -kv[1][2]):
+        out.append(f"{n:4d} {dur:9.1f} us {adds:8.1f} us  {adds / n:6.1f} us each  {name} grid {grid}")
+    return "\n".join(out)
+
+
+def decode_kernel_trace(engine: Engine, batch: int, prompt_len: int, seed: int = 0) -> str:
+    """Time stamps from inside the cluster product kernels of one decode step (needs a build with
+    GIBBS_B200_NVCC_FLAGS=-DGB_DECODE_TRACE and GIBBS_B200_DECODE_ROWS >= batch): for the first CTA
+    of every launch, when its phases were reached, in microseconds after the kernel's start."""
+    import ctypes
+    from ..ops.library import library
+    lib = library("tensorcore")
+    if not hasattr(lib, "gb_linear_decode_trace"):
+        raise RuntimeError("build with GIBBS_B200_NVCC_FLAGS=-DGB_DECODE_TRACE to trace the cluster product")
+    one_step, close = _decode_stepper(engine, batch, prompt_len, seed)
+    for _ in range(6):
+        one_step()
+    torch.cuda.synchronize()
+    buf = torch.zeros(4096 * 48, dtype=torch.int64, device=engine.device)
+    if lib.gb_linear_decode_trace(ctypes.c_void_p(buf.data_ptr())) != 0:
+        raise RuntimeError("gb_linear_decode_trace failed")
+    one_step()
+    torch.cuda.synchronize()
+    lib.gb_linear_decode_trace(ctypes.c_void_p(0))
+    close()
+    t = buf.cpu().numpy().reshape(4096, 3, 16)
+    n = int((t[:, 0, 0] != 0).sum())
+    order = np.argsort(t[:n, 0, 0])
+    lines = ["grid*1000+ranks, 10*normed+mode | start | TMA thread: first weights out, dependency met, last load out | "
+             "MMA thread: all issued | producer/epilogue thread: dependency met, scales, first group, all groups, "
+             "accumulator ready | slices sent, cluster barrier passed, end | what the kernel adds to the chain (us)"]
+    base = prev_end = t[order[0], 0, 0] if n else 0
+    for i in order:
+        a = t[i]
+        s0 = a[0, 0]
+        rel = lambda v: (v - s0) / 1e3 if v else -1.0
+        end = max(a[0, 8], a[1, 8], a[2, 8])
+        lines.append(f"{a[0, 14]:7d} {a[0, 15]:3d} | {(s0 - base) / 1e3:8.1f} | {rel(a[0, 1]):5.1f} {rel(a[0, 2]):5.1f} "
+                     f"{rel(a[0, 3]):5.1f} | {rel(a[1, 2]):5.1f} | {rel(a[2, 1]):5.1f} {rel(a[2, 2]):5.1f} "
+                     f"{rel(a[2, 3]):5.1f} {rel(a[2, 4]):5.1f} {rel(a[2, 5]):5.1f} | {rel(a[2, 6]):5.1f} "
+                     f"{rel(a[2, 7]):5.1f} {rel(end):5.1f} | {(end - prev_end) / 1e3:5.1f}")
+        prev_end = max(prev_end, end)
+    return "\n".join(lines)
+
+
 def measure_decode_e2e(generator, batch: int, prompt_len: int, steps: int, warmup: int, seed: int = 0,
                        repeats: int = 1) -> dict:
     """The same through the public entry point's scheduler: prompts come from host

@@ -29,13 +29,14 @@ from ..parts.base import NotPlannable
 
 OP = np.dtype([("op", "<i4"), ("flags", "<i4"), ("a", "<i8", (24,)), ("f", "<f8", (3,))])
 
-P_EMBED, P_RMSNORM, P_LINEAR, P_SHORT_CONV, P_QKROPE, P_ATTENTION, P_SWIGLU = range(1, 8)
+P_EMBED, P_RMSNORM, P_LINEAR, P_SHORT_CONV, P_QKROPE, P_ATTENTION, P_SWIGLU, P_SCALE_SOFTCAP = range(1, 9)
 LF_RESIDUAL, LF_PARTIALS_IF_ONE_EACH, LF_PARTIALS, LF_NORMED = 1, 2, 4, 8
 NF_LAZY = 1
 
 SYM_BIT = 1 << 62
 (S_N, S_R, S_W, S_MAXQ, S_MAXCTX, S_ONE_EACH, S_TOKEN_IDS, S_TOK_REQ, S_TOK_POS, S_Q_START, S_Q_LEN, S_START_POS,
  S_CTX_LEN, S_SLOT_IDS, S_WANT_ROWS, S_LOGITS, S_BLOCK_TABLE0) = range(17)
+S_TABLE_STRIDE = 31          # entries per request in the step's block tables
 N_SYMBOLS = 32
 
 
@@ -50,7 +51,7 @@ _FUNCTIONS = [("core", "gb_embed"), ("core", "gb_rmsnorm"), ("core", "gb_linear_
               ("tensorcore", "gb_attention_tcgen05_supported"), ("core", "gb_swiglu"),
               ("tensorcore", "gb_linear_decode"), ("tensorcore", "gb_linear_decode_parts"),
               ("tensorcore", "gb_linear_decode_supported"), ("core", "gb_add_pending"),
-              ("tensorcore", "gb_linear_decode_normed_ok")]
+              ("tensorcore", "gb_linear_decode_normed_ok"), ("core", "gb_scale_softcap")]
 
 
 def register_op(name: str, function) -> int:
@@ -241,13 +242,14 @@ class PlanBuilder:
         q_out = self.buffer("q_rotated", heads * hd)
         self.emit(P_QKROPE,
                   [qkv.data_ptr(), qkv.stride(0), self.keep(q_gain), self.keep(k_gain),
-                   self.keep(None if rotary is None else rotary.inv_freq), 0 if rotary is None else rotary.rotary_dim,
+                   self.keep(None if rotary is None else rotary.table), 0 if rotary is None else rotary.rotary_dim,
                    0 if rotary is None else int(rotary.adjacent_pairs), kv_view.block_table.group, kp.shape[2],
                    self.keep(kp) if write_kv else 0, self.keep(vp) if write_kv else 0, kp.shape[0] if write_kv else 0,
                    heads, kv_heads, hd, int(write_kv), ops.dtype_code(qkv.dtype), q_out.data_ptr(), bt_stride], [eps],
                   label="qk_rope")
 
-    def attention(self, heads: int, kv_heads: int, hd: int, scale: float, window: int, kv_view, bt_stride: int):
+    def attention(self, heads: int, kv_heads: int, hd: int, scale: float, window: int, kv_view, bt_stride: int,
+                  softcap: float = 0.0):
         out = self.buffer("mixed", heads * hd)
         kp, vp = kv_view.k_pages, kv_view.v_pages
         # the decode kernel's key splits: every split leaves (head_dim + 2) floats per (token, head); a
@@ -259,8 +261,13 @@ class PlanBuilder:
         self.attn_ws_floats = max(self.attn_ws_floats, need)
         self.emit(P_ATTENTION, [out.data_ptr(), out.stride(0), self.keep(kp), self.keep(vp), kv_view.block_table.group,
                                 kp.shape[2], kp.shape[0], heads, kv_heads, hd, int(window or 0),
-                                ops.dtype_code(out.dtype), bt_stride], [scale], label="attention")
+                                ops.dtype_code(out.dtype), bt_stride], [scale, softcap], label="attention")
         return out
+
+    def scale_softcap(self, values: int, columns: int, rows_symbol: int, scale: float, cap: float) -> None:
+        """values <- values * scale, then cap * tanh(values / cap) when cap > 0; ``values`` is a
+        symbol (the step's logits) or an address, [rows, columns] float32."""
+        self.emit(P_SCALE_SOFTCAP, [values, columns, sym(rows_symbol)], [scale, cap], label="scale_softcap")
 
     def swiglu(self, gate_up: torch.Tensor, inner: int) -> torch.Tensor:
         out = self.buffer("act", inner)
@@ -344,6 +351,7 @@ class StepPlan:
                      (S_CTX_LEN, 6), (S_SLOT_IDS, 7), (S_WANT_ROWS, 8)):
             s[k] = meta_ptr + 4 * offs[i]
         s[S_LOGITS] = logits_ptr
+        s[S_TABLE_STRIDE] = mb
         for g in range(self.n_groups):
             s[S_BLOCK_TABLE0 + g] = meta_ptr + 4 * (offs[9] + g * n_requests * mb)
         rc = self.lib.gb_plan_run(ctypes.byref(self._run), ops._STREAM if ops._STREAM is not None else ops._stream())
@@ -357,11 +365,11 @@ class StepPlan:
 def build_step_plan(model, cache, cap: int, max_requests: int) -> StepPlan:
     """The plan of ``model`` over ``cache`` for steps of up to ``cap`` tokens.  Raises
     NotPlannable if some part of the model cannot be written as operations."""
-    if len(cache.groups) > N_SYMBOLS - S_BLOCK_TABLE0:
+    if len(cache.groups) > S_TABLE_STRIDE - S_BLOCK_TABLE0:
         raise NotPlannable(f"{len(cache.groups)} cache groups")
     with_tc = "tensorcore" in model.kernel_libraries()
     b = PlanBuilder(model.rt, model.hidden_size, cap, max_requests, with_tc)
-    b.bt_stride = cache.max_blocks
+    b.bt_stride = sym(S_TABLE_STRIDE)          # a step packs only as many table columns as its longest context needs
     views = cache.views([TableRef(g) for g in range(len(cache.groups))], SlotRef(), [])
     model.plan_ops(b, views)
     return StepPlan(b, len(cache.groups))

@@ -55,6 +55,47 @@ from ..sampling.params import SamplingParams
 from .step import StepEntry
 
 MAX_PREFILL_CHUNK = 2048        # src/scheduler/mod.rs:341
+INITIAL_PREFILL_CHUNK = 64      # src/scheduler/mod.rs:345: the budget before a prefill has been timed
+IDLE_STEP_S = 0.1               # src/scheduler/mod.rs:348: with nothing decoding a step's prefill takes about this long
+
+
+class PrefillTuner:
+    """Measured costs that size a step's prompt budget, after MisterTK/gibbs ``PrefillTuner``
+    (``src/scheduler/mod.rs:350-403``): 64 tokens before any prefill has been timed; while
+    requests decode, as many prompt tokens as cost about one decode round (1 until a decode
+    round has been timed), so that prompts take roughly half of each step; with nothing
+    decoding, as many as take about 100 ms; always within [1, 2048].  Both costs are
+    exponential averages (0.75 old + 0.25 new) of what the scheduler's steps report.
+
+    Here a step is one batch, so only steps that are all prompt or all decode tell the two
+    costs apart; those are the ones recorded."""
+
+    def __init__(self, whole_prompt: bool = False):
+        self.prefill_s_per_token = 0.0
+        self.decode_round_s = 0.0
+        self.whole_prompt = whole_prompt        # one-shot generation: a prompt in one step
+
+    def budget(self, decoding: bool) -> int:
+        if self.whole_prompt:
+            return 1 << 30
+        if self.prefill_s_per_token == 0.0:
+            return INITIAL_PREFILL_CHUNK
+        if decoding:
+            if self.decode_round_s == 0.0:
+                return 1                         # decode cost not timed yet: the step goes to the decoding requests
+            target = self.decode_round_s
+        else:
+            target = IDLE_STEP_S
+        return max(1, min(MAX_PREFILL_CHUNK, int(target / self.prefill_s_per_token)))
+
+    def record(self, prefill: tuple, decode: tuple) -> None:
+        """``prefill`` = (seconds, prompt tokens), ``decode`` = (seconds, decoded tokens) of one step."""
+        def ewma(old, new):
+            return new if old == 0.0 else 0.75 * old + 0.25 * new
+        if prefill[1] > 0 and decode[1] == 0:
+            self.prefill_s_per_token = ewma(self.prefill_s_per_token, prefill[0] / prefill[1])
+        elif decode[1] > 0 and prefill[1] == 0:
+            self.decode_round_s = ewma(self.decode_round_s, decode[0])
 
 
 class FinishReason(str, Enum):
@@ -82,6 +123,7 @@ class Sequence_:
     state: SeqState = SeqState.WAITING
     finish: Optional[FinishReason] = None
     error: Optional[str] = None
+    logprobs: list = field(default_factory=list)    # a TokenLogprobInfo per emitted token, when asked for
     admitted: int = -1                              # admission order (for preemption)
     preemptions: int = 0
     cancelled: bool = False
@@ -120,6 +162,7 @@ class StepOutput:
     emitted: list = field(default_factory=list)     # (sequence id, token)
     finished: list = field(default_factory=list)    # (sequence id, FinishReason)
     preempted: list = field(default_factory=list)   # sequence ids
+    logprobs: list = field(default_factory=list)    # (sequence id, TokenLogprobInfo) of emitted tokens that asked
 
 
 @dataclass
@@ -143,13 +186,17 @@ class _FailedLaunch:
 class Scheduler:
     def __init__(self, engine, sampler: Callable, max_batch_tokens: int = MAX_PREFILL_CHUNK,
                  max_running: Optional[int] = None, eos_ids: Sequence[int] = (), seed: int = 0,
-                 on_token: Optional[Callable] = None, overlap: bool = False):
+                 on_token: Optional[Callable] = None, overlap: bool = False,
+                 tuner: Optional[PrefillTuner] = None, clock: Callable = time.perf_counter):
         """engine: ``open/close/step/can_run/max_context/max_requests``;
         sampler: ``(logits, params, seeds, counters) -> token ids``.
         ``overlap`` needs ``sampler.sample_async(...)`` (ids that stay on the
         device, with ``wait()`` for the host's copy) and an engine whose
-        ``step`` takes ``feed``."""
+        ``step`` takes ``feed``.  ``tuner``: a ``PrefillTuner`` sizes each step's
+        prompt budget from measured costs, below ``max_batch_tokens``; without one the
+        budget is ``max_batch_tokens``.  ``clock``: what steps are timed with."""
         self.engine, self.sampler = engine, sampler
+        self.tuner, self.clock = tuner, clock
         self.overlap = bool(overlap)
         if self.overlap and not hasattr(sampler, "sample_async"):
             raise ValueError("overlap needs a sampler with sample_async")
@@ -238,10 +285,17 @@ class Scheduler:
             self._admissions += 1
             self.running.append(seq)
 
+    def _prompt_budget(self, n_decoding: int) -> int:
+        """Prompt tokens this step may take beside ``n_decoding`` decoded tokens."""
+        budget = max(self.max_batch_tokens - n_decoding, 0)
+        if self.tuner is not None:
+            budget = min(budget, self.tuner.budget(n_decoding > 0))
+        return budget
+
     def _plan(self) -> list:
         """(sequence, number of tokens) for this step."""
         plan = [(s, 1) for s in self.running if s.decoding]
-        budget = max(self.max_batch_tokens - len(plan), 0)
+        budget = self._prompt_budget(len(plan))
         prefilling = sorted((s for s in self.running if not s.decoding), key=lambda s: (s.remaining, s.submitted))
         if not prefilling:
             return plan
@@ -287,7 +341,7 @@ class Scheduler:
         for seq in [s for s in self.running if s.cancelled]:
             self._finish(seq, FinishReason.CANCELLED, out)
         decoding_now = sum(1 for s in self.running if s.decoding)
-        self._admit(max(self.max_batch_tokens - decoding_now, 1), out)
+        self._admit(max(self._prompt_budget(decoding_now), 1), out)
 
         plan = self._plan()
         # Pages: drop the most recently admitted request until the step fits.
@@ -321,8 +375,10 @@ class Scheduler:
                 n_prefill += n
         # ids may stay on the device when every request of the step picks one
         # (and none only ran to fill its cache, max_new_tokens == 0)
-        lag = self.overlap and len(samplers) == len(plan) and all(s.params.max_new_tokens > 0 for s in samplers)
-        t0 = time.perf_counter()
+        # and nobody asks what the distribution said about its token: that is read from the logits at once)
+        lag = self.overlap and len(samplers) == len(plan) and all(
+            s.params.max_new_tokens > 0 and s.params.top_logprobs is None for s in samplers)
+        t0 = self.clock()
         try:
             logits = self.engine.step(entries)
             args = (logits, [s.params for s in samplers], [s.seed for s in samplers],
@@ -331,6 +387,7 @@ class Scheduler:
                 pending, picked = self.sampler.sample_async(*args), []
             else:
                 pending, picked = None, (self.sampler(*args) if samplers else [])
+                infos = self._logprob_infos(logits, samplers, picked)
         except Exception as e:  # the step failed as a whole: its requests end with an error
             if isinstance(e, (OutOfPages, KeyboardInterrupt)):
                 raise
@@ -344,12 +401,28 @@ class Scheduler:
             self._inflight = _InFlight(samplers, pending, t0, n_prefill, n_decode)
             out.active_sequences = len(self.running)
             return out
-        self._emit(samplers, picked, out)
-        self._account(out, time.perf_counter() - t0, n_prefill, n_decode)
+        self._emit(samplers, picked, out, infos)
+        self._account(out, self.clock() - t0, n_prefill, n_decode)
         out.active_sequences = len(self.running)
         return out
 
-    def _emit(self, samplers, picked, out: StepOutput) -> None:
+    def _logprob_infos(self, logits, samplers, picked) -> dict:
+        """{sequence id: TokenLogprobInfo} for the requests of a step that ask for it (the
+        reference computes it from the same logits the token was picked from,
+        src/scheduler/mod.rs:76-80, 1404)."""
+        rows = [i for i, s in enumerate(samplers) if s.params.top_logprobs is not None]
+        if not rows:
+            return {}
+        k = max(samplers[i].params.top_logprobs for i in rows)
+        infos = self.sampler.logprob_info(logits, picked, k)       # every row of the step; those asked for are kept
+        out = {}
+        for i in rows:
+            info, want = infos[i], samplers[i].params.top_logprobs
+            out[samplers[i].id] = info if want == k else type(info)(
+                info.chosen_id, info.chosen_prob, info.top_candidates[:want], info.entropy)
+        return out
+
+    def _emit(self, samplers, picked, out: StepOutput, infos: Optional[dict] = None) -> None:
         """What the picked ids mean for their requests: emitted, or the end."""
         for s, tok in zip(samplers, picked):
             if s.state != SeqState.RUNNING:
@@ -363,23 +436,27 @@ class Scheduler:
                 continue
             s.output.append(tok)
             out.emitted.append((s.id, tok))
+            if infos and s.id in infos:
+                s.logprobs.append(infos[s.id])
+                out.logprobs.append((s.id, infos[s.id]))
             out.tokens_generated += 1
             if self.on_token:
                 self.on_token(s.id, tok)
             if len(s.prompt) + len(s.output) >= self.ctx or len(s.output) >= s.params.max_new_tokens:
                 self._finish(s, FinishReason.LENGTH, out)
 
-    @staticmethod
-    def _account(out: StepOutput, dt: float, n_prefill: int, n_decode: int) -> None:
+    def _account(self, out: StepOutput, dt: float, n_prefill: int, n_decode: int) -> None:
         total = max(n_prefill + n_decode, 1)
         out.prefill = (dt * n_prefill / total, n_prefill)
         out.decode = (dt * n_decode / total, n_decode)
+        if self.tuner is not None:
+            self.tuner.record(out.prefill, out.decode)
 
     # -- token feedback -----------------------------------------------------------
     def _collect(self, flight: _InFlight, out: StepOutput) -> None:
         """Wait for the ids of a launched step and do what they ask for."""
         self._emit(flight.seqs, flight.pending.wait(), out)
-        self._account(out, time.perf_counter() - flight.launched, flight.n_prefill, flight.n_decode)
+        self._account(out, self.clock() - flight.launched, flight.n_prefill, flight.n_decode)
 
     def _launch_fed(self, prev: _InFlight):
         """The decode step after ``prev``, launched on the ids ``prev`` left on the
@@ -405,7 +482,7 @@ class Scheduler:
         entries = [StepEntry(s.id, [0], [0]) for s in seqs]
         if not self.engine.can_run(entries):
             return None                             # preemption is decided with every id known
-        t0 = time.perf_counter()
+        t0 = self.clock()
         try:
             logits = self.engine.step(entries, feed=(prev.pending.device_ids, places))
         except OutOfPages:

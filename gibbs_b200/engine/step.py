@@ -94,13 +94,15 @@ class StepBuilder:
         self._record(turn)
         return self._state(self.dev_meta, offs, entries, rcs, n_tok, n_req, n_want)
 
-    def _layout(self, n_tok: int, n_req: int, n_want: int, fed: bool = False):
+    def _layout(self, n_tok: int, n_req: int, n_want: int, fed: bool = False, mb: Optional[int] = None):
         """Offsets (in int32) of the sections of the metadata buffer, each
         16-byte aligned: token ids, token->request, token->position; per
         request first row, count, length before, length after, slot; wanted
         rows; one block table per group; and, when ``fed``, for each token the
-        place among the ids picked on the device that it comes from (or -1)."""
-        n_groups, mb = len(self.cache.groups), self.cache.max_blocks
+        place among the ids picked on the device that it comes from (or -1).
+        ``mb``: entries per request in a block table (default: as many as the
+        context allows; a step may pack only what its longest request needs)."""
+        n_groups, mb = len(self.cache.groups), (self.cache.max_blocks if mb is None else mb)
         sizes = [n_tok, n_tok, n_tok, n_req, n_req, n_req, n_req, n_req, max(n_want, 1), n_groups * n_req * mb,
                  n_tok if fed else 0]
         offs, o = [], 0
@@ -109,7 +111,7 @@ class StepBuilder:
             o += _align4(sz)
         return offs, o
 
-    def _fill_staging(self, entries, rcs, offs, n_tok, n_req, n_want, fed_from=None) -> int:
+    def _fill_staging(self, entries, rcs, offs, n_tok, n_req, n_want, fed_from=None, mb: Optional[int] = None) -> int:
         turn = self._turn
         self._turn = (turn + 1) % len(self._staging)
         if self._staging_evt[turn] is not None:
@@ -130,7 +132,7 @@ class StepBuilder:
                 wr[w_i] = row + int(w)
                 w_i += 1
             row += n
-        n_groups, mb = len(self.cache.groups), self.cache.max_blocks
+        n_groups, mb = len(self.cache.groups), (self.cache.max_blocks if mb is None else mb)
         if n_groups:
             bt = buf[offs[9]:offs[9] + n_groups * n_req * mb].reshape(n_groups, n_req, mb)
             self.cache.fill_block_tables(rcs, bt)
@@ -147,11 +149,11 @@ class StepBuilder:
         evt.record()
         self._staging_evt[turn] = evt
 
-    def _state(self, dev, offs, entries, rcs, n_tok, n_req, n_want, fixed: bool = False):
+    def _state(self, dev, offs, entries, rcs, n_tok, n_req, n_want, fixed: bool = False, mb: Optional[int] = None):
         """The step's state and cache views over the device metadata buffer
         ``dev``.  ``fixed`` (graph capture): launch-sizing hints that do not
         depend on the requests' current lengths."""
-        n_groups, mb = len(self.cache.groups), self.cache.max_blocks
+        n_groups, mb = len(self.cache.groups), (self.cache.max_blocks if mb is None else mb)
 
         def view(i, n):
             return dev[offs[i]:offs[i] + n]
@@ -326,9 +328,13 @@ class Engine:
         n_req = len(entries)
         n_want = sum(len(e.want) for e in entries)
         bld = self.builder
-        offs, total = bld._layout(n_tok, n_req, n_want, fed_from is not None)
-        turn = bld._fill_staging(entries, rcs, offs, n_tok, n_req, n_want, fed_from)
         decode = self.use_graphs and n_tok == n_req and n_want == n_req
+        # A step packs only as many block-table columns as its longest request needs; decode
+        # steps, whose metadata layout is frozen into a CUDA graph, keep the context's full width.
+        mb = self.cache.max_blocks if decode else \
+            max(1, max(self.cache.pages_needed(rc.length + len(e.tokens)) for e, rc in zip(entries, rcs)))
+        offs, total = bld._layout(n_tok, n_req, n_want, fed_from is not None, mb)
+        turn = bld._fill_staging(entries, rcs, offs, n_tok, n_req, n_want, fed_from, mb)
 
         def fed(dev):
             if fed_from is not None:
@@ -350,14 +356,14 @@ class Engine:
             fed(dev)
             before = ops.launch_count()
             if self.plan is not None:
-                args = (n_tok, n_req, n_want, max(len(e.tokens) for e in entries), dev.data_ptr(), offs)
+                args = (n_tok, n_req, n_want, max(len(e.tokens) for e in entries), dev.data_ptr(), offs, mb)
                 max_ctx = self.max_context if decode else max(rc.length + len(e.tokens) for e, rc in zip(entries, rcs))
                 with ops.launching_on():
                     logits = self._run_plan(*args, max_ctx)
                 step = caches = None
             else:
                 args = None
-                step, caches = bld._state(dev, offs, entries, rcs, n_tok, n_req, n_want, fixed=decode)
+                step, caches = bld._state(dev, offs, entries, rcs, n_tok, n_req, n_want, fixed=decode, mb=mb)
                 with ops.launching_on():
                     logits = self.model.forward(step, caches)
             if decode:
@@ -373,10 +379,10 @@ class Engine:
             buf = self._graph_bufs[batch] = torch.empty(max(size, total), dtype=torch.int32, device=self.device)
         return buf
 
-    def _run_plan(self, n_tok, n_req, n_want, max_q_len, meta_ptr, offs, max_ctx) -> Optional[torch.Tensor]:
+    def _run_plan(self, n_tok, n_req, n_want, max_q_len, meta_ptr, offs, mb, max_ctx) -> Optional[torch.Tensor]:
         """One call into the step plan; the logits get a buffer of their own."""
         logits = torch.empty((n_want, self.vocab_size), dtype=torch.float32, device=self.device) if n_want else None
-        self.plan.run(n_tok, n_req, n_want, max_q_len, max_ctx, meta_ptr, offs, self.cache.max_blocks,
+        self.plan.run(n_tok, n_req, n_want, max_q_len, max_ctx, meta_ptr, offs, mb,
                       logits.data_ptr() if n_want else 0)
         return logits
 

@@ -575,6 +575,18 @@ def short_conv_partials(bcx: Partials, taps: torch.Tensor, bias: Optional[torch.
     return out
 
 
+def _rotary_table(inv_freq: Optional[torch.Tensor], rotary_dim: int) -> Optional[torch.Tensor]:
+    """The table the rotary kernels read: rotary_dim / 2 frequencies followed by the factor on
+    cosines and sines.  Frequencies alone get the factor 1 appended (``parts.base.Rotary``
+    hands over the finished table)."""
+    if inv_freq is None:
+        return None
+    half = rotary_dim // 2
+    if inv_freq.numel() == half:
+        return torch.cat([inv_freq.to(torch.float32).reshape(-1), torch.ones(1, dtype=torch.float32, device=inv_freq.device)])
+    return _f32vec(inv_freq, half + 1, "rotary table")
+
+
 def _check_pages(k_pages, v_pages, kv_heads, hd, dtype, what):
     for p in (k_pages, v_pages):
         if p.dim() != 4 or p.shape[1] != kv_heads or p.shape[3] != hd or not p.is_contiguous() or p.dtype != dtype:
@@ -602,8 +614,7 @@ def qk_norm_rope_store(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: i
         raise KernelError(f"qk_norm_rope_store: rows of {qkv.shape[1]} columns, {cols} needed")
     _f32vec(q_gain, head_dim, "q gain")
     _f32vec(k_gain, head_dim, "k gain")
-    if inv_freq is not None:
-        _f32vec(inv_freq, rotary_dim // 2, "inv_freq")
+    inv_freq = _rotary_table(inv_freq, rotary_dim)
     _i32(tok_req, "tok_req"), _i32(tok_pos, "tok_pos"), _i32(block_table, "block_table"), _i32(status, "status")
     page_size, n_pages = 1, 0
     if write:
@@ -640,8 +651,7 @@ def qk_norm_rope_store_partials(qkv: Partials, q_out: torch.Tensor, heads: int, 
     _f32vec(qkv.bias, cols, "qkv bias")
     _f32vec(q_gain, head_dim, "q gain")
     _f32vec(k_gain, head_dim, "k gain")
-    if inv_freq is not None:
-        _f32vec(inv_freq, rotary_dim // 2, "inv_freq")
+    inv_freq = _rotary_table(inv_freq, rotary_dim)
     _i32(tok_req, "tok_req"), _i32(tok_pos, "tok_pos"), _i32(block_table, "block_table"), _i32(status, "status")
     page_size, n_pages = 1, 0
     if write:
@@ -659,18 +669,21 @@ def qk_norm_rope_store_partials(qkv: Partials, q_out: torch.Tensor, heads: int, 
 
 def paged_attention(q: torch.Tensor, heads: int, kv_heads: int, head_dim: int, k_pages: torch.Tensor,
                     v_pages: torch.Tensor, block_table: torch.Tensor, tok_req: torch.Tensor, tok_pos: torch.Tensor,
-                    scale: float, window: int, out: torch.Tensor, status: torch.Tensor, hints=None) -> torch.Tensor:
+                    scale: float, window: int, out: torch.Tensor, status: torch.Tensor, hints=None,
+                    softcap: float = 0.0) -> torch.Tensor:
     """out[t, h, :] = softmax over visible keys of (q.K)*scale, times V; q may be
     a column slice of a wider row (its row stride is passed on).  ``hints`` is
     the step's state (per-request starts and lengths and the longest portion):
-    with it, bfloat16 attention runs on the tensor cores."""
+    with it, bfloat16 attention runs on the tensor cores.  ``softcap`` > 0: the
+    scaled scores pass through cap * tanh(s / cap) (the generic kernel only)."""
     _need_cuda(q, k_pages, v_pages, block_table, tok_req, tok_pos, out, status)
     n = q.shape[0]
     if q.shape[1] != heads * head_dim or out.shape != (n, heads * head_dim) or q.dtype != out.dtype:
         raise KernelError("paged_attention: q and out must be [n, heads*head_dim] of one dtype")
     _check_pages(k_pages, v_pages, kv_heads, head_dim, q.dtype, "paged_attention")
     _i32(tok_req, "tok_req"), _i32(tok_pos, "tok_pos"), _i32(block_table, "block_table"), _i32(status, "status")
-    if hints is not None and q.dtype == torch.bfloat16 and attention_tc_supported(q, out, heads, kv_heads, head_dim):
+    if hints is not None and softcap <= 0 and q.dtype == torch.bfloat16 \
+            and attention_tc_supported(q, out, heads, kv_heads, head_dim):
         return _attention_tc(q, heads, kv_heads, head_dim, k_pages, v_pages, block_table, scale, window, out,
                              status, hints)
     lib = library("core")
@@ -679,8 +692,19 @@ def paged_attention(q: torch.Tensor, heads: int, kv_heads: int, head_dim: int, k
         _ptr(q), dtype_code(q.dtype), _c_ll(_rows(q, "q")), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
         _c_int(block_table.shape[1]), _c_int(k_pages.shape[2]), _c_int(k_pages.shape[0]), _ptr(tok_req),
         _ptr(tok_pos), _ptr(out), _c_ll(_rows(out, "out")), _c_int(n), _c_int(heads), _c_int(kv_heads),
-        _c_int(head_dim), _c_float(scale), _c_int(window or 0), _ptr(status), _stream()))
+        _c_int(head_dim), _c_float(scale), _c_float(softcap), _c_int(window or 0), _ptr(status), _stream()))
     return out
+
+
+def scale_softcap(x: torch.Tensor, scale: float, cap: float) -> torch.Tensor:
+    """x <- x * scale, then cap * tanh(x / cap) when cap > 0, in place on contiguous float32."""
+    _need_cuda(x)
+    lib = library("core")
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("scale_softcap: contiguous float32 values expected")
+    _launched(1)
+    check(lib, lib.gb_scale_softcap(_ptr(x), _c_ll(x.numel()), _c_float(scale), _c_float(cap), _stream()))
+    return x
 
 
 def attention_tc_supported(q, out, heads, kv_heads, head_dim) -> bool:
@@ -757,3 +781,26 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
                              _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(seed), _ptr(counter), _ptr(out),
                              _stream()))
     return out
+
+
+def logprob_info(logits: torch.Tensor, chosen: torch.Tensor, k: int):
+    """For each logits row: (probability of chosen[row], entropy of softmax(row), ids [rows, k] and
+    probabilities [rows, k] of the k most probable tokens), all on the device."""
+    _need_cuda(logits, chosen)
+    lib = library("core")
+    rows, vocab = logits.shape
+    if logits.dtype != torch.float32:
+        raise KernelError("logprob_info: logits are float32")
+    _i32(chosen, "logprob_info chosen")
+    if chosen.numel() != rows:
+        raise KernelError("logprob_info: one chosen id per row expected")
+    dev = logits.device
+    prob = torch.empty(rows, dtype=torch.float32, device=dev)
+    entropy = torch.empty(rows, dtype=torch.float32, device=dev)
+    ids = torch.empty((rows, k), dtype=torch.int32, device=dev)
+    probs = torch.empty((rows, k), dtype=torch.float32, device=dev)
+    _launched(1)
+    check(lib, lib.gb_logprob_info(_ptr(logits), _c_ll(_rows(logits, "logits")), _c_int(rows), _c_int(vocab),
+                                   _ptr(chosen), _c_int(k), _ptr(prob), _ptr(entropy), _ptr(ids), _ptr(probs),
+                                   _stream()))
+    return prob, entropy, ids, probs

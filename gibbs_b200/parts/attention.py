@@ -51,6 +51,9 @@ class GQAAttention(Mixer):
         self.window = params.get("window")
         self.shares_kv = bool(params.get("shares_kv", False))
         self.eps = float(params.get("qk_norm_eps", 0.0))
+        # scores pass through cap * tanh(s / cap) before the softmax (arch/lib/transformer.json5:69-75);
+        # 0: none.  Only the generic attention kernel applies one: with a cap the tensor-core kernels stand back.
+        self.softcap = float(params.get("softcap", 0.0) or 0.0)
         names = ["q_proj"] if self.shares_kv else ["q_proj", "k_proj", "v_proj"]
         dtypes = {tensors[n + ".weight"].dtype for n in names}
         if len(dtypes) != 1:
@@ -85,7 +88,7 @@ class GQAAttention(Mixer):
             raise RuntimeError("an attention layer with k/v projections was given a read-only cache")
         qkv = self.qkv.partials(h)
         rot = self.rotary
-        rope = (None if rot is None else rot.inv_freq, 0 if rot is None else rot.rotary_dim,
+        rope = (None if rot is None else rot.table, 0 if rot is None else rot.rotary_dim,
                 False if rot is None else rot.adjacent_pairs)
         pages = (None if self.shares_kv else kv.k_pages, None if self.shares_kv else kv.v_pages)
         a = self.heads * self.head_dim
@@ -101,7 +104,7 @@ class GQAAttention(Mixer):
         out = self.rt.empty(qkv.shape[0], a)
         ops.paged_attention(q, self.heads, self.kv_heads, self.head_dim, kv.k_pages, kv.v_pages,
                             kv.block_table, step.tok_req, step.tok_pos, self.scale, self.window or 0, out,
-                            step.status, hints=step)
+                            step.status, hints=step, softcap=self.softcap)
         self.out_proj(out, out=residual, accumulate=True)
 
     def plan_ops(self, plan, h, caches):
@@ -113,7 +116,7 @@ class GQAAttention(Mixer):
         plan.qk_norm_rope_store(qkv, self.heads, self.kv_heads, self.head_dim, self.q_gain, self.k_gain, self.eps,
                                 self.rotary, kv, not self.shares_kv, plan.bt_stride)
         out = plan.attention(self.heads, self.kv_heads, self.head_dim, self.scale, self.window or 0, kv,
-                             plan.bt_stride)
+                             plan.bt_stride, softcap=self.softcap)
         plan.linear(out, self.out_proj.weight, self.out_proj.bias, None, "residual", role="out_proj")
 
 

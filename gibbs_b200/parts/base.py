@@ -188,6 +188,12 @@ class Rotary:
     inv_freq: torch.Tensor    # float32 [rotary_dim / 2]
     rotary_dim: int
     adjacent_pairs: bool      # pairs (2j, 2j+1) instead of (j, j + rotary_dim/2)
+    mscale: float = 1.0       # the cosines and sines are multiplied by this
+
+    def __post_init__(self):
+        # what the kernels read: the frequencies followed by the factor
+        tail = torch.tensor([self.mscale], dtype=torch.float32, device=self.inv_freq.device)
+        object.__setattr__(self, "table", torch.cat([self.inv_freq.to(torch.float32).reshape(-1), tail]).contiguous())
 
 
 class PositionEncoding(Part):

@@ -29,9 +29,11 @@ class RotaryHalfSplit(PositionEncoding):
         if self.rotary_dim % 2 or not 0 < self.rotary_dim <= self.head_dim:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and at most head_dim {self.head_dim}")
         self.inv_freq = torch.from_numpy(_inv_freq_f32(self.rotary_dim, float(params["theta"]))).to(rt.device)
+        # the factor on cosines and sines (MisterTK/gibbs src/graph/cpu.rs:674-675); 1 unless given
+        self._rotary = Rotary(self.inv_freq, self.rotary_dim, self.adjacent, float(params.get("mscale", 1.0)))
 
     def rotary(self):
-        return Rotary(self.inv_freq, self.rotary_dim, self.adjacent)
+        return self._rotary
 
 
 class RotaryAdjacent(RotaryHalfSplit):

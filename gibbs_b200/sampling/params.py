@@ -12,6 +12,19 @@ DEFAULT_TOP_P = 0.9
 DEFAULT_TOP_K = 50
 GREEDY_BELOW = 1e-4          # temperature at or below this is exact argmax (src/runtime/lm.rs:1073)
 MAX_TOP_K = 64               # src/runtime/lm.rs:1161
+MAX_TOP_LOGPROBS = 32
+
+
+@dataclass(frozen=True)
+class TokenLogprobInfo:
+    """What the model's distribution said about one generated token (MisterTK/gibbs
+    ``TokenLogprobInfo``, ``src/scheduler/mod.rs:417-423``): its probability under the softmax
+    of the raw logits, the ``top_logprobs`` most probable tokens with theirs, and the
+    distribution's entropy."""
+    chosen_id: int
+    chosen_prob: float
+    top_candidates: tuple                    # ((token id, probability), ...), most probable first
+    entropy: float
 
 
 @dataclass(frozen=True)
@@ -22,12 +35,15 @@ class SamplingParams:
     max_new_tokens: int = DEFAULT_MAX_NEW_TOKENS
     seed: Optional[int] = None               # None: derived from the scheduler's seed and the request id
     stop_ids: tuple = ()                     # besides the model's own end-of-sequence ids
+    top_logprobs: Optional[int] = None       # report each token's probability, the entropy and this many candidates
 
     def __post_init__(self):
         if not 1 <= self.top_k <= MAX_TOP_K:
             raise ValueError(f"top_k {self.top_k} outside 1..{MAX_TOP_K}")
         if self.max_new_tokens < 0:
             raise ValueError(f"max_new_tokens {self.max_new_tokens}")
+        if self.top_logprobs is not None and not 1 <= self.top_logprobs <= MAX_TOP_LOGPROBS:
+            raise ValueError(f"top_logprobs {self.top_logprobs} outside 1..{MAX_TOP_LOGPROBS}")
 
     @property
     def resolved_temperature(self) -> float:

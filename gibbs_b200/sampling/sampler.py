@@ -12,7 +12,7 @@ from typing import Sequence
 import torch
 
 from .. import ops
-from .params import SamplingParams
+from .params import SamplingParams, TokenLogprobInfo
 
 _MASK = (1 << 64) - 1
 
@@ -71,6 +71,14 @@ class Sampler:
         """One token id per row of ``logits`` ([rows, vocab] float32 on the device)."""
         out = self.sample_device(logits, params, seeds, counters)
         return out.tolist()
+
+    def logprob_info(self, logits: torch.Tensor, chosen: Sequence[int], k: int) -> list:
+        """``TokenLogprobInfo`` of every row of ``logits`` for the ids in ``chosen`` (computed by
+        a kernel, read back to the host)."""
+        ids = torch.tensor([int(c) for c in chosen], dtype=torch.int32, device=self.device)
+        prob, entropy, top_ids, top_probs = (t.tolist() for t in ops.logprob_info(logits, ids, k))
+        return [TokenLogprobInfo(int(c), p, tuple((i, q) for i, q in zip(ti, tp) if i >= 0), e)
+                for c, p, e, ti, tp in zip(chosen, prob, entropy, top_ids, top_probs)]
 
     def sample_device(self, logits, params, seeds, counters) -> torch.Tensor:
         rows = logits.shape[0]

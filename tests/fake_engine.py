@@ -106,3 +106,15 @@ def expected_greedy(prompt, n_new, vocab, eos=()):
         toks.append(t)
         out.append(t)
     return out
+
+
+def fake_logprob_info(logits, chosen, k):
+    """Host twin of the sampler's ``logprob_info`` for the fake engine's one-hot logits."""
+    from gibbs_b200.sampling import TokenLogprobInfo
+    out = []
+    for row, c in zip(logits, chosen):
+        p = torch.softmax(row.double(), 0)
+        top = torch.argsort(-p, stable=True)[:k]
+        ent = float(-(p * torch.log(p)).sum())
+        out.append(TokenLogprobInfo(int(c), float(p[int(c)]), tuple((int(i), float(p[i])) for i in top), ent))
+    return out

@@ -195,3 +195,26 @@ def test_cluster_products_with_the_norm_inside_give_the_plain_logits(tmp_path_fa
     for x, y in zip(got[0], got[1]):
         for rid in x:
             assert np.array_equal(x[rid], y[rid]), rid
+
+
+def test_a_step_packs_only_the_block_table_columns_it_needs(tmp_path_factory):
+    """An engine laid out for a very long context (65,536 positions: 4,096 table entries a request)
+    copies a few hundred bytes of metadata for a short step, not its tables' full width; only decode
+    steps, whose layout a CUDA graph freezes, carry the full width.  The logits are those of an
+    engine laid out for a short context."""
+    from gibbs_b200 import Engine, StepEntry
+    folder, model = _setup(tmp_path_factory, "B", "bfloat16")
+    ids = random_ids(3, 60, 1000)
+    outs = []
+    for ctx in (512, 65536):
+        eng = Engine(model, n_pages=16, page_size=16, max_requests=4, max_context=ctx)
+        eng.open("a"), eng.open("b")
+        rows = [eng.step([StepEntry("a", ids[:37], [36]), StepEntry("b", ids[:5], [4])]).clone()]
+        if ctx == 65536:
+            offs, total = eng.builder._layout(42, 2, 2, False, 3)
+            assert total < 300 and eng.cache.max_blocks == 4096
+        for t in ids[37:45]:
+            rows.append(eng.step([StepEntry("a", [t], [0]), StepEntry("b", [t], [0])]).clone())
+        eng.check_status()
+        outs.append(torch.cat(rows))
+    assert torch.equal(outs[0], outs[1])

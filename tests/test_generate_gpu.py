@@ -333,3 +333,25 @@ def test_timing_mode_adds_up_the_operations_of_a_step_by_kind(tmp_path):
     assert all(ms > 0 for k, (_, ms) in table.items() if k != "rmsnorm")
     total = sum(ms for _, ms in table.values())
     assert 0 < total < 1000
+
+
+def test_top_logprobs_through_the_entry_point(tmp_path):
+    """A request that asks for top_logprobs gets a report per token whose chosen id is the emitted
+    token and whose numbers agree with the plain logits of the same history."""
+    from gibbs_b200 import SamplingParams
+    folder = make_folder(tmp_path, "A", std=0.08)
+    gen = _gen(folder, "float32")
+    prompt = random_ids(12, 9, 512)
+    sched = gen.scheduler(stop_at_eos=False)
+    sid = sched.submit(prompt, SamplingParams(temperature=0.0, max_new_tokens=5, top_logprobs=4))
+    sched.run()
+    seq = sched.sequences[sid]
+    assert len(seq.logprobs) == len(seq.output) == 5
+    logits = plain_logits(folder, prompt + seq.output)
+    for t, (tok, info) in enumerate(zip(seq.output, seq.logprobs)):
+        row = logits[len(prompt) + t - 1].astype(np.float64)
+        p = np.exp(row - row.max())
+        p /= p.sum()
+        assert info.chosen_id == tok == int(np.argmax(row))
+        assert abs(info.chosen_prob - p[tok]) < 1e-4 and abs(info.entropy + (p * np.log(p)).sum()) < 1e-3
+        assert [i for i, _ in info.top_candidates] == [int(i) for i in np.argsort(-row, kind="stable")[:4]]

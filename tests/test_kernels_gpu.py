@@ -1012,3 +1012,33 @@ def test_linear_simt_gives_the_same_bits_however_the_rows_are_cut(pair):
         part = torch.empty(hi - lo, n, dtype=torch.float32, device=DEV)
         ops.linear_simt(a[lo:hi], w, bias, part)
         assert torch.equal(part, whole[lo:hi]), (lo, hi)
+
+
+@pytest.mark.parametrize("vocab,k", [(1000, 5), (65536, 20), (50257, 1), (7, 32)])
+def test_logprob_info_matches_the_plain_rule(vocab, k):
+    """Probability of the chosen token, entropy and the k most probable tokens of every row,
+    against the reference's rule restated in float64 (src/scheduler/mod.rs:272-315); ties are
+    ordered by id, NaNs never count, rows with fewer than k numbers are padded with -1."""
+    from gibbs_b200 import ops
+    torch.manual_seed(vocab + k)
+    rows = 5
+    logits = torch.randn(rows, vocab) * 3
+    logits[1, : min(vocab, 4)] = 9.0                       # a tie at the top: lowest ids first
+    logits[2, ::2] = float("nan")
+    if vocab > 100:
+        logits[3, 50:] = float("nan")                      # fewer numbers than some k
+    chosen = torch.tensor([0, 1, 1, 3, vocab - 1], dtype=torch.int32)
+    prob, ent, ids, probs = ops.logprob_info(logits.to(DEV), chosen.to(DEV), k)
+    for r in range(rows):
+        row = logits[r].double()
+        ok = ~torch.isnan(row)
+        lse = torch.logsumexp(row[ok], 0)
+        p = torch.where(ok, torch.exp(row - lse), torch.zeros_like(row))
+        want_ent = float(-(p[ok] * (row[ok] - lse))[p[ok] > 1e-12].sum())
+        assert abs(ent[r].item() - want_ent) < 1e-3 * max(1.0, abs(want_ent))
+        assert abs(prob[r].item() - min(float(p[chosen[r]]), 1.0)) < 1e-5
+        order = sorted((i for i in range(vocab) if ok[i]), key=lambda i: (-float(row[i]), i))[:k]
+        got = [int(i) for i in ids[r].tolist()]
+        assert got[:len(order)] == order and all(i == -1 for i in got[len(order):])
+        for j, i in enumerate(order):
+            assert abs(probs[r, j].item() - float(p[i])) < 1e-5

@@ -739,3 +739,104 @@ def test_a_mixer_with_a_kernel_of_its_own_joins_the_step_plan(tmp_path, dtype):
     for a, b in zip(got[True], got[False]):
         for rid in a:
             assert np.array_equal(a[rid], b[rid]), rid
+
+
+# ---------------------------------------------------------------------------
+# constants another architecture would bring: a factor on the rotation, soft caps, a logit scale
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_rotary_factor_attention_soft_cap_and_logit_scale_are_parameters(dtype):
+    """None of these is LFM2's; each is a parameter of a built-in part, given by a plan: the factor
+    on the rotation's cosines and sines (position 'mscale'), a soft cap on the attention scores
+    (mixer 'softcap'; the generic attention kernel applies it, the tensor-core kernels stand back),
+    and the head's 'logit_scale' and 'softcap' (MisterTK/gibbs arch/lib/transformer.json5:59-75,
+    170-175; src/graph/cpu.rs:674-675).  The plan walker and the forward methods agree bit for bit."""
+    from gibbs_b200 import Engine
+    from gibbs_b200.config import ModelPlan, OrderEntry, PartSpec, prenorm_layer
+    from gibbs_b200.parts import build_model
+    from gibbs_b200.weights import TensorDict, expected_tensors
+    from helpers import first_wrong, run_trace_on_engine, trace_portions, trace_tail_decoded, trace_whole, random_ids
+    hidden, heads, kvh, hd, rd, inner, vocab, eps = 64, 4, 2, 32, 16, 128, 260, 1e-6
+    mscale, cap, logit_scale, logit_cap = 1.3, 2.0, 0.25, 5.0
+
+    def norm(name):
+        return PartSpec("rmsnorm", {"dim": hidden, "eps": eps}, {"weight": name})
+
+    attn = PartSpec("gqa_attention", {
+        "hidden": hidden, "heads": heads, "kv_heads": kvh, "head_dim": hd, "bias": False, "qk_norm": False,
+        "scale": 1 / math.sqrt(hd), "window": None, "softcap": cap,
+        "position": PartSpec("rope_half_split", {"head_dim": hd, "rotary_dim": rd, "theta": 1e4, "mscale": mscale})},
+        {"q_proj.weight": "a.q", "k_proj.weight": "a.k", "v_proj.weight": "a.v", "out_proj.weight": "a.o"})
+    ffn = PartSpec("swiglu", {"hidden": hidden, "inner": inner, "bias": False},
+                   {"gate.weight": "f.g", "up.weight": "f.u", "down.weight": "f.d"})
+    emb = PartSpec("token_embedding", {"vocab": vocab, "dim": hidden}, {"weight": "emb"})
+    head = PartSpec("lm_head", {"vocab": vocab, "dim": hidden, "logit_scale": logit_scale, "softcap": logit_cap},
+                    {"weight": "head"})
+    plan = ModelPlan("toy-caps", vocab, hidden, 256, emb, (prenorm_layer(norm("n0"), attn, norm("n1"), ffn),),
+                     (OrderEntry(0),), norm("fn"), head)
+    torch.manual_seed(31)
+    tensors = {}
+    for name, decl in expected_tensors(plan).items():
+        shape = decl.shapes[0]
+        t = 1 + 0.1 * torch.randn(shape) if len(shape) == 1 else \
+            torch.randn(shape) * (0.5 if name == "emb" else 2.0 / math.sqrt(shape[-1]))
+        tensors[name] = t.to(torch.bfloat16) if (dtype == "bfloat16" and len(shape) == 2) else t
+    model = build_model(plan, TensorDict(tensors), torch.bfloat16 if dtype == "bfloat16" else torch.float32, DEV)
+    w = {k: v.double() for k, v in tensors.items()}
+
+    def plain_model(ids):
+        n = len(ids)
+        pos = torch.arange(n)
+        x = w["emb"][torch.tensor(ids)]
+        h = plain.rms_norm(x, w["n0"], eps)
+        q = (h @ w["a.q"].T).reshape(n, heads, hd).clone()
+        k = (h @ w["a.k"].T).reshape(n, kvh, hd).clone()
+        v = (h @ w["a.v"].T).reshape(n, kvh, hd)
+        inv = plain.rope_inv_freq(rd, 1e4, torch.float64)
+        half = rd // 2
+        ang = (pos.float()[:, None] * inv.float()[None, :]).double()
+        c, s = (torch.cos(ang) * mscale)[:, None, :], (torch.sin(ang) * mscale)[:, None, :]
+        for t in (q, k):
+            a, b = t[..., :half].clone(), t[..., half:rd].clone()
+            t[..., :half], t[..., half:rd] = a * c - b * s, a * s + b * c
+        out = torch.zeros(n, heads, hd, dtype=torch.float64)
+        mask = pos[None, :] <= pos[:, None]
+        for hh in range(heads):
+            sc = (q[:, hh] @ k[:, hh // (heads // kvh)].T) / math.sqrt(hd)
+            sc = cap * torch.tanh(sc / cap)
+            sc = torch.where(mask, sc, torch.full_like(sc, float("-inf")))
+            out[:, hh] = torch.softmax(sc, -1) @ v[:, hh // (heads // kvh)]
+        x = x + out.reshape(n, heads * hd) @ w["a.o"].T
+        h = plain.rms_norm(x, w["n1"], eps)
+        g, u = h @ w["f.g"].T, h @ w["f.u"].T
+        x = x + (g / (1 + torch.exp(-g)) * u) @ w["f.d"].T
+        logits = plain.rms_norm(x, w["fn"], eps) @ w["head"].T / logit_scale
+        return (logit_cap * torch.tanh(logits / logit_cap)).numpy()
+
+    reqs = {f"r{i}": random_ids(90 + i, n, vocab) for i, n in enumerate([45, 6, 70])}
+    got = {}
+    for use_plan in (True, False):
+        eng = Engine(model, n_pages=24, page_size=8, max_requests=3, max_step_tokens=128, use_plan=use_plan)
+        assert (eng.plan is not None) == use_plan, eng.plan_refusal
+        got[use_plan] = [run_trace_on_engine(eng, steps) for steps in
+                         (trace_whole(reqs), trace_portions(reqs), trace_tail_decoded(reqs, tail=5))]
+        for run in got[use_plan]:
+            for rid, ids in reqs.items():
+                want = plain_model(ids)
+                assert np.abs(want).max() < logit_cap and np.abs(want).max() > 0.5 * logit_cap   # the cap bites
+                bad = first_wrong(run[rid], want, TOL[dtype] * (1 if dtype == "float32" else 2))
+                assert bad is None, f"{rid}: first wrong position {bad} (plan {use_plan})"
+    for a, b in zip(got[True], got[False]):
+        for rid in a:
+            assert np.array_equal(a[rid], b[rid]), rid
+    # without the factor, the cap or the scale the logits are others: the parameters are read
+    plain_attn = PartSpec("gqa_attention", {**attn.params, "softcap": 0.0,
+                                            "position": PartSpec("rope_half_split", {"head_dim": hd, "rotary_dim": rd, "theta": 1e4})},
+                          attn.tensors)
+    other = ModelPlan("toy-caps", vocab, hidden, 256, emb, (prenorm_layer(norm("n0"), plain_attn, norm("n1"), ffn),),
+                      (OrderEntry(0),), norm("fn"), head)
+    eng = Engine(build_model(other, TensorDict(tensors), model.rt.dtype, DEV), n_pages=24, page_size=8, max_requests=3,
+                 max_step_tokens=128)
+    differs = run_trace_on_engine(eng, trace_whole(reqs))
+    assert rel_err(differs["r2"], got[True][0]["r2"]) > 10 * TOL[dtype]

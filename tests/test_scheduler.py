@@ -343,3 +343,94 @@ def test_a_sampler_that_fails_after_a_fed_step_ends_the_requests():
     assert s.sequences[a].output == expected_greedy([1, 2, 3], 12, eng.vocab)[:len(s.sequences[a].output)]
     assert len(s.sequences[a].output) >= 2
     assert not eng.cache.live and eng.cache.free_pages() == [64]
+
+
+# ---------------------------------------------------------------- measured prompt budget
+def test_prefill_tuner_rules():
+    """The budget rules of the reference's PrefillTuner (src/scheduler/mod.rs:350-403)."""
+    from gibbs_b200.engine.scheduler import PrefillTuner
+    t = PrefillTuner()
+    assert t.budget(False) == 64 and t.budget(True) == 64          # nothing timed yet
+    t.record((0.010, 100), (0.0, 0))                               # 100 us a prompt token
+    assert t.budget(True) == 1                                     # no decode round timed: the step is the decoders'
+    assert t.budget(False) == 1000                                 # about 100 ms of prompt when nothing decodes
+    t.record((0.0, 0), (0.002, 4))                                 # a decode round of 2 ms
+    assert t.budget(True) == 20                                    # as many prompt tokens as cost one decode round
+    t.record((0.030, 100), (0.0, 0))                               # 300 us a token: 0.75 * 100 + 0.25 * 300 = 150
+    assert abs(t.prefill_s_per_token - 150e-6) < 1e-12 and t.budget(True) == 13
+    t.record((0.5, 10), (0.5, 3))                                  # a mixed step tells neither cost: not recorded
+    assert abs(t.prefill_s_per_token - 150e-6) < 1e-12 and t.decode_round_s == 0.002
+    fast = PrefillTuner()
+    fast.record((1e-6, 100), (0.0, 0))
+    assert fast.budget(False) == 2048                              # clamped to the largest portion
+    slow = PrefillTuner()
+    slow.record((10.0, 1), (0.0, 0))
+    slow.record((0.0, 0), (0.001, 1))
+    assert slow.budget(True) == 1                                  # never below one token
+    assert PrefillTuner(whole_prompt=True).budget(True) > 1 << 20
+
+
+def test_scheduler_sizes_prompt_portions_from_measured_costs():
+    """With a tuner, the scheduler times its steps and cuts prompt portions to cost about one decode
+    round while requests decode; the clock here is the fake engine's: 50 us a prompt token, 1 ms a
+    decode round."""
+    from gibbs_b200.engine.scheduler import PrefillTuner
+
+    class Clocked(FakeEngine):
+        now = 0.0
+
+        def step(self, entries, feed=None):
+            n_prompt = sum(len(e.tokens) for e in entries if len(e.tokens) > 1)
+            self.now += 50e-6 * n_prompt + (1e-3 if any(len(e.tokens) == 1 for e in entries) else 0.0)
+            return super().step(entries, feed)
+
+    eng = Clocked(n_pages=400, page_size=4, max_requests=4, max_context=1024)
+    tuner = PrefillTuner()
+    s = Scheduler(eng, argmax_sampler, max_batch_tokens=512, tuner=tuner, clock=lambda: eng.now)
+    a = s.submit([7, 8, 9], SamplingParams(temperature=0.0, max_new_tokens=40))
+    s.step()                                        # 3 prompt tokens: the first prefill is timed
+    assert abs(tuner.prefill_s_per_token - 50e-6) < 1e-9
+    s.step()                                        # a pure decode round is timed
+    assert abs(tuner.decode_round_s - 1e-3) < 1e-9
+    b = s.submit(list(range(1, 301)), GREEDY)
+    portions = []
+    while s.sequences[b].fed < 300:
+        before = s.sequences[b].fed
+        s.step()
+        portions.append(s.sequences[b].fed - before)
+    # one decode round (1 ms) buys 20 prompt tokens at 50 us each: every portion is that, the last the rest
+    assert portions[:-1] == [20] * (len(portions) - 1) and 0 < portions[-1] <= 20 and sum(portions) == 300
+    s.run()
+    assert s.sequences[a].output == expected_greedy([7, 8, 9], 40, eng.vocab)
+    assert s.sequences[b].output == expected_greedy(list(range(1, 301)), 8, eng.vocab)
+    # nothing decoding: about 100 ms of prompt (2,000 tokens), capped by the engine's own limit of 512
+    c = s.submit(list(range(1, 801)), GREEDY)
+    s.step()
+    assert s.sequences[c].fed == 512
+
+
+def test_top_logprobs_are_reported_for_the_requests_that_ask():
+    """A request with ``top_logprobs`` gets, per emitted token, its probability, that many
+    candidates and the entropy (src/scheduler/mod.rs:272-315, 414-423); its neighbour in the batch
+    gets none; with token feedback on, a step with such a request is read at once."""
+    from fake_engine import fake_logprob_info
+    eng = FakeEngine()
+    sampler = LaggingSampler(eng)
+    sampler.logprob_info = fake_logprob_info
+    s = Scheduler(eng, sampler, overlap=True)
+    a = s.submit([3, 4, 5], SamplingParams(temperature=0.0, max_new_tokens=6, top_logprobs=3))
+    b = s.submit([9, 9], SamplingParams(temperature=0.0, max_new_tokens=6))
+    reported = []
+    while s.has_work():
+        reported += s.step().logprobs
+    assert s.sequences[a].output == expected_greedy([3, 4, 5], 6, eng.vocab)
+    assert s.sequences[b].output == expected_greedy([9, 9], 6, eng.vocab)
+    infos = s.sequences[a].logprobs
+    assert [sid for sid, _ in reported] == [a] * 6 and [i for _, i in reported] == infos and not s.sequences[b].logprobs
+    for tok, info in zip(s.sequences[a].output, infos):
+        assert info.chosen_id == tok and len(info.top_candidates) == 3 and info.top_candidates[0][0] == tok
+        assert 0 < info.chosen_prob < 1 and info.entropy > 0
+        assert abs(info.top_candidates[0][1] - info.chosen_prob) < 1e-9
+    assert "launch fed" not in eng.events            # every step held a request whose logits had to be read
+    with pytest.raises(ValueError, match="top_logprobs"):
+        SamplingParams(top_logprobs=0)
