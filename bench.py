@@ -111,6 +111,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
+                    help="float32: the engine's true 32-bit twin on the same (bfloat16-rounded) weights; "
+                         "with --only prefill or --only decode (the benchmark line itself is bfloat16)")
     ap.add_argument("--skip-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--workload", choices=["serve700m", "long2p6b", "sweep"], default=None,
                     help="run one of the other reference workloads instead (prints its own JSON line)")
@@ -140,7 +143,10 @@ def main():
     cfg = Lfm2Config.from_dict(raw)
     peaks = B.load_peaks(os.path.join(ROOT, "MEASURED_PEAKS.json"))
     torch.manual_seed(0)
-    model = random_model(cfg, SEED, dtype="bfloat16", device="cuda:0")
+    if a.dtype != "bfloat16" and a.only not in ("prefill", "decode"):
+        print("bench.py: --dtype float32 goes with --only prefill or --only decode")
+        return 2
+    model = random_model(cfg, SEED, dtype=a.dtype, device="cuda:0", stored_dtype=torch.bfloat16)
 
     page_size = 16
     max_batch = max(64, a.batch)
@@ -150,7 +156,7 @@ def main():
 
     if a.only == "prefill":
         pre = B.measure_prefill(eng, PROMPT_LEN, warmup=a.warmup, runs=a.steps, seed=SEED)
-        print(json.dumps({"partial": "prefill", "prefill": pre}))
+        print(json.dumps({"partial": "prefill", "dtype": a.dtype, "prefill": pre}))
         return 0
     if a.only == "timeline":
         print(B.format_timeline(B.decode_timeline(eng, a.batch, PROMPT_LEN, seed=SEED)))
@@ -160,7 +166,7 @@ def main():
         return 0
     if a.only == "decode":
         dec = B.measure_decode(eng, a.batch, PROMPT_LEN, a.steps, a.warmup, seed=SEED)
-        print(json.dumps({"partial": "decode", "decode": dec}))
+        print(json.dumps({"partial": "decode", "dtype": a.dtype, "decode": dec}))
         return 0
     pre = B.measure_prefill(eng, PROMPT_LEN, warmup=a.warmup, runs=5, seed=SEED)
     pre_flops = B.prefill_flops(model, PROMPT_LEN)
