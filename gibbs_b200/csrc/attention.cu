@@ -200,47 +200,101 @@ __global__ void qk_norm_rope_store_partials_kernel(const float* ws, int splits, 
                                                    const int* block_table, int bt_stride, int page_size,
                                                    bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, int n_pages,
                                                    int n_tokens, int heads, int kv_heads, int hd, int write_kv,
-                                                   int* __restrict__ status) {
-  extern __shared__ float staged[];                      // [warps of the block][hd]
+                                                   int async_copies, int* __restrict__ status) {
+  // per warp: [hd] sums, then (async_copies) [splits][hd] copies of the partial tiles
+  extern __shared__ __align__(16) float staged[];
   pdl_trigger();
-  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  float* mine = staged + (size_t)warp * hd;
+  const int per_warp = hd * (async_copies ? splits + 1 : 1);
+  float* mine = staged + (size_t)warp * per_warp;
+  float* parts = mine + hd;
   const int slots = heads + (write_kv ? 2 * kv_heads : 0);
   const int cols = slots * hd;
   const long long idx = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
   if (idx >= (long long)n_tokens * slots) return;
   const int t = (int)(idx / slots), slot = (int)(idx - (long long)t * slots);
+  // Everything but the product's partial tiles is read, and the rotation worked out, before the
+  // wait for the product: position and page from the step's metadata, gains, bias, angles.
   const int pos = tok_pos[t];
   const bool is_q = slot < heads;
   const bool is_k = !is_q && slot < heads + kv_heads;
   const int kvh = is_q ? 0 : (is_k ? slot - heads : slot - heads - kv_heads);
   bf16* dst;
+  bool bad_page = false;
   if (is_q) {
     dst = q_out + (size_t)t * heads * hd + (size_t)slot * hd;
   } else {
     const int page = block_table[(size_t)tok_req[t] * bt_stride + pos / page_size];
-    if (page < 0 || page >= n_pages) {
-      if (lane == 0) atomicExch(status, STATUS_BAD_PAGE_WRITE);
-      return;
+    bad_page = page < 0 || page >= n_pages;
+    dst = (is_k ? k_pages : v_pages) + (((size_t)(bad_page ? 0 : page) * kv_heads + kvh) * page_size + pos % page_size) * hd;
+  }
+  const float* gain = is_q ? q_gain : (is_k ? k_gain : nullptr);
+  const int half = (inv_freq && (is_q || is_k)) ? rotary_dim / 2 : 0;
+  const float mscale = half ? inv_freq[half] : 1.f;
+  constexpr int PRE = 2;                                 // rotation pairs per lane prepared ahead (head sizes up to 128)
+  float pc[PRE], ps[PRE], pg0[PRE], pg1[PRE];
+#pragma unroll
+  for (int k = 0; k < PRE; ++k) {
+    const int jj = lane + 32 * k;
+    pc[k] = 1.f; ps[k] = 0.f; pg0[k] = 1.f; pg1[k] = 1.f;
+    if (jj < half) {
+      const float ang = (float)pos * inv_freq[jj];
+      pc[k] = cosf(ang) * mscale;
+      ps[k] = sinf(ang) * mscale;
+      if (gain) {
+        pg0[k] = gain[adjacent ? 2 * jj : jj];
+        pg1[k] = gain[adjacent ? 2 * jj + 1 : jj + half];
+      }
     }
-    dst = (is_k ? k_pages : v_pages) + (((size_t)page * kv_heads + kvh) * page_size + pos % page_size) * hd;
+  }
+  float pb[4] = {0.f, 0.f, 0.f, 0.f};                    // bias of this lane's first four columns
+  if (bias) {
+#pragma unroll
+    for (int m = 0; m < 4; ++m)
+      if (lane + 32 * m < hd) pb[m] = bias[slot * hd + lane + 32 * m];
+  }
+  pdl_wait();
+  if (bad_page) {
+    if (lane == 0) atomicExch(status, STATUS_BAD_PAGE_WRITE);
+    return;
+  }
+  const size_t split_stride = (size_t)n_tokens * cols;
+  const float* row0 = ws + (size_t)t * cols + (size_t)slot * hd;
+  if (async_copies) {
+    // all splits of this head's row in one trip to L2: hd / 4 pieces of 16 bytes per split
+    const int pieces = hd >> 2;
+    for (int i = lane; i < splits * pieces; i += 32) {
+      const int sp = i / pieces, c = i - sp * pieces;
+      gb_cp_async_16(parts + (size_t)sp * hd + 4 * c, row0 + (size_t)sp * split_stride + 4 * c);
+    }
+    gb_cp_async_wait_all();
+    __syncwarp();
   }
   float ss = 0.f;
   for (int d0 = 0; d0 < hd; d0 += 128) {                 // four columns per lane at a time
-    size_t at[4];
     float v[4];
+    if (async_copies) {
 #pragma unroll
-    for (int m = 0; m < 4; ++m) {
-      const int d = d0 + lane + 32 * m;
-      at[m] = (size_t)t * cols + (size_t)slot * hd + (d < hd ? d : hd - 1);
+      for (int m = 0; m < 4; ++m) {
+        const int d = d0 + lane + 32 * m;
+        v[m] = 0.f;
+        if (d < hd)
+          for (int sp = 0; sp < splits; ++sp) v[m] += parts[(size_t)sp * hd + d];
+      }
+    } else {
+      size_t at[4];
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        const int d = d0 + lane + 32 * m;
+        at[m] = (size_t)t * cols + (size_t)slot * hd + (d < hd ? d : hd - 1);
+      }
+      sum_partials<4>(ws, splits, split_stride, at, v);
     }
-    sum_partials<4>(ws, splits, (size_t)n_tokens * cols, at, v);
 #pragma unroll
     for (int m = 0; m < 4; ++m) {
       const int d = d0 + lane + 32 * m;
       if (d < hd) {
-        if (bias) v[m] += bias[slot * hd + d];
+        if (bias) v[m] += d0 == 0 ? pb[m] : bias[slot * hd + d];
         const float x = to_f32(from_f32<bf16>(v[m]));
         mine[d] = x;
         ss += x * x;
@@ -252,26 +306,35 @@ __global__ void qk_norm_rope_store_partials_kernel(const float* ws, int splits, 
     for (int d = lane; d < hd; d += 32) dst[d] = __float2bfloat16_rn(mine[d]);
     return;
   }
-  const float* gain = is_q ? q_gain : k_gain;
   float scale = 1.f;
   if (gain) {
     ss = warp_sum(ss);
     scale = 1.0f / sqrtf(ss / (float)hd + eps);
   }
-  const int half = inv_freq ? rotary_dim / 2 : 0;
-  const float mscale = inv_freq ? inv_freq[half] : 1.f;
-  for (int j = lane; j < half; j += 32) {
+  for (int j = lane, k = 0; j < half; j += 32, ++k) {
     const int i0 = adjacent ? 2 * j : j;
     const int i1 = adjacent ? 2 * j + 1 : j + half;
     float a = mine[i0], b = mine[i1];
-    if (gain) {
-      a = a * scale * gain[i0];
-      b = b * scale * gain[i1];
+    float c, sn;
+    if (k < PRE) {
+      // (static indexing keeps the prepared values in registers)
+      c = k == 0 ? pc[0] : pc[1];
+      sn = k == 0 ? ps[0] : ps[1];
+      if (gain) {
+        a = a * scale * (k == 0 ? pg0[0] : pg0[1]);
+        b = b * scale * (k == 0 ? pg1[0] : pg1[1]);
+      }
+    } else {
+      if (gain) {
+        a = a * scale * gain[i0];
+        b = b * scale * gain[i1];
+      }
+      const float ang = (float)pos * inv_freq[j];
+      c = cosf(ang) * mscale;
+      sn = sinf(ang) * mscale;
     }
-    const float ang = (float)pos * inv_freq[j];
-    const float c = cosf(ang) * mscale, s = sinf(ang) * mscale;
-    dst[i0] = __float2bfloat16_rn(a * c - b * s);
-    dst[i1] = __float2bfloat16_rn(a * s + b * c);
+    dst[i0] = __float2bfloat16_rn(a * c - b * sn);
+    dst[i1] = __float2bfloat16_rn(a * sn + b * c);
   }
   for (int d = 2 * half + lane; d < hd; d += 32) {
     float a = mine[d];
@@ -428,10 +491,15 @@ GB_API int gb_qk_norm_rope_store_partials(const float* ws, int splits, const flo
   if (splits < 1 || hd <= 0 || hd > 2048) GB_FAIL(GB_ERR_ARG, "gb_qk_norm_rope_store_partials: %d splits, head_dim %d", splits, hd);
   const int slots = heads + (write_kv ? 2 * kv_heads : 0);
   const long long warps = (long long)n_tokens * slots;
-  gb_launch(qk_norm_rope_store_partials_kernel, dim3(gb_div_up(warps, 4)), dim3(128), (size_t)4 * hd * sizeof(float),
+  // The partial tiles go through shared memory in 16-byte pieces when rows and heads are aligned
+  // for it and the copies fit; else every lane adds its columns with plain loads.
+  const size_t smem_async = (size_t)4 * hd * (splits + 1) * sizeof(float);
+  const int async_copies = (hd % 4 == 0 && ((uintptr_t)ws & 15) == 0 && smem_async <= 48 * 1024) ? 1 : 0;
+  gb_launch(qk_norm_rope_store_partials_kernel, dim3(gb_div_up(warps, 4)), dim3(128),
+            async_copies ? smem_async : (size_t)4 * hd * sizeof(float),
             stream, ws, splits, bias, (bf16*)q_out, q_gain, k_gain, eps, inv_freq, rotary_dim, adjacent, tok_req,
             tok_pos, block_table, bt_stride, page_size, (bf16*)k_pages, (bf16*)v_pages, n_pages, n_tokens, heads,
-            kv_heads, hd, write_kv, status);
+            kv_heads, hd, write_kv, async_copies, status);
   GB_CHECK_LAUNCH("gb_qk_norm_rope_store_partials");
   return GB_OK;
 }

@@ -104,7 +104,8 @@ template <int HD, int NW, bool KSPLIT>
 __global__ void __launch_bounds__(32 * NW)
 attention_tc_kernel(const AttnParams p) {
   pdl_trigger();
-  pdl_wait();
+  // The wait for the kernel in front (which wrote this step's q, k and v) comes further down: the
+  // step's metadata, the page ids and the key tiles that earlier steps filled are fetched first.
   constexpr int BQ = KSPLIT ? 16 : 16 * NW;
   constexpr int NN = KSPLIT ? 2 : KT / 8;                    // 8-key column tiles per warp and key tile
   using TL = Tile<HD>;
@@ -145,14 +146,7 @@ attention_tc_kernel(const AttnParams p) {
   const int per = (t_hi - t_lo + p.splits - 1) / p.splits;
   const int t_begin = t_lo + z * per, t_end = min(t_hi, t_begin + per);
 
-  // Q tile: row = token_local * group + g
-  for (int idx = tid; idx < BQ * CHUNKS; idx += NT) {
-    const int row = idx / CHUNKS, c = idx - row * CHUNKS;
-    const int tl = row / group, g = row - tl * group;
-    const bool valid = tl < n_tok;
-    const bf16* src = p.q + (size_t)(row0 + (valid ? tl : 0)) * p.ldq + (size_t)(kvh * group + g) * HD + c * 8;
-    cp_async_16(sq + TL::at(row, c * 8), src, valid);
-  }
+  const int first_new = p.start_pos[r];                      // positions from here on are written by this step
   // Where each of a tile's 64 keys lies in the pages (element offset of its row, -1: not
   // visible) is worked out once per tile and row, not once per 16-byte piece: slot t % (NS + 1)
   // of row_off belongs to tile t.  It is written an iteration before the tile's loads are
@@ -205,9 +199,27 @@ attention_tc_kernel(const AttnParams p) {
   for (int i = 0; i < NS; ++i)
     if (t_begin + i < t_end) locate(t_begin + i);
   __syncthreads();
+  bool waited = false;                     // (the same in every thread of the CTA)
   for (int i = 0; i < NS - 1; ++i) {       // one commit group per tile, also for tiles that do not exist
-    if (t_begin + i < t_end) load_kv(t_begin + i, i);
+    if (t_begin + i < t_end) {
+      if (!waited && (t_begin + i + 1) * KT > first_new) {
+        pdl_wait();
+        waited = true;
+      }
+      load_kv(t_begin + i, i);
+    }
     cp_async_commit();
+  }
+  if (!waited) pdl_wait();
+  // Q tile: row = token_local * group + g.  Plain loads (the key tiles above are on their way
+  // meanwhile); the barrier at the head of the first iteration makes the tile visible.
+  for (int idx = tid; idx < BQ * CHUNKS; idx += NT) {
+    const int row = idx / CHUNKS, c = idx - row * CHUNKS;
+    const int tl = row / group, g = row - tl * group;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (tl < n_tok)
+      v = __ldcg(reinterpret_cast<const uint4*>(p.q + (size_t)(row0 + tl) * p.ldq + (size_t)(kvh * group + g) * HD + c * 8));
+    *reinterpret_cast<uint4*>(sq + TL::at(row, c * 8)) = v;
   }
 
   // this thread's two rows: g0 = lane/4 and g0 + 8 of the warp's 16
@@ -443,6 +455,16 @@ __global__ void attention_merge_kernel(const float* part_o, const float* part_ml
   pdl_wait();
   const int row = blockIdx.x;                         // token * heads + head
   const size_t rows = (size_t)n_tokens * heads;
+  // Every thread asks for its column of the first sixteen splits before the weights are worked
+  // out, so that the outputs and the (maximum, sum) pairs come back in the same trip to L2.
+  constexpr int AHEAD = 16;
+  const int d_mine = threadIdx.x;
+  float a[AHEAD];
+#pragma unroll
+  for (int z = 0; z < AHEAD; ++z) {
+    const int zz = z < splits ? z : splits - 1;       // (past the last split: read again, not used)
+    a[z] = ldcg_now(part_o + ((size_t)zz * rows + row) * hd + (d_mine < hd ? d_mine : 0));
+  }
   if (threadIdx.x < 32) {
     const int z = threadIdx.x;
     float m = -INFINITY, l = 0.f;
@@ -461,13 +483,11 @@ __global__ void attention_merge_kernel(const float* part_o, const float* part_ml
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float acc = 0.f;
     int z = 0;
-    for (; z + 4 <= splits; z += 4) {
-      const float a0 = part_o[((size_t)z * rows + row) * hd + d], a1 = part_o[((size_t)(z + 1) * rows + row) * hd + d];
-      const float a2 = part_o[((size_t)(z + 2) * rows + row) * hd + d], a3 = part_o[((size_t)(z + 3) * rows + row) * hd + d];
-      acc += wgt[z] * a0;
-      acc += wgt[z + 1] * a1;
-      acc += wgt[z + 2] * a2;
-      acc += wgt[z + 3] * a3;
+    if (d == d_mine) {
+#pragma unroll
+      for (int u = 0; u < AHEAD; ++u)
+        if (u < splits) acc += wgt[u] * a[u];
+      z = splits < AHEAD ? splits : AHEAD;
     }
     for (; z < splits; ++z) acc += wgt[z] * part_o[((size_t)z * rows + row) * hd + d];
     out[(size_t)t * ldo + (size_t)h * hd + d] = __float2bfloat16_rn(acc);

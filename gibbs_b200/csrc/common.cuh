@@ -68,31 +68,57 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   if (lane == 0) scratch[warp] = v;
   __syncthreads();
   const int nw = (blockDim.x + 31) >> 5;
-  float t = (threadIdx.x < nw) ? scratch[threadIdx.x] : 0.f;
-  if (warp == 0) {
-    t = warp_sum(t);
-    if (lane == 0) scratch[0] = t;
-  }
-  __syncthreads();
-  return scratch[0];
+  const float t = (lane < nw) ? scratch[lane] : 0.f;
+  return warp_sum(t);            // every warp adds the same values in the same order
+}
+
+// Asynchronous 16-byte copies from global (through L2) to shared memory: every copy a thread issues
+// is in flight at once, whatever the compiler makes of the code around it, and holds no register.
+// A thread that reads only what it copied itself needs gb_cp_async_wait_all() and no barrier.
+__device__ __forceinline__ void gb_cp_async_16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+               ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void gb_cp_async_4(void* smem, const void* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;"
+               ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void gb_cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
+// L2 loads that are issued where they stand (the compiler neither sinks them to their first use
+// nor drops them): a batch of them written one after the other is in flight together.
+__device__ __forceinline__ float ldcg_now(const float* p) {
+  float v;
+  asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float4 ldcg_now(const float4* p) {
+  float4 v;
+  asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
 }
 
 // NV sums over the `splits` partial tiles a split-K product left in 32-bit ([split][row][col],
-// `stride` elements between splits), at the element offsets at[0..NV): the loads of four splits
-// are requested together and the terms are added in split order.
+// `stride` elements between splits), at the element offsets at[0..NV): the loads of eight splits
+// are requested together (one trip to L2) and the terms are added in split order.
 template <int NV>
-__device__ __forceinline__ void sum_partials(const float* __restrict__ ws, int splits, size_t stride,
+__device__ __forceinline__ void sum_partials(const float* ws, int splits, size_t stride,
                                              const size_t* at, float* acc) {
 #pragma unroll
   for (int v = 0; v < NV; ++v) acc[v] = 0.f;
-  for (int s0 = 0; s0 < splits; s0 += 4) {
-    float a[4][NV];
+  for (int s0 = 0; s0 < splits; s0 += 8) {
+    float a[8][NV];
 #pragma unroll
-    for (int u = 0; u < 4; ++u)
+    for (int u = 0; u < 8; ++u) {
+      // (a split past the last one re-reads the last one and is not added: no branch around a load)
+      const int su = s0 + u < splits ? s0 + u : splits - 1;
 #pragma unroll
-      for (int v = 0; v < NV; ++v) a[u][v] = (s0 + u < splits) ? __ldcg(ws + (size_t)(s0 + u) * stride + at[v]) : 0.f;
+      for (int v = 0; v < NV; ++v) a[u][v] = ldcg_now(ws + (size_t)su * stride + at[v]);
+    }
 #pragma unroll
-    for (int u = 0; u < 4; ++u)
+    for (int u = 0; u < 8; ++u)
       if (s0 + u < splits) {
 #pragma unroll
         for (int v = 0; v < NV; ++v) acc[v] += a[u][v];
@@ -108,17 +134,23 @@ static inline int gb_div_up(long long a, long long b) { return (int)((a + b - 1)
 // is still running.  Every kernel of this library therefore
 //   - calls pdl_trigger() first, which lets the kernel after it start early, and
 //   - calls pdl_wait() before it reads or writes anything an earlier kernel may
-//     still touch (activations, caches, state; weights and launch arguments are
-//     safe).  pdl_wait() returns when the earlier kernels have completed and
-//     their writes are visible.
+//     still touch (activations, caches, state).  pdl_wait() returns when the
+//     earlier kernels have completed and their writes are visible.
 // Outside such a launch both are no-ops.  GIBBS_B200_PDL=0 turns the launch
 // attribute off (kernels then run strictly one after the other).
 //
-// Pointers to anything an earlier kernel writes (activations, cache pages, state, a step's
-// metadata) are NOT declared `const ... __restrict__`: the compiler takes loads through such a
-// pointer for invariant and may move them above pdl_wait() (it did, in a kernel that fetched its
-// first tile right after the wait).  Only what never changes while a model runs (weights, gains,
-// taps, biases, tables) keeps the qualifier.
+// What may be read BEFORE pdl_wait(), so that its trip to L2 is over when the wait returns:
+//   - weights, gains, taps, biases, tables and launch arguments: nothing writes them while a model runs;
+//   - a step's metadata (token->request, positions, lengths, slot ids, block tables, row lists): a
+//     host copy writes it, and that copy completes before the step's first kernel starts.  The one
+//     exception are the token ids, which feed_tokens_kernel may rewrite: only the embedding gather
+//     reads them, after its wait;
+//   - cache pages and state at positions that earlier STEPS wrote (not this step's own tokens).
+//
+// Pointers to anything an earlier kernel writes (activations, cache pages, state) are NOT declared
+// `const ... __restrict__`: the compiler takes loads through such a pointer for invariant and may
+// move them above pdl_wait() (it did, in a kernel that fetched its first tile right after the
+// wait).  Only what never changes while a model runs keeps the qualifier.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 

@@ -235,70 +235,95 @@ __global__ void short_conv_state_kernel(const T* bcx, long long ld, float* __res
 
 // Every request brings exactly one token: output and state update in one pass,
 // one thread per request and channel (it alone reads and writes its state column).
-template <typename T>
+// KT: the kernel width when it is 2, 3 or 4 (the loops unroll and the window stays in registers), else 0.
+template <typename T, int KT>
 __global__ void short_conv_decode_kernel(const T* bcx, long long ld, const float* __restrict__ taps,
                                          const float* __restrict__ bias, float* __restrict__ state,
                                          long long slot_stride, const int* slot_ids,
                                          const int* q_start, T* __restrict__ out, int n_requests,
-                                         int hidden, int K) {
+                                         int hidden, int K_) {
+  const int K = KT ? KT : K_;
   pdl_trigger();
-  pdl_wait();
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= (long long)n_requests * hidden) return;
   const int r = (int)(gid / hidden), c = (int)(gid - (long long)r * hidden);
+  // Metadata, taps and the state an earlier step left are read before the wait for the kernel in
+  // front; after it only this step's [B | C | x] row is missing.
   const int t = q_start[r];
+  float* st = state + (size_t)slot_ids[r] * slot_stride;
+  float old[KT ? KT : MAX_TAPS], tap[KT ? KT : MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < K - 1; ++j) old[j] = st[(size_t)j * hidden + c];
+#pragma unroll
+  for (int j = 0; j < K; ++j) tap[j] = taps[(size_t)c * K + j];
+  const float cb = bias ? bias[c] : 0.f;
+  pdl_wait();
   const T* row = bcx + (size_t)t * ld;
   const float bx = to_f32(row[c]) * to_f32(row[2 * hidden + c]);
-  float* st = state + (size_t)slot_ids[r] * slot_stride;
   float acc = 0.f;
+#pragma unroll
   for (int j = 0; j < K - 1; ++j) {
-    const float v = st[(size_t)j * hidden + c];
-    acc = fmaf(taps[(size_t)c * K + j], v, acc);
-    if (j > 0) st[(size_t)(j - 1) * hidden + c] = v;      // shift the window by one
+    acc = fmaf(tap[j], old[j], acc);
+    if (j > 0) st[(size_t)(j - 1) * hidden + c] = old[j];      // shift the window by one
   }
-  acc = fmaf(taps[(size_t)c * K + K - 1], bx, acc);
+  acc = fmaf(tap[K - 1], bx, acc);
   st[(size_t)(K - 2) * hidden + c] = bx;
-  if (bias) acc += bias[c];
+  if (bias) acc += cb;
   out[(size_t)t * hidden + c] = from_f32<T>(to_f32(row[hidden + c]) * acc);
 }
 
 // The same, reading [B | C | x] as the partial tiles of the split-K product that made it
 // (ws[split][token][3*hidden], 32-bit, plus in_bias): their sum is rounded to bfloat16 exactly
 // where the product's own reduction would have rounded it, then used as above.
+template <int KT>
 __global__ void short_conv_decode_partials_kernel(const float* ws, int splits, long long n_rows,
                                                   const float* __restrict__ in_bias, const float* __restrict__ taps,
                                                   const float* __restrict__ bias, float* __restrict__ state,
                                                   long long slot_stride, const int* slot_ids,
                                                   const int* q_start, bf16* __restrict__ out,
-                                                  int n_requests, int hidden, int K) {
+                                                  int n_requests, int hidden, int K_) {
+  const int K = KT ? KT : K_;
   pdl_trigger();
-  pdl_wait();
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= (long long)n_requests * hidden) return;
   const int r = (int)(gid / hidden), c = (int)(gid - (long long)r * hidden);
+  // Metadata, taps, biases and the state an earlier step left are read before the wait for the
+  // product in front; after it only its partial tiles are missing (one trip to L2).
   const int t = q_start[r];
   const size_t ld = (size_t)3 * hidden;
   const size_t at[3] = {(size_t)t * ld + c, (size_t)t * ld + hidden + c, (size_t)t * ld + 2 * hidden + c};
   float* st = state + (size_t)slot_ids[r] * slot_stride;
-  float old[MAX_TAPS];
-  for (int j = 0; j < K - 1; ++j) old[j] = st[(size_t)j * hidden + c];   // on their way while the sums are formed
+  float old[KT ? KT : MAX_TAPS], tap[KT ? KT : MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < K - 1; ++j) old[j] = st[(size_t)j * hidden + c];
+#pragma unroll
+  for (int j = 0; j < K; ++j) tap[j] = taps[(size_t)c * K + j];
+  const float cb = bias ? bias[c] : 0.f;
+  float ib[3] = {0.f, 0.f, 0.f};
+  if (in_bias) {
+    ib[0] = in_bias[c];
+    ib[1] = in_bias[hidden + c];
+    ib[2] = in_bias[2 * hidden + c];
+  }
+  pdl_wait();
   float v[3];
   sum_partials<3>(ws, splits, (size_t)n_rows * ld, at, v);
   if (in_bias) {
-    v[0] += in_bias[c];
-    v[1] += in_bias[hidden + c];
-    v[2] += in_bias[2 * hidden + c];
+    v[0] += ib[0];
+    v[1] += ib[1];
+    v[2] += ib[2];
   }
   const float bv = to_f32(from_f32<bf16>(v[0])), cv = to_f32(from_f32<bf16>(v[1])), xv = to_f32(from_f32<bf16>(v[2]));
   const float bx = bv * xv;
   float acc = 0.f;
+#pragma unroll
   for (int j = 0; j < K - 1; ++j) {
-    acc = fmaf(taps[(size_t)c * K + j], old[j], acc);
+    acc = fmaf(tap[j], old[j], acc);
     if (j > 0) st[(size_t)(j - 1) * hidden + c] = old[j];
   }
-  acc = fmaf(taps[(size_t)c * K + K - 1], bx, acc);
+  acc = fmaf(tap[K - 1], bx, acc);
   st[(size_t)(K - 2) * hidden + c] = bx;
-  if (bias) acc += bias[c];
+  if (bias) acc += cb;
   out[(size_t)t * hidden + c] = __float2bfloat16_rn(cv * acc);
 }
 
@@ -314,7 +339,10 @@ GB_API int gb_short_conv_partials(const float* ws, int splits, long long n_rows,
   if (K < 2 || K > MAX_TAPS) GB_FAIL(GB_ERR_ARG, "gb_short_conv_partials: kernel width %d outside 2..%d", K, MAX_TAPS);
   if (splits < 1) GB_FAIL(GB_ERR_ARG, "gb_short_conv_partials: %d splits", splits);
   const long long total = (long long)n_requests * hidden;
-  gb_launch(short_conv_decode_partials_kernel, dim3(gb_div_up(total, 128)), dim3(128), 0, stream, ws, splits, n_rows,
+  auto kernel = K == 2 ? short_conv_decode_partials_kernel<2>
+                : K == 3 ? short_conv_decode_partials_kernel<3>
+                : K == 4 ? short_conv_decode_partials_kernel<4> : short_conv_decode_partials_kernel<0>;
+  gb_launch(kernel, dim3(gb_div_up(total, 128)), dim3(128), 0, stream, ws, splits, n_rows,
             in_bias, taps, bias, state, slot_stride, slot_ids, q_start, (bf16*)out, n_requests, hidden, K);
   GB_CHECK_LAUNCH("gb_short_conv_partials");
   return 1;
@@ -333,11 +361,17 @@ GB_API int gb_short_conv(const void* bcx, int dtype, long long ld, const float* 
   const int threads = 256;
   if (max_q_len == 1 && n_tokens == n_requests) {           // one token per request
     const long long total = (long long)n_requests * hidden;
-    if (dtype == GB_F32)
-      gb_launch(short_conv_decode_kernel<float>, dim3(gb_div_up(total, threads)), dim3(threads), 0, stream, (const float*)bcx, ld, taps, bias, state, slot_stride, slot_ids, q_start, (float*)out, n_requests, hidden, K);
-    else if (dtype == GB_BF16)
-      gb_launch(short_conv_decode_kernel<bf16>, dim3(gb_div_up(total, threads)), dim3(threads), 0, stream, (const bf16*)bcx, ld, taps, bias, state, slot_stride, slot_ids, q_start, (bf16*)out, n_requests, hidden, K);
-    else
+    if (dtype == GB_F32) {
+      auto kernel = K == 2 ? short_conv_decode_kernel<float, 2> : K == 3 ? short_conv_decode_kernel<float, 3>
+                    : K == 4 ? short_conv_decode_kernel<float, 4> : short_conv_decode_kernel<float, 0>;
+      gb_launch(kernel, dim3(gb_div_up(total, threads)), dim3(threads), 0, stream, (const float*)bcx, ld, taps, bias,
+                state, slot_stride, slot_ids, q_start, (float*)out, n_requests, hidden, K);
+    } else if (dtype == GB_BF16) {
+      auto kernel = K == 2 ? short_conv_decode_kernel<bf16, 2> : K == 3 ? short_conv_decode_kernel<bf16, 3>
+                    : K == 4 ? short_conv_decode_kernel<bf16, 4> : short_conv_decode_kernel<bf16, 0>;
+      gb_launch(kernel, dim3(gb_div_up(total, threads)), dim3(threads), 0, stream, (const bf16*)bcx, ld, taps, bias,
+                state, slot_stride, slot_ids, q_start, (bf16*)out, n_requests, hidden, K);
+    } else
       GB_FAIL(GB_ERR_ARG, "gb_short_conv: unknown dtype %d", dtype);
     GB_CHECK_LAUNCH("gb_short_conv (decode)");
     return 1;

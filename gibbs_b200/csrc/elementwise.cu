@@ -85,20 +85,30 @@ __device__ __forceinline__ void store4<bf16>(bf16* dst, float4 v) {
 // Instantiated apart so that rows without partial sums, or with one tile set (prompts), do not
 // pay for the registers that hold eight splits' worth of loads.
 template <typename TOut, int VEC, int PEND>
-__global__ void rmsnorm_kernel(float* __restrict__ x, long long ldx, const float* __restrict__ gain,
-                               TOut* __restrict__ out, const int* rows, int dim, float eps,
-                               const float* pend, int splits, long long n_src_rows,
-                               const float* __restrict__ pend_bias) {
+__device__ __forceinline__ void rmsnorm_body(float* __restrict__ x, long long ldx, const float* __restrict__ gain,
+                                             TOut* __restrict__ out, const int* rows, int dim, float eps,
+                                             const float* pend, int splits, long long n_src_rows,
+                                             const float* __restrict__ pend_bias) {
   __shared__ float scratch[32];
   pdl_trigger();
-  pdl_wait();
+  // What no kernel of the step writes (the gain, the row list from the step's metadata) is read
+  // before the wait for the kernel in front: one trip to L2 less after it.
   const int r = blockIdx.x;
   const long long sr = rows ? rows[r] : r;
+  float4 g4[VEC > 0 ? VEC : 1];
+  if (VEC > 0) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      g4[i] = c < (dim >> 2) ? reinterpret_cast<const float4*>(gain)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+  pdl_wait();
   float* src = x + (size_t)sr * ldx;
   const bool write_back = pend != nullptr && rows == nullptr;
   TOut* dst = out + (size_t)r * dim;
   float ss = 0.f;
-  if (VEC > 0) {
+  if constexpr (VEC > 0) {
     float4 v[VEC > 0 ? VEC : 1];
     const int n4 = dim >> 2;
 #pragma unroll
@@ -107,8 +117,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, long long ldx, const float
       v[i] = c < n4 ? reinterpret_cast<const float4*>(src)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     if (PEND > 0 && pend) {
-      // the partial sums of up to eight splits are requested together (one trip to L2, not eight)
-      // and then added in split order
+      // the partial sums of up to PEND splits are requested together (one trip to L2, not one
+      // per split) and then added in split order
       constexpr int G = PEND > 0 ? PEND : 1;
       const size_t split_stride = (size_t)n_src_rows * dim;
       const float* p0 = pend + (size_t)sr * dim;
@@ -116,12 +126,13 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, long long ldx, const float
         float4 a[G][VEC > 0 ? VEC : 1];
 #pragma unroll
         for (int u = 0; u < G; ++u) {
+          // (a split past the last one re-reads the last one and is not added: loads without a
+          // branch around them all go out together)
+          const int su = s0 + u < splits ? s0 + u : splits - 1;
 #pragma unroll
           for (int i = 0; i < VEC; ++i) {
             const int c = threadIdx.x + i * blockDim.x;
-            a[u][i] = (s0 + u < splits && c < n4)
-                          ? __ldcg(reinterpret_cast<const float4*>(p0 + (size_t)(s0 + u) * split_stride) + c)
-                          : make_float4(0.f, 0.f, 0.f, 0.f);
+            a[u][i] = ldcg_now(reinterpret_cast<const float4*>(p0 + (size_t)su * split_stride) + (c < n4 ? c : 0));
           }
         }
 #pragma unroll
@@ -129,7 +140,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, long long ldx, const float
           if (s0 + u < splits) {
 #pragma unroll
             for (int i = 0; i < VEC; ++i) {
-              v[i].x += a[u][i].x; v[i].y += a[u][i].y; v[i].z += a[u][i].z; v[i].w += a[u][i].w;
+              const int c = threadIdx.x + i * blockDim.x;
+              if (c < n4) { v[i].x += a[u][i].x; v[i].y += a[u][i].y; v[i].z += a[u][i].z; v[i].w += a[u][i].w; }
             }
           }
         }
@@ -154,13 +166,13 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, long long ldx, const float
     for (int i = 0; i < VEC; ++i) {
       const int c = threadIdx.x + i * blockDim.x;
       if (c < n4) {
-        const float4 g = reinterpret_cast<const float4*>(gain)[c];
+        const float4 g = g4[i];
         store4<TOut>(dst + 4 * c, make_float4(v[i].x * scale * g.x, v[i].y * scale * g.y, v[i].z * scale * g.z,
                                               v[i].w * scale * g.w));
       }
     }
     return;
-  }
+  } else {
   for (int d = threadIdx.x; d < dim; d += blockDim.x) {
     float v = src[d];
     if (pend) {
@@ -180,6 +192,84 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, long long ldx, const float
     }
     dst[d] = from_f32<TOut>(v * scale * gain[d]);
   }
+  }
+}
+
+// Rows to which a split-K product's partial sums are still to be added (decode steps): every
+// thread copies its 16-byte pieces of all splits to shared memory asynchronously, so that all of
+// them are one trip to L2, and then adds them in split order.  dim % 4 == 0; shared memory:
+// splits * dim floats.
+template <typename TOut>
+__global__ void __launch_bounds__(1024) rmsnorm_splits_kernel(float* x, long long ldx, const float* __restrict__ gain,
+                                                              TOut* __restrict__ out, const int* rows, int dim,
+                                                              float eps, const float* pend, int splits,
+                                                              long long n_src_rows,
+                                                              const float* __restrict__ pend_bias) {
+  extern __shared__ __align__(16) float parts[];            // [splits][dim]
+  __shared__ float scratch[32];
+  pdl_trigger();
+  const int r = blockIdx.x;
+  const long long sr = rows ? rows[r] : r;
+  const int n4 = dim >> 2;
+  constexpr int MAXV = 2;                                    // pieces per thread (the launch sees to it)
+  float4 g4[MAXV], b4[MAXV];
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    g4[i] = c < n4 ? reinterpret_cast<const float4*>(gain)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    b4[i] = (pend_bias && c < n4) ? reinterpret_cast<const float4*>(pend_bias)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  pdl_wait();
+  float* src = x + (size_t)sr * ldx;
+  const bool write_back = rows == nullptr;
+  const float* p0 = pend + (size_t)sr * dim;
+  const size_t split_stride = (size_t)n_src_rows * dim;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < n4)
+      for (int s = 0; s < splits; ++s) gb_cp_async_16(parts + (size_t)s * dim + 4 * c, p0 + (size_t)s * split_stride + 4 * c);
+  }
+  float4 v[MAXV];
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    v[i] = c < n4 ? __ldcg(reinterpret_cast<const float4*>(src) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  gb_cp_async_wait_all();
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < n4) {
+      for (int s = 0; s < splits; ++s) {
+        const float4 a = *reinterpret_cast<const float4*>(parts + (size_t)s * dim + 4 * c);
+        v[i].x += a.x; v[i].y += a.y; v[i].z += a.z; v[i].w += a.w;
+      }
+      if (pend_bias) { v[i].x += b4[i].x; v[i].y += b4[i].y; v[i].z += b4[i].z; v[i].w += b4[i].w; }
+      if (write_back) reinterpret_cast<float4*>(src)[c] = v[i];
+    }
+    ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)dim + eps);
+  TOut* dst = out + (size_t)r * dim;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < n4)
+      store4<TOut>(dst + 4 * c, make_float4(v[i].x * scale * g4[i].x, v[i].y * scale * g4[i].y,
+                                            v[i].z * scale * g4[i].z, v[i].w * scale * g4[i].w));
+  }
+}
+
+// MAXT: the most threads a launch of this variant uses (it bounds the registers a thread may take;
+// the variants that keep many splits' loads in flight need more than a 1,024-thread block leaves).
+template <typename TOut, int VEC, int PEND, int MAXT>
+__global__ void __launch_bounds__(MAXT) rmsnorm_kernel(float* x, long long ldx, const float* gain, TOut* out,
+                                                       const int* rows, int dim, float eps, const float* pend,
+                                                       int splits, long long n_src_rows, const float* pend_bias) {
+  rmsnorm_body<TOut, VEC, PEND>(x, ldx, gain, out, rows, dim, eps, pend, splits, n_src_rows, pend_bias);
 }
 
 template <typename TOut>
@@ -192,19 +282,47 @@ void launch_rmsnorm(float* x, long long ldx, const float* gain, TOut* out, const
   if (vec_ok && n4 <= 2 * 1024) {
     int threads = 32;
     while (threads < 1024 && threads < n4) threads <<= 1;
-    if (threads > 256 && n4 <= 2 * 256) threads = 256;
     const int g = pend ? (splits > 1 ? 8 : 1) : 0;
-    auto kernel = n4 <= threads
-                      ? (g == 8 ? rmsnorm_kernel<TOut, 1, 8> : (g == 1 ? rmsnorm_kernel<TOut, 1, 1> : rmsnorm_kernel<TOut, 1, 0>))
-                      : (g == 8 ? rmsnorm_kernel<TOut, 2, 8> : (g == 1 ? rmsnorm_kernel<TOut, 2, 1> : rmsnorm_kernel<TOut, 2, 0>));
-    gb_launch(kernel, dim3(n_rows), dim3(threads), 0, stream, x, ldx, gain, out, rows, dim, eps, pend, splits,
-              n_src_rows, pend_bias);
+#define GB_NORM_LAUNCH(VEC, PEND, MAXT, THREADS)                                                                       \
+    gb_launch(rmsnorm_kernel<TOut, VEC, PEND, MAXT>, dim3(n_rows), dim3(THREADS), 0, stream, x, ldx, gain, out, rows,  \
+              dim, eps, pend, splits, n_src_rows, pend_bias)
+    if (g == 8) {
+      // Several splits to add: through shared memory while the splits fit there, else two pieces
+      // per thread with the loads of four splits at a time in registers.
+      const size_t smem = (size_t)splits * dim * sizeof(float);
+      if (smem <= 160 * 1024) {
+        static bool attr_set = false;
+        if (!attr_set) {
+          cudaFuncSetAttribute(rmsnorm_splits_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+          attr_set = true;
+        }
+        int th = 32;
+        while (th < 1024 && 2 * th < n4) th <<= 1;      // one piece per thread up to 1,024 columns... two above
+        if (th < n4 && th < 1024) th <<= 1;
+        gb_launch(rmsnorm_splits_kernel<TOut>, dim3(n_rows), dim3(th), smem, stream, x, ldx, gain, out, rows, dim, eps,
+                  pend, splits, n_src_rows, pend_bias);
+      } else {
+        GB_NORM_LAUNCH(2, 4, 1024, 1024);
+      }
+      return;
+    }
+    if (threads > 256 && n4 <= 2 * 256) threads = 256;
+    if (n4 <= threads) {
+      if (g == 1) GB_NORM_LAUNCH(1, 1, 1024, threads);
+      else GB_NORM_LAUNCH(1, 0, 1024, threads);
+    } else if (threads <= 256) {
+      if (g == 1) GB_NORM_LAUNCH(2, 1, 256, threads);
+      else GB_NORM_LAUNCH(2, 0, 256, threads);
+    } else {
+      if (g == 1) GB_NORM_LAUNCH(2, 1, 1024, threads);
+      else GB_NORM_LAUNCH(2, 0, 1024, threads);
+    }
     return;
   }
   int threads = 32;
   while (threads < 512 && threads * 4 < dim) threads <<= 1;
-  gb_launch(rmsnorm_kernel<TOut, 0, 8>, dim3(n_rows), dim3(threads), 0, stream, x, ldx, gain, out, rows, dim, eps,
-            pend, splits, n_src_rows, pend_bias);
+  GB_NORM_LAUNCH(0, 8, 1024, threads);
+#undef GB_NORM_LAUNCH
 }
 
 GB_API int gb_rmsnorm(float* x, long long ldx, const float* gain, void* out, int out_dtype, const int* rows,

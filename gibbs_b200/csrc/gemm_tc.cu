@@ -389,12 +389,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 // commits release the stages and publish the accumulator in both CTAs.  Each CTA keeps the
 // 128 accumulator rows of its own weight rows in its tensor memory (2 x 256 columns, double
 // buffered) and runs its own epilogue.  Persistent: one pair per two SMs walks the tiles.
+#ifdef GB_PAIR_TRACE
+// Debug builds: %globaltimer stamps and waited cycles of the first and the last pair's leader CTA.
+__device__ unsigned long long* g_pair_trace = nullptr;   // [launch][2 CTAs][3 threads][8]
+__device__ unsigned int g_pair_trace_launch = 0;
+__device__ __forceinline__ unsigned long long gtimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define PSTAMP(i) do { if (trace) trace[i] = gtimer(); } while (0)
+#define PWAIT_BEGIN() const long long w0_ = clock64()
+#define PWAIT_END(i) do { if (trace) trace[i] += (unsigned long long)(clock64() - w0_); } while (0)
+#define PPHASE_BEGIN() long long ph_ = clock64()
+#define PPHASE(i) do { const long long now_ = clock64(); if (trace) trace[i] += (unsigned long long)(now_ - ph_); ph_ = now_; } while (0)
+#else
+#define PPHASE_BEGIN() do {} while (0)
+#define PPHASE(i) do {} while (0)
+#define PSTAMP(i) do {} while (0)
+#define PWAIT_BEGIN() do {} while (0)
+#define PWAIT_END(i) do {} while (0)
+#endif
+
 struct PairCfg {
   static constexpr int BNP = 256;                         // tokens per tile
   static constexpr int X_TILE_BYTES = (BNP / 2) * BK * 2; // this CTA's half of the token rows
   static constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES;
-  static constexpr int STAGES = 5;
-  static constexpr int STAGING_BYTES = 128 * 64 * 4 + 128 * 64 * 2;
+#ifndef GB_PAIR_STAGES
+#define GB_PAIR_STAGES 6
+#endif
+  static constexpr int STAGES = GB_PAIR_STAGES;
+  static constexpr int STAGING_BYTES = 32 * 1024;        // 64 token rows in 32-bit, or 128 in bfloat16
   static constexpr int TMEM_COLS = 512;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024;
 };
@@ -418,6 +443,22 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   const int tiles_m = (M + BNP - 1) / BNP, tiles_n = (N + 2 * BM - 1) / (2 * BM);
   const int n_tiles = tiles_m * tiles_n;
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+#ifdef GB_PAIR_TRACE
+  __shared__ unsigned int trace_slot;
+  if (threadIdx.x == 0) trace_slot = blockIdx.x == 0 ? atomicAdd(&g_pair_trace_launch, 1u) : 0u;
+  __syncthreads();
+  unsigned long long* trace = nullptr;
+  if (g_pair_trace && rank == 0 && (pair == 0 || pair == n_pairs - 1) &&
+      (threadIdx.x == 0 || threadIdx.x == 32 || threadIdx.x == 64)) {
+    // the last pair does not know the slot: it uses the launch counter as it finds it (the first
+    // pair of the same launch has already bumped it, or will in a moment; good enough for a probe)
+    const unsigned int slot = pair == 0 ? trace_slot : (*(volatile unsigned int*)&g_pair_trace_launch) - 1u;
+    if (slot < 1024)
+      trace = g_pair_trace + ((size_t)slot * 2 + (pair == 0 ? 0 : 1)) * 24 + (threadIdx.x / 32) * 8;
+  }
+  if (trace) for (int i = 0; i < 8; ++i) trace[i] = 0;
+  PSTAMP(0);
+#endif
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -447,7 +488,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
 
   if (warp == 0) {
     if (elect_one()) {
+      PSTAMP(1);
       pdl_wait();
+      PSTAMP(2);
       int it = 0;
       for (int t = pair; t < n_tiles && !abort_flag; t += n_pairs) {
         const int n0 = (t / tiles_m) * 2 * BM + (int)rank * BM;          // this CTA's weight rows
@@ -465,8 +508,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           if (rank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * C::STAGE_BYTES);
           tma_load_2d_pair(st, &tmap_w, i * BK, n0, &full_bar[s]);
           tma_load_2d_pair(st + W_TILE_BYTES, &tmap_x, i * BK, m0, &full_bar[s]);
+#ifdef GB_PAIR_PREFETCH
+          if (i + GB_PAIR_PREFETCH < nkb) tma_prefetch_2d(&tmap_w, (i + GB_PAIR_PREFETCH) * BK, n0);
+#endif
+          if (it == 0) PSTAMP(3);
         }
       }
+      PSTAMP(4);
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -475,21 +523,30 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       int it = 0, tile_i = 0;
       for (int t = pair; t < n_tiles && !abort_flag; t += n_pairs, ++tile_i) {
         const int a = tile_i & 1;
-        if (!mbar_wait(&tmem_empty_bar[a], ((tile_i >> 1) & 1) ^ 1)) {
-          abort_flag = 1;
-          atomicExch(p.status, STATUS_TIMEOUT + 9);
-          break;
+        {
+          PWAIT_BEGIN();
+          if (!mbar_wait(&tmem_empty_bar[a], ((tile_i >> 1) & 1) ^ 1)) {
+            abort_flag = 1;
+            atomicExch(p.status, STATUS_TIMEOUT + 9);
+            break;
+          }
+          PWAIT_END(5);
         }
         tc_fence_after();
         const uint32_t acc = tmem_base + (uint32_t)(a * BNP);
         for (int i = 0; i < nkb; ++i, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1;
-          if (!mbar_wait(&full_bar[s], ph)) {
-            abort_flag = 1;
-            atomicExch(p.status, STATUS_TIMEOUT + 10);
-            break;
+          {
+            PWAIT_BEGIN();
+            if (!mbar_wait(&full_bar[s], ph)) {
+              abort_flag = 1;
+              atomicExch(p.status, STATUS_TIMEOUT + 10);
+              break;
+            }
+            if (it >= C::STAGES) PWAIT_END(6);
           }
+          if (it == 0) PSTAMP(1);
           if (abort_flag) break;
           tc_fence_after();
           uint8_t* st = tiles + (size_t)s * C::STAGE_BYTES;
@@ -501,7 +558,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           umma_commit_pair(&empty_bar[s]);
         }
         umma_commit_pair(&tmem_full_bar[a]);
+        if (tile_i == 0) PSTAMP(2);
       }
+      PSTAMP(3);
+#ifdef GB_PAIR_TRACE
+      if (trace) trace[4] = (unsigned long long)tile_i;
+#endif
     }
     __syncwarp();
   } else {
@@ -513,7 +575,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       const int a = tile_i & 1;
       const int n0 = (t / tiles_m) * 2 * BM + (int)rank * BM, m0 = (t % tiles_m) * BNP;
       const int n = n0 + row;
+      PWAIT_BEGIN();
       const bool ok = mbar_wait(&tmem_full_bar[a], (tile_i >> 1) & 1);
+      if (tile_i > 0) PWAIT_END(5);
+      if (tile_i == 0) PSTAMP(1);
+      PSTAMP(3);
       if (!ok) {
         abort_flag = 1;
         if (lane == 0) atomicExch(p.status, STATUS_TIMEOUT + 11);
@@ -589,6 +655,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           epilogue_barrier();
         } else if (hc > 0 && fast) {
           float* fb = reinterpret_cast<float*>(staging);
+          PPHASE_BEGIN();
 #pragma unroll 1
           for (int c0 = 0; c0 < hc; c0 += 32) {
             float v[32];
@@ -597,8 +664,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             for (int j = 0; j < 32; ++j)
               if (c0 + j < hc) fb[(c0 + j) * BM + row] = v[j] + b;
           }
+          PPHASE(6);
           tc_fence_before();
           epilogue_barrier();
+          PPHASE(0);
           if (last && et == 0) mbar_arrive_leader(&tmem_empty_bar[a]);
           float* dst = (float*)p.out + (size_t)(m0 + h0) * p.ldo + n0;
           for (int idx = et; idx < hc * 32; idx += 128 * 4) {
@@ -624,7 +693,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
               }
             }
           }
+          PPHASE(7);
           epilogue_barrier();
+          PPHASE(0);
         } else {
           // nothing to store from this chunk, a ragged edge or an unaligned output: element by element
           if (hc > 0 && p.mode == OUT_SWIGLU) {
@@ -668,6 +739,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           if (last && et == 0) mbar_arrive_leader(&tmem_empty_bar[a]);
         }
       }
+      if (tile_i == 0) PSTAMP(2);
+      PSTAMP(4);
     }
   }
   tc_fence_before();
@@ -678,6 +751,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   __syncthreads();
   cluster_sync_all();                   // nobody leaves while its partner may still use its memory
   if (warp == 1) tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
+#ifdef GB_PAIR_TRACE
+  if (threadIdx.x == 0 && trace) { trace[5] = gtimer(); trace[6] = ((unsigned long long)gridDim.x << 48) | ((unsigned long long)p.M << 32) | ((unsigned long long)p.N << 8) | (unsigned long long)p.mode; trace[7] = (unsigned long long)p.total_kb; }
+#endif
 }
 
 // out = epilogue(sum over splits of the partial tiles (+ bias)), in split order.
@@ -1107,3 +1183,13 @@ GB_API int gb_linear_tc_no_alloc(const void* X, long long ldx, const void* W, lo
   }
   return 1;
 }
+
+#ifdef GB_PAIR_TRACE
+// Debug builds: where the pair kernel writes its stamps ([1024][2][3][8] 64-bit words), or null.
+GB_API int gb_linear_pair_trace(unsigned long long* buffer) {
+  unsigned int zero = 0;
+  GB_CUDA(cudaMemcpyToSymbol(g_pair_trace, &buffer, sizeof(buffer)));
+  GB_CUDA(cudaMemcpyToSymbol(g_pair_trace_launch, &zero, sizeof(zero)));
+  return GB_OK;
+}
+#endif

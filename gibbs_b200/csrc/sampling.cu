@@ -301,6 +301,57 @@ __global__ void argmax_kernel(const float* logits, long long ldv, int vocab, int
   }
 }
 
+// The same over a cluster of ARGMAX_CLUSTER blocks per row: each block scans its slice of the row
+// and leaves its best in the first block's shared memory (a store through distributed shared
+// memory); after the cluster barrier the first block picks among them.  (value, id) is a total
+// order, so the result does not depend on which block found what.
+constexpr int ARGMAX_CLUSTER = 8;
+
+__global__ void __cluster_dims__(ARGMAX_CLUSTER, 1, 1) __launch_bounds__(512)
+argmax_cluster_kernel(const float* logits, long long ldv, int vocab, int* __restrict__ out) {
+  __shared__ Cand warp_c[32];
+  __shared__ Cand block_c[ARGMAX_CLUSTER];
+  pdl_trigger();
+  unsigned rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const int row = blockIdx.x / ARGMAX_CLUSTER;
+  // slices of whole 16-byte pieces
+  const int per = (((vocab + ARGMAX_CLUSTER - 1) / ARGMAX_CLUSTER) + 3) & ~3;
+  const int lo = min(vocab, (int)rank * per), hi = min(vocab, lo + per);
+  pdl_wait();
+  const float* x = logits + (size_t)row * ldv;
+  Cand best = {0.f, -1};
+  const bool vec = (ldv % 4 == 0) && (((uintptr_t)logits & 15) == 0);
+  for_each_logit(x + lo, hi - lo, vec, [&](float v, int id) {
+    const Cand c = {v, lo + id};
+    if (v == v && better(c, best)) best = c;
+  });
+  best = warp_best(best);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  if (lane == 0) warp_c[warp] = best;
+  __syncthreads();
+  if (warp == 0) {
+    Cand c = lane < nwarps ? warp_c[lane] : Cand{0.f, -1};
+    c = warp_best(c);
+    if (lane == 0) {
+      const unsigned local = (unsigned)__cvta_generic_to_shared(&block_c[rank]);
+      unsigned remote;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(0u));
+      asm volatile("st.shared::cluster.v2.b32 [%0], {%1, %2};" ::"r"(remote), "r"(__float_as_uint(c.v)), "r"(c.id)
+                   : "memory");
+    }
+  }
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (rank == 0 && threadIdx.x == 0) {
+    Cand c = block_c[0];
+#pragma unroll
+    for (int i = 1; i < ARGMAX_CLUSTER; ++i)
+      if (better(block_c[i], c)) c = block_c[i];
+    out[row] = c.id < 0 ? 0 : c.id;
+  }
+}
+
 // What a row's distribution says about a picked token (MisterTK/gibbs logprob_info,
 // src/scheduler/mod.rs:272-315): the picked token's probability, the exact entropy of
 // softmax(logits) (terms below 1e-12 dropped, as there) and the k most probable tokens, by (logit
@@ -411,7 +462,14 @@ GB_API int gb_sample(const float* logits, long long ldv, int rows, int vocab, co
   int threads = 64;
   while (threads < 1024 && threads * 8 < vocab) threads <<= 1;
   if (temperature == nullptr) {
-    gb_launch(argmax_kernel, dim3(rows), dim3(threads), 0, stream, logits, ldv, vocab, out);
+    if (vocab >= 8192 && rows <= 1024) {
+      // a large row and few of them (decoding): eight blocks share a row
+      int th = 64;
+      while (th < 512 && th * 8 * ARGMAX_CLUSTER < vocab) th <<= 1;
+      gb_launch(argmax_cluster_kernel, dim3(rows * ARGMAX_CLUSTER), dim3(th), 0, stream, logits, ldv, vocab, out);
+    } else {
+      gb_launch(argmax_kernel, dim3(rows), dim3(threads), 0, stream, logits, ldv, vocab, out);
+    }
     GB_CHECK_LAUNCH("gb_sample (argmax)");
     return GB_OK;
   }

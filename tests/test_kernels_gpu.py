@@ -1042,3 +1042,98 @@ def test_logprob_info_matches_the_plain_rule(vocab, k):
         assert got[:len(order)] == order and all(i == -1 for i in got[len(order):])
         for j, i in enumerate(order):
             assert abs(probs[r, j].item() - float(p[i])) < 1e-5
+
+
+# --------------------------------------------------------------------------- kernels of a decode step: one trip to L2
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,dim,splits,use_bias,gather", [
+    (8, 2048, 9, False, False), (1, 2048, 16, True, False), (64, 1536, 8, False, False), (5, 1000, 3, True, True),
+    (3, 4096, 9, False, False), (2, 8192, 4, False, False), (2, 8192, 9, True, False), (7, 72, 2, False, True),
+    (4, 66, 5, True, False)])
+def test_rmsnorm_adds_the_partial_sums_of_many_splits_in_split_order(n, dim, splits, use_bias, gather):
+    """The norm that follows a split-K product: every variant (partial sums through shared memory,
+    in registers when they do not fit there, element by element for rows of no 16-byte pieces)
+    against the sum formed in split order in 32-bit and a float64 norm."""
+    from gibbs_b200 import ops
+    torch.manual_seed(n + dim + splits)
+    eps = 1e-5
+    x0 = torch.randn(n, dim)
+    ws = torch.randn(splits, n, dim) * 0.3
+    bias = torch.randn(dim) if use_bias else None
+    gain = 1 + 0.1 * torch.randn(dim)
+    total = x0.clone()
+    for s in range(splits):
+        total = total + ws[s]                              # float32, split order: the kernel's own order
+    if use_bias:
+        total = total + bias
+    t64 = total.double()
+    want_h = t64 / torch.sqrt((t64 ** 2).mean(-1, keepdim=True) + eps) * gain.double()
+    x = x0.clone().to(DEV)
+    pend = (ws.to(DEV), bias.to(DEV) if use_bias else None)
+    if gather:
+        rows = torch.tensor([n - 1, 0], dtype=torch.int32, device=DEV)
+        out = torch.empty(2, dim, dtype=torch.float32, device=DEV)
+        ops.rmsnorm(x, gain.to(DEV), eps, out, rows, pending=pend)
+        _close(out, want_h[[n - 1, 0]], "float32")
+        assert torch.equal(x.cpu(), x0)
+    else:
+        out = torch.empty(n, dim, dtype=torch.float32, device=DEV)
+        ops.rmsnorm(x, gain.to(DEV), eps, out, None, pending=pend)
+        _close(out, want_h, "float32")
+        assert torch.equal(x.cpu(), total)                 # the stream carries the sum, bit for bit
+
+
+@pytest.mark.gpu
+def test_qk_norm_rope_store_from_partial_tiles_that_are_not_16_byte_aligned():
+    """Partial tiles that start 4 bytes off a 16-byte boundary take the kernel's plain loads instead
+    of its 16-byte copies; same bits either way."""
+    from gibbs_b200 import ops
+    torch.manual_seed(77)
+    heads, kvh, hd, rd, splits = 6, 2, 64, 64, 6
+    before, q_lens, ps, n_pages = [9, 37, 5], [1, 1, 1], 8, 40
+    bt, tok_req, tok_pos = _layout(before, q_lens, ps, n_pages, seed=hd)
+    n = sum(q_lens)
+    cols = (heads + 2 * kvh) * hd
+    ws, total = _split_partials(torch.randn(n, cols), splits, seed=3)
+    buf = torch.empty(ws.numel() + 1, dtype=torch.float32, device=DEV)
+    off = buf[1:].view(ws.shape)
+    off.copy_(ws)
+    assert off.data_ptr() % 16 == 4 and ws.data_ptr() % 16 == 0
+    qg, kg = (1 + 0.2 * torch.randn(hd)).to(DEV), (1 + 0.2 * torch.randn(hd)).to(DEV)
+    inv = torch.tensor([1.0 / (10000.0 ** (2 * j / rd)) for j in range(rd // 2)], dtype=torch.float32, device=DEV)
+    t = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    pages = lambda: torch.zeros(n_pages, kvh, ps, hd, dtype=torch.bfloat16, device=DEV)
+    kp_a, vp_a, kp_b, vp_b = pages(), pages(), pages(), pages()
+    qa = torch.empty(n, heads * hd, dtype=torch.bfloat16, device=DEV)
+    qb = torch.empty_like(qa)
+    for w, q, kp, vp in ((ws, qa, kp_a, vp_a), (off, qb, kp_b, vp_b)):
+        ops.qk_norm_rope_store_partials(ops.Partials(w, None, torch.bfloat16), q, heads, kvh, hd, qg, kg, 1e-5, inv, rd,
+                                        False, t(tok_req), t(tok_pos), t(bt), kp, vp, status)
+    assert torch.equal(qa, qb) and torch.equal(kp_a, kp_b) and torch.equal(vp_a, vp_b)
+    assert qa.float().abs().sum() > 0 and kp_a.float().abs().sum() > 0 and int(status.item()) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("vocab", [65536, 50001, 8192, 8200])
+def test_argmax_over_a_cluster_of_blocks(vocab):
+    """Rows of 8,192 and more are scanned by eight blocks each: ties across their slices go to the
+    lower id, NaN never wins, a maximum at a slice's edge is found."""
+    from gibbs_b200 import ops
+    torch.manual_seed(vocab)
+    per = (((vocab + 7) // 8) + 3) // 4 * 4
+    x = torch.randn(9, vocab)
+    x[0, per - 1] = x[0, per] = 50.0                         # tie across two slices
+    x[1, 3] = float("nan")
+    x[1, vocab - 1] = 60.0                                   # the last element
+    x[2, :] = float("-inf")
+    x[2, 5 * per + 1] = -1e30
+    x[3, :] = float("nan")                                   # nothing can win: id 0
+    x[4, 7 * per] = 70.0                                     # first element of the last slice
+    x[5, 0] = 70.0
+    x[6, 3 * per - 1] = 80.0                                 # last element of a slice
+    x[7, 6 * per + 2] = x[7, 2 * per + 2] = 90.0             # tie far apart
+    out = torch.empty(9, dtype=torch.int32, device=DEV)
+    ops.sample(x.to(DEV), out)
+    want = [per - 1, vocab - 1, 5 * per + 1, 0, 7 * per, 0, 3 * per - 1, 2 * per + 2, int(torch.argmax(x[8]))]
+    assert out.tolist() == want
