@@ -106,6 +106,7 @@ attention_tc_kernel(const AttnParams p) {
   pdl_trigger();
   // The wait for the kernel in front (which wrote this step's q, k and v) comes further down: the
   // step's metadata, the page ids and the key tiles that earlier steps filled are fetched first.
+  // (Asking L2 for the tiles behind those as well changed nothing: measured, not kept.)
   constexpr int BQ = KSPLIT ? 16 : 16 * NW;
   constexpr int NN = KSPLIT ? 2 : KT / 8;                    // 8-key column tiles per warp and key tile
   using TL = Tile<HD>;
@@ -127,10 +128,17 @@ attention_tc_kernel(const AttnParams p) {
   // within a request, from its last tile (which sees the most keys) to its first, so that the
   // long tiles of a causal prompt do not form the tail of the launch.
   int r = p.n_requests - 1, tile = (int)blockIdx.y, found = 0;
-  for (; r >= 0; --r) {
-    const int nt = (p.q_len[r] + tpt - 1) / tpt;
-    if (tile < nt) { found = 1; tile = nt - 1 - tile; break; }
-    tile -= nt;
+  if (KSPLIT) {
+    // (a launch of this kind has one tile per request: no search, no dependent loads)
+    r -= tile;
+    tile = 0;
+    found = r >= 0;
+  } else {
+    for (; r >= 0; --r) {
+      const int nt = (p.q_len[r] + tpt - 1) / tpt;
+      if (tile < nt) { found = 1; tile = nt - 1 - tile; break; }
+      tile -= nt;
+    }
   }
   if (!found) return;
   const int qlen = p.q_len[r], first_tok = tile * tpt;
@@ -369,7 +377,7 @@ attention_tc_kernel(const AttnParams p) {
     l_run[ri] += __shfl_xor_sync(0xffffffffu, l_run[ri], 1);
     l_run[ri] += __shfl_xor_sync(0xffffffffu, l_run[ri], 2);
   }
-  if (KSPLIT) {
+  if constexpr (KSPLIT) {
     // merge the four warps' states: rows 0..15, in warp order
     float* pm = reinterpret_cast<float*>(sk);                // [NW][16] maxima
     float* pl = pm + NW * 16;                                // [NW][16] sums
@@ -416,7 +424,7 @@ attention_tc_kernel(const AttnParams p) {
       }
     }
     return;
-  }
+  } else {
 #pragma unroll
   for (int ri = 0; ri < 2; ++ri) {
     if (!rvalid[ri]) continue;
@@ -440,6 +448,7 @@ attention_tc_kernel(const AttnParams p) {
         p.part_ml[prow * 2 + 1] = l_run[ri];
       }
     }
+  }
   }
 }
 

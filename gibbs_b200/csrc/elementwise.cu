@@ -18,6 +18,31 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* ids, float*
   if (id < 0 || id >= vocab) id = 0;
   const T* src = table + (size_t)id * dim;
   float* dst = out + (size_t)row * dim;
+  if (sizeof(T) == 2 && dim % 8 == 0 && (((uintptr_t)table | (uintptr_t)out) & 15) == 0) {
+    // a bfloat16 row in 16-byte pieces: each thread's loads are requested before any is used
+    const uint4* s8 = reinterpret_cast<const uint4*>(src);
+    const int n8 = dim >> 3;
+    for (int c0 = threadIdx.x; c0 < n8; c0 += 4 * blockDim.x) {
+      uint4 raw[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * blockDim.x;
+        raw[u] = s8[c < n8 ? c : c0];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * blockDim.x;
+        if (c < n8) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+          const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+          const float2 e = __bfloat1622float2(h[2]), f = __bfloat1622float2(h[3]);
+          reinterpret_cast<float4*>(dst)[2 * c] = make_float4(a.x, a.y, b.x, b.y);
+          reinterpret_cast<float4*>(dst)[2 * c + 1] = make_float4(e.x, e.y, f.x, f.y);
+        }
+      }
+    }
+    return;
+  }
   for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = to_f32(src[d]);
 }
 

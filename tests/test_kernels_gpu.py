@@ -33,12 +33,13 @@ def _quant(t, dtype):
 
 # --------------------------------------------------------------------------- embed / norm / swiglu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_embed(dtype):
+@pytest.mark.parametrize("dim", [96, 2048, 100, 4104])     # 16-byte pieces (one or several per thread) or single values
+def test_embed(dtype, dim):
     from gibbs_b200 import ops
     torch.manual_seed(0)
-    table, ref = _quant(torch.randn(1000, 96), dtype)
+    table, ref = _quant(torch.randn(1000, dim), dtype)
     ids = torch.tensor([0, 999, 5, 5, 123], dtype=torch.int32, device=DEV)
-    out = torch.empty(5, 96, dtype=torch.float32, device=DEV)
+    out = torch.empty(5, dim, dtype=torch.float32, device=DEV)
     ops.embed(table, ids, out)
     assert torch.equal(out.cpu().double(), ref[ids.cpu().long()])
 
