@@ -117,9 +117,10 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--workload", choices=["serve700m", "long2p6b", "sweep"], default=None,
                     help="run one of the other reference workloads instead (prints its own JSON line)")
-    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "trace"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "prefill-timeline", "trace"], default=None,
                     help="measure one phase only (for short profiler captures; the line is then partial); "
-                         "'timeline': the kernels of one decode step inside its graph, from CUPTI; 'trace': time "
+                         "'timeline' / 'prefill-timeline': the kernels of one decode step inside its graph / of one "
+                         "prompt step, from CUPTI; 'trace': time "
                          "stamps from inside the cluster product kernels (a -DGB_DECODE_TRACE build)")
     a = ap.parse_args()
     if a.impl == "reference":
@@ -160,6 +161,9 @@ def main():
         return 0
     if a.only == "timeline":
         print(B.format_timeline(B.decode_timeline(eng, a.batch, PROMPT_LEN, seed=SEED)))
+        return 0
+    if a.only == "prefill-timeline":
+        print(B.format_timeline(B.prefill_timeline(eng, PROMPT_LEN, seed=SEED), "prompt"))
         return 0
     if a.only == "trace":
         print(B.decode_kernel_trace(eng, a.batch, PROMPT_LEN, seed=SEED))

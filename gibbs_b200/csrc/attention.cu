@@ -112,28 +112,38 @@ __global__ void qk_norm_rope_store_vec_kernel(bf16* __restrict__ qkv, long long 
                                               int write_kv, int* __restrict__ status) {
   __shared__ float cs[64], sn[64];                       // hd / 2 <= 64
   pdl_trigger();
-  pdl_wait();
   const int t = blockIdx.x;
-  const int pos = tok_pos[t];
   const int half = hd >> 1;
+  const int tps = hd >> 3;                               // threads per head: 4, 8 or 16
+  const int slots = heads + (write_kv ? 2 * kv_heads : 0);
+  const int total = slots * tps;                         // a multiple of 4; the block is padded to whole warps
+  // Position, page and angles come from the step's metadata and from tables: they are worked out
+  // before the wait for the product in front, and this thread's first piece of the row is
+  // requested right after it, before anything that would make it wait.
+  const int pos = tok_pos[t];
   const float mscale = inv_freq[half];
+  int page = 0;
+  bool bad_page = false;
+  if (write_kv) {
+    page = block_table[(size_t)tok_req[t] * bt_stride + pos / page_size];
+    bad_page = page < 0 || page >= n_pages;
+  }
   for (int j = threadIdx.x; j < half; j += blockDim.x) {
     const float ang = (float)pos * inv_freq[j];
     cs[j] = cosf(ang) * mscale;
     sn[j] = sinf(ang) * mscale;
   }
-  __syncthreads();
-  const int tps = hd >> 3;                               // threads per head: 4, 8 or 16
-  const int slots = heads + (write_kv ? 2 * kv_heads : 0);
-  int page = 0;
-  if (write_kv) {
-    page = block_table[(size_t)tok_req[t] * bt_stride + pos / page_size];
-    if (page < 0 || page >= n_pages) {
-      if (threadIdx.x == 0) atomicExch(status, STATUS_BAD_PAGE_WRITE);
-      write_kv = 0;                                      // q is still processed
-    }
+  pdl_wait();
+  uint4 raw0 = make_uint4(0, 0, 0, 0);
+  if ((int)threadIdx.x < total) {
+    const int slot0 = threadIdx.x / tps, sub0 = threadIdx.x - slot0 * tps;
+    raw0 = __ldcg(reinterpret_cast<const uint4*>(qkv + (size_t)t * ld + (size_t)slot0 * hd + sub0 * 8));
   }
-  const int total = slots * tps;                         // a multiple of 4; the block is padded to whole warps
+  __syncthreads();
+  if (bad_page) {
+    if (threadIdx.x == 0) atomicExch(status, STATUS_BAD_PAGE_WRITE);
+    write_kv = 0;                                        // q is still processed
+  }
   for (int idx0 = 0; idx0 < total; idx0 += blockDim.x) {
     const int idx = idx0 + threadIdx.x;
     const bool active = idx < total;
@@ -144,7 +154,7 @@ __global__ void qk_norm_rope_store_vec_kernel(bf16* __restrict__ qkv, long long 
     bf16* src = qkv + (size_t)t * ld + (size_t)slot * hd + sub * 8;
     float v[8];
     {
-      const uint4 raw = active ? *reinterpret_cast<const uint4*>(src) : make_uint4(0, 0, 0, 0);
+      const uint4 raw = idx0 == 0 ? raw0 : (active ? *reinterpret_cast<const uint4*>(src) : make_uint4(0, 0, 0, 0));
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {

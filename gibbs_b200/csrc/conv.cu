@@ -148,19 +148,34 @@ __global__ void short_conv_out_run_kernel(const bf16* bcx, long long ld, const f
   float win[K][8];                                           // win[j]: the product that meets tap j for the current token
   int cur_req = -1, first = 0;
   const int t0 = run * RUN, t1 = min(t0 + RUN, n_tokens);
-  for (int t = t0; t < t1; ++t) {
-    const int r = tok_req[t];
+  // All rows of the run are requested before the first is used (a thread that fetched them token
+  // by token would spend eight memory latencies one after the other).
+  uint4 rb[RUN], rx[RUN], rg[RUN];
+  int rreq[RUN];
+#pragma unroll
+  for (int u = 0; u < RUN; ++u) {
+    const int t = t0 + u < t1 ? t0 + u : t1 - 1;
+    const bf16* row = bcx + (size_t)t * ld;
+    rb[u] = __ldcg(reinterpret_cast<const uint4*>(row + c));
+    rx[u] = __ldcg(reinterpret_cast<const uint4*>(row + 2 * hidden + c));
+    rg[u] = __ldcg(reinterpret_cast<const uint4*>(row + hidden + c));
+    rreq[u] = tok_req[t];
+  }
+#pragma unroll
+  for (int u = 0; u < RUN; ++u) {
+    const int t = t0 + u;
+    if (t >= t1) break;
+    const int r = rreq[u];
     bool restart = r != cur_req;
     if (restart) {
       cur_req = r;
       first = q_start[r];
     }
     const int i = t - first;
-    const bf16* row = bcx + (size_t)t * ld;
     float b[8], x[8], g[8];
-    unpack(*reinterpret_cast<const uint4*>(row + c), b);
-    unpack(*reinterpret_cast<const uint4*>(row + 2 * hidden + c), x);
-    unpack(*reinterpret_cast<const uint4*>(row + hidden + c), g);
+    unpack(rb[u], b);
+    unpack(rx[u], x);
+    unpack(rg[u], g);
     if (restart) {
       // the K-1 older positions: earlier tokens of this request in the batch, or its state
       const float* st = state + (size_t)slot_ids[r] * slot_stride;

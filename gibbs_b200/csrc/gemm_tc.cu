@@ -69,6 +69,7 @@ struct GemmParams {
   int M, N;                     // tokens, weight rows (for SwiGLU: 2 * features)
   int total_kb, kb_per_split, splits;
   float* ws;                    // [splits][M][N] partial tiles (splits > 1)
+  int bnp;                      // CTA-pair kernel: tokens per tile
   int stream_weights;           // 1: read W with an evict-first L2 hint
   int vec_store;                // 1: out rows are 16-byte aligned (base and row stride)
   int* status;
@@ -411,9 +412,13 @@ __device__ __forceinline__ unsigned long long gtimer() {
 #define PWAIT_END(i) do {} while (0)
 #endif
 
+#ifndef GB_PAIR_DIRECT_F32
+#define GB_PAIR_DIRECT_F32 1
+#endif
+
 struct PairCfg {
-  static constexpr int BNP = 256;                         // tokens per tile
-  static constexpr int X_TILE_BYTES = (BNP / 2) * BK * 2; // this CTA's half of the token rows
+  static constexpr int BNP_MAX = 256;                     // most tokens per tile (GemmParams::bnp: 128..256 in steps of 16)
+  static constexpr int X_TILE_BYTES = (BNP_MAX / 2) * BK * 2; // room for this CTA's half of the token rows
   static constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES;
 #ifndef GB_PAIR_STAGES
 #define GB_PAIR_STAGES 6
@@ -428,7 +433,8 @@ __global__ void __launch_bounds__(192)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                     const GemmParams p) {
   using C = PairCfg;
-  constexpr int BNP = C::BNP;
+  const int BNP = p.bnp;                                  // tokens per tile of this launch
+  constexpr int ACC_COLS = C::BNP_MAX;                    // tensor-memory columns per accumulator
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t full_bar[C::STAGES], empty_bar[C::STAGES], tmem_full_bar[2], tmem_empty_bar[2];
   __shared__ uint32_t tmem_slot;
@@ -505,7 +511,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           }
           if (abort_flag) break;
           uint8_t* st = tiles + (size_t)s * C::STAGE_BYTES;
-          if (rank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * C::STAGE_BYTES);
+          if (rank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * (W_TILE_BYTES + (BNP / 2) * BK * 2));
           tma_load_2d_pair(st, &tmap_w, i * BK, n0, &full_bar[s]);
           tma_load_2d_pair(st + W_TILE_BYTES, &tmap_x, i * BK, m0, &full_bar[s]);
 #ifdef GB_PAIR_PREFETCH
@@ -519,7 +525,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     __syncwarp();
   } else if (warp == 1) {
     if (rank == 0 && elect_one()) {
-      constexpr uint32_t idesc = idesc_bf16_f32(2 * BM, BNP);
+      const uint32_t idesc = idesc_bf16_f32(2 * BM, BNP);
       int it = 0, tile_i = 0;
       for (int t = pair; t < n_tiles && !abort_flag; t += n_pairs, ++tile_i) {
         const int a = tile_i & 1;
@@ -533,7 +539,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           PWAIT_END(5);
         }
         tc_fence_after();
-        const uint32_t acc = tmem_base + (uint32_t)(a * BNP);
+        const uint32_t acc = tmem_base + (uint32_t)(a * ACC_COLS);
         for (int i = 0; i < nkb; ++i, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1;
@@ -587,7 +593,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       tc_fence_after();
       epilogue_barrier();
       if (abort_flag) break;
-      const uint32_t acc = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(a * BNP);
+      const uint32_t acc = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(a * ACC_COLS);
       const int cols = max(0, min(BNP, M - m0));
       const bool fast = p.vec_store && n0 + BM <= N;
       const float b = (p.bias && n < N) ? p.bias[n] : 0.f;
@@ -653,6 +659,23 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 *reinterpret_cast<const uint4*>(ob + mm * BM + piece * 8);
           }
           epilogue_barrier();
+        } else if (hc > 0 && fast && p.mode == OUT_F32 && GB_PAIR_DIRECT_F32) {
+          // A plain 32-bit store needs no staging: a lane is a weight row, so one store of a warp
+          // is 128 contiguous bytes of one token's row, a whole line.
+          float* dst = (float*)p.out + (size_t)(m0 + h0) * p.ldo + n;
+#pragma unroll 1
+          for (int c0 = 0; c0 < hc; c0 += 32) {
+            float v[32];
+            tmem_ld_32(acc + (uint32_t)(h0 + c0), v);
+            if (last && c0 + 32 >= hc) {
+              tc_fence_before();
+              epilogue_barrier();
+              if (et == 0) mbar_arrive_leader(&tmem_empty_bar[a]);
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (c0 + j < hc) dst[(size_t)(c0 + j) * p.ldo] = v[j] + b;
+          }
         } else if (hc > 0 && fast) {
           float* fb = reinterpret_cast<float*>(staging);
           PPHASE_BEGIN();
@@ -853,6 +876,26 @@ int gb_pair_min() {
 
 int gb_pair();
 
+// Tokens per tile of the CTA-pair kernel: 256 at most; fewer (in steps of 16, the instruction's
+// grain) when that saves a round of tiles over the 74 pairs or rows of padding.  The cost of a
+// k-block is taken as its shared-memory traffic, which is what the kernel was measured to be
+// bound by: 32 KB for the weight rows plus 192 bytes per token.
+int pick_bnp(int M, int N) {
+  static int forced = -1;
+  if (forced < 0) { const char* e = getenv("GIBBS_B200_PAIR_BNP"); forced = e ? atoi(e) : 0; }
+  if (forced >= 128 && forced <= 256 && forced % 16 == 0) return forced;
+  const long long tiles_n = gb_div_up(N, 2 * BM);
+  int best = 256;
+  long long best_cost = -1;
+  for (int bnp = 256; bnp >= 128; bnp -= 16) {
+    const long long tiles = tiles_n * gb_div_up(M, bnp);
+    const long long rounds = (tiles + 73) / 74;
+    const long long cost = rounds * (32768 + 192 * bnp) + 512 * tiles / 74;   // (a little per tile: its epilogue's tail)
+    if (best_cost < 0 || cost < best_cost) { best = bnp; best_cost = cost; }
+  }
+  return best;
+}
+
 // Whether the product runs on CTA pairs (256 x 256 tiles; they never split K: with K split four
 // ways a pair per tile and split was measured slower than the one-tile CTAs below, at every size).
 bool runs_on_pairs(int M, int N) {
@@ -941,7 +984,7 @@ int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& 
     GB_CUDA(cudaGetDevice(&dev));
     GB_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
   }
-  const long long tiles = (long long)gb_div_up(p.N, 2 * BM) * gb_div_up(p.M, PairCfg::BNP);
+  const long long tiles = (long long)gb_div_up(p.N, 2 * BM) * gb_div_up(p.M, p.bnp);
   const int pairs = (int)(tiles < n_sm / 2 ? tiles : n_sm / 2);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);
@@ -1034,8 +1077,9 @@ GB_API int gb_linear_tc(const void* X, long long ldx, const void* W, long long l
       tw = it->second;
     }
   }
-  const bool pairs = splits == 1 && runs_on_pairs(M, N);    // each CTA of a pair stages 128 token rows
-  if (!make_tmap(&tx, X, M, K, ldx, pairs ? 128 : bn)) GB_FAIL(GB_ERR_CUDA, "gb_linear_tc: cuTensorMapEncodeTiled failed (X)");
+  const bool pairs = splits == 1 && runs_on_pairs(M, N);    // each CTA of a pair stages half of a tile's token rows
+  const int bnp = pairs ? pick_bnp(M, N) : 256;
+  if (!make_tmap(&tx, X, M, K, ldx, pairs ? bnp / 2 : bn)) GB_FAIL(GB_ERR_CUDA, "gb_linear_tc: cuTensorMapEncodeTiled failed (X)");
 
   if (defer == 2 && splits == 1) {
     if (mode != OUT_F32_ACC || workspace == nullptr)
@@ -1050,6 +1094,7 @@ GB_API int gb_linear_tc(const void* X, long long ldx, const void* W, long long l
   p.bias = bias; p.out = out; p.ldo = ldo; p.mode = mode; p.M = M; p.N = N;
   p.total_kb = gb_div_up(K, BK); p.kb_per_split = kb_per_split; p.splits = splits;
   p.ws = workspace;
+  p.bnp = bnp;
   const bool decode_like = M <= 64;
   p.stream_weights = (decode_like && (flags & 1)) ? 1 : 0;   // flags bit 0: evict-first hint for the weights
   p.vec_store = (((uintptr_t)out & 15) == 0 && (ldo * (mode == OUT_BF16 || mode == OUT_SWIGLU ? 2 : 4)) % 16 == 0) ? 1 : 0;
@@ -1161,6 +1206,7 @@ GB_API int gb_linear_tc_no_alloc(const void* X, long long ldx, const void* W, lo
   p.bias = bias; p.out = out; p.ldo = ldo; p.mode = mode; p.M = M; p.N = N;
   p.total_kb = gb_div_up(K, BK); p.kb_per_split = kb_per_split; p.splits = splits;
   p.ws = ws;
+  p.bnp = 256;                  // (the CTA-pair kernel is not used here)
   p.stream_weights = M <= 64 ? 1 : 0;
   p.vec_store = (((uintptr_t)out & 15) == 0 && (ldo * (mode == OUT_BF16 || mode == OUT_SWIGLU ? 2 : 4)) % 16 == 0) ? 1 : 0;
   p.status = status;

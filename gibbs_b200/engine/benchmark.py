@@ -299,10 +299,44 @@ def decode_timeline(engine: Engine, batch: int, prompt_len: int, seed: int = 0) 
     return rows
 
 
-def format_timeline(rows) -> str:
+def prefill_timeline(engine: Engine, n_tokens: int, seed: int = 0) -> list:
+    """The same for ONE prompt step of ``n_tokens`` tokens (launched kernel by kernel, not from a
+    graph): rows (name, grid, start_us, dur_us, adds_us)."""
+    from torch.profiler import ProfilerActivity, profile
+    import tempfile
+    rng = np.random.default_rng(seed)
+
+    def one_step():
+        ids = rng.integers(0, engine.vocab_size, n_tokens).tolist()
+        engine.open("prefill-timeline")
+        engine.step([StepEntry("prefill-timeline", ids, [n_tokens - 1])])
+        torch.cuda.synchronize()
+        engine.close("prefill-timeline")
+
+    for _ in range(3):
+        one_step()
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+        one_step()
+    with tempfile.TemporaryDirectory() as tmp:
+        path = Path(tmp) / "trace.json"
+        prof.export_chrome_trace(str(path))
+        events = [e for e in json.loads(path.read_text())["traceEvents"] if e.get("cat") == "kernel"]
+    events.sort(key=lambda e: e["ts"])
+    first = next(i for i, e in enumerate(events) if "embed_kernel" in e["name"])
+    step = events[first:]
+    t0 = prev_end = step[0]["ts"]
+    rows = []
+    for e in step:
+        end = e["ts"] + e["dur"]
+        rows.append((e["name"], tuple(e["args"].get("grid", ())), e["ts"] - t0, e["dur"], end - prev_end))
+        prev_end = max(prev_end, end)
+    return rows
+
+
+def format_timeline(rows, what: str = "decode") -> str:
     short = lambda n: n.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0]
     span = max(r[2] + r[3] for r in rows)
-    out = [f"one decode step: {len(rows)} kernels, {span:.1f} us from the first kernel's start to the last one's end",
+    out = [f"one {what} step: {len(rows)} kernels, {span:.1f} us from the first kernel's start to the last one's end",
            "by kernel: launches, sum of durations (they overlap), sum added to the chain of dependent launches"]
     agg: dict = {}
     for name, grid, _, dur, adds in rows:

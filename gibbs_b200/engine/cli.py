@@ -30,7 +30,7 @@ def build_parser() -> argparse.ArgumentParser:
                     help="context length (default: the model's max_position_embeddings, at most 4096)")
     ap.add_argument("--temperature", type=float, default=None, help="default 0.7 for --prompt; <= 0 is greedy")
     ap.add_argument("--top-p", type=float, default=None, help="default 0.9")
-    ap.add_argument("--top-k", type=int, default=50, help="1..64, default 50")
+    ap.add_argument("--top-k", type=int, default=50, help="1..64, default 50; 0: off (the sampler's 64 candidates, narrowed by --top-p only)")
     ap.add_argument("--seed", type=int, default=None, help="sampling seed; also the seed of --random")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--page-size", type=int, default=16)

@@ -31,15 +31,15 @@ class TokenLogprobInfo:
 class SamplingParams:
     temperature: Optional[float] = None      # None: DEFAULT_TEMPERATURE; <= 0 is greedy
     top_p: Optional[float] = None            # None: DEFAULT_TOP_P
-    top_k: int = DEFAULT_TOP_K               # 1..64
+    top_k: int = DEFAULT_TOP_K               # 1..64; 0: no narrower limit than the sampler's own 64 candidates
     max_new_tokens: int = DEFAULT_MAX_NEW_TOKENS
     seed: Optional[int] = None               # None: derived from the scheduler's seed and the request id
     stop_ids: tuple = ()                     # besides the model's own end-of-sequence ids
     top_logprobs: Optional[int] = None       # report each token's probability, the entropy and this many candidates
 
     def __post_init__(self):
-        if not 1 <= self.top_k <= MAX_TOP_K:
-            raise ValueError(f"top_k {self.top_k} outside 1..{MAX_TOP_K}")
+        if not 0 <= self.top_k <= MAX_TOP_K:
+            raise ValueError(f"top_k {self.top_k} outside 0..{MAX_TOP_K} (0: off)")
         if self.max_new_tokens < 0:
             raise ValueError(f"max_new_tokens {self.max_new_tokens}")
         if self.top_logprobs is not None and not 1 <= self.top_logprobs <= MAX_TOP_LOGPROBS:
@@ -49,6 +49,12 @@ class SamplingParams:
     def resolved_temperature(self) -> float:
         t = DEFAULT_TEMPERATURE if self.temperature is None else float(self.temperature)
         return max(t, 0.0)
+
+    @property
+    def resolved_top_k(self) -> int:
+        """The number of candidates the sampling kernel keeps: top_k, or all 64 it can hold when
+        top_k is 0 (then top_p alone narrows them)."""
+        return self.top_k if self.top_k > 0 else MAX_TOP_K
 
     @property
     def resolved_top_p(self) -> float:

@@ -87,7 +87,7 @@ class Sampler:
             return ops.sample(logits, out)
         host = torch.tensor(
             [[p.resolved_temperature if not p.greedy else 0.0, p.resolved_top_p] for p in params], dtype=torch.float32)
-        ints = torch.tensor([[p.top_k] for p in params], dtype=torch.int32)
+        ints = torch.tensor([[p.resolved_top_k] for p in params], dtype=torch.int32)
         longs = torch.tensor([[_signed(s), int(c)] for s, c in zip(seeds, counters)], dtype=torch.int64)
         host, ints, longs = (t.to(self.device, non_blocking=True) for t in (host, ints, longs))
         return ops.sample(logits, out, temperature=host[:, 0].contiguous(), top_k=ints[:, 0].contiguous(),

@@ -434,3 +434,14 @@ def test_top_logprobs_are_reported_for_the_requests_that_ask():
     assert "launch fed" not in eng.events            # every step held a request whose logits had to be read
     with pytest.raises(ValueError, match="top_logprobs"):
         SamplingParams(top_logprobs=0)
+
+
+def test_sampling_params_top_k_zero_means_off_and_bounds_are_checked():
+    """top_k 0 switches the narrower limit off: the sampler then keeps all the candidates it can
+    hold (64) and top_p alone cuts them; anything outside 0..64 is refused."""
+    assert SamplingParams(top_k=0).resolved_top_k == 64
+    assert SamplingParams(top_k=1).resolved_top_k == 1
+    assert SamplingParams().resolved_top_k == 50
+    for bad in (-1, 65):
+        with pytest.raises(ValueError):
+            SamplingParams(top_k=bad)
