@@ -133,6 +133,8 @@ __global__ void qk_norm_rope_store_vec_kernel(bf16* __restrict__ qkv, long long 
     cs[j] = cosf(ang) * mscale;
     sn[j] = sinf(ang) * mscale;
   }
+  gb_pin(page);                                          // (stays in front of the wait, see gb_pin)
+  gb_pin(bad_page);
   pdl_wait();
   uint4 raw0 = make_uint4(0, 0, 0, 0);
   if ((int)threadIdx.x < total) {
@@ -263,13 +265,20 @@ __global__ void qk_norm_rope_store_partials_kernel(const float* ws, int splits, 
     for (int m = 0; m < 4; ++m)
       if (lane + 32 * m < hd) pb[m] = bias[slot * hd + lane + 32 * m];
   }
+  // (pinned: all of this stays in front of the wait, see gb_pin)
+#pragma unroll
+  for (int k = 0; k < PRE; ++k) { gb_pin(pc[k]); gb_pin(ps[k]); gb_pin(pg0[k]); gb_pin(pg1[k]); }
+#pragma unroll
+  for (int m = 0; m < 4; ++m) gb_pin(pb[m]);
+  gb_pin(dst);
+  gb_pin(bad_page);
+  const size_t split_stride = (size_t)n_tokens * cols;
+  const float* row0 = ws + (size_t)t * cols + (size_t)slot * hd;
   pdl_wait();
   if (bad_page) {
     if (lane == 0) atomicExch(status, STATUS_BAD_PAGE_WRITE);
     return;
   }
-  const size_t split_stride = (size_t)n_tokens * cols;
-  const float* row0 = ws + (size_t)t * cols + (size_t)slot * hd;
   if (async_copies) {
     // all splits of this head's row in one trip to L2: hd / 4 pieces of 16 bytes per split
     const int pieces = hd >> 2;

@@ -461,9 +461,10 @@ __global__ void attention_merge_kernel(const float* part_o, const float* part_ml
                                        int splits) {
   __shared__ float wgt[32];
   pdl_trigger();
-  pdl_wait();
   const int row = blockIdx.x;                         // token * heads + head
   const size_t rows = (size_t)n_tokens * heads;
+  const int t = row / heads, h = row - t * heads;
+  pdl_wait();
   // Every thread asks for its column of the first sixteen splits before the weights are worked
   // out, so that the outputs and the (maximum, sum) pairs come back in the same trip to L2.
   constexpr int AHEAD = 16;
@@ -471,16 +472,16 @@ __global__ void attention_merge_kernel(const float* part_o, const float* part_ml
   float a[AHEAD];
 #pragma unroll
   for (int z = 0; z < AHEAD; ++z) {
-    const int zz = z < splits ? z : splits - 1;       // (past the last split: read again, not used)
+    const int zz = z < splits ? z : splits - 1;     // (past the last split: read again, not used)
     a[z] = ldcg_now(part_o + ((size_t)zz * rows + row) * hd + (d_mine < hd ? d_mine : 0));
   }
   if (threadIdx.x < 32) {
     const int z = threadIdx.x;
     float m = -INFINITY, l = 0.f;
     if (z < splits) {
-      const float2 ml = *reinterpret_cast<const float2*>(part_ml + ((size_t)z * rows + row) * 2);
-      m = ml.x;
-      l = ml.y;
+      const float* ml = part_ml + ((size_t)z * rows + row) * 2;
+      m = ldcg_now(ml);
+      l = ldcg_now(ml + 1);
     }
     const float M = warp_max(m);
     const float f = (m == -INFINITY) ? 0.f : exp2f(m - M);
@@ -488,7 +489,6 @@ __global__ void attention_merge_kernel(const float* part_o, const float* part_ml
     wgt[z] = L > 0.f ? f / L : 0.f;
   }
   __syncthreads();
-  const int t = row / heads, h = row - t * heads;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float acc = 0.f;
     int z = 0;
@@ -498,7 +498,7 @@ __global__ void attention_merge_kernel(const float* part_o, const float* part_ml
         if (u < splits) acc += wgt[u] * a[u];
       z = splits < AHEAD ? splits : AHEAD;
     }
-    for (; z < splits; ++z) acc += wgt[z] * part_o[((size_t)z * rows + row) * hd + d];
+    for (; z < splits; ++z) acc += wgt[z] * ldcg_now(part_o + ((size_t)z * rows + row) * hd + d);
     out[(size_t)t * ldo + (size_t)h * hd + d] = __float2bfloat16_rn(acc);
   }
 }

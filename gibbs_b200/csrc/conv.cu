@@ -264,17 +264,27 @@ __global__ void short_conv_decode_kernel(const T* bcx, long long ld, const float
   const int r = (int)(gid / hidden), c = (int)(gid - (long long)r * hidden);
   // Metadata, taps and the state an earlier step left are read before the wait for the kernel in
   // front; after it only this step's [B | C | x] row is missing.
-  const int t = q_start[r];
+  int t = q_start[r];
+  gb_pin(t);
   float* st = state + (size_t)slot_ids[r] * slot_stride;
   float old[KT ? KT : MAX_TAPS], tap[KT ? KT : MAX_TAPS];
 #pragma unroll
   for (int j = 0; j < K - 1; ++j) old[j] = st[(size_t)j * hidden + c];
 #pragma unroll
   for (int j = 0; j < K; ++j) tap[j] = taps[(size_t)c * K + j];
-  const float cb = bias ? bias[c] : 0.f;
-  pdl_wait();
+  float cb = bias ? bias[c] : 0.f;
   const T* row = bcx + (size_t)t * ld;
-  const float bx = to_f32(row[c]) * to_f32(row[2 * hidden + c]);
+#pragma unroll
+  for (int j = 0; j < K - 1; ++j) gb_pin(old[j]);
+#pragma unroll
+  for (int j = 0; j < K; ++j) gb_pin(tap[j]);
+  gb_pin(cb);
+  gb_pin(row);
+  gb_pin(st);
+  pdl_wait();
+  // (ldcg_now and not __ldcg, which for bfloat16 is an asm the compiler may move above the wait)
+  const float bx = to_f32(ldcg_now(row + c)) * to_f32(ldcg_now(row + 2 * hidden + c));
+  const float gate = to_f32(ldcg_now(row + hidden + c));
   float acc = 0.f;
 #pragma unroll
   for (int j = 0; j < K - 1; ++j) {
@@ -284,7 +294,7 @@ __global__ void short_conv_decode_kernel(const T* bcx, long long ld, const float
   acc = fmaf(tap[K - 1], bx, acc);
   st[(size_t)(K - 2) * hidden + c] = bx;
   if (bias) acc += cb;
-  out[(size_t)t * hidden + c] = from_f32<T>(to_f32(row[hidden + c]) * acc);
+  out[(size_t)t * hidden + c] = from_f32<T>(gate * acc);
 }
 
 // The same, reading [B | C | x] as the partial tiles of the split-K product that made it
@@ -304,7 +314,8 @@ __global__ void short_conv_decode_partials_kernel(const float* ws, int splits, l
   const int r = (int)(gid / hidden), c = (int)(gid - (long long)r * hidden);
   // Metadata, taps, biases and the state an earlier step left are read before the wait for the
   // product in front; after it only its partial tiles are missing (one trip to L2).
-  const int t = q_start[r];
+  int t = q_start[r];
+  gb_pin(t);
   const size_t ld = (size_t)3 * hidden;
   const size_t at[3] = {(size_t)t * ld + c, (size_t)t * ld + hidden + c, (size_t)t * ld + 2 * hidden + c};
   float* st = state + (size_t)slot_ids[r] * slot_stride;
@@ -313,13 +324,20 @@ __global__ void short_conv_decode_partials_kernel(const float* ws, int splits, l
   for (int j = 0; j < K - 1; ++j) old[j] = st[(size_t)j * hidden + c];
 #pragma unroll
   for (int j = 0; j < K; ++j) tap[j] = taps[(size_t)c * K + j];
-  const float cb = bias ? bias[c] : 0.f;
+  float cb = bias ? bias[c] : 0.f;
   float ib[3] = {0.f, 0.f, 0.f};
   if (in_bias) {
     ib[0] = in_bias[c];
     ib[1] = in_bias[hidden + c];
     ib[2] = in_bias[2 * hidden + c];
   }
+#pragma unroll
+  for (int j = 0; j < K - 1; ++j) gb_pin(old[j]);
+#pragma unroll
+  for (int j = 0; j < K; ++j) gb_pin(tap[j]);
+  gb_pin(cb);
+  gb_pin(ib[0]); gb_pin(ib[1]); gb_pin(ib[2]);
+  gb_pin(st);
   pdl_wait();
   float v[3];
   sum_partials<3>(ws, splits, (size_t)n_rows * ld, at, v);

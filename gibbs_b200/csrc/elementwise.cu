@@ -11,9 +11,9 @@ template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* ids, float* __restrict__ out,
                              int dim, int vocab) {
   pdl_trigger();
-  pdl_wait();
   const int row = blockIdx.x;
-  int id = ids[row];
+  pdl_wait();
+  int id = __ldcg(ids + row);                              // (through L2: the kernel in front may have rewritten it)
   // Token ids are checked on the host before the step; a bad id reads row 0.
   if (id < 0 || id >= vocab) id = 0;
   const T* src = table + (size_t)id * dim;
@@ -41,9 +41,10 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* ids, float*
         }
       }
     }
-    return;
+  } else {
+    for (int d = threadIdx.x; d < dim; d += blockDim.x)
+      dst[d] = to_f32(src[d]);
   }
-  for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = to_f32(src[d]);
 }
 
 GB_API int gb_embed(const void* table, int table_dtype, const int* ids, float* out, int n, int dim, int vocab,
@@ -119,85 +120,90 @@ __device__ __forceinline__ void rmsnorm_body(float* __restrict__ x, long long ld
   // What no kernel of the step writes (the gain, the row list from the step's metadata) is read
   // before the wait for the kernel in front: one trip to L2 less after it.
   const int r = blockIdx.x;
-  const long long sr = rows ? rows[r] : r;
+  long long sr = rows ? rows[r] : r;
+  gb_pin(sr);
   float4 g4[VEC > 0 ? VEC : 1];
   if (VEC > 0) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       const int c = threadIdx.x + i * blockDim.x;
       g4[i] = c < (dim >> 2) ? reinterpret_cast<const float4*>(gain)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+      gb_pin(g4[i]);
     }
   }
-  pdl_wait();
   float* src = x + (size_t)sr * ldx;
-  const bool write_back = pend != nullptr && rows == nullptr;
   TOut* dst = out + (size_t)r * dim;
-  float ss = 0.f;
   if constexpr (VEC > 0) {
-    float4 v[VEC > 0 ? VEC : 1];
-    const int n4 = dim >> 2;
+  pdl_wait();
+  const bool write_back = pend != nullptr && rows == nullptr;
+  float ss = 0.f;
+  float4 v[VEC > 0 ? VEC : 1];
+  const int n4 = dim >> 2;
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-      const int c = threadIdx.x + i * blockDim.x;
-      v[i] = c < n4 ? reinterpret_cast<const float4*>(src)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    if (PEND > 0 && pend) {
-      // the partial sums of up to PEND splits are requested together (one trip to L2, not one
-      // per split) and then added in split order
-      constexpr int G = PEND > 0 ? PEND : 1;
-      const size_t split_stride = (size_t)n_src_rows * dim;
-      const float* p0 = pend + (size_t)sr * dim;
-      for (int s0 = 0; s0 < splits; s0 += G) {
-        float4 a[G][VEC > 0 ? VEC : 1];
+  for (int i = 0; i < VEC; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    v[i] = c < n4 ? __ldcg(reinterpret_cast<const float4*>(src) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (PEND > 0 && pend) {
+    // the partial sums of up to PEND splits are requested together (one trip to L2, not one
+    // per split) and then added in split order
+    constexpr int G = PEND > 0 ? PEND : 1;
+    const size_t split_stride = (size_t)n_src_rows * dim;
+    const float* p0 = pend + (size_t)sr * dim;
+    for (int s0 = 0; s0 < splits; s0 += G) {
+      float4 a[G][VEC > 0 ? VEC : 1];
 #pragma unroll
-        for (int u = 0; u < G; ++u) {
-          // (a split past the last one re-reads the last one and is not added: loads without a
-          // branch around them all go out together)
-          const int su = s0 + u < splits ? s0 + u : splits - 1;
+      for (int u = 0; u < G; ++u) {
+        // (a split past the last one re-reads the last one and is not added: loads without a
+        // branch around them all go out together)
+        const int su = s0 + u < splits ? s0 + u : splits - 1;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          const int c = threadIdx.x + i * blockDim.x;
+          a[u][i] = ldcg_now(reinterpret_cast<const float4*>(p0 + (size_t)su * split_stride) + (c < n4 ? c : 0));
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < G; ++u) {
+        if (s0 + u < splits) {
 #pragma unroll
           for (int i = 0; i < VEC; ++i) {
             const int c = threadIdx.x + i * blockDim.x;
-            a[u][i] = ldcg_now(reinterpret_cast<const float4*>(p0 + (size_t)su * split_stride) + (c < n4 ? c : 0));
+            if (c < n4) { v[i].x += a[u][i].x; v[i].y += a[u][i].y; v[i].z += a[u][i].z; v[i].w += a[u][i].w; }
           }
-        }
-#pragma unroll
-        for (int u = 0; u < G; ++u) {
-          if (s0 + u < splits) {
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) {
-              const int c = threadIdx.x + i * blockDim.x;
-              if (c < n4) { v[i].x += a[u][i].x; v[i].y += a[u][i].y; v[i].z += a[u][i].z; v[i].w += a[u][i].w; }
-            }
-          }
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        const int c = threadIdx.x + i * blockDim.x;
-        if (c < n4) {
-          if (pend_bias) {
-            const float4 b = reinterpret_cast<const float4*>(pend_bias)[c];
-            v[i].x += b.x; v[i].y += b.y; v[i].z += b.z; v[i].w += b.w;
-          }
-          if (write_back) reinterpret_cast<float4*>(src)[c] = v[i];
         }
       }
     }
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
-    ss = block_sum(ss, scratch);
-    const float scale = 1.0f / sqrtf(ss / (float)dim + eps);
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       const int c = threadIdx.x + i * blockDim.x;
       if (c < n4) {
-        const float4 g = g4[i];
-        store4<TOut>(dst + 4 * c, make_float4(v[i].x * scale * g.x, v[i].y * scale * g.y, v[i].z * scale * g.z,
-                                              v[i].w * scale * g.w));
+        if (pend_bias) {
+          const float4 b = reinterpret_cast<const float4*>(pend_bias)[c];
+          v[i].x += b.x; v[i].y += b.y; v[i].z += b.z; v[i].w += b.w;
+        }
+        if (write_back) reinterpret_cast<float4*>(src)[c] = v[i];
       }
     }
+  }
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)dim + eps);
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < n4) {
+      const float4 g = g4[i];
+      store4<TOut>(dst + 4 * c, make_float4(v[i].x * scale * g.x, v[i].y * scale * g.y, v[i].z * scale * g.z,
+                                            v[i].w * scale * g.w));
+    }
+  }
     return;
   } else {
+  pdl_wait();
+  const bool write_back = pend != nullptr && rows == nullptr;
+  float ss = 0.f;
   for (int d = threadIdx.x; d < dim; d += blockDim.x) {
     float v = src[d];
     if (pend) {
@@ -234,7 +240,8 @@ __global__ void __launch_bounds__(1024) rmsnorm_splits_kernel(float* x, long lon
   __shared__ float scratch[32];
   pdl_trigger();
   const int r = blockIdx.x;
-  const long long sr = rows ? rows[r] : r;
+  long long sr = rows ? rows[r] : r;
+  gb_pin(sr);
   const int n4 = dim >> 2;
   constexpr int MAXV = 2;                                    // pieces per thread (the launch sees to it)
   float4 g4[MAXV], b4[MAXV];
@@ -243,12 +250,14 @@ __global__ void __launch_bounds__(1024) rmsnorm_splits_kernel(float* x, long lon
     const int c = threadIdx.x + i * blockDim.x;
     g4[i] = c < n4 ? reinterpret_cast<const float4*>(gain)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
     b4[i] = (pend_bias && c < n4) ? reinterpret_cast<const float4*>(pend_bias)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    gb_pin(g4[i]);
+    gb_pin(b4[i]);
   }
-  pdl_wait();
   float* src = x + (size_t)sr * ldx;
-  const bool write_back = rows == nullptr;
   const float* p0 = pend + (size_t)sr * dim;
   const size_t split_stride = (size_t)n_src_rows * dim;
+  TOut* dst = out + (size_t)r * dim;
+  pdl_wait();
 #pragma unroll
   for (int i = 0; i < MAXV; ++i) {
     const int c = threadIdx.x + i * blockDim.x;
@@ -259,7 +268,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_splits_kernel(float* x, long lon
 #pragma unroll
   for (int i = 0; i < MAXV; ++i) {
     const int c = threadIdx.x + i * blockDim.x;
-    v[i] = c < n4 ? __ldcg(reinterpret_cast<const float4*>(src) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    v[i] = c < n4 ? ldcg_now(reinterpret_cast<const float4*>(src) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   gb_cp_async_wait_all();
   float ss = 0.f;
@@ -272,13 +281,12 @@ __global__ void __launch_bounds__(1024) rmsnorm_splits_kernel(float* x, long lon
         v[i].x += a.x; v[i].y += a.y; v[i].z += a.z; v[i].w += a.w;
       }
       if (pend_bias) { v[i].x += b4[i].x; v[i].y += b4[i].y; v[i].z += b4[i].z; v[i].w += b4[i].w; }
-      if (write_back) reinterpret_cast<float4*>(src)[c] = v[i];
+      if (rows == nullptr) reinterpret_cast<float4*>(src)[c] = v[i];
     }
     ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
   }
   ss = block_sum(ss, scratch);
   const float scale = 1.0f / sqrtf(ss / (float)dim + eps);
-  TOut* dst = out + (size_t)r * dim;
 #pragma unroll
   for (int i = 0; i < MAXV; ++i) {
     const int c = threadIdx.x + i * blockDim.x;

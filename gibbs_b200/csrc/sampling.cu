@@ -42,7 +42,7 @@ __device__ __forceinline__ Cand warp_best(Cand c) {
 // f(value, id) for every element of a row, each thread taking every blockDim-th group of four
 // (or single element when the row cannot be read in 16-byte pieces).  Eight loads are requested
 // before the first is used: a thread that waits for each load in turn spends the row's sixteen
-// memory latencies one after the other.
+// memory latencies one after the other.  The loads go through L2 (a row is read once).
 template <typename F>
 __device__ __forceinline__ void for_each_logit(const float* x, int vocab, bool vec, F f) {
   const int T = blockDim.x;
@@ -51,7 +51,7 @@ __device__ __forceinline__ void for_each_logit(const float* x, int vocab, bool v
     float4 v[8];
 #pragma unroll
     for (int u = 0; u < 8; ++u)
-      if (i0 + u * T < n4) v[u] = reinterpret_cast<const float4*>(x)[i0 + u * T];
+      if (i0 + u * T < n4) v[u] = __ldcg(reinterpret_cast<const float4*>(x) + i0 + u * T);
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
       const int i = i0 + u * T;
@@ -67,7 +67,7 @@ __device__ __forceinline__ void for_each_logit(const float* x, int vocab, bool v
     float v[8];
 #pragma unroll
     for (int u = 0; u < 8; ++u)
-      if (i0 + u * T < vocab) v[u] = x[i0 + u * T];
+      if (i0 + u * T < vocab) v[u] = __ldcg(x + i0 + u * T);
 #pragma unroll
     for (int u = 0; u < 8; ++u)
       if (i0 + u * T < vocab) f(v[u], i0 + u * T);
@@ -318,16 +318,16 @@ argmax_cluster_kernel(const float* logits, long long ldv, int vocab, int* __rest
   // slices of whole 16-byte pieces
   const int per = (((vocab + ARGMAX_CLUSTER - 1) / ARGMAX_CLUSTER) + 3) & ~3;
   const int lo = min(vocab, (int)rank * per), hi = min(vocab, lo + per);
-  pdl_wait();
   const float* x = logits + (size_t)row * ldv;
-  Cand best = {0.f, -1};
   const bool vec = (ldv % 4 == 0) && (((uintptr_t)logits & 15) == 0);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  pdl_wait();
+  Cand best = {0.f, -1};
   for_each_logit(x + lo, hi - lo, vec, [&](float v, int id) {
     const Cand c = {v, lo + id};
     if (v == v && better(c, best)) best = c;
   });
   best = warp_best(best);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   if (lane == 0) warp_c[warp] = best;
   __syncthreads();
   if (warp == 0) {
