@@ -464,24 +464,33 @@ __global__ void attention_merge_kernel(const float* part_o, const float* part_ml
   const int row = blockIdx.x;                         // token * heads + head
   const size_t rows = (size_t)n_tokens * heads;
   const int t = row / heads, h = row - t * heads;
-  pdl_wait();
-  // Every thread asks for its column of the first sixteen splits before the weights are worked
-  // out, so that the outputs and the (maximum, sum) pairs come back in the same trip to L2.
+  // Addresses are worked out (and pinned, see gb_pin) before the wait for the attention kernel;
+  // behind it the first instructions are the loads.  Every thread asks for its column of the first
+  // sixteen splits before the weights are worked out, so that the outputs and the (maximum, sum)
+  // pairs come back in the same trip to L2.
   constexpr int AHEAD = 16;
   const int d_mine = threadIdx.x;
+  const float* po = part_o + (size_t)row * hd + (d_mine < hd ? d_mine : 0);
+  const float* pml = part_ml + ((size_t)(threadIdx.x < splits ? threadIdx.x : 0) * rows + row) * 2;
+  bf16* o = out + (size_t)t * ldo + (size_t)h * hd;
+  long long zstride = (long long)(rows * hd);
+  gb_pin(po);
+  gb_pin(pml);
+  gb_pin(o);
+  gb_pin(zstride);
+  pdl_wait();
   float a[AHEAD];
 #pragma unroll
   for (int z = 0; z < AHEAD; ++z) {
-    const int zz = z < splits ? z : splits - 1;     // (past the last split: read again, not used)
-    a[z] = ldcg_now(part_o + ((size_t)zz * rows + row) * hd + (d_mine < hd ? d_mine : 0));
+    const int zz = z < splits ? z : splits - 1;       // (past the last split: read again, not used)
+    a[z] = ldcg_now(po + (size_t)zz * zstride);
   }
   if (threadIdx.x < 32) {
     const int z = threadIdx.x;
-    float m = -INFINITY, l = 0.f;
-    if (z < splits) {
-      const float* ml = part_ml + ((size_t)z * rows + row) * 2;
-      m = ldcg_now(ml);
-      l = ldcg_now(ml + 1);
+    float m = ldcg_now(pml), l = ldcg_now(pml + 1);
+    if (z >= splits) {
+      m = -INFINITY;
+      l = 0.f;
     }
     const float M = warp_max(m);
     const float f = (m == -INFINITY) ? 0.f : exp2f(m - M);
@@ -499,7 +508,7 @@ __global__ void attention_merge_kernel(const float* part_o, const float* part_ml
       z = splits < AHEAD ? splits : AHEAD;
     }
     for (; z < splits; ++z) acc += wgt[z] * ldcg_now(part_o + ((size_t)z * rows + row) * hd + d);
-    out[(size_t)t * ldo + (size_t)h * hd + d] = __float2bfloat16_rn(acc);
+    o[d] = __float2bfloat16_rn(acc);
   }
 }
 

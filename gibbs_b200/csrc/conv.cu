@@ -338,6 +338,8 @@ __global__ void short_conv_decode_partials_kernel(const float* ws, int splits, l
   gb_pin(cb);
   gb_pin(ib[0]); gb_pin(ib[1]); gb_pin(ib[2]);
   gb_pin(st);
+  bf16* o = out + (size_t)t * hidden + c;
+  gb_pin(o);                                                 // (addresses too are ready before the wait)
   pdl_wait();
   float v[3];
   sum_partials<3>(ws, splits, (size_t)n_rows * ld, at, v);
@@ -357,7 +359,7 @@ __global__ void short_conv_decode_partials_kernel(const float* ws, int splits, l
   acc = fmaf(tap[K - 1], bx, acc);
   st[(size_t)(K - 2) * hidden + c] = bx;
   if (bias) acc += cb;
-  out[(size_t)t * hidden + c] = __float2bfloat16_rn(cv * acc);
+  *o = __float2bfloat16_rn(cv * acc);
 }
 
 }  // namespace

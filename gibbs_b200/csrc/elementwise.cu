@@ -255,8 +255,12 @@ __global__ void __launch_bounds__(1024) rmsnorm_splits_kernel(float* x, long lon
   }
   float* src = x + (size_t)sr * ldx;
   const float* p0 = pend + (size_t)sr * dim;
-  const size_t split_stride = (size_t)n_src_rows * dim;
+  long long split_stride = n_src_rows * dim;
   TOut* dst = out + (size_t)r * dim;
+  gb_pin(src);                                               // (addresses too are ready before the wait)
+  gb_pin(p0);
+  gb_pin(split_stride);
+  gb_pin(dst);
   pdl_wait();
 #pragma unroll
   for (int i = 0; i < MAXV; ++i) {
