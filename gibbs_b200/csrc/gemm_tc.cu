@@ -497,13 +497,31 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   if (warp == 0) {
     if (elect_one()) {
       PSTAMP(1);
+      // The weights do not depend on the kernels before this one: the weight halves of the first
+      // tile's first stages are requested at once, the token halves after the wait.
+      int ahead = 0;
+      if (pair < n_tiles) {
+        ahead = nkb < C::STAGES ? nkb : C::STAGES;
+        const int n0 = (pair / tiles_m) * 2 * BM + (int)rank * BM;
+        for (int i = 0; i < ahead; ++i) {
+          if (rank == 0) mbar_arrive_expect_tx(&full_bar[i], 2 * (W_TILE_BYTES + (BNP / 2) * BK * 2));
+          tma_load_2d_pair(tiles + (size_t)i * C::STAGE_BYTES, &tmap_w, i * BK, n0, &full_bar[i]);
+        }
+      }
+      PSTAMP(3);
       pdl_wait();
       PSTAMP(2);
+      if (pair < n_tiles) {
+        const int m0 = (pair % tiles_m) * BNP + (int)rank * (BNP / 2);
+        for (int i = 0; i < ahead; ++i)
+          tma_load_2d_pair(tiles + (size_t)i * C::STAGE_BYTES + W_TILE_BYTES, &tmap_x, i * BK, m0, &full_bar[i]);
+      }
       int it = 0;
       for (int t = pair; t < n_tiles && !abort_flag; t += n_pairs) {
         const int n0 = (t / tiles_m) * 2 * BM + (int)rank * BM;          // this CTA's weight rows
         const int m0 = (t % tiles_m) * BNP + (int)rank * (BNP / 2);      // this CTA's half of the token rows
         for (int i = 0; i < nkb; ++i, ++it) {
+          if (it < ahead) continue;                                      // (requested above)
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1;
           if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
@@ -519,7 +537,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
 #ifdef GB_PAIR_PREFETCH
           if (i + GB_PAIR_PREFETCH < nkb) tma_prefetch_2d(&tmap_w, (i + GB_PAIR_PREFETCH) * BK, n0);
 #endif
-          if (it == 0) PSTAMP(3);
         }
       }
       PSTAMP(4);
