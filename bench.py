@@ -117,10 +117,11 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--workload", choices=["serve700m", "long2p6b", "sweep"], default=None,
                     help="run one of the other reference workloads instead (prints its own JSON line)")
-    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "prefill-timeline", "trace"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "prefill-timeline", "products", "trace"], default=None,
                     help="measure one phase only (for short profiler captures; the line is then partial); "
                          "'timeline' / 'prefill-timeline': the kernels of one decode step inside its graph / of one "
-                         "prompt step, from CUPTI; 'trace': time "
+                         "prompt step, from CUPTI; 'products': the prompt step's matrix products alone (with "
+                         "-DGB_PAIR_TRACE: and the phases inside the CTA-pair kernel); 'trace': time "
                          "stamps from inside the cluster product kernels (a -DGB_DECODE_TRACE build)")
     a = ap.parse_args()
     if a.impl == "reference":
@@ -147,6 +148,9 @@ def main():
     if a.dtype != "bfloat16" and a.only not in ("prefill", "decode"):
         print("bench.py: --dtype float32 goes with --only prefill or --only decode")
         return 2
+    if a.only == "products":
+        print(B.prompt_product_times(cfg, PROMPT_LEN, peaks["bf16_tflops"]))
+        return 0
     model = random_model(cfg, SEED, dtype=a.dtype, device="cuda:0", stored_dtype=torch.bfloat16)
 
     page_size = 16

@@ -333,6 +333,76 @@ def prefill_timeline(engine: Engine, n_tokens: int, seed: int = 0) -> list:
     return rows
 
 
+def prompt_product_times(cfg, n_tokens: int, peak_tflops: float, device="cuda:0") -> str:
+    """The matrix products of one prompt step, each timed alone (twenty launches back to back, and one
+    launch after L2 was overwritten), with their share of ``peak_tflops``.  With a build that stamps
+    times inside the CTA-pair kernel (GIBBS_B200_NVCC_FLAGS=-DGB_PAIR_TRACE) the phases of the first
+    pair of one launch follow each product: microseconds after the kernel's start at which the
+    producer had set up, met its dependency and issued its last load; the MMA thread saw its first
+    full stage, had issued the first tile and all tiles, and how long it waited for a free
+    accumulator and for full stages (after the pipeline had filled); the epilogue saw the first
+    accumulator, stored the first tile, saw the last accumulator and was done, and how long it waited."""
+    import ctypes
+    from .. import ops
+    from ..ops.library import library
+    lib = library("tensorcore")
+    trace = None
+    if hasattr(lib, "gb_linear_pair_trace"):
+        lib.gb_linear_pair_trace.argtypes = [ctypes.c_void_p]
+        trace = torch.zeros(1024 * 2 * 3 * 8, dtype=torch.int64, device=device)
+    h, f = cfg.hidden_size, cfg.ffn_dim
+    qkv = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
+    shapes = [("gate_up (SwiGLU)", 2 * f, h, "swiglu"), ("down (32-bit out)", h, f, "f32"),
+              ("out_proj (32-bit out)", h, h, "f32"), ("in_proj", 3 * h, h, "bf16"), ("qkv", qkv, h, "bf16")]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    gen = torch.Generator(device=device).manual_seed(0)
+    lines = [f"{n_tokens} tokens; of {peak_tflops:.0f} TFLOP/s"]
+    for name, n, k, mode in shapes:
+        a = (torch.randn(n_tokens, k, device=device, generator=gen) * 0.5).bfloat16()
+        w = (torch.randn(n, k, device=device, generator=gen) * 0.02).bfloat16()
+        out = torch.empty(n_tokens, n // 2 if mode == "swiglu" else n,
+                          dtype=torch.float32 if mode == "f32" else torch.bfloat16, device=device)
+        run = lambda: ops.linear_tc(a, w, None, out, swiglu=(mode == "swiglu"))
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize()
+        e0, e1 = _events()
+        e0.record()
+        for _ in range(20):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        b2b = e0.elapsed_time(e1) / 20 * 1e3
+        cold = []
+        for _ in range(5):
+            flush.fill_(1)
+            torch.cuda.synchronize()
+            e0.record()
+            run()
+            e1.record()
+            torch.cuda.synchronize()
+            cold.append(e0.elapsed_time(e1) * 1e3)
+        flops = 2.0 * n_tokens * n * k
+        lines.append(f"{name:22s} N={n:6d} K={k:5d}  back to back {b2b:6.1f} us = {flops / b2b / 1e6 / peak_tflops:.3f}"
+                     f"   alone, cold L2 {statistics.median(cold):6.1f} us")
+        if trace is not None:
+            trace.zero_()
+            lib.gb_linear_pair_trace(ctypes.c_void_p(trace.data_ptr()))
+            run()
+            torch.cuda.synchronize()
+            lib.gb_linear_pair_trace(ctypes.c_void_p(0))
+            P, M, E = (trace.cpu().view(1024, 2, 3, 8)[0, 0, i].tolist() for i in range(3))
+            if P[0]:
+                us = lambda x: (x - P[0]) / 1e3 if x else -1.0
+                cyc = lambda c: c / 1.9e3                 # cycles of the SM clock -> us, roughly
+                lines.append(f"    producer: set up {us(P[1]):.1f}, dependency {us(P[2]):.1f}, last load {us(P[4]):.1f}, "
+                             f"kernel end {us(P[5]):.1f} | MMA: first stage {us(M[1]):.1f}, first tile issued {us(M[2]):.1f}, "
+                             f"all {us(M[3]):.1f} ({M[4]} tiles), waited ~{cyc(M[5]):.1f} for accumulators, "
+                             f"~{cyc(M[6]):.1f} for stages | epilogue: first accumulator {us(E[1]):.1f}, stored "
+                             f"{us(E[2]):.1f}, last accumulator {us(E[3]):.1f}, done {us(E[4]):.1f}, waited ~{cyc(E[5]):.1f}")
+    return "\n".join(lines)
+
+
 def format_timeline(rows, what: str = "decode") -> str:
     short = lambda n: n.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0]
     span = max(r[2] + r[3] for r in rows)
