@@ -352,6 +352,46 @@ argmax_cluster_kernel(const float* logits, long long ldv, int vocab, int* __rest
   }
 }
 
+// Repetition penalty (MisterTK/gibbs src/runtime/lm.rs:1074-1108 for the greedy rule, :1163-1190
+// for the sampling rule): a token that occurs c times among a row's recent tokens has its logit
+// divided by the penalty when positive, multiplied when not, c times; the greedy rule then
+// subtracts 1.5 * c, the sampling rule subtracts 1.5 after each of the c steps.  Applied in place
+// to the logits row before the pick; rows whose penalty is <= 1 are left alone.
+// recent: [rows][RECENT_MAX] token ids, -1 where a row has fewer.  One block per row, a thread
+// per recent position; the first occurrence of a token does the work for all of them.
+constexpr int RECENT_MAX = 64;
+
+__global__ void repetition_penalty_kernel(float* logits, long long ldv, int vocab, const int* recent,
+                                          const float* penalty, const float* temperature) {
+  __shared__ int toks[RECENT_MAX];
+  pdl_trigger();
+  const int row = blockIdx.x, j = threadIdx.x;
+  const int tok = recent[row * RECENT_MAX + j];
+  const float pen = penalty[row];
+  toks[j] = tok;
+  __syncthreads();
+  pdl_wait();
+  if (!(pen > 1.0f) || tok < 0 || tok >= vocab) return;
+  int count = 0;
+  bool first = true;
+  for (int i = 0; i < RECENT_MAX; ++i) {
+    if (toks[i] == tok) {
+      ++count;
+      if (i < j) first = false;
+    }
+  }
+  if (!first) return;
+  const bool greedy = temperature == nullptr || temperature[row] <= 1e-4f;
+  float* at = logits + (size_t)row * ldv + tok;
+  float v = *at;
+  for (int c = 0; c < count; ++c) {
+    v = v > 0.f ? v / pen : v * pen;
+    if (!greedy) v -= 1.5f;
+  }
+  if (greedy) v -= (float)count * 1.5f;
+  *at = v;
+}
+
 // What a row's distribution says about a picked token (MisterTK/gibbs logprob_info,
 // src/scheduler/mod.rs:272-315): the picked token's probability, the exact entropy of
 // softmax(logits) (terms below 1e-12 dropped, as there) and the k most probable tokens, by (logit
@@ -475,5 +515,17 @@ GB_API int gb_sample(const float* logits, long long ldv, int rows, int vocab, co
   }
   gb_launch(sample_kernel, dim3(rows), dim3(threads), 0, stream, logits, ldv, vocab, temperature, top_k, top_p, seed, counter, out);
   GB_CHECK_LAUNCH("gb_sample");
+  return GB_OK;
+}
+
+// logits [rows, vocab] (row stride ldv) float32, changed in place; recent [rows, 64] int32 (-1:
+// none); penalty [rows] float32; temperature [rows] float32 or null (all rows greedy).
+GB_API int gb_repetition_penalty(float* logits, long long ldv, int vocab, const int* recent, const float* penalty,
+                                 const float* temperature, int rows, cudaStream_t stream) {
+  if (rows <= 0) return GB_OK;
+  if (vocab <= 0) GB_FAIL(GB_ERR_ARG, "gb_repetition_penalty: vocabulary of %d", vocab);
+  gb_launch(repetition_penalty_kernel, dim3(rows), dim3(RECENT_MAX), 0, stream, logits, ldv, vocab, recent, penalty,
+            temperature);
+  GB_CHECK_LAUNCH("gb_repetition_penalty");
   return GB_OK;
 }

@@ -30,6 +30,8 @@ def build_parser() -> argparse.ArgumentParser:
                     help="context length (default: the model's max_position_embeddings, at most 4096)")
     ap.add_argument("--temperature", type=float, default=None, help="default 0.7 for --prompt; <= 0 is greedy")
     ap.add_argument("--top-p", type=float, default=None, help="default 0.9")
+    ap.add_argument("--repetition-penalty", type=float, default=1.0,
+                    help="> 1: tokens among the latest 64 are made less likely (default 1.0: off)")
     ap.add_argument("--top-k", type=int, default=50, help="1..64, default 50; 0: off (the sampler's 64 candidates, narrowed by --top-p only)")
     ap.add_argument("--seed", type=int, default=None, help="sampling seed; also the seed of --random")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
@@ -162,7 +164,8 @@ def main(argv=None) -> int:
         raise SystemExit("give --prompt, --prompt-ids, --probe-top5, --bench or --arch-dump")
     temperature = a.temperature if a.temperature is not None else 0.7        # src/main.rs:746-749
     params = SamplingParams(temperature=temperature, top_p=a.top_p, top_k=a.top_k,
-                            max_new_tokens=a.max_tokens if a.max_tokens is not None else 64, seed=a.seed)
+                            max_new_tokens=a.max_tokens if a.max_tokens is not None else 64, seed=a.seed,
+                            repetition_penalty=a.repetition_penalty)
     import torch
     sched = gen.scheduler()
     sid = sched.submit(prompt, params)

@@ -376,17 +376,24 @@ class Scheduler:
         # ids may stay on the device when every request of the step picks one
         # (and none only ran to fill its cache, max_new_tokens == 0)
         # and nobody asks what the distribution said about its token: that is read from the logits at once)
+        # (nor has a repetition penalty, which needs every token so far on the host)
         lag = self.overlap and len(samplers) == len(plan) and all(
-            s.params.max_new_tokens > 0 and s.params.top_logprobs is None for s in samplers)
+            s.params.max_new_tokens > 0 and s.params.top_logprobs is None and not s.params.penalizes
+            for s in samplers)
         t0 = self.clock()
         try:
             logits = self.engine.step(entries)
             args = (logits, [s.params for s in samplers], [s.seed for s in samplers],
                     [len(s.output) for s in samplers])
+            # the latest tokens of each request, for those that penalise repetition
+            # (MisterTK/gibbs src/scheduler/mod.rs:34-36, 79: the last 64 of prompt + generated)
+            extra = {"recent": [s.span(max(0, len(s.prompt) + len(s.output) - 64), len(s.prompt) + len(s.output))
+                                if s.params.penalizes else () for s in samplers]} \
+                if any(s.params.penalizes for s in samplers) else {}
             if lag:
                 pending, picked = self.sampler.sample_async(*args), []
             else:
-                pending, picked = None, (self.sampler(*args) if samplers else [])
+                pending, picked = None, (self.sampler(*args, **extra) if samplers else [])
                 infos = self._logprob_infos(logits, samplers, picked)
         except Exception as e:  # the step failed as a whole: its requests end with an error
             if isinstance(e, (OutOfPages, KeyboardInterrupt)):

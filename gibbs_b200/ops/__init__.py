@@ -783,6 +783,31 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
     return out
 
 
+RECENT_TOKENS = 64          # how many of a request's latest tokens the repetition penalty looks at
+
+
+def repetition_penalty(logits: torch.Tensor, recent: torch.Tensor, penalty: torch.Tensor,
+                       temperature: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Applies the repetition penalty to ``logits`` [rows, vocab] in place: ``recent`` [rows, 64]
+    int32 holds each row's latest token ids (-1 where there are fewer), ``penalty`` [rows] its
+    factor (<= 1: the row is left alone), ``temperature`` [rows] selects the rule (None or
+    <= 1e-4: the greedy one).  csrc/sampling.cu."""
+    _need_cuda(logits, recent, penalty, temperature)
+    lib = library("core")
+    rows, vocab = logits.shape
+    if logits.dtype != torch.float32:
+        raise KernelError("repetition_penalty: logits are float32")
+    _i32(recent, "repetition_penalty recent")
+    if recent.shape != (rows, RECENT_TOKENS) or not recent.is_contiguous():
+        raise KernelError(f"repetition_penalty: recent must be contiguous int32 [{rows}, {RECENT_TOKENS}]")
+    _f32vec(penalty, rows, "repetition_penalty penalty")
+    _f32vec(temperature, rows, "repetition_penalty temperature")
+    _launched(1)
+    check(lib, lib.gb_repetition_penalty(_ptr(logits), _c_ll(_rows(logits, "logits")), _c_int(vocab), _ptr(recent),
+                                         _ptr(penalty), _ptr(temperature), _c_int(rows), _stream()))
+    return logits
+
+
 def logprob_info(logits: torch.Tensor, chosen: torch.Tensor, k: int):
     """For each logits row: (probability of chosen[row], entropy of softmax(row), ids [rows, k] and
     probabilities [rows, k] of the k most probable tokens), all on the device."""

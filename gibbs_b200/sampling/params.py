@@ -36,10 +36,13 @@ class SamplingParams:
     seed: Optional[int] = None               # None: derived from the scheduler's seed and the request id
     stop_ids: tuple = ()                     # besides the model's own end-of-sequence ids
     top_logprobs: Optional[int] = None       # report each token's probability, the entropy and this many candidates
+    repetition_penalty: float = 1.0          # > 1: tokens among the request's latest 64 are made less likely
 
     def __post_init__(self):
         if not 0 <= self.top_k <= MAX_TOP_K:
             raise ValueError(f"top_k {self.top_k} outside 0..{MAX_TOP_K} (0: off)")
+        if not self.repetition_penalty >= 0.0:
+            raise ValueError(f"repetition_penalty {self.repetition_penalty}")
         if self.max_new_tokens < 0:
             raise ValueError(f"max_new_tokens {self.max_new_tokens}")
         if self.top_logprobs is not None and not 1 <= self.top_logprobs <= MAX_TOP_LOGPROBS:
@@ -49,6 +52,12 @@ class SamplingParams:
     def resolved_temperature(self) -> float:
         t = DEFAULT_TEMPERATURE if self.temperature is None else float(self.temperature)
         return max(t, 0.0)
+
+    @property
+    def penalizes(self) -> bool:
+        """Whether the repetition penalty does anything (MisterTK/gibbs src/runtime/lm.rs:1074: a
+        factor of 1 or less is off)."""
+        return self.repetition_penalty > 1.0
 
     @property
     def resolved_top_k(self) -> int:

@@ -53,9 +53,9 @@ class Sampler:
         self._turn = 0
 
     def sample_async(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
-                     counters: Sequence[int]) -> PendingIds:
+                     counters: Sequence[int], recent=None) -> PendingIds:
         """Pick on the device and start the copy to pinned host memory; nothing waits."""
-        out = self.sample_device(logits, params, seeds, counters)
+        out = self.sample_device(logits, params, seeds, counters, recent)
         rows = out.numel()
         if not self._pinned or self._pinned[0].numel() < rows:
             self._pinned = [torch.empty(max(rows, 64), dtype=torch.int32).pin_memory() for _ in range(4)]
@@ -67,10 +67,30 @@ class Sampler:
         return PendingIds(out, host, event)
 
     def __call__(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
-                 counters: Sequence[int]) -> list[int]:
-        """One token id per row of ``logits`` ([rows, vocab] float32 on the device)."""
-        out = self.sample_device(logits, params, seeds, counters)
+                 counters: Sequence[int], recent=None) -> list[int]:
+        """One token id per row of ``logits`` ([rows, vocab] float32 on the device).  ``recent``:
+        for each row the request's latest tokens (prompt and generated; the last 64 count), needed
+        by the rows whose parameters ask for a repetition penalty."""
+        out = self.sample_device(logits, params, seeds, counters, recent)
         return out.tolist()
+
+    def _penalized(self, logits, params, recent) -> torch.Tensor:
+        """A copy of ``logits`` with the repetition penalty of the rows that ask for one applied
+        (the caller's logits stay as the model gave them: reports about the distribution are made
+        from those)."""
+        if recent is None or len(recent) != len(params):
+            raise ValueError("a repetition penalty needs every row's recent tokens")
+        n = ops.RECENT_TOKENS
+        ids = torch.full((len(params), n), -1, dtype=torch.int32)
+        for r, (p, toks) in enumerate(zip(params, recent)):
+            if p.penalizes and len(toks):
+                last = list(toks)[-n:]
+                ids[r, :len(last)] = torch.tensor(last, dtype=torch.int32)
+        pen = torch.tensor([p.repetition_penalty if p.penalizes else 1.0 for p in params], dtype=torch.float32)
+        temp = torch.tensor([0.0 if p.greedy else p.resolved_temperature for p in params], dtype=torch.float32)
+        ids, pen, temp = (t.to(self.device, non_blocking=True) for t in (ids, pen, temp))
+        work = logits.clone()
+        return ops.repetition_penalty(work, ids, pen, temp)
 
     def logprob_info(self, logits: torch.Tensor, chosen: Sequence[int], k: int) -> list:
         """``TokenLogprobInfo`` of every row of ``logits`` for the ids in ``chosen`` (computed by
@@ -80,8 +100,10 @@ class Sampler:
         return [TokenLogprobInfo(int(c), p, tuple((i, q) for i, q in zip(ti, tp) if i >= 0), e)
                 for c, p, e, ti, tp in zip(chosen, prob, entropy, top_ids, top_probs)]
 
-    def sample_device(self, logits, params, seeds, counters) -> torch.Tensor:
+    def sample_device(self, logits, params, seeds, counters, recent=None) -> torch.Tensor:
         rows = logits.shape[0]
+        if any(p.penalizes for p in params):
+            logits = self._penalized(logits, params, recent)
         out = torch.empty(rows, dtype=torch.int32, device=self.device)
         if all(p.greedy for p in params):
             return ops.sample(logits, out)

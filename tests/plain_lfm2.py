@@ -255,6 +255,42 @@ def greedy(cfg, weights, prompt, n_new, dtype=torch.float64):
 # sampling (src/runtime/lm.rs:1062-1235)
 # ----------------------------------------------------------------------------
 
+def penalized(logits, recent, penalty, greedy):
+    """The logits after the repetition penalty (float32 arithmetic as the reference's).  A token
+    that occurs c times among ``recent`` (the latest 64 tokens count): c times v / penalty if
+    v > 0 else v * penalty; the greedy rule then subtracts 1.5 * c (src/runtime/lm.rs:1086-1101),
+    the sampling rule subtracts 1.5 after each of the c steps (src/runtime/lm.rs:1171-1190).
+    A penalty of 1 or less, or no recent tokens, changes nothing (src/runtime/lm.rs:1074, 1163)."""
+    out = np.array(logits, dtype=np.float32, copy=True)
+    recent = [int(t) for t in recent][-64:]
+    if not penalty > 1.0 or not recent:
+        return out
+    pen = np.float32(penalty)
+    for tok in sorted(set(recent)):
+        if not 0 <= tok < len(out):
+            continue
+        c = recent.count(tok)
+        v = out[tok]
+        for _ in range(c):
+            v = np.float32(v / pen) if v > 0 else np.float32(v * pen)
+            if not greedy:
+                v = np.float32(v - np.float32(1.5))
+        if greedy:
+            v = np.float32(v - np.float32(c) * np.float32(1.5))
+        out[tok] = v
+    return out
+
+
+def greedy_penalized(cfg, weights, prompt, n_new, penalty, dtype=torch.float64):
+    """Greedy continuation under a repetition penalty over the latest 64 tokens of prompt +
+    generated (src/scheduler/mod.rs:34-36, 79; src/runtime/lm.rs:1073-1108)."""
+    ids = list(prompt)
+    for _ in range(n_new):
+        logits = forward(cfg, weights, ids, dtype)[-1].to(torch.float32).numpy()
+        ids.append(int(np.argmax(penalized(logits, ids[-64:], penalty, True))))
+    return ids[len(prompt):]
+
+
 def nucleus_candidates(logits, temperature, top_k, top_p):
     """Top-k by (logit desc, id asc), softmax at the temperature over them,
     shortest prefix whose cumulative probability reaches clamp(top_p, 0.01, 1)

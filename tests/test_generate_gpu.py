@@ -35,6 +35,22 @@ def test_greedy_generation_float32_equals_plain(tmp_path, name):
         assert o == plain.greedy(cfg, w, p, 8)
 
 
+def test_greedy_generation_with_a_repetition_penalty_equals_plain(tmp_path):
+    """The penalty sees the latest 64 tokens of prompt and generated text; with a strong one the
+    continuation differs from the plain greedy one, and equals the plain rule's token by token.
+    A request without a penalty in the same batch is not touched."""
+    from gibbs_b200 import SamplingParams
+    folder = make_folder(tmp_path, "A", std=0.05)
+    cfg, w = plain.load_folder(folder)
+    prompts = [random_ids(5, 70, 512), random_ids(6, 9, 512)]
+    gen = _gen(folder, "float32")
+    pen = SamplingParams(temperature=0.0, max_new_tokens=24, repetition_penalty=1.8)
+    outs = gen.generate(prompts, [pen, SamplingParams(temperature=0.0, max_new_tokens=24)], stop_at_eos=False)
+    assert outs[0] == plain.greedy_penalized(cfg, w, prompts[0], 24, 1.8)
+    assert outs[1] == plain.greedy(cfg, w, prompts[1], 24)
+    assert outs[0] != plain.greedy(cfg, w, prompts[0], 24)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_follows_the_plain_logits(tmp_path, dtype):
     """300 tokens decoded one by one (through CUDA graphs in steady state): every

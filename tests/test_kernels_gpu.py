@@ -1138,3 +1138,34 @@ def test_argmax_over_a_cluster_of_blocks(vocab):
     ops.sample(x.to(DEV), out)
     want = [per - 1, vocab - 1, 5 * per + 1, 0, 7 * per, 0, 3 * per - 1, 2 * per + 2, int(torch.argmax(x[8]))]
     assert out.tolist() == want
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("vocab", [1000, 65536])
+def test_repetition_penalty_matches_the_plain_rule(vocab):
+    """Greedy and sampling rows, tokens that occur once, several times and not at all, positive
+    and negative logits, rows with fewer than 64 recent tokens, a row whose penalty is off and a
+    token id outside the vocabulary (ignored)."""
+    import plain_lfm2 as plain
+    from gibbs_b200 import ops
+    rng = np.random.default_rng(vocab)
+    rows = 6
+    logits = (rng.standard_normal((rows, vocab)) * 3).astype(np.float32)
+    recent = [list(rng.integers(0, vocab, 64)), [5, 5, 5, 7, 5], [], list(rng.integers(0, 20, 64)), [1, 2, 3],
+              [9, vocab + 3, 9]]
+    logits[1, 5], logits[1, 7] = 4.0, -2.0
+    penalty = np.array([1.3, 2.0, 1.5, 1.1, 1.0, 1.7], dtype=np.float32)
+    temperature = np.array([0.0, 0.8, 0.0, 1.2, 0.7, 0.0], dtype=np.float32)
+    ids = np.full((rows, 64), -1, dtype=np.int32)
+    for r, toks in enumerate(recent):
+        ids[r, :len(toks)] = toks
+    got = ops.repetition_penalty(torch.from_numpy(logits).to(DEV), torch.from_numpy(ids).to(DEV),
+                                 torch.from_numpy(penalty).to(DEV), torch.from_numpy(temperature).to(DEV)).cpu().numpy()
+    for r in range(rows):
+        want = plain.penalized(logits[r], recent[r], float(penalty[r]), temperature[r] <= 1e-4)
+        assert np.array_equal(got[r], want), r
+    assert not np.array_equal(got[0], logits[0]) and np.array_equal(got[4], logits[4]) and np.array_equal(got[2], logits[2])
+    # all rows greedy when no temperatures are given
+    got = ops.repetition_penalty(torch.from_numpy(logits).to(DEV), torch.from_numpy(ids).to(DEV),
+                                 torch.from_numpy(penalty).to(DEV)).cpu().numpy()
+    assert np.array_equal(got[1], plain.penalized(logits[1], recent[1], 2.0, True))

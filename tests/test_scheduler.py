@@ -445,3 +445,31 @@ def test_sampling_params_top_k_zero_means_off_and_bounds_are_checked():
     for bad in (-1, 65):
         with pytest.raises(ValueError):
             SamplingParams(top_k=bad)
+
+
+def test_repetition_penalty_gets_the_latest_64_tokens_and_is_not_lagged():
+    """A request with a repetition penalty hands the sampler the last 64 tokens of prompt +
+    generated text with every pick (MisterTK/gibbs src/scheduler/mod.rs:34-36, 79) and is sampled
+    with every id known on the host (no fed step); its neighbour without a penalty passes nothing."""
+    eng = FakeEngine(max_context=512, n_pages=200)
+    seen = []
+
+    class Recorder(LaggingSampler):
+        def __call__(self, logits, params, seeds, counters, recent=None):
+            seen.append((list(params), None if recent is None else [list(r) for r in recent]))
+            return argmax_sampler(logits, params, seeds, counters)
+
+    s = Scheduler(eng, Recorder(eng), max_batch_tokens=256, overlap=True)
+    prompt = list(range(1, 81))
+    pen = s.submit(prompt, SamplingParams(temperature=0.0, max_new_tokens=5, repetition_penalty=1.3))
+    off = s.submit([4, 5, 6], SamplingParams(temperature=0.0, max_new_tokens=5))
+    s.run()
+    out = s.sequences[pen].output
+    assert len(out) == 5 and len(s.sequences[off].output) == 5
+    picks = [(p, r) for p, r in seen if any(q.penalizes for q in p)]
+    assert len(picks) == 5                                    # every token of the penalised request came this way
+    for n, (params, recent) in enumerate(picks):
+        rows = [r for q, r in zip(params, recent) if q.penalizes]
+        assert rows == [(prompt + out[:n])[-64:]]
+        assert all(r == [] for q, r in zip(params, recent) if not q.penalizes)
+    assert eng.cache.check() is None and not eng.cache.live
