@@ -55,11 +55,14 @@ enum OutMode : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2, OUT_SWIGLU = 3 
 // DEEP (64-token tiles): a launch with no more CTAs than SMs (every decode product but the head)
 // has one CTA per SM anyway; it then takes most of the SM's shared memory for its pipeline, so
 // that as many weight bytes are on their way as with the narrower tiles.
+#ifndef GB_NARROW_STAGES
+#define GB_NARROW_STAGES 5
+#endif
 template <int BN, bool DEEP = false> struct Cfg {
   static constexpr int X_TILE_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES;
   static constexpr int STAGES = DEEP ? (BN >= 128 ? 6 : (BN >= 64 ? 8 : (BN >= 32 ? 9 : 10)))
-                                     : (BN >= 128 ? 3 : (BN >= 64 ? 4 : 5));
+                                     : (BN >= 128 ? 3 : (BN >= 64 ? 4 : GB_NARROW_STAGES));
   static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;   // + room to align to 1024
 };
