@@ -880,6 +880,8 @@ struct WKeyHash {
 std::mutex g_wmap_mutex;
 std::unordered_map<WKey, CUtensorMap, WKeyHash> g_wmaps;   // weights do not move: their maps are made once
 
+// (256-token tiles on this kernel, one CTA per SM with four stages, were measured for portions of
+// 256 and 512 tokens: 1.71 and 1.99 ms a step against 1.41 and 1.81 ms with two CTAs of 128 per SM.)
 int pick_bn(int M) {
   if (M <= 16) return 16;
   if (M <= 32) return 32;
