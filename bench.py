@@ -122,7 +122,7 @@ def main():
                          "'timeline' / 'prefill-timeline': the kernels of one decode step inside its graph / of one "
                          "prompt step, from CUPTI; 'products': the prompt step's matrix products alone (with "
                          "-DGB_PAIR_TRACE: and the phases inside the CTA-pair kernel); 'trace': time "
-                         "stamps from inside the cluster product kernels (a -DGB_DECODE_TRACE build)")
+                         "stamps from inside a decode step's product kernels (a -DGB_GEMM_TRACE or -DGB_DECODE_TRACE build)")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm()

@@ -99,6 +99,20 @@ __device__ __forceinline__ void store_value(const GemmParams& p, int m, int n, f
   }
 }
 
+#ifdef GB_GEMM_TRACE
+// Debug builds: %globaltimer stamps of the first CTA of every launch of gemm_tc_kernel.
+__device__ unsigned long long* g_gemm_trace = nullptr;   // [launch][3 threads][16]
+__device__ unsigned int g_gemm_trace_launch = 0;
+__device__ __forceinline__ unsigned long long gtimer_g() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define GSTAMP(row, i) do { if (gtrace) gtrace[(row) * 16 + (i)] = gtimer_g(); } while (0)
+#else
+#define GSTAMP(row, i) do {} while (0)
+#endif
+
 template <int BN, bool DEEP>
 __global__ void __launch_bounds__(192)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
@@ -118,6 +132,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   const int kb_end = min(kb_begin + p.kb_per_split, p.total_kb);
   const int nkb = kb_end - kb_begin;
   const int M = p.M, N = p.N;
+#ifdef GB_GEMM_TRACE
+  __shared__ unsigned int gtrace_slot;
+  if (threadIdx.x == 0) gtrace_slot = (blockIdx.x | blockIdx.y | blockIdx.z) == 0 ? atomicAdd(&g_gemm_trace_launch, 1u) : 0xffffffffu;
+  __syncthreads();
+  unsigned long long* gtrace = (g_gemm_trace && gtrace_slot < 4096u) ? g_gemm_trace + (size_t)gtrace_slot * 48 : nullptr;
+  if (threadIdx.x == 0 && gtrace) {
+    for (int i = 0; i < 48; ++i) gtrace[i] = 0;
+    gtrace[0] = gtimer_g();
+    gtrace[14] = gridDim.x * 1000 + gridDim.z;
+    gtrace[15] = p.mode;
+  }
+  __syncthreads();
+#endif
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -161,8 +188,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       // requested at once.  The activations are read only after those kernels have finished.
       const int head = nkb < C::STAGES ? nkb : C::STAGES;
       for (int i = 0; i < head; ++i) load_w(i, i);
+      GSTAMP(0, 1);
       pdl_wait();
+      GSTAMP(0, 2);
       for (int i = 0; i < head; ++i) load_x(i, i);
+      GSTAMP(0, 3);
       for (int i = head; i < nkb; ++i) {
         const int s = i % C::STAGES;
         const uint32_t ph = (i / C::STAGES) & 1;
@@ -175,6 +205,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         load_w(i, s);
         load_x(i, s);
       }
+      GSTAMP(0, 4);
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -189,6 +220,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
           break;
         }
         if (abort_flag) break;
+        if (i == 0) GSTAMP(1, 1);
+        if (i == C::STAGES) GSTAMP(1, 2);
         tc_fence_after();
         uint8_t* st = tiles + (size_t)s * C::STAGE_BYTES;
         const uint64_t da = smem_desc_sw128(st);
@@ -201,13 +234,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         umma_commit(&empty_bar[s]);   // frees this stage once the MMAs that read it are done
       }
       umma_commit(&tmem_full_bar);    // the accumulator is complete
+      GSTAMP(1, 3);
     }
     __syncwarp();
   } else {
     // ---- epilogue warps (threads 64..191) ----
     const int et = threadIdx.x - 64;            // 0..127
     pdl_wait();    // outputs (and the workspace) may still be read by the kernels before this one
+    if (et == 0) GSTAMP(2, 1);
     const bool ok = mbar_wait(&tmem_full_bar, 0);
+    if (et == 0) GSTAMP(2, 2);
     if (!ok) {
       abort_flag = 1;
       if (lane == 0) atomicExch(p.status, STATUS_TIMEOUT + 2);
@@ -333,20 +369,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         if (m0 + c0 >= M) break;
         float v[16];
         tmem_ld_16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, v);
+        const int jmax = min(16, M - m0 - c0);           // token columns that exist (uniform over the CTA)
         if (row >= 64) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) ubuf[row - 64][j] = v[j] + b;
+          for (int j = 0; j < 16; ++j)
+            if (j < jmax) ubuf[row - 64][j] = v[j] + b;
         }
         epilogue_barrier();
         if (row < 64) {
+          // (the fast exponential and division, as in the CTA-pair kernel's epilogue: the result is
+          // rounded to bfloat16, which hides both; a decode step waits for these few instructions)
+          bf16* o = (bf16*)p.out + (size_t)(m0 + c0) * p.ldo + (n0 >> 1) + row;
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const int m = m0 + c0 + j;
-            if (m < M)
-              ((bf16*)p.out)[(size_t)m * p.ldo + (n0 >> 1) + row] = __float2bfloat16_rn(silu_mul(v[j] + b, ubuf[row][j]));
+            if (j < jmax) {
+              const float g = v[j] + b;
+              o[(size_t)j * p.ldo] = __float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g)) * ubuf[row][j]);
+            }
           }
         }
-        epilogue_barrier();
+        if (c0 + 16 < BN && m0 + c0 + 16 < M) epilogue_barrier();   // ubuf is rewritten by the next chunk
       }
     } else if (good) {
       const float b = (p.bias != nullptr && n < N) ? p.bias[n] : 0.f;
@@ -376,6 +418,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       }
     }
   }
+  if (threadIdx.x == 64) GSTAMP(2, 3);
   tc_fence_before();
   __syncthreads();
   if (abort_flag && threadIdx.x == 0) {
@@ -384,6 +427,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   }
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+  if (threadIdx.x == 64) GSTAMP(2, 8);
 }
 
 // ---------------------------------------------------------------- CTA-pair kernel (prompts)
@@ -1260,6 +1304,16 @@ GB_API int gb_linear_pair_trace(unsigned long long* buffer) {
   unsigned int zero = 0;
   GB_CUDA(cudaMemcpyToSymbol(g_pair_trace, &buffer, sizeof(buffer)));
   GB_CUDA(cudaMemcpyToSymbol(g_pair_trace_launch, &zero, sizeof(zero)));
+  return GB_OK;
+}
+#endif
+
+#ifdef GB_GEMM_TRACE
+// Debug builds: where gemm_tc_kernel writes its stamps ([4096][3][16] 64-bit words), or null.
+GB_API int gb_linear_tc_trace(unsigned long long* buffer) {
+  unsigned int zero = 0;
+  GB_CUDA(cudaMemcpyToSymbol(g_gemm_trace, &buffer, sizeof(buffer)));
+  GB_CUDA(cudaMemcpyToSymbol(g_gemm_trace_launch, &zero, sizeof(zero)));
   return GB_OK;
 }
 #endif

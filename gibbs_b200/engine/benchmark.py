@@ -426,8 +426,11 @@ def decode_kernel_trace(engine: Engine, batch: int, prompt_len: int, seed: int =
     import ctypes
     from ..ops.library import library
     lib = library("tensorcore")
+    if hasattr(lib, "gb_linear_tc_trace"):
+        return _product_kernel_trace(engine, batch, prompt_len, seed, lib)
     if not hasattr(lib, "gb_linear_decode_trace"):
-        raise RuntimeError("build with GIBBS_B200_NVCC_FLAGS=-DGB_DECODE_TRACE to trace the cluster product")
+        raise RuntimeError("build with GIBBS_B200_NVCC_FLAGS=-DGB_GEMM_TRACE (the default products) or "
+                           "-DGB_DECODE_TRACE (the cluster products) to trace a decode step's products")
     one_step, close = _decode_stepper(engine, batch, prompt_len, seed)
     for _ in range(6):
         one_step()
@@ -456,6 +459,40 @@ def decode_kernel_trace(engine: Engine, batch: int, prompt_len: int, seed: int =
                      f"{rel(a[2, 3]):5.1f} {rel(a[2, 4]):5.1f} {rel(a[2, 5]):5.1f} | {rel(a[2, 6]):5.1f} "
                      f"{rel(a[2, 7]):5.1f} {rel(end):5.1f} | {(end - prev_end) / 1e3:5.1f}")
         prev_end = max(prev_end, end)
+    return "\n".join(lines)
+
+
+def _product_kernel_trace(engine: Engine, batch: int, prompt_len: int, seed: int, lib) -> str:
+    """Time stamps from inside ``gemm_tc_kernel`` (a -DGB_GEMM_TRACE build): for the first CTA of every
+    product of one replayed decode step, microseconds after the CTA's start."""
+    import ctypes
+    lib.gb_linear_tc_trace.argtypes = [ctypes.c_void_p]
+    one_step, close = _decode_stepper(engine, batch, prompt_len, seed)
+    for _ in range(6):
+        one_step()
+    torch.cuda.synchronize()
+    buf = torch.zeros(4096 * 48, dtype=torch.int64, device=engine.device)
+    if lib.gb_linear_tc_trace(ctypes.c_void_p(buf.data_ptr())) != 0:
+        raise RuntimeError("gb_linear_tc_trace failed")
+    one_step()
+    torch.cuda.synchronize()
+    lib.gb_linear_tc_trace(ctypes.c_void_p(0))
+    close()
+    t = buf.cpu().numpy().reshape(4096, 3, 16)
+    n = int((t[:, 0, 0] != 0).sum())
+    order = np.argsort(t[:n, 0, 0])
+    base = t[order[0], 0, 0] if n else 0
+    lines = ["tiles*1000+splits, mode (0 bf16, 1 f32, 2 residual, 3 SwiGLU) | start | producer: weights out, dependency "
+             "met, activations out, last load out | MMA thread: first stage full, the ring's first round consumed, all "
+             "issued | epilogue: dependency met, accumulator ready, stored, end | end - dependency (us)"]
+    for i in order:
+        a = t[i]
+        s0 = a[0, 0]
+        rel = lambda v: (v - s0) / 1e3 if v else -1.0
+        lines.append(f"{a[0, 14]:7d} {a[0, 15]:2d} | {(s0 - base) / 1e3:7.1f} | {rel(a[0, 1]):5.1f} {rel(a[0, 2]):5.1f} "
+                     f"{rel(a[0, 3]):5.1f} {rel(a[0, 4]):5.1f} | {rel(a[1, 1]):5.1f} {rel(a[1, 2]):5.1f} {rel(a[1, 3]):5.1f} | "
+                     f"{rel(a[2, 1]):5.1f} {rel(a[2, 2]):5.1f} {rel(a[2, 3]):5.1f} {rel(a[2, 8]):5.1f} | "
+                     f"{(a[2, 8] - a[0, 2]) / 1e3:5.1f}")
     return "\n".join(lines)
 
 
