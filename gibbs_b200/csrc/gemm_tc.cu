@@ -255,19 +255,50 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     const int row = 32 * q + lane;               // lane of the accumulator = weight row within the tile
     const int n = n0 + row;
     const bool split = p.splits > 1;
-    if (good && split) {
-      // partial tile -> workspace
+    if (good && split && BN >= 32 && n0 + BM <= N && (N & 3) == 0 && (((uintptr_t)p.ws) & 15) == 0) {
+      // partial tile -> workspace, 64 token rows at a time through shared memory (the pipeline's
+      // stages are free once the accumulator is complete): a warp then stores 512 contiguous bytes
+      // of one token's row per instruction.  (Stores of 128 bytes each, 8 KB apart, as the lanes
+      // hold them, took 2.7 us for a 64-token tile.)
+      float* fb = reinterpret_cast<float*>(tiles);                                     // [64][128]
+      const int cols = min(BN, M - m0);
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        if (m0 + c0 >= M) break;
-        float v[16];
-        tmem_ld_16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, v);
-        if (n < N) {
+      for (int h0 = 0; h0 < cols; h0 += 64) {
+        const int hc = min(64, cols - h0);
+#pragma unroll 1
+        for (int c0 = 0; c0 < hc; c0 += 32) {
+          float v[32];
+          tmem_ld_32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(h0 + c0), v);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = m0 + c0 + j;
-            if (m < M) p.ws[((size_t)blockIdx.z * M + m) * (size_t)N + n] = v[j];
-          }
+          for (int j = 0; j < 32; ++j)
+            if (c0 + j < hc) fb[(c0 + j) * BM + row] = v[j];
+        }
+        epilogue_barrier();
+        float* dst = p.ws + ((size_t)blockIdx.z * M + m0 + h0) * (size_t)N + n0;
+        for (int idx = et; idx < hc * 32; idx += 128) {         // 32 pieces of 4 floats per row
+          const int mm = idx >> 5, piece = idx & 31;
+          *reinterpret_cast<float4*>(dst + (size_t)mm * N + piece * 4) =
+              *reinterpret_cast<const float4*>(fb + mm * BM + piece * 4);
+        }
+        if (h0 + 64 < cols) epilogue_barrier();
+      }
+    } else if (good && split) {
+      // partial tile -> workspace (a lane is a weight row: a warp's store is 128 contiguous bytes
+      // of one token's row).  32 columns per tensor-memory load where the tile has them: the wait
+      // for a load is paid once per 32 stores, not once per 16.
+      float* wsp = p.ws + ((size_t)blockIdx.z * M + m0) * (size_t)N + n;
+      constexpr int CH = BN >= 32 ? 32 : 16;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += CH) {
+        if (m0 + c0 >= M) break;
+        float v[CH];
+        if (CH == 32) tmem_ld_32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, v);
+        else tmem_ld_16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, v);
+        if (n < N) {
+          const int jmax = min(CH, M - m0 - c0);
+#pragma unroll
+          for (int j = 0; j < CH; ++j)
+            if (j < jmax) wsp[(size_t)(c0 + j) * N] = v[j];
         }
       }
     } else if (good && BN >= 32 && p.vec_store && n0 + BM <= N) {
@@ -277,34 +308,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       const float b = p.bias ? p.bias[n] : 0.f;
       const int cols = min(BN, M - m0);                      // token rows of this tile
       if (p.mode == OUT_SWIGLU) {
-        float* ub = reinterpret_cast<float*>(tiles);                                   // [BN][64] u + bias
-        bf16* ob = reinterpret_cast<bf16*>(tiles + (size_t)BN * 64 * sizeof(float));   // [BN][64] result
+        // g (accumulator rows 0-63) and u (rows 64-127) go to shared memory in 32-bit; then all
+        // 128 threads share the activations, four features of one token at a time, with the fast
+        // exponential and division (the result is rounded to bfloat16, which hides both) and
+        // store 8 bytes each: sixteen threads write the 128 bytes of a token's 64 features.
+        float* gs = reinterpret_cast<float*>(tiles);                                   // [BN][64] g + bias
+        float* us = gs + BN * 64;                                                      // [BN][64] u + bias
+        float* mine = row < 64 ? gs + row : us + (row - 64);
+        constexpr int CH = BN >= 32 ? 32 : 16;
 #pragma unroll 1
-        for (int c0 = 0; c0 < cols; c0 += 16) {
-          float v[16];
-          tmem_ld_16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, v);
-          if (row >= 64) {
+        for (int c0 = 0; c0 < cols; c0 += CH) {
+          float v[CH];
+          if (CH == 32) tmem_ld_32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, v);
+          else tmem_ld_16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, v);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) ub[(c0 + j) * 64 + (row - 64)] = v[j] + b;
-          }
-        }
-        epilogue_barrier();
-        if (row < 64) {
-#pragma unroll 1
-          for (int c0 = 0; c0 < cols; c0 += 16) {
-            float v[16];
-            tmem_ld_16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, v);
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              ob[(c0 + j) * 64 + row] = __float2bfloat16_rn(silu_mul(v[j] + b, ub[(c0 + j) * 64 + row]));
-          }
+          for (int j = 0; j < CH; ++j)
+            if (c0 + j < cols) mine[(c0 + j) * 64] = v[j] + b;
         }
         epilogue_barrier();
         bf16* dst = (bf16*)p.out + (size_t)m0 * p.ldo + (n0 >> 1);
-        for (int idx = et; idx < cols * 8; idx += 128) {        // 8 pieces of 8 bf16 per row
-          const int mm = idx >> 3, piece = idx & 7;
-          *reinterpret_cast<uint4*>(dst + (size_t)mm * p.ldo + piece * 8) =
-              *reinterpret_cast<const uint4*>(ob + mm * 64 + piece * 8);
+        for (int idx = et; idx < cols * 16; idx += 128) {
+          const int mm = idx >> 4, f = (idx & 15) * 4;
+          const float4 g4 = *reinterpret_cast<const float4*>(gs + mm * 64 + f);
+          const float4 u4 = *reinterpret_cast<const float4*>(us + mm * 64 + f);
+          const float r0 = __fdividef(g4.x, 1.0f + __expf(-g4.x)) * u4.x;
+          const float r1 = __fdividef(g4.y, 1.0f + __expf(-g4.y)) * u4.y;
+          const float r2 = __fdividef(g4.z, 1.0f + __expf(-g4.z)) * u4.z;
+          const float r3 = __fdividef(g4.w, 1.0f + __expf(-g4.w)) * u4.w;
+          __nv_bfloat162 lo = __floats2bfloat162_rn(r0, r1), hi = __floats2bfloat162_rn(r2, r3);
+          uint2 packed;
+          packed.x = *reinterpret_cast<uint32_t*>(&lo);
+          packed.y = *reinterpret_cast<uint32_t*>(&hi);
+          *reinterpret_cast<uint2*>(dst + (size_t)mm * p.ldo + f) = packed;
         }
       } else if (p.mode == OUT_BF16) {
         bf16* ob = reinterpret_cast<bf16*>(tiles);                                     // [BN][128]
