@@ -95,20 +95,6 @@ template <int HD> struct Tile {
 // waits on memory, so they keep one more tile on the way.
 template <bool KSPLIT> struct Depth { static constexpr int STAGES = KSPLIT ? 3 : 2; };
 
-#ifdef GB_ATTN_TRACE
-// Debug builds: %globaltimer stamps of one CTA (the last split of the first request and head) per launch.
-__device__ unsigned long long* g_attn_trace = nullptr;   // [launch][16]
-__device__ unsigned int g_attn_trace_launch = 0;
-__device__ __forceinline__ unsigned long long gtimer_a() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define ASTAMP(i) do { if (atrace) atrace[i] = gtimer_a(); } while (0)
-#else
-#define ASTAMP(i) do {} while (0)
-#endif
-
 // KSPLIT = false: NW warps, 16 query rows each, every warp walks all 64 keys of a tile.
 // KSPLIT = true (decoding): ONE 16-row query tile shared by the NW = 4 warps; warp w takes keys
 // 16w .. 16w+15 of every tile with its own running maximum, sum and output, and the four
@@ -118,15 +104,6 @@ template <int HD, int NW, bool KSPLIT>
 __global__ void __launch_bounds__(32 * NW)
 attention_tc_kernel(const AttnParams p) {
   pdl_trigger();
-#ifdef GB_ATTN_TRACE
-  __shared__ unsigned int atrace_slot;
-  const bool traced = KSPLIT && blockIdx.x == 0 && blockIdx.y == gridDim.y - 1 && blockIdx.z == 0;
-  if (threadIdx.x == 0) atrace_slot = traced ? atomicAdd(&g_attn_trace_launch, 1u) : 0xffffffffu;
-  __syncthreads();
-  unsigned long long* atrace = (g_attn_trace && atrace_slot < 4096u && threadIdx.x == 0) ? g_attn_trace + (size_t)atrace_slot * 16 : nullptr;
-  if (atrace) { for (int i = 0; i < 16; ++i) atrace[i] = 0; atrace[14] = gridDim.y * 100 + gridDim.z; }
-  ASTAMP(0);
-#endif
   // The wait for the kernel in front (which wrote this step's q, k and v) comes further down: the
   // step's metadata, the page ids and the key tiles that earlier steps filled are fetched first.
   // (Asking L2 for the tiles behind those as well changed nothing: measured, not kept.)
@@ -230,7 +207,6 @@ attention_tc_kernel(const AttnParams p) {
   for (int i = 0; i < NS; ++i)
     if (t_begin + i < t_end) locate(t_begin + i);
   __syncthreads();
-  ASTAMP(1);                               // pages located
   bool waited = false;                     // (the same in every thread of the CTA)
   for (int i = 0; i < NS - 1; ++i) {       // one commit group per tile, also for tiles that do not exist
     if (t_begin + i < t_end) {
@@ -242,12 +218,7 @@ attention_tc_kernel(const AttnParams p) {
     }
     cp_async_commit();
   }
-  ASTAMP(2);                               // first key tiles requested
   if (!waited) pdl_wait();
-  ASTAMP(3);                               // dependency met
-#ifdef GB_ATTN_TRACE
-  if (atrace) atrace[15] = (unsigned long long)(t_end - t_begin);
-#endif
   // Q tile: row = token_local * group + g.  Plain loads (the key tiles above are on their way
   // meanwhile); the barrier at the head of the first iteration makes the tile visible.
   for (int idx = tid; idx < BQ * CHUNKS; idx += NT) {
@@ -285,9 +256,6 @@ attention_tc_kernel(const AttnParams p) {
   for (int t = t_begin; t < t_end; ++t) {
     const int buf = (t - t_begin) % NS;
     cp_async_wait<NS - 2>();               // all but the NS-2 newest groups: tile t (and Q) have landed
-#ifdef GB_ATTN_TRACE
-    if (atrace && t - t_begin < 6) atrace[4 + (t - t_begin)] = gtimer_a();   // tile t has landed
-#endif
     // The one barrier of an iteration: tile t is visible to every warp, every warp has left tile t - 1
     // (whose buffer the next loads overwrite), and the offsets written a tile ago are visible.
     __syncthreads();
@@ -402,7 +370,6 @@ attention_tc_kernel(const AttnParams p) {
     locate_end();
   }
   cp_async_wait<0>();
-  ASTAMP(10);                              // all tiles done
 
   // row sums across the four threads of a row
 #pragma unroll
@@ -459,7 +426,6 @@ attention_tc_kernel(const AttnParams p) {
         }
       }
     }
-    ASTAMP(11);                            // stored
     return;
   } else {
 #pragma unroll
@@ -640,12 +606,3 @@ GB_API int gb_attention_tc(const void* q, long long ldq, const void* k_pages, co
   return 1;
 }
 
-#ifdef GB_ATTN_TRACE
-// Debug builds: where the decode attention kernel writes its stamps ([4096][16] 64-bit words), or null.
-GB_API int gb_attention_tc_trace(unsigned long long* buffer) {
-  unsigned int zero = 0;
-  GB_CUDA(cudaMemcpyToSymbol(g_attn_trace, &buffer, sizeof(buffer)));
-  GB_CUDA(cudaMemcpyToSymbol(g_attn_trace_launch, &zero, sizeof(zero)));
-  return GB_OK;
-}
-#endif
