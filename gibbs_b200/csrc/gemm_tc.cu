@@ -55,14 +55,17 @@ enum OutMode : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2, OUT_SWIGLU = 3 
 // DEEP (64-token tiles): a launch with no more CTAs than SMs (every decode product but the head)
 // has one CTA per SM anyway; it then takes most of the SM's shared memory for its pipeline, so
 // that as many weight bytes are on their way as with the narrower tiles.
+// Stages of the 16-token tiles (decode batches up to 16): six of 18 KB are the most that leave room
+// for two CTAs per SM (the product after this one then fills its ring while this one streams);
+// five measured 2.5 % slower a step, seven (one CTA per SM) slower still.
 #ifndef GB_NARROW_STAGES
-#define GB_NARROW_STAGES 5
+#define GB_NARROW_STAGES 6
 #endif
 template <int BN, bool DEEP = false> struct Cfg {
   static constexpr int X_TILE_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES;
   static constexpr int STAGES = DEEP ? (BN >= 128 ? 6 : (BN >= 64 ? 8 : (BN >= 32 ? 9 : 10)))
-                                     : (BN >= 128 ? 3 : (BN >= 64 ? 4 : GB_NARROW_STAGES));
+                                     : (BN >= 128 ? 3 : (BN >= 64 ? 4 : (BN >= 32 ? 5 : GB_NARROW_STAGES)));
   static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;   // + room to align to 1024
 };
@@ -123,7 +126,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   __shared__ uint64_t full_bar[C::STAGES], empty_bar[C::STAGES], tmem_full_bar;
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int abort_flag;
-  __shared__ float ubuf[64][17];                 // SwiGLU: u of one 16-column chunk, padded against bank conflicts
 
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -398,6 +400,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         }
       }
     } else if (good && p.mode == OUT_SWIGLU) {
+      // u of one 16-column chunk, padded against bank conflicts, in the pipeline's first stage
+      // (free once the accumulator is complete; static shared memory would cost the second CTA
+      // of an SM its place)
+      float (*ubuf)[17] = reinterpret_cast<float (*)[17]>(tiles);
       const float b = (p.bias && n < N) ? p.bias[n] : 0.f;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
