@@ -57,7 +57,8 @@ enum OutMode : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2, OUT_SWIGLU = 3 
 // that as many weight bytes are on their way as with the narrower tiles.
 // Stages of the 16-token tiles (decode batches up to 16): six of 18 KB are the most that leave room
 // for two CTAs per SM (the product after this one then fills its ring while this one streams);
-// five measured 2.5 % slower a step, seven (one CTA per SM) slower still.
+// five measured 2.5 % slower a step; more would leave room for one CTA per SM only (ten stages
+// that way were measured slower).
 #ifndef GB_NARROW_STAGES
 #define GB_NARROW_STAGES 6
 #endif
