@@ -503,10 +503,6 @@ __device__ __forceinline__ unsigned long long gtimer() {
 #define PWAIT_END(i) do {} while (0)
 #endif
 
-#ifndef GB_PAIR_DIRECT_F32
-#define GB_PAIR_DIRECT_F32 1
-#endif
-
 struct PairCfg {
   static constexpr int BNP_MAX = 256;                     // most tokens per tile (GemmParams::bnp: 128..256 in steps of 16)
   static constexpr int X_TILE_BYTES = (BNP_MAX / 2) * BK * 2; // room for this CTA's half of the token rows
@@ -623,9 +619,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           if (rank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * (W_TILE_BYTES + (BNP / 2) * BK * 2));
           tma_load_2d_pair(st, &tmap_w, i * BK, n0, &full_bar[s]);
           tma_load_2d_pair(st + W_TILE_BYTES, &tmap_x, i * BK, m0, &full_bar[s]);
-#ifdef GB_PAIR_PREFETCH
-          if (i + GB_PAIR_PREFETCH < nkb) tma_prefetch_2d(&tmap_w, (i + GB_PAIR_PREFETCH) * BK, n0);
-#endif
         }
       }
       PSTAMP(4);
@@ -767,7 +760,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 *reinterpret_cast<const uint4*>(ob + mm * BM + piece * 8);
           }
           epilogue_barrier();
-        } else if (hc > 0 && fast && p.mode == OUT_F32 && GB_PAIR_DIRECT_F32) {
+        } else if (hc > 0 && fast && p.mode == OUT_F32) {
           // A plain 32-bit store needs no staging: a lane is a weight row, so one store of a warp
           // is 128 contiguous bytes of one token's row, a whole line.
           float* dst = (float*)p.out + (size_t)(m0 + h0) * p.ldo + n;
