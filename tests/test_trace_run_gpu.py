@@ -16,11 +16,12 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def _run(folder, dtype, steps, out, max_tokens):
+def _run(folder, dtype, steps, out, max_tokens, env=None):
     proc = subprocess.run(
         [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out),
          "--max-tokens", str(max_tokens)],
-        input="".join(json.dumps(s) + "\n" for s in steps), text=True, capture_output=True, timeout=600)
+        input="".join(json.dumps(s) + "\n" for s in steps), text=True, capture_output=True, timeout=600,
+        env=None if env is None else {**os.environ, **env})
     assert proc.returncode == 0, proc.stderr[-2000:]
     done = [l for l in proc.stdout.splitlines() if l.startswith("done ")]
     assert done == [f"done {s['step']}" for s in steps]
@@ -67,6 +68,33 @@ def test_trace_run_mixed_and_sparse_wants(tmp_path, dtype, name):
         rows = sorted(got[rid])
         bad = first_wrong(np.stack([got[rid][p] for p in rows]), want[rows], TOL[dtype])
         assert bad is None, f"{rid}: first wrong wanted place {rows[bad[0]]} (rel err {bad[1]:.3g})"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_without_programmatic_dependent_launch(tmp_path, dtype):
+    """The kernels read what they can before their dependency wait (metadata, weights, cache and state
+    of earlier steps) so that a step's kernels overlap; with GIBBS_B200_PDL=0 every kernel starts
+    after the one in front has ended.  Both ways must give the plain implementation's logits: a
+    difference between them would be a read that was moved in front of the wait by mistake."""
+    stored = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+    folder = make_folder(tmp_path, "C", stored=stored)
+    vocab = TINY["C"][0]["vocab_size"]
+    reqs = {f"q{i}": random_ids(60 + i, n, vocab) for i, n in enumerate([90, 33, 150, 64])}
+    steps = trace_mixed(reqs, capacity_tokens=320, max_live=4, seed=4)
+    want = {rid: plain_logits(folder, ids) for rid, ids in reqs.items()}
+    results = {}
+    for mode, env in (("serial", {"GIBBS_B200_PDL": "0"}), ("overlapped", {"GIBBS_B200_PDL": "1"})):
+        out = tmp_path / f"out_{mode}"
+        _run(folder, dtype, steps, out, max_tokens=320, env=env)
+        got = results[mode] = _collect(steps, out, vocab)
+        for rid in reqs:
+            rows = sorted(got[rid])
+            bad = first_wrong(np.stack([got[rid][p] for p in rows]), want[rid][rows], TOL[dtype])
+            assert bad is None, f"{mode}, {rid}: first wrong place {rows[bad[0]]} (rel err {bad[1]:.3g})"
+    # the same kernels add in the same order either way: the two runs agree to the bit
+    for rid in reqs:
+        for p in sorted(results["serial"][rid]):
+            assert np.array_equal(results["serial"][rid][p], results["overlapped"][rid][p]), (rid, p)
 
 
 def test_trace_run_fresh_env(tmp_path):
