@@ -5,18 +5,19 @@
 //
 // A CTA takes one (request, tile of tokens, kv head).  Its 128 rows are (token, query head of the
 // kv head's group) pairs, 128 / group tokens, so the keys and values are read once for all the
-// heads that share them.  It walks the visible keys in tiles of 128:
+// heads that share them.  It walks the visible keys in tiles of KEYS = 128 (or 64):
 //
 //   producer warp   TMA: Q once; then K_j, V_j, K_j+1, ... through a ring of three buffers
-//   MMA warp        S = Q K_j^T (tensor memory columns 0..127); when the softmax warps have
-//                   written P_j: O += P_j V_j (columns 128..)
+//   MMA warp        S = Q K_j^T (tensor memory columns 0..KEYS-1); when the softmax warps have
+//                   written P_j: O += P_j V_j (columns KEYS..)
 //   softmax warps   thread = row: read S, scale, mask, running maximum m and sum l in 32-bit,
 //                   P = exp2(S - m) as bfloat16 into shared memory (the A operand of the second
 //                   product); when the maximum has grown by more than 8 (a factor of 256) the
 //                   row's O in tensor memory and l are rescaled first; at the end O / l is stored
 //
 // Two CTAs fit on an SM (97 KB of shared memory and 256 tensor-memory columns each at head_dim
-// 64): while one is in its softmax the other's products run.
+// 64, and at head_dim 128 with 64-key tiles): while one is in its softmax the other's products
+// run.  The softmax warps meet at no barrier: each waits for the products itself.
 //
 // V lies in shared memory as [key][head_dim]: for O = P V it is the B operand with its N index
 // contiguous ("MN-major"), which tcgen05 reads directly; nothing is transposed.
@@ -37,7 +38,6 @@ namespace {
 using namespace sm100;
 
 constexpr int ROWS = 128;            // rows of a CTA's tile: tokens x heads of the group
-constexpr int KEYS = 128;            // keys per tile
 constexpr int RING = 3;              // buffers of one K or V tile each
 constexpr int STATUS_ATTN_TIMEOUT = 24;
 
@@ -50,32 +50,73 @@ struct Params {
   int* status;
 };
 
-template <int HD> struct Cfg {
+// KEYS: keys per tile, 64 or 128.
+template <int HD, int KEYS> struct Cfg {
   static constexpr int SUB = HD / 64;                          // 64-column sub-tiles of a K, V or Q tile
   static constexpr int Q_BYTES = ROWS * HD * 2;
   static constexpr int KV_BYTES = KEYS * HD * 2;
   static constexpr int P_BYTES = ROWS * KEYS * 2;
   static constexpr int SMEM_BYTES = Q_BYTES + P_BYTES + RING * KV_BYTES + 1024;
-  static constexpr int TMEM_COLS = 256;                        // S: 128 columns, O: HD columns
+  static constexpr int TMEM_COLS = KEYS + HD <= 128 ? 128 : 256;   // S: KEYS columns, O: HD columns
+  // CTAs per SM: by tensor memory (512 columns), shared memory and registers (64 K for 192 threads each).
+  // (Three CTAs of 64-key tiles at head_dim 64 were measured: not faster than two.)
+  static constexpr int CTAS = SMEM_BYTES <= 113 * 1024 ? 2 : 1;
+  static constexpr int REGS = CTAS == 2 ? 168 : 255;
 };
 
-__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+// Two 32-bit floats in one 64-bit register: fma / add / sub.f32x2 do two operations in one issue slot.
+__device__ __forceinline__ uint64_t pk2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void upk2(uint64_t r, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(r)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// P = exp2(v * scale + neg_m) for one row of a tile, as bfloat16 pairs; returns the row's sum.
+template <int KEYS>
+__device__ __forceinline__ float exp_row(const float (&v)[KEYS], float scale, float neg_m, uint32_t (&packed)[KEYS / 2]) {
+  const uint64_t scale2 = pk2(scale, scale), negm2 = pk2(neg_m, neg_m);
+  uint64_t ls2[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+  for (int i = 0; i < KEYS; i += 2) {
+    const int q = i >> 1;
+    float x0, x1, e0, e1;
+    upk2(fma2(pk2(v[i], v[i + 1]), scale2, negm2), x0, x1);
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(x0));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(x1));
+    ls2[q & 3] = add2(ls2[q & 3], pk2(e0, e1));
+    __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
+    packed[q] = *reinterpret_cast<uint32_t*>(&b2);
+  }
+  float a0, a1, b0, b1;
+  upk2(add2(ls2[0], ls2[1]), a0, a1);
+  upk2(add2(ls2[2], ls2[3]), b0, b1);
+  return (a0 + a1) + (b0 + b1);
+}
 
-template <int HD>
-__global__ void __launch_bounds__(192, 2)
+template <int HD, int KEYS>
+__global__ void __launch_bounds__(192) __maxnreg__((Cfg<HD, KEYS>::REGS))
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const Params p) {
   pdl_trigger();
-  using C = Cfg<HD>;
+  using C = Cfg<HD, KEYS>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t q_full, kv_full[RING], kv_empty[RING], s_full, s_free, p_full, o_full;
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int abort_flag;
-  __shared__ volatile int alive_vote;
 
   uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sq = base;                                          // [SUB][128 rows][128 B]
-  uint8_t* sp = sq + C::Q_BYTES;                               // [2][128 rows][128 B]: keys 0..63, 64..127
+  uint8_t* sp = sq + C::Q_BYTES;                               // [KEYS / 64][128 rows][128 B]: keys 0..63, 64..127
   uint8_t* skv = sp + C::P_BYTES;                              // [RING][SUB][128 keys][128 B]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int group = p.heads / p.kv_heads;
@@ -138,7 +179,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_s = tmem_slot, tmem_o = tmem_slot + 128;
+  const uint32_t tmem_s = tmem_slot, tmem_o = tmem_slot + KEYS;
 
   if (warp == 0) {
     // ---- producer ----
@@ -240,7 +281,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           tc_fence_after();
           const uint8_t* vt = skv + (size_t)s * C::KV_BYTES;
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {               // keys 0..63 and 64..127 of the tile
+          for (int half = 0; half < KEYS / 64; ++half) {       // keys 0..63 (and 64..127) of the tile
             const uint64_t da = smem_desc_sw128(sp + (size_t)half * ROWS * 128);
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
@@ -271,21 +312,19 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int rpos = pos0 + tl;
     const uint32_t lane_off = (uint32_t)(32 * q4) << 16;
     float m_used = -INFINITY, l_run = 0.f;
+    // A wait that runs out ends this warp's loop (one answer for the whole warp); the other warps
+    // see abort_flag at their next tile, or their own waits run out, since this warp no longer arrives.
     bool alive = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int t = t_lo + j;
-      if (!mbar_wait(&s_full, j & 1)) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full, j & 1) && !abort_flag)) {
         abort_flag = 1;
         if (lane == 0) atomicExch(p.status, STATUS_ATTN_TIMEOUT + 2);
+        alive = false;
+        break;
       }
       tc_fence_after();
-      // the whole row of S into registers: four loads on their way together, one wait
-      float v[KEYS];
-      tmem_ld_32_issue(tmem_s + lane_off + 0u, v);
-      tmem_ld_32_issue(tmem_s + lane_off + 32u, v + 32);
-      tmem_ld_32_issue(tmem_s + lane_off + 64u, v + 64);
-      tmem_ld_32_issue(tmem_s + lane_off + 96u, v + 96);
-      // Which of the tile's 128 columns this row may see: lo_c <= column <= hi_c.  Most tiles lie
+      // Which of the tile's columns this row may see: lo_c <= column <= hi_c.  Most tiles lie
       // wholly below the diagonal (and inside the window) for every row: they need no mask.
       const int col0 = t * KEYS;
       const int hi_c = rvalid ? rpos - col0 : -1;
@@ -293,7 +332,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       const bool full = col0 + KEYS - 1 <= pos0 && (p.window <= 0 || col0 + p.window > pos0 + tpt - 1);
       const unsigned span = hi_c >= lo_c ? (unsigned)(hi_c - lo_c) : 0u;
       const bool none = hi_c < lo_c;                           // (then `span` is not used)
-      tmem_ld_wait_128(v);
+      // the whole row of S into registers: the loads on their way together, one wait
+      float v[KEYS];
+#pragma unroll
+      for (int c = 0; c < KEYS; c += 32) tmem_ld_32_issue(tmem_s + lane_off + (uint32_t)c, v + c);
+      tmem_ld_wait_n<KEYS>(v);
       // the row is in registers: the next tile's first product may overwrite S
       tc_fence_before();
       __syncwarp();
@@ -319,31 +362,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         m_used = m_tile;
         l_run *= corr;
       }
-      // P = exp2(S * scale - m); a masked column holds -inf and gives exactly 0
-      const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+      // P = exp2(S * scale - m); a masked column holds -inf and gives exactly 0 (so does every column
+      // of a row that has seen nothing yet: -inf * scale + 0 = -inf)
       uint32_t packed[KEYS / 2];
-#pragma unroll
-      for (int i = 0; i < KEYS; i += 2) {
-        float e0, e1;
-        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(fmaf(v[i], p.scale_log2, neg_m)));
-        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(fmaf(v[i + 1], p.scale_log2, neg_m)));
-        if (m_used == -INFINITY) e0 = e1 = 0.f;                // a row that has seen nothing yet sees nothing here
-        ls[(i >> 1) & 3] += e0 + e1;
-        __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
-        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&b2);
-      }
-      l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+      l_run += exp_row<KEYS>(v, p.scale_log2, (m_used == -INFINITY) ? 0.f : -m_used, packed);
       // P and O of the tile before are still being read by its second product until o_full
-      if (j > 0 && !mbar_wait(&o_full, (j - 1) & 1)) {
+      if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(&o_full, (j - 1) & 1))) {
         abort_flag = 1;
         if (lane == 0) atomicExch(p.status, STATUS_ATTN_TIMEOUT + 3);
+        alive = false;
+        break;
       }
-      if (threadIdx.x == 64) alive_vote = abort_flag ? 0 : 1;  // one answer for all: the group never splits at a barrier
-      softmax_bar();
-      alive = alive_vote != 0;
-      softmax_bar();
-      if (!alive) break;
       tc_fence_after();
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
@@ -357,7 +386,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       }
       // 8 keys (16 bytes) at a time into the swizzled tile
 #pragma unroll
-      for (int chunk = 0; chunk < 16; ++chunk) {
+      for (int chunk = 0; chunk < KEYS / 8; ++chunk) {
         uint8_t* dst = sp + (size_t)(chunk >> 3) * ROWS * 128 + (size_t)row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
         *reinterpret_cast<uint4*>(dst) =
             make_uint4(packed[4 * chunk], packed[4 * chunk + 1], packed[4 * chunk + 2], packed[4 * chunk + 3]);
@@ -368,14 +397,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       if (lane == 0) mbar_arrive(&p_full);
     }
     if (alive && n_tiles > 0) {
-      if (!mbar_wait(&o_full, (n_tiles - 1) & 1)) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&o_full, (n_tiles - 1) & 1))) {
         abort_flag = 1;
         if (lane == 0) atomicExch(p.status, STATUS_ATTN_TIMEOUT + 4);
+        alive = false;
       }
     }
-    if (threadIdx.x == 64) alive_vote = abort_flag ? 0 : 1;
-    softmax_bar();
-    alive = alive && alive_vote != 0;
     tc_fence_after();
     if (alive) {
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
@@ -469,18 +496,33 @@ bool pages_map(CUtensorMap* out, const void* pages, long long rows, int hd, int 
   return true;
 }
 
-template <int HD>
+template <int HD, int KEYS>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, int n_tiles,
            cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
-    GB_CUDA(cudaFuncSetAttribute(attention_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 Cfg<HD>::SMEM_BYTES));
+    GB_CUDA(cudaFuncSetAttribute(attention_tcgen05_kernel<HD, KEYS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<HD, KEYS>::SMEM_BYTES));
     attr_set = true;
   }
-  gb_launch(attention_tcgen05_kernel<HD>, dim3(p.kv_heads, n_tiles), dim3(192), Cfg<HD>::SMEM_BYTES, stream, mq, mk,
-            mv, p);
+  gb_launch(attention_tcgen05_kernel<HD, KEYS>, dim3(p.kv_heads, n_tiles), dim3(192), Cfg<HD, KEYS>::SMEM_BYTES, stream,
+            mq, mk, mv, p);
   return GB_OK;
+}
+
+// Keys per tile.  At head_dim 128 a CTA of 128-key tiles has an SM to itself (161 KB of shared
+// memory); with 64-key tiles two fit, which is the faster way once the launch has several CTAs for
+// every SM (8,192 tokens x 16 / 4 heads: 335 us against 432 us; 4,096: 98 against 125; at 2,048, 260 CTAs, 50
+// against 40).  At head_dim 64 two CTAs fit either way and the wider tile is faster (462 us
+// against 567 us at 8,192 tokens x 32 / 8 heads).  GIBBS_B200_ATTN_KEYS=64|128 overrides.
+int keys_per_tile(int hd, int page_size, long long ctas) {
+  static const int forced = [] {
+    const char* e = getenv("GIBBS_B200_ATTN_KEYS");
+    return e ? atoi(e) : 0;
+  }();
+  if (page_size > 64) return 128;
+  if (forced == 64 || forced == 128) return forced;
+  return (hd == 128 && ctas >= 3 * 148) ? 64 : 128;
 }
 
 }  // namespace
@@ -532,7 +574,11 @@ GB_API int gb_attention_tcgen05(const void* q, long long ldq, const void* k_page
   // upper bound of the number of tiles: sum_r ceil(q_len_r / tpt) <= n_tokens / tpt + n_requests
   const long long n_tiles = ((long long)n_tokens + tpt - 1) / tpt + n_requests;
   if (n_tiles > 65535) GB_FAIL(GB_ERR_ARG, "gb_attention_tcgen05: %lld tiles in one launch", n_tiles);
-  const int rc = hd == 64 ? launch<64>(mq, mk, mv, p, (int)n_tiles, stream) : launch<128>(mq, mk, mv, p, (int)n_tiles, stream);
+  int rc;
+  if (keys_per_tile(hd, page_size, n_tiles * kv_heads) == 64)
+    rc = hd == 64 ? launch<64, 64>(mq, mk, mv, p, (int)n_tiles, stream) : launch<128, 64>(mq, mk, mv, p, (int)n_tiles, stream);
+  else
+    rc = hd == 64 ? launch<64, 128>(mq, mk, mv, p, (int)n_tiles, stream) : launch<128, 128>(mq, mk, mv, p, (int)n_tiles, stream);
   if (rc != GB_OK) return rc;
   GB_CHECK_LAUNCH("gb_attention_tcgen05");
   return 1;

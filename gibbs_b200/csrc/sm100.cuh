@@ -154,7 +154,7 @@ __device__ __forceinline__ void tmem_ld_32(uint32_t taddr, float* v) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
-// The same without waiting: the registers hold the data only after tmem_ld_wait_128 (which names
+// The same without waiting: the registers hold the data only after tmem_ld_wait_n (which names
 // them, so that nothing that reads them can be moved above the wait).
 __device__ __forceinline__ void tmem_ld_32_issue(uint32_t taddr, float* v) {
   asm volatile(
@@ -167,11 +167,12 @@ __device__ __forceinline__ void tmem_ld_32_issue(uint32_t taddr, float* v) {
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void tmem_ld_wait_128(float* v) {
+template <int N>
+__device__ __forceinline__ void tmem_ld_wait_n(float* v) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-  // an empty statement that "rewrites" all 128 registers: uses of them stay below the wait
+  // an empty statement that "rewrites" all N registers: uses of them stay below the wait
 #pragma unroll
-  for (int i = 0; i < 128; i += 16)
+  for (int i = 0; i < N; i += 16)
     asm volatile("" : "+f"(v[i]), "+f"(v[i + 1]), "+f"(v[i + 2]), "+f"(v[i + 3]), "+f"(v[i + 4]), "+f"(v[i + 5]),
                       "+f"(v[i + 6]), "+f"(v[i + 7]), "+f"(v[i + 8]), "+f"(v[i + 9]), "+f"(v[i + 10]), "+f"(v[i + 11]),
                       "+f"(v[i + 12]), "+f"(v[i + 13]), "+f"(v[i + 14]), "+f"(v[i + 15]));
