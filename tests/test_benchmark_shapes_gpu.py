@@ -130,13 +130,15 @@ class _Hints:
         self.max_ctx_len = max(a + b for a, b in zip(before, q_lens))
 
 
-@pytest.mark.parametrize("heads,kvh,start,n", [(32, 8, 0, 2048), (32, 8, 2048, 2048), (24, 8, 100, 2000)])
-def test_prompt_attention_at_2048_tokens(heads, kvh, start, n):
+@pytest.mark.parametrize("heads,kvh,start,n,hd", [(32, 8, 0, 2048, 64), (32, 8, 2048, 2048, 64), (24, 8, 100, 2000, 64),
+                                                  (16, 4, 0, 4096, 128), (16, 4, 1000, 1100, 128)])
+def test_prompt_attention_at_2048_tokens(heads, kvh, start, n, hd):
     """The tcgen05 kernel with 16 (and 32) key tiles a CTA over 8 kv heads, pages in a random
-    order; one key far back is made dominant for the last token of the portion."""
+    order; one key far back is made dominant for the last token of the portion.  Head size 128:
+    a launch of more than 444 CTAs, which takes key tiles of 64, and one below, with tiles of 128."""
     from gibbs_b200 import ops
     torch.manual_seed(heads + start)
-    hd, ps = 64, 16
+    ps = 16
     total = start + n
     nb = -(-total // ps)
     perm = torch.randperm(nb + 5)[:nb]

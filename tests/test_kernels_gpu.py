@@ -564,6 +564,8 @@ TC_CASES = [
     (12, 2, 128, 32, 100, [200, 0], [150, 43]),
     (7, 1, 64, 8, 0, [0, 129], [130, 19]),
     (12, 1, 64, 64, 0, [5], [77]),
+    # head size 128 in a launch of more than 444 CTAs: key tiles of 64, two CTAs per SM; a window
+    (64, 4, 128, 32, 40, [100, 0], [500, 420]),
 ]
 
 
