@@ -117,11 +117,15 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--workload", choices=["serve700m", "long2p6b", "sweep"], default=None,
                     help="run one of the other reference workloads instead (prints its own JSON line)")
-    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "prefill-timeline", "products", "trace"], default=None,
+    ap.add_argument("--prompt-tokens", type=int, default=None,
+                    help="with --only prefill / prefill-timeline / products: another prompt length than 2,048")
+    ap.add_argument("--only", default=None,
+                    choices=["decode", "prefill", "timeline", "prefill-timeline", "products", "attention", "trace"],
                     help="measure one phase only (for short profiler captures; the line is then partial); "
                          "'timeline' / 'prefill-timeline': the kernels of one decode step inside its graph / of one "
                          "prompt step, from CUPTI; 'products': the prompt step's matrix products alone (with "
-                         "-DGB_PAIR_TRACE: and the phases inside the CTA-pair kernel); 'trace': time "
+                         "-DGB_PAIR_TRACE: and the phases inside the CTA-pair kernel); 'attention': the prompt attention "
+                         "kernel alone at 2,048 to 16,384 tokens; 'trace': time "
                          "stamps from inside a decode step's product kernels (a -DGB_GEMM_TRACE or -DGB_DECODE_TRACE build)")
     a = ap.parse_args()
     if a.impl == "reference":
@@ -148,8 +152,17 @@ def main():
     if a.dtype != "bfloat16" and a.only not in ("prefill", "decode"):
         print("bench.py: --dtype float32 goes with --only prefill or --only decode")
         return 2
+    prompt_tokens = PROMPT_LEN
+    if a.prompt_tokens is not None:
+        if a.only not in ("prefill", "prefill-timeline", "products") or not 1 <= a.prompt_tokens <= PROMPT_LEN:
+            print(f"bench.py: --prompt-tokens (1 to {PROMPT_LEN}) goes with --only prefill, prefill-timeline or products")
+            return 2
+        prompt_tokens = a.prompt_tokens
     if a.only == "products":
-        print(B.prompt_product_times(cfg, PROMPT_LEN, peaks["bf16_tflops"]))
+        print(B.prompt_product_times(cfg, prompt_tokens, peaks["bf16_tflops"]))
+        return 0
+    if a.only == "attention":
+        print(B.prompt_attention_times())
         return 0
     model = random_model(cfg, SEED, dtype=a.dtype, device="cuda:0", stored_dtype=torch.bfloat16)
 
@@ -160,14 +173,14 @@ def main():
     eng = gen.engine
 
     if a.only == "prefill":
-        pre = B.measure_prefill(eng, PROMPT_LEN, warmup=a.warmup, runs=a.steps, seed=SEED)
+        pre = B.measure_prefill(eng, prompt_tokens, warmup=a.warmup, runs=a.steps, seed=SEED)
         print(json.dumps({"partial": "prefill", "dtype": a.dtype, "prefill": pre}))
         return 0
     if a.only == "timeline":
         print(B.format_timeline(B.decode_timeline(eng, a.batch, PROMPT_LEN, seed=SEED)))
         return 0
     if a.only == "prefill-timeline":
-        print(B.format_timeline(B.prefill_timeline(eng, PROMPT_LEN, seed=SEED), "prompt"))
+        print(B.format_timeline(B.prefill_timeline(eng, prompt_tokens, seed=SEED), "prompt"))
         return 0
     if a.only == "trace":
         print(B.decode_kernel_trace(eng, a.batch, PROMPT_LEN, seed=SEED))

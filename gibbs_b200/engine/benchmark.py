@@ -403,6 +403,48 @@ def prompt_product_times(cfg, n_tokens: int, peak_tflops: float, device="cuda:0"
     return "\n".join(lines)
 
 
+def prompt_attention_times(lengths=(2048, 4096, 8192, 16384), shapes=((32, 8, 64), (16, 4, 128)), page_size: int = 16,
+                           device="cuda:0") -> str:
+    """The attention kernel of a prompt alone: one request of n tokens from position 0, pages in a
+    random order, twenty launches back to back; for every (heads, kv heads, head size) and length
+    the time of a launch and the rate of its products (the causal half: 2 n (n + 1) heads head_size
+    flops)."""
+    import types
+    from .. import ops
+    gen = torch.Generator(device=device).manual_seed(0)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=device)
+    lines = []
+    for heads, kvh, hd in shapes:
+        for n in lengths:
+            nb = -(-n // page_size)
+            kp = (torch.randn(nb, kvh, page_size, hd, device=device, generator=gen) * 0.5).bfloat16()
+            vp = torch.randn(nb, kvh, page_size, hd, device=device, generator=gen).bfloat16()
+            q = (torch.randn(n, heads * hd, device=device, generator=gen) * 0.5).bfloat16()
+            out = torch.empty_like(q)
+            status = torch.zeros(1, dtype=torch.int32, device=device)
+            table = torch.randperm(nb, device=device, generator=gen).to(torch.int32)[None, :].contiguous()
+            tok_req, tok_pos = torch.zeros(n, dtype=torch.int32, device=device), torch.arange(n, dtype=torch.int32, device=device)
+            step = types.SimpleNamespace(n_requests=1, q_start=i32([0]), q_len=i32([n]), start_pos=i32([0]),
+                                         max_q_len=n, max_ctx_len=n)
+            run = lambda: ops.paged_attention(q, heads, kvh, hd, kp, vp, table, tok_req, tok_pos, hd ** -0.5, 0, out,
+                                              status, hints=step)
+            for _ in range(3):
+                run()
+            torch.cuda.synchronize()
+            e0, e1 = _events()
+            e0.record()
+            for _ in range(20):
+                run()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) / 20 * 1e3
+            if int(status.item()):
+                raise RuntimeError(f"attention reported status {int(status.item())}")
+            flops = 2.0 * n * (n + 1) * heads * hd
+            lines.append(f"{heads:3d} / {kvh} heads of {hd:3d}, {n:6d} tokens: {us:8.1f} us  {flops / us / 1e6:6.0f} TFLOP/s")
+    return "\n".join(lines)
+
+
 def format_timeline(rows, what: str = "decode") -> str:
     short = lambda n: n.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0]
     span = max(r[2] + r[3] for r in rows)
