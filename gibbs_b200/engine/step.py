@@ -111,7 +111,10 @@ class StepBuilder:
             o += _align4(sz)
         return offs, o
 
-    def _fill_staging(self, entries, rcs, offs, n_tok, n_req, n_want, fed_from=None, mb: Optional[int] = None) -> int:
+    def _fill_staging(self, entries, rcs, offs, n_tok, n_req, n_want, fed_from=None, mb: Optional[int] = None,
+                      token_arrays=None) -> int:
+        """``token_arrays``: the entries' token ids as integer arrays, where the caller has made
+        them already (a list of thousands of ids is converted once, not once to check and once to copy)."""
         turn = self._turn
         self._turn = (turn + 1) % len(self._staging)
         if self._staging_evt[turn] is not None:
@@ -123,7 +126,7 @@ class StepBuilder:
         row, w_i = 0, 0
         for r, (e, rc) in enumerate(zip(entries, rcs)):
             n = len(e.tokens)
-            ids[row:row + n] = e.tokens
+            ids[row:row + n] = e.tokens if token_arrays is None else token_arrays[r]
             treq[row:row + n] = r
             tpos[row:row + n] = np.arange(rc.length, rc.length + n, dtype=np.int32)
             qs[r], ql[r], sp[r], cl[r] = row, n, rc.length, rc.length + n
@@ -254,6 +257,7 @@ class Engine:
             raise StepError("a step needs at least one entry")
         seen = set()
         total = 0
+        arrays = []
         for e in entries:
             if e.request_id in seen:
                 raise StepError(f"request {e.request_id!r} appears twice in one step")
@@ -263,10 +267,20 @@ class Engine:
             n = len(e.tokens)
             if n == 0:
                 raise StepError(f"request {e.request_id!r} brings no tokens")
-            bad = [t for t in e.tokens if not 0 <= int(t) < self.vocab_size]
-            if bad:
-                raise StepError(f"request {e.request_id!r}: token id {bad[0]} outside the vocabulary of "
+            if n <= 32:
+                # (a decoded token or a short portion: cheaper to look at than to turn into an array)
+                ids = e.tokens
+                bad = [t for t in ids if not 0 <= int(t) < self.vocab_size]
+            else:
+                ids = np.asarray(e.tokens)
+                if ids.ndim != 1 or ids.dtype.kind not in "iu":
+                    raise StepError(f"request {e.request_id!r}: token ids are a flat sequence of integers")
+                bad = ids[(ids < 0) | (ids >= self.vocab_size)] if int(ids.min()) < 0 or int(ids.max()) >= self.vocab_size \
+                    else ()
+            if len(bad):
+                raise StepError(f"request {e.request_id!r}: token id {int(bad[0])} outside the vocabulary of "
                                 f"{self.vocab_size}")
+            arrays.append(ids)
             for w in e.want:
                 if not 0 <= int(w) < n:
                     raise StepError(f"request {e.request_id!r}: wanted place {w} outside its {n} tokens")
@@ -279,7 +293,7 @@ class Engine:
             raise StepError(f"{len(entries)} requests in one step; the engine was made for {self.max_requests}")
         if total > self.max_step_tokens:
             raise StepError(f"{total} tokens in one step; the engine was made for {self.max_step_tokens}")
-        return total
+        return total, arrays
 
     def step(self, entries: Sequence[StepEntry], feed=None) -> Optional[torch.Tensor]:
         """Run one batch.  Returns float32 logits [number of wanted places,
@@ -298,7 +312,7 @@ class Engine:
         batch size; its logits live in the graph's own buffer and are
         overwritten by the next decode step of the same size."""
         entries = list(entries)
-        n_tok = self._validate(entries)
+        n_tok, token_arrays = self._validate(entries)
         fed_from = None
         if feed is not None:
             picked, fed_from = feed[0], [int(f) for f in feed[1]]
@@ -311,7 +325,8 @@ class Engine:
         rcs = [self.cache.live[e.request_id] for e in entries]
         self.cache.reserve_all([(rc, rc.length + len(e.tokens)) for e, rc in zip(entries, rcs)])
         try:
-            logits = self._launch(entries, rcs, n_tok, fed_from, picked if fed_from is not None else None)
+            logits = self._launch(entries, rcs, n_tok, fed_from, picked if fed_from is not None else None,
+                                  token_arrays)
         except BaseException:
             # nothing was advanced: the pages taken for this step go back, and the caller sees
             # the requests as they stood before it
@@ -323,7 +338,7 @@ class Engine:
         self.steps_run += 1
         return logits
 
-    def _launch(self, entries, rcs, n_tok, fed_from, picked):
+    def _launch(self, entries, rcs, n_tok, fed_from, picked, token_arrays=None):
         """Metadata, transfer and kernels of one step whose pages are reserved."""
         n_req = len(entries)
         n_want = sum(len(e.want) for e in entries)
@@ -334,7 +349,7 @@ class Engine:
         mb = self.cache.max_blocks if decode else \
             max(1, max(self.cache.pages_needed(rc.length + len(e.tokens)) for e, rc in zip(entries, rcs)))
         offs, total = bld._layout(n_tok, n_req, n_want, fed_from is not None, mb)
-        turn = bld._fill_staging(entries, rcs, offs, n_tok, n_req, n_want, fed_from, mb)
+        turn = bld._fill_staging(entries, rcs, offs, n_tok, n_req, n_want, fed_from, mb, token_arrays)
 
         def fed(dev):
             if fed_from is not None:

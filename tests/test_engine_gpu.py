@@ -126,6 +126,34 @@ def test_step_plan_gives_the_same_bits_as_the_parts_forward(tmp_path_factory, na
             assert np.array_equal(pb[rid], fb[rid]), rid
 
 
+def test_token_ids_are_checked_before_anything_changes(tmp_path_factory):
+    """A token id outside the vocabulary, in a short portion or a long one, as a list or as an
+    array, is refused with its value; the request stays as it was and the same tokens given as a
+    list and as an array give the same logits."""
+    from gibbs_b200 import Engine
+    from gibbs_b200.engine.step import StepEntry, StepError
+    folder, model = _setup(tmp_path_factory, "A", "float32")
+    vocab = TINY["A"][0]["vocab_size"]
+    eng = Engine(model, n_pages=16, page_size=16, max_requests=2)
+    eng.open("a")
+    free = eng.cache.free_pages()
+    good = random_ids(11, 70, vocab)
+    for bad_ids, value in (([3, vocab, 5], vocab), ([-1], -1), (good[:40] + [vocab + 7] + good[40:], vocab + 7),
+                           (np.array(good[:50] + [-3], dtype=np.int64), -3)):
+        with pytest.raises(StepError, match=f"token id {value} outside the vocabulary"):
+            eng.step([StepEntry("a", bad_ids, [0])])
+        assert eng.length("a") == 0 and eng.cache.free_pages() == free
+    with pytest.raises(StepError, match="integers"):
+        eng.step([StepEntry("a", [0.5] * 40, [0])])
+    first = eng.step([StepEntry("a", good, [69])]).clone()
+    eng.close("a")
+    eng.open("b")
+    second = eng.step([StepEntry("b", np.array(good, dtype=np.int32), [69])])
+    assert torch.equal(first, second)
+    eng.close("b")
+    eng.cache.check()
+
+
 @pytest.mark.parametrize("use_graphs", [True, False])
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_tokens_fed_from_the_device_equal_tokens_given_by_the_host(tmp_path_factory, dtype, use_graphs):
