@@ -123,7 +123,6 @@ __global__ void short_conv_out_run_kernel(const bf16* bcx, long long ld, const f
                                           bf16* __restrict__ out, int n_tokens, int hidden) {
   constexpr int RUN = 8;
   pdl_trigger();
-  pdl_wait();
   const int groups = hidden >> 3;
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long n_runs = ((long long)n_tokens + RUN - 1) / RUN;
@@ -146,12 +145,29 @@ __global__ void short_conv_out_run_kernel(const bf16* bcx, long long ld, const f
     bs[e] = bias ? bias[c + e] : 0.f;
   }
   float win[K][8];                                           // win[j]: the product that meets tap j for the current token
-  int cur_req = -1, first = 0;
   const int t0 = run * RUN, t1 = min(t0 + RUN, n_tokens);
-  // All rows of the run are requested before the first is used (a thread that fetched them token
-  // by token would spend eight memory latencies one after the other).
-  uint4 rb[RUN], rx[RUN], rg[RUN];
+  // Taps, bias and the step's metadata (which request a token belongs to, where the request starts
+  // in the batch, its state slot) do not come from the product in front: they are read before the
+  // wait for it.  Behind the wait all rows of the run, and the K-1 older positions of its first
+  // token, are requested before the first is used (a thread that fetched them one by one would spend
+  // as many memory latencies one after the other).
   int rreq[RUN];
+#pragma unroll
+  for (int u = 0; u < RUN; ++u) rreq[u] = tok_req[t0 + u < t1 ? t0 + u : t1 - 1];
+  int cur_req = rreq[0], first = q_start[cur_req];
+  const float* st0 = state + (size_t)slot_ids[cur_req] * slot_stride;
+  gb_pin(first);
+  gb_pin(st0);
+#pragma unroll
+  for (int u = 0; u < RUN; ++u) gb_pin(rreq[u]);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+#pragma unroll
+    for (int j = 0; j < K; ++j) gb_pin(tap[j][e]);
+    gb_pin(bs[e]);
+  }
+  pdl_wait();
+  uint4 rb[RUN], rx[RUN], rg[RUN];
 #pragma unroll
   for (int u = 0; u < RUN; ++u) {
     const int t = t0 + u < t1 ? t0 + u : t1 - 1;
@@ -159,14 +175,46 @@ __global__ void short_conv_out_run_kernel(const bf16* bcx, long long ld, const f
     rb[u] = __ldcg(reinterpret_cast<const uint4*>(row + c));
     rx[u] = __ldcg(reinterpret_cast<const uint4*>(row + 2 * hidden + c));
     rg[u] = __ldcg(reinterpret_cast<const uint4*>(row + hidden + c));
-    rreq[u] = tok_req[t];
+  }
+  {
+    // the K-1 older positions of the run's first token: earlier tokens of its request in the batch, or its state
+    const int i0 = t0 - first;
+    uint4 ob[K - 1], ox[K - 1];
+#pragma unroll
+    for (int j = 0; j < K - 1; ++j) {
+      const int src = i0 - (K - 1 - j);
+      if (src >= 0) {
+        const bf16* prow = bcx + (size_t)(first + src) * ld;
+        ob[j] = __ldcg(reinterpret_cast<const uint4*>(prow + c));
+        ox[j] = __ldcg(reinterpret_cast<const uint4*>(prow + 2 * hidden + c));
+      } else {
+        const uint4* sp = reinterpret_cast<const uint4*>(st0 + (size_t)(K - 1 + src) * hidden + c);
+        ob[j] = __ldcg(sp);
+        ox[j] = __ldcg(sp + 1);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < K - 1; ++j) {
+      if (i0 - (K - 1 - j) >= 0) {
+        float pb[8], px[8];
+        unpack(ob[j], pb);
+        unpack(ox[j], px);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) win[j][e] = pb[e] * px[e];
+      } else {
+        win[j][0] = __uint_as_float(ob[j].x); win[j][1] = __uint_as_float(ob[j].y);
+        win[j][2] = __uint_as_float(ob[j].z); win[j][3] = __uint_as_float(ob[j].w);
+        win[j][4] = __uint_as_float(ox[j].x); win[j][5] = __uint_as_float(ox[j].y);
+        win[j][6] = __uint_as_float(ox[j].z); win[j][7] = __uint_as_float(ox[j].w);
+      }
+    }
   }
 #pragma unroll
   for (int u = 0; u < RUN; ++u) {
     const int t = t0 + u;
     if (t >= t1) break;
     const int r = rreq[u];
-    bool restart = r != cur_req;
+    const bool restart = r != cur_req;                       // (never the run's first token: it is prepared above)
     if (restart) {
       cur_req = r;
       first = q_start[r];
