@@ -104,6 +104,55 @@ def test_mixed_batches_with_page_reuse(tmp_path_factory, name, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_random_mixed_traces_without_a_host_wait_between_steps(tmp_path_factory, name, dtype):
+    """The traces above look at the device's status after every step, which makes the host wait for
+    the step.  Here step follows step as a scheduler launches them (the kernels of a step start while
+    the kernel in front still runs, and read what earlier steps left before their dependency is met):
+    random requests (lengths at the edges of pages), page sizes and pool sizes, with and without
+    decode graphs and the step plan; the logits are collected on the device and compared at the end."""
+    from gibbs_b200 import Engine, StepEntry
+    folder, model = _setup(tmp_path_factory, name, dtype)
+    vocab = TINY[name][0]["vocab_size"]
+    for seed in range(1, 13):
+        rng = np.random.default_rng(1000 * seed + ord(name))
+        lens = [int(rng.choice([1, 2, 15, 16, 17, 31, 33, 63, 64, 65, 100, 129, 200, 257]))
+                for _ in range(int(rng.integers(3, 8)))]
+        reqs = {f"s{seed}r{i}": random_ids(seed * 100 + i, n, vocab) for i, n in enumerate(lens)}
+        page = int(rng.choice([8, 16, 32]))
+        cap = max(-(-max(lens) // 64) * 64 + 64, int(rng.choice([192, 320, 448])))
+        steps = trace_mixed(reqs, capacity_tokens=cap, max_live=4, seed=seed)
+        eng = Engine(model, n_pages=cap // page + 4, page_size=page, max_requests=4,
+                     use_graphs=bool(rng.integers(0, 2)), use_plan=bool(rng.integers(0, 4)))
+        outs = []
+        for s in steps:
+            for ent in s["entries"]:
+                if not eng.is_live(ent["id"]):
+                    eng.open(ent["id"])
+            bases = {ent["id"]: eng.length(ent["id"]) for ent in s["entries"]}
+            logits = eng.step([StepEntry(ent["id"], ent["tokens"], ent["want"]) for ent in s["entries"]])
+            if logits is not None:
+                outs.append((s, bases, logits.clone()))      # (a decode graph's logits are overwritten by its next replay)
+            for rid in s["end"]:
+                eng.close(rid)
+        torch.cuda.synchronize()
+        eng.check_status()
+        eng.cache.check()
+        got = {}
+        for s, bases, logits in outs:
+            arr, row = logits.cpu().numpy(), 0
+            for ent in s["entries"]:
+                for w in ent["want"]:
+                    got.setdefault(ent["id"], {})[bases[ent["id"]] + w] = arr[row]
+                    row += 1
+        what = f"seed {seed}, pages of {page}, {cap} tokens, graphs {eng.use_graphs}, plan {eng.plan is not None}"
+        for rid, ids in reqs.items():
+            assert sorted(got[rid]) == list(range(len(ids))), (what, rid)
+            bad = first_wrong(np.stack([got[rid][p] for p in range(len(ids))]), plain_logits(folder, ids), TOL[dtype])
+            assert bad is None, f"{what}: request {rid} of {len(ids)}: first wrong position {bad[0]} (rel err {bad[1]:.3g})"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_step_plan_gives_the_same_bits_as_the_parts_forward(tmp_path_factory, name, dtype):
     """The same model stepped through the C walker of its plan and through the parts' forward
     methods: one sequence of kernels either way, so the logits are equal bit for bit, under mixed
