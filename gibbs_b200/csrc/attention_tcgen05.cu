@@ -125,23 +125,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   // tiles of every head start first.
   const int kvh = blockIdx.x;
 
-  // which request and which of its tiles: heaviest first (last request, last tile first)
+  // Which request and which of its tiles: heaviest first (last request, last tile first).  The
+  // three numbers of a request are asked for together, and the barriers are set up while the first
+  // request's are on their way: a CTA's start is a chain of trips to memory (these numbers, the
+  // block table, the first tiles), and a quarter of all CTA time at 2,048 tokens.
   int r = p.n_requests - 1, tile = (int)blockIdx.y, found = 0;
-  for (; r >= 0; --r) {
-    const int nt = (p.q_len[r] + tpt - 1) / tpt;
-    if (tile < nt) { found = 1; tile = nt - 1 - tile; break; }
-    tile -= nt;
-  }
-  if (!found) return;
-  const int qlen = p.q_len[r], first_tok = tile * tpt;
-  const int n_tok = min(tpt, qlen - first_tok);
-  const int row0 = p.q_start[r] + first_tok;                   // batch row of the tile's first token
-  const int pos0 = p.start_pos[r] + first_tok;                 // its position
-  const int hi_all = pos0 + n_tok;                             // keys < hi_all may be visible
-  const int lo_all = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
-  const int t_lo = lo_all / KEYS, t_hi = (hi_all + KEYS - 1) / KEYS;
-  const int n_tiles = t_hi - t_lo;
-
+  int qlen = p.q_len[r], qstart = p.q_start[r], spos = p.start_pos[r];
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
     for (int s = 0; s < RING; ++s) {
@@ -160,9 +149,43 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     tma_prefetch_desc(&map_k);
     tma_prefetch_desc(&map_v);
   }
+  for (;;) {
+    const int nt = (qlen + tpt - 1) / tpt;
+    if (tile < nt) { found = 1; tile = nt - 1 - tile; break; }
+    tile -= nt;
+    if (--r < 0) break;
+    qlen = p.q_len[r], qstart = p.q_start[r], spos = p.start_pos[r];
+  }
+  if (!found) return;
+  const int first_tok = tile * tpt;
+  const int n_tok = min(tpt, qlen - first_tok);
+  const int row0 = qstart + first_tok;                         // batch row of the tile's first token
+  const int pos0 = spos + first_tok;                           // its position
+  const int hi_all = pos0 + n_tok;                             // keys < hi_all may be visible
+  const int lo_all = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
+  const int t_lo = lo_all / KEYS, t_hi = (hi_all + KEYS - 1) / KEYS;
+  const int n_tiles = t_hi - t_lo;
+
   if (warp == 1) {
     tmem_alloc(&tmem_slot, C::TMEM_COLS);
     tmem_relinquish();
+  }
+  // The producer's first page ids (the block table is part of the step's metadata, in place before
+  // the step's first kernel): asked for here, so that they arrive while the CTA sets up.
+  const int* bt = p.block_table + (size_t)r * p.bt_stride;
+  const int pages_per_tile = KEYS / p.page_size;
+  constexpr int OUTSIDE = -0x7fffffff;
+  auto lookup = [&](int t) {
+    if (lane >= pages_per_tile) return OUTSIDE;
+    const int j0 = t * KEYS + lane * p.page_size;              // first key of this page slot
+    return (j0 < hi_all && j0 + p.page_size > lo_all) ? bt[j0 / p.page_size] : OUTSIDE;
+  };
+  int first_page = 0, page_cur = OUTSIDE;
+  if (warp == 0) {
+    first_page = bt[lo_all / p.page_size];
+    page_cur = t_lo < t_hi ? lookup(t_lo) : OUTSIDE;
+    gb_pin(first_page);                                        // (stay in front of the waits below, see gb_pin)
+    gb_pin(page_cur);
   }
   if (group * tpt < ROWS) {
     // A group that does not divide 128 (3, 5, 6, 7, ...) leaves the tile's last rows without a
@@ -189,20 +212,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       for (int sub = 0; sub < C::SUB; ++sub)
         tma_load_3d(sq + (size_t)sub * ROWS * 128, &map_q, sub * 64, kvh * group, row0, &q_full);
     }
-    const int* bt = p.block_table + (size_t)r * p.bt_stride;
-    const int pages_per_tile = KEYS / p.page_size;
     const int page_bytes = p.page_size * 128;                  // of one 64-column sub-tile
-    const int first_page = bt[lo_all / p.page_size];
     // Lane i brings page slot i of every tile (at most 16 slots).  Its page id for the next tile is
     // read from the block table while this tile's copies are requested, and serves K and V alike: the
     // table is not read between a buffer falling free and its copy going out.
-    constexpr int OUTSIDE = -0x7fffffff;
-    auto lookup = [&](int t) {
-      if (lane >= pages_per_tile) return OUTSIDE;
-      const int j0 = t * KEYS + lane * p.page_size;            // first key of this page slot
-      return (j0 < hi_all && j0 + p.page_size > lo_all) ? bt[j0 / p.page_size] : OUTSIDE;
-    };
-    int page_cur = t_lo < t_hi ? lookup(t_lo) : OUTSIDE;
     int it = 0;
     for (int t = t_lo; t < t_hi && !abort_flag; ++t) {
       const int page_next = t + 1 < t_hi ? lookup(t + 1) : OUTSIDE;
