@@ -246,6 +246,60 @@ def test_two_layers_at_benchmark_widths_whole_cut_and_decoded(tmp_path, name):
         assert np.array_equal(b16, got["bfloat16", False, how]), (name, how)
 
 
+@pytest.mark.parametrize("name", ["1.2B", "700M"])
+def test_random_mixed_batches_at_benchmark_widths(tmp_path, name):
+    """Up to four live requests of 13 to 712 tokens, portions of some beside decoded tokens of others,
+    in a pool so small that pages are used again, with and without decode graphs and the step plan,
+    step after step without a host wait: the bfloat16 engine's logits at the last place of every
+    portion against the float32 engine running each request whole."""
+    from gibbs_b200 import Engine, StepEntry, load_model
+    from helpers import trace_mixed
+    folder = _wide_folder(tmp_path, name)
+    m32, m16 = load_model(folder, dtype="float32"), load_model(folder, dtype="bfloat16")
+    for seed in range(1, 7):
+        rng = np.random.default_rng(seed)
+        lens = [int(rng.choice([1, 2, 33, 64, 100, 129, 255, 256, 257, 400, 513, 700])) + 12
+                for _ in range(int(rng.integers(3, 7)))]
+        reqs = {f"s{seed}r{i}": random_ids(seed * 100 + i, n, 65536) for i, n in enumerate(lens)}
+        cap = max(-(-max(lens) // 64) * 64 + 64, int(rng.choice([512, 896, 1408])))
+        steps = trace_mixed(reqs, capacity_tokens=cap, max_live=4, seed=seed)
+        for s in steps:
+            for e in s["entries"]:
+                e["want"] = e["want"][-1:]
+        eng = Engine(m16, n_pages=cap // 16 + 4, page_size=16, max_requests=4, max_step_tokens=2048,
+                     use_graphs=bool(seed & 1), use_plan=seed != 4)
+        got = {}
+        for s in steps:
+            for ent in s["entries"]:
+                if not eng.is_live(ent["id"]):
+                    eng.open(ent["id"])
+            bases = {ent["id"]: eng.length(ent["id"]) for ent in s["entries"]}
+            logits = eng.step([StepEntry(ent["id"], ent["tokens"], ent["want"]) for ent in s["entries"]])
+            if logits is not None:
+                logits, row = logits.clone(), 0
+                for ent in s["entries"]:
+                    for w in ent["want"]:
+                        got.setdefault(ent["id"], {})[bases[ent["id"]] + w] = logits[row]
+                        row += 1
+            for rid in s["end"]:
+                eng.close(rid)
+        torch.cuda.synchronize()
+        eng.check_status()
+        eng.cache.check()
+        del eng
+        ref = Engine(m32, n_pages=max(lens) // 16 + 4, page_size=16, max_requests=1, max_step_tokens=2048)
+        for rid, ids in reqs.items():
+            places = sorted(got[rid])
+            ref.open(rid)
+            want = ref.step([StepEntry(rid, ids, places)]).double()
+            ref.close(rid)
+            have = torch.stack([got[rid][p] for p in places]).double()
+            err = (have - want).norm(dim=-1) / (want.norm(dim=-1) + 1e-30)
+            assert float(err.max()) < TOL["bfloat16"], \
+                f"seed {seed}: request {rid} of {len(ids)}, place {places[int(err.argmax())]}: rel err {float(err.max()):.3g}"
+        del ref
+
+
 # --------------------------------------------------------------------------- the whole benchmark model and its 32-bit twin
 def test_full_size_model_in_bfloat16_against_its_float32_twin():
     """All 16 layers of the LFM2-1.2B shape with random bfloat16 weights: the bfloat16 engine against
